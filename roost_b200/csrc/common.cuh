@@ -1,0 +1,94 @@
+// Shared helpers of the kernel library: status reporting, dtype load/store, block reductions.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string>
+
+#include "roost_kernels.h"
+
+namespace roost {
+
+void set_error(const std::string& msg);
+
+inline int fail(int code, const std::string& msg) {
+  set_error(msg);
+  return code;
+}
+
+inline int check_launch(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    return fail(ROOST_ERR_CUDA, std::string(what) + ": " + cudaGetErrorString(e));
+  }
+  return ROOST_OK;
+}
+
+#define ROOST_REQUIRE(cond, msg)                           \
+  do {                                                     \
+    if (!(cond)) return ::roost::fail(ROOST_ERR_INVALID, (msg)); \
+  } while (0)
+
+__device__ __forceinline__ float to_float(float v) { return v; }
+__device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T>
+__device__ __forceinline__ T from_float(float v);
+template <>
+__device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// Weight vectors (norm weights) may be stored in either dtype whatever the activations are.
+__device__ __forceinline__ float load_w(const void* w, int i, int wdtype) {
+  return wdtype == ROOST_F32 ? reinterpret_cast<const float*>(w)[i]
+                             : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(w)[i]);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over a block of up to 1024 threads; the order of additions depends on the block size only, so a row's
+// result does not depend on which other rows are in the launch. scratch: 32 floats of shared memory.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  const int nwarps = (blockDim.x + 31) >> 5;
+  float t = (threadIdx.x < nwarps) ? scratch[threadIdx.x] : 0.f;
+  if (warp == 0) {
+    t = warp_sum(t);
+    if (lane == 0) scratch[0] = t;
+  }
+  __syncthreads();
+  return scratch[0];
+}
+
+}  // namespace roost
+
+// Dispatch on an activation dtype code.
+#define ROOST_DISPATCH_DTYPE(code, T, ...)                                                   \
+  do {                                                                                       \
+    if ((code) == ROOST_F32) {                                                               \
+      using T = float;                                                                       \
+      __VA_ARGS__;                                                                           \
+    } else if ((code) == ROOST_BF16) {                                                       \
+      using T = __nv_bfloat16;                                                               \
+      __VA_ARGS__;                                                                           \
+    } else {                                                                                 \
+      return ::roost::fail(ROOST_ERR_INVALID, "dtype code is neither float32 (0) nor bfloat16 (1)"); \
+    }                                                                                        \
+  } while (0)

@@ -1,0 +1,90 @@
+/* roost_b200 kernel library: the C ABI.
+ *
+ * Every entry point is a plain C function that takes device pointers, sizes and a CUDA stream, launches on
+ * that stream and returns a status; nothing here allocates device memory or synchronises. The reference puts
+ * its kernels behind a versioned C ABI with status codes and per-op entry points
+ * (kernels/include/roost_kernels.h:55-72,107-164,244-262); this is the same boundary with this engine's own
+ * op set. A caller checks roost_abi_version() first.
+ *
+ * dtype codes: 0 = float32, 1 = bfloat16. All index tables are int32. Matrices are row-major.
+ */
+#ifndef ROOST_B200_KERNELS_H
+#define ROOST_B200_KERNELS_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ROOST_ABI_VERSION 1
+
+#define ROOST_OK 0
+#define ROOST_ERR_INVALID 1      /* an argument is out of range or inconsistent; nothing was launched */
+#define ROOST_ERR_UNSUPPORTED 2  /* the sizes are valid but no kernel serves them; nothing was launched */
+#define ROOST_ERR_CUDA 3         /* the CUDA runtime reported an error at launch */
+
+#define ROOST_F32 0
+#define ROOST_BF16 1
+
+typedef void* roost_stream_t;
+
+int roost_abi_version(void);
+/* Message of the last non-OK status on this thread. */
+const char* roost_last_error(void);
+
+/* out[t,:] = table[ids[t],:]; an id outside [0, vocab) gives a zero row. */
+int roost_embedding(const void* table, const int32_t* ids, void* out, int tokens, int hidden, int vocab, int dtype,
+                    roost_stream_t stream);
+
+/* out[i,:] = x[r,:] / sqrt(mean(x[r,:]^2) + eps) * w, r = rows ? rows[i] : i. w has dtype wdtype. */
+int roost_rms_norm(const void* x, const void* w, void* out, const int32_t* rows, int n_out, int hidden, float eps,
+                   int dtype, int wdtype, roost_stream_t stream);
+
+/* s = residual[r,:] + x[r,:] rounded to dtype; out[i,:] = rms_norm(s). Without rows, residual[r,:] = s is
+ * written back (the running residual stream); with rows the residual is left as it is. */
+int roost_add_rms_norm(const void* x, void* residual, const void* w, void* out, const int32_t* rows, int n_out,
+                       int hidden, float eps, int dtype, int wdtype, roost_stream_t stream);
+
+/* out[t,i] = silu(x[t,i]) * x[t,inter+i], x: [tokens, 2*inter]. */
+int roost_silu_mul(const void* x, void* out, int tokens, int inter, int dtype, roost_stream_t stream);
+
+/* Per token and head: optional RMS norm over head_dim (q heads with q_w, k heads with k_w), NeoX rotation of
+ * the first rotary_dim elements by angle position * inv_freq[i] (inv_freq: double[rotary_dim/2]; rotary_dim 0
+ * = no rotation), then q to q_out[t, h, :], k and v into their page slot:
+ * pool[(page * kv_heads + h) * page_size + offset][:] with slot = page * page_size + offset from slot_mapping
+ * (a negative slot is skipped). qkv rows hold [q heads | k heads | v heads] with row stride qkv_stride
+ * elements; with write_kv 0 only the q part is read. */
+int roost_qk_norm_rope_cache(const void* qkv, int64_t qkv_stride, void* q_out, void* k_pool, void* v_pool,
+                             const void* q_w, const void* k_w, const double* inv_freq, const int32_t* positions,
+                             const int32_t* slot_mapping, int tokens, int q_heads, int kv_heads, int head_dim,
+                             int rotary_dim, float eps, int page_size, int64_t pool_pages, int write_kv, int dtype,
+                             int wdtype, roost_stream_t stream);
+
+/* Causal grouped-query attention over a paged cache, one query token per block and key/value head; 32-bit
+ * arithmetic throughout. Token t belongs to batch row token_row[t] and sits at absolute position
+ * positions[t]; it sees keys max(0, pos - window + 1) .. pos (window <= 0: from 0). Row b's pages are
+ * kv_indices[kv_indptr[b] ..]; key j lies in page j / page_size. */
+int roost_paged_attention_generic(const void* q, void* out, const void* k_pool, const void* v_pool,
+                                  const int32_t* positions, const int32_t* token_row, const int32_t* kv_indptr,
+                                  const int32_t* kv_indices, int tokens, int q_heads, int kv_heads, int head_dim,
+                                  int page_size, float scale, int window, int dtype, roost_stream_t stream);
+
+/* out[m,n] = sum_k a[m,k] * w[n,k], plain FFMA in 32-bit (no tensor cores, no reduced-precision mode), the
+ * sum over k in increasing order for every output, whatever m is. in_dtype/out_dtype: 0 or 1. */
+int roost_gemm_simt(const void* a, const void* w, void* out, int m, int n, int k, int64_t lda, int64_t ldw,
+                    int64_t ldo, int in_dtype, int out_dtype, roost_stream_t stream);
+
+/* ids[r] = index of the largest logit of row r, ties to the lowest index, NaN never chosen (-1 if none). */
+int roost_argmax(const float* logits, int64_t stride, int rows, int vocab, int32_t* ids, roost_stream_t stream);
+
+/* Temperature / top-k / top-p / min-p sampling with a Philox4x32-10 draw per row; see sampling.cu.
+ * workspace: rows * vocab floats. temperature <= 0 is greedy. */
+int roost_sample(const float* logits, int64_t stride, int rows, int vocab, const float* temperature,
+                 const int32_t* top_k, const float* top_p, const float* min_p, const uint64_t* seeds,
+                 const uint64_t* offsets, float* workspace, int32_t* ids, roost_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,395 @@
+// Greedy choice and temperature / top-k / top-p / min-p sampling on the device.
+//
+// The reference has no device sampler (src/Starlings.Roost.Worker/Eager/CudaOps.cs:293-332 falls back to the host);
+// its definition of the result is CpuOps.Sample (src/Starlings.Roost.Ops/CpuOps.Sampling.cs:10-46, :279-370) and
+// this kernel computes that result without sorting:
+//   * NaN and -inf logits are removed; temperature <= 0 picks the highest logit, ties to the lowest index;
+//   * p = softmax((z - max) / T); tokens are ordered by p descending, ties by lower index;
+//   * top-k keeps the first k of that order, top-p the shortest prefix whose mass reaches top_p * (kept mass),
+//     the crossing token included, min-p drops p < min_p * p_max;
+//   * u = Philox4x32-10(counter = (offset lo, offset hi, 0, 0), key = (seed lo, seed hi)) word 0, top 24 bits
+//     * 2^-24 (src/Starlings.Roost.Ops/CpuPhilox.cs:15-44); the chosen token is the first of the order whose
+//     running kept mass exceeds u * (kept mass), the last kept token if rounding leaves none.
+// A prefix of the order is the set {p > x} plus the first c tokens (by index) with p == x, so every step is a
+// search for x over the bit patterns of p (non-negative floats order like their bits), 32 passes over the row
+// with a block-wide sum each, and a count of ties. The sums run in a fixed order, so a row gives the same
+// token in any batch and on any run. Sums differ in rounding from the reference's sequential sums over a
+// sorted array: a draw within rounding of an interval's edge may fall to the neighbouring token.
+#include "common.cuh"
+
+namespace roost {
+
+constexpr int kThreads = 1024;
+
+__device__ __forceinline__ void philox4x32_10(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3, uint32_t k0, uint32_t k1,
+                                              uint32_t* r0) {
+  const uint32_t M0 = 0xD2511F53u, M1 = 0xCD9E8D57u, W0 = 0x9E3779B9u, W1 = 0xBB67AE85u;
+#pragma unroll
+  for (int i = 0; i < 10; ++i) {
+    const uint32_t hi0 = __umulhi(M0, c0), lo0 = M0 * c0;
+    const uint32_t hi1 = __umulhi(M1, c2), lo1 = M1 * c2;
+    c0 = hi1 ^ c1 ^ k0;
+    c1 = lo1;
+    c2 = hi0 ^ c3 ^ k1;
+    c3 = lo0;
+    k0 += W0;
+    k1 += W1;
+  }
+  *r0 = c0;
+}
+
+struct Scratch {
+  float f[32];
+  int i[32];
+  int idx[32];
+};
+
+__device__ __forceinline__ float block_sum_f(float v, Scratch* s) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) s->f[warp] = v;
+  __syncthreads();
+  float t = s->f[lane];  // kThreads / 32 == 32 warps
+  t = warp_sum(t);
+  return t;
+}
+
+__device__ __forceinline__ int block_sum_i(int v, Scratch* s) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  __syncthreads();
+  if (lane == 0) s->i[warp] = v;
+  __syncthreads();
+  int t = s->i[lane];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+  return t;
+}
+
+// (value, index) maximum with ties to the lower index; NaN and (optionally) -inf never win. Returns -1 when no
+// element qualifies.
+__device__ __forceinline__ int block_argmax(const float* z, int n, bool skip_neg_inf, float* best_out, Scratch* s) {
+  float bv = 0.f;
+  int bi = -1;
+  for (int v = threadIdx.x; v < n; v += kThreads) {
+    const float x = z[v];
+    if (x != x) continue;
+    if (skip_neg_inf && x == -INFINITY) continue;
+    if (bi < 0 || x > bv) {
+      bv = x;
+      bi = v;
+    }
+  }
+  auto better = [](float av, int ai, float cv, int ci) {
+    if (ci < 0) return true;
+    if (ai < 0) return false;
+    return av > cv || (av == cv && ai < ci);
+  };
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (!better(bv, bi, ov, oi)) {
+      bv = ov;
+      bi = oi;
+    }
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  __syncthreads();
+  if (lane == 0) {
+    s->f[warp] = bv;
+    s->idx[warp] = bi;
+  }
+  __syncthreads();
+  bv = s->f[lane];
+  bi = s->idx[lane];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (!better(bv, bi, ov, oi)) {
+      bv = ov;
+      bi = oi;
+    }
+  }
+  if (best_out) *best_out = bv;
+  return bi;
+}
+
+__global__ void __launch_bounds__(kThreads) argmax_kernel(const float* __restrict__ logits, int64_t stride, int vocab,
+                                                         int32_t* __restrict__ ids) {
+  __shared__ Scratch s;
+  const int r = blockIdx.x;
+  const int best = block_argmax(logits + (size_t)r * stride, vocab, false, nullptr, &s);
+  if (threadIdx.x == 0) ids[r] = best;
+}
+
+// The kept prefix: key > xb, or key == xb and fewer than c equal keys lie at lower indices.
+struct Prefix {
+  uint32_t xb;
+  int c;
+};
+
+// mass and count of {key > xb} over the row (keys of removed tokens are 0xFFFFFFFF-marked negatives, skipped).
+__device__ __forceinline__ void mass_count_gt(const float* p, int n, uint32_t xb, float* mass, int* count, Scratch* s) {
+  float m = 0.f;
+  int c = 0;
+  for (int v = threadIdx.x; v < n; v += kThreads) {
+    const float x = p[v];
+    if (x >= 0.f && __float_as_uint(x) > xb) {
+      m += x;
+      ++c;
+    }
+  }
+  *mass = block_sum_f(m, s);
+  *count = block_sum_i(c, s);
+}
+
+__device__ __forceinline__ int count_eq(const float* p, int n, uint32_t xb, Scratch* s) {
+  int c = 0;
+  for (int v = threadIdx.x; v < n; v += kThreads) {
+    const float x = p[v];
+    if (x >= 0.f && __float_as_uint(x) == xb) ++c;
+  }
+  return block_sum_i(c, s);
+}
+
+// Mass of {key >= b} within the prefix `in`.
+__device__ __forceinline__ float mass_ge_within(const float* p, int n, uint32_t b, Prefix in, Scratch* s) {
+  float m = 0.f;
+  for (int v = threadIdx.x; v < n; v += kThreads) {
+    const float x = p[v];
+    if (x >= 0.f) {
+      const uint32_t k = __float_as_uint(x);
+      if (k >= b && k > in.xb) m += x;
+    }
+  }
+  m = block_sum_f(m, s);
+  if (b <= in.xb) m += (float)in.c * __uint_as_float(in.xb);
+  return m;
+}
+
+// Index of the (r+1)-th token (by index) whose key equals xb; -1 if there are fewer.
+__device__ __forceinline__ int nth_equal(const float* p, int n, uint32_t xb, int r, Scratch* s, int* shared_result) {
+  const int chunk = (n + kThreads - 1) / kThreads;
+  const int lo = threadIdx.x * chunk, hi = min(n, lo + chunk);
+  int mine = 0;
+  for (int v = lo; v < hi; ++v) {
+    const float x = p[v];
+    if (x >= 0.f && __float_as_uint(x) == xb) ++mine;
+  }
+  // exclusive prefix over threads: warp scan, then scan of warp totals
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int inc = mine;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int t = __shfl_up_sync(0xffffffffu, inc, o);
+    if (lane >= o) inc += t;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) *shared_result = -1;
+  if (lane == 31) s->i[warp] = inc;
+  __syncthreads();
+  int before = 0;
+  for (int w2 = 0; w2 < warp; ++w2) before += s->i[w2];
+  before += inc - mine;
+  if (r >= before && r < before + mine) {
+    int seen = before;
+    for (int v = lo; v < hi; ++v) {
+      const float x = p[v];
+      if (x >= 0.f && __float_as_uint(x) == xb) {
+        if (seen == r) {
+          *shared_result = v;
+          break;
+        }
+        ++seen;
+      }
+    }
+  }
+  __syncthreads();
+  return *shared_result;
+}
+
+__global__ void __launch_bounds__(kThreads)
+    sample_kernel(const float* __restrict__ logits, int64_t stride, int vocab, const float* __restrict__ temperature,
+                  const int32_t* __restrict__ top_k, const float* __restrict__ top_p, const float* __restrict__ min_p,
+                  const uint64_t* __restrict__ seeds, const uint64_t* __restrict__ offsets, float* __restrict__ workspace,
+                  int32_t* __restrict__ ids) {
+  __shared__ Scratch s;
+  __shared__ int shared_result;
+  const int r = blockIdx.x;
+  const float* z = logits + (size_t)r * stride;
+  float* p = workspace + (size_t)r * vocab;
+  const float temp = temperature[r];
+
+  float zmax;
+  const int imax = block_argmax(z, vocab, true, &zmax, &s);
+  if (temp <= 0.f || imax < 0) {
+    if (threadIdx.x == 0) ids[r] = imax;
+    return;
+  }
+
+  // probabilities; removed tokens are marked -1
+  float part = 0.f;
+  for (int v = threadIdx.x; v < vocab; v += kThreads) {
+    const float x = z[v];
+    float e = -1.f;
+    if (x == x && x != -INFINITY) {
+      e = expf((x - zmax) / temp);
+      part += e;
+    }
+    p[v] = e;
+  }
+  const float total = block_sum_f(part, &s);
+  int allowed = 0;
+  for (int v = threadIdx.x; v < vocab; v += kThreads) {
+    const float e = p[v];
+    if (e >= 0.f) {
+      p[v] = e / total;
+      ++allowed;
+    }
+  }
+  allowed = block_sum_i(allowed, &s);
+  __syncthreads();
+  const float pmax = 1.0f / total;  // exp(0) / total
+
+  // the whole allowed set as a prefix: every key above 0, and all tokens whose probability underflowed to 0
+  Prefix keep;
+  keep.xb = 0u;
+  keep.c = count_eq(p, vocab, 0u, &s);
+  constexpr int kTopBit = 29;  // probabilities are at most 1 = 0x3F800000, so bits 31 and 30 of a key are 0
+
+  // top-k: the k-th largest key is the largest b with count(key >= b) >= k
+  const int k = top_k[r];
+  if (k > 0 && k < allowed) {
+    uint32_t b = 0u;
+    for (int bit = kTopBit; bit >= 0; --bit) {
+      const uint32_t trial = b | (1u << bit);
+      float m;
+      int c;
+      mass_count_gt(p, vocab, trial - 1u, &m, &c, &s);  // keys >= trial
+      if (c >= k) b = trial;
+    }
+    float m;
+    int above;
+    mass_count_gt(p, vocab, b, &m, &above, &s);
+    keep.xb = b;
+    keep.c = k - above;
+  }
+
+  // top-p: the crossing token's key is the largest b with (kept mass of keys >= b) >= top_p * kept mass
+  const float tp = top_p[r];
+  if (tp < 1.0f) {
+    const float kept_total = mass_ge_within(p, vocab, 0u, keep, &s);
+    const float bar = tp * kept_total;
+    uint32_t b = 0u;
+    for (int bit = kTopBit; bit >= 0; --bit) {
+      const uint32_t trial = b | (1u << bit);
+      if (mass_ge_within(p, vocab, trial, keep, &s) >= bar) b = trial;
+    }
+    if (b < keep.xb) b = keep.xb;
+    float gt_mass;
+    int gt_count;
+    mass_count_gt(p, vocab, b, &gt_mass, &gt_count, &s);
+    const float x = __uint_as_float(b);
+    const int ties = (b == keep.xb) ? keep.c : count_eq(p, vocab, b, &s);
+    int need = 1;
+    if (x > 0.f) {
+      need = (int)ceilf((bar - gt_mass) / x);
+      if (need < 1) need = 1;
+    }
+    if (need > ties) need = ties;
+    keep.xb = b;
+    keep.c = need;
+  }
+
+  // min-p: drop p < min_p * p_max; what stays is {key > bits(floor) - 1} when the prefix reached below the floor
+  const float mp = min_p[r];
+  if (mp > 0.f) {
+    const float floor_p = mp * pmax;
+    if (__uint_as_float(keep.xb) < floor_p) {
+      keep.xb = __float_as_uint(floor_p) - 1u;
+      keep.c = 0;
+    }
+  }
+
+  // the draw: the chosen token's key is the largest b with (kept mass of keys >= b) > u * kept mass
+  float above_mass;
+  int above;
+  mass_count_gt(p, vocab, keep.xb, &above_mass, &above, &s);
+  int chosen = -1;
+  if (above == 0 && keep.c == 0) {
+    chosen = imax;  // min-p above 1 left nothing: the reference keeps the first token of the order
+  } else {
+    const float mass = mass_ge_within(p, vocab, 0u, keep, &s);
+    uint32_t r0;
+    const uint64_t seed = seeds[r], off = offsets[r];
+    philox4x32_10((uint32_t)off, (uint32_t)(off >> 32), 0u, 0u, (uint32_t)seed, (uint32_t)(seed >> 32), &r0);
+    const float u = (float)(r0 >> 8) * (1.0f / 16777216.0f);
+    const float target = u * mass;
+    if (mass > target) {
+      uint32_t b = 0u;
+      for (int bit = kTopBit; bit >= 0; --bit) {
+        const uint32_t trial = b | (1u << bit);
+        if (mass_ge_within(p, vocab, trial, keep, &s) > target) b = trial;
+      }
+      if (b < keep.xb) b = keep.xb;
+      float gt_mass;
+      int gt_count;
+      mass_count_gt(p, vocab, b, &gt_mass, &gt_count, &s);
+      const float x = __uint_as_float(b);
+      const int ties = (b == keep.xb) ? keep.c : count_eq(p, vocab, b, &s);
+      if (ties > 0) {
+        int rnk = 0;
+        if (x > 0.f) {
+          rnk = (int)floorf((target - gt_mass) / x);
+          if (rnk < 0) rnk = 0;
+        }
+        if (rnk > ties - 1) rnk = ties - 1;
+        chosen = nth_equal(p, vocab, b, rnk, &s, &shared_result);
+      }
+    }
+    if (chosen < 0) {
+      // rounding left none: the last kept token, i.e. the smallest kept key and its last kept tie
+      uint32_t b = keep.xb;
+      int ties = keep.c;
+      if (ties == 0) {
+        b = 0u;  // the smallest key above keep.xb is the largest b with count(key >= b) >= above
+        for (int bit = kTopBit; bit >= 0; --bit) {
+          const uint32_t trial = b | (1u << bit);
+          float m;
+          int c;
+          mass_count_gt(p, vocab, trial - 1u, &m, &c, &s);
+          if (c >= above) b = trial;
+        }
+        ties = count_eq(p, vocab, b, &s);
+      }
+      chosen = ties > 0 ? nth_equal(p, vocab, b, ties - 1, &s, &shared_result) : imax;
+    }
+  }
+  if (threadIdx.x == 0) ids[r] = chosen;
+}
+
+}  // namespace roost
+
+using namespace roost;
+
+extern "C" int roost_argmax(const float* logits, int64_t stride, int rows, int vocab, int32_t* ids, roost_stream_t stream) {
+  ROOST_REQUIRE(rows >= 0 && vocab > 0 && stride >= vocab, "argmax: rows, vocab and stride must be consistent");
+  if (rows == 0) return ROOST_OK;
+  argmax_kernel<<<rows, kThreads, 0, (cudaStream_t)stream>>>(logits, stride, vocab, ids);
+  return check_launch("argmax");
+}
+
+extern "C" int roost_sample(const float* logits, int64_t stride, int rows, int vocab, const float* temperature,
+                            const int32_t* top_k, const float* top_p, const float* min_p, const uint64_t* seeds,
+                            const uint64_t* offsets, float* workspace, int32_t* ids, roost_stream_t stream) {
+  ROOST_REQUIRE(rows >= 0 && vocab > 0 && stride >= vocab, "sample: rows, vocab and stride must be consistent");
+  ROOST_REQUIRE(temperature && top_k && top_p && min_p && seeds && offsets && workspace && ids, "sample: a parameter table is null");
+  if (rows == 0) return ROOST_OK;
+  sample_kernel<<<rows, kThreads, 0, (cudaStream_t)stream>>>(logits, stride, vocab, temperature, top_k, top_p, min_p, seeds,
+                                                            offsets, workspace, ids);
+  return check_launch("sample");
+}

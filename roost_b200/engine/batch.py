@@ -1,0 +1,131 @@
+"""The tables of one step, built on the host and copied to the device in one transfer.
+
+A step is a list of rows; each row is one request's next tokens at consecutive positions: a whole prompt, a
+portion of one, or a single decoded token, mixed freely. From the rows and the requests' block tables the
+tables below are derived, the same set the reference's worker fills before every forward pass
+(src/Starlings.Roost.Worker/Eager/PlanRegionWriter.cs:19-64): token ids, absolute positions, the slot each
+token's key and value go to, per-row query and page ranges, the rows whose logits are wanted.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import numpy as np
+import torch
+
+from ..cache.block_pool import NULL_PAGE
+
+
+@dataclass
+class GroupTables:
+    """Per cache group. Paged: ``slot_mapping[t]`` = page * page_size + offset for token t, ``kv_indices``
+    the rows' block tables back to back (a page given back to the pool stays as -1), ``kv_indptr`` their
+    bounds. State: ``state_slots[b]`` the row's slot."""
+    slot_mapping: torch.Tensor | None = None
+    kv_indptr: torch.Tensor | None = None
+    kv_indices: torch.Tensor | None = None
+    state_slots: torch.Tensor | None = None
+
+
+@dataclass
+class StepBatch:
+    num_tokens: int
+    num_rows: int
+    num_selected: int
+    ids: torch.Tensor            # [T] int32
+    positions: torch.Tensor      # [T] int32 absolute position of each token
+    token_row: torch.Tensor      # [T] int32 row of each token
+    q_indptr: torch.Tensor       # [B+1] int32 token range of each row
+    kv_lens: torch.Tensor        # [B] int32 tokens of the row's request once this step has run
+    selected: torch.Tensor       # [S] int32 token indices whose logits are wanted
+    groups: list = field(default_factory=list)
+    # host-side facts, for parts written in Python and for kernel selection
+    row_starts: list = field(default_factory=list)       # first position of each row
+    row_counts: list = field(default_factory=list)       # tokens of each row
+    max_position: int = 0
+    max_kv_len: int = 0
+    all_single: bool = False     # every row brings exactly one token
+    host_buffer: object = None   # the pinned staging buffer, kept until the step is done
+
+
+class BatchBuilder:
+    """Packs a step's tables into one pinned host buffer and copies it to the device once."""
+
+    def __init__(self, device, cache_manager):
+        self.device = torch.device(device)
+        self.cm = cache_manager
+
+    def build(self, rows: list[tuple], vocab: int) -> StepBatch:
+        """rows: (request cache, start position, token list, wanted offsets within the tokens)."""
+        T = sum(len(r[2]) for r in rows)
+        B = len(rows)
+        ids = np.empty(T, np.int32)
+        pos = np.empty(T, np.int32)
+        trow = np.empty(T, np.int32)
+        q_indptr = np.zeros(B + 1, np.int32)
+        kv_lens = np.empty(B, np.int32)
+        selected = []
+        at = 0
+        for b, (rc, start, tokens, want) in enumerate(rows):
+            n = len(tokens)
+            ids[at : at + n] = tokens
+            pos[at : at + n] = np.arange(start, start + n, dtype=np.int32)
+            trow[at : at + n] = b
+            q_indptr[b + 1] = at + n
+            kv_lens[b] = start + n
+            selected.extend(at + w for w in want)
+            at += n
+        if T and (ids.min() < 0 or ids.max() >= vocab):
+            bad = int(ids[(ids < 0) | (ids >= vocab)][0])
+            raise ValueError(f"token id {bad} is outside the vocabulary of {vocab}")
+        parts = [ids, pos, trow, q_indptr, kv_lens, np.asarray(selected, np.int32)]
+        group_parts = []
+        for gi, g in enumerate(self.cm.groups):
+            if g.kind == "paged":
+                slot = np.empty(T, np.int32)
+                indptr = np.zeros(B + 1, np.int32)
+                indices = []
+                at = 0
+                for b, (rc, start, tokens, _) in enumerate(rows):
+                    table = rc.tables[gi]
+                    n = len(tokens)
+                    p = np.arange(start, start + n)
+                    tab = np.asarray(table, np.int64)
+                    pages = tab[p // g.page_size]
+                    if (pages == NULL_PAGE).any():
+                        raise RuntimeError(f"request {rc.request_id!r}: a token of this step falls in a page that was given back")
+                    slot[at : at + n] = pages * g.page_size + p % g.page_size
+                    used = -(-(start + n) // g.page_size)
+                    indices.extend(table[:used])
+                    indptr[b + 1] = len(indices)
+                    at += n
+                group_parts.append((slot, indptr, np.asarray(indices, np.int32)))
+            else:
+                group_parts.append((np.asarray([rc.slots[gi] for rc, *_ in rows], np.int32),))
+        flat = parts + [a for gp in group_parts for a in gp]
+        # 16-byte aligned sub-tables in one buffer
+        offsets, total = [], 0
+        for a in flat:
+            offsets.append(total)
+            total += -(-a.size // 4) * 4
+        host = torch.empty(max(total, 4), dtype=torch.int32, pin_memory=self.device.type == "cuda")
+        hv = host.numpy()
+        for a, o in zip(flat, offsets):
+            hv[o : o + a.size] = a
+        dev = host.to(self.device, non_blocking=True)
+        views = [dev[o : o + a.size] for a, o in zip(flat, offsets)]
+        d_ids, d_pos, d_trow, d_qi, d_kvl, d_sel = views[:6]
+        rest = views[6:]
+        groups = []
+        for g in self.cm.groups:
+            if g.kind == "paged":
+                groups.append(GroupTables(slot_mapping=rest[0], kv_indptr=rest[1], kv_indices=rest[2]))
+                rest = rest[3:]
+            else:
+                groups.append(GroupTables(state_slots=rest[0]))
+                rest = rest[1:]
+        return StepBatch(num_tokens=T, num_rows=B, num_selected=len(selected), ids=d_ids, positions=d_pos, token_row=d_trow,
+                         q_indptr=d_qi, kv_lens=d_kvl, selected=d_sel, groups=groups,
+                         row_starts=[r[1] for r in rows], row_counts=[len(r[2]) for r in rows],
+                         max_position=int(pos.max()) if T else 0, max_kv_len=int(kv_lens.max()) if B else 0,
+                         all_single=all(len(r[2]) == 1 for r in rows), host_buffer=host)

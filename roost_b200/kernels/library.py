@@ -1,0 +1,217 @@
+"""The Python side of the kernel library's C ABI: loads the shared object, checks its version and wraps every
+entry point so that tensors go in and a non-OK status becomes an exception with the library's message.
+
+There is no other implementation behind these functions: when the library cannot be built or loaded, or when
+no CUDA device is present, ``load()`` raises and nothing in the engine runs.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_char_p, c_double, c_float, c_int, c_int64, c_void_p
+
+import torch
+
+from . import build
+
+ABI_VERSION = 1
+F32, BF16 = 0, 1
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    if dt == torch.float32:
+        return F32
+    if dt == torch.bfloat16:
+        return BF16
+    raise KernelError(f"dtype {dt} is neither float32 nor bfloat16")
+
+
+def _ptr(t):
+    return None if t is None else c_void_p(t.data_ptr())
+
+
+def _stream():
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _need(t: torch.Tensor, name: str, dtype=None):
+    if not t.is_cuda:
+        raise KernelError(f"{name} is not on a CUDA device")
+    if not t.is_contiguous():
+        raise KernelError(f"{name} is not contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} has dtype {t.dtype}; expected {dtype}")
+
+
+_SIGNATURES = {
+    "roost_embedding": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "roost_rms_norm": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_int, c_void_p],
+    "roost_add_rms_norm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_int, c_void_p],
+    "roost_silu_mul": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "roost_qk_norm_rope_cache": [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                 c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int64, c_int, c_int, c_int,
+                                 c_void_p],
+    "roost_paged_attention_generic": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                      c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p],
+    "roost_gemm_simt": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int, c_int, c_void_p],
+    "roost_argmax": [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p],
+    "roost_sample": [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                     c_void_p, c_void_p],
+}
+
+
+class KernelLibrary:
+    def __init__(self, path):
+        self.path = str(path)
+        self._lib = ctypes.CDLL(self.path)
+        self._lib.roost_abi_version.restype = c_int
+        self._lib.roost_last_error.restype = c_char_p
+        got = self._lib.roost_abi_version()
+        if got != ABI_VERSION:
+            raise KernelError(f"{self.path} has ABI version {got}; this package needs {ABI_VERSION}")
+        for name, args in _SIGNATURES.items():
+            fn = getattr(self._lib, name)
+            fn.argtypes = args
+            fn.restype = c_int
+        self.launches = 0  # kernels launched through this handle (a host-side count of entry-point calls that launch)
+
+    def _call(self, name: str, *args, launches: int = 1):
+        status = getattr(self._lib, name)(*args)
+        if status != 0:
+            msg = self._lib.roost_last_error().decode(errors="replace")
+            raise KernelError(f"{name}: {msg} (status {status})")
+        self.launches += launches
+
+    # ------------------------------------------------------------------ ops
+    def embedding(self, table: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
+        _need(table, "table"); _need(ids, "ids", torch.int32)
+        T, (V, H) = ids.numel(), table.shape
+        out = torch.empty((T, H), dtype=table.dtype, device=table.device)
+        self._call("roost_embedding", _ptr(table), _ptr(ids), _ptr(out), T, H, V, dtype_code(table.dtype), _stream())
+        return out
+
+    def rms_norm(self, x: torch.Tensor, w: torch.Tensor, eps: float, rows: torch.Tensor | None = None) -> torch.Tensor:
+        _need(x, "x"); _need(w, "w")
+        H = x.shape[-1]
+        if w.numel() != H:
+            raise KernelError(f"rms_norm: weight has {w.numel()} elements for rows of {H}")
+        n = x.numel() // H if rows is None else rows.numel()
+        out = torch.empty((n, H) if rows is not None else x.shape, dtype=x.dtype, device=x.device)
+        self._call("roost_rms_norm", _ptr(x), _ptr(w), _ptr(out), _ptr(rows), n, H, eps, dtype_code(x.dtype),
+                   dtype_code(w.dtype), _stream())
+        return out
+
+    def add_rms_norm(self, x: torch.Tensor, residual: torch.Tensor, w: torch.Tensor, eps: float,
+                     rows: torch.Tensor | None = None) -> torch.Tensor:
+        """residual += x (in place, unless ``rows`` gathers) and the norm of the sum."""
+        _need(x, "x"); _need(residual, "residual", x.dtype); _need(w, "w")
+        H = x.shape[-1]
+        if residual.shape != x.shape or w.numel() != H:
+            raise KernelError("add_rms_norm: x, residual and weight do not agree in shape")
+        n = x.numel() // H if rows is None else rows.numel()
+        out = torch.empty((n, H), dtype=x.dtype, device=x.device)
+        self._call("roost_add_rms_norm", _ptr(x), _ptr(residual), _ptr(w), _ptr(out), _ptr(rows), n, H, eps,
+                   dtype_code(x.dtype), dtype_code(w.dtype), _stream())
+        return out
+
+    def silu_mul(self, x: torch.Tensor) -> torch.Tensor:
+        _need(x, "x")
+        T, two_i = x.shape
+        out = torch.empty((T, two_i // 2), dtype=x.dtype, device=x.device)
+        self._call("roost_silu_mul", _ptr(x), _ptr(out), T, two_i // 2, dtype_code(x.dtype), _stream())
+        return out
+
+    def qk_norm_rope_cache(self, qkv, q_heads, kv_heads, head_dim, *, q_w, k_w, eps, inv_freq, rotary_dim, positions,
+                           k_pool=None, v_pool=None, slot_mapping=None, page_size=0, write_kv=True) -> torch.Tensor:
+        """qkv: [T, (q_heads + 2 kv_heads) * head_dim] (or [T, q_heads * head_dim] with write_kv False). Returns
+        q: [T, q_heads, head_dim], normed and rotated; k and v go into the pools."""
+        _need(qkv, "qkv")
+        T = qkv.shape[0]
+        width = (q_heads + (2 * kv_heads if write_kv else 0)) * head_dim
+        if qkv.shape[1] != width:
+            raise KernelError(f"qk_norm_rope_cache: qkv rows have {qkv.shape[1]} elements; expected {width}")
+        q = torch.empty((T, q_heads, head_dim), dtype=qkv.dtype, device=qkv.device)
+        wd = dtype_code(q_w.dtype) if q_w is not None else F32
+        pages = 0
+        if write_kv:
+            _need(k_pool, "k_pool", qkv.dtype); _need(v_pool, "v_pool", qkv.dtype); _need(slot_mapping, "slot_mapping", torch.int32)
+            pages = k_pool.shape[0]
+            if tuple(k_pool.shape[1:]) != (kv_heads, page_size, head_dim) or k_pool.shape != v_pool.shape:
+                raise KernelError(f"qk_norm_rope_cache: pool shape {tuple(k_pool.shape)} is not [pages, {kv_heads}, {page_size}, {head_dim}]")
+        if rotary_dim:
+            _need(inv_freq, "inv_freq", torch.float64); _need(positions, "positions", torch.int32)
+            if inv_freq.numel() != rotary_dim // 2:
+                raise KernelError("qk_norm_rope_cache: inv_freq must have rotary_dim / 2 entries")
+        self._call("roost_qk_norm_rope_cache", _ptr(qkv), qkv.stride(0), _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(q_w),
+                   _ptr(k_w), _ptr(inv_freq), _ptr(positions), _ptr(slot_mapping), T, q_heads, kv_heads, head_dim,
+                   rotary_dim, eps, page_size, pages, 1 if write_kv else 0, dtype_code(qkv.dtype), wd, _stream())
+        return q
+
+    def paged_attention_generic(self, q, k_pool, v_pool, positions, token_row, kv_indptr, kv_indices, scale: float,
+                                window: int | None) -> torch.Tensor:
+        _need(q, "q"); _need(k_pool, "k_pool", q.dtype); _need(v_pool, "v_pool", q.dtype)
+        for n, t in (("positions", positions), ("token_row", token_row), ("kv_indptr", kv_indptr), ("kv_indices", kv_indices)):
+            _need(t, n, torch.int32)
+        T, nq, d = q.shape
+        _, nkv, page, d2 = k_pool.shape
+        if d2 != d:
+            raise KernelError("paged_attention: head_dim of q and of the pool differ")
+        out = torch.empty((T, nq * d), dtype=q.dtype, device=q.device)
+        self._call("roost_paged_attention_generic", _ptr(q), _ptr(out), _ptr(k_pool), _ptr(v_pool), _ptr(positions),
+                   _ptr(token_row), _ptr(kv_indptr), _ptr(kv_indices), T, nq, nkv, d, page, scale,
+                   int(window) if window else 0, dtype_code(q.dtype), _stream())
+        return out
+
+    def gemm_simt(self, a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+        """a [M, K] times w [N, K] transposed, 32-bit FFMA accumulation."""
+        _need(a, "a"); _need(w, "w", a.dtype)
+        M, K = a.shape
+        N, K2 = w.shape
+        if K != K2:
+            raise KernelError(f"gemm: a has {K} columns, w has {K2}")
+        out_dtype = out_dtype or a.dtype
+        out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+        self._call("roost_gemm_simt", _ptr(a), _ptr(w), _ptr(out), M, N, K, a.stride(0), w.stride(0), out.stride(0),
+                   dtype_code(a.dtype), dtype_code(out_dtype), _stream())
+        return out
+
+    def argmax(self, logits: torch.Tensor) -> torch.Tensor:
+        _need(logits, "logits", torch.float32)
+        R, V = logits.shape
+        ids = torch.empty((R,), dtype=torch.int32, device=logits.device)
+        self._call("roost_argmax", _ptr(logits), logits.stride(0), R, V, _ptr(ids), _stream())
+        return ids
+
+    def sample(self, logits, temperature, top_k, top_p, min_p, seeds, offsets, workspace=None) -> torch.Tensor:
+        _need(logits, "logits", torch.float32)
+        R, V = logits.shape
+        for n, t, dt in (("temperature", temperature, torch.float32), ("top_k", top_k, torch.int32), ("top_p", top_p, torch.float32),
+                         ("min_p", min_p, torch.float32), ("seeds", seeds, torch.int64), ("offsets", offsets, torch.int64)):
+            _need(t, n, dt)
+            if t.numel() != R:
+                raise KernelError(f"sample: {n} has {t.numel()} entries for {R} rows")
+        if workspace is None:
+            workspace = torch.empty((R, V), dtype=torch.float32, device=logits.device)
+        ids = torch.empty((R,), dtype=torch.int32, device=logits.device)
+        self._call("roost_sample", _ptr(logits), logits.stride(0), R, V, _ptr(temperature), _ptr(top_k), _ptr(top_p),
+                   _ptr(min_p), _ptr(seeds), _ptr(offsets), _ptr(workspace), _ptr(ids), _stream())
+        return ids
+
+
+_LIB: KernelLibrary | None = None
+
+
+def load() -> KernelLibrary:
+    """The process-wide library handle. Raises when no CUDA device is present or the library cannot be built."""
+    global _LIB
+    if _LIB is None:
+        if not torch.cuda.is_available():
+            raise KernelError("no CUDA device is visible: roost_b200 runs on an sm_100a GPU only and has no CPU path")
+        major, minor = torch.cuda.get_device_capability()
+        if major != 10:
+            raise KernelError(f"the GPU has compute capability {major}.{minor}; the kernel library is built for sm_100a only")
+        _LIB = KernelLibrary(build.library_path())
+    return _LIB

@@ -1,0 +1,152 @@
+"""Interfaces of the parts a model is assembled from, and the registries that map a spec's ``kind`` to a class.
+
+A part is built from its spec and a ``Runtime`` (compute dtype, device, kernel library), declares the
+parameters it wants by local name and shape, receives them through ``load`` and is then called with
+tensors. No part knows which model it is in, which layer it is, or what its neighbours are: the spec carries
+every size and constant. The reference expresses the same rule as op arguments on a node list
+(src/Starlings.Roost.Models.Tiny/RoostTiny.cs:39-56) and checks at load that every op has a kernel
+(src/Starlings.Roost.ModelCompiler/Emit/Emitter.cs:315-334); here a part's constructor refuses sizes no
+kernel serves.
+
+Adding a part: subclass the interface below, give the spec class a new ``kind`` and call the matching
+``register_*`` function (a test does this with a toy mixer without touching this package).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Callable
+
+import torch
+
+
+@dataclass(frozen=True)
+class ParamDecl:
+    """A parameter a part wants. ``row_splits``: when the checkpoint stores the parameter as several
+    tensors concatenated along dimension 0, their row counts in order."""
+    shape: tuple
+    row_splits: tuple | None = None
+    # "matrix": converted to the compute dtype; "vector": kept in its stored dtype (32-bit stays 32-bit) in the
+    # bfloat16 path; "table": integer tables become int32. In the 32-bit path every float becomes float32.
+    role: str = "matrix"
+
+
+@dataclass(frozen=True)
+class CacheNeed:
+    """What one run of a mixer keeps between steps. ``paged``: keys and values, ``kv_heads`` x ``head_dim``
+    per token, every earlier token (window None) or the last ``window`` tokens. ``state``: one tensor of
+    ``state_shape`` per live request, zeroed when the request's first token arrives."""
+    kind: str                       # "paged" | "state"
+    kv_heads: int = 0
+    head_dim: int = 0
+    window: int | None = None
+    state_shape: tuple = ()
+    state_dtype: torch.dtype = torch.float32
+
+
+class Runtime:
+    """What every part is built with: the compute dtype of activations (and of the cache), the device, and
+    the kernel library handle (None only for declaring parameters on a machine without a GPU)."""
+
+    def __init__(self, dtype: torch.dtype, device, kernels=None):
+        if dtype not in (torch.float32, torch.bfloat16):
+            raise ValueError(f"compute dtype {dtype} is not float32 or bfloat16")
+        self.dtype = dtype
+        self.device = torch.device(device)
+        self.kernels = kernels
+
+    @property
+    def full_precision(self) -> bool:
+        return self.dtype == torch.float32
+
+
+class Part:
+    spec = None
+
+    @classmethod
+    def parameters(cls, spec) -> dict[str, ParamDecl]:
+        return {}
+
+    def load(self, params: dict[str, torch.Tensor]) -> None:
+        if params:
+            raise ValueError(f"{type(self).__name__} takes no parameters")
+
+
+class Norm(Part):
+    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        raise NotImplementedError
+
+    def add_norm(self, x: torch.Tensor, residual: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+        """residual + x (rounded once to the activation dtype) and its norm; ``residual`` may be updated in place."""
+        raise NotImplementedError
+
+
+class Mixer(Part):
+    def cache_need(self) -> CacheNeed | None:
+        return None
+
+    def __call__(self, x: torch.Tensor, batch, cache, write_cache: bool = True) -> torch.Tensor:
+        """x: [T, hidden] normed input of this step's tokens. ``batch`` is the step's ``StepBatch``; ``cache``
+        is this run's view of its cache group (None when ``cache_need`` is None). With ``write_cache`` False
+        the run reads another run's cache and must not write it."""
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def __call__(self, x: torch.Tensor, batch) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Block(Part):
+    mixer: Mixer
+
+    def __call__(self, h, residual, batch, cache, write_cache: bool = True):
+        """(h, residual) in, (h, residual) out; ``residual`` is None before the first block."""
+        raise NotImplementedError
+
+    def sub_parts(self) -> dict[str, Part]:
+        raise NotImplementedError
+
+
+class _Registry:
+    def __init__(self, what: str):
+        self.what = what
+        self._kinds: dict[str, Callable] = {}
+
+    def register(self, kind: str, cls) -> None:
+        self._kinds[kind] = cls
+
+    def get(self, kind: str):
+        try:
+            return self._kinds[kind]
+        except KeyError:
+            raise KeyError(f"no {self.what} of kind '{kind}' is registered (registered: {', '.join(sorted(self._kinds)) or 'none'})") from None
+
+    def build(self, spec, runtime: Runtime):
+        return self.get(spec.kind)(spec, runtime)
+
+
+NORMS = _Registry("norm")
+POSITIONS = _Registry("position encoding")
+MIXERS = _Registry("mixer")
+FEED_FORWARDS = _Registry("feed-forward")
+BLOCKS = _Registry("block arrangement")
+
+
+def register_norm(kind, cls):
+    NORMS.register(kind, cls)
+
+
+def register_position(kind, cls):
+    POSITIONS.register(kind, cls)
+
+
+def register_mixer(kind, cls):
+    MIXERS.register(kind, cls)
+
+
+def register_feed_forward(kind, cls):
+    FEED_FORWARDS.register(kind, cls)
+
+
+def register_block(kind, cls):
+    BLOCKS.register(kind, cls)

@@ -1,0 +1,46 @@
+"""y = x W^T for a weight stored [out, in], no bias (src/Starlings.Roost.Ops/CpuOps.cs:395-437).
+
+float32 runs the library's FFMA product (true 32-bit, the same bits for a row whatever the batch). bfloat16
+with 32-bit accumulation goes to cuBLAS through torch, the place where the reference's engine also calls a
+library (kernels/src/gemm.cu:235), unless a hand-written tensor-core product is selected for the shape.
+"""
+from __future__ import annotations
+
+import torch
+
+from .base import Runtime
+
+_MM_OUT_DTYPE = None  # does torch.mm take out_dtype on this build? decided at first use
+
+
+class Linear:
+    def __init__(self, runtime: Runtime, out_features: int, in_features: int):
+        self.rt = runtime
+        self.out_features = out_features
+        self.in_features = in_features
+        self.weight: torch.Tensor | None = None
+
+    def load(self, weight: torch.Tensor) -> None:
+        if tuple(weight.shape) != (self.out_features, self.in_features):
+            raise ValueError(f"linear: weight is {tuple(weight.shape)}; expected {(self.out_features, self.in_features)}")
+        self.weight = weight.to(self.rt.dtype).contiguous()
+
+    def __call__(self, x: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+        global _MM_OUT_DTYPE
+        k = self.rt.kernels
+        out_dtype = out_dtype or self.rt.dtype
+        if self.rt.full_precision:
+            return k.gemm_simt(x, self.weight, torch.float32)
+        if out_dtype == torch.bfloat16:
+            k.launches += 1
+            return torch.matmul(x, self.weight.t())
+        if _MM_OUT_DTYPE is None:
+            try:
+                torch.mm(x[:1], self.weight[:8].t(), out_dtype=torch.float32)
+                _MM_OUT_DTYPE = True
+            except (TypeError, RuntimeError):
+                _MM_OUT_DTYPE = False
+        if _MM_OUT_DTYPE:
+            k.launches += 1
+            return torch.mm(x, self.weight.t(), out_dtype=torch.float32)
+        return k.gemm_simt(x, self.weight, torch.float32)

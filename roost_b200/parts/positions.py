@@ -1,0 +1,51 @@
+"""Position encodings a mixer can be given.
+
+The attention mixer's fused kernel rotates the first ``rotary_dim`` elements of every query and key head by
+the angle position * inv_freq[i], pairing element i with i + rotary_dim/2 (NeoX form,
+src/Starlings.Roost.Ops/CpuOps.cs:111-177). A position encoding therefore hands the mixer a table of
+frequencies in double precision and a rotary width; ``rotary_dim`` 0 means no rotation. Frequency-scaled
+variants are other tables behind the same interface.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..config.spec import PositionSpec
+from .base import Part, Runtime, register_position
+
+
+class PositionEncoding(Part):
+    def rotation(self) -> tuple[torch.Tensor | None, int]:
+        """(inv_freq: float64 [rotary_dim / 2] on the device, rotary_dim)."""
+        raise NotImplementedError
+
+    max_positions: int = 0  # 0: unbounded
+
+
+class RopeNeox(PositionEncoding):
+    """f_i = theta^(-2i / rotary_dim), computed in double once at build."""
+
+    def __init__(self, spec: PositionSpec, runtime: Runtime):
+        if spec.rotary_dim <= 0 or spec.rotary_dim % 2:
+            raise ValueError(f"rope_neox: rotary_dim {spec.rotary_dim} must be positive and even")
+        if spec.theta <= 0:
+            raise ValueError(f"rope_neox: theta {spec.theta} must be positive")
+        self.spec = spec
+        self.max_positions = spec.max_positions
+        i = torch.arange(spec.rotary_dim // 2, dtype=torch.float64)
+        self.inv_freq = torch.pow(torch.tensor(float(spec.theta), dtype=torch.float64), -2.0 * i / spec.rotary_dim).to(runtime.device)
+
+    def rotation(self):
+        return self.inv_freq, self.spec.rotary_dim
+
+
+class NoPosition(PositionEncoding):
+    def __init__(self, spec: PositionSpec, runtime: Runtime):
+        self.spec = spec
+
+    def rotation(self):
+        return None, 0
+
+
+register_position("rope_neox", RopeNeox)
+register_position("none", NoPosition)
