@@ -21,8 +21,8 @@ namespace roost {
 
 constexpr int kThreads = 1024;
 
-__device__ __forceinline__ void philox4x32_10(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3, uint32_t k0, uint32_t k1,
-                                              uint32_t* r0) {
+__device__ __forceinline__ unsigned philox4x32_10(unsigned c0, unsigned c1, unsigned c2, unsigned c3, unsigned k0,
+                                                  unsigned k1) {
   const uint32_t M0 = 0xD2511F53u, M1 = 0xCD9E8D57u, W0 = 0x9E3779B9u, W1 = 0xBB67AE85u;
 #pragma unroll
   for (int i = 0; i < 10; ++i) {
@@ -35,42 +35,44 @@ __device__ __forceinline__ void philox4x32_10(uint32_t c0, uint32_t c1, uint32_t
     k0 += W0;
     k1 += W1;
   }
-  *r0 = c0;
+  return c0;
 }
 
-struct Scratch {
-  float f[32];
-  int i[32];
-  int idx[32];
-};
-
-__device__ __forceinline__ float block_sum_f(float v, Scratch* s) {
+// Block-wide helpers. Every one is called by all 1024 threads under block-uniform control flow; each starts with a
+// barrier so that the shared scratch of the previous call has been read by everyone.
+__device__ __forceinline__ float block_sum_f(float v, float* sf) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   v = warp_sum(v);
   __syncthreads();
-  if (lane == 0) s->f[warp] = v;
+  if (lane == 0) sf[warp] = v;
   __syncthreads();
-  float t = s->f[lane];  // kThreads / 32 == 32 warps
-  t = warp_sum(t);
-  return t;
+  return warp_sum(sf[lane]);  // kThreads / 32 == 32 warps: every warp sums the same 32 values in the same order
 }
 
-__device__ __forceinline__ int block_sum_i(int v, Scratch* s) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+__device__ __forceinline__ int warp_sum_i(int v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-  __syncthreads();
-  if (lane == 0) s->i[warp] = v;
-  __syncthreads();
-  int t = s->i[lane];
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
-  return t;
+  return v;
 }
 
-// (value, index) maximum with ties to the lower index; NaN and (optionally) -inf never win. Returns -1 when no
-// element qualifies.
-__device__ __forceinline__ int block_argmax(const float* z, int n, bool skip_neg_inf, float* best_out, Scratch* s) {
+__device__ __forceinline__ int block_sum_i(int v, int* si) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  v = warp_sum_i(v);
+  __syncthreads();
+  if (lane == 0) si[warp] = v;
+  __syncthreads();
+  return warp_sum_i(si[lane]);
+}
+
+__device__ __forceinline__ bool better(float av, int ai, float cv, int ci) {
+  if (ci < 0) return true;
+  if (ai < 0) return false;
+  return av > cv || (av == cv && ai < ci);
+}
+
+// Index of the maximum with ties to the lower index; NaN and (optionally) -inf never win; -1 when nothing
+// qualifies. The maximum itself is left in sf[0] for the caller to read after the call.
+__device__ __forceinline__ int block_argmax(const float* z, int n, bool skip_neg_inf, float* sf, int* si) {
   float bv = 0.f;
   int bi = -1;
   for (int v = threadIdx.x; v < n; v += kThreads) {
@@ -82,11 +84,6 @@ __device__ __forceinline__ int block_argmax(const float* z, int n, bool skip_neg
       bi = v;
     }
   }
-  auto better = [](float av, int ai, float cv, int ci) {
-    if (ci < 0) return true;
-    if (ai < 0) return false;
-    return av > cv || (av == cv && ai < ci);
-  };
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
     const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
@@ -99,12 +96,12 @@ __device__ __forceinline__ int block_argmax(const float* z, int n, bool skip_neg
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   __syncthreads();
   if (lane == 0) {
-    s->f[warp] = bv;
-    s->idx[warp] = bi;
+    sf[warp] = bv;
+    si[warp] = bi;
   }
   __syncthreads();
-  bv = s->f[lane];
-  bi = s->idx[lane];
+  bv = sf[lane];
+  bi = si[lane];
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
     const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
@@ -114,26 +111,26 @@ __device__ __forceinline__ int block_argmax(const float* z, int n, bool skip_neg
       bi = oi;
     }
   }
-  if (best_out) *best_out = bv;
+  __syncthreads();
+  if (threadIdx.x == 0) sf[0] = bv;
+  __syncthreads();
   return bi;
 }
 
-__global__ void __launch_bounds__(kThreads) argmax_kernel(const float* __restrict__ logits, int64_t stride, int vocab,
-                                                         int32_t* __restrict__ ids) {
-  __shared__ Scratch s;
+__global__ void __launch_bounds__(kThreads) argmax_kernel(const float* __restrict__ logits, long long stride, int vocab,
+                                                         int* __restrict__ ids) {
+  __shared__ float sf[32];
+  __shared__ int si[32];
   const int r = blockIdx.x;
-  const int best = block_argmax(logits + (size_t)r * stride, vocab, false, nullptr, &s);
+  const int best = block_argmax(logits + (size_t)r * stride, vocab, false, sf, si);
   if (threadIdx.x == 0) ids[r] = best;
 }
 
-// The kept prefix: key > xb, or key == xb and fewer than c equal keys lie at lower indices.
-struct Prefix {
-  uint32_t xb;
-  int c;
-};
+// A kept prefix of the order is (xb, c): every key > xb, plus the first c tokens (by index) whose key == xb.
+// Keys are the bit patterns of the probabilities; removed tokens hold -1 and are skipped.
 
-// mass and count of {key > xb} over the row (keys of removed tokens are 0xFFFFFFFF-marked negatives, skipped).
-__device__ __forceinline__ void mass_count_gt(const float* p, int n, uint32_t xb, float* mass, int* count, Scratch* s) {
+// Mass of {key > xb}; the count of the same set is left in *count.
+__device__ __forceinline__ float mass_gt(const float* p, int n, unsigned xb, int& count, float* sf, int* si) {
   float m = 0.f;
   int c = 0;
   for (int v = threadIdx.x; v < n; v += kThreads) {
@@ -143,65 +140,72 @@ __device__ __forceinline__ void mass_count_gt(const float* p, int n, uint32_t xb
       ++c;
     }
   }
-  *mass = block_sum_f(m, s);
-  *count = block_sum_i(c, s);
+  count = block_sum_i(c, si);
+  return block_sum_f(m, sf);
 }
 
-__device__ __forceinline__ int count_eq(const float* p, int n, uint32_t xb, Scratch* s) {
+__device__ __forceinline__ int count_ge(const float* p, int n, unsigned b, int* si) {
+  int c = 0;
+  for (int v = threadIdx.x; v < n; v += kThreads) {
+    const float x = p[v];
+    if (x >= 0.f && __float_as_uint(x) >= b) ++c;
+  }
+  return block_sum_i(c, si);
+}
+
+__device__ __forceinline__ int count_eq(const float* p, int n, unsigned xb, int* si) {
   int c = 0;
   for (int v = threadIdx.x; v < n; v += kThreads) {
     const float x = p[v];
     if (x >= 0.f && __float_as_uint(x) == xb) ++c;
   }
-  return block_sum_i(c, s);
+  return block_sum_i(c, si);
 }
 
-// Mass of {key >= b} within the prefix `in`.
-__device__ __forceinline__ float mass_ge_within(const float* p, int n, uint32_t b, Prefix in, Scratch* s) {
+// Mass of {key >= b} within the prefix (xb, c).
+__device__ __forceinline__ float mass_ge_within(const float* p, int n, unsigned b, unsigned xb, int c, float* sf) {
   float m = 0.f;
   for (int v = threadIdx.x; v < n; v += kThreads) {
     const float x = p[v];
     if (x >= 0.f) {
-      const uint32_t k = __float_as_uint(x);
-      if (k >= b && k > in.xb) m += x;
+      const unsigned k = __float_as_uint(x);
+      if (k >= b && k > xb) m += x;
     }
   }
-  m = block_sum_f(m, s);
-  if (b <= in.xb) m += (float)in.c * __uint_as_float(in.xb);
+  m = block_sum_f(m, sf);
+  if (b <= xb) m += (float)c * __uint_as_float(xb);
   return m;
 }
 
 // Index of the (r+1)-th token (by index) whose key equals xb; -1 if there are fewer.
-__device__ __forceinline__ int nth_equal(const float* p, int n, uint32_t xb, int r, Scratch* s, int* shared_result) {
+__device__ __forceinline__ int nth_equal(const float* p, int n, unsigned xb, int r, int* si, int* result) {
   const int chunk = (n + kThreads - 1) / kThreads;
-  const int lo = threadIdx.x * chunk, hi = min(n, lo + chunk);
+  const int lo = min(n, (int)threadIdx.x * chunk), hi = min(n, lo + chunk);
   int mine = 0;
   for (int v = lo; v < hi; ++v) {
     const float x = p[v];
     if (x >= 0.f && __float_as_uint(x) == xb) ++mine;
   }
-  // exclusive prefix over threads: warp scan, then scan of warp totals
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  int inc = mine;
+  int inc = mine;  // inclusive scan over the warp
 #pragma unroll
   for (int o = 1; o < 32; o <<= 1) {
     const int t = __shfl_up_sync(0xffffffffu, inc, o);
     if (lane >= o) inc += t;
   }
   __syncthreads();
-  if (threadIdx.x == 0) *shared_result = -1;
-  if (lane == 31) s->i[warp] = inc;
+  if (threadIdx.x == 0) *result = -1;
+  if (lane == 31) si[warp] = inc;
   __syncthreads();
-  int before = 0;
-  for (int w2 = 0; w2 < warp; ++w2) before += s->i[w2];
-  before += inc - mine;
+  int before = inc - mine;
+  for (int w2 = 0; w2 < warp; ++w2) before += si[w2];
   if (r >= before && r < before + mine) {
     int seen = before;
     for (int v = lo; v < hi; ++v) {
       const float x = p[v];
       if (x >= 0.f && __float_as_uint(x) == xb) {
         if (seen == r) {
-          *shared_result = v;
+          *result = v;
           break;
         }
         ++seen;
@@ -209,23 +213,27 @@ __device__ __forceinline__ int nth_equal(const float* p, int n, uint32_t xb, int
     }
   }
   __syncthreads();
-  return *shared_result;
+  const int out = *result;
+  __syncthreads();
+  return out;
 }
 
+// seeds and offsets are read as pairs of 32-bit words (low word first).
 __global__ void __launch_bounds__(kThreads)
-    sample_kernel(const float* __restrict__ logits, int64_t stride, int vocab, const float* __restrict__ temperature,
-                  const int32_t* __restrict__ top_k, const float* __restrict__ top_p, const float* __restrict__ min_p,
-                  const uint64_t* __restrict__ seeds, const uint64_t* __restrict__ offsets, float* __restrict__ workspace,
-                  int32_t* __restrict__ ids) {
-  __shared__ Scratch s;
-  __shared__ int shared_result;
+    sample_kernel(const float* __restrict__ logits, long long stride, int vocab, const float* __restrict__ temperature,
+                  const int* __restrict__ top_k, const float* __restrict__ top_p, const float* __restrict__ min_p,
+                  const unsigned* __restrict__ seeds, const unsigned* __restrict__ offsets, float* workspace,
+                  int* __restrict__ ids) {
+  __shared__ float sf[32];
+  __shared__ int si[32];
+  __shared__ int s_result;
   const int r = blockIdx.x;
   const float* z = logits + (size_t)r * stride;
   float* p = workspace + (size_t)r * vocab;
   const float temp = temperature[r];
 
-  float zmax;
-  const int imax = block_argmax(z, vocab, true, &zmax, &s);
+  const int imax = block_argmax(z, vocab, true, sf, si);
+  const float zmax = sf[0];
   if (temp <= 0.f || imax < 0) {
     if (threadIdx.x == 0) ids[r] = imax;
     return;
@@ -233,114 +241,102 @@ __global__ void __launch_bounds__(kThreads)
 
   // probabilities; removed tokens are marked -1
   float part = 0.f;
+  int allowed = 0;
   for (int v = threadIdx.x; v < vocab; v += kThreads) {
     const float x = z[v];
     float e = -1.f;
     if (x == x && x != -INFINITY) {
       e = expf((x - zmax) / temp);
       part += e;
+      ++allowed;
     }
     p[v] = e;
   }
-  const float total = block_sum_f(part, &s);
-  int allowed = 0;
+  const float total = block_sum_f(part, sf);
+  allowed = block_sum_i(allowed, si);
   for (int v = threadIdx.x; v < vocab; v += kThreads) {
     const float e = p[v];
-    if (e >= 0.f) {
-      p[v] = e / total;
-      ++allowed;
-    }
+    if (e >= 0.f) p[v] = e / total;
   }
-  allowed = block_sum_i(allowed, &s);
   __syncthreads();
   const float pmax = 1.0f / total;  // exp(0) / total
 
   // the whole allowed set as a prefix: every key above 0, and all tokens whose probability underflowed to 0
-  Prefix keep;
-  keep.xb = 0u;
-  keep.c = count_eq(p, vocab, 0u, &s);
+  unsigned keep_xb = 0u;
+  int keep_c = count_eq(p, vocab, 0u, si);
   constexpr int kTopBit = 29;  // probabilities are at most 1 = 0x3F800000, so bits 31 and 30 of a key are 0
 
   // top-k: the k-th largest key is the largest b with count(key >= b) >= k
   const int k = top_k[r];
   if (k > 0 && k < allowed) {
-    uint32_t b = 0u;
+    unsigned b = 0u;
     for (int bit = kTopBit; bit >= 0; --bit) {
-      const uint32_t trial = b | (1u << bit);
-      float m;
-      int c;
-      mass_count_gt(p, vocab, trial - 1u, &m, &c, &s);  // keys >= trial
-      if (c >= k) b = trial;
+      const unsigned trial = b | (1u << bit);
+      if (count_ge(p, vocab, trial, si) >= k) b = trial;
     }
-    float m;
     int above;
-    mass_count_gt(p, vocab, b, &m, &above, &s);
-    keep.xb = b;
-    keep.c = k - above;
+    mass_gt(p, vocab, b, above, sf, si);
+    keep_xb = b;
+    keep_c = k - above;
   }
 
   // top-p: the crossing token's key is the largest b with (kept mass of keys >= b) >= top_p * kept mass
   const float tp = top_p[r];
   if (tp < 1.0f) {
-    const float kept_total = mass_ge_within(p, vocab, 0u, keep, &s);
+    const float kept_total = mass_ge_within(p, vocab, 0u, keep_xb, keep_c, sf);
     const float bar = tp * kept_total;
-    uint32_t b = 0u;
+    unsigned b = 0u;
     for (int bit = kTopBit; bit >= 0; --bit) {
-      const uint32_t trial = b | (1u << bit);
-      if (mass_ge_within(p, vocab, trial, keep, &s) >= bar) b = trial;
+      const unsigned trial = b | (1u << bit);
+      if (mass_ge_within(p, vocab, trial, keep_xb, keep_c, sf) >= bar) b = trial;
     }
-    if (b < keep.xb) b = keep.xb;
-    float gt_mass;
+    if (b < keep_xb) b = keep_xb;
     int gt_count;
-    mass_count_gt(p, vocab, b, &gt_mass, &gt_count, &s);
+    const float gt_mass = mass_gt(p, vocab, b, gt_count, sf, si);
     const float x = __uint_as_float(b);
-    const int ties = (b == keep.xb) ? keep.c : count_eq(p, vocab, b, &s);
+    const int ties = (b == keep_xb) ? keep_c : count_eq(p, vocab, b, si);
     int need = 1;
     if (x > 0.f) {
       need = (int)ceilf((bar - gt_mass) / x);
       if (need < 1) need = 1;
     }
     if (need > ties) need = ties;
-    keep.xb = b;
-    keep.c = need;
+    keep_xb = b;
+    keep_c = need;
   }
 
   // min-p: drop p < min_p * p_max; what stays is {key > bits(floor) - 1} when the prefix reached below the floor
   const float mp = min_p[r];
   if (mp > 0.f) {
     const float floor_p = mp * pmax;
-    if (__uint_as_float(keep.xb) < floor_p) {
-      keep.xb = __float_as_uint(floor_p) - 1u;
-      keep.c = 0;
+    if (__uint_as_float(keep_xb) < floor_p) {
+      keep_xb = __float_as_uint(floor_p) - 1u;
+      keep_c = 0;
     }
   }
 
   // the draw: the chosen token's key is the largest b with (kept mass of keys >= b) > u * kept mass
-  float above_mass;
   int above;
-  mass_count_gt(p, vocab, keep.xb, &above_mass, &above, &s);
+  mass_gt(p, vocab, keep_xb, above, sf, si);
   int chosen = -1;
-  if (above == 0 && keep.c == 0) {
+  if (above == 0 && keep_c == 0) {
     chosen = imax;  // min-p above 1 left nothing: the reference keeps the first token of the order
   } else {
-    const float mass = mass_ge_within(p, vocab, 0u, keep, &s);
-    uint32_t r0;
-    const uint64_t seed = seeds[r], off = offsets[r];
-    philox4x32_10((uint32_t)off, (uint32_t)(off >> 32), 0u, 0u, (uint32_t)seed, (uint32_t)(seed >> 32), &r0);
+    const float mass = mass_ge_within(p, vocab, 0u, keep_xb, keep_c, sf);
+    const unsigned r0 = philox4x32_10(offsets[2 * r], offsets[2 * r + 1], 0u, 0u, seeds[2 * r], seeds[2 * r + 1]);
     const float u = (float)(r0 >> 8) * (1.0f / 16777216.0f);
     const float target = u * mass;
     if (mass > target) {
-      uint32_t b = 0u;
+      unsigned b = 0u;
       for (int bit = kTopBit; bit >= 0; --bit) {
-        const uint32_t trial = b | (1u << bit);
-        if (mass_ge_within(p, vocab, trial, keep, &s) > target) b = trial;
+        const unsigned trial = b | (1u << bit);
+        if (mass_ge_within(p, vocab, trial, keep_xb, keep_c, sf) > target) b = trial;
       }
-      if (b < keep.xb) b = keep.xb;
-      float gt_mass;
+      if (b < keep_xb) b = keep_xb;
       int gt_count;
-      mass_count_gt(p, vocab, b, &gt_mass, &gt_count, &s);
+      const float gt_mass = mass_gt(p, vocab, b, gt_count, sf, si);
       const float x = __uint_as_float(b);
-      const int ties = (b == keep.xb) ? keep.c : count_eq(p, vocab, b, &s);
+      const int ties = (b == keep_xb) ? keep_c : count_eq(p, vocab, b, si);
       if (ties > 0) {
         int rnk = 0;
         if (x > 0.f) {
@@ -348,25 +344,22 @@ __global__ void __launch_bounds__(kThreads)
           if (rnk < 0) rnk = 0;
         }
         if (rnk > ties - 1) rnk = ties - 1;
-        chosen = nth_equal(p, vocab, b, rnk, &s, &shared_result);
+        chosen = nth_equal(p, vocab, b, rnk, si, &s_result);
       }
     }
     if (chosen < 0) {
       // rounding left none: the last kept token, i.e. the smallest kept key and its last kept tie
-      uint32_t b = keep.xb;
-      int ties = keep.c;
+      unsigned b = keep_xb;
+      int ties = keep_c;
       if (ties == 0) {
-        b = 0u;  // the smallest key above keep.xb is the largest b with count(key >= b) >= above
+        b = 0u;  // the smallest key above keep_xb is the largest b with count(key >= b) >= above
         for (int bit = kTopBit; bit >= 0; --bit) {
-          const uint32_t trial = b | (1u << bit);
-          float m;
-          int c;
-          mass_count_gt(p, vocab, trial - 1u, &m, &c, &s);
-          if (c >= above) b = trial;
+          const unsigned trial = b | (1u << bit);
+          if (count_ge(p, vocab, trial, si) >= above) b = trial;
         }
-        ties = count_eq(p, vocab, b, &s);
+        ties = count_eq(p, vocab, b, si);
       }
-      chosen = ties > 0 ? nth_equal(p, vocab, b, ties - 1, &s, &shared_result) : imax;
+      chosen = ties > 0 ? nth_equal(p, vocab, b, ties - 1, si, &s_result) : imax;
     }
   }
   if (threadIdx.x == 0) ids[r] = chosen;
@@ -379,7 +372,7 @@ using namespace roost;
 extern "C" int roost_argmax(const float* logits, int64_t stride, int rows, int vocab, int32_t* ids, roost_stream_t stream) {
   ROOST_REQUIRE(rows >= 0 && vocab > 0 && stride >= vocab, "argmax: rows, vocab and stride must be consistent");
   if (rows == 0) return ROOST_OK;
-  argmax_kernel<<<rows, kThreads, 0, (cudaStream_t)stream>>>(logits, stride, vocab, ids);
+  argmax_kernel<<<rows, kThreads, 0, (cudaStream_t)stream>>>(logits, (long long)stride, vocab, ids);
   return check_launch("argmax");
 }
 
@@ -389,7 +382,10 @@ extern "C" int roost_sample(const float* logits, int64_t stride, int rows, int v
   ROOST_REQUIRE(rows >= 0 && vocab > 0 && stride >= vocab, "sample: rows, vocab and stride must be consistent");
   ROOST_REQUIRE(temperature && top_k && top_p && min_p && seeds && offsets && workspace && ids, "sample: a parameter table is null");
   if (rows == 0) return ROOST_OK;
-  sample_kernel<<<rows, kThreads, 0, (cudaStream_t)stream>>>(logits, stride, vocab, temperature, top_k, top_p, min_p, seeds,
-                                                            offsets, workspace, ids);
+  ROOST_REQUIRE(((uintptr_t)logits & 3) == 0 && ((uintptr_t)workspace & 3) == 0 && ((uintptr_t)seeds & 3) == 0 &&
+                    ((uintptr_t)offsets & 3) == 0,
+                "sample: a table is not aligned to its element size");
+  sample_kernel<<<rows, kThreads, 0, (cudaStream_t)stream>>>(logits, (long long)stride, vocab, temperature, top_k, top_p, min_p,
+                                                            (const unsigned*)seeds, (const unsigned*)offsets, workspace, ids);
   return check_launch("sample");
 }

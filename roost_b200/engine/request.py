@@ -1,0 +1,69 @@
+"""Requests as the engine sees them: token ids in, sampling parameters, limits.
+
+Field names and defaults are the reference's request contract
+(src/Starlings.Roost.Abstractions/Requests/Request.cs:19-68 for the sampling parameters, :148-200 for the
+request): temperature 1 unless set (0 means greedy), top_p 1 disables, top_k 0 disables, min_p 0 disables, a
+missing seed is replaced by an engine-chosen one, stop token ids are the model's plus the request's.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+
+class RequestError(ValueError):
+    """A request the engine refuses at admission; ``kind`` is the reference's refusal name."""
+
+    def __init__(self, kind: str, message: str):
+        super().__init__(f"{kind}: {message}")
+        self.kind = kind
+
+
+@dataclass(frozen=True)
+class SamplingParameters:
+    temperature: float = 1.0
+    top_p: float = 1.0
+    top_k: int = 0
+    min_p: float = 0.0
+    seed: int | None = None
+    max_tokens: int | None = None
+    min_tokens: int = 0
+    ignore_eos: bool = False
+
+    def validate(self) -> None:
+        if self.temperature < 0:
+            raise RequestError("InvalidOption", f"temperature {self.temperature} is negative")
+        if not 0 < self.top_p <= 1:
+            raise RequestError("InvalidOption", f"top_p {self.top_p} is outside (0, 1]")
+        if self.top_k < -1:
+            raise RequestError("InvalidOption", f"top_k {self.top_k} is below -1")
+        if not 0 <= self.min_p <= 1:
+            raise RequestError("InvalidOption", f"min_p {self.min_p} is outside [0, 1]")
+        if self.max_tokens is not None and self.max_tokens <= 0:
+            raise RequestError("InvalidOption", f"max_tokens {self.max_tokens} must be positive")
+
+    @property
+    def greedy(self) -> bool:
+        return self.temperature <= 0
+
+
+GREEDY = SamplingParameters(temperature=0.0)
+
+
+@dataclass
+class Request:
+    request_id: object
+    prompt_token_ids: list
+    sampling: SamplingParameters = field(default_factory=SamplingParameters)
+    stop_token_ids: tuple = ()
+    priority: int = 0                 # higher runs first
+    deadline: float | None = None     # earlier runs first among equal priorities; None last
+
+
+@dataclass
+class TokenEvent:
+    """One generated token of one request; ``finish_reason`` is set on the request's last token
+    ("stop": a stop token, "length": max_tokens or the context's end) or, with ``token`` None, when the request
+    was aborted ("aborted": it can never fit in the cache)."""
+    request_id: object
+    token: int | None
+    finish_reason: str | None = None

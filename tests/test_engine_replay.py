@@ -1,0 +1,158 @@
+"""The engine against the plain implementation, for every way of cutting the work.
+
+Each test runs twice: on the GPU with the real kernel library (marked gpu), in float32 and bfloat16, and on the CPU
+with the stand-in kernels of tests/fake_kernels.py, which checks the host side (tables, pages, the step function's
+bookkeeping) where no GPU is present.
+"""
+import pytest
+import torch
+
+from roost_b200.engine.executor import StepEntry, StepExecutor
+from tests import helpers as H
+from tests.conftest import TINY
+
+BACKENDS = [
+    pytest.param(("gpu", torch.float32), id="gpu-f32", marks=pytest.mark.gpu),
+    pytest.param(("gpu", torch.bfloat16), id="gpu-bf16", marks=pytest.mark.gpu),
+    pytest.param(("fake", torch.float32), id="cpu-fake"),
+]
+
+
+@pytest.fixture(params=BACKENDS)
+def backend(request):
+    return request.param
+
+
+@pytest.fixture(params=["A", "B"])
+def tiny(request, tiny_model_dirs):
+    return request.param, tiny_model_dirs[request.param], TINY[request.param]
+
+
+def make_executor(tiny, backend, num_pages):
+    name, model_dir, t = tiny
+    kind, dtype = backend
+    model = H.make_model(model_dir, dtype, kind)
+    return StepExecutor(model, page_size=t["page_size"], num_pages=num_pages, max_requests=4), dtype
+
+
+def check(got, model_dir, ids, dtype, what):
+    want = H.plain_logits(model_dir, ids, bf16=dtype == torch.bfloat16)
+    err = H.scaled_error(got, want)
+    rms = H.rms_error(got, want)
+    print(f"MEASURED {what} {dtype}: worst scaled error {err:.3e}, rms error {rms:.3e}")
+    assert err < H.bound_for(dtype), f"{what}: worst scaled error {err}"
+    if dtype == torch.bfloat16:
+        assert rms < H.BF16_RMS_BOUND, f"{what}: rms error {rms}"
+    if dtype == torch.float32:
+        # greedy tokens agree wherever the plain implementation's top two logits are not a near-tie
+        top2 = want.topk(2, dim=-1).values
+        clear = (top2[:, 0] - top2[:, 1]) > 1e-3
+        assert torch.equal(got.cpu().argmax(-1)[clear], want.argmax(-1)[clear])
+
+
+@pytest.mark.parametrize("length", [7, 19, 33, 150])
+def test_each_request_alone_and_whole(tiny, backend, length):
+    name, model_dir, t = tiny
+    ex, dtype = make_executor(tiny, backend, num_pages=40)
+    ids = H.random_ids(length, t["config"]["vocab_size"], seed=length)
+    check(H.run_whole(ex, "r", ids), model_dir, ids, dtype, f"{name} whole {length}")
+    ex.cache.check_invariants()
+    assert ex.cache.pools[0].free_count == 40
+
+
+def test_first_tokens_of_a_sequence(tiny, backend):
+    """One token, then two: the shortest prompts, the first row of the first page."""
+    name, model_dir, t = tiny
+    ex, dtype = make_executor(tiny, backend, num_pages=8)
+    for n in (1, 2, 3):
+        ids = H.random_ids(n, t["config"]["vocab_size"], seed=100 + n)
+        check(H.run_whole(ex, f"r{n}", ids), model_dir, ids, dtype, f"{name} first {n}")
+    ids = H.random_ids(5, t["config"]["vocab_size"], seed=9)
+    check(H.run_tail_decoded(ex, "one-by-one", ids, tail=5), model_dir, ids, dtype, f"{name} from the first token on")
+
+
+def test_most_in_one_step_then_last_32_one_by_one(tiny, backend):
+    name, model_dir, t = tiny
+    ex, dtype = make_executor(tiny, backend, num_pages=40)
+    ids = H.random_ids(97, t["config"]["vocab_size"], seed=2)
+    check(H.run_tail_decoded(ex, "r", ids, tail=32), model_dir, ids, dtype, f"{name} tail decoded")
+
+
+def test_portions_of_changing_size(tiny, backend):
+    name, model_dir, t = tiny
+    ex, dtype = make_executor(tiny, backend, num_pages=40)
+    ids = H.random_ids(131, t["config"]["vocab_size"], seed=3)
+    for sizes in ([17, 2, 9, 3, 2, 31], [5], [2], [64, 2, 2, 63]):
+        check(H.run_portions(ex, "r", ids, sizes), model_dir, ids, dtype, f"{name} portions {sizes}")
+
+
+def test_long_decoding(tiny, backend):
+    """A short prompt and then two hundred single-token steps: windows pass, pages fill and are crossed."""
+    name, model_dir, t = tiny
+    ex, dtype = make_executor(tiny, backend, num_pages=40)
+    ids = H.random_ids(4 + 200, t["config"]["vocab_size"], seed=4)
+    check(H.run_tail_decoded(ex, "r", ids, tail=200), model_dir, ids, dtype, f"{name} long decoding")
+
+
+def test_mixed_batches_with_pages_used_again(tiny, backend):
+    """Up to four live requests, portions of some beside decoded tokens of others, in a pool so small that the pages a
+    finished request gives back are taken by the next one."""
+    name, model_dir, t = tiny
+    lengths = [40, 23, 64, 17, 51, 9, 70, 33]
+    P = t["page_size"]
+    # the four largest neighbours that can be live together, in whole pages, and not one page more
+    live_max = max(sum(-(-n // P) for n in lengths[i : i + 4]) for i in range(len(lengths)))
+    num_pages = max(live_max, max(sum(sorted(-(-n // P) for n in lengths)[-4:]), live_max))
+    ex, dtype = make_executor(tiny, backend, num_pages=num_pages)
+    reqs = {f"q{i}": H.random_ids(n, t["config"]["vocab_size"], seed=50 + i) for i, n in enumerate(lengths)}
+    taken = set()
+    orig_extend = ex.cache.extend
+
+    def spy(rid, total):
+        rc = orig_extend(rid, total)
+        taken.update((rid, p) for p in rc.tables[0])
+        return rc
+
+    ex.cache.extend = spy
+    got = H.run_mixed(ex, reqs, seed=7)
+    pages_by_request = {}
+    for rid, p in taken:
+        pages_by_request.setdefault(p, set()).add(rid)
+    assert any(len(v) > 1 for v in pages_by_request.values()), "no page was used by two requests: the pool is too large for this test"
+    for rid, ids in reqs.items():
+        check(got[rid], model_dir, ids, dtype, f"{name} mixed {rid}")
+    assert all(p.free_count == p.capacity for p in ex.cache.pools)
+
+
+def test_cuts_agree_with_each_other(tiny, backend):
+    """The same request whole, decoded and in portions: the three runs of the engine agree with each other far more
+    tightly than with the plain implementation (in float32 to the last bit but for the reading order of pages)."""
+    name, model_dir, t = tiny
+    ex, dtype = make_executor(tiny, backend, num_pages=40)
+    ids = H.random_ids(90, t["config"]["vocab_size"], seed=5)
+    whole = H.run_whole(ex, "w", ids)
+    tail = H.run_tail_decoded(ex, "t", ids, tail=32)
+    parts = H.run_portions(ex, "p", ids, [13, 2, 7])
+    kind, _ = backend
+    # the float32 kernels sum in an order that depends on the token alone (measured: identical bits); the CPU stand-in
+    # uses torch's matrix products, which do not keep that promise
+    bound = (1e-6 if kind == "gpu" else 1e-5) if dtype == torch.float32 else 2.0 ** -6
+    print(f"MEASURED {name} {dtype} cuts: tail {H.scaled_error(tail, whole):.3e} portions {H.scaled_error(parts, whole):.3e}")
+    assert H.scaled_error(tail, whole) < bound
+    assert H.scaled_error(parts, whole) < bound
+
+
+def test_a_step_that_does_not_fit_changes_nothing(tiny, backend):
+    from roost_b200.cache.manager import OutOfPages
+    name, model_dir, t = tiny
+    ex, dtype = make_executor(tiny, backend, num_pages=4)
+    P = t["page_size"]
+    ids = H.random_ids(3 * P, t["config"]["vocab_size"], seed=6)
+    ex.step([StepEntry("a", ids, [])])
+    with pytest.raises(OutOfPages):
+        ex.step([StepEntry("b", H.random_ids(2 * P, t["config"]["vocab_size"], seed=8), [0])])
+    assert "b" not in ex.cache
+    ex.cache.check_invariants()
+    ex.finish("a")
+    out = ex.step([StepEntry("b", ids[: 2 * P], [2 * P - 1])])
+    assert out.shape == (1, t["config"]["vocab_size"])

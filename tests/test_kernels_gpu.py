@@ -1,0 +1,272 @@
+"""Each kernel alone against a plain torch float64 restatement of the same op, at sizes other than the engine's
+tiny models: widths and vocabularies that are no power of two, head sizes in steps of 16, odd group sizes."""
+import math
+
+import pytest
+import torch
+
+from tests.plain import qwen3_plain as plain
+
+pytestmark = pytest.mark.gpu
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype, scale=1.0):
+    return (2e-6 if dtype == torch.float32 else 2.0 ** -7) * scale
+
+
+def close(got, want, dtype, what, scale=1.0):
+    err = float(((got.double().cpu() - want.double().cpu()).abs() / (1 + want.double().cpu().abs())).max())
+    print(f"MEASURED {what} {dtype}: {err:.3e}")
+    assert err < tol(dtype, scale), f"{what}: {err}"
+
+
+def rand(shape, dtype, seed, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).to(dtype).cuda()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hidden,vocab", [(80, 131), (1000, 50)])
+def test_embedding(kernels, dtype, hidden, vocab):
+    table = rand((vocab, hidden), dtype, 1)
+    ids = torch.tensor([0, vocab - 1, 3, 3, vocab, -1, 7], dtype=torch.int32).cuda()
+    out = kernels.embedding(table, ids)
+    want = plain.embedding(table.cpu(), [0, vocab - 1, 3, 3, 0, 0, 7]).clone()
+    want[4] = 0
+    want[5] = 0  # an id outside the vocabulary gives a zero row on the device
+    assert torch.equal(out.cpu(), want)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("wdtype", DTYPES)
+@pytest.mark.parametrize("rows,hidden,eps", [(5, 72, 1e-6), (33, 1000, 1e-5), (2, 5120, 1e-6)])
+def test_rms_norm_and_fused_add(kernels, dtype, wdtype, rows, hidden, eps):
+    x = rand((rows, hidden), dtype, 2, 3.0)
+    res = rand((rows, hidden), dtype, 3, 2.0)
+    w = (1 + 0.1 * torch.randn(hidden, generator=torch.Generator().manual_seed(4))).to(wdtype).cuda()
+    close(kernels.rms_norm(x, w, eps), plain.rms_norm(x.double().cpu(), w.double().cpu(), eps), dtype, "rms_norm")
+    sel = torch.tensor([rows - 1, 0], dtype=torch.int32).cuda()
+    close(kernels.rms_norm(x, w, eps, sel), plain.rms_norm(x.double().cpu(), w.double().cpu(), eps)[[rows - 1, 0]], dtype, "rms_norm rows")
+    s = (x.float() + res.float()).to(dtype)  # the sum is rounded once to the activation dtype
+    res_in = res.clone()
+    out = kernels.add_rms_norm(x, res_in, w, eps)
+    assert torch.equal(res_in, s)
+    close(out, plain.rms_norm(s.double().cpu(), w.double().cpu(), eps), dtype, "add_rms_norm")
+    res_in2 = res.clone()
+    out2 = kernels.add_rms_norm(x, res_in2, w, eps, sel)
+    assert torch.equal(res_in2, res), "with gathered rows the residual stays as it is"
+    close(out2, plain.rms_norm(s.double().cpu(), w.double().cpu(), eps)[[rows - 1, 0]], dtype, "add_rms_norm rows")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("tokens,inter", [(3, 100), (17, 1111)])
+def test_silu_mul(kernels, dtype, tokens, inter):
+    x = rand((tokens, 2 * inter), dtype, 5, 3.0)
+    xd = x.double().cpu()
+    close(kernels.silu_mul(x), plain.silu_and_mul(xd[:, :inter], xd[:, inter:]), dtype, "silu_mul")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("m,n,k", [(1, 70, 50), (37, 129, 200), (130, 64, 1024), (64, 387, 96)])
+def test_gemm_simt(kernels, dtype, m, n, k):
+    a = rand((m, k), dtype, 6)
+    w = rand((n, k), dtype, 7)
+    want = a.double().cpu() @ w.double().cpu().T
+    # float32: k additions into a running sum of size ~sqrt(k), each rounded to 2^-24 relative: an absolute error of
+    # the order k * 2^-24 sqrt(...) at worst, against outputs that may be near zero; the bound is k * 2^-23.
+    fp32_scale = k * 2.0 ** -23 / 2e-6
+    close(kernels.gemm_simt(a, w), want, dtype, "gemm", scale=fp32_scale if dtype == torch.float32 else math.sqrt(k) / 8)
+    if dtype == torch.bfloat16:
+        close(kernels.gemm_simt(a, w, torch.float32), want, torch.float32, "gemm f32 out", scale=fp32_scale)
+    # a row's bits do not depend on which other rows are in the product
+    if m > 1:
+        assert torch.equal(kernels.gemm_simt(a[m // 2 : m // 2 + 1].contiguous(), w), kernels.gemm_simt(a, w)[m // 2 : m // 2 + 1])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nq,nkv,d,rot,page", [(4, 2, 16, 16, 16), (6, 1, 32, 32, 8), (5, 5, 48, 32, 4), (8, 2, 128, 128, 16), (3, 1, 80, 80, 32)])
+def test_qk_norm_rope_cache(kernels, dtype, nq, nkv, d, rot, page):
+    T, pages = 11, 9
+    eps, theta = 1e-5, 1e6
+    qkv = rand((T, (nq + 2 * nkv) * d), dtype, 8, 2.0)
+    qw = (1 + 0.1 * torch.randn(d, generator=torch.Generator().manual_seed(9))).to(dtype).cuda()
+    kw = (1 + 0.1 * torch.randn(d, generator=torch.Generator().manual_seed(10))).to(dtype).cuda()
+    positions = torch.tensor([0, 1, 2, 3, 500, 501, 4095, 100000, 7, 8, 9], dtype=torch.int32).cuda()
+    slots = torch.tensor([5, 30, 3, -1, 0, page * pages - 1, 17, 18, 19, 33, 34], dtype=torch.int32)  # distinct, below 36
+    assert page * pages >= 36
+    slots = slots.cuda()
+    inv_freq = torch.pow(torch.tensor(theta, dtype=torch.float64), -2.0 * torch.arange(rot // 2, dtype=torch.float64) / rot).cuda()
+    kp = torch.full((pages, nkv, page, d), 7.0, dtype=dtype).cuda()
+    vp = torch.full((pages, nkv, page, d), 7.0, dtype=dtype).cuda()
+    q = kernels.qk_norm_rope_cache(qkv, nq, nkv, d, q_w=qw, k_w=kw, eps=eps, inv_freq=inv_freq, rotary_dim=rot, positions=positions,
+                                   k_pool=kp, v_pool=vp, slot_mapping=slots, page_size=page)
+    x = qkv.double().cpu()
+    qq = x[:, : nq * d].reshape(T, nq, d)
+    kk = x[:, nq * d : (nq + nkv) * d].reshape(T, nkv, d)
+    vv = x[:, (nq + nkv) * d :].reshape(T, nkv, d)
+    qq, kk = plain.qk_norm(qq, kk, qw.double().cpu(), kw.double().cpu(), eps)
+    pos = positions.cpu().tolist()
+    qq = plain.rope_neox(qq, pos, theta, rot)
+    kk = plain.rope_neox(kk, pos, theta, rot)
+    close(q, qq, dtype, "q normed and rotated", scale=2)
+    want_k = torch.full((pages, nkv, page, d), 7.0, dtype=torch.float64)
+    want_v = want_k.clone()
+    for t, s in enumerate(slots.cpu().tolist()):
+        if s >= 0:
+            want_k[s // page, :, s % page, :] = kk[t]
+            want_v[s // page, :, s % page, :] = vv[t]
+    close(kp, want_k, dtype, "k pages", scale=2)
+    assert torch.equal(vp.double().cpu(), want_v), "values are copied bit for bit, and no other slot is touched"
+    # q only (a run that reads another run's cache), no norm, no rotation
+    q2 = kernels.qk_norm_rope_cache(qkv[:, : nq * d].contiguous(), nq, nkv, d, q_w=None, k_w=None, eps=eps, inv_freq=None, rotary_dim=0,
+                                    positions=positions, write_kv=False)
+    assert torch.equal(q2.reshape(T, -1), qkv[:, : nq * d])
+
+
+def paged_reference(q, keys, values, positions, rows, scale, window):
+    """q [T, nq, d]; keys/values: per row a [len, nkv, d] tensor; float64."""
+    out = torch.zeros(q.shape[0], q.shape[1] * q.shape[2], dtype=torch.float64)
+    group = q.shape[1] // keys[0].shape[1]
+    for t in range(q.shape[0]):
+        p, b = positions[t], rows[t]
+        lo = max(0, p - window + 1) if window else 0
+        k, v = keys[b][lo : p + 1], values[b][lo : p + 1]
+        for h in range(q.shape[1]):
+            s = (k[:, h // group] @ q[t, h]) * scale
+            out[t, h * q.shape[2] : (h + 1) * q.shape[2]] = torch.softmax(s, 0) @ v[:, h // group]
+    return out
+
+
+def build_paged(keys, values, page, dtype, num_pages, seed):
+    """Scatters per-row keys and values into shuffled pages; unused slots hold NaN so that a read of a slot that is
+    not the row's shows."""
+    nkv, d = keys[0].shape[1:]
+    kp = torch.full((num_pages, nkv, page, d), float("nan"), dtype=dtype)
+    vp = torch.full((num_pages, nkv, page, d), float("nan"), dtype=dtype)
+    order = torch.randperm(num_pages, generator=torch.Generator().manual_seed(seed)).tolist()
+    indptr, indices = [0], []
+    for k, v in zip(keys, values):
+        n = k.shape[0]
+        for pi in range(-(-n // page)):
+            pg = order.pop()
+            indices.append(pg)
+            seg = slice(pi * page, min(n, (pi + 1) * page))
+            kp[pg, :, : seg.stop - seg.start] = k[seg].transpose(0, 1).to(dtype)
+            vp[pg, :, : seg.stop - seg.start] = v[seg].transpose(0, 1).to(dtype)
+        indptr.append(len(indices))
+    return kp.cuda(), vp.cuda(), torch.tensor(indptr, dtype=torch.int32).cuda(), torch.tensor(indices, dtype=torch.int32).cuda()
+
+
+ATTN_SHAPES = [(4, 2, 16, 16), (6, 1, 32, 8), (8, 2, 128, 16), (5, 5, 48, 4), (14, 2, 64, 32), (3, 1, 80, 16), (2, 1, 256, 16)]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("window", [None, 37])
+@pytest.mark.parametrize("nq,nkv,d,page", ATTN_SHAPES)
+def test_paged_attention_mixed_rows(kernels, dtype, window, nq, nkv, d, page):
+    """Three rows in one launch: a whole prompt, a portion in the middle of a request, a single decoded token."""
+    g = torch.Generator().manual_seed(11)
+    lens = [45, 133, 300]           # keys each row holds after this step
+    news = [45, 21, 1]              # queries each row brings (the last `news` positions)
+    keys = [torch.randn(n, nkv, d, generator=g).to(dtype).double() for n in lens]
+    values = [torch.randn(n, nkv, d, generator=g).to(dtype).double() for n in lens]
+    positions, rows = [], []
+    for b, (n, m) in enumerate(zip(lens, news)):
+        positions += list(range(n - m, n))
+        rows += [b] * m
+    T = len(positions)
+    q = (torch.randn(T, nq, d, generator=g) * 1.5).to(dtype)
+    kp, vp, indptr, indices = build_paged(keys, values, page, dtype, num_pages=sum(-(-n // page) for n in lens) + 3, seed=12)
+    scale = 1 / math.sqrt(d)
+    out = kernels.paged_attention_generic(q.cuda(), kp, vp, torch.tensor(positions, dtype=torch.int32).cuda(),
+                                          torch.tensor(rows, dtype=torch.int32).cuda(), indptr, indices, scale, window)
+    want = paged_reference(q.double(), keys, values, positions, rows, scale, window)
+    assert not torch.isnan(out).any(), "a slot outside the row's visible keys was read"
+    # a dot product over head_dim and a softmax over hundreds of keys, each in 32-bit: four times the elementwise bound
+    close(out, want, dtype, f"attention window={window}", scale=4)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("case", ["far key", "first key", "page edge", "window edge in", "window edge out"])
+def test_paged_attention_finds_the_one_key_that_matters(kernels, dtype, case):
+    """Random keys would hide a key that is skipped or read from the wrong slot. Here one key's score stands out by
+    construction, so the output must be that key's value (or, for a key just outside the window, must not be)."""
+    nq, nkv, d, page, n = 4, 2, 64, 16, 700
+    window = None
+    target = {"far key": 3, "first key": 0, "page edge": 16 * 20 - 1, "window edge in": n - 50, "window edge out": n - 51}[case]
+    if case.startswith("window"):
+        window = 50
+    g = torch.Generator().manual_seed(13)
+    keys = torch.randn(n, nkv, d, generator=g) * 0.1
+    values = torch.randn(n, nkv, d, generator=g)
+    q = torch.randn(1, nq, d, generator=g) * 0.1
+    direction = torch.nn.functional.normalize(torch.randn(d, generator=g), dim=0)
+    keys[target] = direction * 8.0
+    q[0, :] = direction * 8.0                      # score 64 / sqrt(64) * ... = 8 * 8 / 8 = 8 at the target, ~0 elsewhere
+    q = q * 2                                       # 16 at the target: exp(16) dwarfs 700 keys of exp(~0)
+    keys_d, values_d = keys.to(dtype).double(), values.to(dtype).double()
+    kp, vp, indptr, indices = build_paged([keys_d], [values_d], page, dtype, num_pages=-(-n // page) + 2, seed=14)
+    out = kernels.paged_attention_generic(q.to(dtype).cuda(), kp, vp, torch.tensor([n - 1], dtype=torch.int32).cuda(),
+                                          torch.tensor([0], dtype=torch.int32).cuda(), indptr, indices, 1 / math.sqrt(d), window)
+    want = paged_reference(q.to(dtype).double(), [keys_d], [values_d], [n - 1], [0], 1 / math.sqrt(d), window)
+    close(out, want, dtype, case, scale=4)
+    got_v = out.double().cpu().reshape(nq, d)
+    hit = (got_v - values_d[target][torch.arange(nq) // 2]).abs().max() < 0.05
+    assert hit == (case != "window edge out"), f"{case}: output {'is' if hit else 'is not'} the target's value"
+
+
+def test_argmax_ties_and_nan(kernels):
+    V = 151936 // 8 + 3
+    z = torch.randn(4, V)
+    z[0, 77] = 50.0
+    z[0, 9000] = 50.0          # a tie: the lower index wins
+    z[1, 5] = float("nan")     # never chosen
+    z[1, 6] = 40.0
+    z[2] = float("nan")        # nothing to choose
+    z[3, V - 1] = 60.0
+    ids = kernels.argmax(z.cuda()).cpu().tolist()
+    assert ids == [77, 6, -1, V - 1]
+
+
+@pytest.mark.parametrize("vocab", [387, 5000])
+def test_sampler_matches_the_plain_sampler(kernels, vocab):
+    """Rows with different settings in one launch; a row is compared when the plain sampler's draw is not within
+    1e-4 of the kept mass from an edge of the chosen token's interval."""
+    g = torch.Generator().manual_seed(15)
+    settings = [(0.0, 0, 1.0, 0.0), (1.0, 0, 1.0, 0.0), (0.8, 0, 0.9, 0.0), (0.7, 20, 1.0, 0.0), (1.3, 50, 0.8, 0.0),
+                (1.0, 0, 1.0, 0.05), (0.9, 40, 0.95, 0.02), (0.5, 1, 1.0, 0.0), (2.0, 0, 0.5, 0.0), (1.0, 3, 0.2, 0.0)]
+    rows = []
+    for rep in range(4):
+        for s in settings:
+            rows.append(s)
+    R = len(rows)
+    logits = torch.randn(R, vocab, generator=g) * 3
+    logits[3, 10] = float("-inf")
+    logits[4, 11] = float("nan")
+    logits[5, 40:44] = logits[5, 40]            # ties in the middle of the order
+    seeds = torch.arange(R, dtype=torch.int64) * 7919 + 12345
+    offsets = torch.arange(R, dtype=torch.int64) % 5
+    t = torch.tensor([r[0] for r in rows], dtype=torch.float32)
+    k = torch.tensor([r[1] for r in rows], dtype=torch.int32)
+    p = torch.tensor([r[2] for r in rows], dtype=torch.float32)
+    mp = torch.tensor([r[3] for r in rows], dtype=torch.float32)
+    got = kernels.sample(logits.cuda(), t.cuda(), k.cuda(), p.cuda(), mp.cuda(), seeds.cuda(), offsets.cuda()).cpu().tolist()
+    again = kernels.sample(logits.cuda(), t.cuda(), k.cuda(), p.cuda(), mp.cuda(), seeds.cuda(), offsets.cuda()).cpu().tolist()
+    assert got == again, "the sampler is not repeatable"
+    compared = 0
+    for r in range(R):
+        temp, tk, tp, m = rows[r]
+        if temp <= 0:
+            assert got[r] == plain.sample_row(logits[r].tolist(), 0.0)
+            compared += 1
+            continue
+        want, detail = plain.sample_row(logits[r].tolist(), temp, tk, tp, m, int(seeds[r]), int(offsets[r]), return_detail=True)
+        assert got[r] in detail["kept"] or detail["margin"] < 1e-4, f"row {r}: token {got[r]} is outside the kept set"
+        if detail["margin"] > 1e-4:
+            assert got[r] == want, f"row {r} {rows[r]}: got {got[r]}, want {want} (margin {detail['margin']:.2e})"
+            compared += 1
+    assert compared >= R * 0.8
+    # a row's token does not depend on the batch it is in
+    one = kernels.sample(logits[7:8].cuda(), t[7:8].cuda(), k[7:8].cuda(), p[7:8].cuda(), mp[7:8].cuda(), seeds[7:8].cuda(), offsets[7:8].cuda())
+    assert one.cpu().tolist() == [got[7]]
