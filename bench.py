@@ -1,0 +1,290 @@
+"""Decode and prefill throughput of the engine at Qwen3-8B layer sizes with random weights on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--context 4096] [--layers L] [--impl reference]
+
+Prints ONE JSON line. ``value`` is decoded tokens per second over K timed decode steps of ``--batch`` requests
+that each hold ``--context`` tokens, timed on the device with CUDA events; ``e2e`` is the same through the
+Python entry point (``RoostEngine.step``: host token ids in from pinned memory, sampled ids back to the host,
+every step). ``prefill`` is one 2,048-token prompt; ``roofline`` the decode step's bytes (every weight once and
+the live requests' cache) over its time against the measured copy bandwidth; ``points`` decode at batch 1 and
+64. Weights are seeded random values, token ids seeded uniform-random, and the contexts of the device-timed
+decode runs are filled with random keys and values instead of being prefilled (their values do not change the
+work of a decode step); the e2e run prefills its contexts for real through the engine.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+QWEN3_8B = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=36, hidden_size=4096,
+                num_attention_heads=32, num_key_value_heads=8, head_dim=128, intermediate_size=12288, vocab_size=151936,
+                rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=40960,
+                torch_dtype="bfloat16")
+PAGE = 16
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def peaks() -> tuple[dict, str]:
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            return json.load(f), "measured"
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a timed region runs."""
+    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+        return self
+
+    def __exit__(self, *a):
+        self.samples = []
+        if self.proc is None:
+            return
+        time.sleep(0.15)
+        self.proc.terminate()
+        out, _ = self.proc.communicate(timeout=10)
+        for line in out.splitlines():
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) >= 7:
+                try:
+                    self.samples.append((float(parts[0]), float(parts[1]), parts[3:7]))
+                except ValueError:
+                    pass
+
+    def summary(self) -> dict:
+        if not getattr(self, "samples", None):
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({n for s in self.samples for n, v in zip(names, s[2]) if v.lower().startswith("active")})
+        return {"sm_mhz": statistics.median(s[0] for s in self.samples), "sm_max_mhz": max(s[1] for s in self.samples),
+                "reasons": reasons, "samples": len(self.samples)}
+
+
+def build_model(layers: int, dtype, seed: int = 0):
+    import torch
+
+    from roost_b200.config.qwen3 import Qwen3Config
+    from roost_b200.engine.model import Model
+    from roost_b200.kernels import library
+    from roost_b200.parts import Runtime
+    from roost_b200.weights.random_init import random_parameters
+    cfg = dict(QWEN3_8B, num_hidden_layers=layers)
+    spec = Qwen3Config.from_dict(cfg).to_spec(False)
+    model = Model(spec, Runtime(dtype, "cuda", library.load()))
+    model.load(random_parameters(spec, seed, torch.device("cuda"), dtype, std=0.02))
+    return model, cfg
+
+
+def matrix_bytes(cfg: dict) -> int:
+    """Bytes of every weight a decode step reads once: the layers' matrices and norms, the head (the embedding is read
+    a row per token)."""
+    H, I, V, d = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"], cfg["head_dim"]
+    Q, KV = cfg["num_attention_heads"] * d, cfg["num_key_value_heads"] * d
+    per_layer = (Q + 2 * KV) * H + H * Q + 2 * I * H + H * I + 2 * H + 2 * d
+    return 2 * (cfg["num_hidden_layers"] * per_layer + V * H + H)
+
+
+def kv_bytes_per_token(cfg: dict) -> int:
+    return 2 * cfg["num_hidden_layers"] * cfg["num_key_value_heads"] * cfg["head_dim"] * 2
+
+
+def prefill_flops(cfg: dict, T: int) -> float:
+    H, I, V, d = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"], cfg["head_dim"]
+    Q, KV = cfg["num_attention_heads"] * d, cfg["num_key_value_heads"] * d
+    per_layer = 2.0 * T * ((Q + 2 * KV) * H + H * Q + 2 * I * H + H * I) + 4.0 * T * T / 2 * Q
+    return cfg["num_hidden_layers"] * per_layer + 2.0 * V * H
+
+
+def fill_context(executor, request_ids, context: int, seed: int = 1):
+    """Gives every request ``context`` tokens of cache filled with random keys and values."""
+    import torch
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    for t, grp in zip(executor.storage.tensors, executor.groups):
+        if grp.kind == "paged":
+            for i in range(t.shape[0]):
+                t[i].copy_(torch.randn(t[i].shape, generator=g, device="cuda", dtype=torch.float32) * 0.5)
+    for rid in request_ids:
+        executor.cache.extend(rid, context)
+        executor.cache.commit(rid, context)
+
+
+def timed_decode(model, batch: int, context: int, steps: int, warmup: int):
+    """K decode steps on the device: step function and greedy choice, no host read inside the timed region."""
+    import torch
+
+    from roost_b200.engine.executor import StepEntry, StepExecutor
+    pages = batch * (-(-(context + steps + warmup + 2) // PAGE)) + 8
+    ex = StepExecutor(model, page_size=PAGE, num_pages=pages, max_requests=max(batch, 1))
+    rids = [f"d{i}" for i in range(batch)]
+    start = context - (steps + warmup)
+    fill_context(ex, rids, start)
+    gen = torch.Generator().manual_seed(7)
+    tokens = torch.randint(0, model.spec.vocab, (steps + warmup, batch), generator=gen).tolist()
+    k = model.rt.kernels
+
+    def one(i):
+        logits = ex.step([StepEntry(r, [tokens[i][b]], [0]) for b, r in enumerate(rids)])
+        return k.argmax(logits)
+
+    for i in range(warmup):
+        one(i)
+    torch.cuda.synchronize()
+    launches0 = k.launches
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler() as clocks:
+        torch.cuda.synchronize()
+        e0.record()
+        for i in range(warmup, warmup + steps):
+            one(i)
+        e1.record()
+        torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    launches = k.launches - launches0
+    for r in rids:
+        ex.finish(r)
+    del ex
+    torch.cuda.empty_cache()
+    return batch / (ms / 1e3), ms, launches, clocks.summary()
+
+
+def timed_prefill(model, tokens_n: int, warmup: int = 3, iters: int = 3):
+    import torch
+
+    from roost_b200.engine.executor import StepEntry, StepExecutor
+    ex = StepExecutor(model, page_size=PAGE, num_pages=-(-tokens_n // PAGE) + 2, max_requests=2)
+    gen = torch.Generator().manual_seed(11)
+    ids = torch.randint(0, model.spec.vocab, (tokens_n,), generator=gen).tolist()
+    times = []
+    for i in range(warmup + iters):
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        ex.step([StepEntry("p", ids, [tokens_n - 1])])
+        e1.record()
+        torch.cuda.synchronize()
+        ex.finish("p")
+        if i >= warmup:
+            times.append(e0.elapsed_time(e1))
+    del ex
+    torch.cuda.empty_cache()
+    return min(times)
+
+
+def timed_e2e(model, batch: int, context: int, steps: int, warmup: int):
+    """The same decode through the Python entry point: every step plans, uploads the step's tables from pinned host
+    memory, runs, samples on the device and reads the sampled ids back to the host."""
+    import torch
+
+    from roost_b200 import GenerationOptions, RoostEngine
+    pages = batch * (-(-(context + 2) // PAGE)) + 8
+    engine = RoostEngine(model, page_size=PAGE, attention_blocks=pages, max_sequences=max(batch, 1), max_tokens=2048)
+    gen = torch.Generator().manual_seed(13)
+    prompt_len = context - (steps + warmup)
+    opts = GenerationOptions(max_output_tokens=steps + warmup + 1, ignore_eos=True).sampling()
+    for b in range(batch):
+        engine.add_request(torch.randint(0, model.spec.vocab, (prompt_len,), generator=gen).tolist(), opts)
+    # prefill (untimed): run engine steps until every request decodes
+    while any(s.computed < s.prompt_len for s in engine.scheduler.sequences()) or \
+            any(s.generated == 0 for s in engine.scheduler.sequences()):
+        engine.step()
+    for _ in range(warmup - 1):
+        engine.step()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    produced = 0
+    h2d = d2h = 0
+    for _ in range(steps):
+        events = engine.step()
+        produced += sum(1 for e in events if e.token is not None)
+        h2d += engine.executor.last_upload_bytes
+        d2h += 4 * len(events)
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    del engine
+    torch.cuda.empty_cache()
+    return produced / dt, h2d // steps, d2h // steps
+
+
+def reference_arm() -> int:
+    print(json.dumps({"impl": "reference", "unavailable": "starlinghq/roost is a C#/.NET 10 program with no Python package "
+                      "(pip install of /root/reference finds no setup.py or pyproject.toml) and no .NET SDK or runtime is on this image"}))
+    return 0
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=4096)
+    ap.add_argument("--layers", type=int, default=QWEN3_8B["num_hidden_layers"])
+    ap.add_argument("--prefill-tokens", type=int, default=2048)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--skip-points", action="store_true")
+    ap.add_argument("--skip-e2e", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm()
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not served")
+        return 2
+    warmup = max(args.warmup, 3)
+
+    import torch
+    pk, pk_kind = peaks()
+    model, cfg = build_model(args.layers, torch.bfloat16)
+    tps, ms, launches, clocks = timed_decode(model, args.batch, args.context, args.steps, warmup)
+    decode_bytes = matrix_bytes(cfg) + args.batch * args.context * kv_bytes_per_token(cfg)
+    achieved = decode_bytes / (ms / 1e3) / 1e9
+    pre_ms = timed_prefill(model, args.prefill_tokens)
+    pre_flops = prefill_flops(cfg, args.prefill_tokens)
+    points = {}
+    if not args.skip_points:
+        for name, b in (("decode_b1", 1), ("decode_b64", 64)):
+            points[name] = round(timed_decode(model, b, args.context, max(8, args.steps // 2), warmup)[0], 1)
+    e2e = None
+    if not args.skip_e2e:
+        v, bi, bo = timed_e2e(model, args.batch, args.context, args.steps, warmup)
+        e2e = {"value": round(v, 1), "unit": "tokens/s", "h2d_bytes_per_step": bi, "d2h_bytes_per_step": bo}
+    line = {
+        "metric": "decode tokens/s (batch 8, context 4096), Qwen3-8B layer sizes", "value": round(tps, 1), "unit": "tokens/s",
+        "n_gpus": 1, "steps": args.steps, "warmup": warmup, "ms_per_step": round(ms, 4), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "impl": "ours",
+        "data": "synthetic: seeded random weights N(0, 0.02), seeded uniform-random token ids, device-timed decode contexts filled with random keys/values",
+        "config": {"model": "qwen3-8b-shapes", "global_batch": args.batch, "seq_len": args.context, "parallelism": "single-gpu",
+                   "layers": args.layers, "layers_of_config": QWEN3_8B["num_hidden_layers"], "hidden": cfg["hidden_size"],
+                   "q_heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
+                   "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"], "page_size": PAGE,
+                   "l2": "inputs larger than L2: each step streams all weights (>10 GB) from HBM", "peaks": pk_kind},
+        "prefill": {"value": round(args.prefill_tokens / (pre_ms / 1e3), 1), "tokens": args.prefill_tokens, "ms": round(pre_ms, 3),
+                    "frac": round(pre_flops / (pre_ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "points": points, "clocks": clocks, "gpu_launches": launches,
+    }
+    if e2e is not None:
+        line["e2e"] = e2e
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,224 @@
+"""The ``roost`` command line.
+
+The reference's command is ``roost serve`` (an HTTP server, not built here) and ``roost doctor``
+(src/Starlings.Roost.Server/RoostCli.cs:60-80); its worker takes ``--model --weights --kernels --device
+--max-tokens --max-sequences --attention-blocks --recurrent-slots``
+(src/Starlings.Roost.WorkerHost/WorkerArguments.cs:14-26). The same names and meanings are kept where they
+apply: ``--model`` names what to serve (here a folder with config.json and model.safetensors), ``--kernels`` a
+folder holding the kernel library, ``--device`` the CUDA ordinal, ``--max-tokens`` and ``--max-sequences`` the
+largest token and row count of a step, ``--attention-blocks`` the pages of each paged pool. Parsing is strict
+in the reference's manner (:408-438): an unknown option, a missing value or a repeated option is a usage error
+and exits with 2.
+
+    roost generate --model DIR (--prompt-ids 1,2,3 | --prompt-file FILE) [--max-output-tokens N] [--temperature T]
+                   [--top-p P] [--top-k K] [--min-p P] [--seed S] [--stop-ids a,b] [--ignore-eos] [engine options]
+    roost random-weights --config config.json --out DIR [--seed S] [--std X] [--norm-std X]
+    roost replay --model DIR --dtype bfloat16|float32 --out DIR --max-tokens N      (bin/trace_run)
+    roost doctor [--model DIR] [--kernels DIR] [--no-gpu] [--min-free-memory-gib N]
+  engine options: [--dtype bfloat16|float32] [--device N] [--kernels DIR] [--page-size N] [--attention-blocks N]
+                  [--max-tokens N] [--max-sequences N] [--max-chunk-tokens N]
+"""
+from __future__ import annotations
+
+import json
+import os
+import sys
+
+USAGE = __doc__.split("\n\n", 2)[2]
+
+_ENGINE_VALUED = {"--dtype", "--device", "--kernels", "--page-size", "--attention-blocks", "--max-tokens", "--max-sequences",
+                  "--max-chunk-tokens"}
+_COMMANDS = {
+    "generate": (_ENGINE_VALUED | {"--model", "--prompt-ids", "--prompt-file", "--max-output-tokens", "--temperature", "--top-p",
+                                   "--top-k", "--min-p", "--seed", "--stop-ids"}, {"--ignore-eos"}),
+    "random-weights": ({"--config", "--out", "--seed", "--std", "--norm-std"}, set()),
+    "replay": ({"--model", "--dtype", "--out", "--max-tokens", "--page-size"}, set()),
+    "doctor": ({"--model", "--kernels", "--min-free-memory-gib"}, {"--no-gpu"}),
+}
+
+
+class UsageError(Exception):
+    pass
+
+
+def parse(argv: list[str]) -> tuple[str, dict]:
+    if not argv:
+        raise UsageError("a command is needed")
+    command, rest = argv[0], argv[1:]
+    if command not in _COMMANDS:
+        raise UsageError(f"unknown command '{command}'")
+    valued, flags = _COMMANDS[command]
+    out: dict = {}
+    i = 0
+    while i < len(rest):
+        a = rest[i]
+        if a in out:
+            raise UsageError(f"option {a} is given twice")
+        if a in flags:
+            out[a] = True
+            i += 1
+        elif a in valued:
+            if i + 1 >= len(rest):
+                raise UsageError(f"option {a} needs a value")
+            out[a] = rest[i + 1]
+            i += 2
+        else:
+            raise UsageError(f"unknown option '{a}' for '{command}'")
+    return command, out
+
+
+def _int(opts, key, default=None):
+    if key not in opts:
+        return default
+    try:
+        return int(opts[key])
+    except ValueError:
+        raise UsageError(f"option {key} needs an integer, got '{opts[key]}'") from None
+
+
+def _float(opts, key, default=None):
+    if key not in opts:
+        return default
+    try:
+        return float(opts[key])
+    except ValueError:
+        raise UsageError(f"option {key} needs a number, got '{opts[key]}'") from None
+
+
+def _ids(text: str, key: str) -> list[int]:
+    try:
+        return [int(x) for x in text.replace(",", " ").split()]
+    except ValueError:
+        raise UsageError(f"option {key} needs token ids separated by commas or spaces") from None
+
+
+def _need(opts, key):
+    if key not in opts:
+        raise UsageError(f"option {key} is required")
+    return opts[key]
+
+
+def _apply_common(opts) -> None:
+    if "--device" in opts:
+        os.environ["CUDA_VISIBLE_DEVICES"] = str(_int(opts, "--device"))
+    if "--kernels" in opts:
+        os.environ["ROOST_KERNELS"] = opts["--kernels"]
+
+
+def cmd_generate(opts) -> int:
+    model = _need(opts, "--model")
+    if ("--prompt-ids" in opts) == ("--prompt-file" in opts):
+        raise UsageError("exactly one of --prompt-ids and --prompt-file is needed")
+    if "--prompt-ids" in opts:
+        prompts = [_ids(opts["--prompt-ids"], "--prompt-ids")]
+    else:
+        with open(opts["--prompt-file"]) as f:
+            prompts = [_ids(line, "--prompt-file") for line in f if line.strip()]
+    if not prompts or any(not p for p in prompts):
+        raise UsageError("a prompt is empty")
+    dtype = opts.get("--dtype", "bfloat16")
+    if dtype not in ("bfloat16", "float32"):
+        raise UsageError("--dtype is bfloat16 or float32")
+    _apply_common(opts)
+    from .engine.engine import GenerationOptions, RoostEngine
+    engine = RoostEngine(model, dtype=dtype, page_size=_int(opts, "--page-size", 16), attention_blocks=_int(opts, "--attention-blocks"),
+                         max_sequences=_int(opts, "--max-sequences", 64), max_tokens=_int(opts, "--max-tokens", 2048),
+                         max_chunk_tokens=_int(opts, "--max-chunk-tokens"))
+    go = GenerationOptions(max_output_tokens=_int(opts, "--max-output-tokens", 16), temperature=_float(opts, "--temperature"),
+                           top_p=_float(opts, "--top-p"), top_k=_int(opts, "--top-k"), min_p=_float(opts, "--min-p"),
+                           seed=_int(opts, "--seed"), stop_token_ids=tuple(_ids(opts.get("--stop-ids", ""), "--stop-ids")),
+                           ignore_eos="--ignore-eos" in opts)
+    for prompt, out in zip(prompts, engine.generate(prompts, go)):
+        print(json.dumps({"prompt_tokens": len(prompt), "token_ids": out.token_ids, "finish_reason": out.finish_reason}))
+    return 0
+
+
+def cmd_random_weights(opts) -> int:
+    from .weights.random_init import write_random_model
+    with open(_need(opts, "--config")) as f:
+        config = json.load(f)
+    out = write_random_model(_need(opts, "--out"), config, _int(opts, "--seed", 0), _float(opts, "--std", 0.02), _float(opts, "--norm-std", 0.0))
+    print(out)
+    return 0
+
+
+def cmd_replay(opts) -> int:
+    from .replay import main
+    args = []
+    for k, v in opts.items():
+        args += [k, v]
+    return main(args)
+
+
+def cmd_doctor(opts) -> int:
+    """One line per check; exit 1 when a check fails (src/Starlings.Roost.Server/RoostCli.cs:76-80)."""
+    _apply_common(opts)
+    ok = True
+
+    def line(name, good, detail):
+        nonlocal ok
+        ok = ok and good
+        print(f"{'ok  ' if good else 'FAIL'} {name}: {detail}")
+
+    from .kernels import build
+    try:
+        line("nvcc", True, build.find_nvcc())
+    except build.BuildError as e:
+        line("nvcc", False, str(e))
+    try:
+        line("kernel library", True, str(build.library_path()))
+    except Exception as e:  # noqa: BLE001
+        line("kernel library", False, str(e).splitlines()[0])
+    if "--no-gpu" not in opts:
+        import torch
+        if torch.cuda.is_available():
+            major, minor = torch.cuda.get_device_capability()
+            line("gpu", major == 10, f"{torch.cuda.get_device_name()} (sm_{major}{minor}); the library is built for sm_100a")
+            free, total = torch.cuda.mem_get_info()
+            want = _float(opts, "--min-free-memory-gib", 1.0)
+            line("device memory", free / 2**30 >= want, f"{free / 2**30:.1f} GiB free of {total / 2**30:.1f}")
+            try:
+                from .kernels import library
+                line("kernel ABI", True, f"version {library.load()._lib.roost_abi_version()}")
+            except Exception as e:  # noqa: BLE001
+                line("kernel ABI", False, str(e))
+        else:
+            line("gpu", False, "no CUDA device is visible")
+    if "--model" in opts:
+        try:
+            from .engine.model import parameter_declarations, read_model_config
+            from .weights import loader
+            from .weights.safetensors_io import SafetensorsFile
+            arch, cfg, _ = read_model_config(opts["--model"])
+            line("config.json", True, f"{arch.name}")
+            for w in getattr(cfg, "warnings", []):
+                print(f"note config.json: {w}")
+            tied = cfg.tie_word_embeddings
+            if tied is None:
+                tied = not loader.checkpoint_has(opts["--model"], "lm_head.weight")
+            spec = arch.to_spec(cfg, tied)
+            want = loader.expected_tensors(parameter_declarations(spec), spec.weight_names)
+            have = {}
+            for f in loader.checkpoint_files(opts["--model"]):
+                with SafetensorsFile(f) as st:
+                    have.update({n: tuple(e.shape) for n, e in st.entries.items()})
+            missing = [n for n in want if n not in have]
+            wrong = [n for n in want if n in have and have[n] != want[n]]
+            line("weights", not missing and not wrong, f"{len(want)} tensors wanted, {len(missing)} missing, {len(wrong)} of another shape")
+        except Exception as e:  # noqa: BLE001
+            line("model", False, str(e).splitlines()[0])
+    return 0 if ok else 1
+
+
+def main(argv=None) -> int:
+    argv = list(sys.argv[1:] if argv is None else argv)
+    try:
+        command, opts = parse(argv)
+        return {"generate": cmd_generate, "random-weights": cmd_random_weights, "replay": cmd_replay, "doctor": cmd_doctor}[command](opts)
+    except UsageError as e:
+        print(f"roost: {e}\n\nusage:\n{USAGE}", file=sys.stderr)
+        return 2
+
+
+if __name__ == "__main__":
+    sys.exit(main())

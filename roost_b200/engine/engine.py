@@ -1,0 +1,187 @@
+"""The Python entry point: token ids in, generated token ids out.
+
+``RoostEngine`` ties the parts together the way the reference's driver loop does
+(src/Starlings.Generation.Roost/Driver/WorkerDriver.cs:325-400): admit requests, ask the scheduler for a plan,
+run the plan through the step function, sample the rows that reach their last token, apply the tokens (which
+finishes requests and frees their pages), repeat. Its surface follows the reference's client
+(src/Starlings.Generation.Roost/RoostChatClient.cs:206-231,301-451): a raw completion over prompt token ids with
+options ``max_output_tokens``, ``temperature`` (unset means greedy, as the reference's chat API treats it,
+ChatRequestBuilder.cs:180), ``top_p``, ``top_k``, ``min_p``, ``seed``, ``stop_token_ids``; updates carry the
+new token, the last one a finish reason ("stop" or "length") and the usage counts. The reference ships no
+tokenizer in its repository, so token ids are the contract here; text goes in and out only when the caller
+passes a tokenizer object with ``encode`` and ``decode``.
+"""
+from __future__ import annotations
+
+import random
+from dataclasses import dataclass, field
+from typing import Iterator
+
+import torch
+
+from ..sampling.sampler import Sampler, SamplingRow
+from .executor import StepEntry, StepExecutor
+from .model import Model, load_model
+from .request import GREEDY, Request, RequestError, SamplingParameters, TokenEvent
+from .scheduler import Scheduler, SchedulerOptions, StepPlan
+
+
+@dataclass
+class GenerationOptions:
+    """Options of one completion, with the reference's names in snake case."""
+    max_output_tokens: int | None = None
+    temperature: float | None = None       # None or 0: greedy
+    top_p: float | None = None
+    top_k: int | None = None
+    min_p: float | None = None
+    seed: int | None = None
+    stop_token_ids: tuple = ()
+    ignore_eos: bool = False
+
+    def sampling(self) -> SamplingParameters:
+        return SamplingParameters(temperature=self.temperature or 0.0, top_p=1.0 if self.top_p is None else self.top_p,
+                                  top_k=0 if self.top_k in (None, -1) else self.top_k, min_p=self.min_p or 0.0, seed=self.seed,
+                                  max_tokens=self.max_output_tokens, ignore_eos=self.ignore_eos)
+
+
+@dataclass
+class CompletionUpdate:
+    request_id: object
+    token: int | None
+    finish_reason: str | None = None
+    prompt_tokens: int = 0
+    completion_tokens: int = 0
+
+
+@dataclass
+class Completion:
+    request_id: object
+    token_ids: list = field(default_factory=list)
+    finish_reason: str | None = None
+    prompt_tokens: int = 0
+
+
+class RoostEngine:
+    def __init__(self, model, *, dtype: str | torch.dtype = "bfloat16", device: str = "cuda", page_size: int = 16,
+                 attention_blocks: int | None = None, kv_fraction: float = 0.9, max_sequences: int = 64, max_tokens: int = 2048,
+                 max_chunk_tokens: int | None = None, seed: int | None = None):
+        """``model``: a folder with config.json and model.safetensors, or a built ``Model``. ``attention_blocks``:
+        pages in each paged pool (else ``kv_fraction`` of the free device memory); ``max_tokens`` and
+        ``max_sequences``: the largest token and row count of a step (the reference's worker flags of the same
+        names, src/Starlings.Roost.WorkerHost/WorkerArguments.cs:51-58)."""
+        if isinstance(dtype, str):
+            dtype = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}[dtype]
+        self.model: Model = model if isinstance(model, Model) else load_model(model, dtype, device)
+        self.executor = StepExecutor(self.model, page_size=page_size, num_pages=attention_blocks, max_requests=max_sequences,
+                                     kv_fraction=kv_fraction)
+        spec = self.model.spec
+        self.scheduler = Scheduler(self.executor.cache, SchedulerOptions(
+            max_tokens_per_step=max_tokens, max_sequences_per_step=max_sequences, max_chunk_tokens=max_chunk_tokens,
+            model_stop_token_ids=tuple(spec.stop_token_ids), max_context=spec.max_positions or None))
+        self.sampler = Sampler(self.model.rt.kernels, self.model.rt.device)
+        self._seed_source = random.Random(seed)
+        self._seeds: dict = {}
+        self._next_id = 0
+        self.steps = 0
+        self.last_plan: StepPlan | None = None
+
+    # ------------------------------------------------------------------ requests
+    def add_request(self, prompt_token_ids, sampling: SamplingParameters = GREEDY, *, request_id=None, stop_token_ids=(),
+                    priority: int = 0, deadline: float | None = None):
+        if request_id is None:
+            request_id = f"req-{self._next_id}"
+            self._next_id += 1
+        vocab = self.model.spec.vocab
+        for t in prompt_token_ids:
+            if not 0 <= int(t) < vocab:
+                raise RequestError("InvalidOption", f"prompt token id {t} is outside the vocabulary of {vocab}")
+        req = Request(request_id, [int(t) for t in prompt_token_ids], sampling, tuple(stop_token_ids), priority, deadline)
+        self.scheduler.add(req)
+        # a request without a seed gets an engine-chosen one (src/Starlings.Generation.Roost/RoostChatClient.cs:329)
+        self._seeds[request_id] = sampling.seed if sampling.seed is not None else self._seed_source.getrandbits(64)
+        return request_id
+
+    def cancel(self, request_id) -> bool:
+        self._seeds.pop(request_id, None)
+        return self.scheduler.cancel(request_id)
+
+    def has_unfinished(self) -> bool:
+        return self.scheduler.unfinished > 0
+
+    # ------------------------------------------------------------------ one engine step
+    def step(self) -> list[TokenEvent]:
+        """Plans, runs and applies one step; returns the tokens it produced (possibly none: a step of prompt
+        portions that reach no request's last token)."""
+        plan = self.scheduler.plan()
+        self.last_plan = plan
+        if plan is None:
+            return []
+        tokens = {}
+        if plan.rows:
+            entries = [StepEntry(r.sequence.request_id, r.tokens, [r.count - 1] if r.samples else [], r.start) for r in plan.rows]
+            logits = self.executor.step(entries)
+            sampling_rows = [r for r in plan.rows if r.samples]
+            if sampling_rows:
+                rows = [SamplingRow(r.sequence.request.sampling, self._seeds[r.sequence.request_id], r.sequence.generated)
+                        for r in sampling_rows]
+                ids = self.sampler(logits, rows).cpu().tolist()
+                tokens = {r.sequence.request_id: t for r, t in zip(sampling_rows, ids)}
+            self.steps += 1
+        events = self.scheduler.apply(plan, tokens)
+        for e in events:
+            if e.finish_reason is not None:
+                self._seeds.pop(e.request_id, None)
+        return events
+
+    # ------------------------------------------------------------------ completions
+    def generate(self, prompts: list, options: GenerationOptions | list | None = None) -> list[Completion]:
+        """Runs every prompt (a list of token ids each) to its end; results in the order of the prompts."""
+        if options is None:
+            options = GenerationOptions()
+        opts = options if isinstance(options, list) else [options] * len(prompts)
+        results = {}
+        order = []
+        for prompt, o in zip(prompts, opts):
+            rid = self.add_request(prompt, o.sampling(), stop_token_ids=o.stop_token_ids)
+            results[rid] = Completion(rid, [], None, len(prompt))
+            order.append(rid)
+        while any(results[r].finish_reason is None for r in order):
+            if not self.has_unfinished():
+                break
+            for e in self.step():
+                if e.request_id in results:
+                    if e.token is not None:
+                        results[e.request_id].token_ids.append(e.token)
+                    if e.finish_reason is not None:
+                        results[e.request_id].finish_reason = e.finish_reason
+        return [results[r] for r in order]
+
+    def stream_completion(self, prompt_token_ids, options: GenerationOptions | None = None) -> Iterator[CompletionUpdate]:
+        """One request, one update per generated token; the last update carries the finish reason and usage.
+        Other live requests keep running in the same steps."""
+        o = options or GenerationOptions()
+        rid = self.add_request(prompt_token_ids, o.sampling(), stop_token_ids=o.stop_token_ids)
+        produced = 0
+        done = False
+        while not done:
+            if not self.has_unfinished():
+                break
+            for e in self.step():
+                if e.request_id != rid:
+                    continue
+                if e.token is not None:
+                    produced += 1
+                done = e.finish_reason is not None
+                yield CompletionUpdate(rid, e.token, e.finish_reason, len(prompt_token_ids), produced)
+
+    def complete_text(self, tokenizer, prompt: str, options: GenerationOptions | None = None) -> str:
+        """Text in, text out, for a caller that brings a tokenizer (``encode(str) -> ids``, ``decode(ids) -> str``)."""
+        ids = tokenizer.encode(prompt)
+        ids = getattr(ids, "ids", ids)
+        out = self.generate([list(ids)], options)[0]
+        return tokenizer.decode(out.token_ids)
+
+    # ------------------------------------------------------------------ figures
+    def stats(self) -> dict:
+        return {"steps": self.steps, "kv_cache_usage": self.executor.cache.usage(), "preemptions": self.scheduler.preemption_count,
+                "kernel_launches": self.model.rt.kernels.launches}

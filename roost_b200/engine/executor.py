@@ -26,6 +26,7 @@ class StepEntry:
     request_id: object
     tokens: list
     want: list = field(default_factory=list)
+    start: int | None = None     # the position the caller believes the first token has; checked when given
 
 
 class StepError(ValueError):
@@ -56,6 +57,7 @@ class StepExecutor:
         self.storage = CacheStorage(self.groups, capacities, self.rt.dtype, self.rt.device)
         self.builder = BatchBuilder(self.rt.device, self.cache)
         self.steps_run = 0
+        self.last_upload_bytes = 0
 
     # ------------------------------------------------------------------ one step
     def step(self, entries: list[StepEntry]) -> torch.Tensor:
@@ -75,6 +77,8 @@ class StepExecutor:
                 if not 0 <= w < n:
                     raise StepError(f"request {e.request_id!r} wants offset {w} among {n} tokens")
             start = self.cache.get(e.request_id).tokens if e.request_id in self.cache else 0
+            if e.start is not None and e.start != start:
+                raise StepError(f"request {e.request_id!r}: the row starts at position {e.start} but the cache holds {start} tokens")
             plan.append((e, start, start + n))
         max_pos = self.model.spec.max_positions
         if max_pos:
@@ -102,6 +106,7 @@ class StepExecutor:
             for rid in new_requests:
                 self.cache.free(rid)
             raise
+        self.last_upload_bytes = batch.host_buffer.numel() * batch.host_buffer.element_size()
         self._zero_new_state(rows)
         logits = self.model.forward(batch, self.storage)
         for (e, _, end) in plan:

@@ -84,6 +84,12 @@ def _run(cmd: list[str], what: str) -> None:
 
 def library_path(verbose_ptxas: bool = False) -> Path:
     """Path of an up-to-date library, building it first when needed."""
+    given = os.environ.get("ROOST_KERNELS")  # a folder that already holds the library (the command line's --kernels)
+    if given:
+        lib = Path(given) / LIB_NAME
+        if not lib.exists():
+            raise BuildError(f"{lib}: no kernel library in the folder $ROOST_KERNELS names")
+        return lib
     out_dir = _build_dir()
     lib = out_dir / LIB_NAME
     stamp = out_dir / "stamp"

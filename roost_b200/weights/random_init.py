@@ -62,3 +62,28 @@ def write_random_model(model_dir, config: dict, seed: int, std: float = 0.02, no
     (model_dir / "config.json").write_text(json.dumps(config, indent=2) + "\n")
     write_safetensors(model_dir / "model.safetensors", tensors, metadata={"format": "pt", "seed": seed})
     return model_dir
+
+
+def random_parameters(spec, seed: int, device, dtype: torch.dtype, std: float = 0.02, norm_std: float = 0.0) -> dict:
+    """scope -> local name -> tensor, drawn on ``device`` in ``dtype`` without a file: the random-weights mode of
+    benchmarks, where a model of many gigabytes is made where it will live. Seeded per parameter like
+    ``random_tensors`` (the values differ from the file-writing mode, which draws on the host)."""
+    from ..engine.model import parameter_declarations
+    out: dict = {}
+    for scope, params in parameter_declarations(spec).items():
+        out[scope] = {}
+        for local, decl in params.items():
+            g = torch.Generator(device=device).manual_seed(_tensor_seed(seed, f"{scope}.{local}"))
+            if decl.role == "vector":
+                t = torch.ones(decl.shape, dtype=torch.float32, device=device)
+                if norm_std > 0:
+                    t += torch.randn(decl.shape, generator=g, dtype=torch.float32, device=device) * norm_std
+                out[scope][local] = t.to(dtype)
+            else:
+                t = torch.empty(decl.shape, dtype=dtype, device=device)
+                rows = max(1, (1 << 26) // max(1, t[0].numel()))  # draw in slabs: no float32 copy of a whole matrix
+                for r0 in range(0, decl.shape[0], rows):
+                    part = t[r0 : r0 + rows]
+                    part.copy_(torch.randn(part.shape, generator=g, dtype=torch.float32, device=device) * std)
+                out[scope][local] = t
+    return out
