@@ -23,7 +23,8 @@ F64 = torch.float64
 # --------------------------------------------------------------------------------------------------
 # weights on disk (a reader of its own: the product's reader is under test)
 # --------------------------------------------------------------------------------------------------
-_ST_DTYPES = {"F32": (torch.float32, 4), "BF16": (torch.bfloat16, 2), "F16": (torch.float16, 2), "F64": (torch.float64, 8)}
+_ST_DTYPES = {"F32": (torch.float32, 4), "BF16": (torch.bfloat16, 2), "F16": (torch.float16, 2), "F64": (torch.float64, 8),
+              "I64": (torch.int64, 8), "I32": (torch.int32, 4)}
 
 
 def read_safetensors(path) -> dict[str, torch.Tensor]:

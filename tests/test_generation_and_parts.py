@@ -1,0 +1,328 @@
+"""Generation through the entry point, each part alone, run orders that name a layer twice or share a cache, and a toy
+mixer with state of its own that is registered, built and stepped without a change to the framework's files."""
+import math
+from dataclasses import dataclass
+
+import pytest
+import torch
+
+from roost_b200 import GenerationOptions, RoostEngine
+from roost_b200.config.spec import (AttentionSpec, BlockSpec, GatedMlpSpec, MixerSpec, ModelSpec, NormSpec, PositionSpec, RunEntry)
+from roost_b200.engine.executor import StepEntry, StepExecutor
+from roost_b200.engine.model import Model, parameter_declarations
+from roost_b200.parts import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, CacheNeed, Linear, Mixer, ParamDecl, Runtime, register_mixer)
+from roost_b200.weights import loader
+from tests import helpers as H
+from tests.conftest import TINY
+from tests.plain import qwen3_plain as plain
+
+BACKENDS = [
+    pytest.param(("gpu", torch.float32), id="gpu-f32", marks=pytest.mark.gpu),
+    pytest.param(("gpu", torch.bfloat16), id="gpu-bf16", marks=pytest.mark.gpu),
+    pytest.param(("fake", torch.float32), id="cpu-fake"),
+]
+
+
+@pytest.fixture(params=BACKENDS)
+def backend(request):
+    return request.param
+
+
+def runtime(backend) -> Runtime:
+    kind, dtype = backend
+    if kind == "gpu":
+        from roost_b200.kernels import library
+        return Runtime(dtype, "cuda", library.load())
+    from tests.fake_kernels import FakeKernels
+    return Runtime(dtype, "cpu", FakeKernels())
+
+
+# ------------------------------------------------------------------------------------------ generation
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_greedy_generation_through_the_entry_point(tiny_model_dirs, backend, name):
+    kind, dtype = backend
+    t = TINY[name]
+    model = H.make_model(tiny_model_dirs[name], dtype, kind)
+    engine = RoostEngine(model, page_size=t["page_size"], attention_blocks=64, max_sequences=4, max_tokens=24)
+    V = t["config"]["vocab_size"]
+    prompts = [H.random_ids(n, V, 70 + n) for n in (7, 19, 33)]
+    outs = engine.generate(prompts, GenerationOptions(max_output_tokens=16, ignore_eos=True))
+    cfg, w = plain.load_model_dir(tiny_model_dirs[name])
+    if dtype == torch.bfloat16:
+        w = {k: (v.to(torch.bfloat16).double() if v.dim() >= 2 else v) for k, v in w.items()}
+    for prompt, out in zip(prompts, outs):
+        assert out.finish_reason == "length" and len(out.token_ids) == 16 and out.prompt_tokens == len(prompt)
+        # teacher-forced comparison: at every step the engine's token is the plain implementation's choice for the
+        # engine's own history, unless the plain top two are a near-tie
+        seq = list(prompt)
+        for tok in out.token_ids:
+            logits = plain.forward_logits(cfg, w, seq)[-1]
+            top = logits.topk(2)
+            gap = float(top.values[0] - top.values[1])
+            if gap > (1e-3 if dtype == torch.float32 else 0.15):
+                assert tok == int(top.indices[0]), f"step {len(seq) - len(prompt)}: engine {tok}, plain {int(top.indices[0])} (gap {gap:.3g})"
+            seq.append(tok)
+    assert engine.executor.cache.pools[0].free_count == 64       # every page came back
+    # the same prompts one at a time give the same tokens as the batch did
+    alone = [engine.generate([p], GenerationOptions(max_output_tokens=16, ignore_eos=True))[0].token_ids for p in prompts]
+    if dtype == torch.float32:
+        assert alone == [o.token_ids for o in outs]
+
+
+def test_sampled_generation_is_seeded_and_stops(tiny_model_dirs, backend):
+    kind, dtype = backend
+    t = TINY["B"]
+    model = H.make_model(tiny_model_dirs["B"], dtype, kind)
+    engine = RoostEngine(model, page_size=t["page_size"], attention_blocks=64, max_sequences=8, max_tokens=64)
+    V = t["config"]["vocab_size"]
+    prompts = [H.random_ids(n, V, 90 + n) for n in (1, 4, 17, 40, 64)]
+    opts = [GenerationOptions(max_output_tokens=24, temperature=0.8, top_p=0.9, seed=1000 + i) for i in range(5)]
+    a = engine.generate(prompts, opts)
+    b = engine.generate(prompts, opts)
+    assert [o.token_ids for o in a] == [o.token_ids for o in b]
+    c = engine.generate(prompts[2:3], opts[2:3])                 # alone: the draw does not depend on the batch
+    if dtype == torch.float32:
+        assert c[0].token_ids == a[2].token_ids
+    other = engine.generate(prompts[2:3], [GenerationOptions(max_output_tokens=24, temperature=0.8, top_p=0.9, seed=5)])
+    assert other[0].token_ids != a[2].token_ids
+    # the model's stop ids (eos_token_id of config.json) end a request with "stop" unless ignored
+    assert all(o.finish_reason in ("stop", "length") for o in a)
+    for o in a:
+        if o.finish_reason == "stop":
+            assert o.token_ids[-1] in (5, 7) and not any(x in (5, 7) for x in o.token_ids[:-1])
+    stop = a[3].token_ids[2]
+    s = engine.generate(prompts[3:4], [GenerationOptions(max_output_tokens=24, temperature=0.8, top_p=0.9, seed=1003, stop_token_ids=(stop,))])
+    assert s[0].finish_reason == "stop" and s[0].token_ids == a[3].token_ids[: a[3].token_ids.index(stop) + 1]
+    updates = list(engine.stream_completion(prompts[1], GenerationOptions(max_output_tokens=5, ignore_eos=True)))
+    assert [u.completion_tokens for u in updates] == [1, 2, 3, 4, 5] and updates[-1].finish_reason == "length"
+
+
+def test_generation_with_preemption_gives_the_same_tokens(tiny_model_dirs, backend):
+    kind, dtype = backend
+    if dtype != torch.float32:
+        pytest.skip("compared token for token: float32 only")
+    t = TINY["A"]
+    model = H.make_model(tiny_model_dirs["A"], dtype, kind)
+    V = t["config"]["vocab_size"]
+    prompts = [H.random_ids(n, V, 30 + n) for n in (30, 28, 26)]
+    opt = GenerationOptions(max_output_tokens=30, ignore_eos=True)
+    roomy = RoostEngine(model, page_size=16, attention_blocks=64, max_sequences=4, max_tokens=64)
+    want = [o.token_ids for o in roomy.generate(prompts, opt)]
+    tight = RoostEngine(model, page_size=16, attention_blocks=9, max_sequences=4, max_tokens=64)   # 144 tokens for 3 x ~60
+    got = [o.token_ids for o in tight.generate(prompts, opt)]
+    assert tight.stats()["preemptions"] > 0, "the pool is too large for this test"
+    assert got == want
+    tight.executor.cache.check_invariants()
+
+
+# ------------------------------------------------------------------------------------------ each part alone
+def test_norm_part_alone(backend):
+    rt = runtime(backend)
+    norm = NORMS.build(NormSpec(size=72, eps=1e-5), rt)
+    g = torch.Generator().manual_seed(0)
+    w = 1 + 0.1 * torch.randn(72, generator=g)
+    x = torch.randn(5, 72, generator=g).to(rt.dtype)
+    res = torch.randn(5, 72, generator=g).to(rt.dtype)
+    norm.load({"weight": w.to(rt.device)})
+    y = norm(x.to(rt.device))
+    want = plain.rms_norm(x.double(), w.double(), 1e-5)
+    assert H.scaled_error(y, want) < (2e-6 if rt.full_precision else 2 ** -7)
+    y2, r2 = norm.add_norm(x.to(rt.device), res.to(rt.device).clone())
+    s = (x.float() + res.float()).to(rt.dtype)
+    assert torch.equal(r2.cpu(), s)
+    assert H.scaled_error(y2, plain.rms_norm(s.double(), w.double(), 1e-5)) < (2e-6 if rt.full_precision else 2 ** -7)
+
+
+def test_feed_forward_part_alone(backend):
+    rt = runtime(backend)
+    spec = GatedMlpSpec(hidden=40, intermediate=104)
+    ff = FEED_FORWARDS.build(spec, rt)
+    g = torch.Generator().manual_seed(1)
+    gate_up = (torch.randn(208, 40, generator=g) * 0.2).to(rt.dtype)
+    down = (torch.randn(40, 104, generator=g) * 0.2).to(rt.dtype)
+    ff.load({"gate_up": gate_up.to(rt.device), "down": down.to(rt.device)})
+    x = torch.randn(9, 40, generator=g).to(rt.dtype)
+    want = plain.swiglu_mlp(x.double(), gate_up[:104].double(), gate_up[104:].double(), down.double())
+    assert H.scaled_error(ff(x.to(rt.device), None), want) < (5e-6 if rt.full_precision else 2 ** -5)
+    assert FEED_FORWARDS.get("gated_mlp").parameters(spec)["gate_up"].row_splits == (104, 104)
+    with pytest.raises(ValueError, match="activation"):
+        FEED_FORWARDS.build(GatedMlpSpec(hidden=8, intermediate=8, activation="gelu"), rt)
+
+
+def attention_spec(window=None, position=True):
+    return AttentionSpec(hidden=48, num_heads=6, num_kv_heads=2, head_dim=16, scale=0.25, window=window,
+                         qk_norm=NormSpec(size=16, eps=1e-6), position=PositionSpec(rotary_dim=16, theta=1e4) if position else None)
+
+
+@pytest.mark.parametrize("window", [None, 9])
+def test_attention_mixer_alone_whole_and_in_portions(backend, window):
+    """The mixer as a one-part model: pages, rotation and window through the step function, against the plain mixer."""
+    rt = runtime(backend)
+    spec = attention_spec(window)
+    mixer = MIXERS.build(spec, rt)
+    g = torch.Generator().manual_seed(2)
+    qkv = (torch.randn(160, 48, generator=g) * 0.3).to(rt.dtype)
+    out = (torch.randn(48, 96, generator=g) * 0.2).to(rt.dtype)
+    qn, kn = 1 + 0.1 * torch.randn(16, generator=g), 1 + 0.1 * torch.randn(16, generator=g)
+    mixer.load({"qkv": qkv.to(rt.device), "out": out.to(rt.device), "q_norm": qn.to(rt.device), "k_norm": kn.to(rt.device)})
+    assert mixer.cache_need() == CacheNeed("paged", kv_heads=2, head_dim=16, window=window)
+    T = 37
+    x = torch.randn(T, 48, generator=g).to(rt.dtype)
+    w = {"q_proj.weight": qkv[:96].double(), "k_proj.weight": qkv[96:128].double(), "v_proj.weight": qkv[128:].double(),
+         "o_proj.weight": out.double(), "q_norm.weight": qn.double(), "k_norm.weight": kn.double()}
+    cfg = dict(num_attention_heads=6, num_key_value_heads=2, head_dim=16, rms_norm_eps=1e-6, rope_theta=1e4)
+    want, _ = plain.attention_mixer(x.double(), list(range(T)), w, "", cfg, window)
+
+    from roost_b200.cache.manager import CacheManager, build_groups
+    from roost_b200.cache.storage import CacheStorage
+    from roost_b200.engine.batch import BatchBuilder
+    groups = build_groups([mixer.cache_need()], page_size=4)
+    cm = CacheManager(groups, [12, 2])
+    storage = CacheStorage(groups, [12, 2], rt.dtype, rt.device)
+    builder = BatchBuilder(rt.device, cm)
+    outs, at = [], 0
+    for n in (11, 2, 24):
+        rc = cm.extend("r", at + n)
+        batch = builder.build([(rc, at, [0] * n, [])], vocab=1)
+        outs.append(mixer(x[at : at + n].to(rt.device), batch, storage.view(0)))
+        at += n
+        cm.commit("r", at)
+    assert H.scaled_error(torch.cat(outs), want) < (5e-6 if rt.full_precision else 2 ** -5)
+
+
+def test_parts_refuse_sizes_no_kernel_serves(backend):
+    rt = runtime(backend)
+    with pytest.raises(ValueError, match="multiple"):
+        MIXERS.build(AttentionSpec(hidden=8, num_heads=3, num_kv_heads=2, head_dim=16, scale=1.0), rt)
+    with pytest.raises(ValueError, match="head_dim"):
+        MIXERS.build(AttentionSpec(hidden=8, num_heads=2, num_kv_heads=1, head_dim=1024, scale=1.0), rt)
+    with pytest.raises(KeyError, match="registered"):
+        MIXERS.build(MixerSpec(kind="nonesuch"), rt)
+    with pytest.raises(ValueError):
+        NORMS.build(NormSpec(size=8, eps=0.0), rt)
+
+
+# ------------------------------------------------------------------------------------------ run order as data
+@pytest.mark.parametrize("schedule", [[(0, None), (1, None), (0, None)], [(0, None), (1, None), (0, 0), (1, 1)], [(1, None), (0, None)]])
+def test_a_layer_may_run_twice_or_read_another_runs_cache(tiny_model_dirs, backend, schedule):
+    kind, dtype = backend
+    from dataclasses import replace
+    model_dir = tiny_model_dirs["A"]
+    base = H.make_model(model_dir, dtype, kind)
+    spec = replace(base.spec, schedule=tuple(RunEntry(b, r) for b, r in schedule))
+    model = Model(spec, base.rt)
+    allow = ("lm_head.weight",)
+    model.load(loader.load_checkpoint(model_dir, parameter_declarations(spec), spec.weight_names, allow_unexpected=allow))
+    ex = StepExecutor(model, page_size=16, num_pages=16, max_requests=2)
+    owners = [i for i, (_, r) in enumerate(schedule) if r is None]
+    assert ex.groups[0].runs == tuple(owners)                    # a run that reads another's cache keeps none
+    ids = H.random_ids(41, 256, 5)
+    want = H.plain_logits(model_dir, ids, bf16=dtype == torch.bfloat16, schedule=schedule)
+    got = H.run_portions(ex, "r", ids, [17, 2, 9])
+    assert H.scaled_error(got, want) < H.bound_for(dtype)
+    got = H.run_tail_decoded(ex, "r", ids, tail=8)
+    assert H.scaled_error(got, want) < H.bound_for(dtype)
+
+
+# ------------------------------------------------------------------------------------------ a toy mixer with state of its own
+@dataclass(frozen=True)
+class ToyStateSpec(MixerSpec):
+    kind: str = "toy_running_mean"
+    hidden: int = 0
+    decay: float = 0.5
+
+
+class ToyRunningMean(Mixer):
+    """state <- decay * state + (1 - decay) * (x W^T), token by token; the output is the state. The state is one
+    vector per live request, kept in a slot of the cache manager's fixed-size state group between steps."""
+
+    def __init__(self, spec, rt):
+        self.spec, self.rt = spec, rt
+        self.proj = Linear(rt, spec.hidden, spec.hidden)
+
+    @classmethod
+    def parameters(cls, spec):
+        return {"proj": ParamDecl(shape=(spec.hidden, spec.hidden))}
+
+    def load(self, params):
+        self.proj.load(params["proj"])
+
+    def cache_need(self):
+        return CacheNeed("state", state_shape=(self.spec.hidden,), state_dtype=torch.float32)
+
+    def __call__(self, x, batch, cache, write_cache=True):
+        u = self.proj(x).float()
+        out = torch.empty_like(u)
+        slots = batch.groups[cache.group].state_slots.tolist()
+        at = 0
+        for b, n in enumerate(batch.row_counts):
+            s = cache.state[slots[b]].clone()
+            for i in range(n):
+                s = self.spec.decay * s + (1 - self.spec.decay) * u[at + i]
+                out[at + i] = s
+            cache.state[slots[b]] = s
+            at += n
+        return out.to(x.dtype)
+
+
+def toy_plain(x, w, decay):
+    u = x @ w.T
+    s = torch.zeros(w.shape[0], dtype=torch.float64)
+    out = []
+    for t in range(x.shape[0]):
+        s = decay * s + (1 - decay) * u[t]
+        out.append(s)
+    return torch.stack(out)
+
+
+def test_a_toy_mixer_with_its_own_state_is_registered_built_and_stepped(backend):
+    register_mixer("toy_running_mean", ToyRunningMean)
+    rt = runtime(backend)
+    H_, V, I = 32, 50, 48
+    norm = NormSpec(size=H_, eps=1e-6)
+    attn = AttentionSpec(hidden=H_, num_heads=2, num_kv_heads=1, head_dim=16, scale=0.25, qk_norm=None,
+                         position=PositionSpec(rotary_dim=16, theta=100.0))
+    ff = GatedMlpSpec(hidden=H_, intermediate=I)
+    blocks = (BlockSpec(mixer=ToyStateSpec(hidden=H_, decay=0.75), feed_forward=ff, input_norm=norm, post_mixer_norm=norm),
+              BlockSpec(mixer=attn, feed_forward=ff, input_norm=norm, post_mixer_norm=norm))
+    spec = ModelSpec(architecture="ToyForTests", hidden=H_, vocab=V, blocks=blocks, schedule=(RunEntry(0), RunEntry(1), RunEntry(0)),
+                     final_norm=norm, tie_embeddings=True, max_positions=0)
+    model = Model(spec, rt)
+    assert [n.kind if n else None for n in model.cache_needs] == ["state", "paged", "state"]
+    g = torch.Generator().manual_seed(3)
+    params = {}
+    for scope, decl in parameter_declarations(spec).items():
+        params[scope] = {k: (torch.ones(d.shape) if d.role == "vector" else torch.randn(d.shape, generator=g) * 0.2).to(rt.dtype) for k, d in decl.items()}
+    model.load(params)
+    ex = StepExecutor(model, page_size=4, num_pages=40, max_requests=3)
+    assert [(g_.kind, g_.runs) for g_ in ex.groups] == [("paged", (1,)), ("state", (0, 2))]
+
+    def plain_forward(ids):
+        P = {s: {k: v.double() for k, v in p.items()} for s, p in params.items()}
+        h = P["embed"]["table"][torch.tensor(ids)]
+        pos = list(range(len(ids)))
+        for bi in (0, 1, 0):
+            x = plain.rms_norm(h, P[f"blocks.{bi}.input_norm"]["weight"], 1e-6)
+            if bi == 0:
+                mix = toy_plain(x, P["blocks.0.mixer"]["proj"], 0.75)
+            else:
+                qkv = P["blocks.1.mixer"]["qkv"]
+                q = plain.rope_neox((x @ qkv[:32].T).reshape(-1, 2, 16), pos, 100.0)
+                k = plain.rope_neox((x @ qkv[32:48].T).reshape(-1, 1, 16), pos, 100.0)
+                v = (x @ qkv[48:].T).reshape(-1, 1, 16)
+                mix = plain.causal_gqa_attention(q, k, v, 0.25).reshape(-1, 32) @ P["blocks.1.mixer"]["out"].T
+            h = h + mix
+            y = plain.rms_norm(h, P[f"blocks.{bi}.post_mixer_norm"]["weight"], 1e-6)
+            gu = P[f"blocks.{bi}.feed_forward"]["gate_up"]
+            h = h + plain.swiglu_mlp(y, gu[:I], gu[I:], P[f"blocks.{bi}.feed_forward"]["down"])
+        return plain.rms_norm(h, P["final_norm"]["weight"], 1e-6) @ P["embed"]["table"].T
+
+    a, b = H.random_ids(23, V, 1), H.random_ids(15, V, 2)
+    bound = 2e-5 if rt.full_precision else H.BF16_BOUND
+    got = H.run_mixed(ex, {"a": a, "b": b}, seed=3, max_live=2, decode_tail=4)
+    assert H.scaled_error(got["a"], plain_forward(a)) < bound
+    assert H.scaled_error(got["b"], plain_forward(b)) < bound
+    # a slot that is used again starts from zero: the next request does not see the last one's state
+    got = H.run_portions(ex, "c", b, [4, 2, 9])
+    assert H.scaled_error(got, plain_forward(b)) < bound
+    assert ex.cache.pools[1].free_count == 3
