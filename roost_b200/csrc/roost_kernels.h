@@ -70,6 +70,22 @@ int roost_paged_attention_generic(const void* q, void* out, const void* k_pool, 
                                   const int32_t* kv_indices, int tokens, int q_heads, int kv_heads, int head_dim,
                                   int page_size, float scale, int window, int dtype, roost_stream_t stream);
 
+/* Tensor-core attention for bfloat16 (attention_mma.cu). head_dim must be one roost_attention_mma_supported accepts.
+ * q_indptr[b] .. q_indptr[b+1] are row b's tokens, kv_lens[b] its keys after this step.
+ * prefill work: int32 pairs (batch row, first packed row of a 64-row tile), packed row = token * group + head.
+ * decode work: int32 quadruples (batch row, first key, one past the last key, partial slot or -1); rows with at most
+ * 16 packed rows only. merge_work: quadruples (batch row, first slot, chunks, 0) for rows split into several chunks.
+ * part_o: float[slots * kv_heads * 16 * head_dim], part_ml: float[slots * kv_heads * 16 * 2]. */
+int roost_attention_mma_supported(int head_dim);
+int roost_attention_prefill(const void* q, void* out, const void* k_pool, const void* v_pool, const int32_t* q_indptr,
+                            const int32_t* kv_lens, const int32_t* kv_indptr, const int32_t* kv_indices, const int32_t* work,
+                            int items, int q_heads, int kv_heads, int head_dim, int page_size, float scale, int window,
+                            roost_stream_t stream);
+int roost_attention_decode(const void* q, void* out, const void* k_pool, const void* v_pool, const int32_t* q_indptr,
+                           const int32_t* kv_lens, const int32_t* kv_indptr, const int32_t* kv_indices, const int32_t* work,
+                           int items, const int32_t* merge_work, int merge_items, float* part_o, float* part_ml, int q_heads,
+                           int kv_heads, int head_dim, int page_size, float scale, int window, roost_stream_t stream);
+
 /* out[m,n] = sum_k a[m,k] * w[n,k], plain FFMA in 32-bit (no tensor cores, no reduced-precision mode), the
  * sum over k in increasing order for every output, whatever m is. in_dtype/out_dtype: 0 or 1. */
 int roost_gemm_simt(const void* a, const void* w, void* out, int m, int n, int k, int64_t lda, int64_t ldw,

@@ -46,6 +46,65 @@ class StepBatch:
     max_kv_len: int = 0
     all_single: bool = False     # every row brings exactly one token
     host_buffer: object = None   # the pinned staging buffer, kept until the step is done
+    attention_plans: dict = field(default_factory=dict)   # (group size, window, chunk) -> AttentionPlan, made by the first mixer that asks
+
+    def attention_plan(self, group: int, window: int | None, chunk: int) -> "AttentionPlan":
+        key = (group, window, chunk)
+        plan = self.attention_plans.get(key)
+        if plan is None:
+            plan = plan_attention(self.row_starts, self.row_counts, group, window, chunk, self.ids.device)
+            self.attention_plans[key] = plan
+        return plan
+
+
+@dataclass
+class AttentionPlan:
+    """How the tensor-core attention kernels divide a step's rows (see csrc/attention_mma.cu): rows with at most 16
+    packed rows (tokens x query heads per key/value head) go to the decode kernel in chunks of a fixed number of
+    keys, the others to the prefill kernel in tiles of 64 packed rows."""
+    prefill_items: int = 0
+    decode_items: int = 0
+    merge_items: int = 0
+    slots: int = 0
+    prefill_work: torch.Tensor | None = None
+    decode_work: torch.Tensor | None = None
+    merge_work: torch.Tensor | None = None
+
+
+def plan_attention(row_starts, row_counts, group: int, window: int | None, chunk: int, device) -> AttentionPlan:
+    prefill, decode, merge = [], [], []
+    slots = 0
+    for b, (start, n) in enumerate(zip(row_starts, row_counts)):
+        rows, kv_len = n * group, start + n
+        if rows <= 16:
+            lo = max(0, start - window + 1) if window else 0
+            first = (lo // chunk) * chunk
+            begins = list(range(first, kv_len, chunk))
+            if len(begins) == 1:
+                decode += [b, first, min(first + chunk, kv_len), -1]
+            else:
+                merge += [b, slots, len(begins), 0]
+                for c in begins:
+                    decode += [b, c, min(c + chunk, kv_len), slots]
+                    slots += 1
+        else:
+            # tiles with the longest history first: they run longest
+            for r0 in range(0, rows, 64):
+                prefill += [b, r0]
+    np_, nd, nm = len(prefill) // 2, len(decode) // 4, len(merge) // 4
+    pad = lambda a: a + [0] * (-len(a) % 4)  # noqa: E731  (16-byte aligned sections)
+    flat = pad(prefill) + pad(decode) + pad(merge)
+    plan = AttentionPlan(prefill_items=np_, decode_items=nd, merge_items=nm, slots=slots)
+    if flat:
+        host = torch.tensor(flat, dtype=torch.int32)
+        if torch.device(device).type == "cuda":
+            host = host.pin_memory()
+        dev = host.to(device, non_blocking=True)
+        a = len(pad(prefill))
+        b_ = a + len(pad(decode))
+        plan.prefill_work, plan.decode_work, plan.merge_work = dev[:a], dev[a:b_], dev[b_:]
+        plan.host = host
+    return plan
 
 
 class BatchBuilder:

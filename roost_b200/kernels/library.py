@@ -56,6 +56,11 @@ _SIGNATURES = {
                                  c_void_p],
     "roost_paged_attention_generic": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                       c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p],
+    "roost_attention_mma_supported": [c_int],
+    "roost_attention_prefill": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                c_int, c_int, c_int, c_float, c_int, c_void_p],
+    "roost_attention_decode": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                               c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
     "roost_gemm_simt": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int, c_int, c_void_p],
     "roost_argmax": [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p],
     "roost_sample": [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -76,6 +81,7 @@ class KernelLibrary:
             fn = getattr(self._lib, name)
             fn.argtypes = args
             fn.restype = c_int
+        self.decode_chunk = 256  # keys per CTA of the split decode attention; fixed, so results do not depend on the batch
         self.launches = 0  # kernels launched through this handle (a host-side count of entry-point calls that launch)
 
     def _call(self, name: str, *args, launches: int = 1):
@@ -163,6 +169,34 @@ class KernelLibrary:
         self._call("roost_paged_attention_generic", _ptr(q), _ptr(out), _ptr(k_pool), _ptr(v_pool), _ptr(positions),
                    _ptr(token_row), _ptr(kv_indptr), _ptr(kv_indices), T, nq, nkv, d, page, scale,
                    int(window) if window else 0, dtype_code(q.dtype), _stream())
+        return out
+
+    def attention_mma_supported(self, head_dim: int) -> bool:
+        return bool(self._lib.roost_attention_mma_supported(int(head_dim)))
+
+    def attention_mma(self, q, k_pool, v_pool, q_indptr, kv_lens, kv_indptr, kv_indices, plan, scale: float,
+                      window: int | None) -> torch.Tensor:
+        """Tensor-core attention (bfloat16). ``plan``: an ``AttentionPlan`` whose work lists are on the device."""
+        _need(q, "q", torch.bfloat16); _need(k_pool, "k_pool", torch.bfloat16); _need(v_pool, "v_pool", torch.bfloat16)
+        T, nq, d = q.shape
+        _, nkv, page, d2 = k_pool.shape
+        if d2 != d:
+            raise KernelError("attention_mma: head_dim of q and of the pool differ")
+        out = torch.empty((T, nq * d), dtype=q.dtype, device=q.device)
+        w = int(window) if window else 0
+        if plan.prefill_items:
+            self._call("roost_attention_prefill", _ptr(q), _ptr(out), _ptr(k_pool), _ptr(v_pool), _ptr(q_indptr), _ptr(kv_lens),
+                       _ptr(kv_indptr), _ptr(kv_indices), _ptr(plan.prefill_work), plan.prefill_items, nq, nkv, d, page, scale, w,
+                       _stream())
+        if plan.decode_items:
+            part_o = part_ml = None
+            if plan.slots:
+                part_o = torch.empty((plan.slots * nkv * 16 * d,), dtype=torch.float32, device=q.device)
+                part_ml = torch.empty((plan.slots * nkv * 16 * 2,), dtype=torch.float32, device=q.device)
+            self._call("roost_attention_decode", _ptr(q), _ptr(out), _ptr(k_pool), _ptr(v_pool), _ptr(q_indptr), _ptr(kv_lens),
+                       _ptr(kv_indptr), _ptr(kv_indices), _ptr(plan.decode_work), plan.decode_items, _ptr(plan.merge_work),
+                       plan.merge_items, _ptr(part_o), _ptr(part_ml), nq, nkv, d, page, scale, w, _stream(),
+                       launches=2 if plan.merge_items else 1)
         return out
 
     def gemm_simt(self, a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:

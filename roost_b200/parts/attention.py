@@ -91,7 +91,13 @@ class PagedAttention(Mixer):
         return self.out(o)
 
     def attend(self, q, batch, cache, tables):
+        """bfloat16 with a head size the tensor-core kernels serve goes to them; float32 and every other head size
+        run the 32-bit kernel, which takes any size."""
         s, k = self.spec, self.rt.kernels
+        if q.dtype == torch.bfloat16 and getattr(k, "attention_mma_supported", lambda d: False)(s.head_dim):
+            plan = batch.attention_plan(s.num_heads // s.num_kv_heads, s.window, k.decode_chunk)
+            return k.attention_mma(q, cache.k_pool, cache.v_pool, batch.q_indptr, batch.kv_lens, tables.kv_indptr,
+                                   tables.kv_indices, plan, s.scale, s.window)
         return k.paged_attention_generic(q, cache.k_pool, cache.v_pool, batch.positions, batch.token_row,
                                          tables.kv_indptr, tables.kv_indices, s.scale, s.window)
 

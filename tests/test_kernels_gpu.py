@@ -270,3 +270,90 @@ def test_sampler_matches_the_plain_sampler(kernels, vocab):
     # a row's token does not depend on the batch it is in
     one = kernels.sample(logits[7:8].cuda(), t[7:8].cuda(), k[7:8].cuda(), p[7:8].cuda(), mp[7:8].cuda(), seeds[7:8].cuda(), offsets[7:8].cuda())
     assert one.cpu().tolist() == [got[7]]
+
+
+# ------------------------------------------------------------------------------------------ tensor-core attention (bfloat16)
+def run_mma(kernels, q, kp, vp, lens, news, indptr, indices, scale, window, chunk=None):
+    from roost_b200.engine.batch import plan_attention
+    nq, nkv = q.shape[1], kp.shape[1]
+    starts = [n - m for n, m in zip(lens, news)]
+    plan = plan_attention(starts, news, nq // nkv, window, chunk or kernels.decode_chunk, "cuda")
+    q_indptr = torch.tensor([0] + list(torch.tensor(news).cumsum(0)), dtype=torch.int32).cuda()
+    kv_lens = torch.tensor(lens, dtype=torch.int32).cuda()
+    return kernels.attention_mma(q.cuda(), kp, vp, q_indptr, kv_lens, indptr, indices, plan, scale, window), plan
+
+
+MMA_SHAPES = [(4, 2, 16, 16), (6, 1, 32, 8), (8, 2, 128, 16), (14, 2, 64, 32), (2, 1, 256, 16), (16, 1, 64, 16), (40, 2, 128, 16)]
+
+
+@pytest.mark.parametrize("window", [None, 37, 300])
+@pytest.mark.parametrize("nq,nkv,d,page", MMA_SHAPES)
+def test_attention_mma_mixed_rows(kernels, window, nq, nkv, d, page):
+    """A whole prompt, a portion in the middle of a request, a two-token portion after a long history, single decoded
+    tokens after short and long histories (several chunks of the split decode kernel), all in one launch."""
+    dtype = torch.bfloat16
+    g = torch.Generator().manual_seed(21)
+    lens = [45, 233, 700, 19, 1000, 257]
+    news = [45, 121, 2, 1, 1, 1]
+    keys = [torch.randn(n, nkv, d, generator=g).to(dtype).double() for n in lens]
+    values = [torch.randn(n, nkv, d, generator=g).to(dtype).double() for n in lens]
+    positions, rows = [], []
+    for b, (n, m) in enumerate(zip(lens, news)):
+        positions += list(range(n - m, n))
+        rows += [b] * m
+    q = (torch.randn(len(positions), nq, d, generator=g) * 1.5).to(dtype)
+    kp, vp, indptr, indices = build_paged(keys, values, page, dtype, num_pages=sum(-(-n // page) for n in lens) + 5, seed=22)
+    scale = 1 / math.sqrt(d)
+    out, plan = run_mma(kernels, q, kp, vp, lens, news, indptr, indices, scale, window)
+    assert plan.prefill_items > 0 and (nq // nkv > 16 or (plan.decode_items > 0 and plan.merge_items > 0))
+    want = paged_reference(q.double(), keys, values, positions, rows, scale, window)
+    assert not torch.isnan(out.float()).any(), "a slot outside the rows' visible keys was read"
+    # the softmax weights are rounded to bfloat16 for the second product: 2^-8 of the values' size on top of the
+    # output's own rounding (the reference's attention tolerance, 2^-7 rtol + 2^-8 max|V|, op-class-tolerances)
+    close(out, want, dtype, f"attention_mma window={window}", scale=2)
+    # the 32-bit kernel gives the same answer within the same bound
+    generic = kernels.paged_attention_generic(q.cuda(), kp, vp, torch.tensor(positions, dtype=torch.int32).cuda(),
+                                              torch.tensor(rows, dtype=torch.int32).cuda(), indptr, indices, scale, window)
+    close(out, generic.double(), dtype, "attention_mma against the 32-bit kernel", scale=2)
+
+
+@pytest.mark.parametrize("case", ["far key", "first key", "page edge", "chunk edge", "window edge in", "window edge out"])
+@pytest.mark.parametrize("queries", [1, 40])
+def test_attention_mma_finds_the_one_key_that_matters(kernels, case, queries):
+    dtype = torch.bfloat16
+    nq, nkv, d, page, n = 4, 2, 64, 16, 700
+    window = 50 if case.startswith("window") else None
+    last = n - 1
+    target = {"far key": 3, "first key": 0, "page edge": 16 * 20 - 1, "chunk edge": 256, "window edge in": last - 49, "window edge out": last - 50}[case]
+    g = torch.Generator().manual_seed(23)
+    keys = torch.randn(n, nkv, d, generator=g) * 0.1
+    values = torch.randn(n, nkv, d, generator=g)
+    q = torch.randn(queries, nq, d, generator=g) * 0.1
+    direction = torch.nn.functional.normalize(torch.randn(d, generator=g), dim=0)
+    keys[target] = direction * 8.0
+    q[-1, :] = direction * 16.0
+    keys_d, values_d = keys.to(dtype).double(), values.to(dtype).double()
+    kp, vp, indptr, indices = build_paged([keys_d], [values_d], page, dtype, num_pages=-(-n // page) + 2, seed=24)
+    out, _ = run_mma(kernels, q.to(dtype), kp, vp, [n], [queries], indptr, indices, 1 / math.sqrt(d), window)
+    positions = list(range(n - queries, n))
+    want = paged_reference(q.to(dtype).double(), [keys_d], [values_d], positions, [0] * queries, 1 / math.sqrt(d), window)
+    close(out, want, dtype, f"{case} x{queries}", scale=4)
+    got_v = out[-1].double().cpu().reshape(nq, d)
+    hit = (got_v - values_d[target][torch.arange(nq) // 2]).abs().max() < 0.05
+    assert hit == (case != "window edge out"), f"{case}: the last query's output {'is' if hit else 'is not'} the target's value"
+
+
+def test_attention_mma_rows_do_not_depend_on_the_batch(kernels):
+    """A decode row alone and the same row among others: the same bits (the chunk size is fixed, so is every sum's order)."""
+    dtype = torch.bfloat16
+    nq, nkv, d, page = 8, 2, 128, 16
+    g = torch.Generator().manual_seed(25)
+    lens = [900, 300, 1200]
+    keys = [torch.randn(n, nkv, d, generator=g).to(dtype).double() for n in lens]
+    values = [torch.randn(n, nkv, d, generator=g).to(dtype).double() for n in lens]
+    q = torch.randn(3, nq, d, generator=g).to(dtype)
+    kp, vp, indptr, indices = build_paged(keys, values, page, dtype, num_pages=200, seed=26)
+    together, _ = run_mma(kernels, q, kp, vp, lens, [1, 1, 1], indptr, indices, 0.1, None)
+    alone, _ = run_mma(kernels, q[2:3], kp, vp, lens[2:], [1], torch.tensor([0, int(indptr[3] - indptr[2])], dtype=torch.int32).cuda(),
+                       indices[int(indptr[2]):].contiguous(), 0.1, None)
+    assert torch.equal(together[2:3], alone)
