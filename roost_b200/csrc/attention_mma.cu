@@ -527,3 +527,75 @@ extern "C" int roost_attention_decode(const void* q, void* out, const void* k_po
                                                                 scale, window, (cudaStream_t)stream));
   return ROOST_OK;
 }
+
+// ------------------------------------------------------------------------------------------------ no-allocation variant
+// roost_attention_decode_static: the split decode attention for callers that cannot give it a workspace.
+// (This entry point has no counterpart in the reference; see its declaration in roost_kernels.h.)
+//
+// Some hosts of this library may not allocate device memory while they run: a server that handed the whole GPU to
+// its own arena at start-up and has nothing left for cudaMalloc, a step loop that must never synchronise the device
+// (cudaMalloc and cudaFree do), a plug-in that is forbidden to grow its process's footprint. For them the partial
+// results of the split rows live in the fixed array below instead of caller-provided buffers. Every process that
+// loads the library holds the array on every GPU it touches, until it exits.
+namespace roost {
+
+constexpr size_t kStaticScratchFloats = 4u * 1024u * 1024u;  // 16 MiB
+static __device__ __align__(256) float g_decode_scratch[kStaticScratchFloats];
+
+constexpr int kMaxDevices = 64;
+static float* g_decode_scratch_ptr[kMaxDevices];  // device addresses of the array, per device; null until set up
+
+// In host code g_decode_scratch is only a handle for the runtime, not an address a kernel may use: the device address
+// comes from cudaGetSymbolAddress, asked once per device with that device current.
+static int static_scratch(float** ptr) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(ROOST_ERR_CUDA, std::string("attention_decode_static: cudaGetDevice: ") + cudaGetErrorString(e));
+  if (dev < 0 || dev >= kMaxDevices) return fail(ROOST_ERR_UNSUPPORTED, "attention_decode_static: device ordinal beyond 63");
+  if (g_decode_scratch_ptr[dev] == nullptr) {
+    float* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, g_decode_scratch);
+    if (e != cudaSuccess || p == nullptr) {
+      return fail(ROOST_ERR_CUDA, std::string("attention_decode_static: cudaGetSymbolAddress: ") + cudaGetErrorString(e));
+    }
+    g_decode_scratch_ptr[dev] = p;
+  }
+  *ptr = g_decode_scratch_ptr[dev];
+  return ROOST_OK;
+}
+
+}  // namespace roost
+
+extern "C" int roost_attention_decode_static_capacity_floats(void) { return (int)kStaticScratchFloats; }
+
+extern "C" int roost_attention_decode_static(const void* q, void* out, const void* k_pool, const void* v_pool, const int32_t* q_indptr,
+                                             const int32_t* kv_lens, const int32_t* kv_indptr, const int32_t* kv_indices,
+                                             const int32_t* work, int items, const int32_t* merge_work, int merge_items, int slots,
+                                             int q_heads, int kv_heads, int head_dim, int page_size, float scale, int window,
+                                             roost_stream_t stream) {
+  ROOST_REQUIRE(items >= 0 && merge_items >= 0 && slots >= 0 && q_heads > 0 && kv_heads > 0 && page_size > 0 && head_dim > 0,
+                "attention_decode_static: sizes must be positive");
+  ROOST_REQUIRE(q_heads % kv_heads == 0, "attention_decode_static: q_heads must be a multiple of kv_heads");
+  ROOST_REQUIRE(merge_items == 0 || merge_work != nullptr, "attention_decode_static: merge_work is null");
+  if (kv_heads > 65535) return fail(ROOST_ERR_UNSUPPORTED, "attention_decode_static: more than 65535 key/value heads");
+  // partial outputs first, then (max, sum) pairs, the second region starting on a 256-byte boundary
+  const size_t o_floats = (size_t)slots * kv_heads * 16 * head_dim;
+  const size_t o_padded = (o_floats + 63) / 64 * 64;
+  const size_t ml_floats = (size_t)slots * kv_heads * 16 * 2;
+  if (o_padded + ml_floats > kStaticScratchFloats) {
+    return fail(ROOST_ERR_UNSUPPORTED, "attention_decode_static: " + std::to_string(slots) + " partial slots need " +
+                                           std::to_string((o_padded + ml_floats) * 4) + " bytes of scratch; the fixed array holds " +
+                                           std::to_string(kStaticScratchFloats * 4) + " (use roost_attention_decode with a workspace)");
+  }
+  if (items == 0) return ROOST_OK;
+  float* scratch = nullptr;
+  const int rc = static_scratch(&scratch);
+  if (rc != ROOST_OK) return rc;
+  // Nothing in the array has to start at zero: the decode kernel writes every element of a slot that the merge kernel
+  // reads (all rows below the request's packed-row count, for every key/value head), so what an earlier call left
+  // behind is never read.
+  ROOST_DISPATCH_HEAD_DIM(head_dim, D, return launch_decode<D>(q, out, k_pool, v_pool, q_indptr, kv_lens, kv_indptr, kv_indices, work, items,
+                                                                merge_work, merge_items, scratch, scratch + o_padded, q_heads, kv_heads,
+                                                                page_size, scale, window, (cudaStream_t)stream));
+  return ROOST_OK;
+}

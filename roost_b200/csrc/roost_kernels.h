@@ -86,6 +86,26 @@ int roost_attention_decode(const void* q, void* out, const void* k_pool, const v
                            int items, const int32_t* merge_work, int merge_items, float* part_o, float* part_ml, int q_heads,
                            int kv_heads, int head_dim, int page_size, float scale, int window, roost_stream_t stream);
 
+/* The split decode attention without a workspace argument. It has no counterpart in the reference: it exists for
+ * callers that must not allocate device memory while they run (a host that gave the whole GPU to its own arena at
+ * start-up, a loop that may never synchronise the device as cudaMalloc and cudaFree do, a plug-in that may not grow
+ * its process's footprint). Same arguments and result as roost_attention_decode, except that the partial results of
+ * rows split into several chunks (`slots` of them, as the work lists number them) live in a fixed device array of
+ * roost_attention_decode_static_capacity_floats() floats (16 MiB) inside the library, which every process that
+ * loads the library holds on each GPU it uses until it exits. It calls no cudaMalloc, cudaFree or other allocating
+ * routine. A call whose slots need more than the array holds returns ROOST_ERR_UNSUPPORTED and launches nothing.
+ * The first call on a device looks up the array's device address (cudaGetSymbolAddress, with that device current);
+ * make that first call outside any stream capture. All calls share the one array and it keeps what the last call
+ * wrote; nothing in it needs clearing, because a call writes every element it later reads. Two calls that overlap
+ * on the GPU (different streams, or one stream's call still running when another is launched elsewhere) race on the
+ * array: order them on one stream or with events. */
+int roost_attention_decode_static_capacity_floats(void);
+int roost_attention_decode_static(const void* q, void* out, const void* k_pool, const void* v_pool, const int32_t* q_indptr,
+                                  const int32_t* kv_lens, const int32_t* kv_indptr, const int32_t* kv_indices,
+                                  const int32_t* work, int items, const int32_t* merge_work, int merge_items, int slots,
+                                  int q_heads, int kv_heads, int head_dim, int page_size, float scale, int window,
+                                  roost_stream_t stream);
+
 /* out[m,n] = sum_k a[m,k] * w[n,k], plain FFMA in 32-bit (no tensor cores, no reduced-precision mode), the
  * sum over k in increasing order for every output, whatever m is. in_dtype/out_dtype: 0 or 1. */
 int roost_gemm_simt(const void* a, const void* w, void* out, int m, int n, int k, int64_t lda, int64_t ldw,
