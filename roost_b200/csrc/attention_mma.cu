@@ -11,7 +11,7 @@
 //   * prefill: a CTA of 4 warps owns 64 packed rows of one request and one key/value head and walks the keys in
 //     tiles of 64, double-buffered with cp.async, all warps sharing each tile;
 //   * decode (rows with at most 16 packed rows): a CTA owns one fixed-size chunk of a request's keys; its warps take
-//     the chunk's 32-key tiles in turn, each with a double buffer of its own, and merge their partial results in
+//     the chunk's 16-key tiles in turn, each with a three-stage buffer of its own, and merge their partial results in
 //     shared memory; a request with several chunks writes (max, sum, unnormalised output) per chunk to a workspace
 //     that the merge kernel reduces in chunk order. The chunk size is fixed by the caller, so the order of every sum
 //     depends on the request's own length only, never on what else is in the batch.
@@ -21,6 +21,8 @@
 namespace roost {
 
 constexpr float kLog2e = 1.4426950408889634f;
+constexpr int kDecodeTileKeys = 16;  // keys per tile of a decode warp
+constexpr int kDecodeStages = 3;     // tiles a decode warp keeps in shared memory
 
 __device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, bool valid) {
   const int n = valid ? 16 : 0;  // src-size 0: the 16 bytes are zero-filled and src is not read
@@ -301,12 +303,13 @@ __global__ void __launch_bounds__(NWARPS * 32)
                             const int32_t* __restrict__ kv_lens, const int32_t* __restrict__ kv_indptr,
                             const int32_t* __restrict__ kv_indices, const int4* __restrict__ work, float* __restrict__ part_o,
                             float* __restrict__ part_ml, int q_heads, int kv_heads, int page_size, float scale_log2, int window) {
-  constexpr int BN = 32;
+  constexpr int BN = kDecodeTileKeys, STAGES = kDecodeStages;
   extern __shared__ __align__(128) unsigned char smem_raw[];
   const uint32_t smem = (uint32_t)__cvta_generic_to_shared(smem_raw);
   constexpr uint32_t kTileBytes = BN * D * 2;
   constexpr uint32_t kQBytes = 16 * D * 2;
-  constexpr uint32_t kWarpBytes = 4 * kTileBytes;  // K and V, two stages
+  constexpr uint32_t kStageBytes = 2 * kTileBytes;             // K then V
+  constexpr uint32_t kWarpBytes = STAGES * kStageBytes;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t q_smem = smem;
   const uint32_t wbase = smem + kQBytes + warp * kWarpBytes;
@@ -347,30 +350,34 @@ __global__ void __launch_bounds__(NWARPS * 32)
   st.m[0] = st.m[1] = -INFINITY;
   st.l[0] = st.l[1] = 0.f;
 
-  // tiles of the chunk, taken by the warps in turn
-  const int t0 = kv_begin / BN;
+  // tiles of the chunk from the first visible key on, taken by the warps in turn; each warp keeps STAGES - 1 tiles in
+  // flight ahead of the one it computes on. One commit group per tile slot, empty when the warp has no such tile, so
+  // that the group count is the same for every lane and iteration.
+  const int t0 = lo / BN;
   const int ntiles = hi >= lo ? (hi / BN - t0 + 1) : 0;
-  int mine = warp < ntiles ? (ntiles - warp + NWARPS - 1) / NWARPS : 0;
-  if (mine > 0) {
-    load_kv_tile<D, BN, 32>(wbase, wbase + kTileBytes, k_pool, v_pool, pages, page_size, kv_heads, kvh, (t0 + warp) * BN, lo, hi, lane);
+  const int mine = warp < ntiles ? (ntiles - warp + NWARPS - 1) / NWARPS : 0;
+#pragma unroll
+  for (int s = 0; s < STAGES - 1; ++s) {
+    if (s < mine) {
+      const uint32_t dst = wbase + s * kStageBytes;
+      load_kv_tile<D, BN, 32>(dst, dst + kTileBytes, k_pool, v_pool, pages, page_size, kv_heads, kvh, (t0 + warp + s * NWARPS) * BN, lo, hi, lane);
+    }
+    cp_async_commit();
   }
-  cp_async_commit();
-  cp_async_wait<1>();  // the Q tile (each thread's own copies); made visible to all by the barrier
+  cp_async_wait<STAGES - 1>();  // the Q tile (the oldest group); made visible to all by the barrier
   __syncthreads();
   for (int i = 0; i < mine; ++i) {
     const int t = t0 + warp + i * NWARPS;
-    const uint32_t cur = wbase + (i & 1) * 2 * kTileBytes;
-    const uint32_t nxt = wbase + ((i + 1) & 1) * 2 * kTileBytes;
-    if (i + 1 < mine) {
-      load_kv_tile<D, BN, 32>(nxt, nxt + kTileBytes, k_pool, v_pool, pages, page_size, kv_heads, kvh, (t + NWARPS) * BN, lo, hi, lane);
-      cp_async_commit();
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
+    const uint32_t cur = wbase + (i % STAGES) * kStageBytes;
+    if (i + STAGES - 1 < mine) {
+      const uint32_t dst = wbase + ((i + STAGES - 1) % STAGES) * kStageBytes;
+      load_kv_tile<D, BN, 32>(dst, dst + kTileBytes, k_pool, v_pool, pages, page_size, kv_heads, kvh, (t + (STAGES - 1) * NWARPS) * BN, lo, hi, lane);
     }
+    cp_async_commit();
+    cp_async_wait<STAGES - 1>();  // all but the newest STAGES - 1 groups are done: tile i has arrived
     __syncwarp();
     attend_tile<D, BN>(st, q_smem, 0, cur, cur + kTileBytes, t * BN, qpos, qlo, scale_log2, lane);
-    __syncwarp();
+    __syncwarp();  // every lane is done with `cur` before a later iteration loads into it
   }
   cp_async_wait<0>();
   __syncthreads();
@@ -378,19 +385,21 @@ __global__ void __launch_bounds__(NWARPS * 32)
   // merge the warps' states through shared memory (in warp order), then write the chunk's result
   float* sm_o = reinterpret_cast<float*>(smem_raw + kQBytes);          // [NWARPS][16][D]
   float* sm_ml = sm_o + NWARPS * 16 * D;                               // [NWARPS][16][2]
-  static_assert(NWARPS * 16 * D * 4 + NWARPS * 16 * 2 * 4 <= NWARPS * 4 * BN * D * 2, "merge scratch does not fit in the tile buffers");
+  static_assert(NWARPS * 16 * D * 4 + NWARPS * 16 * 2 * 4 <= NWARPS * kWarpBytes, "merge scratch does not fit in the tile buffers");
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
     const int row = (lane >> 2) + r * 8;
-    float* dst = sm_o + ((size_t)warp * 16 + row) * D + (lane & 3) * 2;
+    if (row < rows_total) {
+      float* dst = sm_o + ((size_t)warp * 16 + row) * D + (lane & 3) * 2;
 #pragma unroll
-    for (int nn = 0; nn < D / 8; ++nn) {
-      dst[nn * 8] = st.o[nn][2 * r];
-      dst[nn * 8 + 1] = st.o[nn][2 * r + 1];
-    }
-    if ((lane & 3) == 0) {
-      sm_ml[(warp * 16 + row) * 2] = st.m[r];
-      sm_ml[(warp * 16 + row) * 2 + 1] = st.l[r];
+      for (int nn = 0; nn < D / 8; ++nn) {
+        dst[nn * 8] = st.o[nn][2 * r];
+        dst[nn * 8 + 1] = st.o[nn][2 * r + 1];
+      }
+      if ((lane & 3) == 0) {
+        sm_ml[(warp * 16 + row) * 2] = st.m[r];
+        sm_ml[(warp * 16 + row) * 2 + 1] = st.l[r];
+      }
     }
   }
   __syncthreads();
@@ -429,17 +438,22 @@ __global__ void attention_merge_kernel(__nv_bfloat16* __restrict__ out, const fl
   const int4 w = merge_work[blockIdx.x];
   const int b = w.x, slot0 = w.y, chunks = w.z;
   const int kvh = blockIdx.y;
+  const int row = blockIdx.z;
   const int group = q_heads / kv_heads;
   const int q_start = q_indptr[b];
   const int rows_total = (q_indptr[b + 1] - q_start) * group;
-  for (int idx = threadIdx.x; idx < rows_total * D; idx += blockDim.x) {
-    const int row = idx / D, col = idx % D;
-    float m = -INFINITY;
-    for (int c = 0; c < chunks; ++c) m = fmaxf(m, part_ml[(((size_t)(slot0 + c) * kv_heads + kvh) * 16 + row) * 2]);
-    const float msafe = m == -INFINITY ? 0.f : m;
+  if (row >= rows_total) return;
+  const size_t pr0 = ((size_t)slot0 * kv_heads + kvh) * 16 + row;
+  const size_t stride = (size_t)kv_heads * 16;  // partial rows from one chunk's slot to the next
+  float m = -INFINITY;
+#pragma unroll 8
+  for (int c = 0; c < chunks; ++c) m = fmaxf(m, part_ml[(pr0 + c * stride) * 2]);
+  const float msafe = m == -INFINITY ? 0.f : m;
+  for (int col = threadIdx.x; col < D; col += blockDim.x) {
     float l = 0.f, o = 0.f;
-    for (int c = 0; c < chunks; ++c) {
-      const size_t pr = ((size_t)(slot0 + c) * kv_heads + kvh) * 16 + row;
+#pragma unroll 8
+    for (int c = 0; c < chunks; ++c) {  // chunk order: the sums do not depend on how the chunks were scheduled
+      const size_t pr = pr0 + c * stride;
       const float f = exp2f(part_ml[pr * 2] - msafe);
       l += part_ml[pr * 2 + 1] * f;
       o += part_o[pr * D + col] * f;
@@ -467,8 +481,8 @@ static int launch_decode(const void* q, void* out, const void* k_pool, const voi
                          const int32_t* kv_indptr, const int32_t* kv_indices, const int32_t* work, int items, const int32_t* merge_work,
                          int merge_items, float* part_o, float* part_ml, int q_heads, int kv_heads, int page_size, float scale, int window,
                          cudaStream_t s) {
-  constexpr int NW = D <= 128 ? 4 : 2;
-  const size_t smem = (size_t)16 * D * 2 + (size_t)NW * 4 * 32 * D * 2;
+  constexpr int NW = 4;
+  const size_t smem = (size_t)16 * D * 2 + (size_t)NW * kDecodeStages * 2 * kDecodeTileKeys * D * 2;
   auto kernel = attention_decode_kernel<D, NW>;
   if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   kernel<<<dim3(items, kv_heads), NW * 32, smem, s>>>((const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const __nv_bfloat16*)k_pool,
@@ -477,7 +491,7 @@ static int launch_decode(const void* q, void* out, const void* k_pool, const voi
                                                       window);
   int rc = check_launch("attention_decode");
   if (rc != ROOST_OK || merge_items == 0) return rc;
-  attention_merge_kernel<D><<<dim3(merge_items, kv_heads), 128, 0, s>>>((__nv_bfloat16*)out, part_o, part_ml, q_indptr,
+  attention_merge_kernel<D><<<dim3(merge_items, kv_heads, 16), D < 128 ? D : 128, 0, s>>>((__nv_bfloat16*)out, part_o, part_ml, q_indptr,
                                                                         (const int4*)merge_work, q_heads, kv_heads);
   return check_launch("attention_merge");
 }

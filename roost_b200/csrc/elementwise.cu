@@ -62,6 +62,102 @@ __global__ void silu_mul_kernel(const T* __restrict__ x, T* __restrict__ out, in
   out[t * inter + i] = from_float<T>(g / (1.0f + expf(-g)) * u);
 }
 
+
+// ---------------------------------------------------------------------------------------------- vectorised forms
+// 16-byte loads and stores (8 bfloat16 or 4 float), the row kept in registers between the sum of squares and the
+// scaling. Used when the row length is a multiple of the vector and short enough for kMaxVec vectors a thread.
+template <typename T>
+struct Vec;
+template <>
+struct Vec<float> {
+  static constexpr int N = 4;
+  __device__ static __forceinline__ void load(const float* p, float (&v)[4]) {
+    const float4 t = *reinterpret_cast<const float4*>(p);
+    v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+  }
+  __device__ static __forceinline__ void store(float* p, const float (&v)[4]) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  }
+};
+template <>
+struct Vec<__nv_bfloat16> {
+  static constexpr int N = 8;
+  __device__ static __forceinline__ void load(const __nv_bfloat16* p, float (&v)[8]) {
+    const uint4 t = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      v[2 * i] = __uint_as_float(w[i] << 16);
+      v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+  }
+  __device__ static __forceinline__ void store(__nv_bfloat16* p, const float (&v)[8]) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      __nv_bfloat162 b = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+      w[i] = *reinterpret_cast<uint32_t*>(&b);
+    }
+    *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+};
+
+constexpr int kMaxVec = 4;
+
+template <typename T, bool ADD>
+__global__ void rms_norm_vec_kernel(const T* __restrict__ x, T* residual, const void* __restrict__ w, T* __restrict__ out,
+                                    const int32_t* __restrict__ rows, int hidden, float eps, int wdtype) {
+  constexpr int N = Vec<T>::N;
+  __shared__ float scratch[32];
+  const int i_out = blockIdx.x;
+  const size_t r = rows ? (size_t)rows[i_out] : (size_t)i_out;
+  const int nvec = hidden / N;
+  float v[kMaxVec][N];
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < kMaxVec; ++k) {
+    const int vi = threadIdx.x + k * blockDim.x;
+    if (vi < nvec) {
+      Vec<T>::load(x + r * hidden + (size_t)vi * N, v[k]);
+      if (ADD) {
+        float res[N];
+        Vec<T>::load(residual + r * hidden + (size_t)vi * N, res);
+#pragma unroll
+        for (int e = 0; e < N; ++e) v[k][e] = to_float(from_float<T>(v[k][e] + res[e]));  // the sum, rounded once
+        if (!rows) Vec<T>::store(residual + r * hidden + (size_t)vi * N, v[k]);
+      }
+#pragma unroll
+      for (int e = 0; e < N; ++e) ss += v[k][e] * v[k][e];
+    }
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = 1.0f / sqrtf(ss / (float)hidden + eps);
+#pragma unroll
+  for (int k = 0; k < kMaxVec; ++k) {
+    const int vi = threadIdx.x + k * blockDim.x;
+    if (vi < nvec) {
+      float o[N];
+#pragma unroll
+      for (int e = 0; e < N; ++e) o[e] = v[k][e] * inv * load_w(w, vi * N + e, wdtype);
+      Vec<T>::store(out + (size_t)i_out * hidden + (size_t)vi * N, o);
+    }
+  }
+}
+
+template <typename T>
+__global__ void silu_mul_vec_kernel(const T* __restrict__ x, T* __restrict__ out, int inter) {
+  constexpr int N = Vec<T>::N;
+  const size_t t = blockIdx.x;
+  const int vi = blockIdx.y * blockDim.x + threadIdx.x;
+  if (vi * N >= inter) return;
+  float g[N], u[N], o[N];
+  Vec<T>::load(x + t * 2 * inter + (size_t)vi * N, g);
+  Vec<T>::load(x + t * 2 * inter + inter + (size_t)vi * N, u);
+#pragma unroll
+  for (int e = 0; e < N; ++e) o[e] = g[e] / (1.0f + expf(-g[e])) * u[e];
+  Vec<T>::store(out + t * inter + (size_t)vi * N, o);
+}
+
 }  // namespace roost
 
 using namespace roost;
@@ -85,6 +181,22 @@ static int launch_norm(const void* x, void* residual, const void* w, void* out, 
   ROOST_REQUIRE(eps > 0.f, "rms_norm: eps must be positive");
   ROOST_REQUIRE(wdtype == ROOST_F32 || wdtype == ROOST_BF16, "rms_norm: weight dtype code is neither 0 nor 1");
   if (n_out == 0) return ROOST_OK;
+  // rows that are whole 16-byte vectors and fit in registers take the vectorised kernel
+  {
+    const int vec = dtype == ROOST_F32 ? 4 : 8;
+    const bool aligned = ((uintptr_t)x % 16 == 0) && ((uintptr_t)out % 16 == 0) && (!ADD || (uintptr_t)residual % 16 == 0);
+    if (hidden % vec == 0 && aligned && (dtype == ROOST_F32 || dtype == ROOST_BF16)) {
+      const int nvec = hidden / vec;
+      int threads = ((nvec + 31) / 32) * 32;
+      if (threads > 512) threads = 512;
+      if (nvec <= threads * kMaxVec) {
+        ROOST_DISPATCH_DTYPE(dtype, T,
+                             rms_norm_vec_kernel<T, ADD><<<n_out, threads, 0, (cudaStream_t)stream>>>(
+                                 (const T*)x, (T*)residual, w, (T*)out, rows, hidden, eps, wdtype));
+        return check_launch("rms_norm");
+      }
+    }
+  }
   const size_t smem = ((size_t)hidden + 32) * sizeof(float);
   if (smem > 200 * 1024) return fail(ROOST_ERR_UNSUPPORTED, "rms_norm: a row of more than 51168 elements does not fit in shared memory");
   const int threads = hidden >= 1024 ? 512 : (hidden >= 256 ? 256 : 64);
@@ -110,6 +222,17 @@ extern "C" int roost_add_rms_norm(const void* x, void* residual, const void* w, 
 extern "C" int roost_silu_mul(const void* x, void* out, int tokens, int inter, int dtype, roost_stream_t stream) {
   ROOST_REQUIRE(tokens >= 0 && inter > 0, "silu_mul: tokens and inter must be positive");
   if (tokens == 0) return ROOST_OK;
+  {
+    const int vec = dtype == ROOST_F32 ? 4 : 8;
+    if (inter % vec == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)out % 16 == 0 && (dtype == ROOST_F32 || dtype == ROOST_BF16)) {
+      const int nvec = inter / vec;
+      dim3 grid(tokens, (nvec + 127) / 128);
+      if (grid.y <= 65535) {
+        ROOST_DISPATCH_DTYPE(dtype, T, silu_mul_vec_kernel<T><<<grid, 128, 0, (cudaStream_t)stream>>>((const T*)x, (T*)out, inter));
+        return check_launch("silu_mul");
+      }
+    }
+  }
   if ((inter + 255) / 256 > 65535) return fail(ROOST_ERR_UNSUPPORTED, "silu_mul: inter beyond 16776960");
   dim3 grid(tokens, (inter + 255) / 256);
   ROOST_DISPATCH_DTYPE(dtype, T, silu_mul_kernel<T><<<grid, 256, 0, (cudaStream_t)stream>>>((const T*)x, (T*)out, inter));

@@ -11,14 +11,28 @@
 
 namespace roost {
 
-// One warp per (token, head slot); head slots are q heads, then k heads, then v heads.
+__device__ __forceinline__ void load2(const float* p, float (&v)[2]) {
+  const float2 t = *reinterpret_cast<const float2*>(p);
+  v[0] = t.x; v[1] = t.y;
+}
+__device__ __forceinline__ void load2(const __nv_bfloat16* p, float (&v)[2]) {
+  const __nv_bfloat162 t = *reinterpret_cast<const __nv_bfloat162*>(p);
+  v[0] = __low2float(t); v[1] = __high2float(t);
+}
+__device__ __forceinline__ void store2(float* p, const float (&v)[2]) { *reinterpret_cast<float2*>(p) = make_float2(v[0], v[1]); }
+__device__ __forceinline__ void store2(__nv_bfloat16* p, const float (&v)[2]) {
+  *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(v[0], v[1]);
+}
+
+// One warp per (token, head slot); head slots are q heads, then k heads, then v heads. vector_ok: every head row of
+// qkv, q_out and the pools starts on a 16-byte boundary (head_dim a multiple of 8 elements, aligned bases and stride).
 template <typename T>
 __global__ void qk_norm_rope_cache_kernel(const T* __restrict__ qkv, int64_t qkv_stride, T* __restrict__ q_out,
                                           T* __restrict__ k_pool, T* __restrict__ v_pool, const void* __restrict__ q_w,
                                           const void* __restrict__ k_w, const double* __restrict__ inv_freq,
                                           const int32_t* __restrict__ positions, const int32_t* __restrict__ slot_mapping,
                                           int q_heads, int kv_heads, int head_dim, int rotary_dim, float eps, int page_size,
-                                          int64_t pool_pages, int slots_per_token, int wdtype) {
+                                          int64_t pool_pages, int slots_per_token, int wdtype, bool vector_ok) {
   const int lane = threadIdx.x & 31;
   const int slot_idx = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (slot_idx >= slots_per_token) return;
@@ -49,7 +63,12 @@ __global__ void qk_norm_rope_cache_kernel(const T* __restrict__ qkv, int64_t qkv
   }
 
   if (kind == 2) {
-    for (int i = lane; i < head_dim; i += 32) dst[i] = src[i];
+    if (vector_ok) {
+      constexpr int N = 16 / sizeof(T);
+      for (int i = lane * N; i < head_dim; i += 32 * N) *reinterpret_cast<uint4*>(dst + i) = *reinterpret_cast<const uint4*>(src + i);
+    } else {
+      for (int i = lane; i < head_dim; i += 32) dst[i] = src[i];
+    }
     return;
   }
 
@@ -66,7 +85,31 @@ __global__ void qk_norm_rope_cache_kernel(const T* __restrict__ qkv, int64_t qkv
   }
   const int half = rotary_dim / 2;
   const double pos = (double)positions[t];
-  // rotated pairs (i, i + half)
+  // rotated pairs (i, i + half); two neighbouring pairs at a time when the layout allows 2-element accesses
+  if (vector_ok && (half & 1) == 0) {
+    for (int i = lane * 2; i < half; i += 64) {
+      float a[2], b[2];
+      load2(src + i, a);
+      load2(src + i + half, b);
+      float o1[2], o2[2];
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        float x1 = a[e], x2 = b[e];
+        if (w != nullptr) {
+          x1 = x1 * inv * load_w(w, i + e, wdtype);
+          x2 = x2 * inv * load_w(w, i + e + half, wdtype);
+        }
+        double ang = pos * inv_freq[i + e];
+        ang -= 6.283185307179586476925286766559 * rint(ang * 0.15915494309189533576888376337251);
+        float s, c;
+        sincosf((float)ang, &s, &c);
+        o1[e] = x1 * c - x2 * s;
+        o2[e] = x2 * c + x1 * s;
+      }
+      store2(dst + i, o1);
+      store2(dst + i + half, o2);
+    }
+  } else
   for (int i = lane; i < half; i += 32) {
     float x1 = to_float(src[i]);
     float x2 = to_float(src[i + half]);
@@ -114,9 +157,12 @@ extern "C" int roost_qk_norm_rope_cache(const void* qkv, int64_t qkv_stride, voi
   const int warps = 4;
   dim3 grid(tokens, (slots + warps - 1) / warps);
   if (grid.y > 65535) return fail(ROOST_ERR_UNSUPPORTED, "qk_norm_rope_cache: more than 262140 head slots per token");
+  const size_t esize = dtype == ROOST_F32 ? 4 : 2;
+  const bool vector_ok = (head_dim * esize) % 16 == 0 && (qkv_stride * esize) % 16 == 0 && (uintptr_t)qkv % 16 == 0 &&
+                         (uintptr_t)q_out % 16 == 0 && (!write_kv || ((uintptr_t)k_pool % 16 == 0 && (uintptr_t)v_pool % 16 == 0));
   ROOST_DISPATCH_DTYPE(dtype, T,
                        qk_norm_rope_cache_kernel<T><<<grid, warps * 32, 0, (cudaStream_t)stream>>>(
                            (const T*)qkv, qkv_stride, (T*)q_out, (T*)k_pool, (T*)v_pool, q_w, k_w, inv_freq, positions,
-                           slot_mapping, q_heads, kv_heads, head_dim, rotary_dim, eps, page_size, pool_pages, slots, wdtype));
+                           slot_mapping, q_heads, kv_heads, head_dim, rotary_dim, eps, page_size, pool_pages, slots, wdtype, vector_ok));
   return check_launch("qk_norm_rope_cache");
 }
