@@ -196,8 +196,11 @@ def timed_e2e(model, batch: int, context: int, steps: int, warmup: int):
     pages = batch * (-(-(context + 2) // PAGE)) + 8
     engine = RoostEngine(model, page_size=PAGE, attention_blocks=pages, max_sequences=max(batch, 1), max_tokens=2048)
     gen = torch.Generator().manual_seed(13)
-    prompt_len = context - (steps + warmup)
-    opts = GenerationOptions(max_output_tokens=steps + warmup + 1, ignore_eos=True).sampling()
+    # requests that finish their prompt first decode while the others still prefill: leave room for those tokens so
+    # that every request stays live, within the context, through the timed steps
+    prefill_steps = -(-batch * context // 2048) + 1
+    prompt_len = context - (steps + warmup + prefill_steps)
+    opts = GenerationOptions(max_output_tokens=4 * (steps + warmup + prefill_steps), ignore_eos=True).sampling()
     for b in range(batch):
         engine.add_request(torch.randint(0, model.spec.vocab, (prompt_len,), generator=gen).tolist(), opts)
     # prefill (untimed): run engine steps until every request decodes
@@ -212,6 +215,7 @@ def timed_e2e(model, batch: int, context: int, steps: int, warmup: int):
     h2d = d2h = 0
     for _ in range(steps):
         events = engine.step()
+        assert len(events) == batch, "a request left the batch inside the timed region"
         produced += sum(1 for e in events if e.token is not None)
         h2d += engine.executor.last_upload_bytes
         d2h += 4 * len(events)

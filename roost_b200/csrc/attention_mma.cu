@@ -228,6 +228,7 @@ __global__ void __launch_bounds__(128) attention_prefill_kernel(const __nv_bfloa
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int2 w = work[blockIdx.x];
   const int b = w.x, row0 = w.y;
+  if (b < 0) return;  // padding of a fixed-size work list
   const int kvh = blockIdx.y;
   const int group = q_heads / kv_heads;
   const int q_start = q_indptr[b];
@@ -316,6 +317,7 @@ __global__ void __launch_bounds__(NWARPS * 32)
 
   const int4 w = work[blockIdx.x];
   const int b = w.x, kv_begin = w.y, kv_end = w.z, slot = w.w;
+  if (b < 0) return;  // padding of a fixed-size work list
   const int kvh = blockIdx.y;
   const int group = q_heads / kv_heads;
   const int q_start = q_indptr[b];
@@ -437,6 +439,7 @@ __global__ void attention_merge_kernel(__nv_bfloat16* __restrict__ out, const fl
                                        int kv_heads) {
   const int4 w = merge_work[blockIdx.x];
   const int b = w.x, slot0 = w.y, chunks = w.z;
+  if (b < 0) return;  // padding of a fixed-size work list
   const int kvh = blockIdx.y;
   const int row = blockIdx.z;
   const int group = q_heads / kv_heads;
@@ -469,7 +472,11 @@ static int launch_prefill(const void* q, void* out, const void* k_pool, const vo
                           int page_size, float scale, int window, cudaStream_t s) {
   const size_t smem = (size_t)(64 + 4 * 64) * D * 2;
   auto kernel = attention_prefill_kernel<D>;
-  if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  static bool attr_set = false;  // once per process: nothing but launches happens on later calls (stream capture)
+  if (smem > 48 * 1024 && !attr_set) {
+    cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    attr_set = true;
+  }
   kernel<<<dim3(items, kv_heads), 128, smem, s>>>((const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const __nv_bfloat16*)k_pool,
                                                   (const __nv_bfloat16*)v_pool, q_indptr, kv_lens, kv_indptr, kv_indices, (const int2*)work,
                                                   q_heads, kv_heads, page_size, scale * kLog2e, window);
@@ -484,7 +491,11 @@ static int launch_decode(const void* q, void* out, const void* k_pool, const voi
   constexpr int NW = 4;
   const size_t smem = (size_t)16 * D * 2 + (size_t)NW * kDecodeStages * 2 * kDecodeTileKeys * D * 2;
   auto kernel = attention_decode_kernel<D, NW>;
-  if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  static bool attr_set = false;
+  if (smem > 48 * 1024 && !attr_set) {
+    cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    attr_set = true;
+  }
   kernel<<<dim3(items, kv_heads), NW * 32, smem, s>>>((const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const __nv_bfloat16*)k_pool,
                                                       (const __nv_bfloat16*)v_pool, q_indptr, kv_lens, kv_indptr, kv_indices,
                                                       (const int4*)work, part_o, part_ml, q_heads, kv_heads, page_size, scale * kLog2e,

@@ -5,6 +5,9 @@ portion of one, or a single decoded token, mixed freely. From the rows and the r
 tables below are derived, the same set the reference's worker fills before every forward pass
 (src/Starlings.Roost.Worker/Eager/PlanRegionWriter.cs:19-64): token ids, absolute positions, the slot each
 token's key and value go to, per-row query and page ranges, the rows whose logits are wanted.
+
+Two placements: a fresh pinned buffer and device buffer per step (any step), or a ``StaticTables`` of fixed
+capacity whose device addresses never change, which a captured CUDA graph of a decode step reads on every replay.
 """
 from __future__ import annotations
 
@@ -28,6 +31,71 @@ class GroupTables:
 
 
 @dataclass
+class AttentionPlan:
+    """How the tensor-core attention kernels divide a step's rows (see csrc/attention_mma.cu): rows with at most 16
+    packed rows (tokens x query heads per key/value head) go to the decode kernel in chunks of a fixed number of
+    keys, the others to the prefill kernel in tiles of 64 packed rows. Item counts may include padding entries
+    (batch row -1), which the kernels skip."""
+    prefill_items: int = 0
+    decode_items: int = 0
+    merge_items: int = 0
+    slots: int = 0
+    prefill_work: torch.Tensor | None = None
+    decode_work: torch.Tensor | None = None
+    merge_work: torch.Tensor | None = None
+
+
+def attention_work(row_starts, row_counts, group: int, window: int | None, chunk: int):
+    """(prefill pairs, decode quadruples, merge quadruples, slots) as flat int lists."""
+    prefill, decode, merge = [], [], []
+    slots = 0
+    for b, (start, n) in enumerate(zip(row_starts, row_counts)):
+        rows, kv_len = n * group, start + n
+        if rows <= 16:
+            lo = max(0, start - window + 1) if window else 0
+            first = (lo // chunk) * chunk
+            begins = range(first, kv_len, chunk)
+            if len(begins) == 1:
+                decode += [b, first, min(first + chunk, kv_len), -1]
+            else:
+                merge += [b, slots, len(begins), 0]
+                for c in begins:
+                    decode += [b, c, min(c + chunk, kv_len), slots]
+                    slots += 1
+        else:
+            for r0 in range(0, rows, 64):
+                prefill += [b, r0]
+    return prefill, decode, merge, slots
+
+
+def attention_caps(num_rows: int, kv_cap: int, group: int, chunk: int) -> tuple[int, int, int]:
+    """Largest item counts of a decode step (one token a row) whose requests hold at most ``kv_cap`` keys."""
+    if group > 16:
+        return num_rows * (-(-group // 64)), 0, 0
+    return 0, num_rows * (-(-kv_cap // chunk)), num_rows
+
+
+def _pad4(a: list) -> list:
+    return a + [0] * (-len(a) % 4)
+
+
+def plan_attention(row_starts, row_counts, group: int, window: int | None, chunk: int, device) -> AttentionPlan:
+    prefill, decode, merge, slots = attention_work(row_starts, row_counts, group, window, chunk)
+    plan = AttentionPlan(prefill_items=len(prefill) // 2, decode_items=len(decode) // 4, merge_items=len(merge) // 4, slots=slots)
+    flat = _pad4(prefill) + _pad4(decode) + _pad4(merge)
+    if flat:
+        host = torch.tensor(flat, dtype=torch.int32)
+        if torch.device(device).type == "cuda":
+            host = host.pin_memory()
+        dev = host.to(device, non_blocking=True)
+        a = len(_pad4(prefill))
+        b_ = a + len(_pad4(decode))
+        plan.prefill_work, plan.decode_work, plan.merge_work = dev[:a], dev[a:b_], dev[b_:]
+        plan.host = host
+    return plan
+
+
+@dataclass
 class StepBatch:
     num_tokens: int
     num_rows: int
@@ -48,7 +116,7 @@ class StepBatch:
     host_buffer: object = None   # the pinned staging buffer, kept until the step is done
     attention_plans: dict = field(default_factory=dict)   # (group size, window, chunk) -> AttentionPlan, made by the first mixer that asks
 
-    def attention_plan(self, group: int, window: int | None, chunk: int) -> "AttentionPlan":
+    def attention_plan(self, group: int, window: int | None, chunk: int) -> AttentionPlan:
         key = (group, window, chunk)
         plan = self.attention_plans.get(key)
         if plan is None:
@@ -58,63 +126,66 @@ class StepBatch:
 
 
 @dataclass
-class AttentionPlan:
-    """How the tensor-core attention kernels divide a step's rows (see csrc/attention_mma.cu): rows with at most 16
-    packed rows (tokens x query heads per key/value head) go to the decode kernel in chunks of a fixed number of
-    keys, the others to the prefill kernel in tiles of 64 packed rows."""
-    prefill_items: int = 0
-    decode_items: int = 0
-    merge_items: int = 0
-    slots: int = 0
-    prefill_work: torch.Tensor | None = None
-    decode_work: torch.Tensor | None = None
-    merge_work: torch.Tensor | None = None
+class HostTables:
+    """A step's tables as numpy arrays, in placement order, with the facts a StepBatch carries on the host."""
+    arrays: list
+    num_tokens: int
+    num_rows: int
+    num_selected: int
+    row_starts: list
+    row_counts: list
+    max_position: int
+    max_kv_len: int
 
 
-def plan_attention(row_starts, row_counts, group: int, window: int | None, chunk: int, device) -> AttentionPlan:
-    prefill, decode, merge = [], [], []
-    slots = 0
-    for b, (start, n) in enumerate(zip(row_starts, row_counts)):
-        rows, kv_len = n * group, start + n
-        if rows <= 16:
-            lo = max(0, start - window + 1) if window else 0
-            first = (lo // chunk) * chunk
-            begins = list(range(first, kv_len, chunk))
-            if len(begins) == 1:
-                decode += [b, first, min(first + chunk, kv_len), -1]
-            else:
-                merge += [b, slots, len(begins), 0]
-                for c in begins:
-                    decode += [b, c, min(c + chunk, kv_len), slots]
-                    slots += 1
-        else:
-            # tiles with the longest history first: they run longest
-            for r0 in range(0, rows, 64):
-                prefill += [b, r0]
-    np_, nd, nm = len(prefill) // 2, len(decode) // 4, len(merge) // 4
-    pad = lambda a: a + [0] * (-len(a) % 4)  # noqa: E731  (16-byte aligned sections)
-    flat = pad(prefill) + pad(decode) + pad(merge)
-    plan = AttentionPlan(prefill_items=np_, decode_items=nd, merge_items=nm, slots=slots)
-    if flat:
-        host = torch.tensor(flat, dtype=torch.int32)
-        if torch.device(device).type == "cuda":
-            host = host.pin_memory()
-        dev = host.to(device, non_blocking=True)
-        a = len(pad(prefill))
-        b_ = a + len(pad(decode))
-        plan.prefill_work, plan.decode_work, plan.merge_work = dev[:a], dev[a:b_], dev[b_:]
-        plan.host = host
-    return plan
+class StaticTables:
+    """Device memory of fixed capacity for a step's tables, with a ring of pinned host buffers. The device addresses
+    of all sections stay the same from step to step, so a captured graph can read them on every replay."""
+
+    RING = 3
+
+    def __init__(self, device, caps: list[int]):
+        self.device = torch.device(device)
+        self.caps = list(caps)
+        self.offsets, total = [], 0
+        for c in self.caps:
+            self.offsets.append(total)
+            total += -(-max(c, 1) // 4) * 4
+        self.total = total
+        self.dev = torch.zeros(total, dtype=torch.int32, device=self.device)
+        self.hosts = [torch.zeros(total, dtype=torch.int32, pin_memory=self.device.type == "cuda") for _ in range(self.RING)]
+        self.events = [None] * self.RING
+        self.turn = 0
+        self.views = [self.dev[o : o + max(c, 1)] for o, c in zip(self.offsets, self.caps)]
+
+    def fits(self, arrays: list) -> bool:
+        return len(arrays) == len(self.caps) and all(a.size <= c for a, c in zip(arrays, self.caps))
+
+    def upload(self, arrays: list, fills: list) -> None:
+        """Copies the arrays into their sections; the rest of each section is filled with ``fills[i]``."""
+        i = self.turn
+        self.turn = (self.turn + 1) % self.RING
+        if self.events[i] is not None:
+            self.events[i].synchronize()  # the copy that last read this host buffer is done
+        hv = self.hosts[i].numpy()
+        for a, o, c, f in zip(arrays, self.offsets, self.caps, fills):
+            hv[o : o + a.size] = a
+            hv[o + a.size : o + c] = f
+        self.dev.copy_(self.hosts[i], non_blocking=True)
+        if self.device.type == "cuda":
+            ev = torch.cuda.Event()
+            ev.record()
+            self.events[i] = ev
 
 
 class BatchBuilder:
-    """Packs a step's tables into one pinned host buffer and copies it to the device once."""
+    """Derives a step's tables and places them: a fresh pinned buffer copied to the device once, or a StaticTables."""
 
     def __init__(self, device, cache_manager):
         self.device = torch.device(device)
         self.cm = cache_manager
 
-    def build(self, rows: list[tuple], vocab: int) -> StepBatch:
+    def host_tables(self, rows: list[tuple], vocab: int) -> HostTables:
         """rows: (request cache, start position, token list, wanted offsets within the tokens)."""
         T = sum(len(r[2]) for r in rows)
         B = len(rows)
@@ -137,8 +208,7 @@ class BatchBuilder:
         if T and (ids.min() < 0 or ids.max() >= vocab):
             bad = int(ids[(ids < 0) | (ids >= vocab)][0])
             raise ValueError(f"token id {bad} is outside the vocabulary of {vocab}")
-        parts = [ids, pos, trow, q_indptr, kv_lens, np.asarray(selected, np.int32)]
-        group_parts = []
+        arrays = [ids, pos, trow, q_indptr, kv_lens, np.asarray(selected, np.int32)]
         for gi, g in enumerate(self.cm.groups):
             if g.kind == "paged":
                 slot = np.empty(T, np.int32)
@@ -148,31 +218,29 @@ class BatchBuilder:
                 for b, (rc, start, tokens, _) in enumerate(rows):
                     table = rc.tables[gi]
                     n = len(tokens)
-                    p = np.arange(start, start + n)
-                    tab = np.asarray(table, np.int64)
-                    pages = tab[p // g.page_size]
-                    if (pages == NULL_PAGE).any():
-                        raise RuntimeError(f"request {rc.request_id!r}: a token of this step falls in a page that was given back")
-                    slot[at : at + n] = pages * g.page_size + p % g.page_size
+                    if n == 1:
+                        page = table[start // g.page_size]
+                        if page == NULL_PAGE:
+                            raise RuntimeError(f"request {rc.request_id!r}: a token of this step falls in a page that was given back")
+                        slot[at] = page * g.page_size + start % g.page_size
+                    else:
+                        p = np.arange(start, start + n)
+                        pages = np.asarray(table, np.int64)[p // g.page_size]
+                        if (pages == NULL_PAGE).any():
+                            raise RuntimeError(f"request {rc.request_id!r}: a token of this step falls in a page that was given back")
+                        slot[at : at + n] = pages * g.page_size + p % g.page_size
                     used = -(-(start + n) // g.page_size)
                     indices.extend(table[:used])
                     indptr[b + 1] = len(indices)
                     at += n
-                group_parts.append((slot, indptr, np.asarray(indices, np.int32)))
+                arrays += [slot, indptr, np.asarray(indices, np.int32)]
             else:
-                group_parts.append((np.asarray([rc.slots[gi] for rc, *_ in rows], np.int32),))
-        flat = parts + [a for gp in group_parts for a in gp]
-        # 16-byte aligned sub-tables in one buffer
-        offsets, total = [], 0
-        for a in flat:
-            offsets.append(total)
-            total += -(-a.size // 4) * 4
-        host = torch.empty(max(total, 4), dtype=torch.int32, pin_memory=self.device.type == "cuda")
-        hv = host.numpy()
-        for a, o in zip(flat, offsets):
-            hv[o : o + a.size] = a
-        dev = host.to(self.device, non_blocking=True)
-        views = [dev[o : o + a.size] for a, o in zip(flat, offsets)]
+                arrays.append(np.asarray([rc.slots[gi] for rc, *_ in rows], np.int32))
+        return HostTables(arrays=arrays, num_tokens=T, num_rows=B, num_selected=len(selected), row_starts=[r[1] for r in rows],
+                          row_counts=[len(r[2]) for r in rows], max_position=int(pos.max()) if T else 0,
+                          max_kv_len=int(kv_lens.max()) if B else 0)
+
+    def _batch(self, ht: HostTables, views: list, host_buffer) -> StepBatch:
         d_ids, d_pos, d_trow, d_qi, d_kvl, d_sel = views[:6]
         rest = views[6:]
         groups = []
@@ -183,8 +251,38 @@ class BatchBuilder:
             else:
                 groups.append(GroupTables(state_slots=rest[0]))
                 rest = rest[1:]
-        return StepBatch(num_tokens=T, num_rows=B, num_selected=len(selected), ids=d_ids, positions=d_pos, token_row=d_trow,
-                         q_indptr=d_qi, kv_lens=d_kvl, selected=d_sel, groups=groups,
-                         row_starts=[r[1] for r in rows], row_counts=[len(r[2]) for r in rows],
-                         max_position=int(pos.max()) if T else 0, max_kv_len=int(kv_lens.max()) if B else 0,
-                         all_single=all(len(r[2]) == 1 for r in rows), host_buffer=host)
+        return StepBatch(num_tokens=ht.num_tokens, num_rows=ht.num_rows, num_selected=ht.num_selected, ids=d_ids, positions=d_pos,
+                         token_row=d_trow, q_indptr=d_qi, kv_lens=d_kvl, selected=d_sel, groups=groups, row_starts=ht.row_starts,
+                         row_counts=ht.row_counts, max_position=ht.max_position, max_kv_len=ht.max_kv_len,
+                         all_single=all(n == 1 for n in ht.row_counts), host_buffer=host_buffer)
+
+    def build(self, rows: list[tuple], vocab: int) -> StepBatch:
+        ht = self.host_tables(rows, vocab)
+        flat = ht.arrays
+        offsets, total = [], 0
+        for a in flat:  # 16-byte aligned sub-tables in one buffer
+            offsets.append(total)
+            total += -(-a.size // 4) * 4
+        host = torch.empty(max(total, 4), dtype=torch.int32, pin_memory=self.device.type == "cuda")
+        hv = host.numpy()
+        for a, o in zip(flat, offsets):
+            hv[o : o + a.size] = a
+        dev = host.to(self.device, non_blocking=True)
+        views = [dev[o : o + a.size] for a, o in zip(flat, offsets)]
+        return self._batch(ht, views, host)
+
+    # ------------------------------------------------------------------ fixed placement for graph replay
+    def table_caps(self, num_rows: int, kv_cap: int) -> list[int]:
+        """Capacities, in placement order, of the tables of a decode step of ``num_rows`` rows whose requests hold at
+        most ``kv_cap`` tokens."""
+        B = num_rows
+        caps = [B, B, B, B + 1, B, B]
+        for g in self.cm.groups:
+            if g.kind == "paged":
+                caps += [B, B + 1, B * (-(-kv_cap // g.page_size))]
+            else:
+                caps.append(B)
+        return caps
+
+    def static_batch(self, ht: HostTables, static: StaticTables, n_table_sections: int) -> StepBatch:
+        return self._batch(ht, static.views[:n_table_sections], None)

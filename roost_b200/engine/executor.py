@@ -14,10 +14,15 @@ from dataclasses import dataclass, field
 
 import torch
 
+import numpy as np
+
 from ..cache.manager import CacheManager, OutOfPages, build_groups
 from ..cache.storage import CacheStorage
-from .batch import BatchBuilder
+from .batch import AttentionPlan, BatchBuilder, HostTables, StaticTables, attention_caps, attention_work
 from .model import Model
+
+GRAPH_KV_GRANULE = 1024   # a captured decode step serves requests of up to a multiple of this many tokens
+MAX_GRAPHS = 24
 
 
 @dataclass
@@ -33,9 +38,79 @@ class StepError(ValueError):
     """A step that was refused before anything was launched."""
 
 
+class DecodeGraph:
+    """A captured CUDA graph of one decode step (every row brings one token and wants its logits) for a fixed number
+    of rows and a bound on the requests' lengths. The step's tables live at fixed device addresses; a replay uploads
+    the new tables and launches the whole forward pass with one call, so the host's per-kernel launch cost (hundreds
+    of launches a step) no longer bounds small batches. The reference's one graph experiment did not replay
+    bit-identically and is unclaimed (kernels/README.md:240-250); here a replay runs the very kernels of the eager
+    path with the same arguments, and the tests compare both with the plain implementation."""
+
+    def __init__(self, executor: "StepExecutor", num_rows: int, kv_cap: int, plan_keys: list):
+        self.ex = executor
+        self.num_rows, self.kv_cap = num_rows, kv_cap
+        self.plan_keys = list(plan_keys)
+        builder = executor.builder
+        table_caps = builder.table_caps(num_rows, kv_cap)
+        self.n_table = len(table_caps)
+        self.plan_caps = [attention_caps(num_rows, kv_cap, g, chunk) for (g, _w, chunk) in self.plan_keys]
+        caps, fills = list(table_caps), [0] * len(table_caps)
+        for pc, dc, mc in self.plan_caps:
+            caps += [pc * 2, dc * 4, mc * 4]
+            fills += [-1, -1, -1]    # padding items name batch row -1, which the kernels skip
+        self.fills = fills
+        self.static = StaticTables(executor.rt.device, caps)
+        self.graph = None
+        self.out = None
+
+    def _arrays(self, ht: HostTables) -> list:
+        arrays = list(ht.arrays)
+        for (g, w, chunk) in self.plan_keys:
+            prefill, decode, merge, _ = attention_work(ht.row_starts, ht.row_counts, g, w, chunk)
+            arrays += [np.asarray(prefill, np.int32), np.asarray(decode, np.int32), np.asarray(merge, np.int32)]
+        return arrays
+
+    def fits(self, ht: HostTables) -> bool:
+        self._pending = self._arrays(ht)
+        return self.static.fits(self._pending)
+
+    def run(self, ht: HostTables) -> torch.Tensor:
+        """Call after ``fits(ht)`` returned True."""
+        self.static.upload(self._pending, self.fills)
+        if self.graph is None:
+            return self._capture(ht)
+        self.graph.replay()
+        self.ex.rt.kernels.launches += self.launches
+        return self.out.clone()
+
+    def _capture(self, ht: HostTables) -> torch.Tensor:
+        ex = self.ex
+        batch = ex.builder.static_batch(ht, self.static, self.n_table)
+        views = self.static.views[self.n_table:]
+        for i, (key, (pc, dc, mc)) in enumerate(zip(self.plan_keys, self.plan_caps)):
+            batch.attention_plans[key] = AttentionPlan(prefill_items=pc, decode_items=dc, merge_items=mc, slots=dc,
+                                                       prefill_work=views[3 * i], decode_work=views[3 * i + 1],
+                                                       merge_work=views[3 * i + 2])
+        # this step's result comes from an eager run on a side stream (which also warms every kernel and library up);
+        # the capture that follows records the same launches without running them
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            result = ex.model.forward(batch, ex.storage).clone()
+        torch.cuda.current_stream().wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        before = ex.rt.kernels.launches
+        with torch.cuda.graph(graph):
+            out = ex.model.forward(batch, ex.storage)
+        self.launches = ex.rt.kernels.launches - before   # kernels one replay launches
+        ex.rt.kernels.launches = before
+        self.graph, self.out, self.batch = graph, out, batch
+        return result
+
+
 class StepExecutor:
     def __init__(self, model: Model, *, page_size: int = 16, num_pages: int | None = None, max_tokens: int | None = None,
-                 max_requests: int = 64, kv_fraction: float = 0.9):
+                 max_requests: int = 64, kv_fraction: float = 0.9, use_graphs: bool = True):
         """``num_pages`` per paged group, or ``max_tokens`` (the most tokens live requests hold at any time,
         rounded up to whole pages), or else ``kv_fraction`` of the device memory that is free now."""
         if page_size <= 0:
@@ -58,6 +133,13 @@ class StepExecutor:
         self.builder = BatchBuilder(self.rt.device, self.cache)
         self.steps_run = 0
         self.last_upload_bytes = 0
+        # decode steps are replayed from captured graphs when every run keeps paged keys and values only (a mixer with
+        # state of its own may be written in Python and may not be idempotent, so such models run eagerly)
+        self.use_graphs = (use_graphs and self.rt.device.type == "cuda"
+                           and all(g.kind == "paged" or not g.runs for g in self.groups))
+        self._graphs: dict = {}
+        self._plan_keys: list | None = None
+        self.graph_replays = 0
 
     # ------------------------------------------------------------------ one step
     def step(self, entries: list[StepEntry]) -> torch.Tensor:
@@ -101,18 +183,42 @@ class StepExecutor:
             rc = self.cache.extend(e.request_id, end)
             rows.append((rc, start, e.tokens, e.want))
         try:
-            batch = self.builder.build(rows, self.model.spec.vocab)
+            logits = self._run_graph(rows) if self.use_graphs else None
+            if logits is None:
+                batch = self.builder.build(rows, self.model.spec.vocab)
         except Exception:
             for rid in new_requests:
                 self.cache.free(rid)
             raise
-        self.last_upload_bytes = batch.host_buffer.numel() * batch.host_buffer.element_size()
-        self._zero_new_state(rows)
-        logits = self.model.forward(batch, self.storage)
+        if logits is None:
+            self.last_upload_bytes = batch.host_buffer.numel() * batch.host_buffer.element_size()
+            self._zero_new_state(rows)
+            logits = self.model.forward(batch, self.storage)
+            if self._plan_keys is None:
+                self._plan_keys = sorted(batch.attention_plans, key=repr)
         for (e, _, end) in plan:
             self.cache.commit(e.request_id, end)
         self.steps_run += 1
         return logits
+
+    def _run_graph(self, rows):
+        """Logits of a decode step through a captured graph, or None when the step is not one (or cannot be captured yet:
+        the first steps of a model run eagerly and tell which attention plans its mixers ask for)."""
+        if self._plan_keys is None or not all(len(r[2]) == 1 and list(r[3]) == [0] for r in rows):
+            return None
+        ht = self.builder.host_tables(rows, self.model.spec.vocab)
+        kv_cap = -(-ht.max_kv_len // GRAPH_KV_GRANULE) * GRAPH_KV_GRANULE
+        key = (ht.num_rows, kv_cap)
+        g = self._graphs.get(key)
+        if g is None:
+            if len(self._graphs) >= MAX_GRAPHS:
+                self._graphs.pop(next(iter(self._graphs)))
+            g = self._graphs[key] = DecodeGraph(self, ht.num_rows, kv_cap, self._plan_keys)
+        if not g.fits(ht):
+            return None
+        self.last_upload_bytes = g.static.total * 4
+        self.graph_replays += 1
+        return g.run(ht)
 
     def _zero_new_state(self, rows) -> None:
         """A request's fixed-size state starts at zero when its first token arrives, as the reference's worker
