@@ -62,39 +62,35 @@ struct Tile {
 };
 
 // Loads keys [j0, j0 + ROWS) of one key/value head into a K and a V tile. Keys outside [lo, hi] are zero-filled.
+// A thread owns one 16-byte chunk column and every (NTHREADS / chunks)-th row. The block-table lookups of all its
+// rows are issued first, then the copies, so the lookups' latencies overlap instead of adding up in front of each copy.
 template <int D, int ROWS, int NTHREADS>
 __device__ __forceinline__ void load_kv_tile(uint32_t k_smem, uint32_t v_smem, const __nv_bfloat16* __restrict__ k_pool,
                                              const __nv_bfloat16* __restrict__ v_pool, const int32_t* __restrict__ pages,
-                                             int page_size, int kv_heads, int kvh, int j0, int lo, int hi, int tid) {
+                                             int page_size, int page_shift, int kv_heads, int kvh, int j0, int lo, int hi, int tid) {
   constexpr int C = Tile<D>::kChunks;
-  static_assert((ROWS * C) % NTHREADS == 0 || NTHREADS % C == 0, "tile does not divide among the threads");
-  if constexpr (NTHREADS >= C) {
-    constexpr int ROWS_PER_PASS = NTHREADS / C;
-    const int ch = tid % C;
-    for (int r = tid / C; r < ROWS; r += ROWS_PER_PASS) {
+  static_assert(NTHREADS % C == 0 && NTHREADS >= C, "a row's chunks must divide the threads");
+  constexpr int ROWS_PER_PASS = NTHREADS / C;
+  constexpr int ITER = (ROWS + ROWS_PER_PASS - 1) / ROWS_PER_PASS;
+  const int ch = tid % C;
+  const int r0 = tid / C;
+  int page[ITER];
+#pragma unroll
+  for (int k = 0; k < ITER; ++k) {
+    const int j = j0 + r0 + k * ROWS_PER_PASS;
+    const bool valid = j >= lo && j <= hi && (r0 + k * ROWS_PER_PASS) < ROWS;
+    page[k] = valid ? pages[page_shift >= 0 ? (j >> page_shift) : (j / page_size)] : -1;
+  }
+#pragma unroll
+  for (int k = 0; k < ITER; ++k) {
+    const int r = r0 + k * ROWS_PER_PASS;
+    if (r < ROWS) {
       const int j = j0 + r;
-      const bool valid = j >= lo && j <= hi;
-      size_t base = 0;
-      if (valid) {
-        const int page = pages[j / page_size];
-        base = (((size_t)page * kv_heads + kvh) * page_size + (j % page_size)) * D + ch * 8;
-      }
+      const bool valid = page[k] >= 0;
+      const int off = page_shift >= 0 ? (j & (page_size - 1)) : (j % page_size);
+      const size_t base = valid ? (((size_t)page[k] * kv_heads + kvh) * page_size + off) * D + ch * 8 : 0;
       cp_async_16(k_smem + Tile<D>::offset(r, ch), k_pool + base, valid);
       cp_async_16(v_smem + Tile<D>::offset(r, ch), v_pool + base, valid);
-    }
-  } else {
-    for (int r = 0; r < ROWS; ++r) {
-      const int j = j0 + r;
-      const bool valid = j >= lo && j <= hi;
-      size_t base = 0;
-      if (valid) {
-        const int page = pages[j / page_size];
-        base = (((size_t)page * kv_heads + kvh) * page_size + (j % page_size)) * D;
-      }
-      for (int ch = tid; ch < C; ch += NTHREADS) {
-        cp_async_16(k_smem + Tile<D>::offset(r, ch), k_pool + base + ch * 8, valid);
-        cp_async_16(v_smem + Tile<D>::offset(r, ch), v_pool + base + ch * 8, valid);
-      }
     }
   }
 }
@@ -216,7 +212,7 @@ __global__ void __launch_bounds__(128) attention_prefill_kernel(const __nv_bfloa
                                                                 const int32_t* __restrict__ q_indptr, const int32_t* __restrict__ kv_lens,
                                                                 const int32_t* __restrict__ kv_indptr,
                                                                 const int32_t* __restrict__ kv_indices, const int2* __restrict__ work,
-                                                                int q_heads, int kv_heads, int page_size, float scale_log2, int window) {
+                                                                int q_heads, int kv_heads, int page_size, int page_shift, float scale_log2, int window) {
   constexpr int BM = 64, BN = 64, NT = 128;
   extern __shared__ __align__(128) unsigned char smem_raw[];
   const uint32_t smem = (uint32_t)__cvta_generic_to_shared(smem_raw);
@@ -258,7 +254,7 @@ __global__ void __launch_bounds__(128) attention_prefill_kernel(const __nv_bfloa
   const int t0 = lo / BN, t1 = hi / BN;
 
   load_q_tile<D, BM, NT>(q_smem, q, q_start, q_heads, group, kvh, row0, rows_total, tid);
-  load_kv_tile<D, BN, NT>(k_smem[0], v_smem[0], k_pool, v_pool, pages, page_size, kv_heads, kvh, t0 * BN, lo, hi, tid);
+  load_kv_tile<D, BN, NT>(k_smem[0], v_smem[0], k_pool, v_pool, pages, page_size, page_shift, kv_heads, kvh, t0 * BN, lo, hi, tid);
   cp_async_commit();
 
   RowState<D> st;
@@ -270,7 +266,7 @@ __global__ void __launch_bounds__(128) attention_prefill_kernel(const __nv_bfloa
   for (int t = t0; t <= t1; ++t) {
     const int stage = (t - t0) & 1;
     if (t + 1 <= t1) {
-      load_kv_tile<D, BN, NT>(k_smem[stage ^ 1], v_smem[stage ^ 1], k_pool, v_pool, pages, page_size, kv_heads, kvh, (t + 1) * BN, lo, hi, tid);
+      load_kv_tile<D, BN, NT>(k_smem[stage ^ 1], v_smem[stage ^ 1], k_pool, v_pool, pages, page_size, page_shift, kv_heads, kvh, (t + 1) * BN, lo, hi, tid);
       cp_async_commit();
       cp_async_wait<1>();
     } else {
@@ -303,7 +299,7 @@ __global__ void __launch_bounds__(NWARPS * 32)
                             const __nv_bfloat16* __restrict__ v_pool, const int32_t* __restrict__ q_indptr,
                             const int32_t* __restrict__ kv_lens, const int32_t* __restrict__ kv_indptr,
                             const int32_t* __restrict__ kv_indices, const int4* __restrict__ work, float* __restrict__ part_o,
-                            float* __restrict__ part_ml, int q_heads, int kv_heads, int page_size, float scale_log2, int window) {
+                            float* __restrict__ part_ml, int q_heads, int kv_heads, int page_size, int page_shift, float scale_log2, int window) {
   constexpr int BN = kDecodeTileKeys, STAGES = kDecodeStages;
   extern __shared__ __align__(128) unsigned char smem_raw[];
   const uint32_t smem = (uint32_t)__cvta_generic_to_shared(smem_raw);
@@ -362,7 +358,7 @@ __global__ void __launch_bounds__(NWARPS * 32)
   for (int s = 0; s < STAGES - 1; ++s) {
     if (s < mine) {
       const uint32_t dst = wbase + s * kStageBytes;
-      load_kv_tile<D, BN, 32>(dst, dst + kTileBytes, k_pool, v_pool, pages, page_size, kv_heads, kvh, (t0 + warp + s * NWARPS) * BN, lo, hi, lane);
+      load_kv_tile<D, BN, 32>(dst, dst + kTileBytes, k_pool, v_pool, pages, page_size, page_shift, kv_heads, kvh, (t0 + warp + s * NWARPS) * BN, lo, hi, lane);
     }
     cp_async_commit();
   }
@@ -373,7 +369,7 @@ __global__ void __launch_bounds__(NWARPS * 32)
     const uint32_t cur = wbase + (i % STAGES) * kStageBytes;
     if (i + STAGES - 1 < mine) {
       const uint32_t dst = wbase + ((i + STAGES - 1) % STAGES) * kStageBytes;
-      load_kv_tile<D, BN, 32>(dst, dst + kTileBytes, k_pool, v_pool, pages, page_size, kv_heads, kvh, (t + (STAGES - 1) * NWARPS) * BN, lo, hi, lane);
+      load_kv_tile<D, BN, 32>(dst, dst + kTileBytes, k_pool, v_pool, pages, page_size, page_shift, kv_heads, kvh, (t + (STAGES - 1) * NWARPS) * BN, lo, hi, lane);
     }
     cp_async_commit();
     cp_async_wait<STAGES - 1>();  // all but the newest STAGES - 1 groups are done: tile i has arrived
@@ -466,6 +462,13 @@ __global__ void attention_merge_kernel(__nv_bfloat16* __restrict__ out, const fl
   }
 }
 
+static int page_shift_of(int page_size) {
+  if (page_size & (page_size - 1)) return -1;
+  int s = 0;
+  while ((1 << s) < page_size) ++s;
+  return s;
+}
+
 template <int D>
 static int launch_prefill(const void* q, void* out, const void* k_pool, const void* v_pool, const int32_t* q_indptr, const int32_t* kv_lens,
                           const int32_t* kv_indptr, const int32_t* kv_indices, const int32_t* work, int items, int q_heads, int kv_heads,
@@ -479,7 +482,7 @@ static int launch_prefill(const void* q, void* out, const void* k_pool, const vo
   }
   kernel<<<dim3(items, kv_heads), 128, smem, s>>>((const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const __nv_bfloat16*)k_pool,
                                                   (const __nv_bfloat16*)v_pool, q_indptr, kv_lens, kv_indptr, kv_indices, (const int2*)work,
-                                                  q_heads, kv_heads, page_size, scale * kLog2e, window);
+                                                  q_heads, kv_heads, page_size, page_shift_of(page_size), scale * kLog2e, window);
   return check_launch("attention_prefill");
 }
 
@@ -498,8 +501,8 @@ static int launch_decode(const void* q, void* out, const void* k_pool, const voi
   }
   kernel<<<dim3(items, kv_heads), NW * 32, smem, s>>>((const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const __nv_bfloat16*)k_pool,
                                                       (const __nv_bfloat16*)v_pool, q_indptr, kv_lens, kv_indptr, kv_indices,
-                                                      (const int4*)work, part_o, part_ml, q_heads, kv_heads, page_size, scale * kLog2e,
-                                                      window);
+                                                      (const int4*)work, part_o, part_ml, q_heads, kv_heads, page_size, page_shift_of(page_size),
+                                                      scale * kLog2e, window);
   int rc = check_launch("attention_decode");
   if (rc != ROOST_OK || merge_items == 0) return rc;
   attention_merge_kernel<D><<<dim3(merge_items, kv_heads, 16), D < 128 ? D : 128, 0, s>>>((__nv_bfloat16*)out, part_o, part_ml, q_indptr,
