@@ -111,6 +111,13 @@ int roost_attention_decode_static(const void* q, void* out, const void* k_pool, 
 int roost_gemm_simt(const void* a, const void* w, void* out, int m, int n, int k, int64_t lda, int64_t ldw,
                     int64_t ldo, int in_dtype, int out_dtype, roost_stream_t stream);
 
+/* out[m,n] = sum_k x[m,k] * w[n,k] for 1 <= m <= 32 rows of bfloat16 x: weight-streaming, 32-bit accumulation
+ * (gemm_skinny.cu). roost_gemm_skinny_supported tells whether the sizes are served (n a multiple of 16, k a multiple
+ * of 32 and at least 256, rows of x and w on 16-byte boundaries). out_dtype: 1 bfloat16, 0 float32. */
+int roost_gemm_skinny_supported(int m, int n, int k, int64_t ldx, int64_t ldw);
+int roost_gemm_skinny(const void* x, const void* w, void* out, int m, int n, int k, int64_t ldx, int64_t ldw, int64_t ldo,
+                      int out_dtype, roost_stream_t stream);
+
 /* ids[r] = index of the largest logit of row r, ties to the lowest index, NaN never chosen (-1 if none). */
 int roost_argmax(const float* logits, int64_t stride, int rows, int vocab, int32_t* ids, roost_stream_t stream);
 

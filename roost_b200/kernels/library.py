@@ -62,6 +62,8 @@ _SIGNATURES = {
     "roost_attention_decode": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
     "roost_gemm_simt": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int, c_int, c_void_p],
+    "roost_gemm_skinny_supported": [c_int, c_int, c_int, c_int64, c_int64],
+    "roost_gemm_skinny": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int, c_void_p],
     "roost_argmax": [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p],
     "roost_sample": [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                      c_void_p, c_void_p],
@@ -81,7 +83,7 @@ class KernelLibrary:
             fn = getattr(self._lib, name)
             fn.argtypes = args
             fn.restype = c_int
-        self.decode_chunk = 256  # keys per CTA of the split decode attention; fixed, so results do not depend on the batch
+        self.decode_chunk = 512  # keys per CTA of the split decode attention; fixed, so results do not depend on the batch
         self.launches = 0  # kernels launched through this handle (a host-side count of entry-point calls that launch)
 
     def _call(self, name: str, *args, launches: int = 1):
@@ -210,6 +212,22 @@ class KernelLibrary:
         out = torch.empty((M, N), dtype=out_dtype, device=a.device)
         self._call("roost_gemm_simt", _ptr(a), _ptr(w), _ptr(out), M, N, K, a.stride(0), w.stride(0), out.stride(0),
                    dtype_code(a.dtype), dtype_code(out_dtype), _stream())
+        return out
+
+    def gemm_skinny_supported(self, m: int, n: int, k: int, ldx: int, ldw: int) -> bool:
+        return bool(self._lib.roost_gemm_skinny_supported(m, n, k, ldx, ldw))
+
+    def gemm_skinny(self, x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+        """x [M <= 32, K] times w [N, K] transposed, bfloat16 operands streamed once, 32-bit accumulation."""
+        _need(x, "x", torch.bfloat16); _need(w, "w", torch.bfloat16)
+        M, K = x.shape
+        N, K2 = w.shape
+        if K != K2:
+            raise KernelError(f"gemm_skinny: x has {K} columns, w has {K2}")
+        out_dtype = out_dtype or torch.bfloat16
+        out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+        self._call("roost_gemm_skinny", _ptr(x), _ptr(w), _ptr(out), M, N, K, x.stride(0), w.stride(0), out.stride(0),
+                   dtype_code(out_dtype), _stream())
         return out
 
     def argmax(self, logits: torch.Tensor) -> torch.Tensor:

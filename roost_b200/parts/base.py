@@ -53,6 +53,7 @@ class Runtime:
         self.dtype = dtype
         self.device = torch.device(device)
         self.kernels = kernels
+        self.use_skinny_gemm = False   # route products of at most 32 rows to the library's weight-streaming kernel
 
     @property
     def full_precision(self) -> bool:

@@ -2,7 +2,9 @@
 
 float32 runs the library's FFMA product (true 32-bit, the same bits for a row whatever the batch). bfloat16
 with 32-bit accumulation goes to cuBLAS through torch, the place where the reference's engine also calls a
-library (kernels/src/gemm.cu:235), unless a hand-written tensor-core product is selected for the shape.
+library (kernels/src/gemm.cu:235); with ``Runtime.use_skinny_gemm`` products of at most 32 rows run the library's
+own weight-streaming kernel instead (measured on a B200 it matches cuBLAS at 1 to 8 rows and is slower at 32, so
+it is off by default).
 """
 from __future__ import annotations
 
@@ -31,6 +33,9 @@ class Linear:
         out_dtype = out_dtype or self.rt.dtype
         if self.rt.full_precision:
             return k.gemm_simt(x, self.weight, torch.float32)
+        if self.rt.use_skinny_gemm and x.shape[0] <= 32 and x.is_contiguous() and k.gemm_skinny_supported(
+                x.shape[0], self.out_features, self.in_features, x.stride(0), self.weight.stride(0)):
+            return k.gemm_skinny(x, self.weight, out_dtype)   # a few rows: the library's weight-streaming product
         if out_dtype == torch.bfloat16:
             k.launches += 1
             return torch.matmul(x, self.weight.t())

@@ -305,7 +305,7 @@ def test_attention_mma_mixed_rows(kernels, window, nq, nkv, d, page):
     kp, vp, indptr, indices = build_paged(keys, values, page, dtype, num_pages=sum(-(-n // page) for n in lens) + 5, seed=22)
     scale = 1 / math.sqrt(d)
     out, plan = run_mma(kernels, q, kp, vp, lens, news, indptr, indices, scale, window)
-    assert plan.prefill_items > 0 and (nq // nkv > 16 or (plan.decode_items > 0 and plan.merge_items > 0))
+    assert plan.prefill_items > 0 and (nq // nkv > 16 or (plan.decode_items > 0 and (plan.merge_items > 0 or window is not None)))
     want = paged_reference(q.double(), keys, values, positions, rows, scale, window)
     assert not torch.isnan(out.float()).any(), "a slot outside the rows' visible keys was read"
     # the softmax weights are rounded to bfloat16 for the second product: 2^-8 of the values' size on top of the
@@ -357,3 +357,22 @@ def test_attention_mma_rows_do_not_depend_on_the_batch(kernels):
     alone, _ = run_mma(kernels, q[2:3], kp, vp, lens[2:], [1], torch.tensor([0, int(indptr[3] - indptr[2])], dtype=torch.int32).cuda(),
                        indices[int(indptr[2]):].contiguous(), 0.1, None)
     assert torch.equal(together[2:3], alone)
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 6144, 4096), (8, 4096, 12288), (5, 272, 320), (20, 64, 256), (32, 1024, 1056), (17, 9504, 512)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_gemm_skinny(kernels, m, n, k, out_dtype):
+    assert kernels.gemm_skinny_supported(m, n, k, k, k)
+    a = rand((m, k), torch.bfloat16, 31)
+    w = rand((n, k), torch.bfloat16, 32)
+    want = a.double().cpu() @ w.double().cpu().T
+    got = kernels.gemm_skinny(a, w, out_dtype)
+    if out_dtype == torch.float32:
+        close(got, want, torch.float32, "gemm_skinny f32 out", scale=k * 2.0 ** -23 / 2e-6)
+    else:
+        close(got, want, torch.bfloat16, "gemm_skinny", scale=math.sqrt(k) / 8)
+    # a row's bits do not depend on which other rows are in the product
+    r = m // 2
+    assert torch.equal(kernels.gemm_skinny(a[r : r + 1].contiguous(), w, out_dtype), got[r : r + 1])
+    assert not kernels.gemm_skinny_supported(33, n, k, k, k) and not kernels.gemm_skinny_supported(m, n + 1, k, k, k)
+    assert not kernels.gemm_skinny_supported(m, n, k + 8, k + 8, k + 8) and not kernels.gemm_skinny_supported(m, n, 128, 128, 128)
