@@ -1,0 +1,379 @@
+// out[m,n] = sum_k a[m,k] * w[n,k] in bfloat16 with 32-bit accumulation on the fifth-generation tensor cores:
+// TMA loads into 128-byte-swizzled shared memory, tcgen05.mma with the accumulator in tensor memory, a persistent
+// warp-specialised kernel. Definition of the result: src/Starlings.Roost.Ops/CpuOps.cs:395-437 (TransposeB, alpha 1, no
+// bias, 32-bit accumulation, one rounding); the reference calls cuBLASLt here (kernels/src/gemm.cu:235) and has no
+// Blackwell kernel of its own.
+//
+// One CTA per SM walks output tiles of 128 x 256 (m fastest, so neighbouring CTAs share a tile of w). Roles:
+//   warp 0, one lane: producer. Per k-block of 64 it waits for a free stage, arms the stage's barrier with the byte
+//     count and issues two TMA loads (a: 128 x 64, w: 256 x 64). Rows beyond m, n or k are zero-filled by the TMA unit.
+//   warp 1, one lane: issues four tcgen05.mma (128 x 256 x 16) per k-block into one of two accumulators of 256 tensor
+//     memory columns; tcgen05.commit hands the stage back to the producer and, after the last k-block, the accumulator
+//     to the epilogue.
+//   warps 2..5: epilogue. Each reads its 32 lanes of the accumulator (tcgen05.ld), rounds to the output type and stores
+//     rows of 32 columns; the other accumulator is being filled meanwhile.
+// Every wait on a barrier is bounded: a wait that does not complete within about a tenth of a second raises an abort
+// flag that every role polls, the kernel records an error code, lets copies in flight land, frees its tensor memory and
+// returns. roost_gemm_tcgen05_status() reads the code back.
+#include <cuda.h>
+
+#include <map>
+#include <mutex>
+#include <tuple>
+
+#include "common.cuh"
+
+namespace roost {
+
+constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4;
+constexpr int kUmmaK = 16;
+constexpr uint32_t kStageABytes = BM * BK * 2;
+constexpr uint32_t kStageBBytes = BN * BK * 2;
+constexpr uint32_t kStageBytes = kStageABytes + kStageBBytes;
+constexpr uint32_t kTmemCols = 512;  // two accumulators of BN columns
+constexpr long long kWaitCycles = 400000000LL;
+
+__device__ int g_gemm_tcgen05_error = 0;
+
+// ------------------------------------------------------------------------------------------------ PTX wrappers
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Waits for the barrier's phase with the given parity. Returns false when the wait was given up: another role raised
+// the abort flag, or the time limit passed (then this call raises it and records `code`).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (true) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (clock64() - t0 > kWaitCycles) {
+      *abort_flag = 1;
+      atomicCAS(&g_gemm_tcgen05_error, 0, code);
+      return false;
+    }
+    __nanosleep(64);
+  }
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c_inner, int c_outer) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n" ::"r"(dst),
+               "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c_inner), "r"(c_outer)
+               : "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tcgen05_mma_f16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_d), "l"(a_desc),
+      "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tcgen05_ld_32x32b_x32(uint32_t taddr, uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]),
+        "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]),
+        "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]),
+        "=r"(v[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64 bfloat16), 128-byte swizzle: eight-row
+// groups are 1024 bytes apart (stride byte offset), the leading byte offset is not used by swizzled K-major layouts.
+__device__ __forceinline__ uint64_t umma_desc_k_major_sw128(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);   // start address, 16-byte units
+  d |= (uint64_t)1 << 16;                        // leading byte offset (unused): 16 bytes
+  d |= (uint64_t)(1024 >> 4) << 32;              // stride byte offset
+  d |= (uint64_t)1 << 46;                        // descriptor version of this architecture
+  d |= (uint64_t)2 << 61;                        // layout: 128-byte swizzle
+  return d;
+}
+
+// Instruction descriptor of kind::f16: D float32, A and B bfloat16, both K-major, M x N as given.
+__host__ __device__ constexpr uint32_t umma_idesc_bf16(int m, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+template <typename TOut>
+__device__ __forceinline__ void store_row32(TOut* dst, const uint32_t (&v)[32], int valid_cols, bool vec_ok);
+
+template <>
+__device__ __forceinline__ void store_row32<__nv_bfloat16>(__nv_bfloat16* dst, const uint32_t (&v)[32], int valid_cols, bool vec_ok) {
+  if (valid_cols >= 32 && vec_ok) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      uint32_t p[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        __nv_bfloat162 b = __floats2bfloat162_rn(__uint_as_float(v[i * 8 + 2 * j]), __uint_as_float(v[i * 8 + 2 * j + 1]));
+        p[j] = *reinterpret_cast<uint32_t*>(&b);
+      }
+      *reinterpret_cast<uint4*>(dst + i * 8) = make_uint4(p[0], p[1], p[2], p[3]);
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i)
+      if (i < valid_cols) dst[i] = __float2bfloat16_rn(__uint_as_float(v[i]));
+  }
+}
+template <>
+__device__ __forceinline__ void store_row32<float>(float* dst, const uint32_t (&v)[32], int valid_cols, bool vec_ok) {
+  if (valid_cols >= 32 && vec_ok) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) *reinterpret_cast<uint4*>(dst + i * 4) = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i)
+      if (i < valid_cols) dst[i] = __uint_as_float(v[i]);
+  }
+}
+
+template <typename TOut>
+__global__ void __launch_bounds__(192, 1)
+    gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, TOut* __restrict__ out, int M,
+                        int N, int K, int64_t ldo) {
+  extern __shared__ unsigned char smem_raw[];
+  // tiles want 1024-byte alignment (the swizzle pattern repeats every 1024 bytes)
+  const uint32_t smem_base = ((uint32_t)__cvta_generic_to_shared(smem_raw) + 1023u) & ~1023u;
+  __shared__ __align__(8) uint64_t bars[2 * STAGES + 4];
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+  const uint32_t bar0 = (uint32_t)__cvta_generic_to_shared(bars);
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES + s); };
+  auto acc_full_bar = [&](int a) { return bar0 + 8u * (2 * STAGES + a); };
+  auto acc_empty_bar = [&](int a) { return bar0 + 8u * (2 * STAGES + 2 + a); };
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(acc_full_bar(a), 1);
+      mbar_init(acc_empty_bar(a), 4);  // one arrival per epilogue warp
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"((uint32_t)__cvta_generic_to_shared(&tmem_base_slot)),
+                 "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+  volatile int* abortp = &abort_flag;
+
+  const int m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN;
+  const int k_blocks = (K + BK - 1) / BK;
+  const int tiles = m_tiles * n_tiles;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
+        const int m0 = (t % m_tiles) * BM, n0 = (t / m_tiles) * BN;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!(ok = mbar_wait(empty_bar(stage), phase ^ 1u, abortp, 1))) break;
+          const uint32_t sa = smem_base + stage * kStageBytes;
+          mbar_expect_tx(full_bar(stage), kStageBytes);
+          tma_load_2d(sa, &tma_a, full_bar(stage), kb * BK, m0);
+          tma_load_2d(sa + kStageABytes, &tma_b, full_bar(stage), kb * BK, n0);
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int it = 0;
+      for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++it) {
+        const int acc = it & 1;
+        const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
+        if (!(ok = mbar_wait(acc_empty_bar(acc), acc_phase ^ 1u, abortp, 2))) break;
+        tcgen05_fence_after();
+        const uint32_t tmem_d = tmem_base + (uint32_t)acc * BN;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!(ok = mbar_wait(full_bar(stage), phase, abortp, 3))) break;
+          tcgen05_fence_after();
+          const uint32_t sa = smem_base + stage * kStageBytes;
+          const uint64_t a_desc = umma_desc_k_major_sw128(sa);
+          const uint64_t b_desc = umma_desc_k_major_sw128(sa + kStageABytes);
+#pragma unroll
+          for (int k = 0; k < BK / kUmmaK; ++k) {
+            // inside the 128-byte swizzle row a step of 16 elements is 32 bytes: two 16-byte units of the address field
+            tcgen05_mma_f16(tmem_d, a_desc + (uint64_t)(2 * k), b_desc + (uint64_t)(2 * k), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          tcgen05_commit(empty_bar(stage));  // the stage is free once these products have read it
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (ok) tcgen05_commit(acc_full_bar(acc));
+      }
+    }
+  } else {
+    // epilogue warps 2..5; warp w may read tensor-memory lanes 32 * (w % 4) .. + 31
+    const int lane_group = warp & 3;
+    const bool vec_ok = (ldo * (int64_t)sizeof(TOut)) % 16 == 0 && ((uintptr_t)out % 16) == 0;
+    bool ok = true;
+    int it = 0;
+    for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++it) {
+      const int acc = it & 1;
+      const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
+      const int m0 = (t % m_tiles) * BM, n0 = (t / m_tiles) * BN;
+      if (!(ok = mbar_wait(acc_full_bar(acc), acc_phase, abortp, 4))) break;
+      tcgen05_fence_after();
+      const int row = m0 + lane_group * 32 + lane;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t v[32];
+        tcgen05_ld_32x32b_x32(tmem_base + ((uint32_t)(lane_group * 32) << 16) + (uint32_t)(acc * BN + c * 32), v);
+        const int col = n0 + c * 32;
+        if (row < M && col < N) store_row32<TOut>(out + (size_t)row * ldo + col, v, N - col, vec_ok);
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_empty_bar(acc));
+    }
+  }
+
+  // common exit: on an abort give copies in flight time to land before shared memory is released
+  __syncwarp();
+  if (*abortp) {
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000LL) __nanosleep(256);
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+  });
+  return fn;
+}
+
+// A [rows, k] bfloat16 matrix with row stride ld elements as a 2-D tensor map with boxes of box_rows x 64 elements.
+static int make_map(CUtensorMap* map, const void* base, int rows, int k, int64_t ld, int box_rows) {
+  EncodeTiledFn enc = encode_tiled();
+  if (!enc) return fail(ROOST_ERR_CUDA, "gemm_tcgen05: the driver does not export cuTensorMapEncodeTiled");
+  const cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  const cuuint32_t elem[2] = {1, 1};
+  const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(ROOST_ERR_CUDA, "gemm_tcgen05: cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
+  return ROOST_OK;
+}
+
+template <typename TOut>
+static int launch_tcgen05(const CUtensorMap& ma, const CUtensorMap& mb, void* out, int m, int n, int k, int64_t ldo, cudaStream_t s) {
+  static int sms = 0;
+  static bool attr_set = false;
+  const size_t smem = (size_t)STAGES * kStageBytes + 1024;
+  auto kernel = gemm_tcgen05_kernel<TOut>;
+  if (!attr_set) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    attr_set = true;
+  }
+  const int tiles = ((m + BM - 1) / BM) * ((n + BN - 1) / BN);
+  const int grid = tiles < sms ? tiles : sms;
+  kernel<<<grid, 192, smem, s>>>(ma, mb, (TOut*)out, m, n, k, ldo);
+  return check_launch("gemm_tcgen05");
+}
+
+}  // namespace roost
+
+using namespace roost;
+
+extern "C" int roost_gemm_tcgen05_supported(int m, int n, int k, int64_t lda, int64_t ldw) {
+  return m >= 1 && n >= 1 && k >= 8 && k % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0;
+}
+
+// The error code a kernel recorded when it gave a wait up (0: none), cleared by the call. 1: producer waiting for a free
+// stage, 2: issuer waiting for a free accumulator, 3: issuer waiting for a stage's data, 4: epilogue waiting for an
+// accumulator. Synchronises the device.
+extern "C" int roost_gemm_tcgen05_status(void) {
+  int code = 0;
+  if (cudaMemcpyFromSymbol(&code, g_gemm_tcgen05_error, sizeof(int)) != cudaSuccess) return -1;
+  if (code != 0) {
+    const int zero = 0;
+    cudaMemcpyToSymbol(g_gemm_tcgen05_error, &zero, sizeof(int));
+  }
+  return code;
+}
+
+extern "C" int roost_gemm_tcgen05(const void* a, const void* w, void* out, int m, int n, int k, int64_t lda, int64_t ldw, int64_t ldo,
+                                  int out_dtype, roost_stream_t stream) {
+  ROOST_REQUIRE(out_dtype == ROOST_BF16 || out_dtype == ROOST_F32, "gemm_tcgen05: the output is bfloat16 (1) or float32 (0)");
+  ROOST_REQUIRE(lda >= k && ldw >= k && ldo >= n, "gemm_tcgen05: a leading dimension is smaller than its row");
+  if (!roost_gemm_tcgen05_supported(m, n, k, lda, ldw)) {
+    return fail(ROOST_ERR_UNSUPPORTED, "gemm_tcgen05: k and the row strides must be multiples of 8 elements (TMA wants 16-byte strides)");
+  }
+  ROOST_REQUIRE(((uintptr_t)a % 16 == 0) && ((uintptr_t)w % 16 == 0), "gemm_tcgen05: a and w must start on 16-byte boundaries");
+  CUtensorMap ma, mb;
+  int rc = make_map(&ma, a, m, k, lda, BM);
+  if (rc != ROOST_OK) return rc;
+  rc = make_map(&mb, w, n, k, ldw, BN);
+  if (rc != ROOST_OK) return rc;
+  if (out_dtype == ROOST_BF16) return launch_tcgen05<__nv_bfloat16>(ma, mb, out, m, n, k, ldo, (cudaStream_t)stream);
+  return launch_tcgen05<float>(ma, mb, out, m, n, k, ldo, (cudaStream_t)stream);
+}

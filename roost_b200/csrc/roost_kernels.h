@@ -118,6 +118,15 @@ int roost_gemm_skinny_supported(int m, int n, int k, int64_t ldx, int64_t ldw);
 int roost_gemm_skinny(const void* x, const void* w, void* out, int m, int n, int k, int64_t ldx, int64_t ldw, int64_t ldo,
                       int out_dtype, roost_stream_t stream);
 
+/* out[m,n] = sum_k a[m,k] * w[n,k], bfloat16 operands, 32-bit accumulation in tensor memory (tcgen05.mma fed by TMA;
+ * gemm_tcgen05.cu). k and the row strides must be multiples of 8. out_dtype: 1 bfloat16, 0 float32. Every wait inside
+ * the kernel is bounded; roost_gemm_tcgen05_status() returns the code of a wait that was given up since the last call
+ * (0: none) and synchronises the device. */
+int roost_gemm_tcgen05_supported(int m, int n, int k, int64_t lda, int64_t ldw);
+int roost_gemm_tcgen05(const void* a, const void* w, void* out, int m, int n, int k, int64_t lda, int64_t ldw, int64_t ldo,
+                       int out_dtype, roost_stream_t stream);
+int roost_gemm_tcgen05_status(void);
+
 /* ids[r] = index of the largest logit of row r, ties to the lowest index, NaN never chosen (-1 if none). */
 int roost_argmax(const float* logits, int64_t stride, int rows, int vocab, int32_t* ids, roost_stream_t stream);
 

@@ -64,6 +64,9 @@ _SIGNATURES = {
     "roost_gemm_simt": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int, c_int, c_void_p],
     "roost_gemm_skinny_supported": [c_int, c_int, c_int, c_int64, c_int64],
     "roost_gemm_skinny": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int, c_void_p],
+    "roost_gemm_tcgen05_supported": [c_int, c_int, c_int, c_int64, c_int64],
+    "roost_gemm_tcgen05": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int, c_void_p],
+    "roost_gemm_tcgen05_status": [],
     "roost_argmax": [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p],
     "roost_sample": [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                      c_void_p, c_void_p],
@@ -229,6 +232,26 @@ class KernelLibrary:
         self._call("roost_gemm_skinny", _ptr(x), _ptr(w), _ptr(out), M, N, K, x.stride(0), w.stride(0), out.stride(0),
                    dtype_code(out_dtype), _stream())
         return out
+
+    def gemm_tcgen05_supported(self, m: int, n: int, k: int, lda: int, ldw: int) -> bool:
+        return bool(self._lib.roost_gemm_tcgen05_supported(m, n, k, lda, ldw))
+
+    def gemm_tcgen05(self, a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+        """a [M, K] times w [N, K] transposed on the tcgen05 tensor cores (TMA loads, accumulator in tensor memory)."""
+        _need(a, "a", torch.bfloat16); _need(w, "w", torch.bfloat16)
+        M, K = a.shape
+        N, K2 = w.shape
+        if K != K2:
+            raise KernelError(f"gemm_tcgen05: a has {K} columns, w has {K2}")
+        out_dtype = out_dtype or torch.bfloat16
+        out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+        self._call("roost_gemm_tcgen05", _ptr(a), _ptr(w), _ptr(out), M, N, K, a.stride(0), w.stride(0), out.stride(0),
+                   dtype_code(out_dtype), _stream())
+        return out
+
+    def gemm_tcgen05_status(self) -> int:
+        """The code of a bounded wait the tcgen05 product gave up since the last call (0: none); synchronises."""
+        return int(self._lib.roost_gemm_tcgen05_status())
 
     def argmax(self, logits: torch.Tensor) -> torch.Tensor:
         _need(logits, "logits", torch.float32)
