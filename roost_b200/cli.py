@@ -119,15 +119,18 @@ def cmd_generate(opts) -> int:
     dtype = opts.get("--dtype", "bfloat16")
     if dtype not in ("bfloat16", "float32"):
         raise UsageError("--dtype is bfloat16 or float32")
+    # every option is read before anything is loaded, so a bad value is a usage error whatever the model is
+    engine_opts = dict(page_size=_int(opts, "--page-size", 16), attention_blocks=_int(opts, "--attention-blocks"),
+                       max_sequences=_int(opts, "--max-sequences", 64), max_tokens=_int(opts, "--max-tokens", 2048),
+                       max_chunk_tokens=_int(opts, "--max-chunk-tokens"))
+    gen_opts = dict(max_output_tokens=_int(opts, "--max-output-tokens", 16), temperature=_float(opts, "--temperature"),
+                    top_p=_float(opts, "--top-p"), top_k=_int(opts, "--top-k"), min_p=_float(opts, "--min-p"),
+                    seed=_int(opts, "--seed"), stop_token_ids=tuple(_ids(opts.get("--stop-ids", ""), "--stop-ids")),
+                    ignore_eos="--ignore-eos" in opts)
     _apply_common(opts)
     from .engine.engine import GenerationOptions, RoostEngine
-    engine = RoostEngine(model, dtype=dtype, page_size=_int(opts, "--page-size", 16), attention_blocks=_int(opts, "--attention-blocks"),
-                         max_sequences=_int(opts, "--max-sequences", 64), max_tokens=_int(opts, "--max-tokens", 2048),
-                         max_chunk_tokens=_int(opts, "--max-chunk-tokens"))
-    go = GenerationOptions(max_output_tokens=_int(opts, "--max-output-tokens", 16), temperature=_float(opts, "--temperature"),
-                           top_p=_float(opts, "--top-p"), top_k=_int(opts, "--top-k"), min_p=_float(opts, "--min-p"),
-                           seed=_int(opts, "--seed"), stop_token_ids=tuple(_ids(opts.get("--stop-ids", ""), "--stop-ids")),
-                           ignore_eos="--ignore-eos" in opts)
+    engine = RoostEngine(model, dtype=dtype, **engine_opts)
+    go = GenerationOptions(**gen_opts)
     for prompt, out in zip(prompts, engine.generate(prompts, go)):
         print(json.dumps({"prompt_tokens": len(prompt), "token_ids": out.token_ids, "finish_reason": out.finish_reason}))
     return 0
@@ -218,6 +221,9 @@ def main(argv=None) -> int:
     except UsageError as e:
         print(f"roost: {e}\n\nusage:\n{USAGE}", file=sys.stderr)
         return 2
+    except (ValueError, RuntimeError, OSError) as e:  # a config, weight, request or kernel error: one line, no traceback
+        print(f"roost: error: {e}", file=sys.stderr)
+        return 1
 
 
 if __name__ == "__main__":

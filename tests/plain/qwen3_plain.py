@@ -63,7 +63,7 @@ def load_model_dir(model_dir, round_to_bf16: bool = False) -> tuple[dict, dict[s
 # --------------------------------------------------------------------------------------------------
 def embedding(table: torch.Tensor, ids) -> torch.Tensor:
     """h0[t,:] = table[ids[t],:], no scaling (src/Starlings.Roost.Ops/CpuOps.cs:441-458)."""
-    ids = torch.as_tensor(ids, dtype=torch.long)
+    ids = torch.as_tensor(ids, dtype=torch.long, device=table.device)
     if ((ids < 0) | (ids >= table.shape[0])).any():
         raise ValueError("token id outside the vocabulary")
     return table[ids]
@@ -90,9 +90,9 @@ def rope_neox(x: torch.Tensor, positions, theta: float, rotary_dim: int | None =
     d = x.shape[-1]
     rot = d if rotary_dim is None else rotary_dim
     half = rot // 2
-    pos = torch.as_tensor(positions, dtype=F64)
-    i = torch.arange(half, dtype=F64)
-    freq = torch.pow(torch.tensor(float(theta), dtype=F64), -2.0 * i / rot)
+    pos = torch.as_tensor(positions, dtype=F64, device=x.device)
+    i = torch.arange(half, dtype=F64, device=x.device)
+    freq = torch.pow(torch.tensor(float(theta), dtype=F64, device=x.device), -2.0 * i / rot)
     ang = pos[:, None] * freq[None, :]
     c = torch.cos(ang)[:, None, :].to(x.dtype)
     s = torch.sin(ang)[:, None, :].to(x.dtype)
@@ -113,7 +113,7 @@ def causal_gqa_attention(q, k, v, scale: float, window: int | None = None) -> to
     nkv = k.shape[1]
     group = nq // nkv
     out = torch.zeros_like(q)
-    idx = torch.arange(T)
+    idx = torch.arange(T, device=q.device)
     visible = idx[None, :] <= idx[:, None]
     if window is not None:
         visible &= idx[None, :] > (idx[:, None] - window)

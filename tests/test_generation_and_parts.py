@@ -326,3 +326,65 @@ def test_a_toy_mixer_with_its_own_state_is_registered_built_and_stepped(backend)
     got = H.run_portions(ex, "c", b, [4, 2, 9])
     assert H.scaled_error(got, plain_forward(b)) < bound
     assert ex.cache.pools[1].free_count == 3
+
+
+# ------------------------------------------------------------------------------------------ position encoding and block alone
+def test_position_encoding_part_alone(backend):
+    from roost_b200.parts import POSITIONS
+    rt = runtime(backend)
+    rope = POSITIONS.build(PositionSpec(kind="rope_neox", rotary_dim=48, theta=5e5, max_positions=77), rt)
+    inv_freq, rot = rope.rotation()
+    assert rot == 48 and inv_freq.dtype == torch.float64 and rope.max_positions == 77
+    want = torch.pow(torch.tensor(5e5, dtype=torch.float64), -2.0 * torch.arange(24, dtype=torch.float64) / 48)
+    assert torch.allclose(inv_freq.cpu(), want, rtol=0, atol=0)
+    assert POSITIONS.build(PositionSpec(kind="none"), rt).rotation() == (None, 0)
+    with pytest.raises(ValueError):
+        POSITIONS.build(PositionSpec(kind="rope_neox", rotary_dim=7, theta=1e4), rt)
+    # through the fused kernel: rotating x at position p equals the plain rotation (no norm, no cache write)
+    g = torch.Generator().manual_seed(4)
+    x = torch.randn(5, 3 * 64, generator=g).to(rt.dtype)
+    positions = torch.tensor([0, 1, 17, 300, 76], dtype=torch.int32)
+    got = rt.kernels.qk_norm_rope_cache(x.to(rt.device), 3, 0, 64, q_w=None, k_w=None, eps=1.0, inv_freq=inv_freq, rotary_dim=48,
+                                        positions=positions.to(rt.device), write_kv=False)
+    want_x = plain.rope_neox(x.double().reshape(5, 3, 64), positions.tolist(), 5e5, 48)
+    assert H.scaled_error(got, want_x) < (4e-6 if rt.full_precision else 2 ** -6)
+
+
+def test_block_arrangement_alone(backend, tiny_model_dirs):
+    """One pre-norm block over the step function's tables: h' = h + mixer(norm1(h)); out = h' + ff(norm2(h'))."""
+    from roost_b200.cache.manager import CacheManager, build_groups
+    from roost_b200.cache.storage import CacheStorage
+    from roost_b200.engine.batch import BatchBuilder
+    rt = runtime(backend)
+    norm = NormSpec(size=48, eps=1e-5)
+    spec = BlockSpec(mixer=attention_spec(None), feed_forward=GatedMlpSpec(hidden=48, intermediate=80), input_norm=norm, post_mixer_norm=norm)
+    block = BLOCKS.build(spec, rt)
+    g = torch.Generator().manual_seed(5)
+    P = {"input_norm": {"weight": 1 + 0.1 * torch.randn(48, generator=g)}, "post_mixer_norm": {"weight": 1 + 0.1 * torch.randn(48, generator=g)},
+         # weights small enough that the block's output stays O(1): bfloat16 rounding is relative to the values' size
+         "mixer": {"qkv": torch.randn(160, 48, generator=g) * 0.1, "out": torch.randn(48, 96, generator=g) * 0.1,
+                   "q_norm": 1 + 0.1 * torch.randn(16, generator=g), "k_norm": 1 + 0.1 * torch.randn(16, generator=g)},
+         "feed_forward": {"gate_up": torch.randn(160, 48, generator=g) * 0.1, "down": torch.randn(48, 80, generator=g) * 0.1}}
+    P = {s: {k: (v.to(rt.dtype) if v.dim() == 2 else v) for k, v in p.items()} for s, p in P.items()}
+    for name, part in block.sub_parts().items():
+        part.load({k: v.to(rt.device) for k, v in P[name].items()})
+    T = 21
+    h = torch.randn(T, 48, generator=g).to(rt.dtype)
+    D = {s: {k: v.double() for k, v in p.items()} for s, p in P.items()}
+    x = plain.rms_norm(h.double(), D["input_norm"]["weight"], 1e-5)
+    w = {"q_proj.weight": D["mixer"]["qkv"][:96], "k_proj.weight": D["mixer"]["qkv"][96:128], "v_proj.weight": D["mixer"]["qkv"][128:],
+         "o_proj.weight": D["mixer"]["out"], "q_norm.weight": D["mixer"]["q_norm"], "k_norm.weight": D["mixer"]["k_norm"]}
+    cfg = dict(num_attention_heads=6, num_key_value_heads=2, head_dim=16, rms_norm_eps=1e-6, rope_theta=1e4)
+    mix, _ = plain.attention_mixer(x, list(range(T)), w, "", cfg, None)
+    hm = h.double() + mix
+    y = plain.rms_norm(hm, D["post_mixer_norm"]["weight"], 1e-5)
+    want = hm + plain.swiglu_mlp(y, D["feed_forward"]["gate_up"][:80], D["feed_forward"]["gate_up"][80:], D["feed_forward"]["down"])
+
+    groups = build_groups([block.mixer.cache_need()], page_size=8)
+    cm = CacheManager(groups, [6, 2])
+    storage = CacheStorage(groups, [6, 2], rt.dtype, rt.device)
+    rc = cm.extend("r", T)
+    batch = BatchBuilder(rt.device, cm).build([(rc, 0, [0] * T, [])], vocab=1)
+    out, residual = block(h.to(rt.device), None, batch, storage.view(0))
+    got = out.double().cpu() + residual.double().cpu()       # the block hands back the branch output and the stream it joins
+    assert H.scaled_error(got, want) < (1e-5 if rt.full_precision else 2 ** -4)
