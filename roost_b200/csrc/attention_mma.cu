@@ -124,17 +124,29 @@ __device__ __forceinline__ void attend_tile(RowState<D>& st, uint32_t q_smem, in
       mma_bf16(s[2 * n2 + 1], a0, a1, a2, a3, b2, b3);
     }
   }
-  // mask and running maximum
+  // mask and running maximum; a tile every key of which both rows see needs no per-element test
   float mx[2] = {-INFINITY, -INFINITY};
+  const bool all_visible = j0 + BN - 1 <= min(qpos[0], qpos[1]) && j0 >= max(qlo[0], qlo[1]);
+  if (__all_sync(0xffffffffu, all_visible)) {
 #pragma unroll
-  for (int n = 0; n < NT; ++n) {
+    for (int n = 0; n < NT; ++n) {
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const int r = e >> 1;
-      const int j = j0 + n * 8 + (lane & 3) * 2 + (e & 1);
-      const float v = (j <= qpos[r] && j >= qlo[r]) ? s[n][e] * scale_log2 : -INFINITY;
-      s[n][e] = v;
-      mx[r] = fmaxf(mx[r], v);
+      for (int e = 0; e < 4; ++e) {
+        s[n][e] *= scale_log2;
+        mx[e >> 1] = fmaxf(mx[e >> 1], s[n][e]);
+      }
+    }
+  } else {
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int r = e >> 1;
+        const int j = j0 + n * 8 + (lane & 3) * 2 + (e & 1);
+        const float v = (j <= qpos[r] && j >= qlo[r]) ? s[n][e] * scale_log2 : -INFINITY;
+        s[n][e] = v;
+        mx[r] = fmaxf(mx[r], v);
+      }
     }
   }
   float corr[2], msafe[2];

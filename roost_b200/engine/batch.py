@@ -47,7 +47,7 @@ class AttentionPlan:
 
 def attention_work(row_starts, row_counts, group: int, window: int | None, chunk: int):
     """(prefill pairs, decode quadruples, merge quadruples, slots) as flat int lists."""
-    prefill, decode, merge = [], [], []
+    prefill, decode, merge, tiles = [], [], [], []
     slots = 0
     for b, (start, n) in enumerate(zip(row_starts, row_counts)):
         rows, kv_len = n * group, start + n
@@ -64,7 +64,10 @@ def attention_work(row_starts, row_counts, group: int, window: int | None, chunk
                     slots += 1
         else:
             for r0 in range(0, rows, 64):
-                prefill += [b, r0]
+                tiles.append((start + min(rows, r0 + 64) // group, b, r0))
+    # the tiles with the longest history run longest: they go first, so that the last wave of CTAs is the lightest
+    for _, b, r0 in sorted(tiles, key=lambda t: -t[0]):
+        prefill += [b, r0]
     return prefill, decode, merge, slots
 
 
