@@ -53,12 +53,14 @@ __global__ void rms_norm_kernel(const T* __restrict__ x, T* residual, const void
 
 // ---------------------------------------------------------------------------------------------- silu and multiply
 template <typename T>
-__global__ void silu_mul_kernel(const T* __restrict__ x, T* __restrict__ out, int inter) {
+__global__ void silu_mul_kernel(const T* __restrict__ x, T* __restrict__ out, int inter, int block) {
   const size_t t = blockIdx.x;
   const int i = blockIdx.y * blockDim.x + threadIdx.x;
   if (i >= inter) return;
-  const float g = to_float(x[t * 2 * inter + i]);
-  const float u = to_float(x[t * 2 * inter + inter + i]);
+  const size_t g_at = block ? (size_t)(i / block) * 2 * block + i % block : (size_t)i;
+  const size_t u_at = block ? g_at + block : (size_t)inter + i;
+  const float g = to_float(x[t * 2 * inter + g_at]);
+  const float u = to_float(x[t * 2 * inter + u_at]);
   out[t * inter + i] = from_float<T>(g / (1.0f + expf(-g)) * u);
 }
 
@@ -144,15 +146,19 @@ __global__ void rms_norm_vec_kernel(const T* __restrict__ x, T* residual, const 
   }
 }
 
+// block 0: a row of x is [gate (inter) | up (inter)]; block b > 0: blocks of b gate values followed by their b up values.
 template <typename T>
-__global__ void silu_mul_vec_kernel(const T* __restrict__ x, T* __restrict__ out, int inter) {
+__global__ void silu_mul_vec_kernel(const T* __restrict__ x, T* __restrict__ out, int inter, int block) {
   constexpr int N = Vec<T>::N;
   const size_t t = blockIdx.x;
   const int vi = blockIdx.y * blockDim.x + threadIdx.x;
   if (vi * N >= inter) return;
   float g[N], u[N], o[N];
-  Vec<T>::load(x + t * 2 * inter + (size_t)vi * N, g);
-  Vec<T>::load(x + t * 2 * inter + inter + (size_t)vi * N, u);
+  const int j = vi * N;
+  const size_t g_at = block ? (size_t)(j / block) * 2 * block + j % block : (size_t)j;
+  const size_t u_at = block ? g_at + block : (size_t)inter + j;
+  Vec<T>::load(x + t * 2 * inter + g_at, g);
+  Vec<T>::load(x + t * 2 * inter + u_at, u);
 #pragma unroll
   for (int e = 0; e < N; ++e) o[e] = g[e] / (1.0f + expf(-g[e])) * u[e];
   Vec<T>::store(out + t * inter + (size_t)vi * N, o);
@@ -219,8 +225,10 @@ extern "C" int roost_add_rms_norm(const void* x, void* residual, const void* w, 
   return launch_norm<true>(x, residual, w, out, rows, n_out, hidden, eps, dtype, wdtype, stream);
 }
 
-extern "C" int roost_silu_mul(const void* x, void* out, int tokens, int inter, int dtype, roost_stream_t stream) {
+extern "C" int roost_silu_mul(const void* x, void* out, int tokens, int inter, int block, int dtype, roost_stream_t stream) {
   ROOST_REQUIRE(tokens >= 0 && inter > 0, "silu_mul: tokens and inter must be positive");
+  ROOST_REQUIRE(block >= 0 && (block == 0 || (inter % block == 0 && block % 8 == 0)),
+                "silu_mul: the interleave block must divide inter and be a multiple of 8");
   if (tokens == 0) return ROOST_OK;
   {
     const int vec = dtype == ROOST_F32 ? 4 : 8;
@@ -228,13 +236,13 @@ extern "C" int roost_silu_mul(const void* x, void* out, int tokens, int inter, i
       const int nvec = inter / vec;
       dim3 grid(tokens, (nvec + 127) / 128);
       if (grid.y <= 65535) {
-        ROOST_DISPATCH_DTYPE(dtype, T, silu_mul_vec_kernel<T><<<grid, 128, 0, (cudaStream_t)stream>>>((const T*)x, (T*)out, inter));
+        ROOST_DISPATCH_DTYPE(dtype, T, silu_mul_vec_kernel<T><<<grid, 128, 0, (cudaStream_t)stream>>>((const T*)x, (T*)out, inter, block));
         return check_launch("silu_mul");
       }
     }
   }
   if ((inter + 255) / 256 > 65535) return fail(ROOST_ERR_UNSUPPORTED, "silu_mul: inter beyond 16776960");
   dim3 grid(tokens, (inter + 255) / 256);
-  ROOST_DISPATCH_DTYPE(dtype, T, silu_mul_kernel<T><<<grid, 256, 0, (cudaStream_t)stream>>>((const T*)x, (T*)out, inter));
+  ROOST_DISPATCH_DTYPE(dtype, T, silu_mul_kernel<T><<<grid, 256, 0, (cudaStream_t)stream>>>((const T*)x, (T*)out, inter, block));
   return check_launch("silu_mul");
 }

@@ -54,26 +54,43 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n.reg .pred p;\nmbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
 // Waits for the barrier's phase with the given parity. Returns false when the wait was given up: another role raised
 // the abort flag, or the time limit passed (then this call raises it and records `code`).
+template <bool CLUSTER = false>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
-  if (mbar_try_wait(bar, parity)) return true;
+  auto try_wait = [&]() { return CLUSTER ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity); };
+  if (try_wait()) return true;
   const long long t0 = clock64();
   while (true) {
-    if (mbar_try_wait(bar, parity)) return true;
+    if (try_wait()) return true;
     if (*abort_flag) return false;
     if (clock64() - t0 > kWaitCycles) {
       *abort_flag = 1;
       atomicCAS(&g_gemm_tcgen05_error, 0, code);
       return false;
     }
-    __nanosleep(64);
   }
 }
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c_inner, int c_outer) {
   asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n" ::"r"(dst),
                "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c_inner), "r"(c_outer)
                : "memory");
+}
+// The pair form: the barrier may live in the other CTA of the pair (a shared::cluster address).
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t cluster_bar, int c_inner, int c_outer) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(cluster_bar), "r"(c_inner), "r"(c_outer)
+      : "memory");
 }
 __device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
 __device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
@@ -150,7 +167,12 @@ __device__ __forceinline__ void store_row32<float>(float* dst, const uint32_t (&
   }
 }
 
-template <typename TOut>
+__device__ __forceinline__ float silu_f(float g) { return g / (1.0f + expf(-g)); }
+
+// EPI 0: out = acc. EPI 1 (SwiGLU): w's rows come in blocks of 256, 128 gate rows followed by the 128 up rows of the same
+// outputs, so a tile's columns 0..127 are gate and 128..255 the matching up values: out[m, n0/2 + j] = silu(gate_j) * up_j,
+// and out has n/2 columns.
+template <typename TOut, int EPI>
 __global__ void __launch_bounds__(192, 1)
     gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, TOut* __restrict__ out, int M,
                         int N, int K, int64_t ldo) {
@@ -261,12 +283,26 @@ __global__ void __launch_bounds__(192, 1)
       if (!(ok = mbar_wait(acc_full_bar(acc), acc_phase, abortp, 4))) break;
       tcgen05_fence_after();
       const int row = m0 + lane_group * 32 + lane;
+      if (EPI == 0) {
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t v[32];
-        tcgen05_ld_32x32b_x32(tmem_base + ((uint32_t)(lane_group * 32) << 16) + (uint32_t)(acc * BN + c * 32), v);
-        const int col = n0 + c * 32;
-        if (row < M && col < N) store_row32<TOut>(out + (size_t)row * ldo + col, v, N - col, vec_ok);
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t v[32];
+          tcgen05_ld_32x32b_x32(tmem_base + ((uint32_t)(lane_group * 32) << 16) + (uint32_t)(acc * BN + c * 32), v);
+          const int col = n0 + c * 32;
+          if (row < M && col < N) store_row32<TOut>(out + (size_t)row * ldo + col, v, N - col, vec_ok);
+        }
+      } else {
+        const int n_out = N / 2;
+#pragma unroll 1
+        for (int c = 0; c < BN / 64; ++c) {
+          uint32_t g[32], u[32];
+          tcgen05_ld_32x32b_x32(tmem_base + ((uint32_t)(lane_group * 32) << 16) + (uint32_t)(acc * BN + c * 32), g);
+          tcgen05_ld_32x32b_x32(tmem_base + ((uint32_t)(lane_group * 32) << 16) + (uint32_t)(acc * BN + BN / 2 + c * 32), u);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) g[i] = __float_as_uint(silu_f(__uint_as_float(g[i])) * __uint_as_float(u[i]));
+          const int col = n0 / 2 + c * 32;
+          if (row < M && col < n_out) store_row32<TOut>(out + (size_t)row * ldo + col, g, n_out - col, vec_ok);
+        }
       }
       tcgen05_fence_before();
       __syncwarp();
@@ -285,6 +321,210 @@ __global__ void __launch_bounds__(192, 1)
   if (warp == 1) {
     tcgen05_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ CTA pairs
+// The same product with two CTAs (a cluster of two SMs) on one 256 x 256 tile: tcgen05.mma.cta_group::2 multiplies the
+// pair's 256 rows of a by 256 rows of w, of which each CTA stages its own 128 rows of a and 128 rows of w, so a CTA
+// fills half as much shared memory per product as in the single-CTA kernel and six stages fit. The even CTA of the pair
+// issues every product. Both CTAs' TMA loads count their bytes on the even CTA's barrier (the cta_group::2 form of the
+// load allows a barrier in the peer), and the even CTA's tcgen05.commit releases the stage in both CTAs (a multicast
+// arrive). Each CTA's epilogue reads its own 128 lanes of tensor memory and tells the even CTA when the
+// accumulator is free again. No TMA load is multicast. Waits are bounded as above; the pair meets on the cluster barrier
+// before tensor memory is freed.
+constexpr int STAGES2 = 6;
+constexpr uint32_t kStage2ABytes = 128 * BK * 2;
+constexpr uint32_t kStage2BBytes = 128 * BK * 2;
+constexpr uint32_t kStage2Bytes = kStage2ABytes + kStage2BBytes;
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t mapa_shared(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];\n" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ void tcgen05_commit_pair(uint32_t bar) {
+  const uint16_t mask = 3;  // the barrier at this offset in both CTAs of the pair
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;\n" ::"r"(bar), "h"(mask)
+               : "memory");
+}
+__device__ __forceinline__ void tcgen05_mma_f16_pair(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_d), "l"(a_desc),
+      "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+template <typename TOut, int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
+    gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, TOut* __restrict__ out,
+                             int M, int N, int K, int64_t ldo) {
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t smem_base = ((uint32_t)__cvta_generic_to_shared(smem_raw) + 1023u) & ~1023u;
+  // full, empty, peer_full per stage; acc_full, acc_empty per accumulator
+  __shared__ __align__(8) uint64_t bars[3 * STAGES2 + 4];
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+  const uint32_t bar0 = (uint32_t)__cvta_generic_to_shared(bars);
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES2 + s); };
+  auto peer_full_bar = [&](int s) { return bar0 + 8u * (2 * STAGES2 + s); };
+  auto acc_full_bar = [&](int a) { return bar0 + 8u * (3 * STAGES2 + a); };
+  auto acc_empty_bar = [&](int a) { return bar0 + 8u * (3 * STAGES2 + 2 + a); };
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < STAGES2; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+      mbar_init(peer_full_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(acc_full_bar(a), 1);
+      mbar_init(acc_empty_bar(a), 8);  // four epilogue warps in each CTA of the pair
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"((uint32_t)__cvta_generic_to_shared(&tmem_base_slot)),
+                 "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;\n" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // both CTAs' barriers exist before anyone arrives on the other's
+  tcgen05_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+  volatile int* abortp = &abort_flag;
+
+  const int m_tiles = (M + 255) / 256, n_tiles = (N + BN - 1) / BN;
+  const int k_blocks = (K + BK - 1) / BK;
+  const int tiles = m_tiles * n_tiles;
+  const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t leader_full[STAGES2];
+#pragma unroll
+      for (int s2 = 0; s2 < STAGES2; ++s2) leader_full[s2] = mapa_shared(full_bar(s2), 0);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = pair; t < tiles && ok; t += pairs) {
+        const int m0 = (t % m_tiles) * 256 + (int)rank * 128, n0 = (t / m_tiles) * BN + (int)rank * 128;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!(ok = mbar_wait(empty_bar(stage), phase ^ 1u, abortp, 1))) break;
+          const uint32_t sa = smem_base + stage * kStage2Bytes;
+          // both CTAs' loads count on the even CTA's barrier, which expects the bytes of both
+          if (leader) mbar_expect_tx(full_bar(stage), 2 * kStage2Bytes);
+          const uint32_t bar = leader_full[stage];
+          tma_load_2d_pair(sa, &tma_a, bar, kb * BK, m0);
+          tma_load_2d_pair(sa + kStage2ABytes, &tma_b, bar, kb * BK, n0);
+          if (++stage == STAGES2) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && leader) {
+      constexpr uint32_t idesc = umma_idesc_bf16(256, BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int it = 0;
+      for (int t = pair; t < tiles && ok; t += pairs, ++it) {
+        const int acc = it & 1;
+        const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
+        if (!(ok = mbar_wait<true>(acc_empty_bar(acc), acc_phase ^ 1u, abortp, 2))) break;
+        tcgen05_fence_after();
+        const uint32_t tmem_d = tmem_base + (uint32_t)acc * BN;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!(ok = mbar_wait<true>(full_bar(stage), phase, abortp, 3))) break;
+          tcgen05_fence_after();
+          const uint32_t sa = smem_base + stage * kStage2Bytes;
+          const uint64_t a_desc = umma_desc_k_major_sw128(sa);
+          const uint64_t b_desc = umma_desc_k_major_sw128(sa + kStage2ABytes);
+#pragma unroll
+          for (int k = 0; k < BK / kUmmaK; ++k) {
+            tcgen05_mma_f16_pair(tmem_d, a_desc + (uint64_t)(2 * k), b_desc + (uint64_t)(2 * k), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          tcgen05_commit_pair(empty_bar(stage));  // frees the stage in both CTAs once these products have read it
+          if (++stage == STAGES2) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (ok) tcgen05_commit_pair(acc_full_bar(acc));
+      }
+    }
+  } else {
+    const int lane_group = warp & 3;
+    const bool vec_ok = (ldo * (int64_t)sizeof(TOut)) % 16 == 0 && ((uintptr_t)out % 16) == 0;
+    const uint32_t leader_acc_empty[2] = {mapa_shared(acc_empty_bar(0), 0), mapa_shared(acc_empty_bar(1), 0)};
+    bool ok = true;
+    int it = 0;
+    for (int t = pair; t < tiles && ok; t += pairs, ++it) {
+      const int acc = it & 1;
+      const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
+      const int m0 = (t % m_tiles) * 256 + (int)rank * 128, n0 = (t / m_tiles) * BN;
+      if (!(ok = mbar_wait(acc_full_bar(acc), acc_phase, abortp, 4))) break;
+      tcgen05_fence_after();
+      const int row = m0 + lane_group * 32 + lane;
+      if (EPI == 0) {
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t v[32];
+          tcgen05_ld_32x32b_x32(tmem_base + ((uint32_t)(lane_group * 32) << 16) + (uint32_t)(acc * BN + c * 32), v);
+          const int col = n0 + c * 32;
+          if (row < M && col < N) store_row32<TOut>(out + (size_t)row * ldo + col, v, N - col, vec_ok);
+        }
+      } else {
+        const int n_out = N / 2;
+#pragma unroll 1
+        for (int c = 0; c < BN / 64; ++c) {
+          uint32_t g[32], u[32];
+          tcgen05_ld_32x32b_x32(tmem_base + ((uint32_t)(lane_group * 32) << 16) + (uint32_t)(acc * BN + c * 32), g);
+          tcgen05_ld_32x32b_x32(tmem_base + ((uint32_t)(lane_group * 32) << 16) + (uint32_t)(acc * BN + BN / 2 + c * 32), u);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) g[i] = __float_as_uint(silu_f(__uint_as_float(g[i])) * __uint_as_float(u[i]));
+          const int col = n0 / 2 + c * 32;
+          if (row < M && col < n_out) store_row32<TOut>(out + (size_t)row * ldo + col, g, n_out - col, vec_ok);
+        }
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(leader_acc_empty[acc]);
+    }
+  }
+
+  __syncwarp();
+  if (*abortp) {
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000LL) __nanosleep(256);
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // neither CTA frees shared or tensor memory the other may still be using
+  if (warp == 1) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
   }
 }
 
@@ -321,12 +561,12 @@ static int make_map(CUtensorMap* map, const void* base, int rows, int k, int64_t
   return ROOST_OK;
 }
 
-template <typename TOut>
+template <typename TOut, int EPI>
 static int launch_tcgen05(const CUtensorMap& ma, const CUtensorMap& mb, void* out, int m, int n, int k, int64_t ldo, cudaStream_t s) {
   static int sms = 0;
   static bool attr_set = false;
   const size_t smem = (size_t)STAGES * kStageBytes + 1024;
-  auto kernel = gemm_tcgen05_kernel<TOut>;
+  auto kernel = gemm_tcgen05_kernel<TOut, EPI>;
   if (!attr_set) {
     int dev = 0;
     cudaGetDevice(&dev);
@@ -340,9 +580,34 @@ static int launch_tcgen05(const CUtensorMap& ma, const CUtensorMap& mb, void* ou
   return check_launch("gemm_tcgen05");
 }
 
+template <typename TOut, int EPI>
+static int launch_tcgen05_pair(const CUtensorMap& ma, const CUtensorMap& mb, void* out, int m, int n, int k, int64_t ldo, cudaStream_t s) {
+  static int sms = 0;
+  static bool attr_set = false;
+  const size_t smem = (size_t)STAGES2 * kStage2Bytes + 1024;
+  auto kernel = gemm_tcgen05_pair_kernel<TOut, EPI>;
+  if (!attr_set) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    attr_set = true;
+  }
+  const int tiles = ((m + 255) / 256) * ((n + BN - 1) / BN);
+  int pairs = sms / 2;
+  if (tiles < pairs) pairs = tiles;
+  kernel<<<2 * pairs, 192, smem, s>>>(ma, mb, (TOut*)out, m, n, k, ldo);
+  return check_launch("gemm_tcgen05_pair");
+}
+
+static bool g_use_pairs = true;
+
 }  // namespace roost
 
 using namespace roost;
+
+// 1: products run on pairs of CTAs (256 x 256 tiles, tcgen05 cta_group::2); 0: one CTA a tile (128 x 256).
+extern "C" void roost_gemm_tcgen05_set_pairs(int on) { g_use_pairs = on != 0; }
 
 extern "C" int roost_gemm_tcgen05_supported(int m, int n, int k, int64_t lda, int64_t ldw) {
   return m >= 1 && n >= 1 && k >= 8 && k % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0;
@@ -372,8 +637,30 @@ extern "C" int roost_gemm_tcgen05(const void* a, const void* w, void* out, int m
   CUtensorMap ma, mb;
   int rc = make_map(&ma, a, m, k, lda, BM);
   if (rc != ROOST_OK) return rc;
-  rc = make_map(&mb, w, n, k, ldw, BN);
+  rc = make_map(&mb, w, n, k, ldw, g_use_pairs ? 128 : BN);
   if (rc != ROOST_OK) return rc;
-  if (out_dtype == ROOST_BF16) return launch_tcgen05<__nv_bfloat16>(ma, mb, out, m, n, k, ldo, (cudaStream_t)stream);
-  return launch_tcgen05<float>(ma, mb, out, m, n, k, ldo, (cudaStream_t)stream);
+  if (g_use_pairs) {
+    if (out_dtype == ROOST_BF16) return launch_tcgen05_pair<__nv_bfloat16, 0>(ma, mb, out, m, n, k, ldo, (cudaStream_t)stream);
+    return launch_tcgen05_pair<float, 0>(ma, mb, out, m, n, k, ldo, (cudaStream_t)stream);
+  }
+  if (out_dtype == ROOST_BF16) return launch_tcgen05<__nv_bfloat16, 0>(ma, mb, out, m, n, k, ldo, (cudaStream_t)stream);
+  return launch_tcgen05<float, 0>(ma, mb, out, m, n, k, ldo, (cudaStream_t)stream);
+}
+
+// a [m, k] times the gate/up weight w [n, k] (n = 2 * inter, rows interleaved in blocks of 128 gate rows then their 128 up
+// rows), SiLU(gate) * up applied to the accumulator: out [m, n / 2] bfloat16. The [m, n] product never reaches memory.
+extern "C" int roost_gemm_tcgen05_swiglu(const void* a, const void* w, void* out, int m, int n, int k, int64_t lda, int64_t ldw,
+                                         int64_t ldo, roost_stream_t stream) {
+  ROOST_REQUIRE(lda >= k && ldw >= k && ldo >= n / 2, "gemm_tcgen05_swiglu: a leading dimension is smaller than its row");
+  if (!roost_gemm_tcgen05_supported(m, n, k, lda, ldw) || n % 256 != 0) {
+    return fail(ROOST_ERR_UNSUPPORTED, "gemm_tcgen05_swiglu: n must be a multiple of 256 (gate and up rows interleaved in blocks of 128), k and the strides multiples of 8");
+  }
+  ROOST_REQUIRE(((uintptr_t)a % 16 == 0) && ((uintptr_t)w % 16 == 0), "gemm_tcgen05_swiglu: a and w must start on 16-byte boundaries");
+  CUtensorMap ma, mb;
+  int rc = make_map(&ma, a, m, k, lda, BM);
+  if (rc != ROOST_OK) return rc;
+  rc = make_map(&mb, w, n, k, ldw, g_use_pairs ? 128 : BN);
+  if (rc != ROOST_OK) return rc;
+  if (g_use_pairs) return launch_tcgen05_pair<__nv_bfloat16, 1>(ma, mb, out, m, n, k, ldo, (cudaStream_t)stream);
+  return launch_tcgen05<__nv_bfloat16, 1>(ma, mb, out, m, n, k, ldo, (cudaStream_t)stream);
 }

@@ -17,7 +17,7 @@
 extern "C" {
 #endif
 
-#define ROOST_ABI_VERSION 1
+#define ROOST_ABI_VERSION 2
 
 #define ROOST_OK 0
 #define ROOST_ERR_INVALID 1      /* an argument is out of range or inconsistent; nothing was launched */
@@ -46,8 +46,9 @@ int roost_rms_norm(const void* x, const void* w, void* out, const int32_t* rows,
 int roost_add_rms_norm(const void* x, void* residual, const void* w, void* out, const int32_t* rows, int n_out,
                        int hidden, float eps, int dtype, int wdtype, roost_stream_t stream);
 
-/* out[t,i] = silu(x[t,i]) * x[t,inter+i], x: [tokens, 2*inter]. */
-int roost_silu_mul(const void* x, void* out, int tokens, int inter, int dtype, roost_stream_t stream);
+/* out[t,i] = silu(gate_i) * up_i, x: [tokens, 2*inter]. block 0: a row of x is [gate | up]; block b > 0: blocks of b gate
+ * values followed by their b up values (the layout the fused product below wants its weight rows in). */
+int roost_silu_mul(const void* x, void* out, int tokens, int inter, int block, int dtype, roost_stream_t stream);
 
 /* Per token and head: optional RMS norm over head_dim (q heads with q_w, k heads with k_w), NeoX rotation of
  * the first rotary_dim elements by angle position * inv_freq[i] (inv_freq: double[rotary_dim/2]; rotary_dim 0
@@ -126,6 +127,12 @@ int roost_gemm_tcgen05_supported(int m, int n, int k, int64_t lda, int64_t ldw);
 int roost_gemm_tcgen05(const void* a, const void* w, void* out, int m, int n, int k, int64_t lda, int64_t ldw, int64_t ldo,
                        int out_dtype, roost_stream_t stream);
 int roost_gemm_tcgen05_status(void);
+/* 1 (default): tiles of 256 x 256 on pairs of CTAs (tcgen05 cta_group::2); 0: tiles of 128 x 256 on single CTAs. */
+void roost_gemm_tcgen05_set_pairs(int on);
+/* The gate/up product with SiLU(gate) * up applied to the accumulator: w [n = 2 * inter, k] with rows in blocks of 128
+ * gate rows followed by their 128 up rows; out [m, n / 2] bfloat16. n must be a multiple of 256. */
+int roost_gemm_tcgen05_swiglu(const void* a, const void* w, void* out, int m, int n, int k, int64_t lda, int64_t ldw,
+                              int64_t ldo, roost_stream_t stream);
 
 /* ids[r] = index of the largest logit of row r, ties to the lowest index, NaN never chosen (-1 if none). */
 int roost_argmax(const float* logits, int64_t stride, int rows, int vocab, int32_t* ids, roost_stream_t stream);

@@ -13,7 +13,7 @@ import torch
 
 from . import build
 
-ABI_VERSION = 1
+ABI_VERSION = 2
 F32, BF16 = 0, 1
 
 
@@ -50,7 +50,8 @@ _SIGNATURES = {
     "roost_embedding": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "roost_rms_norm": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_int, c_void_p],
     "roost_add_rms_norm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_int, c_void_p],
-    "roost_silu_mul": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "roost_silu_mul": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "roost_gemm_tcgen05_swiglu": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_void_p],
     "roost_qk_norm_rope_cache": [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                  c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int64, c_int, c_int, c_int,
                                  c_void_p],
@@ -128,11 +129,23 @@ class KernelLibrary:
                    dtype_code(x.dtype), dtype_code(w.dtype), _stream())
         return out
 
-    def silu_mul(self, x: torch.Tensor) -> torch.Tensor:
+    def silu_mul(self, x: torch.Tensor, block: int = 0) -> torch.Tensor:
+        """silu(gate) * up over rows [gate | up] (block 0) or rows of blocks of ``block`` gate then ``block`` up values."""
         _need(x, "x")
         T, two_i = x.shape
         out = torch.empty((T, two_i // 2), dtype=x.dtype, device=x.device)
-        self._call("roost_silu_mul", _ptr(x), _ptr(out), T, two_i // 2, dtype_code(x.dtype), _stream())
+        self._call("roost_silu_mul", _ptr(x), _ptr(out), T, two_i // 2, block, dtype_code(x.dtype), _stream())
+        return out
+
+    def gemm_tcgen05_swiglu(self, a: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+        """silu(a Wg^T) * (a Wu^T) in one kernel; w holds gate and up rows interleaved in blocks of 128."""
+        _need(a, "a", torch.bfloat16); _need(w, "w", torch.bfloat16)
+        M, K = a.shape
+        N, K2 = w.shape
+        if K != K2:
+            raise KernelError(f"gemm_tcgen05_swiglu: a has {K} columns, w has {K2}")
+        out = torch.empty((M, N // 2), dtype=torch.bfloat16, device=a.device)
+        self._call("roost_gemm_tcgen05_swiglu", _ptr(a), _ptr(w), _ptr(out), M, N, K, a.stride(0), w.stride(0), out.stride(0), _stream())
         return out
 
     def qk_norm_rope_cache(self, qkv, q_heads, kv_heads, head_dim, *, q_w, k_w, eps, inv_freq, rotary_dim, positions,
@@ -248,6 +261,10 @@ class KernelLibrary:
         self._call("roost_gemm_tcgen05", _ptr(a), _ptr(w), _ptr(out), M, N, K, a.stride(0), w.stride(0), out.stride(0),
                    dtype_code(out_dtype), _stream())
         return out
+
+    def gemm_tcgen05_set_pairs(self, on: bool) -> None:
+        """Tiles on pairs of CTAs (cta_group::2, the default) or on single CTAs."""
+        self._lib.roost_gemm_tcgen05_set_pairs(1 if on else 0)
 
     def gemm_tcgen05_status(self) -> int:
         """The code of a bounded wait the tcgen05 product gave up since the last call (0: none); synchronises."""

@@ -18,6 +18,14 @@ class GatedMlp(FeedForward):
         self.rt = runtime
         self.gate_up = Linear(runtime, 2 * spec.intermediate, spec.hidden)
         self.down = Linear(runtime, spec.hidden, spec.intermediate)
+        # In bfloat16 with an intermediate size that is a multiple of 128 the gate and up rows are stored interleaved in
+        # blocks of 128, the layout in which the tensor-core product applies SiLU(gate) * up to its accumulator, so that
+        # for many rows of x the [T, 2I] product never goes to memory; few rows keep the library product and the
+        # SiLU kernel, which reads the same layout.
+        k = runtime.kernels
+        self.interleave = 128 if (not runtime.full_precision and spec.intermediate % 128 == 0 and spec.hidden % 8 == 0
+                                  and hasattr(k, "gemm_tcgen05_swiglu")) else 0
+        self.fused_min_rows = 256   # below this the 128-row tiles are mostly empty and the library product is faster
 
     @classmethod
     def parameters(cls, spec: GatedMlpSpec):
@@ -25,11 +33,18 @@ class GatedMlp(FeedForward):
         return {"gate_up": ParamDecl(shape=(2 * I, H), row_splits=(I, I)), "down": ParamDecl(shape=(H, I))}
 
     def load(self, params):
-        self.gate_up.load(params["gate_up"])
+        w = params["gate_up"]
+        if self.interleave:
+            I, H, b = self.spec.intermediate, self.spec.hidden, self.interleave
+            w = w.reshape(2, I // b, b, H).permute(1, 0, 2, 3).reshape(2 * I, H)   # [gate; up] -> blocks of (gate, up)
+        self.gate_up.load(w)
         self.down.load(params["down"])
 
     def __call__(self, x, batch=None):
-        return self.down(self.rt.kernels.silu_mul(self.gate_up(x)))
+        k = self.rt.kernels
+        if self.interleave and x.shape[0] >= self.fused_min_rows and x.is_contiguous():
+            return self.down(k.gemm_tcgen05_swiglu(x, self.gate_up.weight))
+        return self.down(k.silu_mul(self.gate_up(x), self.interleave))
 
 
 register_feed_forward("gated_mlp", GatedMlp)

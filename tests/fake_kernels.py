@@ -31,8 +31,10 @@ class FakeKernels:
             residual.copy_(s)
         return self.rms_norm(s, w, eps, rows)
 
-    def silu_mul(self, x):
+    def silu_mul(self, x, block=0):
         i = x.shape[1] // 2
+        if block:
+            x = x.reshape(x.shape[0], i // block, 2, block).permute(0, 2, 1, 3).reshape(x.shape[0], 2 * i)
         g, u = x[:, :i].float(), x[:, i:].float()
         return (g / (1 + torch.exp(-g)) * u).to(x.dtype)
 

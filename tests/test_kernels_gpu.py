@@ -376,3 +376,39 @@ def test_gemm_skinny(kernels, m, n, k, out_dtype):
     assert torch.equal(kernels.gemm_skinny(a[r : r + 1].contiguous(), w, out_dtype), got[r : r + 1])
     assert not kernels.gemm_skinny_supported(33, n, k, k, k) and not kernels.gemm_skinny_supported(m, n + 1, k, k, k)
     assert not kernels.gemm_skinny_supported(m, n, k + 8, k + 8, k + 8) and not kernels.gemm_skinny_supported(m, n, 128, 128, 128)
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (300, 272, 96), (1, 256, 64), (77, 18992, 1024), (2048, 6144, 4096), (513, 512, 12288)])
+def test_gemm_tcgen05(kernels, m, n, k):
+    """TMA + tcgen05 product: tiles that end inside m, n and k (zero-filled by the TMA unit), one row, many tiles a CTA."""
+    a = rand((m, k), torch.bfloat16, 41)
+    w = rand((n, k), torch.bfloat16, 42)
+    want = a.double().cpu() @ w.double().cpu().T
+    got = kernels.gemm_tcgen05(a, w)
+    assert kernels.gemm_tcgen05_status() == 0, "a bounded wait inside the kernel was given up"
+    close(got, want, torch.bfloat16, "gemm_tcgen05", scale=math.sqrt(k) / 8)
+    got32 = kernels.gemm_tcgen05(a, w, torch.float32)
+    assert kernels.gemm_tcgen05_status() == 0
+    # the tensor cores add products with less than full 32-bit rounding: the same bound as the library product shows
+    lib = torch.mm(a, w.t(), out_dtype=torch.float32) if hasattr(torch, "mm") else None
+    err = float(((got32.double().cpu() - want).abs() / (1 + want.abs())).max())
+    err_lib = float(((lib.double().cpu() - want).abs() / (1 + want.abs())).max())
+    print(f"MEASURED gemm_tcgen05 f32 out: {err:.3e} (cuBLAS {err_lib:.3e})")
+    assert err < max(2 * err_lib, k * 2.0 ** -23)
+    assert not kernels.gemm_tcgen05_supported(m, n, k + 4, k + 4, k + 4)
+
+
+@pytest.mark.parametrize("m,inter,k", [(64, 128, 64), (200, 384, 96), (2048, 12288, 4096)])
+def test_gemm_tcgen05_swiglu(kernels, m, inter, k):
+    a = rand((m, k), torch.bfloat16, 43)
+    gate = rand((inter, k), torch.bfloat16, 44, 1 / math.sqrt(k))
+    up = rand((inter, k), torch.bfloat16, 45, 1 / math.sqrt(k))
+    w = torch.stack([gate.reshape(inter // 128, 128, k), up.reshape(inter // 128, 128, k)], dim=1).reshape(2 * inter, k).contiguous()
+    got = kernels.gemm_tcgen05_swiglu(a, w)
+    assert kernels.gemm_tcgen05_status() == 0
+    ad = a.double().cpu()
+    want = plain.silu_and_mul(ad @ gate.double().cpu().T, ad @ up.double().cpu().T)
+    close(got, want, torch.bfloat16, "gemm_tcgen05_swiglu")
+    # the unfused pair on the same interleaved layout
+    two = kernels.silu_mul(torch.matmul(a, w.t()), 128)
+    close(two, want, torch.bfloat16, "library product + silu_mul on the interleaved layout", scale=2)
