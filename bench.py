@@ -14,6 +14,7 @@ work of a decode step); the e2e run prefills its contexts for real through the e
 from __future__ import annotations
 
 import argparse
+import gc
 import json
 import os
 import statistics
@@ -157,9 +158,9 @@ def timed_decode(model, batch: int, context: int, steps: int, warmup: int):
         torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / steps
     launches = k.launches - launches0
-    for r in rids:
-        ex.finish(r)
+    ex.close()
     del ex
+    gc.collect()
     torch.cuda.empty_cache()
     return batch / (ms / 1e3), ms, launches, clocks.summary()
 
@@ -182,7 +183,9 @@ def timed_prefill(model, tokens_n: int, warmup: int = 3, iters: int = 3):
         ex.finish("p")
         if i >= warmup:
             times.append(e0.elapsed_time(e1))
+    ex.close()
     del ex
+    gc.collect()
     torch.cuda.empty_cache()
     return min(times)
 
@@ -221,7 +224,9 @@ def timed_e2e(model, batch: int, context: int, steps: int, warmup: int):
         d2h += 4 * len(events)
     torch.cuda.synchronize()
     dt = time.perf_counter() - t0
+    engine.executor.close()
     del engine
+    gc.collect()
     torch.cuda.empty_cache()
     return produced / dt, h2d // steps, d2h // steps
 

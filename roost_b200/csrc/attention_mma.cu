@@ -234,6 +234,8 @@ __global__ void __launch_bounds__(128) attention_prefill_kernel(const __nv_bfloa
   const uint32_t v_smem[2] = {k_smem[0] + kTileBytes, k_smem[1] + kTileBytes};
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  pdl_launch_dependents();
+  pdl_wait();
   const int2 w = work[blockIdx.x];
   const int b = w.x, row0 = w.y;
   if (b < 0) return;  // padding of a fixed-size work list
@@ -323,6 +325,8 @@ __global__ void __launch_bounds__(NWARPS * 32)
   const uint32_t q_smem = smem;
   const uint32_t wbase = smem + kQBytes + warp * kWarpBytes;
 
+  pdl_launch_dependents();
+  pdl_wait();
   const int4 w = work[blockIdx.x];
   const int b = w.x, kv_begin = w.y, kv_end = w.z, slot = w.w;
   if (b < 0) return;  // padding of a fixed-size work list
@@ -445,6 +449,8 @@ template <int D>
 __global__ void attention_merge_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                        const int32_t* __restrict__ q_indptr, const int4* __restrict__ merge_work, int q_heads,
                                        int kv_heads) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int4 w = merge_work[blockIdx.x];
   const int b = w.x, slot0 = w.y, chunks = w.z;
   if (b < 0) return;  // padding of a fixed-size work list
@@ -492,9 +498,9 @@ static int launch_prefill(const void* q, void* out, const void* k_pool, const vo
     cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     attr_set = true;
   }
-  kernel<<<dim3(items, kv_heads), 128, smem, s>>>((const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const __nv_bfloat16*)k_pool,
-                                                  (const __nv_bfloat16*)v_pool, q_indptr, kv_lens, kv_indptr, kv_indices, (const int2*)work,
-                                                  q_heads, kv_heads, page_size, page_shift_of(page_size), scale * kLog2e, window);
+  launch_kernel(kernel, dim3(items, kv_heads), dim3(128), smem, s, (const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const __nv_bfloat16*)k_pool,
+                (const __nv_bfloat16*)v_pool, q_indptr, kv_lens, kv_indptr, kv_indices, (const int2*)work, q_heads, kv_heads, page_size,
+                page_shift_of(page_size), scale * kLog2e, window);
   return check_launch("attention_prefill");
 }
 
@@ -511,14 +517,13 @@ static int launch_decode(const void* q, void* out, const void* k_pool, const voi
     cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     attr_set = true;
   }
-  kernel<<<dim3(items, kv_heads), NW * 32, smem, s>>>((const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const __nv_bfloat16*)k_pool,
-                                                      (const __nv_bfloat16*)v_pool, q_indptr, kv_lens, kv_indptr, kv_indices,
-                                                      (const int4*)work, part_o, part_ml, q_heads, kv_heads, page_size, page_shift_of(page_size),
-                                                      scale * kLog2e, window);
+  launch_kernel(kernel, dim3(items, kv_heads), dim3(NW * 32), smem, s, (const __nv_bfloat16*)q, (__nv_bfloat16*)out,
+                (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, q_indptr, kv_lens, kv_indptr, kv_indices, (const int4*)work, part_o,
+                part_ml, q_heads, kv_heads, page_size, page_shift_of(page_size), scale * kLog2e, window);
   int rc = check_launch("attention_decode");
   if (rc != ROOST_OK || merge_items == 0) return rc;
-  attention_merge_kernel<D><<<dim3(merge_items, kv_heads, 16), D < 128 ? D : 128, 0, s>>>((__nv_bfloat16*)out, part_o, part_ml, q_indptr,
-                                                                        (const int4*)merge_work, q_heads, kv_heads);
+  launch_kernel(attention_merge_kernel<D>, dim3(merge_items, kv_heads, 16), dim3(D < 128 ? D : 128), 0, s, (__nv_bfloat16*)out,
+                (const float*)part_o, (const float*)part_ml, q_indptr, (const int4*)merge_work, q_heads, kv_heads);
   return check_launch("attention_merge");
 }
 

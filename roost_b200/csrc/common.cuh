@@ -13,6 +13,31 @@ namespace roost {
 
 void set_error(const std::string& msg);
 
+// Programmatic dependent launch. A kernel launched through launch_kernel() with the switch on may begin while the kernel
+// before it on the stream is still running: what it does before pdl_wait() (index arithmetic, barrier set-up, loads of
+// weights, which no kernel writes) overlaps that kernel's tail; pdl_wait() returns once the earlier kernel has finished
+// and its writes are visible. pdl_launch_dependents() lets the next kernel start its own preamble. Both are no-ops for a
+// kernel launched without the attribute. The switch is process-wide (roost_set_pdl).
+extern bool g_pdl_enabled;
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = g_pdl_enabled ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+
 inline int fail(int code, const std::string& msg) {
   set_error(msg);
   return code;

@@ -10,11 +10,14 @@ namespace roost {
 
 static thread_local std::string g_last_error;
 void set_error(const std::string& msg) { g_last_error = msg; }
+bool g_pdl_enabled = false;
 
 // ---------------------------------------------------------------------------------------------- embedding
 template <typename T>
 __global__ void embedding_kernel(const T* __restrict__ table, const int32_t* __restrict__ ids, T* __restrict__ out,
                                  int hidden, int vocab) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   const int id = ids[t];
   const bool ok = id >= 0 && id < vocab;
@@ -31,6 +34,8 @@ __global__ void rms_norm_kernel(const T* __restrict__ x, T* residual, const void
                                 const int32_t* __restrict__ rows, int hidden, float eps, int wdtype) {
   extern __shared__ float row[];  // hidden floats, then 32 floats of reduction scratch
   float* scratch = row + hidden;
+  pdl_launch_dependents();
+  pdl_wait();
   const int i_out = blockIdx.x;
   const size_t r = rows ? (size_t)rows[i_out] : (size_t)i_out;
   const T* xr = x + r * hidden;
@@ -56,6 +61,8 @@ template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ x, T* __restrict__ out, int inter, int block) {
   const size_t t = blockIdx.x;
   const int i = blockIdx.y * blockDim.x + threadIdx.x;
+  pdl_launch_dependents();
+  pdl_wait();
   if (i >= inter) return;
   const size_t g_at = block ? (size_t)(i / block) * 2 * block + i % block : (size_t)i;
   const size_t u_at = block ? g_at + block : (size_t)inter + i;
@@ -111,6 +118,8 @@ __global__ void rms_norm_vec_kernel(const T* __restrict__ x, T* residual, const 
                                     const int32_t* __restrict__ rows, int hidden, float eps, int wdtype) {
   constexpr int N = Vec<T>::N;
   __shared__ float scratch[32];
+  pdl_launch_dependents();
+  pdl_wait();
   const int i_out = blockIdx.x;
   const size_t r = rows ? (size_t)rows[i_out] : (size_t)i_out;
   const int nvec = hidden / N;
@@ -152,6 +161,8 @@ __global__ void silu_mul_vec_kernel(const T* __restrict__ x, T* __restrict__ out
   constexpr int N = Vec<T>::N;
   const size_t t = blockIdx.x;
   const int vi = blockIdx.y * blockDim.x + threadIdx.x;
+  pdl_launch_dependents();
+  pdl_wait();
   if (vi * N >= inter) return;
   float g[N], u[N], o[N];
   const int j = vi * N;
@@ -169,6 +180,7 @@ __global__ void silu_mul_vec_kernel(const T* __restrict__ x, T* __restrict__ out
 using namespace roost;
 
 extern "C" int roost_abi_version(void) { return ROOST_ABI_VERSION; }
+extern "C" void roost_set_pdl(int on) { g_pdl_enabled = on != 0; }
 extern "C" const char* roost_last_error(void) { return g_last_error.c_str(); }
 
 extern "C" int roost_embedding(const void* table, const int32_t* ids, void* out, int tokens, int hidden, int vocab,
@@ -176,7 +188,7 @@ extern "C" int roost_embedding(const void* table, const int32_t* ids, void* out,
   ROOST_REQUIRE(tokens >= 0 && hidden > 0 && vocab > 0, "embedding: tokens, hidden and vocab must be positive");
   if (tokens == 0) return ROOST_OK;
   ROOST_DISPATCH_DTYPE(dtype, T,
-                       embedding_kernel<T><<<tokens, 256, 0, (cudaStream_t)stream>>>((const T*)table, ids, (T*)out, hidden, vocab));
+                       launch_kernel(embedding_kernel<T>, dim3(tokens), dim3(256), 0, (cudaStream_t)stream, (const T*)table, ids, (T*)out, hidden, vocab));
   return check_launch("embedding");
 }
 
@@ -197,8 +209,8 @@ static int launch_norm(const void* x, void* residual, const void* w, void* out, 
       if (threads > 512) threads = 512;
       if (nvec <= threads * kMaxVec) {
         ROOST_DISPATCH_DTYPE(dtype, T,
-                             rms_norm_vec_kernel<T, ADD><<<n_out, threads, 0, (cudaStream_t)stream>>>(
-                                 (const T*)x, (T*)residual, w, (T*)out, rows, hidden, eps, wdtype));
+                             launch_kernel(rms_norm_vec_kernel<T, ADD>, dim3(n_out), dim3(threads), 0, (cudaStream_t)stream,
+                                           (const T*)x, (T*)residual, w, (T*)out, rows, hidden, eps, wdtype));
         return check_launch("rms_norm");
       }
     }
@@ -209,7 +221,8 @@ static int launch_norm(const void* x, void* residual, const void* w, void* out, 
   ROOST_DISPATCH_DTYPE(dtype, T, {
     auto kernel = rms_norm_kernel<T, ADD>;
     if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    kernel<<<n_out, threads, smem, (cudaStream_t)stream>>>((const T*)x, (T*)residual, w, (T*)out, rows, hidden, eps, wdtype);
+    launch_kernel(kernel, dim3(n_out), dim3(threads), smem, (cudaStream_t)stream, (const T*)x, (T*)residual, w, (T*)out, rows, hidden, eps,
+                  wdtype);
   });
   return check_launch("rms_norm");
 }
@@ -236,13 +249,13 @@ extern "C" int roost_silu_mul(const void* x, void* out, int tokens, int inter, i
       const int nvec = inter / vec;
       dim3 grid(tokens, (nvec + 127) / 128);
       if (grid.y <= 65535) {
-        ROOST_DISPATCH_DTYPE(dtype, T, silu_mul_vec_kernel<T><<<grid, 128, 0, (cudaStream_t)stream>>>((const T*)x, (T*)out, inter, block));
+        ROOST_DISPATCH_DTYPE(dtype, T, launch_kernel(silu_mul_vec_kernel<T>, grid, dim3(128), 0, (cudaStream_t)stream, (const T*)x, (T*)out, inter, block));
         return check_launch("silu_mul");
       }
     }
   }
   if ((inter + 255) / 256 > 65535) return fail(ROOST_ERR_UNSUPPORTED, "silu_mul: inter beyond 16776960");
   dim3 grid(tokens, (inter + 255) / 256);
-  ROOST_DISPATCH_DTYPE(dtype, T, silu_mul_kernel<T><<<grid, 256, 0, (cudaStream_t)stream>>>((const T*)x, (T*)out, inter, block));
+  ROOST_DISPATCH_DTYPE(dtype, T, launch_kernel(silu_mul_kernel<T>, grid, dim3(256), 0, (cudaStream_t)stream, (const T*)x, (T*)out, inter, block));
   return check_launch("silu_mul");
 }

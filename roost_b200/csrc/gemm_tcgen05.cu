@@ -528,6 +528,245 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
   }
 }
 
+// ------------------------------------------------------------------------------------------------ few rows: weight streaming
+// out[m,n] = sum_k x[m,k] * w[n,k] for at most 64 rows of x (decode steps). The work is reading w once at memory speed,
+// so the operands swap roles: 128 rows of w are the 128-row operand of tcgen05.mma, the rows of x (padded to 16, 32 or 64)
+// its columns, and the accumulator holds out transposed, [128 rows of w] x [rows of x]. One persistent CTA per SM; the
+// units of work are (128 rows of w) x (64 of k), 16 KB of w each, and CTA c takes the contiguous range of units
+// [c U / G, (c + 1) U / G): every SM streams the same number of bytes, whatever n and k are. A CTA's range covers parts
+// of one to three 128-row tiles. A part that is a whole tile is written straight to out. Otherwise the CTA that holds the
+// tile's first k-blocks (it reaches them at the END of its range) finishes the tile: the CTAs holding the later k-blocks
+// (which they compute at the START of theirs) leave their partial sums in a workspace slot and raise a flag; the finisher
+// waits for the flags (a bounded wait), adds the partial sums in CTA order, writes out and lowers the flags. The order of
+// every sum is fixed by the geometry alone, so results are the same on every run and for every batch.
+constexpr int STAGES_S = 8;
+constexpr uint32_t kStageSWBytes = 128 * BK * 2;
+constexpr uint32_t kStageSXBytes = 64 * BK * 2;
+constexpr uint32_t kStageSBytes = kStageSWBytes + kStageSXBytes;
+constexpr int kStreamMaxCtas = 256;
+
+__device__ __forceinline__ void tcgen05_ld_32x32b_x16(uint32_t taddr, uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]),
+        "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+}
+
+template <typename TOut>
+__global__ void __launch_bounds__(192, 1)
+    gemm_stream_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_constant__ CUtensorMap tma_x, TOut* __restrict__ out, int M,
+                       int N, int K, int64_t ldo, int ntok, float* ws, int* flags) {
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t smem_base = ((uint32_t)__cvta_generic_to_shared(smem_raw) + 1023u) & ~1023u;
+  __shared__ __align__(8) uint64_t bars[2 * STAGES_S + 4];
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+  const uint32_t bar0 = (uint32_t)__cvta_generic_to_shared(bars);
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES_S + s); };
+  auto acc_full_bar = [&](int a) { return bar0 + 8u * (2 * STAGES_S + a); };
+  auto acc_empty_bar = [&](int a) { return bar0 + 8u * (2 * STAGES_S + 2 + a); };
+  constexpr uint32_t kCols = 128;  // two accumulators of 64 columns
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_tiles = (N + 127) / 128;
+  const int kbs = (K + BK - 1) / BK;
+  const long long units = (long long)n_tiles * kbs;
+  const int G = gridDim.x, c = blockIdx.x;
+  const long long u0 = units * c / G, u1 = units * (c + 1) / G;
+  const int t_first = (int)(u0 / kbs), t_last = (int)((u1 - 1) / kbs);  // u1 > u0: the host launches at most `units` CTAs
+  int prologue = 0;  // units whose loads the producer issued before the CTA-wide barrier
+  if (threadIdx.x == 0) {
+    asm volatile("prefetch.tensormap [%0];\n" ::"l"(reinterpret_cast<uint64_t>(&tma_w)) : "memory");
+    asm volatile("prefetch.tensormap [%0];\n" ::"l"(reinterpret_cast<uint64_t>(&tma_x)) : "memory");
+    abort_flag = 0;
+    for (int s = 0; s < STAGES_S; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(acc_full_bar(a), 1);
+      mbar_init(acc_empty_bar(a), 4);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    // the first stages are free by construction: the loads of w start now (no kernel writes the weights), while tensor
+    // memory is still being allocated and, under programmatic dependent launch, while the kernel that produces x is still
+    // running; the loads of x follow once that kernel has finished
+    pdl_launch_dependents();
+    for (long long u = u0; u < u1 && prologue < STAGES_S; ++u, ++prologue) {
+      const int t = (int)(u / kbs), kb = (int)(u % kbs);
+      const uint32_t sw = smem_base + prologue * kStageSBytes;
+      mbar_expect_tx(full_bar(prologue), kStageSWBytes + (uint32_t)ntok * BK * 2);
+      tma_load_2d(sw, &tma_w, full_bar(prologue), kb * BK, t * 128);
+    }
+    pdl_wait();
+    for (int i = 0; i < prologue; ++i) {
+      const int kb = (int)((u0 + i) % kbs);
+      tma_load_2d(smem_base + i * kStageSBytes + kStageSWBytes, &tma_x, full_bar(i), kb * BK, 0);
+    }
+  } else {
+    pdl_wait();  // every thread that later reads what earlier kernels wrote (workspace, flags) has waited
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"((uint32_t)__cvta_generic_to_shared(&tmem_base_slot)),
+                 "r"(kCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+  volatile int* abortp = &abort_flag;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = prologue % STAGES_S;
+      uint32_t phase = prologue == STAGES_S ? 1u : 0u;
+      bool ok = true;
+      for (long long u = u0 + prologue; u < u1 && ok; ++u) {
+        const int t = (int)(u / kbs), kb = (int)(u % kbs);
+        if (!(ok = mbar_wait(empty_bar(stage), phase ^ 1u, abortp, 1))) break;
+        const uint32_t sw = smem_base + stage * kStageSBytes;
+        mbar_expect_tx(full_bar(stage), kStageSWBytes + (uint32_t)ntok * BK * 2);
+        tma_load_2d(sw, &tma_w, full_bar(stage), kb * BK, t * 128);
+        tma_load_2d(sw + kStageSWBytes, &tma_x, full_bar(stage), kb * BK, 0);
+        if (++stage == STAGES_S) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc_bf16(128, ntok);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int it = 0;
+      for (int t = t_first; t <= t_last && ok; ++t, ++it) {
+        const long long s0 = max(u0, (long long)t * kbs), s1 = min(u1, (long long)(t + 1) * kbs);
+        const int acc = it & 1;
+        const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
+        if (!(ok = mbar_wait(acc_empty_bar(acc), acc_phase ^ 1u, abortp, 2))) break;
+        tcgen05_fence_after();
+        const uint32_t tmem_d = tmem_base + (uint32_t)acc * 64;
+        for (long long u = s0; u < s1; ++u) {
+          if (!(ok = mbar_wait(full_bar(stage), phase, abortp, 3))) break;
+          tcgen05_fence_after();
+          const uint32_t sw = smem_base + stage * kStageSBytes;
+          const uint64_t a_desc = umma_desc_k_major_sw128(sw);
+          const uint64_t b_desc = umma_desc_k_major_sw128(sw + kStageSWBytes);
+#pragma unroll
+          for (int k = 0; k < BK / kUmmaK; ++k) {
+            tcgen05_mma_f16(tmem_d, a_desc + (uint64_t)(2 * k), b_desc + (uint64_t)(2 * k), idesc, (u > s0 || k > 0) ? 1u : 0u);
+          }
+          tcgen05_commit(empty_bar(stage));
+          if (++stage == STAGES_S) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (ok) tcgen05_commit(acc_full_bar(acc));
+      }
+    }
+  } else {
+    const int lane_group = warp & 3;
+    const int etid = (warp - 2) * 32 + lane;  // 0..127 among the epilogue threads
+    bool ok = true;
+    int it = 0;
+    for (int t = t_first; t <= t_last && ok; ++t, ++it) {
+      const long long s0 = max(u0, (long long)t * kbs), s1 = min(u1, (long long)(t + 1) * kbs);
+      const int k0 = (int)(s0 - (long long)t * kbs), k1 = (int)(s1 - (long long)t * kbs);
+      const int acc = it & 1;
+      const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
+      if (!(ok = mbar_wait(acc_full_bar(acc), acc_phase, abortp, 4))) break;
+      tcgen05_fence_after();
+      const int r = lane_group * 32 + lane;  // row of w within the tile = lane of tensor memory
+      const int n = t * 128 + r;
+      const uint32_t taddr = tmem_base + ((uint32_t)(lane_group * 32) << 16) + (uint32_t)(acc * 64);
+      if (k0 > 0) {
+        // a later part of the tile: leave the partial sums for the CTA that holds the tile's first k-blocks
+        for (int cb = 0; cb < ntok; cb += 16) {
+          uint32_t v[16];
+          tcgen05_ld_32x32b_x16(taddr + cb, v);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) ws[((size_t)c * 64 + cb + i) * 128 + r] = __uint_as_float(v[i]);
+        }
+        __threadfence();
+        asm volatile("bar.sync 1, 128;\n" ::: "memory");  // the four epilogue warps
+        if (etid == 0) {
+          __threadfence();
+          atomicExch(&flags[c], 1);
+        }
+      } else {
+        // the tile's first part: a whole tile, or the finisher of a tile that continues in the next CTAs
+        int contributors = 0;
+        if (k1 < kbs) {
+          long long covered = s1;
+          while (covered < (long long)(t + 1) * kbs && c + 1 + contributors < G) {
+            ++contributors;
+            covered = units * (c + 1 + contributors) / G;
+          }
+          if (etid < contributors) {
+            const long long w0 = clock64();
+            while (atomicAdd(&flags[c + 1 + etid], 0) == 0) {
+              if (*abortp || clock64() - w0 > kWaitCycles) {
+                *abortp = 1;
+                atomicCAS(&g_gemm_tcgen05_error, 0, 7);
+                break;
+              }
+            }
+            __threadfence();
+          }
+          asm volatile("bar.sync 1, 128;\n" ::: "memory");
+        }
+        for (int cb = 0; cb < ntok; cb += 16) {
+          uint32_t v[16];
+          tcgen05_ld_32x32b_x16(taddr + cb, v);
+          float sum[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) sum[i] = __uint_as_float(v[i]);
+          for (int j = 0; j < contributors; ++j) {  // CTA order; the sixteen loads of a contributor are independent
+            float part[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) part[i] = __ldcg(&ws[((size_t)(c + 1 + j) * 64 + cb + i) * 128 + r]);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) sum[i] += part[i];
+          }
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const int m = cb + i;
+            if (m < M && n < N) out[(size_t)m * ldo + n] = from_float<TOut>(sum[i]);
+          }
+        }
+        if (contributors > 0) {
+          asm volatile("bar.sync 1, 128;\n" ::: "memory");
+          if (etid < contributors) atomicExch(&flags[c + 1 + etid], 0);  // lowered for the next launch
+        }
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_empty_bar(acc));
+    }
+  }
+
+  __syncwarp();
+  if (*abortp) {
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000LL) __nanosleep(256);
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(kCols) : "memory");
+  }
+}
+
 // ------------------------------------------------------------------------------------------------ host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -600,6 +839,27 @@ static int launch_tcgen05_pair(const CUtensorMap& ma, const CUtensorMap& mb, voi
   return check_launch("gemm_tcgen05_pair");
 }
 
+template <typename TOut>
+static int launch_stream(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int m, int n, int k, int64_t ldo, int ntok, float* ws,
+                         int* flags, cudaStream_t s) {
+  static int sms = 0;
+  static bool attr_set = false;
+  const size_t smem = (size_t)STAGES_S * kStageSBytes + 1024;
+  auto kernel = gemm_stream_kernel<TOut>;
+  if (!attr_set) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    attr_set = true;
+  }
+  const long long units = (long long)((n + 127) / 128) * ((k + BK - 1) / BK);
+  long long grid = sms < kStreamMaxCtas ? sms : kStreamMaxCtas;
+  if (units < grid) grid = units;
+  launch_kernel(kernel, dim3((int)grid), dim3(192), smem, s, mw, mx, (TOut*)out, m, n, k, ldo, ntok, ws, flags);
+  return check_launch("gemm_stream");
+}
+
 static bool g_use_pairs = true;
 
 }  // namespace roost
@@ -663,4 +923,32 @@ extern "C" int roost_gemm_tcgen05_swiglu(const void* a, const void* w, void* out
   if (rc != ROOST_OK) return rc;
   if (g_use_pairs) return launch_tcgen05_pair<__nv_bfloat16, 1>(ma, mb, out, m, n, k, ldo, (cudaStream_t)stream);
   return launch_tcgen05<__nv_bfloat16, 1>(ma, mb, out, m, n, k, ldo, (cudaStream_t)stream);
+}
+
+// Workspace of the weight-streaming product: floats for the partial sums and ints for the flags (zero before the first
+// call; every call leaves them zero).
+extern "C" int roost_gemm_stream_workspace_floats(void) { return kStreamMaxCtas * 64 * 128; }
+extern "C" int roost_gemm_stream_workspace_flags(void) { return kStreamMaxCtas; }
+
+extern "C" int roost_gemm_stream_supported(int m, int n, int k, int64_t ldx, int64_t ldw) {
+  return m >= 1 && m <= 64 && n >= 1 && k >= 8 && k % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0;
+}
+
+extern "C" int roost_gemm_stream(const void* x, const void* w, void* out, int m, int n, int k, int64_t ldx, int64_t ldw, int64_t ldo,
+                                 int out_dtype, float* ws, int32_t* flags, roost_stream_t stream) {
+  ROOST_REQUIRE(out_dtype == ROOST_BF16 || out_dtype == ROOST_F32, "gemm_stream: the output is bfloat16 (1) or float32 (0)");
+  ROOST_REQUIRE(ldx >= k && ldw >= k && ldo >= n, "gemm_stream: a leading dimension is smaller than its row");
+  ROOST_REQUIRE(ws != nullptr && flags != nullptr, "gemm_stream: the workspace is missing");
+  if (!roost_gemm_stream_supported(m, n, k, ldx, ldw)) {
+    return fail(ROOST_ERR_UNSUPPORTED, "gemm_stream: needs 1 <= m <= 64, k and the row strides multiples of 8");
+  }
+  ROOST_REQUIRE(((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0), "gemm_stream: x and w must start on 16-byte boundaries");
+  const int ntok = m <= 16 ? 16 : (m <= 32 ? 32 : 64);
+  CUtensorMap mw, mx;
+  int rc = make_map(&mw, w, n, k, ldw, 128);
+  if (rc != ROOST_OK) return rc;
+  rc = make_map(&mx, x, m, k, ldx, ntok);
+  if (rc != ROOST_OK) return rc;
+  if (out_dtype == ROOST_BF16) return launch_stream<__nv_bfloat16>(mw, mx, out, m, n, k, ldo, ntok, ws, flags, (cudaStream_t)stream);
+  return launch_stream<float>(mw, mx, out, m, n, k, ldo, ntok, ws, flags, (cudaStream_t)stream);
 }

@@ -30,6 +30,9 @@ extern "C" {
 typedef void* roost_stream_t;
 
 int roost_abi_version(void);
+/* Programmatic dependent launch for the library's kernels (off by default): a kernel may start its preamble, and the
+ * weight-streaming product its first loads of weights, while the kernel before it on the stream is finishing. */
+void roost_set_pdl(int on);
 /* Message of the last non-OK status on this thread. */
 const char* roost_last_error(void);
 
@@ -133,6 +136,17 @@ void roost_gemm_tcgen05_set_pairs(int on);
  * gate rows followed by their 128 up rows; out [m, n / 2] bfloat16. n must be a multiple of 256. */
 int roost_gemm_tcgen05_swiglu(const void* a, const void* w, void* out, int m, int n, int k, int64_t lda, int64_t ldw,
                               int64_t ldo, roost_stream_t stream);
+
+/* out[m,n] = sum_k x[m,k] * w[n,k] for 1 <= m <= 64 rows of bfloat16 x: w streamed once by TMA through a persistent
+ * CTA per SM, the products on tcgen05 with w's rows as the 128-row operand, the work split into equal contiguous ranges
+ * of (128 rows x 64 k) units with a fixed-order fix-up of tiles shared by neighbouring CTAs (gemm_tcgen05.cu).
+ * ws: roost_gemm_stream_workspace_floats() floats, flags: roost_gemm_stream_workspace_flags() int32, zero before the first
+ * call and left zero by every call. */
+int roost_gemm_stream_workspace_floats(void);
+int roost_gemm_stream_workspace_flags(void);
+int roost_gemm_stream_supported(int m, int n, int k, int64_t ldx, int64_t ldw);
+int roost_gemm_stream(const void* x, const void* w, void* out, int m, int n, int k, int64_t ldx, int64_t ldw, int64_t ldo,
+                      int out_dtype, float* ws, int32_t* flags, roost_stream_t stream);
 
 /* ids[r] = index of the largest logit of row r, ties to the lowest index, NaN never chosen (-1 if none). */
 int roost_argmax(const float* logits, int64_t stride, int rows, int vocab, int32_t* ids, roost_stream_t stream);

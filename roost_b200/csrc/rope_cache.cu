@@ -35,6 +35,8 @@ __global__ void qk_norm_rope_cache_kernel(const T* __restrict__ qkv, int64_t qkv
                                           int64_t pool_pages, int slots_per_token, int wdtype, bool vector_ok) {
   const int lane = threadIdx.x & 31;
   const int slot_idx = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  pdl_launch_dependents();
+  pdl_wait();
   if (slot_idx >= slots_per_token) return;
   const size_t t = blockIdx.x;
   const T* row = qkv + t * qkv_stride;
@@ -161,7 +163,7 @@ extern "C" int roost_qk_norm_rope_cache(const void* qkv, int64_t qkv_stride, voi
   const bool vector_ok = (head_dim * esize) % 16 == 0 && (qkv_stride * esize) % 16 == 0 && (uintptr_t)qkv % 16 == 0 &&
                          (uintptr_t)q_out % 16 == 0 && (!write_kv || ((uintptr_t)k_pool % 16 == 0 && (uintptr_t)v_pool % 16 == 0));
   ROOST_DISPATCH_DTYPE(dtype, T,
-                       qk_norm_rope_cache_kernel<T><<<grid, warps * 32, 0, (cudaStream_t)stream>>>(
+                       launch_kernel(qk_norm_rope_cache_kernel<T>, grid, dim3(warps * 32), 0, (cudaStream_t)stream,
                            (const T*)qkv, qkv_stride, (T*)q_out, (T*)k_pool, (T*)v_pool, q_w, k_w, inv_freq, positions,
                            slot_mapping, q_heads, kv_heads, head_dim, rotary_dim, eps, page_size, pool_pages, slots, wdtype, vector_ok));
   return check_launch("qk_norm_rope_cache");

@@ -10,6 +10,7 @@ checked on the host before anything is launched (src/Starlings.Roost.Worker/Eage
 """
 from __future__ import annotations
 
+import weakref
 from dataclasses import dataclass, field
 
 import torch
@@ -47,7 +48,7 @@ class DecodeGraph:
     path with the same arguments, and the tests compare both with the plain implementation."""
 
     def __init__(self, executor: "StepExecutor", num_rows: int, kv_cap: int, plan_keys: list):
-        self.ex = executor
+        self.ex = weakref.proxy(executor)   # the executor owns its graphs; no reference cycle keeps its cache alive
         self.num_rows, self.kv_cap = num_rows, kv_cap
         self.plan_keys = list(plan_keys)
         builder = executor.builder
@@ -230,6 +231,13 @@ class StepExecutor:
             if fresh:
                 idx = torch.tensor(fresh, dtype=torch.long, device=self.rt.device)
                 self.storage.tensors[gi].index_fill_(1, idx, 0)
+
+    def close(self) -> None:
+        """Drops the captured graphs and the cache's device memory."""
+        self._graphs.clear()
+        self.cache.free_all()
+        self.storage.tensors.clear()
+        self.storage._view_of_run.clear()
 
     def finish(self, request_id) -> None:
         """The request is done: everything it holds goes back to the pools."""

@@ -68,6 +68,11 @@ _SIGNATURES = {
     "roost_gemm_tcgen05_supported": [c_int, c_int, c_int, c_int64, c_int64],
     "roost_gemm_tcgen05": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int, c_void_p],
     "roost_gemm_tcgen05_status": [],
+    "roost_gemm_stream_workspace_floats": [],
+    "roost_gemm_stream_workspace_flags": [],
+    "roost_gemm_stream_supported": [c_int, c_int, c_int, c_int64, c_int64],
+    "roost_gemm_stream": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int, c_void_p, c_void_p,
+                          c_void_p],
     "roost_argmax": [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p],
     "roost_sample": [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                      c_void_p, c_void_p],
@@ -262,6 +267,32 @@ class KernelLibrary:
                    dtype_code(out_dtype), _stream())
         return out
 
+    def set_pdl(self, on: bool) -> None:
+        """Programmatic dependent launch for the library's kernels."""
+        self._lib.roost_set_pdl(1 if on else 0)
+        self.pdl = bool(on)
+
+    def gemm_stream_supported(self, m: int, n: int, k: int, ldx: int, ldw: int) -> bool:
+        return bool(self._lib.roost_gemm_stream_supported(m, n, k, ldx, ldw))
+
+    def gemm_stream(self, x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+        """x [M <= 64, K] times w [N, K] transposed: the weight-streaming tcgen05 product of decode steps."""
+        _need(x, "x", torch.bfloat16); _need(w, "w", torch.bfloat16)
+        M, K = x.shape
+        N, K2 = w.shape
+        if K != K2:
+            raise KernelError(f"gemm_stream: x has {K} columns, w has {K2}")
+        ws = getattr(self, "_stream_ws", None)
+        if ws is None or ws[0].device != x.device:
+            # allocated once, outside any stream capture (the first decode step of a model runs eagerly)
+            ws = self._stream_ws = (torch.zeros(self._lib.roost_gemm_stream_workspace_floats(), dtype=torch.float32, device=x.device),
+                                    torch.zeros(self._lib.roost_gemm_stream_workspace_flags(), dtype=torch.int32, device=x.device))
+        out_dtype = out_dtype or torch.bfloat16
+        out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+        self._call("roost_gemm_stream", _ptr(x), _ptr(w), _ptr(out), M, N, K, x.stride(0), w.stride(0), out.stride(0),
+                   dtype_code(out_dtype), _ptr(ws[0]), _ptr(ws[1]), _stream())
+        return out
+
     def gemm_tcgen05_set_pairs(self, on: bool) -> None:
         """Tiles on pairs of CTAs (cta_group::2, the default) or on single CTAs."""
         self._lib.roost_gemm_tcgen05_set_pairs(1 if on else 0)
@@ -306,4 +337,8 @@ def load() -> KernelLibrary:
         if major != 10:
             raise KernelError(f"the GPU has compute capability {major}.{minor}; the kernel library is built for sm_100a only")
         _LIB = KernelLibrary(build.library_path())
+        import os
+        # programmatic dependent launch is on unless ROOST_PDL=0: the library's kernels overlap their preambles, and the
+        # weight-streaming product its first loads of weights, with the tail of the kernel before them
+        _LIB.set_pdl(os.environ.get("ROOST_PDL", "1") != "0")
     return _LIB

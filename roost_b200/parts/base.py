@@ -53,7 +53,7 @@ class Runtime:
         self.dtype = dtype
         self.device = torch.device(device)
         self.kernels = kernels
-        self.use_skinny_gemm = False   # route products of at most 32 rows to the library's weight-streaming kernel
+        self.small_gemm = "auto"        # products of at most 64 rows: "auto" | "library" | "stream" | "skinny" (parts/linear.py)
 
     @property
     def full_precision(self) -> bool:

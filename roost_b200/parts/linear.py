@@ -2,9 +2,10 @@
 
 float32 runs the library's FFMA product (true 32-bit, the same bits for a row whatever the batch). bfloat16
 with 32-bit accumulation goes to cuBLAS through torch, the place where the reference's engine also calls a
-library (kernels/src/gemm.cu:235); with ``Runtime.use_skinny_gemm`` products of at most 32 rows run the library's
-own weight-streaming kernel instead (measured on a B200 it matches cuBLAS at 1 to 8 rows and is slower at 32, so
-it is off by default).
+library (kernels/src/gemm.cu:235), except where a kernel of this library is faster. ``Runtime.small_gemm`` decides for
+products of at most 64 rows (decode steps): "auto" streams the weights through the TMA/tcgen05 kernel where that was
+measured faster than cuBLAS on a B200 (at most 16 rows and a reduction length of 8192 or more, or the vocabulary-sized
+head) and leaves the rest to cuBLAS; "stream" and "skinny" force one of the library's kernels, "library" forces cuBLAS.
 """
 from __future__ import annotations
 
@@ -33,9 +34,15 @@ class Linear:
         out_dtype = out_dtype or self.rt.dtype
         if self.rt.full_precision:
             return k.gemm_simt(x, self.weight, torch.float32)
-        if self.rt.use_skinny_gemm and x.shape[0] <= 32 and x.is_contiguous() and k.gemm_skinny_supported(
-                x.shape[0], self.out_features, self.in_features, x.stride(0), self.weight.stride(0)):
-            return k.gemm_skinny(x, self.weight, out_dtype)   # a few rows: the library's weight-streaming product
+        M = x.shape[0]
+        if M <= 64 and x.is_contiguous():
+            policy = self.rt.small_gemm
+            if policy == "stream" or (policy == "auto" and M <= 16 and (self.in_features >= 8192 or self.out_features >= 65536)):
+                if k.gemm_stream_supported(M, self.out_features, self.in_features, x.stride(0), self.weight.stride(0)):
+                    return k.gemm_stream(x, self.weight, out_dtype)   # weights streamed once by TMA, tcgen05 products
+            if policy == "skinny" and M <= 32 and k.gemm_skinny_supported(M, self.out_features, self.in_features, x.stride(0),
+                                                                          self.weight.stride(0)):
+                return k.gemm_skinny(x, self.weight, out_dtype)
         if out_dtype == torch.bfloat16:
             k.launches += 1
             return torch.matmul(x, self.weight.t())

@@ -92,6 +92,12 @@ class FakeKernels:
                 out[t, h * d : (h + 1) * d] = (p @ vv[:, h // group, :]).to(q.dtype)
         return out
 
+    def gemm_stream_supported(self, *a):
+        return False
+
+    def gemm_skinny_supported(self, *a):
+        return False
+
     def gemm_simt(self, a, w, out_dtype=None):
         return (a.float() @ w.float().t()).to(out_dtype or a.dtype)
 

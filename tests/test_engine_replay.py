@@ -161,3 +161,16 @@ def test_a_step_that_does_not_fit_changes_nothing(tiny, backend):
     ex.finish("a")
     out = ex.step([StepEntry("b", ids[: 2 * P], [2 * P - 1])])
     assert out.shape == (1, t["config"]["vocab_size"])
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("policy", ["stream", "skinny", "library"])
+def test_every_small_product_kernel_serves_the_engine(tiny_model_dirs, policy):
+    """Decode steps through each of the kernels a product of few rows can run on (the default picks by size)."""
+    name, t = "B", TINY["B"]
+    model = H.make_model(tiny_model_dirs[name], torch.bfloat16, "gpu")
+    model.rt.small_gemm = policy
+    ex = StepExecutor(model, page_size=t["page_size"], num_pages=40, max_requests=4)
+    ids = H.random_ids(60, t["config"]["vocab_size"], seed=44)
+    check(H.run_tail_decoded(ex, "r", ids, tail=32), tiny_model_dirs[name], ids, torch.bfloat16, f"{name} decode with {policy} products")
+    assert model.rt.kernels.gemm_tcgen05_status() == 0

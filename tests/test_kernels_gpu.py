@@ -412,3 +412,28 @@ def test_gemm_tcgen05_swiglu(kernels, m, inter, k):
     # the unfused pair on the same interleaved layout
     two = kernels.silu_mul(torch.matmul(a, w.t()), 128)
     close(two, want, torch.bfloat16, "library product + silu_mul on the interleaved layout", scale=2)
+
+
+@pytest.mark.parametrize("m,n,k", [(8, 128, 64), (17, 272, 96), (1, 6144, 4096), (8, 4096, 12288), (64, 2048, 512), (33, 4096, 4096), (5, 151936, 1024)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_gemm_stream(kernels, m, n, k, out_dtype):
+    """The weight-streaming product of decode steps: equal ranges of (128 rows x 64 k) units per CTA, tiles shared by
+    neighbouring CTAs fixed up in CTA order, flags left at zero, the same bits on every run and for every batch."""
+    assert kernels.gemm_stream_supported(m, n, k, k, k)
+    a = rand((m, k), torch.bfloat16, 51)
+    w = rand((n, k), torch.bfloat16, 52)
+    want = a.double().cpu() @ w.double().cpu().T
+    got = kernels.gemm_stream(a, w, out_dtype)
+    assert kernels.gemm_tcgen05_status() == 0, "a bounded wait inside the kernel was given up"
+    assert int(kernels._stream_ws[1].abs().sum()) == 0, "a flag was left raised"
+    if out_dtype == torch.float32:
+        lib = torch.mm(a, w.t(), out_dtype=torch.float32)
+        err = float(((got.double().cpu() - want).abs() / (1 + want.abs())).max())
+        err_lib = float(((lib.double().cpu() - want).abs() / (1 + want.abs())).max())
+        assert err < max(2 * err_lib, k * 2.0 ** -23), f"{err} against the library's {err_lib}"
+    else:
+        close(got, want, torch.bfloat16, "gemm_stream", scale=math.sqrt(k) / 8)
+    assert torch.equal(kernels.gemm_stream(a, w, out_dtype), got), "the product is not repeatable"
+    r = m // 2
+    assert torch.equal(kernels.gemm_stream(a[r : r + 1].contiguous(), w, out_dtype), got[r : r + 1]), "a row depends on its batch"
+    assert not kernels.gemm_stream_supported(65, n, k, k, k) and not kernels.gemm_stream_supported(m, n, k + 4, k + 4, k + 4)
