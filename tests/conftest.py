@@ -35,7 +35,14 @@ TINY_B = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden
               rope_theta=1000000.0, rms_norm_eps=1e-5, tie_word_embeddings=False, max_position_embeddings=1024,
               torch_dtype="bfloat16", hidden_act="silu", sliding_window=40,
               layer_types=["full_attention", "sliding_attention", "full_attention"], eos_token_id=[5, 7])
-TINY = {"A": dict(config=TINY_A, seed=0, std=0.08, norm_std=0.0, page_size=16),
+# A third one with sizes no fast path serves: a width that is no multiple of 8 (no 16-byte vectors, no TMA strides), a
+# head size of 48 (no tensor-core attention: the 32-bit kernel runs in bfloat16 too), one query head per key/value head.
+TINY_C = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=2, hidden_size=44,
+              num_attention_heads=3, num_key_value_heads=3, head_dim=48, intermediate_size=100, vocab_size=131,
+              rope_theta=50000.0, rms_norm_eps=1e-6, tie_word_embeddings=True, max_position_embeddings=300,
+              torch_dtype="float32", hidden_act="silu", sliding_window=24, use_sliding_window=True, max_window_layers=1)
+TINY = {"C": dict(config=TINY_C, seed=2, std=0.1, norm_std=0.05, page_size=4),
+        "A": dict(config=TINY_A, seed=0, std=0.08, norm_std=0.0, page_size=16),
         "B": dict(config=TINY_B, seed=1, std=0.06, norm_std=0.1, page_size=8)}
 
 
