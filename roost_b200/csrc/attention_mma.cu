@@ -8,15 +8,16 @@
 // The query heads that share a key/value head are packed into the rows of one tile: packed row r of a request's
 // step is (token r / G, head r % G), so a decode step of one token still fills G rows of a 16-row MMA tile and a
 // key is loaded once for all G heads. Two kernels share the per-tile arithmetic:
-//   * prefill: a CTA of 4 warps owns 64 packed rows of one request and one key/value head and walks the keys in
-//     tiles of 64, double-buffered with cp.async, all warps sharing each tile;
+//   * prefill: a CTA of 4 warps owns 64 or 128 packed rows of one request and one key/value head and walks the keys
+//     in tiles of 64, double-buffered with cp.async, all warps sharing each tile; with 128 rows a warp carries two row
+//     tiles of 16, so each key and value fragment it loads feeds two products;
 //   * decode (rows with at most 16 packed rows): a CTA owns one fixed-size chunk of a request's keys; its warps take
 //     the chunk's 16-key tiles in turn, each with a three-stage buffer of its own, and merge their partial results in
 //     shared memory; a request with several chunks writes (max, sum, unnormalised output) per chunk to a workspace
 //     that the merge kernel reduces in chunk order. The chunk size is fixed by the caller, so the order of every sum
 //     depends on the request's own length only, never on what else is in the batch.
 // Keys outside a request's visible range are never read: their shared-memory rows are zero-filled.
-#include "common.cuh"
+#include "tma.cuh"
 
 namespace roost {
 
@@ -103,11 +104,12 @@ struct RowState {
   float l[2];  // running sum of 2^(s - m)
 };
 
-// One warp, 16 query rows (A operand from q_smem rows q_row0..+15), BN keys from a K/V tile: S = Q K^T, online
-// softmax, O += P V. qpos/qlo: per held row, the last and first visible key position (qlo > qpos masks the row).
-template <int D, int BN>
-__device__ __forceinline__ void attend_tile(RowState<D>& st, uint32_t q_smem, int q_row0, uint32_t k_smem, uint32_t v_smem, int j0,
-                                            const int (&qpos)[2], const int (&qlo)[2], float scale_log2, int lane) {
+// One warp, 16 query rows, BN keys from a K/V tile laid out as L: S = Q K^T, online softmax, O += P V. q_frag(kk, a0..a3)
+// yields the A operand of k-step kk. qpos/qlo: per held row, the last and first visible key position (qlo > qpos masks
+// the row).
+template <int D, int BN, typename L, typename QFrag>
+__device__ __forceinline__ void attend_core(RowState<D>& st, QFrag q_frag, uint32_t k_smem, uint32_t v_smem, int j0, const int (&qpos)[2],
+                                            const int (&qlo)[2], float scale_log2, int lane) {
   constexpr int NT = BN / 8;
   float s[NT][4];
 #pragma unroll
@@ -115,11 +117,11 @@ __device__ __forceinline__ void attend_tile(RowState<D>& st, uint32_t q_smem, in
 #pragma unroll
   for (int kk = 0; kk < D / 16; ++kk) {
     uint32_t a0, a1, a2, a3;
-    ldmatrix_x4(q_smem + Tile<D>::offset(q_row0 + (lane & 15), kk * 2 + (lane >> 4)), a0, a1, a2, a3);
+    q_frag(kk, a0, a1, a2, a3);
 #pragma unroll
     for (int n2 = 0; n2 < NT / 2; ++n2) {
       uint32_t b0, b1, b2, b3;
-      ldmatrix_x4(k_smem + Tile<D>::offset(n2 * 16 + (lane & 7) + ((lane >> 4) << 3), kk * 2 + ((lane >> 3) & 1)), b0, b1, b2, b3);
+      ldmatrix_x4(k_smem + L::offset(n2 * 16 + (lane & 7) + ((lane >> 4) << 3), kk * 2 + ((lane >> 3) & 1)), b0, b1, b2, b3);
       mma_bf16(s[2 * n2], a0, a1, a2, a3, b0, b1);
       mma_bf16(s[2 * n2 + 1], a0, a1, a2, a3, b2, b3);
     }
@@ -192,12 +194,150 @@ __device__ __forceinline__ void attend_tile(RowState<D>& st, uint32_t q_smem, in
 #pragma unroll
     for (int n2 = 0; n2 < D / 16; ++n2) {
       uint32_t b0, b1, b2, b3;
-      ldmatrix_x4_trans(v_smem + Tile<D>::offset(kk * 16 + (lane & 7) + (((lane >> 3) & 1) << 3), n2 * 2 + (lane >> 4)), b0, b1, b2, b3);
+      ldmatrix_x4_trans(v_smem + L::offset(kk * 16 + (lane & 7) + (((lane >> 3) & 1) << 3), n2 * 2 + (lane >> 4)), b0, b1, b2, b3);
       mma_bf16(st.o[2 * n2], a0, a1, a2, a3, b0, b1);
       mma_bf16(st.o[2 * n2 + 1], a0, a1, a2, a3, b2, b3);
     }
   }
 }
+
+// The same with the query rows q_row0..+15 of a shared-memory tile as the A operand and K/V tiles in the same layout.
+template <int D, int BN>
+__device__ __forceinline__ void attend_tile(RowState<D>& st, uint32_t q_smem, int q_row0, uint32_t k_smem, uint32_t v_smem, int j0,
+                                            const int (&qpos)[2], const int (&qlo)[2], float scale_log2, int lane) {
+  attend_core<D, BN, Tile<D>>(
+      st,
+      [&](int kk, uint32_t& a0, uint32_t& a1, uint32_t& a2, uint32_t& a3) {
+        ldmatrix_x4(q_smem + Tile<D>::offset(q_row0 + (lane & 15), kk * 2 + (lane >> 4)), a0, a1, a2, a3);
+      },
+      k_smem, v_smem, j0, qpos, qlo, scale_log2, lane);
+}
+
+// The same for MT row tiles of 16 per warp: a key or value fragment loaded from shared memory feeds MT products, which is
+// what lifts the ratio of tensor-core work to shared-memory traffic in prefill. Keys key_row0 .. key_row0 + BN - 1 of the
+// K/V tile are used; j0 is the position of the first of them.
+template <int D, int MT>
+struct RowStateM {
+  float o[MT][D / 8][4];
+  float m[MT][2];
+  float l[MT][2];
+};
+
+template <int D, int BN, int MT>
+__device__ __forceinline__ void attend_tile_m(RowStateM<D, MT>& st, uint32_t q_smem, int q_row0, uint32_t k_smem, uint32_t v_smem,
+                                              int key_row0, int j0, const int (&qpos)[MT][2], const int (&qlo)[MT][2], float scale_log2,
+                                              int lane) {
+  constexpr int NT = BN / 8;
+  float s[MT][NT][4];
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+    for (int n = 0; n < NT; ++n) s[mt][n][0] = s[mt][n][1] = s[mt][n][2] = s[mt][n][3] = 0.f;
+#pragma unroll
+  for (int kk = 0; kk < D / 16; ++kk) {
+    uint32_t a[MT][4];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+      ldmatrix_x4(q_smem + Tile<D>::offset(q_row0 + mt * 16 + (lane & 15), kk * 2 + (lane >> 4)), a[mt][0], a[mt][1], a[mt][2], a[mt][3]);
+#pragma unroll
+    for (int n2 = 0; n2 < NT / 2; ++n2) {
+      uint32_t b0, b1, b2, b3;
+      ldmatrix_x4(k_smem + Tile<D>::offset(key_row0 + n2 * 16 + (lane & 7) + ((lane >> 4) << 3), kk * 2 + ((lane >> 3) & 1)), b0, b1, b2, b3);
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) {
+        mma_bf16(s[mt][2 * n2], a[mt][0], a[mt][1], a[mt][2], a[mt][3], b0, b1);
+        mma_bf16(s[mt][2 * n2 + 1], a[mt][0], a[mt][1], a[mt][2], a[mt][3], b2, b3);
+      }
+    }
+  }
+  float corr[MT][2];
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt) {
+    float mx[2] = {-INFINITY, -INFINITY};
+    const bool all_visible = j0 + BN - 1 <= min(qpos[mt][0], qpos[mt][1]) && j0 >= max(qlo[mt][0], qlo[mt][1]);
+    if (__all_sync(0xffffffffu, all_visible)) {
+#pragma unroll
+      for (int n = 0; n < NT; ++n) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          s[mt][n][e] *= scale_log2;
+          mx[e >> 1] = fmaxf(mx[e >> 1], s[mt][n][e]);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int n = 0; n < NT; ++n) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int r = e >> 1;
+          const int j = j0 + n * 8 + (lane & 3) * 2 + (e & 1);
+          const float v = (j <= qpos[mt][r] && j >= qlo[mt][r]) ? s[mt][n][e] * scale_log2 : -INFINITY;
+          s[mt][n][e] = v;
+          mx[r] = fmaxf(mx[r], v);
+        }
+      }
+    }
+    float msafe[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+      const float m_new = fmaxf(st.m[mt][r], mx[r]);
+      msafe[r] = m_new == -INFINITY ? 0.f : m_new;
+      corr[mt][r] = exp2f(st.m[mt][r] - msafe[r]);
+      st.m[mt][r] = m_new;
+    }
+    float sum[2] = {0.f, 0.f};
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float p = exp2f(s[mt][n][e] - msafe[e >> 1]);
+        s[mt][n][e] = p;
+        sum[e >> 1] += p;
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 1);
+      sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 2);
+      st.l[mt][r] = st.l[mt][r] * corr[mt][r] + sum[r];
+    }
+    // the running maximum rarely moves after a row's first tiles: a factor of exactly 1 for every row of the warp needs
+    // no pass over the accumulator
+    if (__any_sync(0xffffffffu, corr[mt][0] != 1.0f || corr[mt][1] != 1.0f)) {
+#pragma unroll
+      for (int n = 0; n < D / 8; ++n) {
+        st.o[mt][n][0] *= corr[mt][0];
+        st.o[mt][n][1] *= corr[mt][0];
+        st.o[mt][n][2] *= corr[mt][1];
+        st.o[mt][n][3] *= corr[mt][1];
+      }
+    }
+  }
+#pragma unroll
+  for (int kk = 0; kk < BN / 16; ++kk) {
+    uint32_t a[MT][4];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+      a[mt][0] = pack_bf16(s[mt][2 * kk][0], s[mt][2 * kk][1]);
+      a[mt][1] = pack_bf16(s[mt][2 * kk][2], s[mt][2 * kk][3]);
+      a[mt][2] = pack_bf16(s[mt][2 * kk + 1][0], s[mt][2 * kk + 1][1]);
+      a[mt][3] = pack_bf16(s[mt][2 * kk + 1][2], s[mt][2 * kk + 1][3]);
+    }
+#pragma unroll
+    for (int n2 = 0; n2 < D / 16; ++n2) {
+      uint32_t b0, b1, b2, b3;
+      ldmatrix_x4_trans(v_smem + Tile<D>::offset(key_row0 + kk * 16 + (lane & 7) + (((lane >> 3) & 1) << 3), n2 * 2 + (lane >> 4)), b0, b1, b2, b3);
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) {
+        mma_bf16(st.o[mt][2 * n2], a[mt][0], a[mt][1], a[mt][2], a[mt][3], b0, b1);
+        mma_bf16(st.o[mt][2 * n2 + 1], a[mt][0], a[mt][1], a[mt][2], a[mt][3], b2, b3);
+      }
+    }
+  }
+}
+
 
 // Loads packed query rows [row0, row0 + ROWS) of one request and key/value head into a Q tile (rows past the
 // request's last packed row are zero-filled).
@@ -216,8 +356,8 @@ __device__ __forceinline__ void load_q_tile(uint32_t q_smem, const __nv_bfloat16
 }
 
 // ------------------------------------------------------------------------------------------------ prefill
-// work[i] = (batch row, first packed row of the tile)
-template <int D>
+// work[i] = (batch row, first packed row of the tile); a tile is 64 * MT packed rows, 16 * MT per warp
+template <int D, int MT>
 __global__ void __launch_bounds__(128) attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out,
                                                                 const __nv_bfloat16* __restrict__ k_pool,
                                                                 const __nv_bfloat16* __restrict__ v_pool,
@@ -225,7 +365,7 @@ __global__ void __launch_bounds__(128) attention_prefill_kernel(const __nv_bfloa
                                                                 const int32_t* __restrict__ kv_indptr,
                                                                 const int32_t* __restrict__ kv_indices, const int2* __restrict__ work,
                                                                 int q_heads, int kv_heads, int page_size, int page_shift, float scale_log2, int window) {
-  constexpr int BM = 64, BN = 64, NT = 128;
+  constexpr int BM = 64 * MT, BN = 64, HALF = 32, NT = 128;
   extern __shared__ __align__(128) unsigned char smem_raw[];
   const uint32_t smem = (uint32_t)__cvta_generic_to_shared(smem_raw);
   constexpr uint32_t kTileBytes = BN * D * 2;
@@ -248,34 +388,44 @@ __global__ void __launch_bounds__(128) attention_prefill_kernel(const __nv_bfloa
   const int rows_total = n * group;
   const int32_t* pages = kv_indices + kv_indptr[b];
 
-  // this thread's two rows
-  int qpos[2], qlo[2];
+  // this thread's rows: two in each of the warp's MT row tiles
+  int qpos[MT][2], qlo[MT][2];
 #pragma unroll
-  for (int r = 0; r < 2; ++r) {
-    const int pr = row0 + warp * 16 + (lane >> 2) + r * 8;
-    if (pr < rows_total) {
-      qpos[r] = pos0 + pr / group;
-      qlo[r] = window > 0 ? max(0, qpos[r] - window + 1) : 0;
-    } else {
-      qpos[r] = -1;  // sees nothing
-      qlo[r] = 0;
+  for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const int pr = row0 + warp * 16 * MT + mt * 16 + (lane >> 2) + r * 8;
+      if (pr < rows_total) {
+        qpos[mt][r] = pos0 + pr / group;
+        qlo[mt][r] = window > 0 ? max(0, qpos[mt][r] - window + 1) : 0;
+      } else {
+        qpos[mt][r] = -1;  // sees nothing
+        qlo[mt][r] = 0;
+      }
     }
   }
-  // the tile's key range
+  // the tile's key range, and this warp's own (a warp skips key tiles none of its rows can see)
   const int last_row = min(row0 + BM, rows_total) - 1;
   const int hi = pos0 + last_row / group;
   const int lo = window > 0 ? max(0, pos0 + row0 / group - window + 1) : 0;
   const int t0 = lo / BN, t1 = hi / BN;
+  const int warp_first = row0 + warp * 16 * MT;
+  const int warp_last = min(warp_first + 16 * MT, rows_total) - 1;
+  const int warp_hi = warp_last >= warp_first ? pos0 + warp_last / group : -1;
+  const int warp_lo = window > 0 ? max(0, pos0 + warp_first / group - window + 1) : 0;
 
   load_q_tile<D, BM, NT>(q_smem, q, q_start, q_heads, group, kvh, row0, rows_total, tid);
   load_kv_tile<D, BN, NT>(k_smem[0], v_smem[0], k_pool, v_pool, pages, page_size, page_shift, kv_heads, kvh, t0 * BN, lo, hi, tid);
   cp_async_commit();
 
-  RowState<D> st;
+  RowStateM<D, MT> st;
 #pragma unroll
-  for (int i = 0; i < D / 8; ++i) st.o[i][0] = st.o[i][1] = st.o[i][2] = st.o[i][3] = 0.f;
-  st.m[0] = st.m[1] = -INFINITY;
-  st.l[0] = st.l[1] = 0.f;
+  for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) st.o[mt][i][0] = st.o[mt][i][1] = st.o[mt][i][2] = st.o[mt][i][3] = 0.f;
+    st.m[mt][0] = st.m[mt][1] = -INFINITY;
+    st.l[mt][0] = st.l[mt][1] = 0.f;
+  }
 
   for (int t = t0; t <= t1; ++t) {
     const int stage = (t - t0) & 1;
@@ -287,19 +437,28 @@ __global__ void __launch_bounds__(128) attention_prefill_kernel(const __nv_bfloa
       cp_async_wait<0>();
     }
     __syncthreads();
-    attend_tile<D, BN>(st, q_smem, warp * 16, k_smem[stage], v_smem[stage], t * BN, qpos, qlo, scale_log2, lane);
+#pragma unroll
+    for (int half = 0; half < BN / HALF; ++half) {
+      const int j0 = t * BN + half * HALF;
+      if (j0 <= warp_hi && j0 + HALF - 1 >= warp_lo) {  // uniform in the warp
+        attend_tile_m<D, HALF, MT>(st, q_smem, warp * 16 * MT, k_smem[stage], v_smem[stage], half * HALF, j0, qpos, qlo, scale_log2, lane);
+      }
+    }
     __syncthreads();
   }
 
 #pragma unroll
-  for (int r = 0; r < 2; ++r) {
-    const int pr = row0 + warp * 16 + (lane >> 2) + r * 8;
-    if (pr >= rows_total) continue;
-    const float inv = st.l[r] > 0.f ? 1.0f / st.l[r] : 0.f;
-    __nv_bfloat16* dst = out + ((size_t)(q_start + pr / group) * q_heads + kvh * group + pr % group) * D + (lane & 3) * 2;
+  for (int mt = 0; mt < MT; ++mt) {
 #pragma unroll
-    for (int nn = 0; nn < D / 8; ++nn) {
-      *reinterpret_cast<uint32_t*>(dst + nn * 8) = pack_bf16(st.o[nn][2 * r] * inv, st.o[nn][2 * r + 1] * inv);
+    for (int r = 0; r < 2; ++r) {
+      const int pr = row0 + warp * 16 * MT + mt * 16 + (lane >> 2) + r * 8;
+      if (pr >= rows_total) continue;
+      const float inv = st.l[mt][r] > 0.f ? 1.0f / st.l[mt][r] : 0.f;
+      __nv_bfloat16* dst = out + ((size_t)(q_start + pr / group) * q_heads + kvh * group + pr % group) * D + (lane & 3) * 2;
+#pragma unroll
+      for (int nn = 0; nn < D / 8; ++nn) {
+        *reinterpret_cast<uint32_t*>(dst + nn * 8) = pack_bf16(st.o[mt][nn][2 * r] * inv, st.o[mt][nn][2 * r + 1] * inv);
+      }
     }
   }
 }
@@ -325,8 +484,8 @@ __global__ void __launch_bounds__(NWARPS * 32)
   const uint32_t q_smem = smem;
   const uint32_t wbase = smem + kQBytes + warp * kWarpBytes;
 
-  pdl_launch_dependents();
-  pdl_wait();
+  pdl_launch_dependents(4);
+  pdl_wait(4);
   const int4 w = work[blockIdx.x];
   const int b = w.x, kv_begin = w.y, kv_end = w.z, slot = w.w;
   if (b < 0) return;  // padding of a fixed-size work list
@@ -444,13 +603,307 @@ __global__ void __launch_bounds__(NWARPS * 32)
   }
 }
 
+// ------------------------------------------------------------------------------------------------ decode, keys and values by TMA
+// The same chunks, streamed by the copy engine through one ring of shared-memory stages per CTA. The CTAs are persistent:
+// CTA c takes the (chunk, key/value head) pairs c, c + G, c + 2G, ... of the work list, and the ring keeps running
+// across them, so the loads of the next chunk are in flight while the last tiles of this one are computed and merged.
+//   warp 4 (producer): per chunk it reads the chunk's row of the step tables, publishes them to the consumers through a
+//     two-entry descriptor ring, and walks the chunk in tiles of 32 keys: it looks the pages up (32 block-table entries
+//     a load, one batch ahead, kept one a lane as pool rows), waits for a free stage and issues one tensor copy per page
+//     that brings the page's keys and values (a 4-D box over the pool: 64 columns x rows x column blocks x {K, V}) into
+//     128-byte-swizzled shared memory; the copies complete on the stage's barrier.
+//   warps 0..3 (consumers): tile g of the CTA's stream goes to warp g % 4. Each keeps the query fragments in registers
+//     and a running state of its own, hands the stage back after its products, and the four merge through shared memory
+//     in warp order when the chunk ends, four packed rows a pass.
+// A page is copied whole: rows of a tile that lie outside the row's visible keys hold whatever the pool holds there.
+// Their scores are masked by position; their value rows are zeroed in shared memory by the consuming warp before the
+// second product (only the first and last tile of a chunk have such rows), so nothing outside the visible range reaches
+// a result. A page the request has given back (block-table entry -1) is replaced by the request's last page.
+// Every wait is bounded: a wait given up raises the CTA's abort flag, records a code that roost_attention_status()
+// returns, and the CTA lets its copies land before it exits.
+constexpr int kTmaTileKeys = 32;
+constexpr int kTmaConsumers = 4;
+constexpr int kTmaMergeRows = 4;  // packed rows merged per pass
+__device__ int g_attention_error = 0;
+
+// A tile of TK keys as the copies leave it: [page of RPC rows][K, V][D / 64 column blocks][RPC][64 bfloat16], 128-byte
+// swizzle, 1024-byte aligned. offset() is relative to the tile's keys; the values follow at kValues.
+template <int D, int RPC>
+struct TileTma {
+  static constexpr uint32_t kValues = (D / 64) * RPC * 128;
+  static constexpr uint32_t kPage = 2 * kValues;
+  __device__ static __forceinline__ uint32_t offset(int row, int chunk) {
+    return (uint32_t)((row / RPC) * kPage + (chunk >> 3) * RPC * 128 + (row % RPC) * 128 + (((chunk & 7) ^ (row & 7)) << 4));
+  }
+};
+
+struct DecodeChunk {  // what the producer tells the consumers about a chunk
+  int b, kvh, slot, q_start, n, kv_len, lo, hi, t0, ntiles;
+};
+
+template <int D>
+constexpr int tma_decode_stages() {
+  return (96 * 1024) / (2 * kTmaTileKeys * D * 2);  // 6 at head size 128, 12 at 64
+}
+
+template <int D, int RPC>
+__global__ void __launch_bounds__((kTmaConsumers + 1) * 32, 2)
+    attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out,
+                                const int32_t* __restrict__ q_indptr, const int32_t* __restrict__ kv_lens,
+                                const int32_t* __restrict__ kv_indptr, const int32_t* __restrict__ kv_indices,
+                                const int4* __restrict__ work, int items, float* __restrict__ part_o, float* __restrict__ part_ml, int q_heads,
+                                int kv_heads, int page_size, float scale_log2, int window) {
+  constexpr int TK = kTmaTileKeys, STAGES = tma_decode_stages<D>(), NW = kTmaConsumers, MR = kTmaMergeRows;
+  constexpr uint32_t kStageBytes = 2 * TK * D * 2;  // keys and values of TK positions
+  constexpr uint32_t kQBytes = 16 * D * 2;
+  constexpr int kScratchStride = D + 8;              // floats; the pad spreads the rows over the banks
+  using L = TileTma<D, RPC>;
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t smem_base = ((uint32_t)__cvta_generic_to_shared(smem_raw) + 1023u) & ~1023u;
+  unsigned char* smem_gen = smem_raw + (smem_base - (uint32_t)__cvta_generic_to_shared(smem_raw));
+  const uint32_t q_smem = smem_base + STAGES * kStageBytes;
+  float* sm_o = reinterpret_cast<float*>(smem_gen + STAGES * kStageBytes + kQBytes);  // [NW][MR][kScratchStride]
+  float* sm_ml = sm_o + NW * MR * kScratchStride;                                      // [NW][MR][2]
+  __shared__ __align__(8) uint64_t bars[2 * STAGES + 4];
+  __shared__ DecodeChunk desc[2];
+  __shared__ int abort_flag;
+  const uint32_t bar0 = (uint32_t)__cvta_generic_to_shared(bars);
+  auto full_bar = [&](int st) { return bar0 + 8u * st; };
+  auto empty_bar = [&](int st) { return bar0 + 8u * (STAGES + st); };
+  auto desc_full = [&](int d) { return bar0 + 8u * (2 * STAGES + d); };
+  auto desc_empty = [&](int d) { return bar0 + 8u * (2 * STAGES + 2 + d); };
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+  if (tid == 0) {
+    prefetch_tensormap(&map_kv);
+    abort_flag = 0;
+    for (int st = 0; st < STAGES; ++st) {
+      mbar_init(full_bar(st), 1);
+      mbar_init(empty_bar(st), 1);
+    }
+    for (int d = 0; d < 2; ++d) {
+      mbar_init(desc_full(d), 1);
+      mbar_init(desc_empty(d), NW);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  pdl_launch_dependents(4);
+  pdl_wait(4);
+  __syncthreads();  // the barriers are initialised
+  const int group = q_heads / kv_heads;
+  const long long total = (long long)items * kv_heads;
+  volatile int* abortp = &abort_flag;
+
+  if (warp == NW) {
+    // ---- producer: all lanes walk the loops (a lane holds one block-table entry of the current 32, as the pool row its
+    // page starts at); lane 0 waits, publishes and issues
+    constexpr int COPIES = TK / RPC;
+    const int page_shift = 31 - __clz(page_size);  // a power of two here
+    bool ok = true;
+    int g = 0;  // tiles issued so far
+    int k = 0;  // chunks published so far
+    for (long long f = blockIdx.x; ok; f += gridDim.x, ++k) {
+      DecodeChunk c;
+      c.b = -1;
+      if (f < total) {
+        const int4 w = work[f / kv_heads];
+        c.b = w.x;  // padding entries (batch row -1) end the list
+        if (c.b >= 0) {
+          c.kvh = (int)(f % kv_heads);
+          c.slot = w.w;
+          c.q_start = q_indptr[c.b];
+          c.n = q_indptr[c.b + 1] - c.q_start;
+          c.kv_len = kv_lens[c.b];
+          const int pos0 = c.kv_len - c.n;
+          c.hi = min(w.z - 1, c.kv_len - 1);
+          c.lo = max(w.y, window > 0 ? max(0, pos0 - window + 1) : 0);
+          c.t0 = c.lo / TK;
+          c.ntiles = c.hi >= c.lo ? (c.hi / TK - c.t0 + 1) : 0;
+        }
+      }
+      if (lane == 0) {
+        if (k >= 2) ok = mbar_wait_limited(desc_empty(k & 1), (uint32_t)((k >> 1) - 1) & 1u, abortp, 4, &g_attention_error);
+        if (ok) {
+          desc[k & 1] = c;
+          mbar_arrive(desc_full(k & 1));  // releases the descriptor to the consumers
+        }
+      }
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      if (c.b < 0 || !ok) break;
+      if (c.ntiles == 0) continue;
+      const int32_t* pages = kv_indices + kv_indptr[c.b];
+      const int p_first = (c.t0 * TK) >> page_shift, p_last = c.hi >> page_shift;
+      const int fallback = pages[p_last];
+      auto row_of = [&](int p, int entry) {  // first pool row of page p of the request, given its block-table entry
+        const bool visible = ((p + 1) << page_shift) > c.lo && (p << page_shift) <= c.hi;
+        return ((visible && entry >= 0 ? entry : fallback) * kv_heads + c.kvh) << page_shift;
+      };
+      int batch0 = p_first;  // the page lane 0 holds
+      int cur = row_of(batch0 + lane, batch0 + lane <= p_last ? pages[batch0 + lane] : -1);
+      int nxt_entry = batch0 + 32 + lane <= p_last ? pages[batch0 + 32 + lane] : -1;
+      for (int i = 0; i < c.ntiles && ok; ++i, ++g) {
+        const int stage = g % STAGES;
+        const uint32_t dst = smem_base + stage * kStageBytes;
+        const int j = (c.t0 + i) * TK;
+        if ((j >> page_shift) >= batch0 + 32) {  // uniform in the warp
+          batch0 += 32;
+          cur = row_of(batch0 + lane, nxt_entry);
+          nxt_entry = batch0 + 32 + lane <= p_last ? pages[batch0 + 32 + lane] : -1;
+        }
+        int rows[COPIES];
+#pragma unroll
+        for (int cc = 0; cc < COPIES; ++cc) {
+          const int jc = j + cc * RPC;
+          rows[cc] = __shfl_sync(0xffffffffu, cur, ((jc >> page_shift) - batch0) & 31) + (jc & (page_size - 1));
+        }
+        if (lane == 0) {
+          if (g >= STAGES) ok = mbar_wait_limited(empty_bar(stage), (uint32_t)((g / STAGES) - 1) & 1u, abortp, 1, &g_attention_error);
+          if (ok) {
+            mbar_expect_tx(full_bar(stage), kStageBytes);
+#pragma unroll
+            for (int cc = 0; cc < COPIES; ++cc) tma_load_4d(dst + cc * L::kPage, &map_kv, full_bar(stage), 0, rows[cc], 0, 0);
+          }
+        }
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      }
+    }
+    if (*abortp) {  // copies in flight land before the CTA's shared memory is given back
+      const long long c0 = clock64();
+      while (clock64() - c0 < 2000000LL) __nanosleep(256);
+    }
+    return;
+  }
+
+  // ---- consumers
+  bool ok = true;
+  int g0 = 0;  // tiles of the chunks before this one
+  for (int k = 0; ok; ++k) {
+    if (!(ok = mbar_wait_limited(desc_full(k & 1), (uint32_t)(k >> 1) & 1u, abortp, 5, &g_attention_error))) break;
+    const DecodeChunk c = desc[k & 1];
+    __syncwarp();
+    if (lane == 0) mbar_arrive(desc_empty(k & 1));  // this warp holds the descriptor in registers
+    if (c.b < 0) break;
+    const int rows_total = c.n * group;  // at most 16
+    const int pos0 = c.kv_len - c.n;
+    // every warp is past its reads of the previous chunk's Q tile and merge scratch (the barriers that end a chunk)
+    load_q_tile<D, 16, NW * 32>(q_smem, q, c.q_start, q_heads, group, c.kvh, 0, rows_total, tid);
+    cp_async_commit();
+    cp_async_wait<0>();
+    asm volatile("bar.sync 1, %0;\n" ::"n"(NW * 32) : "memory");
+    uint32_t qf[D / 16][4];
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) {
+      ldmatrix_x4(q_smem + Tile<D>::offset(lane & 15, kk * 2 + (lane >> 4)), qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3]);
+    }
+    int qpos[2], qlo[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const int pr = (lane >> 2) + r * 8;
+      if (pr < rows_total) {
+        qpos[r] = pos0 + pr / group;
+        qlo[r] = window > 0 ? max(0, qpos[r] - window + 1) : 0;
+      } else {
+        qpos[r] = -1;
+        qlo[r] = 0;
+      }
+    }
+    RowState<D> st;
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) st.o[i][0] = st.o[i][1] = st.o[i][2] = st.o[i][3] = 0.f;
+    st.m[0] = st.m[1] = -INFINITY;
+    st.l[0] = st.l[1] = 0.f;
+
+    for (int i = (warp - g0 % NW + NW) % NW; i < c.ntiles; i += NW) {
+      const int g = g0 + i;
+      const int stage = g % STAGES;
+      // A wait names its phase by parity only, so it must not be asked of a barrier two phases behind. The stage's
+      // previous tile (g - STAGES) may belong to another warp, which may not have taken it yet: once it has handed the
+      // stage back, the full barrier is in this tile's phase and no earlier one.
+      if (g >= STAGES && !(ok = mbar_wait_limited(empty_bar(stage), (uint32_t)((g / STAGES) - 1) & 1u, abortp, 3, &g_attention_error))) break;
+      if (!(ok = mbar_wait_limited(full_bar(stage), (uint32_t)(g / STAGES) & 1u, abortp, 2, &g_attention_error))) break;
+      const uint32_t k_tile = smem_base + stage * kStageBytes, v_tile = k_tile + L::kValues;
+      const int j0 = (c.t0 + i) * TK;
+      if (j0 < c.lo || j0 + TK - 1 > c.hi) {
+        // value rows outside the visible keys: zero, so that whatever the pool holds there cannot reach the product
+        for (int idx = lane; idx < TK * (D / 8); idx += 32) {
+          const int r = idx / (D / 8), ch = idx % (D / 8);
+          if (j0 + r < c.lo || j0 + r > c.hi) {
+            asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};\n" ::"r"(v_tile + L::offset(r, ch)), "r"(0u) : "memory");
+          }
+        }
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // ordered before the copy that reuses the stage
+        __syncwarp();
+      }
+      attend_core<D, TK, L>(
+          st, [&](int kk, uint32_t& a0, uint32_t& a1, uint32_t& a2, uint32_t& a3) { a0 = qf[kk][0]; a1 = qf[kk][1]; a2 = qf[kk][2]; a3 = qf[kk][3]; },
+          k_tile, v_tile, j0, qpos, qlo, scale_log2, lane);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(empty_bar(stage));
+    }
+    g0 += c.ntiles;
+
+    // merge the warps' states through shared memory (in warp order), MR packed rows a pass, and write the chunk's result
+    for (int r0 = 0; r0 < rows_total; r0 += MR) {
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        const int row = (lane >> 2) + r * 8;
+        if (row >= r0 && row < r0 + MR && row < rows_total) {
+          float* dst = sm_o + ((size_t)warp * MR + (row - r0)) * kScratchStride + (lane & 3) * 2;
+#pragma unroll
+          for (int nn = 0; nn < D / 8; ++nn) {
+            dst[nn * 8] = st.o[nn][2 * r];
+            dst[nn * 8 + 1] = st.o[nn][2 * r + 1];
+          }
+          if ((lane & 3) == 0) {
+            sm_ml[(warp * MR + (row - r0)) * 2] = st.m[r];
+            sm_ml[(warp * MR + (row - r0)) * 2 + 1] = st.l[r];
+          }
+        }
+      }
+      asm volatile("bar.sync 1, %0;\n" ::"n"(NW * 32) : "memory");
+      const int pass_rows = min(MR, rows_total - r0);
+      for (int idx = tid; idx < pass_rows * D; idx += NW * 32) {
+        const int pr = idx / D, col = idx % D;
+        const int row = r0 + pr;
+        float m = -INFINITY;
+#pragma unroll
+        for (int ww = 0; ww < NW; ++ww) m = fmaxf(m, sm_ml[(ww * MR + pr) * 2]);
+        const float msafe = m == -INFINITY ? 0.f : m;
+        float l = 0.f, o = 0.f;
+#pragma unroll
+        for (int ww = 0; ww < NW; ++ww) {
+          const float fac = exp2f(sm_ml[(ww * MR + pr) * 2] - msafe);
+          l += sm_ml[(ww * MR + pr) * 2 + 1] * fac;
+          o += sm_o[((size_t)ww * MR + pr) * kScratchStride + col] * fac;
+        }
+        if (c.slot < 0) {
+          const float inv = l > 0.f ? 1.0f / l : 0.f;
+          out[((size_t)(c.q_start + row / group) * q_heads + c.kvh * group + row % group) * D + col] = __float2bfloat16_rn(o * inv);
+        } else {
+          const size_t prow = ((size_t)c.slot * kv_heads + c.kvh) * 16 + row;
+          part_o[prow * D + col] = o;
+          if (col == 0) {
+            part_ml[prow * 2] = m;
+            part_ml[prow * 2 + 1] = l;
+          }
+        }
+      }
+      asm volatile("bar.sync 1, %0;\n" ::"n"(NW * 32) : "memory");  // the scratch (and the Q tile) may be written again
+    }
+  }
+  if (!ok) {  // a copy that was waited for in vain may still land
+    const long long c0 = clock64();
+    while (clock64() - c0 < 2000000LL) __nanosleep(256);
+  }
+}
+
 // merge_work[i] = (batch row, first partial slot, number of chunks)
 template <int D>
 __global__ void attention_merge_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                        const int32_t* __restrict__ q_indptr, const int4* __restrict__ merge_work, int q_heads,
                                        int kv_heads) {
-  pdl_launch_dependents();
-  pdl_wait();
+  pdl_launch_dependents(5);
+  pdl_wait(5);
   const int4 w = merge_work[blockIdx.x];
   const int b = w.x, slot0 = w.y, chunks = w.z;
   if (b < 0) return;  // padding of a fixed-size work list
@@ -487,12 +940,17 @@ static int page_shift_of(int page_size) {
   return s;
 }
 
-template <int D>
+// A prefill warp carries one or two row tiles of 16. Two halve the shared-memory traffic per product, which pays once the
+// grid fills the device several times over; with less work the smaller tiles spread it over more SMs. Both compute a row
+// with the same operations in the same order, so the choice does not show in the result.
+constexpr int kPrefillWideMinRows = 65536;  // packed rows x key/value heads from which 128-row tiles are used
+
+template <int D, int MT>
 static int launch_prefill(const void* q, void* out, const void* k_pool, const void* v_pool, const int32_t* q_indptr, const int32_t* kv_lens,
                           const int32_t* kv_indptr, const int32_t* kv_indices, const int32_t* work, int items, int q_heads, int kv_heads,
                           int page_size, float scale, int window, cudaStream_t s) {
-  const size_t smem = (size_t)(64 + 4 * 64) * D * 2;
-  auto kernel = attention_prefill_kernel<D>;
+  const size_t smem = (size_t)(64 * MT + 4 * 64) * D * 2;
+  auto kernel = attention_prefill_kernel<D, MT>;
   static bool attr_set = false;  // once per process: nothing but launches happens on later calls (stream capture)
   if (smem > 48 * 1024 && !attr_set) {
     cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -504,23 +962,91 @@ static int launch_prefill(const void* q, void* out, const void* k_pool, const vo
   return check_launch("attention_prefill");
 }
 
+static bool g_decode_tma = true;
+
+// Whether the copy-engine decode kernel serves these sizes: head sizes whose rows are whole 128-byte swizzle spans, pages
+// of 16, 32, 64, ... rows (a power of two), keys and values in one allocation (the values after the keys, so that one
+// tensor map covers both), a pool whose rows fit a tensor map.
+static bool decode_tma_serves(int head_dim, int page_size, long long pool_pages, int kv_heads, const void* k_pool, const void* v_pool) {
+  if (!g_decode_tma || pool_pages <= 0 || (head_dim != 64 && head_dim != 128)) return false;
+  if (page_size < 16 || (page_size & (page_size - 1)) != 0) return false;
+  if (pool_pages * kv_heads * page_size >= (1LL << 31)) return false;
+  const long long pool_bytes = pool_pages * kv_heads * page_size * head_dim * 2;
+  const long long gap = (const char*)v_pool - (const char*)k_pool;
+  if (gap < pool_bytes || gap % 16 != 0 || gap >= (1LL << 40)) return false;
+  return (uintptr_t)k_pool % 128 == 0 && encode_tiled() != nullptr;
+}
+
+// Both pools [pages, kv_heads, page_size, D] as one tensor: 64 columns x pool rows x D / 64 column blocks x {keys, values},
+// in boxes of one page's (or 32) rows of both.
+static int make_pool_map(CUtensorMap* map, const void* k_pool, const void* v_pool, long long rows, int head_dim, int box_rows) {
+  const cuuint64_t dims[4] = {64u, (cuuint64_t)rows, (cuuint64_t)head_dim / 64, 2u};
+  const cuuint64_t strides[3] = {(cuuint64_t)head_dim * 2, 128u, (cuuint64_t)((const char*)v_pool - (const char*)k_pool)};
+  const cuuint32_t box[4] = {64u, (cuuint32_t)box_rows, (cuuint32_t)head_dim / 64, 2u};
+  const cuuint32_t elem[4] = {1, 1, 1, 1};
+  const CUresult r = encode_tiled()(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(k_pool), dims, strides, box, elem,
+                                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(ROOST_ERR_CUDA, "attention_decode: cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
+  return ROOST_OK;
+}
+
+template <int D>
+static int launch_decode_tma(const void* q, void* out, const void* k_pool, const void* v_pool, const int32_t* q_indptr, const int32_t* kv_lens,
+                             const int32_t* kv_indptr, const int32_t* kv_indices, const int32_t* work, int items, float* part_o,
+                             float* part_ml, int q_heads, int kv_heads, int page_size, long long pool_pages, float scale, int window,
+                             cudaStream_t s) {
+  CUtensorMap map;
+  const int box_rows = page_size < kTmaTileKeys ? page_size : kTmaTileKeys;
+  const int rc = make_pool_map(&map, k_pool, v_pool, pool_pages * kv_heads * page_size, D, box_rows);
+  if (rc != ROOST_OK) return rc;
+  constexpr size_t smem = (size_t)tma_decode_stages<D>() * 2 * kTmaTileKeys * D * 2 + 16 * D * 2 +
+                          (size_t)kTmaConsumers * kTmaMergeRows * (D + 8 + 2) * 4 + 1024;
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    cudaFuncSetAttribute(attention_decode_tma_kernel<D, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaFuncSetAttribute(attention_decode_tma_kernel<D, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  }
+  const long long total = (long long)items * kv_heads;
+  const int grid = (int)(total < 2LL * sms ? total : 2LL * sms);  // two CTAs fit an SM
+  auto kernel = box_rows == 16 ? attention_decode_tma_kernel<D, 16> : attention_decode_tma_kernel<D, 32>;
+  launch_kernel(kernel, dim3(grid), dim3((kTmaConsumers + 1) * 32), smem, s, map, (const __nv_bfloat16*)q, (__nv_bfloat16*)out, q_indptr,
+                kv_lens, kv_indptr, kv_indices, (const int4*)work, items, part_o, part_ml, q_heads, kv_heads, page_size, scale * kLog2e,
+                window);
+  return check_launch("attention_decode_tma");
+}
+
 template <int D>
 static int launch_decode(const void* q, void* out, const void* k_pool, const void* v_pool, const int32_t* q_indptr, const int32_t* kv_lens,
                          const int32_t* kv_indptr, const int32_t* kv_indices, const int32_t* work, int items, const int32_t* merge_work,
-                         int merge_items, float* part_o, float* part_ml, int q_heads, int kv_heads, int page_size, float scale, int window,
-                         cudaStream_t s) {
-  constexpr int NW = 4;
-  const size_t smem = (size_t)16 * D * 2 + (size_t)NW * kDecodeStages * 2 * kDecodeTileKeys * D * 2;
-  auto kernel = attention_decode_kernel<D, NW>;
-  static bool attr_set = false;
-  if (smem > 48 * 1024 && !attr_set) {
-    cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    attr_set = true;
+                         int merge_items, float* part_o, float* part_ml, int q_heads, int kv_heads, int page_size, long long pool_pages,
+                         float scale, int window, cudaStream_t s) {
+  int rc = ROOST_OK;
+  bool launched = false;
+  if constexpr (D == 64 || D == 128) {
+    if (decode_tma_serves(D, page_size, pool_pages, kv_heads, k_pool, v_pool)) {
+      rc = launch_decode_tma<D>(q, out, k_pool, v_pool, q_indptr, kv_lens, kv_indptr, kv_indices, work, items, part_o, part_ml, q_heads,
+                                kv_heads, page_size, pool_pages, scale, window, s);
+      launched = true;
+    }
   }
-  launch_kernel(kernel, dim3(items, kv_heads), dim3(NW * 32), smem, s, (const __nv_bfloat16*)q, (__nv_bfloat16*)out,
-                (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, q_indptr, kv_lens, kv_indptr, kv_indices, (const int4*)work, part_o,
-                part_ml, q_heads, kv_heads, page_size, page_shift_of(page_size), scale * kLog2e, window);
-  int rc = check_launch("attention_decode");
+  if (!launched) {
+    constexpr int NW = 4;
+    const size_t smem = (size_t)16 * D * 2 + (size_t)NW * kDecodeStages * 2 * kDecodeTileKeys * D * 2;
+    auto kernel = attention_decode_kernel<D, NW>;
+    static bool attr_set = false;
+    if (smem > 48 * 1024 && !attr_set) {
+      cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      attr_set = true;
+    }
+    launch_kernel(kernel, dim3(items, kv_heads), dim3(NW * 32), smem, s, (const __nv_bfloat16*)q, (__nv_bfloat16*)out,
+                  (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, q_indptr, kv_lens, kv_indptr, kv_indices, (const int4*)work, part_o,
+                  part_ml, q_heads, kv_heads, page_size, page_shift_of(page_size), scale * kLog2e, window);
+    rc = check_launch("attention_decode");
+  }
   if (rc != ROOST_OK || merge_items == 0) return rc;
   launch_kernel(attention_merge_kernel<D>, dim3(merge_items, kv_heads, 16), dim3(D < 128 ? D : 128), 0, s, (__nv_bfloat16*)out,
                 (const float*)part_o, (const float*)part_ml, q_indptr, (const int4*)merge_work, q_heads, kv_heads);
@@ -541,27 +1067,60 @@ using namespace roost;
     default: return fail(ROOST_ERR_UNSUPPORTED, "attention_mma: head_dim is not one of 16, 32, 64, 128, 256"); \
   }
 
+// Packed rows of one prefill work item, for a head size the tensor-core kernels serve and a step that brings
+// `packed_rows` packed rows (tokens x query heads per key/value head) in all to the prefill kernel.
+extern "C" int roost_attention_prefill_tile_rows(int head_dim, long long packed_rows, int kv_heads) {
+  if (!roost_attention_mma_supported(head_dim)) return 0;
+  return head_dim <= 128 && packed_rows * kv_heads >= kPrefillWideMinRows ? 128 : 64;
+}
+
+// 1: decode rows stream keys and values through the copy engine where the sizes allow (the default); 0: always cp.async.
+extern "C" void roost_attention_set_decode_tma(int on) { g_decode_tma = on != 0; }
+
+// 0, or the code of the first wait a decode kernel gave up since the last call (1, 3: a free stage; 2: a tile's copies;
+// 4, 5: the chunk descriptors).
+extern "C" int roost_attention_status(void) {
+  int code = 0;
+  if (cudaMemcpyFromSymbol(&code, g_attention_error, sizeof(int)) != cudaSuccess) return -1;
+  if (code != 0) {
+    const int zero = 0;
+    cudaMemcpyToSymbol(g_attention_error, &zero, sizeof(int));
+  }
+  return code;
+}
+
 extern "C" int roost_attention_mma_supported(int head_dim) {
   return head_dim == 16 || head_dim == 32 || head_dim == 64 || head_dim == 128 || head_dim == 256;
 }
 
 extern "C" int roost_attention_prefill(const void* q, void* out, const void* k_pool, const void* v_pool, const int32_t* q_indptr,
                                        const int32_t* kv_lens, const int32_t* kv_indptr, const int32_t* kv_indices,
-                                       const int32_t* work, int items, int q_heads, int kv_heads, int head_dim, int page_size,
-                                       float scale, int window, roost_stream_t stream) {
+                                       const int32_t* work, int items, int tile_rows, int q_heads, int kv_heads, int head_dim,
+                                       int page_size, float scale, int window, roost_stream_t stream) {
   ROOST_REQUIRE(items >= 0 && q_heads > 0 && kv_heads > 0 && page_size > 0, "attention_prefill: sizes must be positive");
+  ROOST_REQUIRE(tile_rows == 64 || (tile_rows == 128 && head_dim <= 128), "attention_prefill: a work item has 64 packed rows, or 128 up to head size 128");
   ROOST_REQUIRE(q_heads % kv_heads == 0, "attention_prefill: q_heads must be a multiple of kv_heads");
   if (kv_heads > 65535) return fail(ROOST_ERR_UNSUPPORTED, "attention_prefill: more than 65535 key/value heads");
   if (items == 0) return ROOST_OK;
-  ROOST_DISPATCH_HEAD_DIM(head_dim, D, return launch_prefill<D>(q, out, k_pool, v_pool, q_indptr, kv_lens, kv_indptr, kv_indices, work, items,
-                                                                 q_heads, kv_heads, page_size, scale, window, (cudaStream_t)stream));
+  if (tile_rows == 128) {
+    switch (head_dim) {
+      case 16: return launch_prefill<16, 2>(q, out, k_pool, v_pool, q_indptr, kv_lens, kv_indptr, kv_indices, work, items, q_heads, kv_heads, page_size, scale, window, (cudaStream_t)stream);
+      case 32: return launch_prefill<32, 2>(q, out, k_pool, v_pool, q_indptr, kv_lens, kv_indptr, kv_indices, work, items, q_heads, kv_heads, page_size, scale, window, (cudaStream_t)stream);
+      case 64: return launch_prefill<64, 2>(q, out, k_pool, v_pool, q_indptr, kv_lens, kv_indptr, kv_indices, work, items, q_heads, kv_heads, page_size, scale, window, (cudaStream_t)stream);
+      case 128: return launch_prefill<128, 2>(q, out, k_pool, v_pool, q_indptr, kv_lens, kv_indptr, kv_indices, work, items, q_heads, kv_heads, page_size, scale, window, (cudaStream_t)stream);
+      default: return fail(ROOST_ERR_UNSUPPORTED, "attention_prefill: no tensor-core kernel for this head size");
+    }
+  }
+  ROOST_DISPATCH_HEAD_DIM(head_dim, D, return launch_prefill<D, 1>(q, out, k_pool, v_pool, q_indptr, kv_lens, kv_indptr, kv_indices, work, items,
+                                                                    q_heads, kv_heads, page_size, scale, window, (cudaStream_t)stream));
   return ROOST_OK;
 }
 
 extern "C" int roost_attention_decode(const void* q, void* out, const void* k_pool, const void* v_pool, const int32_t* q_indptr,
                                       const int32_t* kv_lens, const int32_t* kv_indptr, const int32_t* kv_indices, const int32_t* work,
                                       int items, const int32_t* merge_work, int merge_items, float* part_o, float* part_ml, int q_heads,
-                                      int kv_heads, int head_dim, int page_size, float scale, int window, roost_stream_t stream) {
+                                      int kv_heads, int head_dim, int page_size, long long pool_pages, float scale, int window,
+                                      roost_stream_t stream) {
   ROOST_REQUIRE(items >= 0 && merge_items >= 0 && q_heads > 0 && kv_heads > 0 && page_size > 0, "attention_decode: sizes must be positive");
   ROOST_REQUIRE(q_heads % kv_heads == 0, "attention_decode: q_heads must be a multiple of kv_heads");
   ROOST_REQUIRE(merge_items == 0 || (part_o && part_ml && merge_work), "attention_decode: the workspace for split rows is missing");
@@ -569,7 +1128,7 @@ extern "C" int roost_attention_decode(const void* q, void* out, const void* k_po
   if (items == 0) return ROOST_OK;
   ROOST_DISPATCH_HEAD_DIM(head_dim, D, return launch_decode<D>(q, out, k_pool, v_pool, q_indptr, kv_lens, kv_indptr, kv_indices, work, items,
                                                                 merge_work, merge_items, part_o, part_ml, q_heads, kv_heads, page_size,
-                                                                scale, window, (cudaStream_t)stream));
+                                                                pool_pages, scale, window, (cudaStream_t)stream));
   return ROOST_OK;
 }
 
@@ -641,6 +1200,9 @@ extern "C" int roost_attention_decode_static(const void* q, void* out, const voi
   // behind is never read.
   ROOST_DISPATCH_HEAD_DIM(head_dim, D, return launch_decode<D>(q, out, k_pool, v_pool, q_indptr, kv_lens, kv_indptr, kv_indices, work, items,
                                                                 merge_work, merge_items, scratch, scratch + o_padded, q_heads, kv_heads,
-                                                                page_size, scale, window, (cudaStream_t)stream));
+                                                                page_size, /*pool_pages unknown: the cp.async kernel*/ 0, scale, window,
+                                                                (cudaStream_t)stream));
   return ROOST_OK;
 }
+
+ROOST_TRACE_TU(attention_mma)

@@ -118,8 +118,8 @@ __global__ void rms_norm_vec_kernel(const T* __restrict__ x, T* residual, const 
                                     const int32_t* __restrict__ rows, int hidden, float eps, int wdtype) {
   constexpr int N = Vec<T>::N;
   __shared__ float scratch[32];
-  pdl_launch_dependents();
-  pdl_wait();
+  pdl_launch_dependents(1);
+  pdl_wait(1);
   const int i_out = blockIdx.x;
   const size_t r = rows ? (size_t)rows[i_out] : (size_t)i_out;
   const int nvec = hidden / N;
@@ -161,8 +161,8 @@ __global__ void silu_mul_vec_kernel(const T* __restrict__ x, T* __restrict__ out
   constexpr int N = Vec<T>::N;
   const size_t t = blockIdx.x;
   const int vi = blockIdx.y * blockDim.x + threadIdx.x;
-  pdl_launch_dependents();
-  pdl_wait();
+  pdl_launch_dependents(2);
+  pdl_wait(2);
   if (vi * N >= inter) return;
   float g[N], u[N], o[N];
   const int j = vi * N;
@@ -259,3 +259,5 @@ extern "C" int roost_silu_mul(const void* x, void* out, int tokens, int inter, i
   ROOST_DISPATCH_DTYPE(dtype, T, launch_kernel(silu_mul_kernel<T>, grid, dim3(256), 0, (cudaStream_t)stream, (const T*)x, (T*)out, inter, block));
   return check_launch("silu_mul");
 }
+
+ROOST_TRACE_TU(elementwise)

@@ -15,13 +15,10 @@
 // Every wait on a barrier is bounded: a wait that does not complete within about a tenth of a second raises an abort
 // flag that every role polls, the kernel records an error code, lets copies in flight land, frees its tensor memory and
 // returns. roost_gemm_tcgen05_status() reads the code back.
-#include <cuda.h>
-
 #include <map>
-#include <mutex>
 #include <tuple>
 
-#include "common.cuh"
+#include "tma.cuh"
 
 namespace roost {
 
@@ -31,59 +28,13 @@ constexpr uint32_t kStageABytes = BM * BK * 2;
 constexpr uint32_t kStageBBytes = BN * BK * 2;
 constexpr uint32_t kStageBytes = kStageABytes + kStageBBytes;
 constexpr uint32_t kTmemCols = 512;  // two accumulators of BN columns
-constexpr long long kWaitCycles = 400000000LL;
 
 __device__ int g_gemm_tcgen05_error = 0;
 
 // ------------------------------------------------------------------------------------------------ PTX wrappers
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n.reg .pred p;\nmbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// Waits for the barrier's phase with the given parity. Returns false when the wait was given up: another role raised
-// the abort flag, or the time limit passed (then this call raises it and records `code`).
 template <bool CLUSTER = false>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
-  auto try_wait = [&]() { return CLUSTER ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity); };
-  if (try_wait()) return true;
-  const long long t0 = clock64();
-  while (true) {
-    if (try_wait()) return true;
-    if (*abort_flag) return false;
-    if (clock64() - t0 > kWaitCycles) {
-      *abort_flag = 1;
-      atomicCAS(&g_gemm_tcgen05_error, 0, code);
-      return false;
-    }
-  }
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c_inner, int c_outer) {
-  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n" ::"r"(dst),
-               "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c_inner), "r"(c_outer)
-               : "memory");
+  return mbar_wait_limited<CLUSTER>(bar, parity, abort_flag, code, &g_gemm_tcgen05_error);
 }
 // The pair form: the barrier may live in the other CTA of the pair (a shared::cluster address).
 __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t cluster_bar, int c_inner, int c_outer) {
@@ -595,14 +546,14 @@ __global__ void __launch_bounds__(192, 1)
     // the first stages are free by construction: the loads of w start now (no kernel writes the weights), while tensor
     // memory is still being allocated and, under programmatic dependent launch, while the kernel that produces x is still
     // running; the loads of x follow once that kernel has finished
-    pdl_launch_dependents();
+    pdl_launch_dependents(6);
     for (long long u = u0; u < u1 && prologue < STAGES_S; ++u, ++prologue) {
       const int t = (int)(u / kbs), kb = (int)(u % kbs);
       const uint32_t sw = smem_base + prologue * kStageSBytes;
       mbar_expect_tx(full_bar(prologue), kStageSWBytes + (uint32_t)ntok * BK * 2);
       tma_load_2d(sw, &tma_w, full_bar(prologue), kb * BK, t * 128);
     }
-    pdl_wait();
+    pdl_wait(6);
     for (int i = 0; i < prologue; ++i) {
       const int kb = (int)((u0 + i) % kbs);
       tma_load_2d(smem_base + i * kStageSBytes + kStageSWBytes, &tma_x, full_bar(i), kb * BK, 0);
@@ -754,6 +705,7 @@ __global__ void __launch_bounds__(192, 1)
     }
   }
 
+  trace_point(6, 2);
   __syncwarp();
   if (*abortp) {
     const long long t0 = clock64();
@@ -768,23 +720,6 @@ __global__ void __launch_bounds__(192, 1)
 }
 
 // ------------------------------------------------------------------------------------------------ host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_tiled() {
-  static EncodeTiledFn fn = nullptr;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess) {
-      fn = reinterpret_cast<EncodeTiledFn>(p);
-    }
-  });
-  return fn;
-}
-
 // A [rows, k] bfloat16 matrix with row stride ld elements as a 2-D tensor map with boxes of box_rows x 64 elements.
 static int make_map(CUtensorMap* map, const void* base, int rows, int k, int64_t ld, int box_rows) {
   EncodeTiledFn enc = encode_tiled();
@@ -952,3 +887,5 @@ extern "C" int roost_gemm_stream(const void* x, const void* w, void* out, int m,
   if (out_dtype == ROOST_BF16) return launch_stream<__nv_bfloat16>(mw, mx, out, m, n, k, ldo, ntok, ws, flags, (cudaStream_t)stream);
   return launch_stream<float>(mw, mx, out, m, n, k, ldo, ntok, ws, flags, (cudaStream_t)stream);
 }
+
+ROOST_TRACE_TU(gemm_tcgen05)

@@ -17,7 +17,7 @@
 extern "C" {
 #endif
 
-#define ROOST_ABI_VERSION 2
+#define ROOST_ABI_VERSION 3
 
 #define ROOST_OK 0
 #define ROOST_ERR_INVALID 1      /* an argument is out of range or inconsistent; nothing was launched */
@@ -76,19 +76,29 @@ int roost_paged_attention_generic(const void* q, void* out, const void* k_pool, 
 
 /* Tensor-core attention for bfloat16 (attention_mma.cu). head_dim must be one roost_attention_mma_supported accepts.
  * q_indptr[b] .. q_indptr[b+1] are row b's tokens, kv_lens[b] its keys after this step.
- * prefill work: int32 pairs (batch row, first packed row of a 64-row tile), packed row = token * group + head.
+ * prefill work: int32 pairs (batch row, first packed row of a tile of tile_rows rows; roost_attention_prefill_tile_rows picks 64 or 128),
+ * packed row = token * group + head.
  * decode work: int32 quadruples (batch row, first key, one past the last key, partial slot or -1); rows with at most
- * 16 packed rows only. merge_work: quadruples (batch row, first slot, chunks, 0) for rows split into several chunks.
- * part_o: float[slots * kv_heads * 16 * head_dim], part_ml: float[slots * kv_heads * 16 * 2]. */
+ * 16 packed rows only; the first key of an item is a multiple of 64. merge_work: quadruples (batch row, first slot, chunks, 0) for rows split into several chunks.
+ * part_o: float[slots * kv_heads * 16 * head_dim], part_ml: float[slots * kv_heads * 16 * 2].
+ * pool_pages: pages of k_pool and v_pool; with head size 64 or 128, pages of 8, 16 or a multiple of 32 rows and pools
+ * on 128-byte boundaries, decode streams keys and values through the copy engine (TMA) unless
+ * roost_attention_set_decode_tma(0) was called; 0 when not known (the cp.async kernel runs). It copies whole pages:
+ * every slot of a page a block table names must be readable, whatever it holds.
+ * roost_attention_status(): 0, or the code of a wait the copy-engine kernel gave up (read and cleared). */
 int roost_attention_mma_supported(int head_dim);
+int roost_attention_prefill_tile_rows(int head_dim, long long packed_rows, int kv_heads);
 int roost_attention_prefill(const void* q, void* out, const void* k_pool, const void* v_pool, const int32_t* q_indptr,
                             const int32_t* kv_lens, const int32_t* kv_indptr, const int32_t* kv_indices, const int32_t* work,
-                            int items, int q_heads, int kv_heads, int head_dim, int page_size, float scale, int window,
-                            roost_stream_t stream);
+                            int items, int tile_rows, int q_heads, int kv_heads, int head_dim, int page_size, float scale,
+                            int window, roost_stream_t stream);
 int roost_attention_decode(const void* q, void* out, const void* k_pool, const void* v_pool, const int32_t* q_indptr,
                            const int32_t* kv_lens, const int32_t* kv_indptr, const int32_t* kv_indices, const int32_t* work,
                            int items, const int32_t* merge_work, int merge_items, float* part_o, float* part_ml, int q_heads,
-                           int kv_heads, int head_dim, int page_size, float scale, int window, roost_stream_t stream);
+                           int kv_heads, int head_dim, int page_size, long long pool_pages, float scale, int window,
+                           roost_stream_t stream);
+void roost_attention_set_decode_tma(int on);
+int roost_attention_status(void);
 
 /* The split decode attention without a workspace argument. It has no counterpart in the reference: it exists for
  * callers that must not allocate device memory while they run (a host that gave the whole GPU to its own arena at

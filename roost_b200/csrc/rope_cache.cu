@@ -35,8 +35,8 @@ __global__ void qk_norm_rope_cache_kernel(const T* __restrict__ qkv, int64_t qkv
                                           int64_t pool_pages, int slots_per_token, int wdtype, bool vector_ok) {
   const int lane = threadIdx.x & 31;
   const int slot_idx = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  pdl_launch_dependents();
-  pdl_wait();
+  pdl_launch_dependents(3);
+  pdl_wait(3);
   if (slot_idx >= slots_per_token) return;
   const size_t t = blockIdx.x;
   const T* row = qkv + t * qkv_stride;
@@ -168,3 +168,5 @@ extern "C" int roost_qk_norm_rope_cache(const void* qkv, int64_t qkv_stride, voi
                            slot_mapping, q_heads, kv_heads, head_dim, rotary_dim, eps, page_size, pool_pages, slots, wdtype, vector_ok));
   return check_launch("qk_norm_rope_cache");
 }
+
+ROOST_TRACE_TU(rope_cache)

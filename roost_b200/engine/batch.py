@@ -34,9 +34,10 @@ class GroupTables:
 class AttentionPlan:
     """How the tensor-core attention kernels divide a step's rows (see csrc/attention_mma.cu): rows with at most 16
     packed rows (tokens x query heads per key/value head) go to the decode kernel in chunks of a fixed number of
-    keys, the others to the prefill kernel in tiles of 64 packed rows. Item counts may include padding entries
-    (batch row -1), which the kernels skip."""
+    keys, the others to the prefill kernel in tiles of ``prefill_tile_rows`` packed rows. Item counts may include
+    padding entries (batch row -1), which the kernels skip."""
     prefill_items: int = 0
+    prefill_tile_rows: int = 64
     decode_items: int = 0
     merge_items: int = 0
     slots: int = 0
@@ -45,8 +46,11 @@ class AttentionPlan:
     merge_work: torch.Tensor | None = None
 
 
-def attention_work(row_starts, row_counts, group: int, window: int | None, chunk: int):
-    """(prefill pairs, decode quadruples, merge quadruples, slots) as flat int lists."""
+def attention_work(row_starts, row_counts, group: int, window: int | None, chunk: int, tile_rows: int = 64):
+    """(prefill pairs, decode quadruples, merge quadruples, slots) as flat int lists. ``chunk`` is a multiple of 64: a
+    chunk starts on a boundary of the decode kernels' key tiles."""
+    if chunk <= 0 or chunk % 64:
+        raise ValueError(f"decode chunk {chunk} is not a positive multiple of 64")
     prefill, decode, merge, tiles = [], [], [], []
     slots = 0
     for b, (start, n) in enumerate(zip(row_starts, row_counts)):
@@ -63,18 +67,18 @@ def attention_work(row_starts, row_counts, group: int, window: int | None, chunk
                     decode += [b, c, min(c + chunk, kv_len), slots]
                     slots += 1
         else:
-            for r0 in range(0, rows, 64):
-                tiles.append((start + min(rows, r0 + 64) // group, b, r0))
+            for r0 in range(0, rows, tile_rows):
+                tiles.append((start + min(rows, r0 + tile_rows) // group, b, r0))
     # the tiles with the longest history run longest: they go first, so that the last wave of CTAs is the lightest
     for _, b, r0 in sorted(tiles, key=lambda t: -t[0]):
         prefill += [b, r0]
     return prefill, decode, merge, slots
 
 
-def attention_caps(num_rows: int, kv_cap: int, group: int, chunk: int) -> tuple[int, int, int]:
+def attention_caps(num_rows: int, kv_cap: int, group: int, chunk: int, tile_rows: int = 64) -> tuple[int, int, int]:
     """Largest item counts of a decode step (one token a row) whose requests hold at most ``kv_cap`` keys."""
     if group > 16:
-        return num_rows * (-(-group // 64)), 0, 0
+        return num_rows * (-(-group // tile_rows)), 0, 0
     return 0, num_rows * (-(-kv_cap // chunk)), num_rows
 
 
@@ -82,9 +86,9 @@ def _pad4(a: list) -> list:
     return a + [0] * (-len(a) % 4)
 
 
-def plan_attention(row_starts, row_counts, group: int, window: int | None, chunk: int, device) -> AttentionPlan:
-    prefill, decode, merge, slots = attention_work(row_starts, row_counts, group, window, chunk)
-    plan = AttentionPlan(prefill_items=len(prefill) // 2, decode_items=len(decode) // 4, merge_items=len(merge) // 4, slots=slots)
+def plan_attention(row_starts, row_counts, group: int, window: int | None, chunk: int, device, tile_rows: int = 64) -> AttentionPlan:
+    prefill, decode, merge, slots = attention_work(row_starts, row_counts, group, window, chunk, tile_rows)
+    plan = AttentionPlan(prefill_items=len(prefill) // 2, prefill_tile_rows=tile_rows, decode_items=len(decode) // 4, merge_items=len(merge) // 4, slots=slots)
     flat = _pad4(prefill) + _pad4(decode) + _pad4(merge)
     if flat:
         host = torch.tensor(flat, dtype=torch.int32)
@@ -119,11 +123,11 @@ class StepBatch:
     host_buffer: object = None   # the pinned staging buffer, kept until the step is done
     attention_plans: dict = field(default_factory=dict)   # (group size, window, chunk) -> AttentionPlan, made by the first mixer that asks
 
-    def attention_plan(self, group: int, window: int | None, chunk: int) -> AttentionPlan:
-        key = (group, window, chunk)
+    def attention_plan(self, group: int, window: int | None, chunk: int, tile_rows: int = 64) -> AttentionPlan:
+        key = (group, window, chunk, tile_rows)
         plan = self.attention_plans.get(key)
         if plan is None:
-            plan = plan_attention(self.row_starts, self.row_counts, group, window, chunk, self.ids.device)
+            plan = plan_attention(self.row_starts, self.row_counts, group, window, chunk, self.ids.device, tile_rows)
             self.attention_plans[key] = plan
         return plan
 

@@ -54,7 +54,7 @@ class DecodeGraph:
         builder = executor.builder
         table_caps = builder.table_caps(num_rows, kv_cap)
         self.n_table = len(table_caps)
-        self.plan_caps = [attention_caps(num_rows, kv_cap, g, chunk) for (g, _w, chunk) in self.plan_keys]
+        self.plan_caps = [attention_caps(num_rows, kv_cap, g, chunk, rows) for (g, _w, chunk, rows) in self.plan_keys]
         caps, fills = list(table_caps), [0] * len(table_caps)
         for pc, dc, mc in self.plan_caps:
             caps += [pc * 2, dc * 4, mc * 4]
@@ -66,8 +66,8 @@ class DecodeGraph:
 
     def _arrays(self, ht: HostTables) -> list:
         arrays = list(ht.arrays)
-        for (g, w, chunk) in self.plan_keys:
-            prefill, decode, merge, _ = attention_work(ht.row_starts, ht.row_counts, g, w, chunk)
+        for (g, w, chunk, rows) in self.plan_keys:
+            prefill, decode, merge, _ = attention_work(ht.row_starts, ht.row_counts, g, w, chunk, rows)
             arrays += [np.asarray(prefill, np.int32), np.asarray(decode, np.int32), np.asarray(merge, np.int32)]
         return arrays
 
@@ -89,7 +89,7 @@ class DecodeGraph:
         batch = ex.builder.static_batch(ht, self.static, self.n_table)
         views = self.static.views[self.n_table:]
         for i, (key, (pc, dc, mc)) in enumerate(zip(self.plan_keys, self.plan_caps)):
-            batch.attention_plans[key] = AttentionPlan(prefill_items=pc, decode_items=dc, merge_items=mc, slots=dc,
+            batch.attention_plans[key] = AttentionPlan(prefill_items=pc, prefill_tile_rows=key[3], decode_items=dc, merge_items=mc, slots=dc,
                                                        prefill_work=views[3 * i], decode_work=views[3 * i + 1],
                                                        merge_work=views[3 * i + 2])
         # this step's result comes from an eager run on a side stream (which also warms every kernel and library up);

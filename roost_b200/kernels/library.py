@@ -13,7 +13,7 @@ import torch
 
 from . import build
 
-ABI_VERSION = 2
+ABI_VERSION = 3
 F32, BF16 = 0, 1
 
 
@@ -58,16 +58,19 @@ _SIGNATURES = {
     "roost_paged_attention_generic": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                       c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p],
     "roost_attention_mma_supported": [c_int],
+    "roost_attention_prefill_tile_rows": [c_int, ctypes.c_longlong, c_int],
     "roost_attention_prefill": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
-                                c_int, c_int, c_int, c_float, c_int, c_void_p],
+                                c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
     "roost_attention_decode": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
-                               c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+                               c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, ctypes.c_longlong, c_float, c_int, c_void_p],
     "roost_gemm_simt": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int, c_int, c_void_p],
     "roost_gemm_skinny_supported": [c_int, c_int, c_int, c_int64, c_int64],
     "roost_gemm_skinny": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int, c_void_p],
     "roost_gemm_tcgen05_supported": [c_int, c_int, c_int, c_int64, c_int64],
     "roost_gemm_tcgen05": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int, c_void_p],
     "roost_gemm_tcgen05_status": [],
+    "roost_attention_status": [],
+    "roost_attention_set_decode_tma": [c_int],
     "roost_gemm_stream_workspace_floats": [],
     "roost_gemm_stream_workspace_flags": [],
     "roost_gemm_stream_supported": [c_int, c_int, c_int, c_int64, c_int64],
@@ -197,6 +200,10 @@ class KernelLibrary:
     def attention_mma_supported(self, head_dim: int) -> bool:
         return bool(self._lib.roost_attention_mma_supported(int(head_dim)))
 
+    def attention_prefill_tile_rows(self, head_dim: int, packed_rows: int = 0, kv_heads: int = 1) -> int:
+        """Packed rows of a prefill work item for a step that brings ``packed_rows`` packed rows in all."""
+        return int(self._lib.roost_attention_prefill_tile_rows(int(head_dim), int(packed_rows), int(kv_heads)))
+
     def attention_mma(self, q, k_pool, v_pool, q_indptr, kv_lens, kv_indptr, kv_indices, plan, scale: float,
                       window: int | None) -> torch.Tensor:
         """Tensor-core attention (bfloat16). ``plan``: an ``AttentionPlan`` whose work lists are on the device."""
@@ -209,7 +216,7 @@ class KernelLibrary:
         w = int(window) if window else 0
         if plan.prefill_items:
             self._call("roost_attention_prefill", _ptr(q), _ptr(out), _ptr(k_pool), _ptr(v_pool), _ptr(q_indptr), _ptr(kv_lens),
-                       _ptr(kv_indptr), _ptr(kv_indices), _ptr(plan.prefill_work), plan.prefill_items, nq, nkv, d, page, scale, w,
+                       _ptr(kv_indptr), _ptr(kv_indices), _ptr(plan.prefill_work), plan.prefill_items, plan.prefill_tile_rows, nq, nkv, d, page, scale, w,
                        _stream())
         if plan.decode_items:
             part_o = part_ml = None
@@ -218,7 +225,7 @@ class KernelLibrary:
                 part_ml = torch.empty((plan.slots * nkv * 16 * 2,), dtype=torch.float32, device=q.device)
             self._call("roost_attention_decode", _ptr(q), _ptr(out), _ptr(k_pool), _ptr(v_pool), _ptr(q_indptr), _ptr(kv_lens),
                        _ptr(kv_indptr), _ptr(kv_indices), _ptr(plan.decode_work), plan.decode_items, _ptr(plan.merge_work),
-                       plan.merge_items, _ptr(part_o), _ptr(part_ml), nq, nkv, d, page, scale, w, _stream(),
+                       plan.merge_items, _ptr(part_o), _ptr(part_ml), nq, nkv, d, page, k_pool.shape[0], scale, w, _stream(),
                        launches=2 if plan.merge_items else 1)
         return out
 
@@ -292,6 +299,21 @@ class KernelLibrary:
         self._call("roost_gemm_stream", _ptr(x), _ptr(w), _ptr(out), M, N, K, x.stride(0), w.stride(0), out.stride(0),
                    dtype_code(out_dtype), _ptr(ws[0]), _ptr(ws[1]), _stream())
         return out
+
+    def attention_set_decode_tma(self, on: bool) -> None:
+        """Decode rows stream keys and values through the copy engine where the sizes allow (the default), or never."""
+        self._lib.roost_attention_set_decode_tma(1 if on else 0)
+
+    def attention_status(self) -> int:
+        """The code of a bounded wait the copy-engine decode kernel gave up since the last call (0: none); synchronises."""
+        return int(self._lib.roost_attention_status())
+
+    def check_device_status(self) -> None:
+        """Raises when a kernel gave up one of its bounded waits since the last call (its results are then not valid)."""
+        gemm, attn = self.gemm_tcgen05_status(), self.attention_status()
+        if gemm or attn:
+            raise KernelError(f"a kernel gave up a bounded wait (tcgen05 product: code {gemm}, decode attention: code {attn}); "
+                              "the step's results are not valid")
 
     def gemm_tcgen05_set_pairs(self, on: bool) -> None:
         """Tiles on pairs of CTAs (cta_group::2, the default) or on single CTAs."""

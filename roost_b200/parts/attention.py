@@ -95,7 +95,9 @@ class PagedAttention(Mixer):
         run the 32-bit kernel, which takes any size."""
         s, k = self.spec, self.rt.kernels
         if q.dtype == torch.bfloat16 and getattr(k, "attention_mma_supported", lambda d: False)(s.head_dim):
-            plan = batch.attention_plan(s.num_heads // s.num_kv_heads, s.window, k.decode_chunk)
+            group = s.num_heads // s.num_kv_heads
+            tile_rows = k.attention_prefill_tile_rows(s.head_dim, batch.num_tokens * group, s.num_kv_heads)
+            plan = batch.attention_plan(group, s.window, k.decode_chunk, tile_rows)
             return k.attention_mma(q, cache.k_pool, cache.v_pool, batch.q_indptr, batch.kv_lens, tables.kv_indptr,
                                    tables.kv_indices, plan, s.scale, s.window)
         return k.paged_attention_generic(q, cache.k_pool, cache.v_pool, batch.positions, batch.token_row,

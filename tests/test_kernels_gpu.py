@@ -142,8 +142,8 @@ def build_paged(keys, values, page, dtype, num_pages, seed):
     """Scatters per-row keys and values into shuffled pages; unused slots hold NaN so that a read of a slot that is
     not the row's shows."""
     nkv, d = keys[0].shape[1:]
-    kp = torch.full((num_pages, nkv, page, d), float("nan"), dtype=dtype)
-    vp = torch.full((num_pages, nkv, page, d), float("nan"), dtype=dtype)
+    pool = torch.full((2, num_pages, nkv, page, d), float("nan"), dtype=dtype)   # keys then values, as the engine's cache holds them
+    kp, vp = pool[0], pool[1]
     order = torch.randperm(num_pages, generator=torch.Generator().manual_seed(seed)).tolist()
     indptr, indices = [0], []
     for k, v in zip(keys, values):
@@ -155,7 +155,8 @@ def build_paged(keys, values, page, dtype, num_pages, seed):
             kp[pg, :, : seg.stop - seg.start] = k[seg].transpose(0, 1).to(dtype)
             vp[pg, :, : seg.stop - seg.start] = v[seg].transpose(0, 1).to(dtype)
         indptr.append(len(indices))
-    return kp.cuda(), vp.cuda(), torch.tensor(indptr, dtype=torch.int32).cuda(), torch.tensor(indices, dtype=torch.int32).cuda()
+    pool = pool.cuda()
+    return pool[0], pool[1], torch.tensor(indptr, dtype=torch.int32).cuda(), torch.tensor(indices, dtype=torch.int32).cuda()
 
 
 ATTN_SHAPES = [(4, 2, 16, 16), (6, 1, 32, 8), (8, 2, 128, 16), (5, 5, 48, 4), (14, 2, 64, 32), (3, 1, 80, 16), (2, 1, 256, 16)]
@@ -273,11 +274,12 @@ def test_sampler_matches_the_plain_sampler(kernels, vocab):
 
 
 # ------------------------------------------------------------------------------------------ tensor-core attention (bfloat16)
-def run_mma(kernels, q, kp, vp, lens, news, indptr, indices, scale, window, chunk=None):
+def run_mma(kernels, q, kp, vp, lens, news, indptr, indices, scale, window, chunk=None, tile_rows=None):
     from roost_b200.engine.batch import plan_attention
     nq, nkv = q.shape[1], kp.shape[1]
     starts = [n - m for n, m in zip(lens, news)]
-    plan = plan_attention(starts, news, nq // nkv, window, chunk or kernels.decode_chunk, "cuda")
+    plan = plan_attention(starts, news, nq // nkv, window, chunk or kernels.decode_chunk, "cuda",
+                          tile_rows or kernels.attention_prefill_tile_rows(q.shape[2]))
     q_indptr = torch.tensor([0] + list(torch.tensor(news).cumsum(0)), dtype=torch.int32).cuda()
     kv_lens = torch.tensor(lens, dtype=torch.int32).cuda()
     return kernels.attention_mma(q.cuda(), kp, vp, q_indptr, kv_lens, indptr, indices, plan, scale, window), plan
@@ -315,6 +317,20 @@ def test_attention_mma_mixed_rows(kernels, window, nq, nkv, d, page):
     generic = kernels.paged_attention_generic(q.cuda(), kp, vp, torch.tensor(positions, dtype=torch.int32).cuda(),
                                               torch.tensor(rows, dtype=torch.int32).cuda(), indptr, indices, scale, window)
     close(out, generic.double(), dtype, "attention_mma against the 32-bit kernel", scale=2)
+    # the decode rows again through the cp.async kernel (where the copy-engine kernel served them above)
+    kernels.attention_set_decode_tma(False)
+    try:
+        plain_copy, _ = run_mma(kernels, q, kp, vp, lens, news, indptr, indices, scale, window)
+    finally:
+        kernels.attention_set_decode_tma(True)
+    assert kernels.attention_status() == 0, "a bounded wait inside the decode kernel was given up"
+    assert not torch.isnan(plain_copy.float()).any()
+    close(plain_copy, want, dtype, f"attention_mma (cp.async decode) window={window}", scale=2)
+    if d <= 128:
+        # work items of 128 packed rows (two row tiles a warp) compute every row with the same operations in the same order
+        wide, wide_plan = run_mma(kernels, q, kp, vp, lens, news, indptr, indices, scale, window, tile_rows=128)
+        assert wide_plan.prefill_items < plan.prefill_items or nq // nkv * max(news) <= 64
+        assert torch.equal(wide, out), "64-row and 128-row prefill tiles differ"
 
 
 @pytest.mark.parametrize("case", ["far key", "first key", "page edge", "chunk edge", "window edge in", "window edge out"])

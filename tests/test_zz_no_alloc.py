@@ -46,11 +46,15 @@ def test_decode_attention_without_a_workspace_matches_the_one_with(kernels):
         q = (torch.randn(len(lens), nq, d, generator=g) * 1.5).to(dtype).cuda()
         kp, vp, indptr, indices = build_paged(keys, values, page, dtype, num_pages=sum(-(-n // page) for n in lens) + 3, seed=seed)
         starts = [n - 1 for n in lens]
-        plan = plan_attention(starts, news, nq // nkv, None, kernels.decode_chunk, "cuda")
+        plan = plan_attention(starts, news, nq // nkv, None, kernels.decode_chunk, "cuda", kernels.attention_prefill_tile_rows(d, 0, 1))
         assert plan.merge_items > 0 and plan.slots > 1
         q_indptr = torch.arange(len(lens) + 1, dtype=torch.int32).cuda()
         kv_lens = torch.tensor(lens, dtype=torch.int32).cuda()
-        want = kernels.attention_mma(q, kp, vp, q_indptr, kv_lens, indptr, indices, plan, scale, None)
+        kernels.attention_set_decode_tma(False)   # the static entry point runs the cp.async kernel: compare like with like
+        try:
+            want = kernels.attention_mma(q, kp, vp, q_indptr, kv_lens, indptr, indices, plan, scale, None)
+        finally:
+            kernels.attention_set_decode_tma(True)
         got = torch.full_like(want, float("nan"))
         rc = fn(_p(q), _p(got), _p(kp), _p(vp), _p(q_indptr), _p(kv_lens), _p(indptr), _p(indices), _p(plan.decode_work), plan.decode_items,
                 _p(plan.merge_work), plan.merge_items, plan.slots, nq, nkv, d, page, scale, 0, stream)
