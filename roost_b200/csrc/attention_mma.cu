@@ -897,39 +897,36 @@ __global__ void __launch_bounds__((kTmaConsumers + 1) * 32, 2)
   }
 }
 
-// merge_work[i] = (batch row, first partial slot, number of chunks)
+// merge_work[i] = (batch row, first partial slot, number of chunks | packed rows << 24, the row's first token)
 template <int D>
 __global__ void attention_merge_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                       const int32_t* __restrict__ q_indptr, const int4* __restrict__ merge_work, int q_heads,
-                                       int kv_heads) {
+                                       const int4* __restrict__ merge_work, int q_heads, int kv_heads) {
   pdl_launch_dependents(5);
   pdl_wait(5);
   const int4 w = merge_work[blockIdx.x];
-  const int b = w.x, slot0 = w.y, chunks = w.z;
+  const int b = w.x, slot0 = w.y, chunks = w.z & 0xffffff, rows_total = w.z >> 24, q_start = w.w;
   if (b < 0) return;  // padding of a fixed-size work list
   const int kvh = blockIdx.y;
-  const int row = blockIdx.z;
   const int group = q_heads / kv_heads;
-  const int q_start = q_indptr[b];
-  const int rows_total = (q_indptr[b + 1] - q_start) * group;
-  if (row >= rows_total) return;
-  const size_t pr0 = ((size_t)slot0 * kv_heads + kvh) * 16 + row;
   const size_t stride = (size_t)kv_heads * 16;  // partial rows from one chunk's slot to the next
-  float m = -INFINITY;
+  for (int row = blockIdx.z; row < rows_total; row += gridDim.z) {
+    const size_t pr0 = ((size_t)slot0 * kv_heads + kvh) * 16 + row;
+    float m = -INFINITY;
 #pragma unroll 8
-  for (int c = 0; c < chunks; ++c) m = fmaxf(m, part_ml[(pr0 + c * stride) * 2]);
-  const float msafe = m == -INFINITY ? 0.f : m;
-  for (int col = threadIdx.x; col < D; col += blockDim.x) {
-    float l = 0.f, o = 0.f;
+    for (int c = 0; c < chunks; ++c) m = fmaxf(m, part_ml[(pr0 + c * stride) * 2]);
+    const float msafe = m == -INFINITY ? 0.f : m;
+    for (int col = threadIdx.x; col < D; col += blockDim.x) {
+      float l = 0.f, o = 0.f;
 #pragma unroll 8
-    for (int c = 0; c < chunks; ++c) {  // chunk order: the sums do not depend on how the chunks were scheduled
-      const size_t pr = pr0 + c * stride;
-      const float f = exp2f(part_ml[pr * 2] - msafe);
-      l += part_ml[pr * 2 + 1] * f;
-      o += part_o[pr * D + col] * f;
+      for (int c = 0; c < chunks; ++c) {  // chunk order: the sums do not depend on how the chunks were scheduled
+        const size_t pr = pr0 + c * stride;
+        const float f = exp2f(part_ml[pr * 2] - msafe);
+        l += part_ml[pr * 2 + 1] * f;
+        o += part_o[pr * D + col] * f;
+      }
+      const float inv = l > 0.f ? 1.0f / l : 0.f;
+      out[((size_t)(q_start + row / group) * q_heads + kvh * group + row % group) * D + col] = __float2bfloat16_rn(o * inv);
     }
-    const float inv = l > 0.f ? 1.0f / l : 0.f;
-    out[((size_t)(q_start + row / group) * q_heads + kvh * group + row % group) * D + col] = __float2bfloat16_rn(o * inv);
   }
 }
 
@@ -1022,8 +1019,8 @@ static int launch_decode_tma(const void* q, void* out, const void* k_pool, const
 template <int D>
 static int launch_decode(const void* q, void* out, const void* k_pool, const void* v_pool, const int32_t* q_indptr, const int32_t* kv_lens,
                          const int32_t* kv_indptr, const int32_t* kv_indices, const int32_t* work, int items, const int32_t* merge_work,
-                         int merge_items, float* part_o, float* part_ml, int q_heads, int kv_heads, int page_size, long long pool_pages,
-                         float scale, int window, cudaStream_t s) {
+                         int merge_items, int merge_rows, float* part_o, float* part_ml, int q_heads, int kv_heads, int page_size,
+                         long long pool_pages, float scale, int window, cudaStream_t s) {
   int rc = ROOST_OK;
   bool launched = false;
   if constexpr (D == 64 || D == 128) {
@@ -1048,8 +1045,9 @@ static int launch_decode(const void* q, void* out, const void* k_pool, const voi
     rc = check_launch("attention_decode");
   }
   if (rc != ROOST_OK || merge_items == 0) return rc;
-  launch_kernel(attention_merge_kernel<D>, dim3(merge_items, kv_heads, 16), dim3(D < 128 ? D : 128), 0, s, (__nv_bfloat16*)out,
-                (const float*)part_o, (const float*)part_ml, q_indptr, (const int4*)merge_work, q_heads, kv_heads);
+  const int rows = merge_rows < 1 ? 1 : (merge_rows > 16 ? 16 : merge_rows);  // blocks along z; each walks the rows beyond
+  launch_kernel(attention_merge_kernel<D>, dim3(merge_items, kv_heads, rows), dim3(D < 128 ? D : 128), 0, s, (__nv_bfloat16*)out,
+                (const float*)part_o, (const float*)part_ml, (const int4*)merge_work, q_heads, kv_heads);
   return check_launch("attention_merge");
 }
 
@@ -1118,8 +1116,8 @@ extern "C" int roost_attention_prefill(const void* q, void* out, const void* k_p
 
 extern "C" int roost_attention_decode(const void* q, void* out, const void* k_pool, const void* v_pool, const int32_t* q_indptr,
                                       const int32_t* kv_lens, const int32_t* kv_indptr, const int32_t* kv_indices, const int32_t* work,
-                                      int items, const int32_t* merge_work, int merge_items, float* part_o, float* part_ml, int q_heads,
-                                      int kv_heads, int head_dim, int page_size, long long pool_pages, float scale, int window,
+                                      int items, const int32_t* merge_work, int merge_items, int merge_rows, float* part_o, float* part_ml,
+                                      int q_heads, int kv_heads, int head_dim, int page_size, long long pool_pages, float scale, int window,
                                       roost_stream_t stream) {
   ROOST_REQUIRE(items >= 0 && merge_items >= 0 && q_heads > 0 && kv_heads > 0 && page_size > 0, "attention_decode: sizes must be positive");
   ROOST_REQUIRE(q_heads % kv_heads == 0, "attention_decode: q_heads must be a multiple of kv_heads");
@@ -1127,8 +1125,8 @@ extern "C" int roost_attention_decode(const void* q, void* out, const void* k_po
   if (kv_heads > 65535) return fail(ROOST_ERR_UNSUPPORTED, "attention_decode: more than 65535 key/value heads");
   if (items == 0) return ROOST_OK;
   ROOST_DISPATCH_HEAD_DIM(head_dim, D, return launch_decode<D>(q, out, k_pool, v_pool, q_indptr, kv_lens, kv_indptr, kv_indices, work, items,
-                                                                merge_work, merge_items, part_o, part_ml, q_heads, kv_heads, page_size,
-                                                                pool_pages, scale, window, (cudaStream_t)stream));
+                                                                merge_work, merge_items, merge_rows, part_o, part_ml, q_heads, kv_heads,
+                                                                page_size, pool_pages, scale, window, (cudaStream_t)stream));
   return ROOST_OK;
 }
 
@@ -1199,7 +1197,7 @@ extern "C" int roost_attention_decode_static(const void* q, void* out, const voi
   // reads (all rows below the request's packed-row count, for every key/value head), so what an earlier call left
   // behind is never read.
   ROOST_DISPATCH_HEAD_DIM(head_dim, D, return launch_decode<D>(q, out, k_pool, v_pool, q_indptr, kv_lens, kv_indptr, kv_indices, work, items,
-                                                                merge_work, merge_items, scratch, scratch + o_padded, q_heads, kv_heads,
+                                                                merge_work, merge_items, 16, scratch, scratch + o_padded, q_heads, kv_heads,
                                                                 page_size, /*pool_pages unknown: the cp.async kernel*/ 0, scale, window,
                                                                 (cudaStream_t)stream));
   return ROOST_OK;

@@ -488,8 +488,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
 // of one to three 128-row tiles. A part that is a whole tile is written straight to out. Otherwise the CTA that holds the
 // tile's first k-blocks (it reaches them at the END of its range) finishes the tile: the CTAs holding the later k-blocks
 // (which they compute at the START of theirs) leave their partial sums in a workspace slot and raise a flag; the finisher
-// waits for the flags (a bounded wait), adds the partial sums in CTA order, writes out and lowers the flags. The order of
-// every sum is fixed by the geometry alone, so results are the same on every run and for every batch.
+// waits for the flags (a bounded wait), adds the partial sums up in CTA order, adds its own, writes out and lowers the
+// flags. The order of every sum is fixed by the geometry alone, so results are the same on every run and for every batch.
 constexpr int STAGES_S = 8;
 constexpr uint32_t kStageSWBytes = 128 * BK * 2;
 constexpr uint32_t kStageSXBytes = 64 * BK * 2;
@@ -598,6 +598,9 @@ __global__ void __launch_bounds__(192, 1)
       uint32_t phase = 0;
       bool ok = true;
       int it = 0;
+#ifdef ROOST_TRACE
+      unsigned long long tr_mma[2] = {0, 0};
+#endif
       for (int t = t_first; t <= t_last && ok; ++t, ++it) {
         const long long s0 = max(u0, (long long)t * kbs), s1 = min(u1, (long long)(t + 1) * kbs);
         const int acc = it & 1;
@@ -608,6 +611,9 @@ __global__ void __launch_bounds__(192, 1)
         for (long long u = s0; u < s1; ++u) {
           if (!(ok = mbar_wait(full_bar(stage), phase, abortp, 3))) break;
           tcgen05_fence_after();
+#ifdef ROOST_TRACE
+          if (u == u0) tr_mma[0] = trace_now();
+#endif
           const uint32_t sw = smem_base + stage * kStageSBytes;
           const uint64_t a_desc = umma_desc_k_major_sw128(sw);
           const uint64_t b_desc = umma_desc_k_major_sw128(sw + kStageSWBytes);
@@ -623,10 +629,17 @@ __global__ void __launch_bounds__(192, 1)
         }
         if (ok) tcgen05_commit(acc_full_bar(acc));
       }
+#ifdef ROOST_TRACE
+      tr_mma[1] = trace_now();
+      trace_flush(6 * 4 + 3, blockIdx.x * 8, tr_mma, 2);
+#endif
     }
   } else {
     const int lane_group = warp & 3;
     const int etid = (warp - 2) * 32 + lane;  // 0..127 among the epilogue threads
+#ifdef ROOST_TRACE
+    unsigned long long tr_epi[3] = {0, 0, 0};
+#endif
     bool ok = true;
     int it = 0;
     for (int t = t_first; t <= t_last && ok; ++t, ++it) {
@@ -634,13 +647,13 @@ __global__ void __launch_bounds__(192, 1)
       const int k0 = (int)(s0 - (long long)t * kbs), k1 = (int)(s1 - (long long)t * kbs);
       const int acc = it & 1;
       const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
-      if (!(ok = mbar_wait(acc_full_bar(acc), acc_phase, abortp, 4))) break;
-      tcgen05_fence_after();
       const int r = lane_group * 32 + lane;  // row of w within the tile = lane of tensor memory
       const int n = t * 128 + r;
       const uint32_t taddr = tmem_base + ((uint32_t)(lane_group * 32) << 16) + (uint32_t)(acc * 64);
       if (k0 > 0) {
         // a later part of the tile: leave the partial sums for the CTA that holds the tile's first k-blocks
+        if (!(ok = mbar_wait(acc_full_bar(acc), acc_phase, abortp, 4))) break;
+        tcgen05_fence_after();
         for (int cb = 0; cb < ntok; cb += 16) {
           uint32_t v[16];
           tcgen05_ld_32x32b_x16(taddr + cb, v);
@@ -654,8 +667,11 @@ __global__ void __launch_bounds__(192, 1)
           atomicExch(&flags[c], 1);
         }
       } else {
-        // the tile's first part: a whole tile, or the finisher of a tile that continues in the next CTAs
+        // the tile's first part: a whole tile, or the finisher of a tile that continues in the next CTAs. Those CTAs
+        // reach their part of this tile first of all, so their partial sums are there long before this CTA's own
+        // accumulator is: they are fetched and added up (in CTA order) while the tensor cores still work on it.
         int contributors = 0;
+        float psum[4][16];
         if (k1 < kbs) {
           long long covered = s1;
           while (covered < (long long)(t + 1) * kbs && c + 1 + contributors < G) {
@@ -674,24 +690,50 @@ __global__ void __launch_bounds__(192, 1)
             __threadfence();
           }
           asm volatile("bar.sync 1, 128;\n" ::: "memory");
-        }
-        for (int cb = 0; cb < ntok; cb += 16) {
-          uint32_t v[16];
-          tcgen05_ld_32x32b_x16(taddr + cb, v);
-          float sum[16];
 #pragma unroll
-          for (int i = 0; i < 16; ++i) sum[i] = __uint_as_float(v[i]);
-          for (int j = 0; j < contributors; ++j) {  // CTA order; the sixteen loads of a contributor are independent
-            float part[16];
+          for (int q = 0; q < 4; ++q) {
+            if (q * 16 < ntok) {
 #pragma unroll
-            for (int i = 0; i < 16; ++i) part[i] = __ldcg(&ws[((size_t)(c + 1 + j) * 64 + cb + i) * 128 + r]);
+              for (int i = 0; i < 16; ++i) psum[q][i] = 0.f;
+              for (int j0 = 0; j0 < contributors; j0 += 4) {  // the loads of four contributors are in flight together
+                float part[4][16];
 #pragma unroll
-            for (int i = 0; i < 16; ++i) sum[i] += part[i];
+                for (int jj = 0; jj < 4; ++jj) {
+                  if (j0 + jj < contributors) {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) part[jj][i] = __ldcg(&ws[((size_t)(c + 1 + j0 + jj) * 64 + q * 16 + i) * 128 + r]);
+                  }
+                }
+#pragma unroll
+                for (int jj = 0; jj < 4; ++jj) {
+                  if (j0 + jj < contributors) {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) psum[q][i] += part[jj][i];
+                  }
+                }
+              }
+            }
           }
+        }
+#ifdef ROOST_TRACE
+        tr_epi[0] = trace_now();
+#endif
+        if (!(ok = mbar_wait(acc_full_bar(acc), acc_phase, abortp, 4))) break;
+        tcgen05_fence_after();
+#ifdef ROOST_TRACE
+        tr_epi[1] = trace_now();
+#endif
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const int m = cb + i;
-            if (m < M && n < N) out[(size_t)m * ldo + n] = from_float<TOut>(sum[i]);
+        for (int q = 0; q < 4; ++q) {
+          if (q * 16 < ntok) {
+            uint32_t v[16];
+            tcgen05_ld_32x32b_x16(taddr + q * 16, v);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const int m = q * 16 + i;
+              const float sum = contributors > 0 ? __uint_as_float(v[i]) + psum[q][i] : __uint_as_float(v[i]);
+              if (m < M && n < N) out[(size_t)m * ldo + n] = from_float<TOut>(sum);
+            }
           }
         }
         if (contributors > 0) {
@@ -703,6 +745,10 @@ __global__ void __launch_bounds__(192, 1)
       __syncwarp();
       if (lane == 0) mbar_arrive(acc_empty_bar(acc));
     }
+#ifdef ROOST_TRACE
+    tr_epi[2] = trace_now();
+    if (etid == 0) trace_flush(6 * 4 + 3, blockIdx.x * 8 + 2, tr_epi, 3);
+#endif
   }
 
   trace_point(6, 2);

@@ -79,7 +79,9 @@ int roost_paged_attention_generic(const void* q, void* out, const void* k_pool, 
  * prefill work: int32 pairs (batch row, first packed row of a tile of tile_rows rows; roost_attention_prefill_tile_rows picks 64 or 128),
  * packed row = token * group + head.
  * decode work: int32 quadruples (batch row, first key, one past the last key, partial slot or -1); rows with at most
- * 16 packed rows only; the first key of an item is a multiple of 64. merge_work: quadruples (batch row, first slot, chunks, 0) for rows split into several chunks.
+ * 16 packed rows only; the first key of an item is a multiple of 64. merge_work: quadruples (batch row, first slot,
+ * chunks | packed rows << 24, the row's first token) for rows split into several chunks; merge_rows: the most packed
+ * rows any of them has.
  * part_o: float[slots * kv_heads * 16 * head_dim], part_ml: float[slots * kv_heads * 16 * 2].
  * pool_pages: pages of k_pool and v_pool; with head size 64 or 128, pages of 8, 16 or a multiple of 32 rows and pools
  * on 128-byte boundaries, decode streams keys and values through the copy engine (TMA) unless
@@ -94,8 +96,8 @@ int roost_attention_prefill(const void* q, void* out, const void* k_pool, const 
                             int window, roost_stream_t stream);
 int roost_attention_decode(const void* q, void* out, const void* k_pool, const void* v_pool, const int32_t* q_indptr,
                            const int32_t* kv_lens, const int32_t* kv_indptr, const int32_t* kv_indices, const int32_t* work,
-                           int items, const int32_t* merge_work, int merge_items, float* part_o, float* part_ml, int q_heads,
-                           int kv_heads, int head_dim, int page_size, long long pool_pages, float scale, int window,
+                           int items, const int32_t* merge_work, int merge_items, int merge_rows, float* part_o, float* part_ml,
+                           int q_heads, int kv_heads, int head_dim, int page_size, long long pool_pages, float scale, int window,
                            roost_stream_t stream);
 void roost_attention_set_decode_tma(int on);
 int roost_attention_status(void);

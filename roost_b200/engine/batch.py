@@ -38,6 +38,7 @@ class AttentionPlan:
     padding entries (batch row -1), which the kernels skip."""
     prefill_items: int = 0
     prefill_tile_rows: int = 64
+    merge_rows: int = 16         # the most packed rows a split row has (the merge kernel's blocks along z)
     decode_items: int = 0
     merge_items: int = 0
     slots: int = 0
@@ -53,8 +54,10 @@ def attention_work(row_starts, row_counts, group: int, window: int | None, chunk
         raise ValueError(f"decode chunk {chunk} is not a positive multiple of 64")
     prefill, decode, merge, tiles = [], [], [], []
     slots = 0
+    token = 0    # the row's first token among the step's tokens
     for b, (start, n) in enumerate(zip(row_starts, row_counts)):
         rows, kv_len = n * group, start + n
+        first_token, token = token, token + n
         if rows <= 16:
             lo = max(0, start - window + 1) if window else 0
             first = (lo // chunk) * chunk
@@ -62,7 +65,7 @@ def attention_work(row_starts, row_counts, group: int, window: int | None, chunk
             if len(begins) == 1:
                 decode += [b, first, min(first + chunk, kv_len), -1]
             else:
-                merge += [b, slots, len(begins), 0]
+                merge += [b, slots, len(begins) | (rows << 24), first_token]
                 for c in begins:
                     decode += [b, c, min(c + chunk, kv_len), slots]
                     slots += 1
@@ -88,7 +91,8 @@ def _pad4(a: list) -> list:
 
 def plan_attention(row_starts, row_counts, group: int, window: int | None, chunk: int, device, tile_rows: int = 64) -> AttentionPlan:
     prefill, decode, merge, slots = attention_work(row_starts, row_counts, group, window, chunk, tile_rows)
-    plan = AttentionPlan(prefill_items=len(prefill) // 2, prefill_tile_rows=tile_rows, decode_items=len(decode) // 4, merge_items=len(merge) // 4, slots=slots)
+    plan = AttentionPlan(prefill_items=len(prefill) // 2, prefill_tile_rows=tile_rows, decode_items=len(decode) // 4, merge_items=len(merge) // 4, slots=slots,
+                         merge_rows=max((z >> 24 for z in merge[2::4]), default=1))
     flat = _pad4(prefill) + _pad4(decode) + _pad4(merge)
     if flat:
         host = torch.tensor(flat, dtype=torch.int32)

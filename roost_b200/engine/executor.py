@@ -90,6 +90,7 @@ class DecodeGraph:
         views = self.static.views[self.n_table:]
         for i, (key, (pc, dc, mc)) in enumerate(zip(self.plan_keys, self.plan_caps)):
             batch.attention_plans[key] = AttentionPlan(prefill_items=pc, prefill_tile_rows=key[3], decode_items=dc, merge_items=mc, slots=dc,
+                                                       merge_rows=min(16, key[0]),   # one token a row: its query heads per key/value head
                                                        prefill_work=views[3 * i], decode_work=views[3 * i + 1],
                                                        merge_work=views[3 * i + 2])
         # this step's result comes from an eager run on a side stream (which also warms every kernel and library up);

@@ -62,7 +62,8 @@ _SIGNATURES = {
     "roost_attention_prefill": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                 c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
     "roost_attention_decode": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
-                               c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, ctypes.c_longlong, c_float, c_int, c_void_p],
+                               c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, ctypes.c_longlong, c_float, c_int,
+                               c_void_p],
     "roost_gemm_simt": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int, c_int, c_void_p],
     "roost_gemm_skinny_supported": [c_int, c_int, c_int, c_int64, c_int64],
     "roost_gemm_skinny": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int, c_void_p],
@@ -225,7 +226,7 @@ class KernelLibrary:
                 part_ml = torch.empty((plan.slots * nkv * 16 * 2,), dtype=torch.float32, device=q.device)
             self._call("roost_attention_decode", _ptr(q), _ptr(out), _ptr(k_pool), _ptr(v_pool), _ptr(q_indptr), _ptr(kv_lens),
                        _ptr(kv_indptr), _ptr(kv_indices), _ptr(plan.decode_work), plan.decode_items, _ptr(plan.merge_work),
-                       plan.merge_items, _ptr(part_o), _ptr(part_ml), nq, nkv, d, page, k_pool.shape[0], scale, w, _stream(),
+                       plan.merge_items, plan.merge_rows, _ptr(part_o), _ptr(part_ml), nq, nkv, d, page, k_pool.shape[0], scale, w, _stream(),
                        launches=2 if plan.merge_items else 1)
         return out
 

@@ -13,6 +13,7 @@ Adding a part: subclass the interface below, give the spec class a new ``kind`` 
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 from typing import Callable
 
@@ -53,7 +54,10 @@ class Runtime:
         self.dtype = dtype
         self.device = torch.device(device)
         self.kernels = kernels
-        self.small_gemm = "auto"        # products of at most 64 rows: "auto" | "library" | "stream" | "skinny" (parts/linear.py)
+        # products of at most 64 rows: "auto" | "library" | "stream" | "skinny" (parts/linear.py)
+        self.small_gemm = os.environ.get("ROOST_SMALL_GEMM", "auto")
+        if self.small_gemm not in ("auto", "library", "stream", "skinny"):
+            raise ValueError(f"ROOST_SMALL_GEMM={self.small_gemm!r} is not one of auto, library, stream, skinny")
 
     @property
     def full_precision(self) -> bool:
