@@ -490,10 +490,20 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
 // (which they compute at the START of theirs) leave their partial sums in a workspace slot and raise a flag; the finisher
 // waits for the flags (a bounded wait), adds the partial sums up in CTA order, adds its own, writes out and lowers the
 // flags. The order of every sum is fixed by the geometry alone, so results are the same on every run and for every batch.
-constexpr int STAGES_S = 8;
-constexpr uint32_t kStageSWBytes = 128 * BK * 2;
-constexpr uint32_t kStageSXBytes = 64 * BK * 2;
-constexpr uint32_t kStageSBytes = kStageSWBytes + kStageSXBytes;
+// SWIGLU: w's rows come in blocks of 256, 128 gate rows followed by the 128 up rows of the same outputs (the layout of the
+// fused product for many rows above). A tile is then such a block, with two accumulators that share the x operand; a row
+// of tensor memory holds the gate and the up value of one output, and the CTA that finishes the tile writes
+// silu(gate) * up, so out has n / 2 columns.
+template <bool SWIGLU>
+struct StreamCfg {
+  static constexpr int kWRows = SWIGLU ? 256 : 128;           // rows of w in a tile
+  static constexpr int kStages = SWIGLU ? 5 : 8;
+  static constexpr uint32_t kStageW = kWRows * BK * 2;
+  static constexpr uint32_t kStageX = 64 * BK * 2;
+  static constexpr uint32_t kStage = kStageW + kStageX;
+  static constexpr uint32_t kAccCols = SWIGLU ? 128 : 64;     // tensor-memory columns of one tile's accumulators
+  static constexpr int kParts = SWIGLU ? 2 : 1;                // accumulators a tile has
+};
 constexpr int kStreamMaxCtas = 256;
 
 __device__ __forceinline__ void tcgen05_ld_32x32b_x16(uint32_t taddr, uint32_t (&v)[16]) {
@@ -506,10 +516,14 @@ __device__ __forceinline__ void tcgen05_ld_32x32b_x16(uint32_t taddr, uint32_t (
   asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
 }
 
-template <typename TOut>
+template <typename TOut, bool SWIGLU>
 __global__ void __launch_bounds__(192, 1)
     gemm_stream_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_constant__ CUtensorMap tma_x, TOut* __restrict__ out, int M,
                        int N, int K, int64_t ldo, int ntok, float* ws, int* flags) {
+  using Cfg = StreamCfg<SWIGLU>;
+  constexpr int STAGES_S = Cfg::kStages;
+  constexpr uint32_t kStageSWBytes = Cfg::kStageW, kStageSBytes = Cfg::kStage;
+  constexpr int WR = Cfg::kWRows;
   extern __shared__ unsigned char smem_raw[];
   const uint32_t smem_base = ((uint32_t)__cvta_generic_to_shared(smem_raw) + 1023u) & ~1023u;
   __shared__ __align__(8) uint64_t bars[2 * STAGES_S + 4];
@@ -520,10 +534,10 @@ __global__ void __launch_bounds__(192, 1)
   auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES_S + s); };
   auto acc_full_bar = [&](int a) { return bar0 + 8u * (2 * STAGES_S + a); };
   auto acc_empty_bar = [&](int a) { return bar0 + 8u * (2 * STAGES_S + 2 + a); };
-  constexpr uint32_t kCols = 128;  // two accumulators of 64 columns
+  constexpr uint32_t kCols = 2 * Cfg::kAccCols;  // two tiles' accumulators
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n_tiles = (N + 127) / 128;
+  const int n_tiles = (N + WR - 1) / WR;
   const int kbs = (K + BK - 1) / BK;
   const long long units = (long long)n_tiles * kbs;
   const int G = gridDim.x, c = blockIdx.x;
@@ -551,7 +565,7 @@ __global__ void __launch_bounds__(192, 1)
       const int t = (int)(u / kbs), kb = (int)(u % kbs);
       const uint32_t sw = smem_base + prologue * kStageSBytes;
       mbar_expect_tx(full_bar(prologue), kStageSWBytes + (uint32_t)ntok * BK * 2);
-      tma_load_2d(sw, &tma_w, full_bar(prologue), kb * BK, t * 128);
+      tma_load_2d(sw, &tma_w, full_bar(prologue), kb * BK, t * WR);
     }
     pdl_wait(6);
     for (int i = 0; i < prologue; ++i) {
@@ -583,7 +597,7 @@ __global__ void __launch_bounds__(192, 1)
         if (!(ok = mbar_wait(empty_bar(stage), phase ^ 1u, abortp, 1))) break;
         const uint32_t sw = smem_base + stage * kStageSBytes;
         mbar_expect_tx(full_bar(stage), kStageSWBytes + (uint32_t)ntok * BK * 2);
-        tma_load_2d(sw, &tma_w, full_bar(stage), kb * BK, t * 128);
+        tma_load_2d(sw, &tma_w, full_bar(stage), kb * BK, t * WR);
         tma_load_2d(sw + kStageSWBytes, &tma_x, full_bar(stage), kb * BK, 0);
         if (++stage == STAGES_S) {
           stage = 0;
@@ -607,7 +621,7 @@ __global__ void __launch_bounds__(192, 1)
         const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
         if (!(ok = mbar_wait(acc_empty_bar(acc), acc_phase ^ 1u, abortp, 2))) break;
         tcgen05_fence_after();
-        const uint32_t tmem_d = tmem_base + (uint32_t)acc * 64;
+        const uint32_t tmem_d = tmem_base + (uint32_t)acc * Cfg::kAccCols;
         for (long long u = s0; u < s1; ++u) {
           if (!(ok = mbar_wait(full_bar(stage), phase, abortp, 3))) break;
           tcgen05_fence_after();
@@ -620,6 +634,10 @@ __global__ void __launch_bounds__(192, 1)
 #pragma unroll
           for (int k = 0; k < BK / kUmmaK; ++k) {
             tcgen05_mma_f16(tmem_d, a_desc + (uint64_t)(2 * k), b_desc + (uint64_t)(2 * k), idesc, (u > s0 || k > 0) ? 1u : 0u);
+            if constexpr (SWIGLU) {  // the up rows, 128 rows (16 KB) further down the stage
+              tcgen05_mma_f16(tmem_d + 64, a_desc + (uint64_t)(2 * k) + (uint64_t)((128 * BK * 2) >> 4), b_desc + (uint64_t)(2 * k), idesc,
+                              (u > s0 || k > 0) ? 1u : 0u);
+            }
           }
           tcgen05_commit(empty_bar(stage));
           if (++stage == STAGES_S) {
@@ -647,18 +665,24 @@ __global__ void __launch_bounds__(192, 1)
       const int k0 = (int)(s0 - (long long)t * kbs), k1 = (int)(s1 - (long long)t * kbs);
       const int acc = it & 1;
       const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
-      const int r = lane_group * 32 + lane;  // row of w within the tile = lane of tensor memory
-      const int n = t * 128 + r;
-      const uint32_t taddr = tmem_base + ((uint32_t)(lane_group * 32) << 16) + (uint32_t)(acc * 64);
+      constexpr int P = Cfg::kParts;         // accumulators of a tile: the product, or gate and up
+      constexpr int QMAX = SWIGLU ? 2 : 4;   // sixteen-column groups of x rows this variant serves
+      const int r = lane_group * 32 + lane;  // row within the tile's accumulators = lane of tensor memory
+      const int n = t * 128 + r;             // column of out
+      const int n_out = SWIGLU ? N / 2 : N;
+      const uint32_t taddr = tmem_base + ((uint32_t)(lane_group * 32) << 16) + (uint32_t)(acc * Cfg::kAccCols);
       if (k0 > 0) {
         // a later part of the tile: leave the partial sums for the CTA that holds the tile's first k-blocks
         if (!(ok = mbar_wait(acc_full_bar(acc), acc_phase, abortp, 4))) break;
         tcgen05_fence_after();
-        for (int cb = 0; cb < ntok; cb += 16) {
-          uint32_t v[16];
-          tcgen05_ld_32x32b_x16(taddr + cb, v);
 #pragma unroll
-          for (int i = 0; i < 16; ++i) ws[((size_t)c * 64 + cb + i) * 128 + r] = __uint_as_float(v[i]);
+        for (int p = 0; p < P; ++p) {
+          for (int cb = 0; cb < ntok; cb += 16) {
+            uint32_t v[16];
+            tcgen05_ld_32x32b_x16(taddr + p * 64 + cb, v);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) ws[(((size_t)c * P + p) * 64 + cb + i) * 128 + r] = __uint_as_float(v[i]);
+          }
         }
         __threadfence();
         asm volatile("bar.sync 1, 128;\n" ::: "memory");  // the four epilogue warps
@@ -668,10 +692,10 @@ __global__ void __launch_bounds__(192, 1)
         }
       } else {
         // the tile's first part: a whole tile, or the finisher of a tile that continues in the next CTAs. Those CTAs
-        // reach their part of this tile first of all, so their partial sums are there long before this CTA's own
+        // reach their part of this tile first of all, so their partial sums are often there before this CTA's own
         // accumulator is: they are fetched and added up (in CTA order) while the tensor cores still work on it.
         int contributors = 0;
-        float psum[4][16];
+        float psum[P][QMAX][16];
         if (k1 < kbs) {
           long long covered = s1;
           while (covered < (long long)(t + 1) * kbs && c + 1 + contributors < G) {
@@ -691,24 +715,27 @@ __global__ void __launch_bounds__(192, 1)
           }
           asm volatile("bar.sync 1, 128;\n" ::: "memory");
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            if (q * 16 < ntok) {
+          for (int p = 0; p < P; ++p) {
 #pragma unroll
-              for (int i = 0; i < 16; ++i) psum[q][i] = 0.f;
-              for (int j0 = 0; j0 < contributors; j0 += 4) {  // the loads of four contributors are in flight together
-                float part[4][16];
+            for (int q = 0; q < QMAX; ++q) {
+              if (q * 16 < ntok) {
 #pragma unroll
-                for (int jj = 0; jj < 4; ++jj) {
-                  if (j0 + jj < contributors) {
+                for (int i = 0; i < 16; ++i) psum[p][q][i] = 0.f;
+                for (int j0 = 0; j0 < contributors; j0 += 4) {  // the loads of four contributors are in flight together
+                  float part[4][16];
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) part[jj][i] = __ldcg(&ws[((size_t)(c + 1 + j0 + jj) * 64 + q * 16 + i) * 128 + r]);
+                  for (int jj = 0; jj < 4; ++jj) {
+                    if (j0 + jj < contributors) {
+#pragma unroll
+                      for (int i = 0; i < 16; ++i) part[jj][i] = __ldcg(&ws[(((size_t)(c + 1 + j0 + jj) * P + p) * 64 + q * 16 + i) * 128 + r]);
+                    }
                   }
-                }
 #pragma unroll
-                for (int jj = 0; jj < 4; ++jj) {
-                  if (j0 + jj < contributors) {
+                  for (int jj = 0; jj < 4; ++jj) {
+                    if (j0 + jj < contributors) {
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) psum[q][i] += part[jj][i];
+                      for (int i = 0; i < 16; ++i) psum[p][q][i] += part[jj][i];
+                    }
                   }
                 }
               }
@@ -724,15 +751,19 @@ __global__ void __launch_bounds__(192, 1)
         tr_epi[1] = trace_now();
 #endif
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
+        for (int q = 0; q < QMAX; ++q) {
           if (q * 16 < ntok) {
-            uint32_t v[16];
-            tcgen05_ld_32x32b_x16(taddr + q * 16, v);
+            uint32_t v[P][16];
+#pragma unroll
+            for (int p = 0; p < P; ++p) tcgen05_ld_32x32b_x16(taddr + p * 64 + q * 16, v[p]);
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
               const int m = q * 16 + i;
-              const float sum = contributors > 0 ? __uint_as_float(v[i]) + psum[q][i] : __uint_as_float(v[i]);
-              if (m < M && n < N) out[(size_t)m * ldo + n] = from_float<TOut>(sum);
+              float val[P];
+#pragma unroll
+              for (int p = 0; p < P; ++p) val[p] = contributors > 0 ? __uint_as_float(v[p][i]) + psum[p][q][i] : __uint_as_float(v[p][i]);
+              const float res = SWIGLU ? silu_f(val[0]) * val[P - 1] : val[0];
+              if (m < M && n < n_out) out[(size_t)m * ldo + n] = from_float<TOut>(res);
             }
           }
         }
@@ -820,13 +851,14 @@ static int launch_tcgen05_pair(const CUtensorMap& ma, const CUtensorMap& mb, voi
   return check_launch("gemm_tcgen05_pair");
 }
 
-template <typename TOut>
+template <typename TOut, bool SWIGLU>
 static int launch_stream(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int m, int n, int k, int64_t ldo, int ntok, float* ws,
                          int* flags, cudaStream_t s) {
+  using Cfg = StreamCfg<SWIGLU>;
   static int sms = 0;
   static bool attr_set = false;
-  const size_t smem = (size_t)STAGES_S * kStageSBytes + 1024;
-  auto kernel = gemm_stream_kernel<TOut>;
+  const size_t smem = (size_t)Cfg::kStages * Cfg::kStage + 1024;
+  auto kernel = gemm_stream_kernel<TOut, SWIGLU>;
   if (!attr_set) {
     int dev = 0;
     cudaGetDevice(&dev);
@@ -834,7 +866,7 @@ static int launch_stream(const CUtensorMap& mw, const CUtensorMap& mx, void* out
     cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     attr_set = true;
   }
-  const long long units = (long long)((n + 127) / 128) * ((k + BK - 1) / BK);
+  const long long units = (long long)((n + Cfg::kWRows - 1) / Cfg::kWRows) * ((k + BK - 1) / BK);
   long long grid = sms < kStreamMaxCtas ? sms : kStreamMaxCtas;
   if (units < grid) grid = units;
   launch_kernel(kernel, dim3((int)grid), dim3(192), smem, s, mw, mx, (TOut*)out, m, n, k, ldo, ntok, ws, flags);
@@ -908,7 +940,7 @@ extern "C" int roost_gemm_tcgen05_swiglu(const void* a, const void* w, void* out
 
 // Workspace of the weight-streaming product: floats for the partial sums and ints for the flags (zero before the first
 // call; every call leaves them zero).
-extern "C" int roost_gemm_stream_workspace_floats(void) { return kStreamMaxCtas * 64 * 128; }
+extern "C" int roost_gemm_stream_workspace_floats(void) { return kStreamMaxCtas * 2 * 64 * 128; }  // two accumulators a CTA
 extern "C" int roost_gemm_stream_workspace_flags(void) { return kStreamMaxCtas; }
 
 extern "C" int roost_gemm_stream_supported(int m, int n, int k, int64_t ldx, int64_t ldw) {
@@ -930,8 +962,33 @@ extern "C" int roost_gemm_stream(const void* x, const void* w, void* out, int m,
   if (rc != ROOST_OK) return rc;
   rc = make_map(&mx, x, m, k, ldx, ntok);
   if (rc != ROOST_OK) return rc;
-  if (out_dtype == ROOST_BF16) return launch_stream<__nv_bfloat16>(mw, mx, out, m, n, k, ldo, ntok, ws, flags, (cudaStream_t)stream);
-  return launch_stream<float>(mw, mx, out, m, n, k, ldo, ntok, ws, flags, (cudaStream_t)stream);
+  if (out_dtype == ROOST_BF16) return launch_stream<__nv_bfloat16, false>(mw, mx, out, m, n, k, ldo, ntok, ws, flags, (cudaStream_t)stream);
+  return launch_stream<float, false>(mw, mx, out, m, n, k, ldo, ntok, ws, flags, (cudaStream_t)stream);
+}
+
+extern "C" int roost_gemm_stream_swiglu_supported(int m, int n, int k, int64_t ldx, int64_t ldw) {
+  return m >= 1 && m <= 32 && n >= 256 && n % 256 == 0 && k >= 8 && k % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0;
+}
+
+// out[m, j] = silu(gate_j) * up_j for w's rows in blocks of 256 (128 gate rows, then the 128 up rows of the same outputs);
+// out has n / 2 columns.
+extern "C" int roost_gemm_stream_swiglu(const void* x, const void* w, void* out, int m, int n, int k, int64_t ldx, int64_t ldw, int64_t ldo,
+                                        int out_dtype, float* ws, int32_t* flags, roost_stream_t stream) {
+  ROOST_REQUIRE(out_dtype == ROOST_BF16 || out_dtype == ROOST_F32, "gemm_stream_swiglu: the output is bfloat16 (1) or float32 (0)");
+  ROOST_REQUIRE(ldx >= k && ldw >= k && ldo >= n / 2, "gemm_stream_swiglu: a leading dimension is smaller than its row");
+  ROOST_REQUIRE(ws != nullptr && flags != nullptr, "gemm_stream_swiglu: the workspace is missing");
+  if (!roost_gemm_stream_swiglu_supported(m, n, k, ldx, ldw)) {
+    return fail(ROOST_ERR_UNSUPPORTED, "gemm_stream_swiglu: needs 1 <= m <= 32, n a multiple of 256, k and the row strides multiples of 8");
+  }
+  ROOST_REQUIRE(((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0), "gemm_stream_swiglu: x and w must start on 16-byte boundaries");
+  const int ntok = m <= 16 ? 16 : 32;
+  CUtensorMap mw, mx;
+  int rc = make_map(&mw, w, n, k, ldw, 256);
+  if (rc != ROOST_OK) return rc;
+  rc = make_map(&mx, x, m, k, ldx, ntok);
+  if (rc != ROOST_OK) return rc;
+  if (out_dtype == ROOST_BF16) return launch_stream<__nv_bfloat16, true>(mw, mx, out, m, n, k, ldo, ntok, ws, flags, (cudaStream_t)stream);
+  return launch_stream<float, true>(mw, mx, out, m, n, k, ldo, ntok, ws, flags, (cudaStream_t)stream);
 }
 
 ROOST_TRACE_TU(gemm_tcgen05)

@@ -159,6 +159,11 @@ int roost_gemm_stream_workspace_flags(void);
 int roost_gemm_stream_supported(int m, int n, int k, int64_t ldx, int64_t ldw);
 int roost_gemm_stream(const void* x, const void* w, void* out, int m, int n, int k, int64_t ldx, int64_t ldw, int64_t ldo,
                       int out_dtype, float* ws, int32_t* flags, roost_stream_t stream);
+/* The same with the SwiGLU of the fused product: w's rows in blocks of 256 (128 gate rows, then the 128 up rows of the
+ * same outputs), out[m, j] = silu(gate_j) * up_j with n / 2 columns; at most 32 rows of x, n a multiple of 256. */
+int roost_gemm_stream_swiglu_supported(int m, int n, int k, int64_t ldx, int64_t ldw);
+int roost_gemm_stream_swiglu(const void* x, const void* w, void* out, int m, int n, int k, int64_t ldx, int64_t ldw, int64_t ldo,
+                             int out_dtype, float* ws, int32_t* flags, roost_stream_t stream);
 
 /* ids[r] = index of the largest logit of row r, ties to the lowest index, NaN never chosen (-1 if none). */
 int roost_argmax(const float* logits, int64_t stride, int rows, int vocab, int32_t* ids, roost_stream_t stream);

@@ -77,6 +77,9 @@ _SIGNATURES = {
     "roost_gemm_stream_supported": [c_int, c_int, c_int, c_int64, c_int64],
     "roost_gemm_stream": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int, c_void_p, c_void_p,
                           c_void_p],
+    "roost_gemm_stream_swiglu_supported": [c_int, c_int, c_int, c_int64, c_int64],
+    "roost_gemm_stream_swiglu": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int, c_void_p, c_void_p,
+                                 c_void_p],
     "roost_argmax": [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p],
     "roost_sample": [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                      c_void_p, c_void_p],
@@ -283,6 +286,14 @@ class KernelLibrary:
     def gemm_stream_supported(self, m: int, n: int, k: int, ldx: int, ldw: int) -> bool:
         return bool(self._lib.roost_gemm_stream_supported(m, n, k, ldx, ldw))
 
+    def _stream_workspace(self, device):
+        ws = getattr(self, "_stream_ws", None)
+        if ws is None or ws[0].device != device:
+            # allocated once, outside any stream capture (the first decode step of a model runs eagerly)
+            ws = self._stream_ws = (torch.zeros(self._lib.roost_gemm_stream_workspace_floats(), dtype=torch.float32, device=device),
+                                    torch.zeros(self._lib.roost_gemm_stream_workspace_flags(), dtype=torch.int32, device=device))
+        return ws
+
     def gemm_stream(self, x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
         """x [M <= 64, K] times w [N, K] transposed: the weight-streaming tcgen05 product of decode steps."""
         _need(x, "x", torch.bfloat16); _need(w, "w", torch.bfloat16)
@@ -290,14 +301,28 @@ class KernelLibrary:
         N, K2 = w.shape
         if K != K2:
             raise KernelError(f"gemm_stream: x has {K} columns, w has {K2}")
-        ws = getattr(self, "_stream_ws", None)
-        if ws is None or ws[0].device != x.device:
-            # allocated once, outside any stream capture (the first decode step of a model runs eagerly)
-            ws = self._stream_ws = (torch.zeros(self._lib.roost_gemm_stream_workspace_floats(), dtype=torch.float32, device=x.device),
-                                    torch.zeros(self._lib.roost_gemm_stream_workspace_flags(), dtype=torch.int32, device=x.device))
+        ws = self._stream_workspace(x.device)
         out_dtype = out_dtype or torch.bfloat16
         out = torch.empty((M, N), dtype=out_dtype, device=x.device)
         self._call("roost_gemm_stream", _ptr(x), _ptr(w), _ptr(out), M, N, K, x.stride(0), w.stride(0), out.stride(0),
+                   dtype_code(out_dtype), _ptr(ws[0]), _ptr(ws[1]), _stream())
+        return out
+
+    def gemm_stream_swiglu_supported(self, m: int, n: int, k: int, ldx: int, ldw: int) -> bool:
+        return bool(self._lib.roost_gemm_stream_swiglu_supported(m, n, k, ldx, ldw))
+
+    def gemm_stream_swiglu(self, x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+        """silu(x Wg^T) * (x Wu^T) for x [M <= 32, K] and w [2I, K] with gate and up rows interleaved in blocks of 128:
+        the weight-streaming product with the activation applied to its accumulators; returns [M, I]."""
+        _need(x, "x", torch.bfloat16); _need(w, "w", torch.bfloat16)
+        M, K = x.shape
+        N, K2 = w.shape
+        if K != K2:
+            raise KernelError(f"gemm_stream_swiglu: x has {K} columns, w has {K2}")
+        ws = self._stream_workspace(x.device)
+        out_dtype = out_dtype or torch.bfloat16
+        out = torch.empty((M, N // 2), dtype=out_dtype, device=x.device)
+        self._call("roost_gemm_stream_swiglu", _ptr(x), _ptr(w), _ptr(out), M, N, K, x.stride(0), w.stride(0), out.stride(0),
                    dtype_code(out_dtype), _ptr(ws[0]), _ptr(ws[1]), _stream())
         return out
 

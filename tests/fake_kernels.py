@@ -98,6 +98,9 @@ class FakeKernels:
     def gemm_skinny_supported(self, *a):
         return False
 
+    def gemm_stream_swiglu_supported(self, *a):
+        return False
+
     def gemm_simt(self, a, w, out_dtype=None):
         return (a.float() @ w.float().t()).to(out_dtype or a.dtype)
 
