@@ -153,7 +153,7 @@ class StaticTables:
     """Device memory of fixed capacity for a step's tables, with a ring of pinned host buffers. The device addresses
     of all sections stay the same from step to step, so a captured graph can read them on every replay."""
 
-    RING = 3
+    RING = 4
 
     def __init__(self, device, caps: list[int]):
         self.device = torch.device(device)
@@ -172,8 +172,10 @@ class StaticTables:
     def fits(self, arrays: list) -> bool:
         return len(arrays) == len(self.caps) and all(a.size <= c for a, c in zip(arrays, self.caps))
 
-    def upload(self, arrays: list, fills: list) -> None:
-        """Copies the arrays into their sections; the rest of each section is filled with ``fills[i]``."""
+    def stage(self, arrays: list, fills: list) -> int:
+        """Writes the arrays into the next pinned buffer (the rest of each section filled with ``fills[i]``) and returns
+        its index; ``send`` copies it to the device. Between the two the caller may still change values in place
+        through ``staged``."""
         i = self.turn
         self.turn = (self.turn + 1) % self.RING
         if self.events[i] is not None:
@@ -182,11 +184,23 @@ class StaticTables:
         for a, o, c, f in zip(arrays, self.offsets, self.caps, fills):
             hv[o : o + a.size] = a
             hv[o + a.size : o + c] = f
+        return i
+
+    def staged(self, i: int, section: int):
+        """The pinned copy of one section, as a numpy view."""
+        o = self.offsets[section]
+        return self.hosts[i].numpy()[o : o + self.caps[section]]
+
+    def send(self, i: int) -> None:
         self.dev.copy_(self.hosts[i], non_blocking=True)
         if self.device.type == "cuda":
             ev = torch.cuda.Event()
             ev.record()
             self.events[i] = ev
+
+    def upload(self, arrays: list, fills: list) -> None:
+        """Copies the arrays into their sections; the rest of each section is filled with ``fills[i]``."""
+        self.send(self.stage(arrays, fills))
 
 
 class BatchBuilder:

@@ -84,6 +84,7 @@ class RoostEngine:
         self._next_id = 0
         self.steps = 0
         self.last_plan: StepPlan | None = None
+        self._prepared = None     # the next decode step's tables, made while the device ran the last one
 
     # ------------------------------------------------------------------ requests
     def add_request(self, prompt_token_ids, sampling: SamplingParameters = GREEDY, *, request_id=None, stop_token_ids=(),
@@ -119,12 +120,22 @@ class RoostEngine:
         tokens = {}
         if plan.rows:
             entries = [StepEntry(r.sequence.request_id, r.tokens, [r.count - 1] if r.samples else [], r.start) for r in plan.rows]
-            logits = self.executor.step(entries)
+            prepared, self._prepared = self._prepared, None
+            if prepared is not None and self.executor.matches_prepared(prepared, entries):
+                logits = self.executor.run_prepared(prepared, entries)
+            else:
+                logits = self.executor.step(entries)
             sampling_rows = [r for r in plan.rows if r.samples]
             if sampling_rows:
                 rows = [SamplingRow(r.sequence.request.sampling, self._seeds[r.sequence.request_id], r.sequence.generated)
                         for r in sampling_rows]
-                ids = self.sampler(logits, rows).cpu().tolist()
+                ids_device = self.sampler(logits, rows)
+                # While the device runs this step: the tables of the next one, should it be these rows' next tokens and
+                # nothing else (no request waiting for its prompt, none ending now). The host then only fills the
+                # tokens in when they arrive.
+                if len(sampling_rows) == len(plan.rows) and all(r.count == 1 for r in plan.rows) and self._decode_only():
+                    self._prepared = self.executor.prepare_decode([r.sequence.request_id for r in plan.rows])
+                ids = ids_device.cpu().tolist()
                 tokens = {r.sequence.request_id: t for r, t in zip(sampling_rows, ids)}
             self.steps += 1
         events = self.scheduler.apply(plan, tokens)
@@ -132,6 +143,10 @@ class RoostEngine:
             if e.finish_reason is not None:
                 self._seeds.pop(e.request_id, None)
         return events
+
+    def _decode_only(self) -> bool:
+        """Every live request has its prompt in the cache: the next step can only be one more token for each."""
+        return all(s.computed >= s.prompt_len and s.request_id in self.executor.cache for s in self.scheduler.sequences())
 
     # ------------------------------------------------------------------ completions
     def generate(self, prompts: list, options: GenerationOptions | list | None = None) -> list[Completion]:

@@ -39,6 +39,15 @@ class StepError(ValueError):
     """A step that was refused before anything was launched."""
 
 
+@dataclass
+class PreparedDecode:
+    """The tables of a decode step made before its token ids are known (see ``StepExecutor.prepare_decode``)."""
+    request_ids: list
+    starts: list
+    graph: object
+    staged: int       # the pinned buffer of the graph's tables that holds this step's tables; section 0 is the token ids
+
+
 class DecodeGraph:
     """A captured CUDA graph of one decode step (every row brings one token and wants its logits) for a fixed number
     of rows and a bound on the requests' lengths. The step's tables live at fixed device addresses; a replay uploads
@@ -80,6 +89,13 @@ class DecodeGraph:
         self.static.upload(self._pending, self.fills)
         if self.graph is None:
             return self._capture(ht)
+        self.graph.replay()
+        self.ex.rt.kernels.launches += self.launches
+        return self.out.clone()
+
+    def run_staged(self, staged: int) -> torch.Tensor:
+        """A replay with tables staged earlier (the graph is captured already)."""
+        self.static.send(staged)
         self.graph.replay()
         self.ex.rt.kernels.launches += self.launches
         return self.out.clone()
@@ -142,6 +158,7 @@ class StepExecutor:
         self._graphs: dict = {}
         self._plan_keys: list | None = None
         self.graph_replays = 0
+        self.prepared_replays = 0    # replays whose tables were made while the step before was still running
 
     # ------------------------------------------------------------------ one step
     def step(self, entries: list[StepEntry]) -> torch.Tensor:
@@ -221,6 +238,62 @@ class StepExecutor:
         self.last_upload_bytes = g.static.total * 4
         self.graph_replays += 1
         return g.run(ht)
+
+    # ------------------------------------------------------------------ a decode step prepared ahead of its tokens
+    def prepare_decode(self, request_ids: list) -> PreparedDecode | None:
+        """Everything of the next decode step of these requests (one token each, logits wanted) that does not depend on
+        the tokens' values: pages, tables, attention work lists. A caller makes it while the device still runs the step
+        before, and hands it to ``run_prepared`` with the tokens once they are known; when the next step turns out to be
+        another one, the preparation is simply dropped (the pages it took belong to their requests and go back with
+        them). None when the step cannot be prepared: no captured graph serves it yet, or pages are short."""
+        if not self.use_graphs or self._plan_keys is None or not request_ids:
+            return None
+        max_pos = self.model.spec.max_positions
+        need = [0] * len(self.groups)
+        starts = []
+        for rid in request_ids:
+            if rid not in self.cache:
+                return None
+            start = self.cache.get(rid).tokens
+            if max_pos and start + 1 > max_pos:
+                return None
+            starts.append(start)
+            for gi, n in enumerate(self.cache.pages_needed(rid, start + 1)):
+                need[gi] += n
+        if any(n > self.cache.pools[gi].free_count for gi, n in enumerate(need)):
+            return None
+        rows = [(self.cache.extend(rid, start + 1), start, [0], [0]) for rid, start in zip(request_ids, starts)]
+        ht = self.builder.host_tables(rows, self.model.spec.vocab)
+        kv_cap = -(-ht.max_kv_len // GRAPH_KV_GRANULE) * GRAPH_KV_GRANULE
+        g = self._graphs.get((ht.num_rows, kv_cap))
+        if g is None or g.graph is None or not g.fits(ht):
+            return None
+        return PreparedDecode(list(request_ids), starts, g, g.static.stage(g._pending, g.fills))
+
+    def matches_prepared(self, prep: PreparedDecode, entries: list[StepEntry]) -> bool:
+        return (len(entries) == len(prep.request_ids) and prep.graph.graph is not None
+                and self._graphs.get((prep.graph.num_rows, prep.graph.kv_cap)) is prep.graph
+                and all(e.request_id == rid and len(e.tokens) == 1 and list(e.want) == [0] and (e.start is None or e.start == st)
+                        and rid in self.cache and self.cache.get(rid).tokens == st
+                        for e, rid, st in zip(entries, prep.request_ids, prep.starts)))
+
+    def run_prepared(self, prep: PreparedDecode, entries: list[StepEntry]) -> torch.Tensor:
+        """The step ``prepare_decode`` prepared, with its tokens. Call only when ``matches_prepared`` holds."""
+        vocab = self.model.spec.vocab
+        ids = prep.graph.static.staged(prep.staged, 0)
+        for i, e in enumerate(entries):
+            t = int(e.tokens[0])
+            if not 0 <= t < vocab:
+                raise ValueError(f"token id {t} is outside the vocabulary of {vocab}")
+            ids[i] = t
+        logits = prep.graph.run_staged(prep.staged)
+        self.last_upload_bytes = prep.graph.static.total * 4
+        self.graph_replays += 1
+        self.prepared_replays += 1
+        for rid, st in zip(prep.request_ids, prep.starts):
+            self.cache.commit(rid, st + 1)
+        self.steps_run += 1
+        return logits
 
     def _zero_new_state(self, rows) -> None:
         """A request's fixed-size state starts at zero when its first token arrives, as the reference's worker

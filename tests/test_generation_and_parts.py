@@ -63,6 +63,9 @@ def test_greedy_generation_through_the_entry_point(tiny_model_dirs, backend, nam
                 assert tok == int(top.indices[0]), f"step {len(seq) - len(prompt)}: engine {tok}, plain {int(top.indices[0])} (gap {gap:.3g})"
             seq.append(tok)
     assert engine.executor.cache.pools[0].free_count == 64       # every page came back
+    if kind == "gpu":
+        # decode steps replayed captured graphs, most of them with tables made while the step before was still running
+        assert engine.executor.graph_replays > 0 and engine.executor.prepared_replays > 0
     # the same prompts one at a time give the same tokens as the batch did
     alone = [engine.generate([p], GenerationOptions(max_output_tokens=16, ignore_eos=True))[0].token_ids for p in prompts]
     if dtype == torch.float32:
