@@ -607,14 +607,16 @@ __global__ void __launch_bounds__(NWARPS * 32)
 // The same chunks, streamed by the copy engine through one ring of shared-memory stages per CTA. The CTAs are persistent:
 // CTA c takes the (chunk, key/value head) pairs c, c + G, c + 2G, ... of the work list, and the ring keeps running
 // across them, so the loads of the next chunk are in flight while the last tiles of this one are computed and merged.
-//   warp 4 (producer): per chunk it reads the chunk's row of the step tables, publishes them to the consumers through a
-//     two-entry descriptor ring, and walks the chunk in tiles of 32 keys: it looks the pages up (32 block-table entries
-//     a load, one batch ahead, kept one a lane as pool rows), waits for a free stage and issues one tensor copy per page
-//     that brings the page's keys and values (a 4-D box over the pool: 64 columns x rows x column blocks x {K, V}) into
-//     128-byte-swizzled shared memory; the copies complete on the stage's barrier.
-//   warps 0..3 (consumers): tile g of the CTA's stream goes to warp g % 4. Each keeps the query fragments in registers
-//     and a running state of its own, hands the stage back after its products, and the four merge through shared memory
-//     in warp order when the chunk ends, four packed rows a pass.
+//   warp 4 (producer): per chunk it reads the chunk's row of the step tables (one chunk ahead, in three dependent rounds
+//     spread over the tiles of the chunk before, so that their latencies are hidden), copies the chunk's Q tile into a
+//     two-entry ring and publishes the chunk's facts beside it (the descriptor's barrier completes when both are in
+//     shared memory), and walks the chunk in tiles of 32 keys: it looks the pages up (32 block-table entries a load,
+//     kept one a lane as pool rows), waits for a free stage and issues one tensor copy per page that brings the page's
+//     keys and values (a 4-D box over the pool: 64 columns x rows x column blocks x {K, V}) into 128-byte-swizzled
+//     shared memory; the copies complete on the stage's barrier.
+//   warps 0..3 (consumers): tile g of the CTA's stream goes to warp g % 4. Each takes the query fragments into registers
+//     when a chunk begins, keeps a running state of its own, hands the stage back after its products, and the four
+//     merge through shared memory in warp order when the chunk ends, two packed rows a pass.
 // A page is copied whole: rows of a tile that lie outside the row's visible keys hold whatever the pool holds there.
 // Their scores are masked by position; their value rows are zeroed in shared memory by the consuming warp before the
 // second product (only the first and last tile of a chunk have such rows), so nothing outside the visible range reaches
@@ -623,7 +625,7 @@ __global__ void __launch_bounds__(NWARPS * 32)
 // returns, and the CTA lets its copies land before it exits.
 constexpr int kTmaTileKeys = 32;
 constexpr int kTmaConsumers = 4;
-constexpr int kTmaMergeRows = 4;  // packed rows merged per pass
+constexpr int kTmaMergeRows = 2;  // packed rows merged per pass
 __device__ int g_attention_error = 0;
 
 // A tile of TK keys as the copies leave it: [page of RPC rows][K, V][D / 64 column blocks][RPC][64 bfloat16], 128-byte
@@ -662,7 +664,7 @@ __global__ void __launch_bounds__((kTmaConsumers + 1) * 32, 2)
   const uint32_t smem_base = ((uint32_t)__cvta_generic_to_shared(smem_raw) + 1023u) & ~1023u;
   unsigned char* smem_gen = smem_raw + (smem_base - (uint32_t)__cvta_generic_to_shared(smem_raw));
   const uint32_t q_smem = smem_base + STAGES * kStageBytes;
-  float* sm_o = reinterpret_cast<float*>(smem_gen + STAGES * kStageBytes + kQBytes);  // [NW][MR][kScratchStride]
+  float* sm_o = reinterpret_cast<float*>(smem_gen + STAGES * kStageBytes + 2 * kQBytes);  // [NW][MR][kScratchStride]
   float* sm_ml = sm_o + NW * MR * kScratchStride;                                      // [NW][MR][2]
   __shared__ __align__(8) uint64_t bars[2 * STAGES + 4];
   __shared__ DecodeChunk desc[2];
@@ -682,7 +684,7 @@ __global__ void __launch_bounds__((kTmaConsumers + 1) * 32, 2)
       mbar_init(empty_bar(st), 1);
     }
     for (int d = 0; d < 2; ++d) {
-      mbar_init(desc_full(d), 1);
+      mbar_init(desc_full(d), 33);  // the producer's 32 copy completions and its descriptor
       mbar_init(desc_empty(d), NW);
     }
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -696,52 +698,91 @@ __global__ void __launch_bounds__((kTmaConsumers + 1) * 32, 2)
 
   if (warp == NW) {
     // ---- producer: all lanes walk the loops (a lane holds one block-table entry of the current 32, as the pool row its
-    // page starts at); lane 0 waits, publishes and issues
+    // page starts at); lane 0 waits, publishes and issues. What the next chunk needs from the step tables is fetched in
+    // three dependent rounds (work item; the row's lengths; its block-table entries) spread over the tiles of this one.
     constexpr int COPIES = TK / RPC;
     const int page_shift = 31 - __clz(page_size);  // a power of two here
     bool ok = true;
     int g = 0;  // tiles issued so far
-    int k = 0;  // chunks published so far
-    for (long long f = blockIdx.x; ok; f += gridDim.x, ++k) {
-      DecodeChunk c;
-      c.b = -1;
-      if (f < total) {
-        const int4 w = work[f / kv_heads];
-        c.b = w.x;  // padding entries (batch row -1) end the list
-        if (c.b >= 0) {
-          c.kvh = (int)(f % kv_heads);
-          c.slot = w.w;
-          c.q_start = q_indptr[c.b];
-          c.n = q_indptr[c.b + 1] - c.q_start;
-          c.kv_len = kv_lens[c.b];
-          const int pos0 = c.kv_len - c.n;
-          c.hi = min(w.z - 1, c.kv_len - 1);
-          c.lo = max(w.y, window > 0 ? max(0, pos0 - window + 1) : 0);
-          c.t0 = c.lo / TK;
-          c.ntiles = c.hi >= c.lo ? (c.hi / TK - c.t0 + 1) : 0;
+    // the chunk being fetched: work item (round 1), row facts (round 2), chunk and block-table entries (round 3)
+    long long nf = blockIdx.x;
+    int4 nw = make_int4(-1, 0, 0, 0);
+    int nq0 = 0, nq1 = 0, nkvl = 0, ntbl = 0;
+    DecodeChunk nc;
+    int n_fallback = 0, n_cur = -1, n_nxt = -1;
+    auto round1 = [&]() { nw = nf < total ? work[nf / kv_heads] : make_int4(-1, 0, 0, 0); };
+    auto round2 = [&]() {
+      if (nw.x >= 0) {
+        nq0 = q_indptr[nw.x];
+        nq1 = q_indptr[nw.x + 1];
+        nkvl = kv_lens[nw.x];
+        ntbl = kv_indptr[nw.x];
+      }
+    };
+    auto round3 = [&]() {
+      nc.b = nw.x;  // padding entries (batch row -1) end the list
+      nc.ntiles = 0;
+      if (nc.b >= 0) {
+        nc.kvh = (int)(nf % kv_heads);
+        nc.slot = nw.w;
+        nc.q_start = nq0;
+        nc.n = nq1 - nq0;
+        nc.kv_len = nkvl;
+        const int pos0 = nc.kv_len - nc.n;
+        nc.hi = min(nw.z - 1, nc.kv_len - 1);
+        nc.lo = max(nw.y, window > 0 ? max(0, pos0 - window + 1) : 0);
+        nc.t0 = nc.lo / TK;
+        nc.ntiles = nc.hi >= nc.lo ? (nc.hi / TK - nc.t0 + 1) : 0;
+        if (nc.ntiles > 0) {
+          const int32_t* pages = kv_indices + ntbl;
+          const int p_first = (nc.t0 * TK) >> page_shift, p_last = nc.hi >> page_shift;
+          n_fallback = pages[p_last];
+          n_cur = p_first + lane <= p_last ? pages[p_first + lane] : -1;
+          n_nxt = p_first + 32 + lane <= p_last ? pages[p_first + 32 + lane] : -1;
         }
       }
-      if (lane == 0) {
-        if (k >= 2) ok = mbar_wait_limited(desc_empty(k & 1), (uint32_t)((k >> 1) - 1) & 1u, abortp, 4, &g_attention_error);
-        if (ok) {
-          desc[k & 1] = c;
-          mbar_arrive(desc_full(k & 1));  // releases the descriptor to the consumers
-        }
+    };
+    round1();
+    round2();
+    round3();
+    for (int k = 0; ok; ++k) {
+      const DecodeChunk c = nc;
+      const int fallback = n_fallback;
+      const int first_entry = n_cur;
+      int nxt_entry = n_nxt;
+      const int32_t* pages = kv_indices + ntbl;
+      nf += gridDim.x;
+      int rounds = 0;  // rounds of the next chunk's fetch done so far
+      if (c.b >= 0) {
+        round1();
+        rounds = 1;
       }
+      if (lane == 0 && k >= 2) ok = mbar_wait_limited(desc_empty(k & 1), (uint32_t)((k >> 1) - 1) & 1u, abortp, 4, &g_attention_error);
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-      if (c.b < 0 || !ok) break;
-      if (c.ntiles == 0) continue;
-      const int32_t* pages = kv_indices + kv_indptr[c.b];
+      if (!ok) break;
+      // the chunk's Q tile, then the descriptor: the barrier completes when both are in shared memory
+      if (c.b >= 0) load_q_tile<D, 16, 32>(q_smem + (k & 1) * kQBytes, q, c.q_start, q_heads, group, c.kvh, 0, c.n * group, lane);
+      asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];\n" ::"r"(desc_full(k & 1)) : "memory");
+      if (lane == 0) {
+        desc[k & 1] = c;
+        mbar_arrive(desc_full(k & 1));  // releases the descriptor to the consumers
+      }
+      if (c.b < 0) break;
       const int p_first = (c.t0 * TK) >> page_shift, p_last = c.hi >> page_shift;
-      const int fallback = pages[p_last];
       auto row_of = [&](int p, int entry) {  // first pool row of page p of the request, given its block-table entry
         const bool visible = ((p + 1) << page_shift) > c.lo && (p << page_shift) <= c.hi;
         return ((visible && entry >= 0 ? entry : fallback) * kv_heads + c.kvh) << page_shift;
       };
       int batch0 = p_first;  // the page lane 0 holds
-      int cur = row_of(batch0 + lane, batch0 + lane <= p_last ? pages[batch0 + lane] : -1);
-      int nxt_entry = batch0 + 32 + lane <= p_last ? pages[batch0 + 32 + lane] : -1;
+      int cur = row_of(batch0 + lane, first_entry);
       for (int i = 0; i < c.ntiles && ok; ++i, ++g) {
+        if (i == 2 && rounds == 1) {
+          round2();
+          rounds = 2;
+        } else if (i == 5 && rounds == 2) {
+          round3();
+          rounds = 3;
+        }
         const int stage = g % STAGES;
         const uint32_t dst = smem_base + stage * kStageBytes;
         const int j = (c.t0 + i) * TK;
@@ -766,6 +807,8 @@ __global__ void __launch_bounds__((kTmaConsumers + 1) * 32, 2)
         }
         ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
       }
+      if (rounds < 2) round2();
+      if (rounds < 3) round3();
     }
     if (*abortp) {  // copies in flight land before the CTA's shared memory is given back
       const long long c0 = clock64();
@@ -780,21 +823,16 @@ __global__ void __launch_bounds__((kTmaConsumers + 1) * 32, 2)
   for (int k = 0; ok; ++k) {
     if (!(ok = mbar_wait_limited(desc_full(k & 1), (uint32_t)(k >> 1) & 1u, abortp, 5, &g_attention_error))) break;
     const DecodeChunk c = desc[k & 1];
-    __syncwarp();
-    if (lane == 0) mbar_arrive(desc_empty(k & 1));  // this warp holds the descriptor in registers
     if (c.b < 0) break;
     const int rows_total = c.n * group;  // at most 16
     const int pos0 = c.kv_len - c.n;
-    // every warp is past its reads of the previous chunk's Q tile and merge scratch (the barriers that end a chunk)
-    load_q_tile<D, 16, NW * 32>(q_smem, q, c.q_start, q_heads, group, c.kvh, 0, rows_total, tid);
-    cp_async_commit();
-    cp_async_wait<0>();
-    asm volatile("bar.sync 1, %0;\n" ::"n"(NW * 32) : "memory");
     uint32_t qf[D / 16][4];
 #pragma unroll
     for (int kk = 0; kk < D / 16; ++kk) {
-      ldmatrix_x4(q_smem + Tile<D>::offset(lane & 15, kk * 2 + (lane >> 4)), qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3]);
+      ldmatrix_x4(q_smem + (k & 1) * kQBytes + Tile<D>::offset(lane & 15, kk * 2 + (lane >> 4)), qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3]);
     }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(desc_empty(k & 1));  // this warp holds the descriptor and the Q fragments in registers
     int qpos[2], qlo[2];
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
@@ -997,7 +1035,7 @@ static int launch_decode_tma(const void* q, void* out, const void* k_pool, const
   const int box_rows = page_size < kTmaTileKeys ? page_size : kTmaTileKeys;
   const int rc = make_pool_map(&map, k_pool, v_pool, pool_pages * kv_heads * page_size, D, box_rows);
   if (rc != ROOST_OK) return rc;
-  constexpr size_t smem = (size_t)tma_decode_stages<D>() * 2 * kTmaTileKeys * D * 2 + 16 * D * 2 +
+  constexpr size_t smem = (size_t)tma_decode_stages<D>() * 2 * kTmaTileKeys * D * 2 + 2 * 16 * D * 2 +
                           (size_t)kTmaConsumers * kTmaMergeRows * (D + 8 + 2) * 4 + 1024;
   static int sms = 0;
   if (sms == 0) {
