@@ -1,0 +1,160 @@
+"""Times single kernels of the library on synthetic inputs, with CUDA events on the launching stream.
+
+    python -m roost_b200.kernels.microbench attention-decode --batch 64 --context 4096
+    python -m roost_b200.kernels.microbench attention-prefill --tokens 8192
+    python -m roost_b200.kernels.microbench gemm-small --rows 8
+    python -m roost_b200.kernels.microbench gemm-large --rows 2048
+
+Each case prints one line per measurement: the time of one call, the achieved bandwidth or arithmetic rate, and what
+the same bytes or operations would take at the device's measured peaks when a peak is given. The inputs are larger
+than L2 (or rotate through several copies) so that DRAM figures mean something. It is the program the kernel profiles
+under ``profiles/`` were taken with (``--iters 2 --warmup 1`` under a profiler).
+"""
+from __future__ import annotations
+
+import argparse
+import math
+import sys
+
+
+def _time(fn, warmup: int, iters: int) -> float:
+    """Microseconds of one call."""
+    import torch
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    total = 0.0
+    for _ in range(iters):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        total += e0.elapsed_time(e1)
+    return total / iters * 1e3
+
+
+def _graph_time(fns: list, warmup: int, iters: int) -> float:
+    """Microseconds of one call when the calls of ``fns`` are replayed back to back from one CUDA graph."""
+    import torch
+    for f in fns:
+        f()
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for f in fns:
+            f()
+    torch.cuda.current_stream().wait_stream(side)
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for f in fns:
+            f()
+    return _time(g.replay, warmup, iters) / len(fns)
+
+
+def attention_decode(k, a) -> None:
+    import torch
+
+    from ..engine.batch import plan_attention
+    nq, nkv, d, page = a.q_heads, a.kv_heads, a.head_dim, a.page_size
+    pages_per = -(-a.context // page)
+    npages = pages_per * a.batch
+    pool = torch.randn(2, npages, nkv, page, d, device="cuda", dtype=torch.bfloat16)   # keys then values, as the cache holds them
+    q = torch.randn(a.batch, nq, d, device="cuda", dtype=torch.bfloat16)
+    chunk = a.chunk or k.decode_chunk
+    plan = plan_attention([a.context - 1] * a.batch, [1] * a.batch, nq // nkv, None, chunk, "cuda", 64)
+    q_indptr = torch.arange(a.batch + 1, dtype=torch.int32, device="cuda")
+    kv_lens = torch.full((a.batch,), a.context, dtype=torch.int32, device="cuda")
+    kv_indptr = torch.arange(a.batch + 1, dtype=torch.int32, device="cuda") * pages_per
+    gen = torch.Generator(device="cuda").manual_seed(0)
+    kv_indices = (torch.arange(npages, device="cuda") if a.sequential_pages else torch.randperm(npages, device="cuda", generator=gen)).to(torch.int32)
+    k.attention_set_decode_tma(not a.cp_async)
+    us = _time(lambda: k.attention_mma(q, pool[0], pool[1], q_indptr, kv_lens, kv_indptr, kv_indices, plan, d ** -0.5, None), a.warmup, a.iters)
+    nbytes = a.batch * a.context * nkv * d * 2 * 2
+    print(f"attention-decode batch={a.batch} context={a.context} chunk={chunk} items={plan.decode_items} "
+          f"{'cp.async' if a.cp_async else 'tma'}: {us:.1f} us, {nbytes / us / 1e6:.2f} TB/s of keys and values "
+          f"(decode and merge kernels, eager launches), status {k.attention_status()}", flush=True)
+
+
+def attention_prefill(k, a) -> None:
+    import torch
+
+    from ..engine.batch import plan_attention
+    nq, nkv, d, page = a.q_heads, a.kv_heads, a.head_dim, a.page_size
+    T = a.tokens
+    pages_per = -(-T // page)
+    npages = pages_per * a.batch
+    pool = torch.randn(2, npages, nkv, page, d, device="cuda", dtype=torch.bfloat16)
+    q = torch.randn(T * a.batch, nq, d, device="cuda", dtype=torch.bfloat16)
+    group = nq // nkv
+    rows = a.tile_rows or k.attention_prefill_tile_rows(d, T * a.batch * group, nkv)
+    plan = plan_attention([0] * a.batch, [T] * a.batch, group, None, k.decode_chunk, "cuda", rows)
+    q_indptr = torch.arange(a.batch + 1, dtype=torch.int32, device="cuda") * T
+    kv_lens = torch.full((a.batch,), T, dtype=torch.int32, device="cuda")
+    kv_indptr = torch.arange(a.batch + 1, dtype=torch.int32, device="cuda") * pages_per
+    kv_indices = torch.randperm(npages, device="cuda").to(torch.int32)
+    us = _time(lambda: k.attention_mma(q, pool[0], pool[1], q_indptr, kv_lens, kv_indptr, kv_indices, plan, d ** -0.5, None), a.warmup, a.iters)
+    flops = 4 * T * T / 2 * nq * d * a.batch
+    print(f"attention-prefill tokens={T} batch={a.batch} heads={nq}/{nkv} head_dim={d} tile_rows={rows}: {us:.1f} us, "
+          f"{flops / us / 1e6:.0f} TFLOP/s (causal half counted)", flush=True)
+
+
+def gemm_small(k, a) -> None:
+    import torch
+    shapes = [(a.n, a.k)] if a.n and a.k else [(6144, 4096), (4096, 4096), (24576, 4096), (4096, 12288)]
+    for n, kk in shapes:
+        copies = max(4, int(600e6 // (n * kk * 2)))     # rotate through more than L2 holds
+        ws = [torch.randn(n, kk, device="cuda", dtype=torch.bfloat16) for _ in range(copies)]
+        x = torch.randn(a.rows, kk, device="cuda", dtype=torch.bfloat16)
+        t_stream = _graph_time([(lambda w=w: k.gemm_stream(x, w)) for w in ws], a.warmup, a.iters)
+        t_lib = _graph_time([(lambda w=w: torch.matmul(x, w.t())) for w in ws], a.warmup, a.iters)
+        print(f"gemm-small rows={a.rows} n={n} k={kk}: stream {t_stream:.1f} us ({n * kk * 2 / t_stream / 1e6:.2f} TB/s of weights), "
+              f"cuBLAS {t_lib:.1f} us, in one graph back to back; status {k.gemm_tcgen05_status()}", flush=True)
+
+
+def gemm_large(k, a) -> None:
+    import torch
+    shapes = [(a.n, a.k)] if a.n and a.k else [(6144, 4096), (4096, 4096), (24576, 4096), (4096, 12288)]
+    for n, kk in shapes:
+        w = torch.randn(n, kk, device="cuda", dtype=torch.bfloat16)
+        x = torch.randn(a.rows, kk, device="cuda", dtype=torch.bfloat16)
+        flops = 2.0 * a.rows * n * kk
+        for pairs in (True, False):
+            k.gemm_tcgen05_set_pairs(pairs)
+            us = _time(lambda: k.gemm_tcgen05(x, w), a.warmup, a.iters)
+            print(f"gemm-large rows={a.rows} n={n} k={kk} tcgen05 {'CTA pairs' if pairs else 'single CTAs'}: {us:.1f} us, {flops / us / 1e6:.0f} TFLOP/s",
+                  flush=True)
+        k.gemm_tcgen05_set_pairs(True)
+        us = _time(lambda: torch.matmul(x, w.t()), a.warmup, a.iters)
+        print(f"gemm-large rows={a.rows} n={n} k={kk} cuBLAS: {us:.1f} us, {flops / us / 1e6:.0f} TFLOP/s; status {k.gemm_tcgen05_status()}", flush=True)
+
+
+def main(argv=None) -> int:
+    p = argparse.ArgumentParser(prog="python -m roost_b200.kernels.microbench", description=__doc__.split("\n")[0])
+    p.add_argument("case", choices=["attention-decode", "attention-prefill", "gemm-small", "gemm-large"])
+    p.add_argument("--batch", type=int, default=8)
+    p.add_argument("--context", type=int, default=4096)
+    p.add_argument("--tokens", type=int, default=2048)
+    p.add_argument("--rows", type=int, default=8)
+    p.add_argument("--n", type=int, default=0)
+    p.add_argument("--k", type=int, default=0)
+    p.add_argument("--q-heads", type=int, default=32)
+    p.add_argument("--kv-heads", type=int, default=8)
+    p.add_argument("--head-dim", type=int, default=128)
+    p.add_argument("--page-size", type=int, default=16)
+    p.add_argument("--chunk", type=int, default=0, help="keys per decode work item (default: the library's)")
+    p.add_argument("--tile-rows", type=int, default=0, help="packed rows per prefill work item (default: the library's choice)")
+    p.add_argument("--cp-async", action="store_true", help="decode attention through the cp.async kernel instead of TMA")
+    p.add_argument("--sequential-pages", action="store_true")
+    p.add_argument("--iters", type=int, default=10)
+    p.add_argument("--warmup", type=int, default=3)
+    a = p.parse_args(argv)
+    from . import library
+    k = library.load()
+    {"attention-decode": attention_decode, "attention-prefill": attention_prefill, "gemm-small": gemm_small, "gemm-large": gemm_large}[a.case](k, a)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
