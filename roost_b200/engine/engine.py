@@ -138,11 +138,21 @@ class RoostEngine:
                 ids = ids_device.cpu().tolist()
                 tokens = {r.sequence.request_id: t for r, t in zip(sampling_rows, ids)}
             self.steps += 1
+            if self.steps % self.STATUS_EVERY == 0:
+                self.check_device()
         events = self.scheduler.apply(plan, tokens)
         for e in events:
             if e.finish_reason is not None:
                 self._seeds.pop(e.request_id, None)
         return events
+
+    STATUS_EVERY = 256   # steps between looks at the kernels' status words
+
+    def check_device(self) -> None:
+        """Raises if a kernel gave up one of its bounded waits since the last look (its results were then not valid)."""
+        check = getattr(self.model.rt.kernels, "check_device_status", None)
+        if check is not None:
+            check()
 
     def _decode_only(self) -> bool:
         """Every live request has its prompt in the cache: the next step can only be one more token for each."""

@@ -48,6 +48,7 @@ def main(argv=None) -> int:
             logits = executor.step(entries)
             if logits.shape[0] > 0:
                 logits.to("cpu", torch.float32).contiguous().numpy().astype("<f4").tofile(out_dir / f"{step}.f32")
+            model.rt.kernels.check_device_status()   # a kernel that gave up a bounded wait makes the step an error, not a file
         for rid in rec.get("end", []):
             executor.finish(rid)
         print(f"done {step}", flush=True)
