@@ -165,7 +165,7 @@ def timed_decode(model, batch: int, context: int, steps: int, warmup: int):
     return batch / (ms / 1e3), ms, launches, clocks.summary()
 
 
-def timed_prefill(model, tokens_n: int, warmup: int = 3, iters: int = 3):
+def timed_prefill(model, tokens_n: int, warmup: int = 3, iters: int = 6):
     import torch
 
     from roost_b200.engine.executor import StepEntry, StepExecutor

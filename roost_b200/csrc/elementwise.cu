@@ -113,6 +113,28 @@ struct Vec<__nv_bfloat16> {
 
 constexpr int kMaxVec = 4;
 
+// N consecutive weights starting at element i (a multiple of N; the vector is then 8-byte aligned at least).
+template <int N>
+__device__ __forceinline__ void load_w_vec(const void* w, int i, int wdtype, float (&o)[N]) {
+  static_assert(N == 4 || N == 8, "vectors of four or eight elements");
+  if (wdtype == ROOST_F32) {
+    const float4* p = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(w) + i);
+#pragma unroll
+    for (int k = 0; k < N / 4; ++k) {
+      const float4 f = p[k];
+      o[4 * k] = f.x; o[4 * k + 1] = f.y; o[4 * k + 2] = f.z; o[4 * k + 3] = f.w;
+    }
+  } else {
+    const uint2* p = reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(w) + i);
+#pragma unroll
+    for (int k = 0; k < N / 4; ++k) {
+      const uint2 u = p[k];
+      o[4 * k] = __uint_as_float(u.x << 16); o[4 * k + 1] = __uint_as_float(u.x & 0xffff0000u);
+      o[4 * k + 2] = __uint_as_float(u.y << 16); o[4 * k + 3] = __uint_as_float(u.y & 0xffff0000u);
+    }
+  }
+}
+
 template <typename T, bool ADD>
 __global__ void rms_norm_vec_kernel(const T* __restrict__ x, T* residual, const void* __restrict__ w, T* __restrict__ out,
                                     const int32_t* __restrict__ rows, int hidden, float eps, int wdtype) {
@@ -147,9 +169,10 @@ __global__ void rms_norm_vec_kernel(const T* __restrict__ x, T* residual, const 
   for (int k = 0; k < kMaxVec; ++k) {
     const int vi = threadIdx.x + k * blockDim.x;
     if (vi < nvec) {
-      float o[N];
+      float o[N], wv[N];
+      load_w_vec<N>(w, vi * N, wdtype, wv);
 #pragma unroll
-      for (int e = 0; e < N; ++e) o[e] = v[k][e] * inv * load_w(w, vi * N + e, wdtype);
+      for (int e = 0; e < N; ++e) o[e] = v[k][e] * inv * wv[e];
       Vec<T>::store(out + (size_t)i_out * hidden + (size_t)vi * N, o);
     }
   }
@@ -202,7 +225,8 @@ static int launch_norm(const void* x, void* residual, const void* w, void* out, 
   // rows that are whole 16-byte vectors and fit in registers take the vectorised kernel
   {
     const int vec = dtype == ROOST_F32 ? 4 : 8;
-    const bool aligned = ((uintptr_t)x % 16 == 0) && ((uintptr_t)out % 16 == 0) && (!ADD || (uintptr_t)residual % 16 == 0);
+    const bool aligned = ((uintptr_t)x % 16 == 0) && ((uintptr_t)out % 16 == 0) && ((uintptr_t)w % 16 == 0) &&
+                         (!ADD || (uintptr_t)residual % 16 == 0);
     if (hidden % vec == 0 && aligned && (dtype == ROOST_F32 || dtype == ROOST_BF16)) {
       const int nvec = hidden / vec;
       int threads = ((nvec + 31) / 32) * 32;

@@ -24,114 +24,125 @@ __device__ __forceinline__ void store2(__nv_bfloat16* p, const float (&v)[2]) {
   *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(v[0], v[1]);
 }
 
-// One warp per (token, head slot); head slots are q heads, then k heads, then v heads. vector_ok: every head row of
-// qkv, q_out and the pools starts on a 16-byte boundary (head_dim a multiple of 8 elements, aligned bases and stride).
-template <typename T>
+// One block per token (and, for few tokens, per group of head slots); a warp takes head slots in turn. Head slots are
+// q heads, then k heads, then v heads. The rotation's cosines and sines depend on the token's position only: with TABLE
+// the block computes them once into shared memory and every head of the token uses them (many tokens: the arithmetic
+// is the cost); without, every warp computes its own while its loads are in flight (few tokens: the latency is). vector_ok: every head row of qkv, q_out
+// and the pools starts on a 16-byte boundary (head_dim a multiple of 8 elements, aligned bases and stride).
+template <typename T, bool TABLE>
 __global__ void qk_norm_rope_cache_kernel(const T* __restrict__ qkv, int64_t qkv_stride, T* __restrict__ q_out,
                                           T* __restrict__ k_pool, T* __restrict__ v_pool, const void* __restrict__ q_w,
                                           const void* __restrict__ k_w, const double* __restrict__ inv_freq,
                                           const int32_t* __restrict__ positions, const int32_t* __restrict__ slot_mapping,
                                           int q_heads, int kv_heads, int head_dim, int rotary_dim, float eps, int page_size,
                                           int64_t pool_pages, int slots_per_token, int wdtype, bool vector_ok) {
+  extern __shared__ float2 cos_sin[];  // [rotary_dim / 2]
   const int lane = threadIdx.x & 31;
-  const int slot_idx = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int warps = blockDim.x >> 5;
   pdl_launch_dependents(3);
   pdl_wait(3);
-  if (slot_idx >= slots_per_token) return;
   const size_t t = blockIdx.x;
   const T* row = qkv + t * qkv_stride;
-
-  int kind, head;  // 0 q, 1 k, 2 v
-  if (slot_idx < q_heads) {
-    kind = 0; head = slot_idx;
-  } else if (slot_idx < q_heads + kv_heads) {
-    kind = 1; head = slot_idx - q_heads;
-  } else {
-    kind = 2; head = slot_idx - q_heads - kv_heads;
-  }
-  const T* src = row + (size_t)slot_idx * head_dim;  // [q heads | k heads | v heads], each head_dim wide
-
-  T* dst;
-  if (kind == 0) {
-    dst = q_out + (t * q_heads + head) * head_dim;
-  } else {
-    const int slot = slot_mapping[t];
-    if (slot < 0) return;
-    const int64_t page = slot / page_size;
-    const int off = slot % page_size;
-    if (page >= pool_pages) return;  // never write beyond the pool
-    T* pool = kind == 1 ? k_pool : v_pool;
-    dst = pool + ((page * kv_heads + head) * page_size + off) * head_dim;
-  }
-
-  if (kind == 2) {
-    if (vector_ok) {
-      constexpr int N = 16 / sizeof(T);
-      for (int i = lane * N; i < head_dim; i += 32 * N) *reinterpret_cast<uint4*>(dst + i) = *reinterpret_cast<const uint4*>(src + i);
-    } else {
-      for (int i = lane; i < head_dim; i += 32) dst[i] = src[i];
-    }
-    return;
-  }
-
-  const void* w = kind == 0 ? q_w : k_w;
-  float inv = 1.0f;
-  if (w != nullptr) {
-    float ss = 0.f;
-    for (int i = lane; i < head_dim; i += 32) {
-      const float v = to_float(src[i]);
-      ss += v * v;
-    }
-    ss = warp_sum(ss);
-    inv = 1.0f / sqrtf(ss / (float)head_dim + eps);
-  }
   const int half = rotary_dim / 2;
-  const double pos = (double)positions[t];
-  // rotated pairs (i, i + half); two neighbouring pairs at a time when the layout allows 2-element accesses
-  if (vector_ok && (half & 1) == 0) {
-    for (int i = lane * 2; i < half; i += 64) {
-      float a[2], b[2];
-      load2(src + i, a);
-      load2(src + i + half, b);
-      float o1[2], o2[2];
-#pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        float x1 = a[e], x2 = b[e];
-        if (w != nullptr) {
-          x1 = x1 * inv * load_w(w, i + e, wdtype);
-          x2 = x2 * inv * load_w(w, i + e + half, wdtype);
-        }
-        double ang = pos * inv_freq[i + e];
-        ang -= 6.283185307179586476925286766559 * rint(ang * 0.15915494309189533576888376337251);
-        float s, c;
-        sincosf((float)ang, &s, &c);
-        o1[e] = x1 * c - x2 * s;
-        o2[e] = x2 * c + x1 * s;
-      }
-      store2(dst + i, o1);
-      store2(dst + i + half, o2);
-    }
-  } else
-  for (int i = lane; i < half; i += 32) {
-    float x1 = to_float(src[i]);
-    float x2 = to_float(src[i + half]);
-    if (w != nullptr) {
-      // the normed value stays in 32-bit until the rotation has used it: one rounding per output element
-      x1 = x1 * inv * load_w(w, i, wdtype);
-      x2 = x2 * inv * load_w(w, i + half, wdtype);
-    }
+  const double pos = half > 0 ? (double)positions[t] : 0.0;
+  auto rotation = [&](int i) {  // (cos, sin) of the pair i
     double ang = pos * inv_freq[i];
     ang -= 6.283185307179586476925286766559 * rint(ang * 0.15915494309189533576888376337251);
-    float s, c;
-    sincosf((float)ang, &s, &c);
-    dst[i] = from_float<T>(x1 * c - x2 * s);
-    dst[i + half] = from_float<T>(x2 * c + x1 * s);
+    float sn, cs;
+    sincosf((float)ang, &sn, &cs);
+    return make_float2(cs, sn);
+  };
+  if (TABLE && half > 0) {
+    for (int i = threadIdx.x; i < half; i += blockDim.x) cos_sin[i] = rotation(i);
+    __syncthreads();
   }
-  // elements at and beyond rotary_dim are normed only
-  for (int i = rotary_dim + lane; i < head_dim; i += 32) {
-    float x = to_float(src[i]);
-    if (w != nullptr) x = x * inv * load_w(w, i, wdtype);
-    dst[i] = from_float<T>(x);
+
+  for (int slot_idx = blockIdx.y * warps + (threadIdx.x >> 5); slot_idx < slots_per_token; slot_idx += gridDim.y * warps) {
+    int kind, head;  // 0 q, 1 k, 2 v
+    if (slot_idx < q_heads) {
+      kind = 0; head = slot_idx;
+    } else if (slot_idx < q_heads + kv_heads) {
+      kind = 1; head = slot_idx - q_heads;
+    } else {
+      kind = 2; head = slot_idx - q_heads - kv_heads;
+    }
+    const T* src = row + (size_t)slot_idx * head_dim;  // [q heads | k heads | v heads], each head_dim wide
+
+    T* dst;
+    if (kind == 0) {
+      dst = q_out + (t * q_heads + head) * head_dim;
+    } else {
+      const int slot = slot_mapping[t];
+      if (slot < 0) continue;
+      const int64_t page = slot / page_size;
+      const int off = slot % page_size;
+      if (page >= pool_pages) continue;  // never write beyond the pool
+      T* pool = kind == 1 ? k_pool : v_pool;
+      dst = pool + ((page * kv_heads + head) * page_size + off) * head_dim;
+    }
+
+    if (kind == 2) {
+      if (vector_ok) {
+        constexpr int N = 16 / sizeof(T);
+        for (int i = lane * N; i < head_dim; i += 32 * N) *reinterpret_cast<uint4*>(dst + i) = *reinterpret_cast<const uint4*>(src + i);
+      } else {
+        for (int i = lane; i < head_dim; i += 32) dst[i] = src[i];
+      }
+      continue;
+    }
+
+    const void* w = kind == 0 ? q_w : k_w;
+    float inv = 1.0f;
+    if (w != nullptr) {
+      float ss = 0.f;
+      for (int i = lane; i < head_dim; i += 32) {
+        const float v = to_float(src[i]);
+        ss += v * v;
+      }
+      ss = warp_sum(ss);
+      inv = 1.0f / sqrtf(ss / (float)head_dim + eps);
+    }
+    // rotated pairs (i, i + half); two neighbouring pairs at a time when the layout allows 2-element accesses
+    if (vector_ok && (half & 1) == 0) {
+      for (int i = lane * 2; i < half; i += 64) {
+        float a[2], b[2];
+        load2(src + i, a);
+        load2(src + i + half, b);
+        float o1[2], o2[2];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          float x1 = a[e], x2 = b[e];
+          if (w != nullptr) {
+            x1 = x1 * inv * load_w(w, i + e, wdtype);
+            x2 = x2 * inv * load_w(w, i + e + half, wdtype);
+          }
+          const float2 r = TABLE ? cos_sin[i + e] : rotation(i + e);
+          o1[e] = x1 * r.x - x2 * r.y;
+          o2[e] = x2 * r.x + x1 * r.y;
+        }
+        store2(dst + i, o1);
+        store2(dst + i + half, o2);
+      }
+    } else {
+      for (int i = lane; i < half; i += 32) {
+        float x1 = to_float(src[i]);
+        float x2 = to_float(src[i + half]);
+        if (w != nullptr) {
+          // the normed value stays in 32-bit until the rotation has used it: one rounding per output element
+          x1 = x1 * inv * load_w(w, i, wdtype);
+          x2 = x2 * inv * load_w(w, i + half, wdtype);
+        }
+        const float2 r = TABLE ? cos_sin[i] : rotation(i);
+        dst[i] = from_float<T>(x1 * r.x - x2 * r.y);
+        dst[i + half] = from_float<T>(x2 * r.x + x1 * r.y);
+      }
+    }
+    // elements at and beyond rotary_dim are normed only
+    for (int i = rotary_dim + lane; i < head_dim; i += 32) {
+      float x = to_float(src[i]);
+      if (w != nullptr) x = x * inv * load_w(w, i, wdtype);
+      dst[i] = from_float<T>(x);
+    }
   }
 }
 
@@ -156,16 +167,23 @@ extern "C" int roost_qk_norm_rope_cache(const void* qkv, int64_t qkv_stride, voi
   }
   if (tokens == 0) return ROOST_OK;
   const int slots = q_heads + (write_kv ? 2 * kv_heads : 0);
-  const int warps = 4;
-  dim3 grid(tokens, (slots + warps - 1) / warps);
+  // many tokens: one block of eight warps a token, the rotation table computed once a token; few tokens: four head
+  // slots a block, so that a decode step still spreads over the device
+  const bool many = tokens >= 512;
+  const int warps = many ? 8 : 4;
+  dim3 grid(tokens, many ? 1 : (slots + warps - 1) / warps);
   if (grid.y > 65535) return fail(ROOST_ERR_UNSUPPORTED, "qk_norm_rope_cache: more than 262140 head slots per token");
+  const size_t table_bytes = (size_t)(rotary_dim / 2) * sizeof(float2);
+  if (table_bytes > 48 * 1024) return fail(ROOST_ERR_UNSUPPORTED, "qk_norm_rope_cache: a rotary width beyond 12288");
   const size_t esize = dtype == ROOST_F32 ? 4 : 2;
   const bool vector_ok = (head_dim * esize) % 16 == 0 && (qkv_stride * esize) % 16 == 0 && (uintptr_t)qkv % 16 == 0 &&
                          (uintptr_t)q_out % 16 == 0 && (!write_kv || ((uintptr_t)k_pool % 16 == 0 && (uintptr_t)v_pool % 16 == 0));
-  ROOST_DISPATCH_DTYPE(dtype, T,
-                       launch_kernel(qk_norm_rope_cache_kernel<T>, grid, dim3(warps * 32), 0, (cudaStream_t)stream,
-                           (const T*)qkv, qkv_stride, (T*)q_out, (T*)k_pool, (T*)v_pool, q_w, k_w, inv_freq, positions,
-                           slot_mapping, q_heads, kv_heads, head_dim, rotary_dim, eps, page_size, pool_pages, slots, wdtype, vector_ok));
+  ROOST_DISPATCH_DTYPE(dtype, T, {
+    auto kernel = many ? qk_norm_rope_cache_kernel<T, true> : qk_norm_rope_cache_kernel<T, false>;
+    launch_kernel(kernel, grid, dim3(warps * 32), many ? table_bytes : 0, (cudaStream_t)stream, (const T*)qkv, qkv_stride, (T*)q_out,
+                  (T*)k_pool, (T*)v_pool, q_w, k_w, inv_freq, positions, slot_mapping, q_heads, kv_heads, head_dim, rotary_dim, eps,
+                  page_size, pool_pages, slots, wdtype, vector_ok);
+  });
   return check_launch("qk_norm_rope_cache");
 }
 
