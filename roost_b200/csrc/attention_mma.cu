@@ -968,6 +968,15 @@ __global__ void attention_merge_kernel(__nv_bfloat16* __restrict__ out, const fl
   }
 }
 
+// attention_tc.cu
+bool prefill_tc_serves(int head_dim, int q_heads, int kv_heads, int page_size, long long pool_pages, const void* k_pool, const void* v_pool,
+                       const void* q);
+int launch_prefill_tc(const void* q, long long tokens, void* out, const void* k_pool, const void* v_pool, const int32_t* q_indptr,
+                      const int32_t* kv_lens, const int32_t* kv_indptr, const int32_t* kv_indices, const int32_t* work, int items, int q_heads,
+                      int kv_heads, int head_dim, int page_size, long long pool_pages, float scale, int window, cudaStream_t s);
+void set_prefill_tc(bool on);
+int prefill_tc_status();
+
 static int page_shift_of(int page_size) {
   if (page_size & (page_size - 1)) return -1;
   int s = 0;
@@ -1103,12 +1112,18 @@ using namespace roost;
     default: return fail(ROOST_ERR_UNSUPPORTED, "attention_mma: head_dim is not one of 16, 32, 64, 128, 256"); \
   }
 
-// Packed rows of one prefill work item, for a head size the tensor-core kernels serve and a step that brings
-// `packed_rows` packed rows (tokens x query heads per key/value head) in all to the prefill kernel.
-extern "C" int roost_attention_prefill_tile_rows(int head_dim, long long packed_rows, int kv_heads) {
+// Packed rows of one prefill work item for these sizes and pools and a step that brings `packed_rows` packed rows
+// (tokens x query heads per key/value head) in all to the prefill kernels: 128 where the tcgen05 kernel serves (or the
+// grid of the mma.sync kernel is large), else 64; 0 for a head size no tensor-core kernel serves.
+extern "C" int roost_attention_prefill_tile_rows(int head_dim, int q_heads, int kv_heads, int page_size, long long pool_pages,
+                                                 const void* k_pool, const void* v_pool, long long packed_rows) {
   if (!roost_attention_mma_supported(head_dim)) return 0;
+  if (prefill_tc_serves(head_dim, q_heads, kv_heads, page_size, pool_pages, k_pool, v_pool, nullptr)) return 128;
   return head_dim <= 128 && packed_rows * kv_heads >= kPrefillWideMinRows ? 128 : 64;
 }
+
+// 1: prompt portions run the tcgen05 kernel where the sizes allow (the default); 0: always the mma.sync kernel.
+extern "C" void roost_attention_set_prefill_tc(int on) { set_prefill_tc(on != 0); }
 
 // 1: decode rows stream keys and values through the copy engine where the sizes allow (the default); 0: always cp.async.
 extern "C" void roost_attention_set_decode_tma(int on) { g_decode_tma = on != 0; }
@@ -1122,6 +1137,8 @@ extern "C" int roost_attention_status(void) {
     const int zero = 0;
     cudaMemcpyToSymbol(g_attention_error, &zero, sizeof(int));
   }
+  const int tc = prefill_tc_status();  // codes of the tcgen05 prefill kernel come back as 100 + code
+  if (code == 0 && tc != 0) code = tc < 0 ? tc : 100 + tc;
   return code;
 }
 
@@ -1129,15 +1146,19 @@ extern "C" int roost_attention_mma_supported(int head_dim) {
   return head_dim == 16 || head_dim == 32 || head_dim == 64 || head_dim == 128 || head_dim == 256;
 }
 
-extern "C" int roost_attention_prefill(const void* q, void* out, const void* k_pool, const void* v_pool, const int32_t* q_indptr,
-                                       const int32_t* kv_lens, const int32_t* kv_indptr, const int32_t* kv_indices,
-                                       const int32_t* work, int items, int tile_rows, int q_heads, int kv_heads, int head_dim,
-                                       int page_size, float scale, int window, roost_stream_t stream) {
+extern "C" int roost_attention_prefill(const void* q, long long tokens, void* out, const void* k_pool, const void* v_pool,
+                                       const int32_t* q_indptr, const int32_t* kv_lens, const int32_t* kv_indptr,
+                                       const int32_t* kv_indices, const int32_t* work, int items, int tile_rows, int q_heads, int kv_heads,
+                                       int head_dim, int page_size, long long pool_pages, float scale, int window, roost_stream_t stream) {
   ROOST_REQUIRE(items >= 0 && q_heads > 0 && kv_heads > 0 && page_size > 0, "attention_prefill: sizes must be positive");
   ROOST_REQUIRE(tile_rows == 64 || (tile_rows == 128 && head_dim <= 128), "attention_prefill: a work item has 64 packed rows, or 128 up to head size 128");
   ROOST_REQUIRE(q_heads % kv_heads == 0, "attention_prefill: q_heads must be a multiple of kv_heads");
   if (kv_heads > 65535) return fail(ROOST_ERR_UNSUPPORTED, "attention_prefill: more than 65535 key/value heads");
   if (items == 0) return ROOST_OK;
+  if (tile_rows == 128 && tokens > 0 && prefill_tc_serves(head_dim, q_heads, kv_heads, page_size, pool_pages, k_pool, v_pool, q)) {
+    return launch_prefill_tc(q, tokens, out, k_pool, v_pool, q_indptr, kv_lens, kv_indptr, kv_indices, work, items, q_heads, kv_heads, head_dim,
+                             page_size, pool_pages, scale, window, (cudaStream_t)stream);
+  }
   if (tile_rows == 128) {
     switch (head_dim) {
       case 16: return launch_prefill<16, 2>(q, out, k_pool, v_pool, q_indptr, kv_lens, kv_indptr, kv_indices, work, items, q_heads, kv_heads, page_size, scale, window, (cudaStream_t)stream);

@@ -1,0 +1,476 @@
+// Causal grouped-query attention over the paged cache for prompt portions (rows with more than 16 packed rows), on the
+// fifth-generation tensor cores: both products are tcgen05.mma with the accumulators in tensor memory.
+//
+// Definition and numerics as in attention_mma.cu (src/Starlings.Roost.Ops/CpuOps.cs:181-298; 32-bit scores, maxima,
+// exponentials, sums and output accumulation; the softmax weights rounded to bfloat16 as the operand of the second
+// product, kernels/README.md:234-236). A CTA owns 128 packed rows (token r / G, head r % G) of one request and one
+// key/value head and walks the keys in tiles of 64 at fixed absolute positions, so a row's bits do not depend on how
+// the prompt was cut or on what else is in the batch.
+//   warp 0 (producer): one 5-D tensor copy brings the Q tile [128 rows x D] into 128-byte-swizzled shared memory; per key
+//     tile it looks the pages up and its lanes issue the stage's copies side by side: per page one copy per 64-column
+//     block of the keys, placed so that the tile's 64 key rows are consecutive in each block (one product then takes
+//     them all), and one copy of the values.
+//   warp 1 (issuer, one lane): S = Q K^T (M 128, N 64, K = D) into one of two score buffers in tensor memory; O += P V, one product per 16 keys (M 128, N = D, K 16) with P from shared
+//     memory and V as the N-major operand exactly as the copy left it. tcgen05.commit tells the others when the scores
+//     are there, when a stage is free and when the output accumulator has taken a tile in.
+//   warps 2..5 (softmax, one thread a row): read the row's 64 scores from tensor memory, scale, mask by position, keep
+//     the running maximum and sum, rescale the row of the output accumulator in tensor memory when the maximum moved
+//     (skipped when no row of the warp moved), write the weights as bfloat16 into the swizzled P tile, and at the end
+//     divide the accumulator by the sum and write the row out.
+// The scores of tile j + 1 are computed while the softmax of tile j runs. Value rows at positions the request does not
+// hold yet (the rest of its last page) or before the CTA's first visible key are zeroed in shared memory before the second product, so that whatever the pool
+// holds there cannot reach a result; their scores are masked by position. Every wait is bounded (see tma.cuh): a wait
+// given up raises the CTA's abort flag and records a code that roost_attention_status() returns.
+#include "tcgen05.cuh"
+
+namespace roost {
+
+constexpr float kLog2eTc = 1.4426950408889634f;
+constexpr int kTcRows = 128;   // packed rows of a CTA
+constexpr int kTcKeys = 64;    // keys of a tile
+__device__ int g_attention_tc_error = 0;
+
+__device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2, int c3, int c4) {
+  asm volatile("cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];\n" ::"r"(dst),
+               "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
+               : "memory");
+}
+
+template <int D>
+constexpr int tc_stages() {
+  return D == 128 ? 4 : 6;
+}
+
+// work[i] = (batch row, first packed row of the tile of 128)
+template <int D, int RPC>
+__global__ void __launch_bounds__(192, 1)
+    attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                                const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out, const int32_t* __restrict__ q_indptr, const int32_t* __restrict__ kv_lens,
+                                const int32_t* __restrict__ kv_indptr, const int32_t* __restrict__ kv_indices, const int2* __restrict__ work,
+                                int q_heads, int kv_heads, int page_size, float scale_log2, int window) {
+  constexpr int BM = kTcRows, TK = kTcKeys, STAGES = tc_stages<D>(), NP = TK / RPC, CB = D / 64;
+  constexpr uint32_t kQBytes = BM * D * 2;
+  constexpr uint32_t kStageBytes = 2 * TK * D * 2;          // keys and values of TK positions
+  constexpr uint32_t kKeys = TK * D * 2;                    // a stage's keys: [column block][TK rows][128 B], K-major for one product
+  constexpr uint32_t kVPage = CB * RPC * 128;               // its values, page copy by page copy: [column block][RPC rows][128 B]
+  constexpr int kOps = NP * (CB + 1);                       // copies a stage takes: per page one per column block of keys, one of values
+  static_assert(kOps <= 32, "one lane a copy");
+  constexpr uint32_t kPBytes = BM * 128;                    // P tile: 128 rows x 64 keys of bfloat16
+  constexpr uint32_t kTmemCols = 2 * TK + D <= 256 ? 256 : 512;
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t smem_base = ((uint32_t)__cvta_generic_to_shared(smem_raw) + 1023u) & ~1023u;
+  const uint32_t q_smem = smem_base;
+  const uint32_t kv_smem = q_smem + kQBytes;
+  const uint32_t p_smem = kv_smem + STAGES * kStageBytes;
+  __shared__ __align__(8) uint64_t bars[1 + 2 * STAGES + 8];
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+  const uint32_t bar0 = (uint32_t)__cvta_generic_to_shared(bars);
+  const uint32_t q_full = bar0;
+  auto kv_full = [&](int s) { return bar0 + 8u * (1 + s); };
+  auto kv_empty = [&](int s) { return bar0 + 8u * (1 + STAGES + s); };
+  auto s_full = [&](int i) { return bar0 + 8u * (1 + 2 * STAGES + i); };
+  auto s_empty = [&](int i) { return bar0 + 8u * (1 + 2 * STAGES + 2 + i); };
+  auto p_full = [&](int i) { return bar0 + 8u * (1 + 2 * STAGES + 4 + i); };
+  auto pv_done = [&](int i) { return bar0 + 8u * (1 + 2 * STAGES + 6 + i); };
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    prefetch_tensormap(&map_q);
+    prefetch_tensormap(&map_k);
+    prefetch_tensormap(&map_v);
+    abort_flag = 0;
+    mbar_init(q_full, 1);
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(kv_full(s), 1);
+      mbar_init(kv_empty(s), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(s_full(i), 1);
+      mbar_init(s_empty(i), 4);
+      mbar_init(p_full(i), 4);
+      mbar_init(pv_done(i), 1);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  pdl_launch_dependents();
+  pdl_wait();
+  const int2 w = work[blockIdx.x];
+  const int b = w.x, row0 = w.y;
+  if (b < 0) return;  // padding of a fixed-size work list (before anything is allocated)
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"((uint32_t)__cvta_generic_to_shared(&tmem_slot)),
+                 "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = tmem_slot;
+  const uint32_t tmem_s[2] = {tmem_base, tmem_base + TK};
+  const uint32_t tmem_o = tmem_base + 2 * TK;
+  volatile int* abortp = &abort_flag;
+
+  const int kvh = blockIdx.y;
+  const int group = q_heads / kv_heads;
+  const int q_start = q_indptr[b];
+  const int n = q_indptr[b + 1] - q_start;
+  const int kv_len = kv_lens[b];
+  const int pos0 = kv_len - n;
+  const int rows_total = n * group;
+  // the tile's key range: up to the last row's position, from the first row's window
+  const int last_row = min(row0 + BM, rows_total) - 1;
+  const int hi = pos0 + last_row / group;
+  const int lo = window > 0 ? max(0, pos0 + row0 / group - window + 1) : 0;
+  const int t0 = lo / TK, ntiles = hi / TK - t0 + 1;
+
+  if (warp == 0) {
+    // ---- producer
+    const int page_shift = 31 - __clz(page_size);  // a power of two here
+    const int32_t* pages = kv_indices + kv_indptr[b];
+    const int p_first = (t0 * TK) >> page_shift, p_last = hi >> page_shift;
+    const int fallback = pages[p_last];
+    auto row_of = [&](int p, int entry) {  // first pool row of page p of the request, given its block-table entry
+      const bool visible = ((p + 1) << page_shift) > lo && (p << page_shift) <= hi;
+      return ((visible && entry >= 0 ? entry : fallback) * kv_heads + kvh) << page_shift;
+    };
+    int batch0 = p_first;
+    int cur = row_of(batch0 + lane, batch0 + lane <= p_last ? pages[batch0 + lane] : -1);
+    int nxt_entry = batch0 + 32 + lane <= p_last ? pages[batch0 + 32 + lane] : -1;
+    if (lane == 0) {
+      mbar_expect_tx(q_full, kQBytes);
+      tma_load_5d(q_smem, &map_q, q_full, 0, 0, kvh, q_start + row0 / group, 0);
+    }
+    bool ok = true;
+    for (int i = 0; i < ntiles && ok; ++i) {
+      const int stage = i % STAGES;
+      const uint32_t dst = kv_smem + stage * kStageBytes;
+      const int j = (t0 + i) * TK;
+      if ((j >> page_shift) >= batch0 + 32) {  // uniform in the warp
+        batch0 += 32;
+        cur = row_of(batch0 + lane, nxt_entry);
+        nxt_entry = batch0 + 32 + lane <= p_last ? pages[batch0 + 32 + lane] : -1;
+      }
+      // lane L issues copy L of the stage: page copy L / (CB + 1); column block L % (CB + 1) of its keys, or its values.
+      // A tile never straddles two batches of 32 pages: both start on tile boundaries.
+      const int c = lane / (CB + 1), part = lane % (CB + 1);
+      const int jc = j + (c < NP ? c : 0) * RPC;
+      const int my_row = __shfl_sync(0xffffffffu, cur, ((jc >> page_shift) - batch0) & 31) + (jc & (page_size - 1));
+      if (lane == 0) {
+        if (i >= STAGES) ok = mbar_wait_limited(kv_empty(stage), (uint32_t)((i / STAGES) - 1) & 1u, abortp, 1, &g_attention_tc_error);
+        if (ok) mbar_expect_tx(kv_full(stage), kStageBytes);
+      }
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;  // also orders the expected bytes before the copies
+      if (ok && lane < kOps) {
+        if (part < CB) {
+          tma_load_2d(dst + part * (TK * 128) + c * (RPC * 128), &map_k, kv_full(stage), part * 64, my_row);
+        } else {
+          tma_load_3d(dst + kKeys + c * kVPage, &map_v, kv_full(stage), 0, my_row, 0);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---- issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = umma_idesc_bf16(BM, TK);
+      constexpr uint32_t idesc_o = umma_idesc_bf16_b_mn(BM, D);
+      bool ok = mbar_wait_limited(q_full, 0, abortp, 2, &g_attention_tc_error);
+      tcgen05_fence_after();
+      auto issue_pv = [&](int j) {  // O += P_j V_j
+        const int stage = j % STAGES;
+        if (!(ok = mbar_wait_limited(p_full(j & 1), (uint32_t)(j >> 1) & 1u, abortp, 3, &g_attention_tc_error))) return;
+        tcgen05_fence_after();
+        const uint32_t v0 = kv_smem + stage * kStageBytes + kKeys;
+#pragma unroll
+        for (int kk = 0; kk < TK / 16; ++kk) {
+          const uint32_t v_rows = v0 + (uint32_t)((kk * 16) / RPC) * kVPage + (uint32_t)((kk * 16) % RPC) * 128;
+          const uint64_t a_desc = umma_desc_k_major_sw128(p_smem + (j & 1) * kPBytes) + (uint64_t)(2 * kk);
+          const uint64_t b_desc = umma_desc_mn_major_sw128(v_rows, RPC * 128, 1024);
+          tcgen05_mma_f16(tmem_o, a_desc, b_desc, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+        }
+        tcgen05_commit(kv_empty(stage));  // the stage is free once these products have read it
+        tcgen05_commit(pv_done(j & 1));
+      };
+#ifdef ROOST_TRACE
+      unsigned long long tr_i[16][2];
+#endif
+      for (int j = 0; j < ntiles && ok; ++j) {
+        const int stage = j % STAGES;
+        if (!(ok = mbar_wait_limited(kv_full(stage), (uint32_t)(j / STAGES) & 1u, abortp, 4, &g_attention_tc_error))) break;
+        if (j >= 2 && !(ok = mbar_wait_limited(s_empty(j & 1), (uint32_t)((j >> 1) - 1) & 1u, abortp, 5, &g_attention_tc_error))) break;
+        tcgen05_fence_after();
+        const uint32_t k0 = kv_smem + stage * kStageBytes;
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint64_t a_desc = umma_desc_k_major_sw128(q_smem + (k / 4) * (BM * 128)) + (uint64_t)(2 * (k % 4));
+          const uint64_t b_desc = umma_desc_k_major_sw128(k0 + (k / 4) * (TK * 128)) + (uint64_t)(2 * (k % 4));
+          tcgen05_mma_f16(tmem_s[j & 1], a_desc, b_desc, idesc_s, k > 0 ? 1u : 0u);
+        }
+        tcgen05_commit(s_full(j & 1));
+#ifdef ROOST_TRACE
+        if (j < 16) tr_i[j][0] = trace_now();
+#endif
+        if (j >= 1) issue_pv(j - 1);
+#ifdef ROOST_TRACE
+        if (j < 16) tr_i[j][1] = trace_now();
+#endif
+      }
+      if (ok && ntiles > 0) issue_pv(ntiles - 1);
+#ifdef ROOST_TRACE
+      if (blockIdx.x == 0 && blockIdx.y == 0) trace_flush(200, 0, &tr_i[0][0], 2 * min(ntiles, 16));
+#endif
+    }
+  } else {
+    // ---- softmax, correction, epilogue: one thread a row
+    const int lane_group = warp & 3;               // the tensor-memory lanes this warp may touch
+    const int row = lane_group * 32 + lane;
+    const int pr = row0 + row;
+    const bool valid = pr < rows_total;
+    const int qpos = valid ? pos0 + pr / group : -1;
+    const int qlo = valid && window > 0 ? max(0, qpos - window + 1) : 0;
+    const uint32_t lane_addr = (uint32_t)(lane_group * 32) << 16;
+    float m = -INFINITY, l = 0.f;
+    bool ok = true;
+#ifdef ROOST_TRACE
+    unsigned long long tr_s[16][4];
+#endif
+    for (int j = 0; j < ntiles && ok; ++j) {
+      const int stage = j % STAGES;
+      const int j0 = (t0 + j) * TK;
+      if (!(ok = mbar_wait_limited(s_full(j & 1), (uint32_t)(j >> 1) & 1u, abortp, 6, &g_attention_tc_error))) break;
+#ifdef ROOST_TRACE
+      if (j < 16) tr_s[j][0] = trace_now();
+#endif
+      tcgen05_fence_after();
+      float s[TK];
+#pragma unroll
+      for (int c = 0; c < TK / 32; ++c) {
+        uint32_t v[32];
+        tcgen05_ld_32x32b_x32(tmem_s[j & 1] + lane_addr + c * 32, v);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) s[c * 32 + i] = __uint_as_float(v[i]);
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(s_empty(j & 1));  // the scores are in registers: the buffer may take tile j + 2
+      float mx = -INFINITY;
+      if (j0 + TK - 1 <= qpos && j0 >= qlo) {
+#pragma unroll
+        for (int i = 0; i < TK; ++i) {
+          s[i] *= scale_log2;
+          mx = fmaxf(mx, s[i]);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < TK; ++i) {
+          const int key = j0 + i;
+          s[i] = (key <= qpos && key >= qlo) ? s[i] * scale_log2 : -INFINITY;
+          mx = fmaxf(mx, s[i]);
+        }
+      }
+      const float m_new = fmaxf(m, mx);
+      const float msafe = m_new == -INFINITY ? 0.f : m_new;  // a row that has seen no key yet: every weight below is 0
+      const float corr = exp2f(m - msafe);                     // 0 when m is -inf
+      m = m_new;
+      float sum = 0.f;
+      uint32_t packed[TK / 2];
+#pragma unroll
+      for (int i = 0; i < TK; i += 2) {
+        const float p0 = exp2f(s[i] - msafe), p1 = exp2f(s[i + 1] - msafe);
+        sum += p0 + p1;
+        __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
+        packed[i / 2] = *reinterpret_cast<uint32_t*>(&pb);
+      }
+      l = l * corr + sum;
+      // the accumulator holds tiles 0 .. j - 1 once the product of tile j - 1 is done; then its row may be rescaled
+      // and the P buffer (read by the product of tile j - 2) written
+#ifdef ROOST_TRACE
+      if (j < 16) tr_s[j][1] = trace_now();
+#endif
+      if (j >= 1 && !(ok = mbar_wait_limited(pv_done((j - 1) & 1), (uint32_t)((j - 1) >> 1) & 1u, abortp, 7, &g_attention_tc_error))) break;
+#ifdef ROOST_TRACE
+      if (j < 16) tr_s[j][2] = trace_now();
+#endif
+      tcgen05_fence_after();
+      if (j >= 1 && __any_sync(0xffffffffu, corr != 1.0f)) {
+#pragma unroll 1
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t v[32];
+          tcgen05_ld_32x32b_x32(tmem_o + lane_addr + c * 32, v);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * corr);
+          tcgen05_st_32x32b_x32(tmem_o + lane_addr + c * 32, v);
+        }
+      }
+      // value rows at positions the request does not hold yet, and rows before the first visible key (their page may
+      // have been given back and replaced by another): zero (the copies of this stage have landed: the scores of this
+      // tile were computed from the same stage)
+      if (j0 + TK > kv_len || j0 < lo) {
+        const uint32_t v0 = kv_smem + stage * kStageBytes + kKeys;
+        for (int idx = threadIdx.x - 64; idx < TK * (D / 8); idx += 128) {
+          const int r = idx / (D / 8), ch = idx % (D / 8);
+          if (j0 + r >= kv_len || j0 + r < lo) {
+            const uint32_t addr = v0 + (uint32_t)(r / RPC) * kVPage + (uint32_t)(ch >> 3) * (RPC * 128) + (uint32_t)(r % RPC) * 128 +
+                                  (uint32_t)(((ch & 7) ^ (r & 7)) << 4);
+            asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};\n" ::"r"(addr), "r"(0u) : "memory");
+          }
+        }
+      }
+      // the row of P: 64 bfloat16 = 128 bytes = eight 16-byte chunks, swizzled by the row
+      const uint32_t p_row = p_smem + (j & 1) * kPBytes + (uint32_t)row * 128;
+#pragma unroll
+      for (int ch = 0; ch < 8; ++ch) {
+        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};\n" ::"r"(p_row + (uint32_t)((ch ^ (row & 7)) << 4)), "r"(packed[4 * ch]),
+                     "r"(packed[4 * ch + 1]), "r"(packed[4 * ch + 2]), "r"(packed[4 * ch + 3])
+                     : "memory");
+      }
+      asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // the stores are visible to the tensor cores' reads
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full(j & 1));
+#ifdef ROOST_TRACE
+      if (j < 16) tr_s[j][3] = trace_now();
+#endif
+    }
+#ifdef ROOST_TRACE
+    if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 64) trace_flush(201, 0, &tr_s[0][0], 4 * min(ntiles, 16));
+#endif
+    // epilogue: O / l
+    if (ok && ntiles > 0) ok = mbar_wait_limited(pv_done((ntiles - 1) & 1), (uint32_t)((ntiles - 1) >> 1) & 1u, abortp, 8, &g_attention_tc_error);
+    if (ok) {
+      tcgen05_fence_after();
+      const float inv = l > 0.f ? 1.0f / l : 0.f;
+      __nv_bfloat16* dst = valid ? out + ((size_t)(q_start + pr / group) * q_heads + kvh * group + pr % group) * D : nullptr;
+#pragma unroll 1
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t v[32];
+        tcgen05_ld_32x32b_x32(tmem_o + lane_addr + c * 32, v);
+        if (valid) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            uint32_t o[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              __nv_bfloat162 ob = __floats2bfloat162_rn(__uint_as_float(v[i + 2 * e]) * inv, __uint_as_float(v[i + 2 * e + 1]) * inv);
+              o[e] = *reinterpret_cast<uint32_t*>(&ob);
+            }
+            *reinterpret_cast<uint4*>(dst + c * 32 + i) = make_uint4(o[0], o[1], o[2], o[3]);
+          }
+        }
+      }
+    }
+  }
+
+  __syncwarp();
+  if (*abortp) {  // copies in flight land before shared memory is released
+    const long long c0 = clock64();
+    while (clock64() - c0 < 2000000LL) __nanosleep(256);
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ host side
+static bool g_prefill_tc = true;
+
+bool prefill_tc_serves(int head_dim, int q_heads, int kv_heads, int page_size, long long pool_pages, const void* k_pool, const void* v_pool,
+                       const void* q) {
+  if (!g_prefill_tc || pool_pages <= 0 || (head_dim != 64 && head_dim != 128) || kv_heads <= 0 || q_heads % kv_heads != 0) return false;
+  const int group = q_heads / kv_heads;
+  if (group > 128 || (group & (group - 1)) != 0) return false;  // a CTA's 128 packed rows are whole tokens
+  if (page_size < 16 || (page_size & (page_size - 1)) != 0) return false;
+  if (pool_pages * kv_heads * page_size >= (1LL << 31)) return false;
+  const long long pool_bytes = pool_pages * kv_heads * page_size * head_dim * 2;
+  const long long gap = (const char*)v_pool - (const char*)k_pool;
+  if (gap < pool_bytes || gap % 16 != 0 || gap >= (1LL << 40)) return false;
+  return (uintptr_t)k_pool % 128 == 0 && (q == nullptr || (uintptr_t)q % 16 == 0) && encode_tiled() != nullptr;
+}
+
+template <int D, int RPC>
+static int launch_tc(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, void* out, const int32_t* q_indptr, const int32_t* kv_lens,
+                     const int32_t* kv_indptr, const int32_t* kv_indices, const int32_t* work, int items, int q_heads, int kv_heads,
+                     int page_size, float scale, int window, cudaStream_t s) {
+  constexpr size_t smem = (size_t)kTcRows * D * 2 + (size_t)tc_stages<D>() * 2 * kTcKeys * D * 2 + 2 * kTcRows * 128 + 1024;
+  auto kernel = attention_prefill_tc_kernel<D, RPC>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    attr_set = true;
+  }
+  launch_kernel(kernel, dim3(items, kv_heads), dim3(192), smem, s, mq, mk, mv, (__nv_bfloat16*)out, q_indptr, kv_lens, kv_indptr, kv_indices,
+                (const int2*)work, q_heads, kv_heads, page_size, scale * kLog2eTc, window);
+  return check_launch("attention_prefill_tc");
+}
+
+int launch_prefill_tc(const void* q, long long tokens, void* out, const void* k_pool, const void* v_pool, const int32_t* q_indptr,
+                      const int32_t* kv_lens, const int32_t* kv_indptr, const int32_t* kv_indices, const int32_t* work, int items, int q_heads,
+                      int kv_heads, int head_dim, int page_size, long long pool_pages, float scale, int window, cudaStream_t s) {
+  const int group = q_heads / kv_heads;
+  CUtensorMap mq;
+  {
+    // q [tokens][kv_heads][group][D] as 64 columns x group x kv heads x tokens x column blocks; a box is 128 packed rows
+    // of one key/value head: [column block][token][head of the group][64]
+    const cuuint64_t dims[5] = {64u, (cuuint64_t)group, (cuuint64_t)kv_heads, (cuuint64_t)tokens, (cuuint64_t)head_dim / 64};
+    const cuuint64_t strides[4] = {(cuuint64_t)head_dim * 2, (cuuint64_t)group * head_dim * 2, (cuuint64_t)q_heads * head_dim * 2, 128u};
+    const cuuint32_t box[5] = {64u, (cuuint32_t)group, 1u, (cuuint32_t)(kTcRows / group), (cuuint32_t)head_dim / 64};
+    const cuuint32_t elem[5] = {1, 1, 1, 1, 1};
+    const CUresult r = encode_tiled()(&mq, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void*>(q), dims, strides, box, elem,
+                                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(ROOST_ERR_CUDA, "attention_prefill: cuTensorMapEncodeTiled (q) failed with code " + std::to_string((int)r));
+  }
+  const int box_rows = page_size < 32 ? page_size : 32;
+  const cuuint64_t pool_rows = (cuuint64_t)(pool_pages * kv_heads * page_size);
+  CUtensorMap mk, mv;
+  {
+    const cuuint64_t dims[2] = {(cuuint64_t)head_dim, pool_rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)head_dim * 2};
+    const cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult r = encode_tiled()(&mk, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(k_pool), dims, strides, box, elem,
+                                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(ROOST_ERR_CUDA, "attention_prefill: cuTensorMapEncodeTiled (keys) failed with code " + std::to_string((int)r));
+  }
+  {
+    const cuuint64_t dims[3] = {64u, pool_rows, (cuuint64_t)head_dim / 64};
+    const cuuint64_t strides[2] = {(cuuint64_t)head_dim * 2, 128u};
+    const cuuint32_t box[3] = {64u, (cuuint32_t)box_rows, (cuuint32_t)head_dim / 64};
+    const cuuint32_t elem[3] = {1, 1, 1};
+    const CUresult r = encode_tiled()(&mv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(v_pool), dims, strides, box, elem,
+                                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(ROOST_ERR_CUDA, "attention_prefill: cuTensorMapEncodeTiled (values) failed with code " + std::to_string((int)r));
+  }
+#define ROOST_TC_CASE(DD, RR)                                                                                                          \
+  if (head_dim == DD && box_rows == RR)                                                                                                \
+    return launch_tc<DD, RR>(mq, mk, mv, out, q_indptr, kv_lens, kv_indptr, kv_indices, work, items, q_heads, kv_heads, page_size, scale, \
+                             window, s);
+  ROOST_TC_CASE(128, 16)
+  ROOST_TC_CASE(128, 32)
+  ROOST_TC_CASE(64, 16)
+  ROOST_TC_CASE(64, 32)
+#undef ROOST_TC_CASE
+  return fail(ROOST_ERR_UNSUPPORTED, "attention_prefill: no tcgen05 kernel for these sizes");
+}
+
+void set_prefill_tc(bool on) { g_prefill_tc = on; }
+
+int prefill_tc_status() {
+  int code = 0;
+  if (cudaMemcpyFromSymbol(&code, g_attention_tc_error, sizeof(int)) != cudaSuccess) return -1;
+  if (code != 0) {
+    const int zero = 0;
+    cudaMemcpyToSymbol(g_attention_tc_error, &zero, sizeof(int));
+  }
+  return code;
+}
+
+}  // namespace roost
+
+ROOST_TRACE_TU(attention_tc)

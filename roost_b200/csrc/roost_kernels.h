@@ -77,7 +77,9 @@ int roost_paged_attention_generic(const void* q, void* out, const void* k_pool, 
 /* Tensor-core attention for bfloat16 (attention_mma.cu). head_dim must be one roost_attention_mma_supported accepts.
  * q_indptr[b] .. q_indptr[b+1] are row b's tokens, kv_lens[b] its keys after this step.
  * prefill work: int32 pairs (batch row, first packed row of a tile of tile_rows rows; roost_attention_prefill_tile_rows picks 64 or 128),
- * packed row = token * group + head.
+ * packed row = token * group + head. With 128-row tiles, head size 64 or 128, a power-of-two number of query heads per
+ * key/value head, pages of 16, 32, 64, ... rows and K and V in one allocation, prompt portions run the tcgen05 kernel
+ * (attention_tc.cu) unless roost_attention_set_prefill_tc(0) was called; q then has `tokens` rows.
  * decode work: int32 quadruples (batch row, first key, one past the last key, partial slot or -1); rows with at most
  * 16 packed rows only; the first key of an item is a multiple of 64. merge_work: quadruples (batch row, first slot,
  * chunks | packed rows << 24, the row's first token) for rows split into several chunks; merge_rows: the most packed
@@ -89,11 +91,13 @@ int roost_paged_attention_generic(const void* q, void* out, const void* k_pool, 
  * every slot of a page a block table names must be readable, whatever it holds.
  * roost_attention_status(): 0, or the code of a wait the copy-engine kernel gave up (read and cleared). */
 int roost_attention_mma_supported(int head_dim);
-int roost_attention_prefill_tile_rows(int head_dim, long long packed_rows, int kv_heads);
-int roost_attention_prefill(const void* q, void* out, const void* k_pool, const void* v_pool, const int32_t* q_indptr,
+int roost_attention_prefill_tile_rows(int head_dim, int q_heads, int kv_heads, int page_size, long long pool_pages, const void* k_pool,
+                                      const void* v_pool, long long packed_rows);
+void roost_attention_set_prefill_tc(int on);
+int roost_attention_prefill(const void* q, long long tokens, void* out, const void* k_pool, const void* v_pool, const int32_t* q_indptr,
                             const int32_t* kv_lens, const int32_t* kv_indptr, const int32_t* kv_indices, const int32_t* work,
-                            int items, int tile_rows, int q_heads, int kv_heads, int head_dim, int page_size, float scale,
-                            int window, roost_stream_t stream);
+                            int items, int tile_rows, int q_heads, int kv_heads, int head_dim, int page_size, long long pool_pages,
+                            float scale, int window, roost_stream_t stream);
 int roost_attention_decode(const void* q, void* out, const void* k_pool, const void* v_pool, const int32_t* q_indptr,
                            const int32_t* kv_lens, const int32_t* kv_indptr, const int32_t* kv_indices, const int32_t* work,
                            int items, const int32_t* merge_work, int merge_items, int merge_rows, float* part_o, float* part_ml,

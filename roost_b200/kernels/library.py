@@ -58,9 +58,10 @@ _SIGNATURES = {
     "roost_paged_attention_generic": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                       c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p],
     "roost_attention_mma_supported": [c_int],
-    "roost_attention_prefill_tile_rows": [c_int, ctypes.c_longlong, c_int],
-    "roost_attention_prefill": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
-                                c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+    "roost_attention_prefill_tile_rows": [c_int, c_int, c_int, c_int, ctypes.c_longlong, c_void_p, c_void_p, ctypes.c_longlong],
+    "roost_attention_set_prefill_tc": [c_int],
+    "roost_attention_prefill": [c_void_p, ctypes.c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                c_int, c_int, c_int, c_int, c_int, c_int, ctypes.c_longlong, c_float, c_int, c_void_p],
     "roost_attention_decode": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, ctypes.c_longlong, c_float, c_int,
                                c_void_p],
@@ -204,9 +205,15 @@ class KernelLibrary:
     def attention_mma_supported(self, head_dim: int) -> bool:
         return bool(self._lib.roost_attention_mma_supported(int(head_dim)))
 
-    def attention_prefill_tile_rows(self, head_dim: int, packed_rows: int = 0, kv_heads: int = 1) -> int:
-        """Packed rows of a prefill work item for a step that brings ``packed_rows`` packed rows in all."""
-        return int(self._lib.roost_attention_prefill_tile_rows(int(head_dim), int(packed_rows), int(kv_heads)))
+    def attention_prefill_tile_rows(self, q_heads: int, k_pool: torch.Tensor, v_pool: torch.Tensor, packed_rows: int = 0) -> int:
+        """Packed rows of a prefill work item (64 or 128) for these pools [pages, kv_heads, page_size, head_dim] and a step
+        that brings ``packed_rows`` packed rows in all to the prefill kernels."""
+        pages, nkv, page, d = k_pool.shape
+        return int(self._lib.roost_attention_prefill_tile_rows(d, int(q_heads), nkv, page, pages, _ptr(k_pool), _ptr(v_pool), int(packed_rows)))
+
+    def attention_set_prefill_tc(self, on: bool) -> None:
+        """Prompt portions run the tcgen05 attention kernel where the sizes allow (the default), or never."""
+        self._lib.roost_attention_set_prefill_tc(1 if on else 0)
 
     def attention_mma(self, q, k_pool, v_pool, q_indptr, kv_lens, kv_indptr, kv_indices, plan, scale: float,
                       window: int | None) -> torch.Tensor:
@@ -219,9 +226,9 @@ class KernelLibrary:
         out = torch.empty((T, nq * d), dtype=q.dtype, device=q.device)
         w = int(window) if window else 0
         if plan.prefill_items:
-            self._call("roost_attention_prefill", _ptr(q), _ptr(out), _ptr(k_pool), _ptr(v_pool), _ptr(q_indptr), _ptr(kv_lens),
-                       _ptr(kv_indptr), _ptr(kv_indices), _ptr(plan.prefill_work), plan.prefill_items, plan.prefill_tile_rows, nq, nkv, d, page, scale, w,
-                       _stream())
+            self._call("roost_attention_prefill", _ptr(q), T, _ptr(out), _ptr(k_pool), _ptr(v_pool), _ptr(q_indptr), _ptr(kv_lens),
+                       _ptr(kv_indptr), _ptr(kv_indices), _ptr(plan.prefill_work), plan.prefill_items, plan.prefill_tile_rows, nq, nkv, d, page,
+                       k_pool.shape[0], scale, w, _stream())
         if plan.decode_items:
             part_o = part_ml = None
             if plan.slots:

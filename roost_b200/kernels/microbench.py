@@ -88,7 +88,8 @@ def attention_prefill(k, a) -> None:
     pool = torch.randn(2, npages, nkv, page, d, device="cuda", dtype=torch.bfloat16)
     q = torch.randn(T * a.batch, nq, d, device="cuda", dtype=torch.bfloat16)
     group = nq // nkv
-    rows = a.tile_rows or k.attention_prefill_tile_rows(d, T * a.batch * group, nkv)
+    k.attention_set_prefill_tc(not a.mma_sync)
+    rows = a.tile_rows or k.attention_prefill_tile_rows(nq, pool[0], pool[1], T * a.batch * group)
     plan = plan_attention([0] * a.batch, [T] * a.batch, group, None, k.decode_chunk, "cuda", rows)
     q_indptr = torch.arange(a.batch + 1, dtype=torch.int32, device="cuda") * T
     kv_lens = torch.full((a.batch,), T, dtype=torch.int32, device="cuda")
@@ -96,7 +97,7 @@ def attention_prefill(k, a) -> None:
     kv_indices = torch.randperm(npages, device="cuda").to(torch.int32)
     us = _time(lambda: k.attention_mma(q, pool[0], pool[1], q_indptr, kv_lens, kv_indptr, kv_indices, plan, d ** -0.5, None), a.warmup, a.iters)
     flops = 4 * T * T / 2 * nq * d * a.batch
-    print(f"attention-prefill tokens={T} batch={a.batch} heads={nq}/{nkv} head_dim={d} tile_rows={rows}: {us:.1f} us, "
+    print(f"attention-prefill tokens={T} batch={a.batch} heads={nq}/{nkv} head_dim={d} tile_rows={rows} {'mma.sync' if a.mma_sync else 'tcgen05'}: {us:.1f} us, "
           f"{flops / us / 1e6:.0f} TFLOP/s (causal half counted)", flush=True)
 
 
@@ -146,6 +147,7 @@ def main(argv=None) -> int:
     p.add_argument("--chunk", type=int, default=0, help="keys per decode work item (default: the library's)")
     p.add_argument("--tile-rows", type=int, default=0, help="packed rows per prefill work item (default: the library's choice)")
     p.add_argument("--cp-async", action="store_true", help="decode attention through the cp.async kernel instead of TMA")
+    p.add_argument("--mma-sync", action="store_true", help="prefill attention through the mma.sync kernel instead of tcgen05")
     p.add_argument("--sequential-pages", action="store_true")
     p.add_argument("--iters", type=int, default=10)
     p.add_argument("--warmup", type=int, default=3)

@@ -96,7 +96,7 @@ class PagedAttention(Mixer):
         s, k = self.spec, self.rt.kernels
         if q.dtype == torch.bfloat16 and getattr(k, "attention_mma_supported", lambda d: False)(s.head_dim):
             group = s.num_heads // s.num_kv_heads
-            tile_rows = k.attention_prefill_tile_rows(s.head_dim, batch.num_tokens * group, s.num_kv_heads)
+            tile_rows = k.attention_prefill_tile_rows(s.num_heads, cache.k_pool, cache.v_pool, batch.num_tokens * group)
             plan = batch.attention_plan(group, s.window, k.decode_chunk, tile_rows)
             return k.attention_mma(q, cache.k_pool, cache.v_pool, batch.q_indptr, batch.kv_lens, tables.kv_indptr,
                                    tables.kv_indices, plan, s.scale, s.window)

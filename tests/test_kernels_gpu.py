@@ -279,7 +279,7 @@ def run_mma(kernels, q, kp, vp, lens, news, indptr, indices, scale, window, chun
     nq, nkv = q.shape[1], kp.shape[1]
     starts = [n - m for n, m in zip(lens, news)]
     plan = plan_attention(starts, news, nq // nkv, window, chunk or kernels.decode_chunk, "cuda",
-                          tile_rows or kernels.attention_prefill_tile_rows(q.shape[2]))
+                          tile_rows or kernels.attention_prefill_tile_rows(nq, kp, vp))
     q_indptr = torch.tensor([0] + list(torch.tensor(news).cumsum(0)), dtype=torch.int32).cuda()
     kv_lens = torch.tensor(lens, dtype=torch.int32).cuda()
     return kernels.attention_mma(q.cuda(), kp, vp, q_indptr, kv_lens, indptr, indices, plan, scale, window), plan
@@ -326,11 +326,28 @@ def test_attention_mma_mixed_rows(kernels, window, nq, nkv, d, page):
     assert kernels.attention_status() == 0, "a bounded wait inside the decode kernel was given up"
     assert not torch.isnan(plain_copy.float()).any()
     close(plain_copy, want, dtype, f"attention_mma (cp.async decode) window={window}", scale=2)
+    # the prompt portions again through the mma.sync kernel (where the tcgen05 kernel served them above)
+    kernels.attention_set_prefill_tc(False)
+    try:
+        legacy, _ = run_mma(kernels, q, kp, vp, lens, news, indptr, indices, scale, window)
+    finally:
+        kernels.attention_set_prefill_tc(True)
+    assert kernels.attention_status() == 0, "a bounded wait inside an attention kernel was given up"
+    assert not torch.isnan(legacy.float()).any()
+    close(legacy, want, dtype, f"attention_mma (mma.sync prefill) window={window}", scale=2)
+    group = nq // nkv
+    tc_serves = d in (64, 128) and group & (group - 1) == 0 and page >= 16
+    assert torch.equal(legacy, out) != tc_serves, "the tcgen05 kernel serves exactly these sizes (its tiles round differently)"
     if d <= 128:
         # work items of 128 packed rows (two row tiles a warp) compute every row with the same operations in the same order
-        wide, wide_plan = run_mma(kernels, q, kp, vp, lens, news, indptr, indices, scale, window, tile_rows=128)
-        assert wide_plan.prefill_items < plan.prefill_items or nq // nkv * max(news) <= 64
-        assert torch.equal(wide, out), "64-row and 128-row prefill tiles differ"
+        kernels.attention_set_prefill_tc(False)
+        try:
+            wide, wide_plan = run_mma(kernels, q, kp, vp, lens, news, indptr, indices, scale, window, tile_rows=128)
+            narrow, narrow_plan = run_mma(kernels, q, kp, vp, lens, news, indptr, indices, scale, window, tile_rows=64)
+        finally:
+            kernels.attention_set_prefill_tc(True)
+        assert wide_plan.prefill_items < narrow_plan.prefill_items or nq // nkv * max(news) <= 64
+        assert torch.equal(wide, narrow), "64-row and 128-row prefill tiles differ"
 
 
 @pytest.mark.parametrize("case", ["far key", "first key", "page edge", "chunk edge", "window edge in", "window edge out"])

@@ -46,7 +46,7 @@ def test_decode_attention_without_a_workspace_matches_the_one_with(kernels):
         q = (torch.randn(len(lens), nq, d, generator=g) * 1.5).to(dtype).cuda()
         kp, vp, indptr, indices = build_paged(keys, values, page, dtype, num_pages=sum(-(-n // page) for n in lens) + 3, seed=seed)
         starts = [n - 1 for n in lens]
-        plan = plan_attention(starts, news, nq // nkv, None, kernels.decode_chunk, "cuda", kernels.attention_prefill_tile_rows(d, 0, 1))
+        plan = plan_attention(starts, news, nq // nkv, None, kernels.decode_chunk, "cuda", 64)
         assert plan.merge_items > 0 and plan.slots > 1
         q_indptr = torch.arange(len(lens) + 1, dtype=torch.int32).cuda()
         kv_lens = torch.tensor(lens, dtype=torch.int32).cuda()
