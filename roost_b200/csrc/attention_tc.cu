@@ -36,6 +36,13 @@ __device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* map
                : "memory");
 }
 
+// 2^x in one special-function instruction (inputs here are at most 0 or -inf; results below 2^-126 flush to zero)
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
+
 template <int D>
 constexpr int tc_stages() {
   return D == 128 ? 4 : 6;
@@ -244,44 +251,49 @@ __global__ void __launch_bounds__(192, 1)
 #endif
       tcgen05_fence_after();
       float s[TK];
+      {
+        uint32_t v[TK / 32][32];
 #pragma unroll
-      for (int c = 0; c < TK / 32; ++c) {
-        uint32_t v[32];
-        tcgen05_ld_32x32b_x32(tmem_s[j & 1] + lane_addr + c * 32, v);
+        for (int c = 0; c < TK / 32; ++c) tcgen05_ld_32x32b_x32_nowait(tmem_s[j & 1] + lane_addr + c * 32, v[c]);
+        tcgen05_wait_ld();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) s[c * 32 + i] = __uint_as_float(v[i]);
+        for (int c = 0; c < TK / 32; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) s[c * 32 + i] = __uint_as_float(v[c][i]);
       }
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(s_empty(j & 1));  // the scores are in registers: the buffer may take tile j + 2
-      float mx = -INFINITY;
-      if (j0 + TK - 1 <= qpos && j0 >= qlo) {
-#pragma unroll
-        for (int i = 0; i < TK; ++i) {
-          s[i] *= scale_log2;
-          mx = fmaxf(mx, s[i]);
-        }
-      } else {
+      // the maximum of the raw scores (the scale is positive), masked by position; the scale goes into the exponent's
+      // multiply-add
+      if (!(j0 + TK - 1 <= qpos && j0 >= qlo)) {
 #pragma unroll
         for (int i = 0; i < TK; ++i) {
           const int key = j0 + i;
-          s[i] = (key <= qpos && key >= qlo) ? s[i] * scale_log2 : -INFINITY;
-          mx = fmaxf(mx, s[i]);
+          s[i] = (key <= qpos && key >= qlo) ? s[i] : -INFINITY;
         }
       }
-      const float m_new = fmaxf(m, mx);
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four chains: the maximum is not one long dependency
+#pragma unroll
+      for (int i = 0; i < TK; i += 4) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) mx4[e] = fmaxf(mx4[e], s[i + e]);
+      }
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      const float m_new = fmaxf(m, mx * scale_log2);
       const float msafe = m_new == -INFINITY ? 0.f : m_new;  // a row that has seen no key yet: every weight below is 0
-      const float corr = exp2f(m - msafe);                     // 0 when m is -inf
+      const float corr = ex2(m - msafe);                       // 0 when m is -inf
       m = m_new;
-      float sum = 0.f;
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
       uint32_t packed[TK / 2];
 #pragma unroll
       for (int i = 0; i < TK; i += 2) {
-        const float p0 = exp2f(s[i] - msafe), p1 = exp2f(s[i + 1] - msafe);
-        sum += p0 + p1;
+        const float p0 = ex2(fmaf(s[i], scale_log2, -msafe)), p1 = ex2(fmaf(s[i + 1], scale_log2, -msafe));
+        sum4[(i / 2) & 3] += p0 + p1;
         __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
         packed[i / 2] = *reinterpret_cast<uint32_t*>(&pb);
       }
+      const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       l = l * corr + sum;
       // the accumulator holds tiles 0 .. j - 1 once the product of tile j - 1 is done; then its row may be rescaled
       // and the P buffer (read by the product of tile j - 2) written
