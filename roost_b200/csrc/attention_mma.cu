@@ -972,8 +972,8 @@ __global__ void attention_merge_kernel(__nv_bfloat16* __restrict__ out, const fl
 bool prefill_tc_serves(int head_dim, int q_heads, int kv_heads, int page_size, long long pool_pages, const void* k_pool, const void* v_pool,
                        const void* q);
 int launch_prefill_tc(const void* q, long long tokens, void* out, const void* k_pool, const void* v_pool, const int32_t* q_indptr,
-                      const int32_t* kv_lens, const int32_t* kv_indptr, const int32_t* kv_indices, const int32_t* work, int items, int q_heads,
-                      int kv_heads, int head_dim, int page_size, long long pool_pages, float scale, int window, cudaStream_t s);
+                      const int32_t* kv_lens, const int32_t* kv_indptr, const int32_t* kv_indices, const int32_t* work, int items, int tile_rows,
+                      int q_heads, int kv_heads, int head_dim, int page_size, long long pool_pages, float scale, int window, cudaStream_t s);
 void set_prefill_tc(bool on);
 int prefill_tc_status();
 
@@ -988,6 +988,7 @@ static int page_shift_of(int page_size) {
 // grid fills the device several times over; with less work the smaller tiles spread it over more SMs. Both compute a row
 // with the same operations in the same order, so the choice does not show in the result.
 constexpr int kPrefillWideMinRows = 65536;  // packed rows x key/value heads from which 128-row tiles are used
+constexpr int kPrefillTwoGroupsMinRows = 32768;  // ... from which the tcgen05 kernel takes 256 rows a CTA
 
 template <int D, int MT>
 static int launch_prefill(const void* q, void* out, const void* k_pool, const void* v_pool, const int32_t* q_indptr, const int32_t* kv_lens,
@@ -1118,7 +1119,11 @@ using namespace roost;
 extern "C" int roost_attention_prefill_tile_rows(int head_dim, int q_heads, int kv_heads, int page_size, long long pool_pages,
                                                  const void* k_pool, const void* v_pool, long long packed_rows) {
   if (!roost_attention_mma_supported(head_dim)) return 0;
-  if (prefill_tc_serves(head_dim, q_heads, kv_heads, page_size, pool_pages, k_pool, v_pool, nullptr)) return 128;
+  if (prefill_tc_serves(head_dim, q_heads, kv_heads, page_size, pool_pages, k_pool, v_pool, nullptr)) {
+    // two row groups a CTA keep the tensor cores busy while the other group's softmax runs; with little work the
+    // smaller items spread over more SMs
+    return packed_rows * kv_heads >= kPrefillTwoGroupsMinRows ? 256 : 128;
+  }
   return head_dim <= 128 && packed_rows * kv_heads >= kPrefillWideMinRows ? 128 : 64;
 }
 
@@ -1151,13 +1156,15 @@ extern "C" int roost_attention_prefill(const void* q, long long tokens, void* ou
                                        const int32_t* kv_indices, const int32_t* work, int items, int tile_rows, int q_heads, int kv_heads,
                                        int head_dim, int page_size, long long pool_pages, float scale, int window, roost_stream_t stream) {
   ROOST_REQUIRE(items >= 0 && q_heads > 0 && kv_heads > 0 && page_size > 0, "attention_prefill: sizes must be positive");
-  ROOST_REQUIRE(tile_rows == 64 || (tile_rows == 128 && head_dim <= 128), "attention_prefill: a work item has 64 packed rows, or 128 up to head size 128");
+  ROOST_REQUIRE(tile_rows == 64 || ((tile_rows == 128 || tile_rows == 256) && head_dim <= 128),
+                "attention_prefill: a work item has 64 packed rows, or 128 or 256 up to head size 128");
   ROOST_REQUIRE(q_heads % kv_heads == 0, "attention_prefill: q_heads must be a multiple of kv_heads");
   if (kv_heads > 65535) return fail(ROOST_ERR_UNSUPPORTED, "attention_prefill: more than 65535 key/value heads");
   if (items == 0) return ROOST_OK;
-  if (tile_rows == 128 && tokens > 0 && prefill_tc_serves(head_dim, q_heads, kv_heads, page_size, pool_pages, k_pool, v_pool, q)) {
-    return launch_prefill_tc(q, tokens, out, k_pool, v_pool, q_indptr, kv_lens, kv_indptr, kv_indices, work, items, q_heads, kv_heads, head_dim,
-                             page_size, pool_pages, scale, window, (cudaStream_t)stream);
+  if ((tile_rows == 128 || tile_rows == 256) && tokens > 0 &&
+      prefill_tc_serves(head_dim, q_heads, kv_heads, page_size, pool_pages, k_pool, v_pool, q)) {
+    return launch_prefill_tc(q, tokens, out, k_pool, v_pool, q_indptr, kv_lens, kv_indptr, kv_indices, work, items, tile_rows, q_heads, kv_heads,
+                             head_dim, page_size, pool_pages, scale, window, (cudaStream_t)stream);
   }
   if (tile_rows == 128) {
     switch (head_dim) {

@@ -43,43 +43,47 @@ __device__ __forceinline__ float ex2(float x) {
   return y;
 }
 
-template <int D>
-constexpr int tc_stages() {
-  return D == 128 ? 4 : 6;
+template <int D, int NG>
+constexpr int tc_stages() {  // what fits beside NG Q tiles and NG P tiles in 227 KB
+  return D == 128 ? (NG == 1 ? 4 : 3) : 6;
 }
 
-// work[i] = (batch row, first packed row of the tile of 128)
-template <int D, int RPC>
-__global__ void __launch_bounds__(192, 1)
+// work[i] = (batch row, first packed row of the CTA's NG x 128 rows)
+template <int D, int RPC, int NG>
+__global__ void __launch_bounds__(64 + NG * 128, 1)
     attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                                const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out, const int32_t* __restrict__ q_indptr, const int32_t* __restrict__ kv_lens,
-                                const int32_t* __restrict__ kv_indptr, const int32_t* __restrict__ kv_indices, const int2* __restrict__ work,
-                                int q_heads, int kv_heads, int page_size, float scale_log2, int window) {
-  constexpr int BM = kTcRows, TK = kTcKeys, STAGES = tc_stages<D>(), NP = TK / RPC, CB = D / 64;
-  constexpr uint32_t kQBytes = BM * D * 2;
+                                const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out, const int32_t* __restrict__ q_indptr,
+                                const int32_t* __restrict__ kv_lens, const int32_t* __restrict__ kv_indptr,
+                                const int32_t* __restrict__ kv_indices, const int2* __restrict__ work, int q_heads, int kv_heads, int page_size,
+                                float scale_log2, int window) {
+  constexpr int BM = kTcRows, TK = kTcKeys, STAGES = tc_stages<D, NG>(), NP = TK / RPC, CB = D / 64;
+  constexpr uint32_t kQBytes = BM * D * 2;                  // one row group's Q tile
   constexpr uint32_t kStageBytes = 2 * TK * D * 2;          // keys and values of TK positions
   constexpr uint32_t kKeys = TK * D * 2;                    // a stage's keys: [column block][TK rows][128 B], K-major for one product
   constexpr uint32_t kVPage = CB * RPC * 128;               // its values, page copy by page copy: [column block][RPC rows][128 B]
   constexpr int kOps = NP * (CB + 1);                       // copies a stage takes: per page one per column block of keys, one of values
   static_assert(kOps <= 32, "one lane a copy");
-  constexpr uint32_t kPBytes = BM * 128;                    // P tile: 128 rows x 64 keys of bfloat16
-  constexpr uint32_t kTmemCols = 2 * TK + D <= 256 ? 256 : 512;
+  constexpr uint32_t kPBytes = BM * 128;                    // a row group's P tile: 128 rows x 64 keys of bfloat16
+  constexpr uint32_t kGroupCols = 2 * TK + D;               // tensor-memory columns of a row group: two score buffers and the output
+  constexpr uint32_t kTmemCols = NG * kGroupCols <= 256 ? 256 : 512;
+  static_assert(NG * kGroupCols <= 512, "tensor memory has 512 columns");
+  constexpr int kGroupBars = 8;                             // s_full[2], s_empty[2], p_full[2], pv_done[2]
   extern __shared__ unsigned char smem_raw[];
   const uint32_t smem_base = ((uint32_t)__cvta_generic_to_shared(smem_raw) + 1023u) & ~1023u;
   const uint32_t q_smem = smem_base;
-  const uint32_t kv_smem = q_smem + kQBytes;
+  const uint32_t kv_smem = q_smem + NG * kQBytes;
   const uint32_t p_smem = kv_smem + STAGES * kStageBytes;
-  __shared__ __align__(8) uint64_t bars[1 + 2 * STAGES + 8];
+  __shared__ __align__(8) uint64_t bars[1 + 2 * STAGES + NG * kGroupBars];
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
   const uint32_t bar0 = (uint32_t)__cvta_generic_to_shared(bars);
   const uint32_t q_full = bar0;
   auto kv_full = [&](int s) { return bar0 + 8u * (1 + s); };
   auto kv_empty = [&](int s) { return bar0 + 8u * (1 + STAGES + s); };
-  auto s_full = [&](int i) { return bar0 + 8u * (1 + 2 * STAGES + i); };
-  auto s_empty = [&](int i) { return bar0 + 8u * (1 + 2 * STAGES + 2 + i); };
-  auto p_full = [&](int i) { return bar0 + 8u * (1 + 2 * STAGES + 4 + i); };
-  auto pv_done = [&](int i) { return bar0 + 8u * (1 + 2 * STAGES + 6 + i); };
+  auto s_full = [&](int g, int i) { return bar0 + 8u * (1 + 2 * STAGES + g * kGroupBars + i); };
+  auto s_empty = [&](int g, int i) { return bar0 + 8u * (1 + 2 * STAGES + g * kGroupBars + 2 + i); };
+  auto p_full = [&](int g, int i) { return bar0 + 8u * (1 + 2 * STAGES + g * kGroupBars + 4 + i); };
+  auto pv_done = [&](int g, int i) { return bar0 + 8u * (1 + 2 * STAGES + g * kGroupBars + 6 + i); };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
@@ -90,13 +94,15 @@ __global__ void __launch_bounds__(192, 1)
     mbar_init(q_full, 1);
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(kv_full(s), 1);
-      mbar_init(kv_empty(s), 1);
+      mbar_init(kv_empty(s), NG);  // every row group hands the stage back (or the issuer does for a group that skips the tile)
     }
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(s_full(i), 1);
-      mbar_init(s_empty(i), 4);
-      mbar_init(p_full(i), 4);
-      mbar_init(pv_done(i), 1);
+    for (int g = 0; g < NG; ++g) {
+      for (int i = 0; i < 2; ++i) {
+        mbar_init(s_full(g, i), 1);
+        mbar_init(s_empty(g, i), 4);
+        mbar_init(p_full(g, i), 4);
+        mbar_init(pv_done(g, i), 1);
+      }
     }
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
@@ -115,8 +121,8 @@ __global__ void __launch_bounds__(192, 1)
   __syncthreads();
   tcgen05_fence_after();
   const uint32_t tmem_base = tmem_slot;
-  const uint32_t tmem_s[2] = {tmem_base, tmem_base + TK};
-  const uint32_t tmem_o = tmem_base + 2 * TK;
+  auto tmem_s = [&](int g, int i) { return tmem_base + (uint32_t)g * kGroupCols + (uint32_t)i * TK; };
+  auto tmem_o = [&](int g) { return tmem_base + (uint32_t)g * kGroupCols + 2 * TK; };
   volatile int* abortp = &abort_flag;
 
   const int kvh = blockIdx.y;
@@ -126,11 +132,29 @@ __global__ void __launch_bounds__(192, 1)
   const int kv_len = kv_lens[b];
   const int pos0 = kv_len - n;
   const int rows_total = n * group;
-  // the tile's key range: up to the last row's position, from the first row's window
-  const int last_row = min(row0 + BM, rows_total) - 1;
-  const int hi = pos0 + last_row / group;
-  const int lo = window > 0 ? max(0, pos0 + row0 / group - window + 1) : 0;
-  const int t0 = lo / TK, ntiles = hi / TK - t0 + 1;
+  // Key tiles of each row group: from its first row's window to its last row's position; a group past the request's
+  // rows has none. The CTA walks the union (the groups' ranges overlap or touch: later rows see later keys).
+  int g_first[NG], g_last[NG];  // first and last key tile of the group (last < first: none)
+#pragma unroll
+  for (int g = 0; g < NG; ++g) {
+    const int r0 = row0 + g * BM;
+    if (r0 < rows_total) {
+      const int last_row = min(r0 + BM, rows_total) - 1;
+      g_last[g] = (pos0 + last_row / group) / TK;
+      g_first[g] = (window > 0 ? max(0, pos0 + r0 / group - window + 1) : 0) / TK;
+    } else {
+      g_first[g] = 1;
+      g_last[g] = 0;
+    }
+  }
+  int t0 = g_first[0], t1 = g_last[0];
+#pragma unroll
+  for (int g = 1; g < NG; ++g) {
+    if (g_last[g] >= g_first[g]) t1 = max(t1, g_last[g]);
+  }
+  const int ntiles = t1 - t0 + 1;
+  const int lo = window > 0 ? max(0, pos0 + row0 / group - window + 1) : 0;                    // first key any row of the CTA sees
+  const int hi = min(pos0 + (min(row0 + NG * BM, rows_total) - 1) / group, (t1 + 1) * TK - 1);  // last one
 
   if (warp == 0) {
     // ---- producer
@@ -146,8 +170,9 @@ __global__ void __launch_bounds__(192, 1)
     int cur = row_of(batch0 + lane, batch0 + lane <= p_last ? pages[batch0 + lane] : -1);
     int nxt_entry = batch0 + 32 + lane <= p_last ? pages[batch0 + 32 + lane] : -1;
     if (lane == 0) {
-      mbar_expect_tx(q_full, kQBytes);
-      tma_load_5d(q_smem, &map_q, q_full, 0, 0, kvh, q_start + row0 / group, 0);
+      mbar_expect_tx(q_full, NG * kQBytes);  // rows past the tensor's last token are filled with zeros and counted
+#pragma unroll
+      for (int g = 0; g < NG; ++g) tma_load_5d(q_smem + g * kQBytes, &map_q, q_full, 0, 0, kvh, q_start + (row0 + g * BM) / group, 0);
     }
     bool ok = true;
     for (int i = 0; i < ntiles && ok; ++i) {
@@ -184,77 +209,81 @@ __global__ void __launch_bounds__(192, 1)
       constexpr uint32_t idesc_o = umma_idesc_bf16_b_mn(BM, D);
       bool ok = mbar_wait_limited(q_full, 0, abortp, 2, &g_attention_tc_error);
       tcgen05_fence_after();
-      auto issue_pv = [&](int j) {  // O += P_j V_j
-        const int stage = j % STAGES;
-        if (!(ok = mbar_wait_limited(p_full(j & 1), (uint32_t)(j >> 1) & 1u, abortp, 3, &g_attention_tc_error))) return;
+      // O_g += P V of the group's tile number j (the CTA's tile i): after it the stage is the group's no longer
+      auto issue_pv = [&](int g, int j, int i) {
+        const int stage = i % STAGES;
+        if (!(ok = mbar_wait_limited(p_full(g, j & 1), (uint32_t)(j >> 1) & 1u, abortp, 3, &g_attention_tc_error))) return;
         tcgen05_fence_after();
         const uint32_t v0 = kv_smem + stage * kStageBytes + kKeys;
 #pragma unroll
         for (int kk = 0; kk < TK / 16; ++kk) {
           const uint32_t v_rows = v0 + (uint32_t)((kk * 16) / RPC) * kVPage + (uint32_t)((kk * 16) % RPC) * 128;
-          const uint64_t a_desc = umma_desc_k_major_sw128(p_smem + (j & 1) * kPBytes) + (uint64_t)(2 * kk);
+          const uint64_t a_desc = umma_desc_k_major_sw128(p_smem + g * kPBytes) + (uint64_t)(2 * kk);
           const uint64_t b_desc = umma_desc_mn_major_sw128(v_rows, RPC * 128, 1024);
-          tcgen05_mma_f16(tmem_o, a_desc, b_desc, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+          tcgen05_mma_f16(tmem_o(g), a_desc, b_desc, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
         }
-        tcgen05_commit(kv_empty(stage));  // the stage is free once these products have read it
-        tcgen05_commit(pv_done(j & 1));
+        tcgen05_commit(kv_empty(stage));  // the stage is free (for this group) once these products have read it
+        tcgen05_commit(pv_done(g, j & 1));
       };
-#ifdef ROOST_TRACE
-      unsigned long long tr_i[16][2];
-#endif
-      for (int j = 0; j < ntiles && ok; ++j) {
-        const int stage = j % STAGES;
-        if (!(ok = mbar_wait_limited(kv_full(stage), (uint32_t)(j / STAGES) & 1u, abortp, 4, &g_attention_tc_error))) break;
-        if (j >= 2 && !(ok = mbar_wait_limited(s_empty(j & 1), (uint32_t)((j >> 1) - 1) & 1u, abortp, 5, &g_attention_tc_error))) break;
+      // the second product of tile i for every group that has it; a group without it gives the stage back at once
+      auto finish_tile = [&](int i) {
+#pragma unroll
+        for (int g = 0; g < NG; ++g) {
+          const int t = t0 + i;
+          if (t >= g_first[g] && t <= g_last[g]) {
+            if (ok) issue_pv(g, t - g_first[g], i);
+          } else {
+            mbar_arrive(kv_empty(i % STAGES));
+          }
+        }
+      };
+      for (int i = 0; i < ntiles && ok; ++i) {
+        const int stage = i % STAGES, t = t0 + i;
+        if (!(ok = mbar_wait_limited(kv_full(stage), (uint32_t)(i / STAGES) & 1u, abortp, 4, &g_attention_tc_error))) break;
         tcgen05_fence_after();
         const uint32_t k0 = kv_smem + stage * kStageBytes;
 #pragma unroll
-        for (int k = 0; k < D / 16; ++k) {
-          const uint64_t a_desc = umma_desc_k_major_sw128(q_smem + (k / 4) * (BM * 128)) + (uint64_t)(2 * (k % 4));
-          const uint64_t b_desc = umma_desc_k_major_sw128(k0 + (k / 4) * (TK * 128)) + (uint64_t)(2 * (k % 4));
-          tcgen05_mma_f16(tmem_s[j & 1], a_desc, b_desc, idesc_s, k > 0 ? 1u : 0u);
+        for (int g = 0; g < NG; ++g) {
+          if (t < g_first[g] || t > g_last[g]) continue;
+          const int j = t - g_first[g];
+          if (j >= 2 && !(ok = mbar_wait_limited(s_empty(g, j & 1), (uint32_t)((j >> 1) - 1) & 1u, abortp, 5, &g_attention_tc_error))) break;
+          tcgen05_fence_after();
+#pragma unroll
+          for (int k = 0; k < D / 16; ++k) {
+            const uint64_t a_desc = umma_desc_k_major_sw128(q_smem + g * kQBytes + (k / 4) * (BM * 128)) + (uint64_t)(2 * (k % 4));
+            const uint64_t b_desc = umma_desc_k_major_sw128(k0 + (k / 4) * (TK * 128)) + (uint64_t)(2 * (k % 4));
+            tcgen05_mma_f16(tmem_s(g, j & 1), a_desc, b_desc, idesc_s, k > 0 ? 1u : 0u);
+          }
+          tcgen05_commit(s_full(g, j & 1));
         }
-        tcgen05_commit(s_full(j & 1));
-#ifdef ROOST_TRACE
-        if (j < 16) tr_i[j][0] = trace_now();
-#endif
-        if (j >= 1) issue_pv(j - 1);
-#ifdef ROOST_TRACE
-        if (j < 16) tr_i[j][1] = trace_now();
-#endif
+        if (ok && i >= 1) finish_tile(i - 1);
       }
-      if (ok && ntiles > 0) issue_pv(ntiles - 1);
-#ifdef ROOST_TRACE
-      if (blockIdx.x == 0 && blockIdx.y == 0) trace_flush(200, 0, &tr_i[0][0], 2 * min(ntiles, 16));
-#endif
+      if (ok && ntiles > 0) finish_tile(ntiles - 1);
     }
   } else {
-    // ---- softmax, correction, epilogue: one thread a row
+    // ---- softmax, correction, epilogue: one thread a row, four warps a row group
+    const int g = (warp - 2) / 4;
     const int lane_group = warp & 3;               // the tensor-memory lanes this warp may touch
-    const int row = lane_group * 32 + lane;
-    const int pr = row0 + row;
+    const int row = lane_group * 32 + lane;        // row within the group
+    const int pr = row0 + g * BM + row;
     const bool valid = pr < rows_total;
     const int qpos = valid ? pos0 + pr / group : -1;
     const int qlo = valid && window > 0 ? max(0, qpos - window + 1) : 0;
     const uint32_t lane_addr = (uint32_t)(lane_group * 32) << 16;
+    const int my_tiles = g_last[g] - g_first[g] + 1;  // at most 0 for a group without rows
+    const int tid_g = threadIdx.x - 64 - g * 128;     // 0 .. 127 within the group
     float m = -INFINITY, l = 0.f;
     bool ok = true;
-#ifdef ROOST_TRACE
-    unsigned long long tr_s[16][4];
-#endif
-    for (int j = 0; j < ntiles && ok; ++j) {
-      const int stage = j % STAGES;
-      const int j0 = (t0 + j) * TK;
-      if (!(ok = mbar_wait_limited(s_full(j & 1), (uint32_t)(j >> 1) & 1u, abortp, 6, &g_attention_tc_error))) break;
-#ifdef ROOST_TRACE
-      if (j < 16) tr_s[j][0] = trace_now();
-#endif
+    for (int j = 0; j < my_tiles && ok; ++j) {
+      const int stage = (g_first[g] + j - t0) % STAGES;
+      const int j0 = (g_first[g] + j) * TK;
+      if (!(ok = mbar_wait_limited(s_full(g, j & 1), (uint32_t)(j >> 1) & 1u, abortp, 6, &g_attention_tc_error))) break;
       tcgen05_fence_after();
       float s[TK];
       {
         uint32_t v[TK / 32][32];
 #pragma unroll
-        for (int c = 0; c < TK / 32; ++c) tcgen05_ld_32x32b_x32_nowait(tmem_s[j & 1] + lane_addr + c * 32, v[c]);
+        for (int c = 0; c < TK / 32; ++c) tcgen05_ld_32x32b_x32_nowait(tmem_s(g, j & 1) + lane_addr + c * 32, v[c]);
         tcgen05_wait_ld();
 #pragma unroll
         for (int c = 0; c < TK / 32; ++c)
@@ -263,9 +292,7 @@ __global__ void __launch_bounds__(192, 1)
       }
       tcgen05_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(s_empty(j & 1));  // the scores are in registers: the buffer may take tile j + 2
-      // the maximum of the raw scores (the scale is positive), masked by position; the scale goes into the exponent's
-      // multiply-add
+      if (lane == 0) mbar_arrive(s_empty(g, j & 1));  // the scores are in registers: the buffer may take tile j + 2
       if (!(j0 + TK - 1 <= qpos && j0 >= qlo)) {
 #pragma unroll
         for (int i = 0; i < TK; ++i) {
@@ -273,7 +300,8 @@ __global__ void __launch_bounds__(192, 1)
           s[i] = (key <= qpos && key >= qlo) ? s[i] : -INFINITY;
         }
       }
-      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four chains: the maximum is not one long dependency
+      // the maximum of the raw scores (the scale is positive); four chains, so that it is not one long dependency
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
       for (int i = 0; i < TK; i += 4) {
 #pragma unroll
@@ -293,34 +321,27 @@ __global__ void __launch_bounds__(192, 1)
         __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
         packed[i / 2] = *reinterpret_cast<uint32_t*>(&pb);
       }
-      const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-      l = l * corr + sum;
+      l = l * corr + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
       // the accumulator holds tiles 0 .. j - 1 once the product of tile j - 1 is done; then its row may be rescaled
-      // and the P buffer (read by the product of tile j - 2) written
-#ifdef ROOST_TRACE
-      if (j < 16) tr_s[j][1] = trace_now();
-#endif
-      if (j >= 1 && !(ok = mbar_wait_limited(pv_done((j - 1) & 1), (uint32_t)((j - 1) >> 1) & 1u, abortp, 7, &g_attention_tc_error))) break;
-#ifdef ROOST_TRACE
-      if (j < 16) tr_s[j][2] = trace_now();
-#endif
+      // and the P tile (which that product read) written again
+      if (j >= 1 && !(ok = mbar_wait_limited(pv_done(g, (j - 1) & 1), (uint32_t)((j - 1) >> 1) & 1u, abortp, 7, &g_attention_tc_error))) break;
       tcgen05_fence_after();
       if (j >= 1 && __any_sync(0xffffffffu, corr != 1.0f)) {
 #pragma unroll 1
         for (int c = 0; c < D / 32; ++c) {
           uint32_t v[32];
-          tcgen05_ld_32x32b_x32(tmem_o + lane_addr + c * 32, v);
+          tcgen05_ld_32x32b_x32(tmem_o(g) + lane_addr + c * 32, v);
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * corr);
-          tcgen05_st_32x32b_x32(tmem_o + lane_addr + c * 32, v);
+          tcgen05_st_32x32b_x32(tmem_o(g) + lane_addr + c * 32, v);
         }
       }
       // value rows at positions the request does not hold yet, and rows before the first visible key (their page may
       // have been given back and replaced by another): zero (the copies of this stage have landed: the scores of this
-      // tile were computed from the same stage)
+      // tile were computed from the same stage). Every row group does it before its own second product.
       if (j0 + TK > kv_len || j0 < lo) {
         const uint32_t v0 = kv_smem + stage * kStageBytes + kKeys;
-        for (int idx = threadIdx.x - 64; idx < TK * (D / 8); idx += 128) {
+        for (int idx = tid_g; idx < TK * (D / 8); idx += 128) {
           const int r = idx / (D / 8), ch = idx % (D / 8);
           if (j0 + r >= kv_len || j0 + r < lo) {
             const uint32_t addr = v0 + (uint32_t)(r / RPC) * kVPage + (uint32_t)(ch >> 3) * (RPC * 128) + (uint32_t)(r % RPC) * 128 +
@@ -330,7 +351,7 @@ __global__ void __launch_bounds__(192, 1)
         }
       }
       // the row of P: 64 bfloat16 = 128 bytes = eight 16-byte chunks, swizzled by the row
-      const uint32_t p_row = p_smem + (j & 1) * kPBytes + (uint32_t)row * 128;
+      const uint32_t p_row = p_smem + g * kPBytes + (uint32_t)row * 128;
 #pragma unroll
       for (int ch = 0; ch < 8; ++ch) {
         asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};\n" ::"r"(p_row + (uint32_t)((ch ^ (row & 7)) << 4)), "r"(packed[4 * ch]),
@@ -340,24 +361,20 @@ __global__ void __launch_bounds__(192, 1)
       asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // the stores are visible to the tensor cores' reads
       tcgen05_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(p_full(j & 1));
-#ifdef ROOST_TRACE
-      if (j < 16) tr_s[j][3] = trace_now();
-#endif
+      if (lane == 0) mbar_arrive(p_full(g, j & 1));
     }
-#ifdef ROOST_TRACE
-    if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 64) trace_flush(201, 0, &tr_s[0][0], 4 * min(ntiles, 16));
-#endif
     // epilogue: O / l
-    if (ok && ntiles > 0) ok = mbar_wait_limited(pv_done((ntiles - 1) & 1), (uint32_t)((ntiles - 1) >> 1) & 1u, abortp, 8, &g_attention_tc_error);
-    if (ok) {
+    if (ok && my_tiles > 0) {
+      ok = mbar_wait_limited(pv_done(g, (my_tiles - 1) & 1), (uint32_t)((my_tiles - 1) >> 1) & 1u, abortp, 8, &g_attention_tc_error);
+    }
+    if (ok && my_tiles > 0) {
       tcgen05_fence_after();
       const float inv = l > 0.f ? 1.0f / l : 0.f;
       __nv_bfloat16* dst = valid ? out + ((size_t)(q_start + pr / group) * q_heads + kvh * group + pr % group) * D : nullptr;
 #pragma unroll 1
       for (int c = 0; c < D / 32; ++c) {
         uint32_t v[32];
-        tcgen05_ld_32x32b_x32(tmem_o + lane_addr + c * 32, v);
+        tcgen05_ld_32x32b_x32(tmem_o(g) + lane_addr + c * 32, v);
         if (valid) {
 #pragma unroll
           for (int i = 0; i < 32; i += 8) {
@@ -403,25 +420,27 @@ bool prefill_tc_serves(int head_dim, int q_heads, int kv_heads, int page_size, l
   return (uintptr_t)k_pool % 128 == 0 && (q == nullptr || (uintptr_t)q % 16 == 0) && encode_tiled() != nullptr;
 }
 
-template <int D, int RPC>
+template <int D, int RPC, int NG>
 static int launch_tc(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, void* out, const int32_t* q_indptr, const int32_t* kv_lens,
                      const int32_t* kv_indptr, const int32_t* kv_indices, const int32_t* work, int items, int q_heads, int kv_heads,
                      int page_size, float scale, int window, cudaStream_t s) {
-  constexpr size_t smem = (size_t)kTcRows * D * 2 + (size_t)tc_stages<D>() * 2 * kTcKeys * D * 2 + 2 * kTcRows * 128 + 1024;
-  auto kernel = attention_prefill_tc_kernel<D, RPC>;
+  constexpr size_t smem = (size_t)NG * kTcRows * D * 2 + (size_t)tc_stages<D, NG>() * 2 * kTcKeys * D * 2 + (size_t)NG * kTcRows * 128 + 1024;
+  auto kernel = attention_prefill_tc_kernel<D, RPC, NG>;
   static bool attr_set = false;
   if (!attr_set) {
     cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     attr_set = true;
   }
-  launch_kernel(kernel, dim3(items, kv_heads), dim3(192), smem, s, mq, mk, mv, (__nv_bfloat16*)out, q_indptr, kv_lens, kv_indptr, kv_indices,
-                (const int2*)work, q_heads, kv_heads, page_size, scale * kLog2eTc, window);
+  launch_kernel(kernel, dim3(items, kv_heads), dim3(64 + NG * 128), smem, s, mq, mk, mv, (__nv_bfloat16*)out, q_indptr, kv_lens, kv_indptr,
+                kv_indices, (const int2*)work, q_heads, kv_heads, page_size, scale * kLog2eTc, window);
   return check_launch("attention_prefill_tc");
 }
 
 int launch_prefill_tc(const void* q, long long tokens, void* out, const void* k_pool, const void* v_pool, const int32_t* q_indptr,
-                      const int32_t* kv_lens, const int32_t* kv_indptr, const int32_t* kv_indices, const int32_t* work, int items, int q_heads,
-                      int kv_heads, int head_dim, int page_size, long long pool_pages, float scale, int window, cudaStream_t s) {
+                      const int32_t* kv_lens, const int32_t* kv_indptr, const int32_t* kv_indices, const int32_t* work, int items, int tile_rows,
+                      int q_heads, int kv_heads, int head_dim, int page_size, long long pool_pages, float scale, int window, cudaStream_t s) {
+  if (tile_rows != 128 && tile_rows != 256) return fail(ROOST_ERR_INVALID, "attention_prefill: the tcgen05 kernel takes work items of 128 or 256 packed rows");
+  const int groups = tile_rows / kTcRows;
   const int group = q_heads / kv_heads;
   CUtensorMap mq;
   {
@@ -459,14 +478,18 @@ int launch_prefill_tc(const void* q, long long tokens, void* out, const void* k_
                                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(ROOST_ERR_CUDA, "attention_prefill: cuTensorMapEncodeTiled (values) failed with code " + std::to_string((int)r));
   }
-#define ROOST_TC_CASE(DD, RR)                                                                                                          \
-  if (head_dim == DD && box_rows == RR)                                                                                                \
-    return launch_tc<DD, RR>(mq, mk, mv, out, q_indptr, kv_lens, kv_indptr, kv_indices, work, items, q_heads, kv_heads, page_size, scale, \
-                             window, s);
-  ROOST_TC_CASE(128, 16)
-  ROOST_TC_CASE(128, 32)
-  ROOST_TC_CASE(64, 16)
-  ROOST_TC_CASE(64, 32)
+#define ROOST_TC_CASE(DD, RR, GG)                                                                                                      \
+  if (head_dim == DD && box_rows == RR && groups == GG)                                                                                \
+    return launch_tc<DD, RR, GG>(mq, mk, mv, out, q_indptr, kv_lens, kv_indptr, kv_indices, work, items, q_heads, kv_heads, page_size, \
+                                 scale, window, s);
+  ROOST_TC_CASE(128, 16, 1)
+  ROOST_TC_CASE(128, 32, 1)
+  ROOST_TC_CASE(64, 16, 1)
+  ROOST_TC_CASE(64, 32, 1)
+  ROOST_TC_CASE(128, 16, 2)
+  ROOST_TC_CASE(128, 32, 2)
+  ROOST_TC_CASE(64, 16, 2)
+  ROOST_TC_CASE(64, 32, 2)
 #undef ROOST_TC_CASE
   return fail(ROOST_ERR_UNSUPPORTED, "attention_prefill: no tcgen05 kernel for these sizes");
 }

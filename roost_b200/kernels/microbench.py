@@ -145,7 +145,7 @@ def main(argv=None) -> int:
     p.add_argument("--head-dim", type=int, default=128)
     p.add_argument("--page-size", type=int, default=16)
     p.add_argument("--chunk", type=int, default=0, help="keys per decode work item (default: the library's)")
-    p.add_argument("--tile-rows", type=int, default=0, help="packed rows per prefill work item (default: the library's choice)")
+    p.add_argument("--tile-rows", type=int, default=0, help="packed rows per prefill work item: 64, 128 or 256 (default: the library's choice)")
     p.add_argument("--cp-async", action="store_true", help="decode attention through the cp.async kernel instead of TMA")
     p.add_argument("--mma-sync", action="store_true", help="prefill attention through the mma.sync kernel instead of tcgen05")
     p.add_argument("--sequential-pages", action="store_true")

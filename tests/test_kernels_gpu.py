@@ -338,6 +338,11 @@ def test_attention_mma_mixed_rows(kernels, window, nq, nkv, d, page):
     group = nq // nkv
     tc_serves = d in (64, 128) and group & (group - 1) == 0 and page >= 16
     assert torch.equal(legacy, out) != tc_serves, "the tcgen05 kernel serves exactly these sizes (its tiles round differently)"
+    if tc_serves:
+        # two row groups a CTA (work items of 256 packed rows) compute every row as one group does
+        both, both_plan = run_mma(kernels, q, kp, vp, lens, news, indptr, indices, scale, window, tile_rows=256)
+        assert both_plan.prefill_items < plan.prefill_items
+        assert torch.equal(both, out), "one and two row groups a CTA differ"
     if d <= 128:
         # work items of 128 packed rows (two row tiles a warp) compute every row with the same operations in the same order
         kernels.attention_set_prefill_tc(False)
