@@ -988,7 +988,7 @@ static int page_shift_of(int page_size) {
 // grid fills the device several times over; with less work the smaller tiles spread it over more SMs. Both compute a row
 // with the same operations in the same order, so the choice does not show in the result.
 constexpr int kPrefillWideMinRows = 65536;  // packed rows x key/value heads from which 128-row tiles are used
-constexpr int kPrefillTwoGroupsMinRows = 32768;  // ... from which the tcgen05 kernel takes 256 rows a CTA
+constexpr int kPrefillTwoGroupsMinRows = 131072;  // ... from which the tcgen05 kernel takes 256 rows a CTA
 
 template <int D, int MT>
 static int launch_prefill(const void* q, void* out, const void* k_pool, const void* v_pool, const int32_t* q_indptr, const int32_t* kv_lens,

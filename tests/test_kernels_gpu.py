@@ -285,7 +285,8 @@ def run_mma(kernels, q, kp, vp, lens, news, indptr, indices, scale, window, chun
     return kernels.attention_mma(q.cuda(), kp, vp, q_indptr, kv_lens, indptr, indices, plan, scale, window), plan
 
 
-MMA_SHAPES = [(4, 2, 16, 16), (6, 1, 32, 8), (8, 2, 128, 16), (14, 2, 64, 32), (2, 1, 256, 16), (16, 1, 64, 16), (40, 2, 128, 16)]
+MMA_SHAPES = [(4, 2, 16, 16), (6, 1, 32, 8), (8, 2, 128, 16), (14, 2, 64, 32), (2, 1, 256, 16), (16, 1, 64, 16), (40, 2, 128, 16),
+              (8, 2, 64, 32), (4, 1, 128, 64)]
 
 
 @pytest.mark.parametrize("window", [None, 37, 300])
