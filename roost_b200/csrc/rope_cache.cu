@@ -167,10 +167,10 @@ extern "C" int roost_qk_norm_rope_cache(const void* qkv, int64_t qkv_stride, voi
   }
   if (tokens == 0) return ROOST_OK;
   const int slots = q_heads + (write_kv ? 2 * kv_heads : 0);
-  // many tokens: one block of sixteen warps a token, the rotation table computed once a token; few tokens: four head
+  // many tokens: one block of eight warps a token, the rotation table computed once a token; few tokens: four head
   // slots a block, so that a decode step still spreads over the device
   const bool many = tokens >= 512;
-  const int warps = many ? 16 : 4;
+  const int warps = many ? 8 : 4;
   dim3 grid(tokens, many ? 1 : (slots + warps - 1) / warps);
   if (grid.y > 65535) return fail(ROOST_ERR_UNSUPPORTED, "qk_norm_rope_cache: more than 262140 head slots per token");
   const size_t table_bytes = (size_t)(rotary_dim / 2) * sizeof(float2);
