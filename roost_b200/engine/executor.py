@@ -152,9 +152,11 @@ class StepExecutor:
         self.steps_run = 0
         self.last_upload_bytes = 0
         # decode steps are replayed from captured graphs when every run keeps paged keys and values only (a mixer with
-        # state of its own may be written in Python and may not be idempotent, so such models run eagerly)
+        # state of its own may be written in Python and may not be idempotent, so such models run eagerly) and every
+        # part says that its call can be captured
         self.use_graphs = (use_graphs and self.rt.device.type == "cuda"
-                           and all(g.kind == "paged" or not g.runs for g in self.groups))
+                           and all(g.kind == "paged" or not g.runs for g in self.groups)
+                           and all(getattr(p, "capturable", True) for p in model.parts()))
         self._graphs: dict = {}
         self._plan_keys: list | None = None
         self.graph_replays = 0

@@ -77,6 +77,12 @@ class Model:
         else:
             self.lm_head.load(placed["lm_head"]["weight"])
 
+    def parts(self):
+        """Every part of every block, for questions asked of all of them."""
+        for b in self.blocks:
+            yield b
+            yield from b.sub_parts().values()
+
     def weight_bytes(self) -> int:
         seen, total = set(), 0
 

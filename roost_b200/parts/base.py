@@ -66,6 +66,10 @@ class Runtime:
 
 class Part:
     spec = None
+    # False for a part whose call reads device values on the host or launches a number of kernels that depends on the
+    # data (routing written in Python, say): a model with such a part runs its decode steps eagerly instead of
+    # replaying a captured CUDA graph. A class that does not derive from Part may set the attribute all the same.
+    capturable = True
 
     @classmethod
     def parameters(cls, spec) -> dict[str, ParamDecl]:

@@ -391,3 +391,152 @@ def test_block_arrangement_alone(backend, tiny_model_dirs):
     out, residual = block(h.to(rt.device), None, batch, storage.view(0))
     got = out.double().cpu() + residual.double().cpu()       # the block hands back the branch output and the stream it joins
     assert H.scaled_error(got, want) < (1e-5 if rt.full_precision else 2 ** -4)
+
+
+# ------------------------------------------------------------------------------------------ a toy feed-forward with routing, a toy position encoding
+@dataclass(frozen=True)
+class ToyRoutedSpec:
+    """Two (or more) small SwiGLU experts and a router that sends every token to the expert with the largest logit and
+    scales the expert's output by the softmax weight of that logit."""
+    kind: str = "toy_top1_experts"
+    hidden: int = 0
+    intermediate: int = 0
+    experts: int = 2
+
+
+class ToyTop1Experts:
+    """Defined in the test only: registered, built, loaded and stepped through the package's interfaces."""
+    capturable = False   # the routing below reads device values on the host: no CUDA graph for this model's decode steps
+
+    def __init__(self, spec, rt):
+        self.spec, self.rt = spec, rt
+        self.router = Linear(rt, spec.experts, spec.hidden)
+        self.gate_up = [Linear(rt, 2 * spec.intermediate, spec.hidden) for _ in range(spec.experts)]
+        self.down = [Linear(rt, spec.hidden, spec.intermediate) for _ in range(spec.experts)]
+
+    @classmethod
+    def parameters(cls, spec):
+        decl = {"router": ParamDecl(shape=(spec.experts, spec.hidden))}
+        for e in range(spec.experts):
+            decl[f"gate_up_{e}"] = ParamDecl(shape=(2 * spec.intermediate, spec.hidden))
+            decl[f"down_{e}"] = ParamDecl(shape=(spec.hidden, spec.intermediate))
+        return decl
+
+    def load(self, params):
+        self.router.load(params["router"])
+        for e in range(self.spec.experts):
+            self.gate_up[e].load(params[f"gate_up_{e}"])
+            self.down[e].load(params[f"down_{e}"])
+
+    def __call__(self, x, batch=None):
+        logits = self.router(x, out_dtype=torch.float32) if self.rt.full_precision else self.router(x).float()   # router logits in 32-bit
+        weight, choice = torch.softmax(logits, dim=-1).max(dim=-1)
+        out = torch.zeros_like(x, dtype=torch.float32)
+        I = self.spec.intermediate
+        for e in range(self.spec.experts):
+            rows = (choice == e).nonzero().flatten()
+            if rows.numel():
+                gu = self.gate_up[e](x[rows].contiguous()).float()
+                act = (gu[:, :I] / (1 + torch.exp(-gu[:, :I])) * gu[:, I:]).to(x.dtype)
+                out[rows] = self.down[e](act).float() * weight[rows, None]
+        return out.to(x.dtype)
+
+
+@dataclass(frozen=True)
+class ToyScaledRopeSpec:
+    """NeoX rotation over part of the head with every frequency divided by a factor (positions stretched)."""
+    kind: str = "toy_scaled_rope"
+    rotary_dim: int = 0
+    theta: float = 10000.0
+    factor: float = 1.0
+    max_positions: int = 0
+
+
+class ToyScaledRope:
+    def __init__(self, spec, rt):
+        self.spec = spec
+        self.max_positions = spec.max_positions
+        i = torch.arange(spec.rotary_dim // 2, dtype=torch.float64)
+        self.inv_freq = (torch.pow(torch.tensor(float(spec.theta), dtype=torch.float64), -2.0 * i / spec.rotary_dim) / spec.factor).to(rt.device)
+
+    def rotation(self):
+        return self.inv_freq, self.spec.rotary_dim
+
+
+def test_a_toy_routed_feed_forward_and_a_toy_position_encoding_are_registered_built_and_stepped(backend):
+    """Generality of the parts: a feed-forward with routing and another position encoding, both defined here, go into a
+    model beside the package's own parts without a change to the package, and every way of stepping agrees with a
+    plain whole-sequence computation."""
+    from roost_b200.parts import register_feed_forward, register_position
+    register_feed_forward("toy_top1_experts", ToyTop1Experts)
+    register_position("toy_scaled_rope", ToyScaledRope)
+    rt = runtime(backend)
+    H_, V, I, E = 48, 61, 32, 3
+    norm = NormSpec(size=H_, eps=1e-5)
+    attn = AttentionSpec(hidden=H_, num_heads=3, num_kv_heads=1, head_dim=16, scale=0.25, qk_norm=NormSpec(size=16, eps=1e-5),
+                         position=ToyScaledRopeSpec(rotary_dim=8, theta=50.0, factor=4.0))
+    blocks = (BlockSpec(mixer=attn, feed_forward=ToyRoutedSpec(hidden=H_, intermediate=I, experts=E), input_norm=norm, post_mixer_norm=norm),
+              BlockSpec(mixer=attn, feed_forward=GatedMlpSpec(hidden=H_, intermediate=I), input_norm=norm, post_mixer_norm=norm))
+    spec = ModelSpec(architecture="ToyRoutedForTests", hidden=H_, vocab=V, blocks=blocks, schedule=(RunEntry(0), RunEntry(1)),
+                     final_norm=norm, tie_embeddings=True, max_positions=0)
+    model = Model(spec, rt)
+    g = torch.Generator().manual_seed(5)
+    params = {}
+    for scope, decl in parameter_declarations(spec).items():
+        params[scope] = {k: (torch.ones(d.shape) + 0.1 * torch.randn(d.shape, generator=g) if d.role == "vector"
+                             else torch.randn(d.shape, generator=g) * 0.25).to(rt.dtype) for k, d in decl.items()}
+    # well separated router logits: a rounding difference must not send a token to another expert
+    params["blocks.0.feed_forward"]["router"] = (torch.randn(E, H_, generator=g) * 2.0).to(rt.dtype)
+    model.load(params)
+    ex = StepExecutor(model, page_size=4, num_pages=48, max_requests=3)
+
+    def rope(x, pos):   # the toy encoding, plainly: the first 8 elements of a head, frequencies divided by 4
+        half = 4
+        freq = torch.pow(torch.tensor(50.0, dtype=torch.float64), -2.0 * torch.arange(half, dtype=torch.float64) / 8) / 4.0
+        ang = torch.tensor(pos, dtype=torch.float64)[:, None] * freq[None, :]
+        c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+        out = x.clone()
+        out[..., :half] = x[..., :half] * c - x[..., half:8] * s
+        out[..., half:8] = x[..., half:8] * c + x[..., :half] * s
+        return out
+
+    def plain_forward(ids):
+        P = {s: {k: v.double() for k, v in p.items()} for s, p in params.items()}
+        h = P["embed"]["table"][torch.tensor(ids)]
+        pos = list(range(len(ids)))
+        margins = []
+        for bi in (0, 1):
+            x = plain.rms_norm(h, P[f"blocks.{bi}.input_norm"]["weight"], 1e-5)
+            m = P[f"blocks.{bi}.mixer"]
+            qkv = m["qkv"]
+            q = rope(plain.rms_norm((x @ qkv[:48].T).reshape(-1, 3, 16), m["q_norm"], 1e-5), pos)
+            k = rope(plain.rms_norm((x @ qkv[48:64].T).reshape(-1, 1, 16), m["k_norm"], 1e-5), pos)
+            v = (x @ qkv[64:].T).reshape(-1, 1, 16)
+            h = h + plain.causal_gqa_attention(q, k, v, 0.25).reshape(-1, 48) @ m["out"].T
+            y = plain.rms_norm(h, P[f"blocks.{bi}.post_mixer_norm"]["weight"], 1e-5)
+            f = P[f"blocks.{bi}.feed_forward"]
+            if bi == 0:
+                probs = torch.softmax(y @ f["router"].T, dim=-1)
+                weight, choice = probs.max(dim=-1)
+                top2 = probs.topk(2, dim=-1).values
+                margins.append(float((top2[:, 0] - top2[:, 1]).min()))
+                ff = torch.zeros_like(y)
+                for t in range(y.shape[0]):
+                    e = int(choice[t])
+                    ff[t] = plain.swiglu_mlp(y[t : t + 1], f[f"gate_up_{e}"][:I], f[f"gate_up_{e}"][I:], f[f"down_{e}"])[0] * weight[t]
+                h = h + ff
+            else:
+                h = h + plain.swiglu_mlp(y, f["gate_up"][:I], f["gate_up"][I:], f["down"])
+        return plain.rms_norm(h, P["final_norm"]["weight"], 1e-5) @ P["embed"]["table"].T, min(margins)
+
+    a, b = H.random_ids(21, V, 11), H.random_ids(14, V, 12)
+    want_a, margin_a = plain_forward(a)
+    want_b, margin_b = plain_forward(b)
+    assert min(margin_a, margin_b) > 0.02, "the test's router must separate its experts clearly"
+    bound = 2e-5 if rt.full_precision else H.BF16_BOUND
+    got = H.run_mixed(ex, {"a": a, "b": b}, seed=4, max_live=2, decode_tail=3)
+    assert H.scaled_error(got["a"], want_a) < bound
+    assert H.scaled_error(got["b"], want_b) < bound
+    got = H.run_portions(ex, "c", a, [5, 2, 14])
+    assert H.scaled_error(got, want_a) < bound
+    assert not ex.use_graphs and ex.graph_replays == 0
