@@ -57,6 +57,92 @@ __global__ void qk_norm_rope_cache_kernel(const T* __restrict__ qkv, int64_t qkv
     __syncthreads();
   }
 
+  // Many tokens of bfloat16 with every element rotated and a head of 64, 128 or 256: a lane owns eight neighbouring
+  // elements (one 16-byte access) of a head slot, so a warp serves 32 / (head_dim / 8) slots at a time; the lane that
+  // holds the other element of each of its pairs is head_dim / 16 lanes away, and the sum of squares is reduced over
+  // the slot's lanes only. A fifth of the instructions of the element-by-element form below.
+  if constexpr (TABLE && sizeof(T) == 2) {
+    if (vector_ok && rotary_dim == head_dim && (head_dim == 64 || head_dim == 128 || head_dim == 256)) {
+      const int lanes_per_slot = head_dim / 8, slots_per_pass = 32 / lanes_per_slot;
+      const int sub = lane / lanes_per_slot, c = lane % lanes_per_slot;  // which slot of the pass, which chunk of its head
+      const int pair_lanes = lanes_per_slot / 2;                        // the lane that holds the pairs' other elements: lane ^ pair_lanes
+      const bool second = c >= pair_lanes;                              // this lane's elements are the x2 of their pairs
+      const int i0 = (c % pair_lanes) * 8;                              // first pair index of the lane
+      float wq[8], wk[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        wq[e] = q_w ? load_w(q_w, c * 8 + e, wdtype) : 1.0f;
+        wk[e] = k_w ? load_w(k_w, c * 8 + e, wdtype) : 1.0f;
+      }
+      float cs[8], sn[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float2 r = cos_sin[i0 + e];
+        cs[e] = r.x;
+        sn[e] = second ? r.y : -r.y;  // x1' = x1 c - x2 s; x2' = x2 c + x1 s: own * c + other * (-+s)
+      }
+      const int slot = slot_mapping ? slot_mapping[t] : -1;
+      const int64_t page = slot >= 0 ? slot / page_size : 0;
+      const int off = slot >= 0 ? slot % page_size : 0;
+      const bool cache_ok = slot >= 0 && page < pool_pages;
+      const int first_warp_slot = (blockIdx.y * warps + (threadIdx.x >> 5)) * slots_per_pass;
+      const int pass_stride = gridDim.y * warps * slots_per_pass;
+      float x_next[8];
+      auto fetch = [&](int base) {  // the lane's eight elements of the pass that starts at slot `base`
+        if (base + sub < slots_per_token) {
+          Vec<T>::load(row + (size_t)(base + sub) * head_dim + c * 8, x_next);
+        } else {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) x_next[e] = 0.f;
+        }
+      };
+      fetch(first_warp_slot);
+      for (int base = first_warp_slot; base < slots_per_token; base += pass_stride) {
+        const int slot_idx = base + sub;
+        const bool live = slot_idx < slots_per_token;
+        int kind = 0, head = 0;
+        if (live) {
+          if (slot_idx < q_heads) {
+            kind = 0; head = slot_idx;
+          } else if (slot_idx < q_heads + kv_heads) {
+            kind = 1; head = slot_idx - q_heads;
+          } else {
+            kind = 2; head = slot_idx - q_heads - kv_heads;
+          }
+        }
+        float x[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) x[e] = x_next[e];
+        fetch(base + pass_stride);  // the next pass's elements travel while this pass is computed
+        float ss = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ss += x[e] * x[e];
+        for (int o = lanes_per_slot / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        const void* w = kind == 0 ? q_w : k_w;
+        const float inv = (kind != 2 && w != nullptr) ? 1.0f / sqrtf(ss / (float)head_dim + eps) : 1.0f;
+        float y[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) y[e] = kind == 2 ? x[e] : x[e] * inv * (kind == 0 ? wq[e] : wk[e]);
+        float out[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const float other = __shfl_xor_sync(0xffffffffu, y[e], pair_lanes);
+          out[e] = kind == 2 ? y[e] : y[e] * cs[e] + other * sn[e];
+        }
+        if (!live) continue;
+        T* dst;
+        if (kind == 0) {
+          dst = q_out + (t * q_heads + head) * head_dim;
+        } else {
+          if (!cache_ok) continue;  // a skipped token, or a slot beyond the pool: never written
+          dst = (kind == 1 ? k_pool : v_pool) + ((page * kv_heads + head) * page_size + off) * head_dim;
+        }
+        Vec<T>::store(dst + c * 8, out);
+      }
+      return;
+    }
+  }
+
   for (int slot_idx = blockIdx.y * warps + (threadIdx.x >> 5); slot_idx < slots_per_token; slot_idx += gridDim.y * warps) {
     int kind, head;  // 0 q, 1 k, 2 v
     if (slot_idx < q_heads) {
