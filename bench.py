@@ -1,6 +1,8 @@
 """Decode and prefill throughput of the engine at Qwen3-8B layer sizes with random weights on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--context 4096] [--layers L] [--impl reference]
+    python bench.py --sizes 0.6b|8b|32b          the same line at another model's layer sizes
+    python bench.py --workload serving --sizes 0.6b [--requests 32] [--budget 512] [--new-tokens 256] [--max-prompt 2048]
 
 Prints ONE JSON line. ``value`` is decoded tokens per second over K timed decode steps of ``--batch`` requests
 that each hold ``--context`` tokens, timed on the device with CUDA events; ``e2e`` is the same through the
@@ -10,6 +12,9 @@ the live requests' cache) over its time against the measured copy bandwidth; ``p
 64. Weights are seeded random values, token ids seeded uniform-random, and the contexts of the device-timed
 decode runs are filled with random keys and values instead of being prefilled (their values do not change the
 work of a decode step); the e2e run prefills its contexts for real through the engine.
+
+``--workload serving`` prints another line instead: concurrent requests whose prompts are cut into portions under a
+token budget and mixed with the decoding of the others, by wall clock through the Python entry point.
 """
 from __future__ import annotations
 
@@ -29,6 +34,12 @@ QWEN3_8B = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidd
                 num_attention_heads=32, num_key_value_heads=8, head_dim=128, intermediate_size=12288, vocab_size=151936,
                 rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=40960,
                 torch_dtype="bfloat16")
+# layer sizes of the other two models the baseline names; every key a config.json of the architecture has
+QWEN3_0_6B = dict(QWEN3_8B, num_hidden_layers=28, hidden_size=1024, num_attention_heads=16, num_key_value_heads=8, head_dim=128,
+                  intermediate_size=3072, tie_word_embeddings=True)
+QWEN3_32B = dict(QWEN3_8B, num_hidden_layers=64, hidden_size=5120, num_attention_heads=64, num_key_value_heads=8, head_dim=128,
+                 intermediate_size=25600)
+SIZES = {"0.6b": QWEN3_0_6B, "8b": QWEN3_8B, "32b": QWEN3_32B}
 PAGE = 16
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
@@ -78,7 +89,7 @@ class ClockSampler:
                 "reasons": reasons, "samples": len(self.samples)}
 
 
-def build_model(layers: int, dtype, seed: int = 0):
+def build_model(layers: int, dtype, seed: int = 0, sizes: dict = QWEN3_8B):
     import torch
 
     from roost_b200.config.qwen3 import Qwen3Config
@@ -86,8 +97,8 @@ def build_model(layers: int, dtype, seed: int = 0):
     from roost_b200.kernels import library
     from roost_b200.parts import Runtime
     from roost_b200.weights.random_init import random_parameters
-    cfg = dict(QWEN3_8B, num_hidden_layers=layers)
-    spec = Qwen3Config.from_dict(cfg).to_spec(False)
+    cfg = dict(sizes, num_hidden_layers=layers)
+    spec = Qwen3Config.from_dict(cfg).to_spec(bool(cfg["tie_word_embeddings"]))
     model = Model(spec, Runtime(dtype, "cuda", library.load()))
     model.load(random_parameters(spec, seed, torch.device("cuda"), dtype, std=0.02))
     return model, cfg
@@ -231,6 +242,83 @@ def timed_e2e(model, batch: int, context: int, steps: int, warmup: int):
     return produced / dt, h2d // steps, d2h // steps
 
 
+def timed_serving(model, requests: int, budget: int, new_tokens: int, max_prompt: int, seed: int = 17) -> dict:
+    """The serving workload: ``requests`` concurrent requests with prompt lengths uniform in [16, max_prompt], prompts
+    cut into portions under a ``budget`` of tokens a step and mixed with the decoding of the others, ``new_tokens``
+    greedy tokens each, through the Python entry point (host token ids in, sampled ids out, every step). Wall clock
+    from the first step to the last, after one untimed pass of the same requests through the same engine (a server
+    that has been up for a while: its allocator is warm and its decode steps are captured)."""
+    import torch
+
+    from roost_b200 import GenerationOptions, RoostEngine
+    gen = torch.Generator().manual_seed(seed)
+    lengths = torch.randint(16, max_prompt + 1, (requests,), generator=gen).tolist()
+    prompts = [torch.randint(0, model.spec.vocab, (n,), generator=gen).tolist() for n in lengths]
+    pages = sum(-(-(n + new_tokens + 1) // PAGE) for n in lengths) + 8
+    opts = GenerationOptions(max_output_tokens=new_tokens, ignore_eos=True).sampling()
+    out = {}
+    engine = RoostEngine(model, page_size=PAGE, attention_blocks=pages, max_sequences=requests, max_tokens=budget)
+    for timed in (False, True):
+        replays0 = engine.executor.prepared_replays
+        steps0 = engine.steps
+        for p in prompts:
+            engine.add_request(p, opts)
+        kinds = {"mixed": [0, 0.0, 0], "decode": [0, 0.0, 0]}     # steps, seconds, tokens run
+        produced = 0
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        while engine.has_unfinished():
+            t1 = time.perf_counter()
+            events = engine.step()
+            plan = engine.last_plan
+            if plan is None or not plan.rows:
+                continue
+            kind = kinds["decode" if all(r.count == 1 for r in plan.rows) else "mixed"]
+            kind[0] += 1
+            kind[1] += time.perf_counter() - t1
+            kind[2] += plan.num_tokens
+            produced += sum(1 for e in events if e.token is not None)
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        stats = engine.stats()
+        stats["steps"] -= steps0
+        replays = engine.executor.prepared_replays - replays0
+        if timed:
+            out = {"seconds": round(dt, 3), "output_tokens": produced, "prompt_tokens": sum(lengths),
+                   "output_tokens_per_s": round(produced / dt, 1), "total_tokens_per_s": round((produced + sum(lengths)) / dt, 1),
+                   "steps": stats["steps"], "preemptions": stats["preemptions"], "prepared_replays": replays,
+                   "mixed_steps": kinds["mixed"][0], "mixed_ms_per_step": round(kinds["mixed"][1] / max(kinds["mixed"][0], 1) * 1e3, 3),
+                   "mixed_tokens_per_step": round(kinds["mixed"][2] / max(kinds["mixed"][0], 1), 1),
+                   "decode_steps": kinds["decode"][0], "decode_ms_per_step": round(kinds["decode"][1] / max(kinds["decode"][0], 1) * 1e3, 3),
+                   "decode_rows_per_step": round(kinds["decode"][2] / max(kinds["decode"][0], 1), 1),
+                   "captured_steps": len(engine.executor._graphs)}
+    engine.executor.close()
+    del engine
+    gc.collect()
+    torch.cuda.empty_cache()
+    return out
+
+
+def serving_main(args) -> int:
+    import torch
+    sizes = SIZES[args.sizes]
+    layers = args.layers if args.layers else sizes["num_hidden_layers"]
+    model, cfg = build_model(layers, torch.bfloat16, sizes=sizes)
+    with ClockSampler() as clocks:
+        r = timed_serving(model, args.requests, args.budget, args.new_tokens, args.max_prompt)
+    line = {"metric": f"serving output tokens/s ({args.requests} concurrent requests, prompts 16..{args.max_prompt}, {args.budget}-token step budget, "
+                      f"{args.new_tokens} new tokens each), Qwen3-{args.sizes.upper()} layer sizes",
+            "value": r["output_tokens_per_s"], "unit": "tokens/s", "n_gpus": 1, "higher_is_better": True, "dtype": "bf16", "impl": "ours",
+            "data": "synthetic: seeded random weights N(0, 0.02), seeded uniform-random prompts, greedy decoding, wall clock through RoostEngine.step",
+            "config": {"model": f"qwen3-{args.sizes}-shapes", "layers": layers, "layers_of_config": sizes["num_hidden_layers"],
+                       "hidden": cfg["hidden_size"], "q_heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
+                       "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"], "page_size": PAGE,
+                       "requests": args.requests, "budget": args.budget, "new_tokens": args.new_tokens, "max_prompt": args.max_prompt},
+            "serving": r, "clocks": clocks.summary()}
+    print(json.dumps(line))
+    return 0
+
+
 def reference_arm() -> int:
     print(json.dumps({"impl": "reference", "unavailable": "starlinghq/roost is a C#/.NET 10 program with no Python package "
                       "(pip install of /root/reference finds no setup.py or pyproject.toml) and no .NET SDK or runtime is on this image"}))
@@ -244,7 +332,14 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=4096)
-    ap.add_argument("--layers", type=int, default=QWEN3_8B["num_hidden_layers"])
+    ap.add_argument("--layers", type=int, default=0, help="layers built (default: all the layers of --sizes)")
+    ap.add_argument("--sizes", default="8b", choices=sorted(SIZES), help="whose layer sizes: Qwen3-0.6B, -8B (the headline) or -32B")
+    ap.add_argument("--workload", default="decode", choices=["decode", "serving"],
+                    help="decode: the headline line; serving: concurrent requests with chunked prefill mixed with decoding")
+    ap.add_argument("--requests", type=int, default=32)
+    ap.add_argument("--budget", type=int, default=512)
+    ap.add_argument("--new-tokens", type=int, default=256)
+    ap.add_argument("--max-prompt", type=int, default=2048)
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true")
@@ -256,10 +351,14 @@ def main() -> int:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not served")
         return 2
     warmup = max(args.warmup, 3)
+    if args.workload == "serving":
+        return serving_main(args)
 
     import torch
     pk, pk_kind = peaks()
-    model, cfg = build_model(args.layers, torch.bfloat16)
+    sizes = SIZES[args.sizes]
+    args.layers = args.layers or sizes["num_hidden_layers"]
+    model, cfg = build_model(args.layers, torch.bfloat16, sizes=sizes)
     tps, ms, launches, clocks = timed_decode(model, args.batch, args.context, args.steps, warmup)
     decode_bytes = matrix_bytes(cfg) + args.batch * args.context * kv_bytes_per_token(cfg)
     achieved = decode_bytes / (ms / 1e3) / 1e9
@@ -274,12 +373,12 @@ def main() -> int:
         v, bi, bo = timed_e2e(model, args.batch, args.context, args.steps, warmup)
         e2e = {"value": round(v, 1), "unit": "tokens/s", "h2d_bytes_per_step": bi, "d2h_bytes_per_step": bo}
     line = {
-        "metric": "decode tokens/s (batch 8, context 4096), Qwen3-8B layer sizes", "value": round(tps, 1), "unit": "tokens/s",
+        "metric": f"decode tokens/s (batch {args.batch}, context {args.context}), Qwen3-{args.sizes.upper()} layer sizes", "value": round(tps, 1), "unit": "tokens/s",
         "n_gpus": 1, "steps": args.steps, "warmup": warmup, "ms_per_step": round(ms, 4), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "impl": "ours",
         "data": "synthetic: seeded random weights N(0, 0.02), seeded uniform-random token ids, device-timed decode contexts filled with random keys/values",
-        "config": {"model": "qwen3-8b-shapes", "global_batch": args.batch, "seq_len": args.context, "parallelism": "single-gpu",
-                   "layers": args.layers, "layers_of_config": QWEN3_8B["num_hidden_layers"], "hidden": cfg["hidden_size"],
+        "config": {"model": f"qwen3-{args.sizes}-shapes", "global_batch": args.batch, "seq_len": args.context, "parallelism": "single-gpu",
+                   "layers": args.layers, "layers_of_config": sizes["num_hidden_layers"], "hidden": cfg["hidden_size"],
                    "q_heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
                    "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"], "page_size": PAGE,
                    "l2": "inputs larger than L2: each step streams all weights (>10 GB) from HBM", "peaks": pk_kind},

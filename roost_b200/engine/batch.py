@@ -19,6 +19,29 @@ import torch
 from ..cache.block_pool import NULL_PAGE
 
 
+def pad_row(tokens: int) -> tuple:
+    """A row that only fills a captured step up to the rows and tokens it was captured for: ``tokens`` tokens (id 0,
+    possibly none) at position -1 of no request. It holds no keys (kv_len 0, an empty page range), writes no key or
+    value (slot -1, which the cache write skips), gets no attention work and wants no logits. A token's values never
+    mix with another row's, so whatever a padding row carries stays in it."""
+    return (None, -1, [0] * tokens, [])
+
+
+def padded_rows(rows: list, tokens_cap: int, rows_cap: int) -> list:
+    """``rows`` followed by padding rows, up to ``rows_cap`` rows and ``tokens_cap`` tokens: the padding tokens go
+    one to a padding row, what is left over to the first of them."""
+    pad_rows = rows_cap - len(rows)
+    pad_tokens = tokens_cap - sum(len(r[2]) for r in rows)
+    if pad_rows < 0 or pad_tokens < 0 or (pad_tokens and not pad_rows):
+        raise ValueError(f"{len(rows)} rows do not fit a step of {rows_cap} rows and {tokens_cap} tokens")
+    out = list(rows)
+    for i in range(pad_rows):
+        n = min(1, pad_tokens) if i else pad_tokens - min(pad_tokens, pad_rows - 1)
+        out.append(pad_row(n))
+        pad_tokens -= n
+    return out
+
+
 @dataclass
 class GroupTables:
     """Per cache group. Paged: ``slot_mapping[t]`` = page * page_size + offset for token t, ``kv_indices``
@@ -58,6 +81,8 @@ def attention_work(row_starts, row_counts, group: int, window: int | None, chunk
     for b, (start, n) in enumerate(zip(row_starts, row_counts)):
         rows, kv_len = n * group, start + n
         first_token, token = token, token + n
+        if start < 0:
+            continue   # a padding row (see PAD_ROW): no keys, no work
         if rows <= 16:
             lo = max(0, start - window + 1) if window else 0
             first = (lo // chunk) * chunk
@@ -78,11 +103,15 @@ def attention_work(row_starts, row_counts, group: int, window: int | None, chunk
     return prefill, decode, merge, slots
 
 
-def attention_caps(num_rows: int, kv_cap: int, group: int, chunk: int, tile_rows: int = 64) -> tuple[int, int, int]:
-    """Largest item counts of a decode step (one token a row) whose requests hold at most ``kv_cap`` keys."""
-    if group > 16:
-        return num_rows * (-(-group // tile_rows)), 0, 0
-    return 0, num_rows * (-(-kv_cap // chunk)), num_rows
+def attention_caps(num_tokens: int, num_rows: int, kv_cap: int, group: int, chunk: int, tile_rows: int = 64) -> tuple[int, int, int]:
+    """Largest (prefill, decode, merge) item counts of a step of ``num_tokens`` tokens in ``num_rows`` rows whose
+    requests hold at most ``kv_cap`` keys. A step of one token a row has work of one kind only."""
+    chunks = -(-kv_cap // chunk)
+    if num_tokens == num_rows:
+        if group > 16:
+            return num_rows * (-(-group // tile_rows)), 0, 0
+        return 0, num_rows * chunks, num_rows
+    return -(-num_tokens * group // tile_rows) + num_rows, num_rows * chunks, num_rows
 
 
 def _pad4(a: list) -> list:
@@ -224,10 +253,10 @@ class BatchBuilder:
         for b, (rc, start, tokens, want) in enumerate(rows):
             n = len(tokens)
             ids[at : at + n] = tokens
-            pos[at : at + n] = np.arange(start, start + n, dtype=np.int32)
+            pos[at : at + n] = np.arange(start, start + n, dtype=np.int32) if rc is not None else -1
             trow[at : at + n] = b
             q_indptr[b + 1] = at + n
-            kv_lens[b] = start + n
+            kv_lens[b] = start + n if rc is not None else 0
             selected.extend(at + w for w in want)
             at += n
         if T and (ids.min() < 0 or ids.max() >= vocab):
@@ -241,8 +270,13 @@ class BatchBuilder:
                 indices = []
                 at = 0
                 for b, (rc, start, tokens, _) in enumerate(rows):
-                    table = rc.tables[gi]
                     n = len(tokens)
+                    if rc is None:     # padding: nothing is written, no pages are read
+                        slot[at : at + n] = -1
+                        indptr[b + 1] = len(indices)
+                        at += n
+                        continue
+                    table = rc.tables[gi]
                     if n == 1:
                         page = table[start // g.page_size]
                         if page == NULL_PAGE:
@@ -260,9 +294,9 @@ class BatchBuilder:
                     at += n
                 arrays += [slot, indptr, np.asarray(indices, np.int32)]
             else:
-                arrays.append(np.asarray([rc.slots[gi] for rc, *_ in rows], np.int32))
+                arrays.append(np.asarray([rc.slots[gi] if rc is not None else 0 for rc, *_ in rows], np.int32))
         return HostTables(arrays=arrays, num_tokens=T, num_rows=B, num_selected=len(selected), row_starts=[r[1] for r in rows],
-                          row_counts=[len(r[2]) for r in rows], max_position=int(pos.max()) if T else 0,
+                          row_counts=[len(r[2]) for r in rows], max_position=max(int(pos.max()), 0) if T else 0,
                           max_kv_len=int(kv_lens.max()) if B else 0)
 
     def _batch(self, ht: HostTables, views: list, host_buffer) -> StepBatch:
@@ -282,7 +316,10 @@ class BatchBuilder:
                          all_single=all(n == 1 for n in ht.row_counts), host_buffer=host_buffer)
 
     def build(self, rows: list[tuple], vocab: int) -> StepBatch:
-        ht = self.host_tables(rows, vocab)
+        return self.place(self.host_tables(rows, vocab))
+
+    def place(self, ht: HostTables) -> StepBatch:
+        """The tables in a fresh pinned buffer, copied to the device in one transfer."""
         flat = ht.arrays
         offsets, total = [], 0
         for a in flat:  # 16-byte aligned sub-tables in one buffer
@@ -297,17 +334,21 @@ class BatchBuilder:
         return self._batch(ht, views, host)
 
     # ------------------------------------------------------------------ fixed placement for graph replay
-    def table_caps(self, num_rows: int, kv_cap: int) -> list[int]:
-        """Capacities, in placement order, of the tables of a decode step of ``num_rows`` rows whose requests hold at
-        most ``kv_cap`` tokens."""
-        B = num_rows
-        caps = [B, B, B, B + 1, B, B]
+    def table_caps(self, num_tokens: int, num_rows: int, kv_cap: int) -> list[int]:
+        """Capacities, in placement order, of the tables of a step of ``num_tokens`` tokens in ``num_rows`` rows whose
+        requests hold at most ``kv_cap`` tokens and which wants at most one row of logits a row."""
+        T, B = num_tokens, num_rows
+        caps = [T, T, T, B + 1, B, B]
         for g in self.cm.groups:
             if g.kind == "paged":
-                caps += [B, B + 1, B * (-(-kv_cap // g.page_size))]
+                caps += [T, B + 1, B * (-(-kv_cap // g.page_size))]
             else:
                 caps.append(B)
         return caps
 
     def static_batch(self, ht: HostTables, static: StaticTables, n_table_sections: int) -> StepBatch:
-        return self._batch(ht, static.views[:n_table_sections], None)
+        """A batch over the fixed tables, with the counts of the step they were made for (``ht`` filled up with padding
+        rows): every table at its capacity, as many logits as rows."""
+        full = HostTables(arrays=ht.arrays, num_tokens=ht.num_tokens, num_rows=ht.num_rows, num_selected=ht.num_rows,
+                          row_starts=ht.row_starts, row_counts=ht.row_counts, max_position=ht.max_position, max_kv_len=ht.max_kv_len)
+        return self._batch(full, static.views[:n_table_sections], None)

@@ -19,11 +19,46 @@ import numpy as np
 
 from ..cache.manager import CacheManager, OutOfPages, build_groups
 from ..cache.storage import CacheStorage
-from .batch import AttentionPlan, BatchBuilder, HostTables, StaticTables, attention_caps, attention_work
+from .batch import AttentionPlan, BatchBuilder, HostTables, StaticTables, attention_caps, attention_work, padded_rows
 from .model import Model
 
-GRAPH_KV_GRANULE = 1024   # a captured decode step serves requests of up to a multiple of this many tokens
-MAX_GRAPHS = 24
+MAX_GRAPHS = 64
+GRAPH_TOKENS = 1024   # a step of more tokens runs eagerly: the device bounds it, not the host's launches
+
+
+def graph_tokens(n: int) -> int:
+    """Tokens of the captured step that serves a step of ``n`` tokens of which some row brings more than one: 8, 16, 32,
+    then the next multiple of 64 up to 512 and of 128 beyond. A scheduler that fills a token budget asks for the
+    budget's own size step after step."""
+    for m in (8, 16, 32):
+        if n <= m:
+            return m
+    granule = 64 if n <= 512 else 128
+    return -(-n // granule) * granule
+
+
+def graph_rows(n: int) -> int:
+    """Rows of the captured decode step that serves ``n`` rows: up to 8 exactly, then 12, 16, 24, 32, 48, 64 and so on
+    (at most half as many again), filled up with padding rows. A server's batch shrinks and grows by one request at a
+    time; without the steps every size would be captured for itself."""
+    if n <= 8:
+        return n
+    b = 8
+    while True:
+        for m in (b * 3 // 2, b * 2):
+            if n <= m:
+                return m
+        b *= 2
+
+
+def graph_kv_cap(kv_len: int) -> int:
+    """The bound on the requests' lengths a captured decode step is made for: the next multiple of 1024 up to 8192
+    tokens, of 4096 up to 32768, of 16384 beyond. It sizes the step's page tables and attention work lists, whose unused
+    entries cost an upload of a few bytes each and nothing on the device."""
+    for limit, granule in ((8192, 1024), (32768, 4096)):
+        if kv_len <= limit:
+            return max(granule, -(-kv_len // granule) * granule)
+    return -(-kv_len // 16384) * 16384
 
 
 @dataclass
@@ -48,22 +83,23 @@ class PreparedDecode:
     staged: int       # the pinned buffer of the graph's tables that holds this step's tables; section 0 is the token ids
 
 
-class DecodeGraph:
-    """A captured CUDA graph of one decode step (every row brings one token and wants its logits) for a fixed number
-    of rows and a bound on the requests' lengths. The step's tables live at fixed device addresses; a replay uploads
-    the new tables and launches the whole forward pass with one call, so the host's per-kernel launch cost (hundreds
-    of launches a step) no longer bounds small batches. The reference's one graph experiment did not replay
-    bit-identically and is unclaimed (kernels/README.md:240-250); here a replay runs the very kernels of the eager
-    path with the same arguments, and the tests compare both with the plain implementation."""
+class StepGraph:
+    """A captured CUDA graph of one step for a fixed number of tokens and rows and a bound on the requests' lengths.
+    The step's tables live at fixed device addresses; a replay uploads the new tables and launches the whole forward
+    pass with one call, so the host's per-kernel launch cost (hundreds of launches a step) no longer bounds small
+    batches and small models. A step with fewer rows or tokens is filled up with padding rows (``batch.pad_row``), its
+    work lists with items the kernels skip. The reference's one graph experiment did not replay bit-identically and is
+    unclaimed (kernels/README.md:240-250); here a replay runs the very kernels of the eager path with the same
+    arguments, and the tests compare both with the plain implementation."""
 
-    def __init__(self, executor: "StepExecutor", num_rows: int, kv_cap: int, plan_keys: list):
+    def __init__(self, executor: "StepExecutor", num_tokens: int, num_rows: int, kv_cap: int, plan_keys: list):
         self.ex = weakref.proxy(executor)   # the executor owns its graphs; no reference cycle keeps its cache alive
-        self.num_rows, self.kv_cap = num_rows, kv_cap
+        self.num_tokens, self.num_rows, self.kv_cap = num_tokens, num_rows, kv_cap
         self.plan_keys = list(plan_keys)
         builder = executor.builder
-        table_caps = builder.table_caps(num_rows, kv_cap)
+        table_caps = builder.table_caps(num_tokens, num_rows, kv_cap)
         self.n_table = len(table_caps)
-        self.plan_caps = [attention_caps(num_rows, kv_cap, g, chunk, rows) for (g, _w, chunk, rows) in self.plan_keys]
+        self.plan_caps = [attention_caps(num_tokens, num_rows, kv_cap, g, chunk, rows) for (g, _w, chunk, rows) in self.plan_keys]
         caps, fills = list(table_caps), [0] * len(table_caps)
         for pc, dc, mc in self.plan_caps:
             caps += [pc * 2, dc * 4, mc * 4]
@@ -84,46 +120,43 @@ class DecodeGraph:
         self._pending = self._arrays(ht)
         return self.static.fits(self._pending)
 
-    def run(self, ht: HostTables) -> torch.Tensor:
-        """Call after ``fits(ht)`` returned True."""
+    def run(self, live: int) -> torch.Tensor:
+        """A replay with the tables of the last ``fits`` that returned True. ``live``: the rows of logits that are wanted."""
         self.static.upload(self._pending, self.fills)
-        if self.graph is None:
-            return self._capture(ht)
         self.graph.replay()
         self.ex.rt.kernels.launches += self.launches
-        return self.out.clone()
+        return self.out[:live].clone()
 
-    def run_staged(self, staged: int) -> torch.Tensor:
-        """A replay with tables staged earlier (the graph is captured already)."""
+    def run_staged(self, staged: int, live: int) -> torch.Tensor:
+        """A replay with tables staged earlier."""
         self.static.send(staged)
         self.graph.replay()
         self.ex.rt.kernels.launches += self.launches
-        return self.out.clone()
+        return self.out[:live].clone()
 
-    def _capture(self, ht: HostTables) -> torch.Tensor:
+    def capture(self, ht: HostTables) -> None:
+        """Records the step over the fixed tables (after ``fits(ht)`` returned True). Nothing runs: the step's own result
+        comes from the eager run before it, which also told which attention plans the model's mixers ask for."""
         ex = self.ex
+        self.static.upload(self._pending, self.fills)
         batch = ex.builder.static_batch(ht, self.static, self.n_table)
         views = self.static.views[self.n_table:]
         for i, (key, (pc, dc, mc)) in enumerate(zip(self.plan_keys, self.plan_caps)):
             batch.attention_plans[key] = AttentionPlan(prefill_items=pc, prefill_tile_rows=key[3], decode_items=dc, merge_items=mc, slots=dc,
-                                                       merge_rows=min(16, key[0]),   # one token a row: its query heads per key/value head
+                                                       merge_rows=min(16, key[0]) if self.num_tokens == self.num_rows else 16,
                                                        prefill_work=views[3 * i], decode_work=views[3 * i + 1],
                                                        merge_work=views[3 * i + 2])
-        # this step's result comes from an eager run on a side stream (which also warms every kernel and library up);
-        # the capture that follows records the same launches without running them
-        side = torch.cuda.Stream()
-        side.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(side):
-            result = ex.model.forward(batch, ex.storage).clone()
-        torch.cuda.current_stream().wait_stream(side)
         graph = torch.cuda.CUDAGraph()
         before = ex.rt.kernels.launches
-        with torch.cuda.graph(graph):
+        # one memory pool for all of an executor's graphs: they never run at the same time, so what one capture used
+        # and freed serves the next
+        with torch.cuda.graph(graph, pool=ex.graph_pool()):
             out = ex.model.forward(batch, ex.storage)
         self.launches = ex.rt.kernels.launches - before   # kernels one replay launches
         ex.rt.kernels.launches = before
+        if sorted(batch.attention_plans, key=repr) != sorted(self.plan_keys, key=repr):
+            raise RuntimeError("the captured step asked for other attention plans than the eager step before it")
         self.graph, self.out, self.batch = graph, out, batch
-        return result
 
 
 class StepExecutor:
@@ -158,7 +191,8 @@ class StepExecutor:
                            and all(g.kind == "paged" or not g.runs for g in self.groups)
                            and all(getattr(p, "capturable", True) for p in model.parts()))
         self._graphs: dict = {}
-        self._plan_keys: list | None = None
+        self._graph_pool = None
+        self._seen: dict = {}        # sizes of steps of several tokens a row that ran eagerly, and how often
         self.graph_replays = 0
         self.prepared_replays = 0    # replays whose tables were made while the step before was still running
 
@@ -215,31 +249,66 @@ class StepExecutor:
             self.last_upload_bytes = batch.host_buffer.numel() * batch.host_buffer.element_size()
             self._zero_new_state(rows)
             logits = self.model.forward(batch, self.storage)
-            if self._plan_keys is None:
-                self._plan_keys = sorted(batch.attention_plans, key=repr)
         for (e, _, end) in plan:
             self.cache.commit(e.request_id, end)
         self.steps_run += 1
         return logits
 
     def _run_graph(self, rows):
-        """Logits of a decode step through a captured graph, or None when the step is not one (or cannot be captured yet:
-        the first steps of a model run eagerly and tell which attention plans its mixers ask for)."""
-        if self._plan_keys is None or not all(len(r[2]) == 1 and list(r[3]) == [0] for r in rows):
-            return None
-        ht = self.builder.host_tables(rows, self.model.spec.vocab)
-        kv_cap = -(-ht.max_kv_len // GRAPH_KV_GRANULE) * GRAPH_KV_GRANULE
-        key = (ht.num_rows, kv_cap)
-        g = self._graphs.get(key)
+        """Logits of the step through a captured graph, or None when it is to run eagerly: a step of many tokens, one
+        that wants more rows of logits than it has rows, or a step of several tokens a row whose sizes are seen for the
+        first time (a decode step is captured at once, any other when its sizes come again)."""
+        tokens, wanted = sum(len(r[2]) for r in rows), sum(len(r[3]) for r in rows)
+        decode = all(len(r[2]) == 1 and list(r[3]) == [0] for r in rows)
+        if decode:
+            tokens_cap = rows_cap = graph_rows(len(rows))
+        else:
+            if tokens > GRAPH_TOKENS:
+                return None
+            tokens_cap = graph_tokens(tokens)
+            rows_cap = graph_rows(len(rows) + (1 if tokens_cap > tokens else 0))
+            if wanted > rows_cap:
+                return None
+        ht = self.builder.host_tables(padded_rows(rows, tokens_cap, rows_cap), self.model.spec.vocab)
+        key = (tokens_cap, rows_cap, graph_kv_cap(ht.max_kv_len))
+        g = self._touch(key)
         if g is None:
-            if len(self._graphs) >= MAX_GRAPHS:
-                self._graphs.pop(next(iter(self._graphs)))
-            g = self._graphs[key] = DecodeGraph(self, ht.num_rows, kv_cap, self._plan_keys)
+            if not decode:
+                if len(self._seen) > 4096:
+                    self._seen.clear()
+                self._seen[key] = self._seen.get(key, 0) + 1
+                if self._seen[key] < 2:
+                    return None
+            # the eager run of the padded step gives this step's result and tells which attention plans the mixers ask
+            # for; the capture that follows records the same launches over fixed tables without running them
+            batch = self.builder.place(ht)
+            self.last_upload_bytes = batch.host_buffer.numel() * batch.host_buffer.element_size()
+            logits = self.model.forward(batch, self.storage)
+            g = StepGraph(self, tokens_cap, rows_cap, key[2], sorted(batch.attention_plans, key=repr))
+            if g.fits(ht):
+                g.capture(ht)
+                if len(self._graphs) >= MAX_GRAPHS:
+                    self._graphs.pop(next(iter(self._graphs)))
+                self._graphs[key] = g
+            return logits[:wanted]
         if not g.fits(ht):
             return None
         self.last_upload_bytes = g.static.total * 4
         self.graph_replays += 1
-        return g.run(ht)
+        return g.run(wanted)
+
+    def _touch(self, key):
+        """The captured step of this key, marked as the most recently used (the least recently used one goes when there
+        are too many)."""
+        g = self._graphs.pop(key, None)
+        if g is not None:
+            self._graphs[key] = g
+        return g
+
+    def graph_pool(self):
+        if self._graph_pool is None:
+            self._graph_pool = torch.cuda.graph_pool_handle()
+        return self._graph_pool
 
     # ------------------------------------------------------------------ a decode step prepared ahead of its tokens
     def prepare_decode(self, request_ids: list) -> PreparedDecode | None:
@@ -248,7 +317,7 @@ class StepExecutor:
         before, and hands it to ``run_prepared`` with the tokens once they are known; when the next step turns out to be
         another one, the preparation is simply dropped (the pages it took belong to their requests and go back with
         them). None when the step cannot be prepared: no captured graph serves it yet, or pages are short."""
-        if not self.use_graphs or self._plan_keys is None or not request_ids:
+        if not self.use_graphs or not request_ids:
             return None
         max_pos = self.model.spec.max_positions
         need = [0] * len(self.groups)
@@ -265,16 +334,16 @@ class StepExecutor:
         if any(n > self.cache.pools[gi].free_count for gi, n in enumerate(need)):
             return None
         rows = [(self.cache.extend(rid, start + 1), start, [0], [0]) for rid, start in zip(request_ids, starts)]
-        ht = self.builder.host_tables(rows, self.model.spec.vocab)
-        kv_cap = -(-ht.max_kv_len // GRAPH_KV_GRANULE) * GRAPH_KV_GRANULE
-        g = self._graphs.get((ht.num_rows, kv_cap))
-        if g is None or g.graph is None or not g.fits(ht):
+        cap = graph_rows(len(rows))
+        ht = self.builder.host_tables(padded_rows(rows, cap, cap), self.model.spec.vocab)
+        g = self._touch((cap, cap, graph_kv_cap(ht.max_kv_len)))
+        if g is None or not g.fits(ht):
             return None
         return PreparedDecode(list(request_ids), starts, g, g.static.stage(g._pending, g.fills))
 
     def matches_prepared(self, prep: PreparedDecode, entries: list[StepEntry]) -> bool:
-        return (len(entries) == len(prep.request_ids) and prep.graph.graph is not None
-                and self._graphs.get((prep.graph.num_rows, prep.graph.kv_cap)) is prep.graph
+        return (len(entries) == len(prep.request_ids)
+                and self._graphs.get((prep.graph.num_tokens, prep.graph.num_rows, prep.graph.kv_cap)) is prep.graph
                 and all(e.request_id == rid and len(e.tokens) == 1 and list(e.want) == [0] and (e.start is None or e.start == st)
                         and rid in self.cache and self.cache.get(rid).tokens == st
                         for e, rid, st in zip(entries, prep.request_ids, prep.starts)))
@@ -288,7 +357,7 @@ class StepExecutor:
             if not 0 <= t < vocab:
                 raise ValueError(f"token id {t} is outside the vocabulary of {vocab}")
             ids[i] = t
-        logits = prep.graph.run_staged(prep.staged)
+        logits = prep.graph.run_staged(prep.staged, len(entries))
         self.last_upload_bytes = prep.graph.static.total * 4
         self.graph_replays += 1
         self.prepared_replays += 1

@@ -176,3 +176,98 @@ def test_every_small_product_kernel_serves_the_engine(tiny_model_dirs, policy):
     ids = H.random_ids(60, t["config"]["vocab_size"], seed=44)
     check(H.run_tail_decoded(ex, "r", ids, tail=32), tiny_model_dirs[name], ids, torch.bfloat16, f"{name} decode with {policy} products")
     assert model.rt.kernels.gemm_tcgen05_status() == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+def test_a_captured_step_filled_up_with_padding_rows(tiny_model_dirs, dtype):
+    """Eleven, then nine decoding requests are served by the captured step of twelve rows. The logits are those of an
+    executor without graphs and of the plain implementation, and no byte of the cache outside the requests' own slots
+    changes (a padding row writes nothing)."""
+    from roost_b200.engine.executor import graph_rows
+    name, t = "B", TINY["B"]
+    V, P = t["config"]["vocab_size"], t["page_size"]
+    model = H.make_model(tiny_model_dirs[name], dtype, "gpu")
+    execs = [StepExecutor(model, page_size=P, num_pages=48, max_requests=16, use_graphs=g) for g in (True, False)]
+    for ex in execs:
+        for ten in ex.storage.tensors:
+            ten.fill_(7.0)
+    seqs = {f"r{i}": H.random_ids(3 + i, V, seed=300 + i) for i in range(11)}
+    logits = []
+    for ex in execs:
+        got = []
+        live = dict((k, list(v)) for k, v in seqs.items())
+        ex.step([StepEntry(r, ids, []) for r, ids in live.items()])
+        for step in range(10):
+            if step == 5:
+                for r in ("r2", "r7"):
+                    ex.finish(r)
+                    del live[r]
+            nxt = {r: H.random_ids(1, V, seed=900 + 31 * step + i)[0] for i, r in enumerate(live)}
+            got.append(ex.step([StepEntry(r, [tok], [0]) for r, tok in nxt.items()]))
+            for r, tok in nxt.items():
+                live[r].append(tok)
+        logits.append(got)
+        final = live
+    graphs, eager = execs
+    assert graph_rows(11) == graph_rows(9) == 12
+    assert graphs.graph_replays >= 8 and set(k[0] for k in graphs._graphs) == {12}
+    for a, b in zip(*logits):
+        assert a.shape == b.shape and a.shape[0] in (11, 9)
+        assert H.scaled_error(a, b) <= H.bound_for(dtype) / 4
+    for r, row in zip(final, logits[0][-1]):
+        want = H.plain_logits(tiny_model_dirs[name], final[r], dtype == torch.bfloat16)[-1]
+        assert H.scaled_error(row, want) <= H.bound_for(dtype), r
+    for a, b in zip(graphs.storage.tensors, eager.storage.tensors):
+        if a.numel() == 0:
+            continue   # the group of fixed-size state, which this architecture leaves empty
+        untouched = b == 7.0
+        assert untouched.any() and bool((a[untouched] == 7.0).all())
+        assert H.scaled_error(a, b) <= H.bound_for(dtype)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", ["B", "C"])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+def test_steps_of_prompt_portions_beside_decoded_tokens_replayed_from_captured_graphs(tiny_model_dirs, name, dtype):
+    """The same sizes of mixed steps come again and again (a scheduler that fills a token budget): from their second
+    coming on they are captured and replayed, filled up with padding rows and tokens. Every step's logits are those of
+    an executor without graphs; the last ones are checked against the plain implementation; requests longer than the
+    window, pages used again."""
+    t = TINY[name]
+    V, P = t["config"]["vocab_size"], t["page_size"]
+    model = H.make_model(tiny_model_dirs[name], dtype, "gpu")
+    pages = 4 * (-(-100 // P)) + 2
+    execs = [StepExecutor(model, page_size=P, num_pages=pages, max_requests=8, use_graphs=g) for g in (True, False)]
+    results = []
+    for ex in execs:
+        got, hist = [], {}
+        for rep in range(4):
+            a, b, c = (f"{x}{rep}" for x in "abc")
+            hist[a] = H.random_ids(50 + rep, V, seed=10 * rep + 1)
+            hist[b] = H.random_ids(21, V, seed=10 * rep + 2)
+            ex.step([StepEntry(a, hist[a], []), StepEntry(b, hist[b], [])])                  # sizes differ from rep to rep: eager
+            prompt = H.random_ids(37, V, seed=10 * rep + 3)
+            hist[c] = []
+            cuts = [(0, 13), (13, 27), (27, 37)]
+            for lo, hi in cuts:                                                               # 2 decoded tokens beside a portion
+                na, nb = H.random_ids(2, V, seed=100 * rep + lo)
+                want_c = [hi - lo - 1] if hi == 37 else []
+                got.append(ex.step([StepEntry(a, [na], [0]), StepEntry(c, prompt[lo:hi], want_c), StepEntry(b, [nb], [0])]))
+                hist[a].append(na); hist[b].append(nb); hist[c] = prompt[:hi]
+            final = {r: list(hist[r]) for r in (a, b, c)}
+            for r in (a, b, c):
+                ex.finish(r)
+        results.append(got)
+        ex.cache.check_invariants()
+    graphs, eager = execs
+    mixed_keys = [k for k in graphs._graphs if k[0] != k[1]]
+    assert mixed_keys and graphs.graph_replays >= 4, (list(graphs._graphs), graphs.graph_replays)
+    for i, (x, y) in enumerate(zip(*results)):
+        assert x.shape == y.shape, i
+        assert H.scaled_error(x, y) <= H.bound_for(dtype) / 4, i
+    last = results[0][-1]      # rows: a's decoded token, c's last prompt token, b's decoded token
+    order = list(final)        # a, b, c
+    for row, r in zip(last, (order[0], order[2], order[1])):
+        want = H.plain_logits(tiny_model_dirs[name], final[r], dtype == torch.bfloat16)[-1]
+        assert H.scaled_error(row, want) <= H.bound_for(dtype), r

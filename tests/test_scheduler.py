@@ -171,3 +171,38 @@ def test_plans_are_a_function_of_the_calls():
             log.append([(r.sequence.request_id, r.start, r.count, r.samples) for r in plan.rows] + plan.preempted)
         return log
     assert trace() == trace()
+
+
+def test_sizes_of_captured_steps_and_padding_rows():
+    """The steps in which captured decode steps grow, and the tables of a row that only fills one up."""
+    import numpy as np
+
+    from roost_b200.cache.manager import CacheManager, build_groups
+    from roost_b200.engine.batch import BatchBuilder, attention_work, pad_row, padded_rows
+    from roost_b200.engine.executor import graph_kv_cap, graph_rows
+    from roost_b200.parts import CacheNeed
+    assert [graph_rows(n) for n in (1, 5, 8, 9, 12, 13, 17, 33, 64, 65, 100)] == [1, 5, 8, 12, 12, 16, 24, 48, 64, 96, 128]
+    assert all(n <= graph_rows(n) <= max(n, n * 3 // 2 + 1) for n in range(1, 600))
+    assert [graph_kv_cap(n) for n in (1, 1024, 1025, 8192, 8193, 32768, 32769)] == [1024, 1024, 2048, 8192, 12288, 32768, 49152]
+    groups = build_groups([CacheNeed(kind="paged", kv_heads=1, head_dim=16, window=None)], 4)
+    cm = CacheManager(groups, [8, 4])     # the paged group and the (empty) group of fixed-size state
+    rc = cm.extend("a", 6)
+    rows = padded_rows([(rc, 5, [9], [0])], 3, 3)
+    assert rows[1:] == [pad_row(1), pad_row(1)]
+    ht = BatchBuilder("cpu", cm).host_tables(rows, vocab=16)
+    ids, pos, trow, q_indptr, kv_lens, selected, slot, indptr, indices, state_slots = ht.arrays
+    assert state_slots.tolist()[1:] == [0, 0] and selected.tolist() == [0]
+    assert pos.tolist() == [5, -1, -1] and kv_lens.tolist() == [6, 0, 0] and q_indptr.tolist() == [0, 1, 2, 3]
+    assert slot.tolist()[1:] == [-1, -1] and slot[0] >= 0 and indptr.tolist() == [0, 2, 2, 2] and len(indices) == 2
+    assert ht.max_position == 5 and ht.max_kv_len == 6 and ht.row_starts == [5, -1, -1]
+    prefill, decode, merge, slots = attention_work(ht.row_starts, ht.row_counts, 4, None, 64)
+    assert decode == [0, 0, 6, -1] and not prefill and not merge and slots == 0
+    # a step of several tokens a row: the padding tokens one to a padding row, the rest to the first; rows may stay empty
+    assert [len(r[2]) for r in padded_rows([(rc, 2, [1, 2, 3], [2])], 8, 4)] == [3, 3, 1, 1]
+    assert [len(r[2]) for r in padded_rows([(rc, 2, [1, 2, 3], [2])], 4, 4)] == [3, 0, 1, 0]
+    ht = BatchBuilder("cpu", cm).host_tables(padded_rows([(rc, 2, [1, 2, 3], [2])], 4, 4), vocab=16)
+    assert ht.arrays[3].tolist() == [0, 3, 3, 4, 4] and ht.arrays[4].tolist() == [5, 0, 0, 0] and ht.arrays[1].tolist() == [2, 3, 4, -1]
+    with pytest.raises(ValueError):
+        padded_rows([(rc, 2, [1, 2, 3], [2])], 4, 1)
+    from roost_b200.engine.executor import graph_tokens
+    assert [graph_tokens(n) for n in (2, 8, 9, 33, 64, 65, 505, 512, 513, 1000)] == [8, 8, 16, 64, 64, 128, 512, 512, 640, 1024]
