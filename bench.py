@@ -246,8 +246,8 @@ def timed_serving(model, requests: int, budget: int, new_tokens: int, max_prompt
     """The serving workload: ``requests`` concurrent requests with prompt lengths uniform in [16, max_prompt], prompts
     cut into portions under a ``budget`` of tokens a step and mixed with the decoding of the others, ``new_tokens``
     greedy tokens each, through the Python entry point (host token ids in, sampled ids out, every step). Wall clock
-    from the first step to the last, after one untimed pass of the same requests through the same engine (a server
-    that has been up for a while: its allocator is warm and its decode steps are captured)."""
+    from the first step to the last, after two untimed passes of the same requests through the same engine (a server
+    that has been up for a while: its allocator is warm and the steps whose sizes come again are captured)."""
     import torch
 
     from roost_b200 import GenerationOptions, RoostEngine
@@ -258,7 +258,7 @@ def timed_serving(model, requests: int, budget: int, new_tokens: int, max_prompt
     opts = GenerationOptions(max_output_tokens=new_tokens, ignore_eos=True).sampling()
     out = {}
     engine = RoostEngine(model, page_size=PAGE, attention_blocks=pages, max_sequences=requests, max_tokens=budget)
-    for timed in (False, True):
+    for timed in (False, False, True):
         replays0 = engine.executor.prepared_replays
         steps0 = engine.steps
         for p in prompts:
