@@ -12,6 +12,8 @@ and exits with 2.
 
     roost generate --model DIR (--prompt-ids 1,2,3 | --prompt-file FILE) [--max-output-tokens N] [--temperature T]
                    [--top-p P] [--top-k K] [--min-p P] [--seed S] [--stop-ids a,b] [--ignore-eos] [engine options]
+    roost chat --model DIR [--tokenizer tokenizer.json] [--template TEXT] [--max-output-tokens N] [sampling options as
+               for generate] [engine options]                       a console: /reset clears the conversation, /exit quits
     roost random-weights --config config.json --out DIR [--seed S] [--std X] [--norm-std X]
     roost replay --model DIR --dtype bfloat16|float32 --out DIR --max-tokens N      (bin/trace_run)
     roost doctor [--model DIR] [--kernels DIR] [--no-gpu] [--min-free-memory-gib N]
@@ -31,6 +33,8 @@ _ENGINE_VALUED = {"--dtype", "--device", "--kernels", "--page-size", "--attentio
 _COMMANDS = {
     "generate": (_ENGINE_VALUED | {"--model", "--prompt-ids", "--prompt-file", "--max-output-tokens", "--temperature", "--top-p",
                                    "--top-k", "--min-p", "--seed", "--stop-ids"}, {"--ignore-eos"}),
+    "chat": (_ENGINE_VALUED | {"--model", "--tokenizer", "--template", "--max-output-tokens", "--temperature", "--top-p", "--top-k",
+                               "--min-p", "--seed", "--stop-ids"}, {"--ignore-eos"}),
     "random-weights": ({"--config", "--out", "--seed", "--std", "--norm-std"}, set()),
     "replay": ({"--model", "--dtype", "--out", "--max-tokens", "--page-size"}, set()),
     "doctor": ({"--model", "--kernels", "--min-free-memory-gib"}, {"--no-gpu"}),
@@ -136,6 +140,89 @@ def cmd_generate(opts) -> int:
     return 0
 
 
+CHAT_TEMPLATE = "<|im_start|>user\n{message}<|im_end|>\n<|im_start|>assistant\n"
+
+
+def cmd_chat(opts, lines=None, out=None) -> int:
+    """A console in the manner of the reference's sample (samples/ChatConsole/Program.cs:84-120): a line is a turn,
+    the whole conversation so far is the prompt of every turn, ``/reset`` clears it, ``/exit`` or an empty line
+    quits; a turn that no longer fits is dropped with its error's code. With a tokenizer (``--tokenizer``, or
+    tokenizer.json in the model folder, and the ``tokenizers`` package) a line is text, wrapped by ``--template``
+    (``{message}`` is the line; the default is the ChatML turn Qwen3 checkpoints are tuned on) and the reply is printed
+    as text; without one a line is token ids and so is the reply."""
+    model = _need(opts, "--model")
+    dtype = opts.get("--dtype", "bfloat16")
+    if dtype not in ("bfloat16", "float32"):
+        raise UsageError("--dtype is bfloat16 or float32")
+    engine_opts = dict(page_size=_int(opts, "--page-size", 16), attention_blocks=_int(opts, "--attention-blocks"),
+                       max_sequences=_int(opts, "--max-sequences", 1), max_tokens=_int(opts, "--max-tokens", 2048),
+                       max_chunk_tokens=_int(opts, "--max-chunk-tokens"))
+    gen_opts = dict(max_output_tokens=_int(opts, "--max-output-tokens", 256), temperature=_float(opts, "--temperature"),
+                    top_p=_float(opts, "--top-p"), top_k=_int(opts, "--top-k"), min_p=_float(opts, "--min-p"),
+                    seed=_int(opts, "--seed"), stop_token_ids=tuple(_ids(opts.get("--stop-ids", ""), "--stop-ids")),
+                    ignore_eos="--ignore-eos" in opts)
+    template = opts.get("--template", CHAT_TEMPLATE)
+    if "{message}" not in template:
+        raise UsageError("--template needs the placeholder {message}")
+    tokenizer_path = opts.get("--tokenizer") or os.path.join(model, "tokenizer.json")
+    tokenizer = None
+    if os.path.exists(tokenizer_path):
+        try:
+            from tokenizers import Tokenizer
+        except ImportError:
+            raise UsageError("a tokenizer file is given but the 'tokenizers' package is not installed") from None
+        tokenizer = Tokenizer.from_file(tokenizer_path)
+    elif "--tokenizer" in opts:
+        raise UsageError(f"--tokenizer: {tokenizer_path} does not exist")
+    _apply_common(opts)
+    from .engine.engine import GenerationOptions, RoostEngine
+    from .engine.request import RequestError
+    out = out or sys.stdout
+    engine = RoostEngine(model, dtype=dtype, **engine_opts)
+    go = GenerationOptions(**gen_opts)
+    print(f"Ready: {model}, {'text' if tokenizer else 'token ids'} in and out. /reset clears the conversation, /exit quits.", file=out, flush=True)
+    history: list[int] = []
+    lines = sys.stdin if lines is None else lines
+    read = lines.readline if hasattr(lines, "readline") else (lambda it=iter(lines): next(it, ""))
+    while True:
+        print("> ", end="", file=out, flush=True)
+        text = read().strip()
+        if not text or text == "/exit":
+            return 0
+        if text == "/reset":
+            history.clear()
+            print("(conversation cleared)", file=out, flush=True)
+            continue
+        if tokenizer is not None:
+            # turns are separated by a line break, as the template ends its own lines
+            turn = tokenizer.encode(("\n" if history else "") + template.replace("{message}", text), add_special_tokens=False).ids
+        else:
+            try:
+                turn = _ids(text, "a turn")
+            except UsageError:
+                print("[InvalidOption] a turn is token ids separated by commas or spaces", file=out, flush=True)
+                continue
+        reply: list[int] = []
+        shown = ""
+        try:
+            for update in engine.stream_completion(history + turn, go):
+                if update.token is None:
+                    continue
+                reply.append(update.token)
+                if tokenizer is None:
+                    print(("" if len(reply) == 1 else " ") + str(update.token), end="", file=out, flush=True)
+                else:   # decode the whole reply and print what is new: a token may end inside a character
+                    whole = tokenizer.decode(reply, skip_special_tokens=True)
+                    if not whole.endswith("\ufffd"):
+                        print(whole[len(shown):], end="", file=out, flush=True)
+                        shown = whole
+        except RequestError as e:
+            print(f"\n[{e.kind}] {e} (type /reset to start over)", file=out, flush=True)
+            continue
+        print(file=out, flush=True)
+        history += turn + reply
+
+
 def cmd_random_weights(opts) -> int:
     from .weights.random_init import write_random_model
     with open(_need(opts, "--config")) as f:
@@ -217,7 +304,7 @@ def main(argv=None) -> int:
     argv = list(sys.argv[1:] if argv is None else argv)
     try:
         command, opts = parse(argv)
-        return {"generate": cmd_generate, "random-weights": cmd_random_weights, "replay": cmd_replay, "doctor": cmd_doctor}[command](opts)
+        return {"generate": cmd_generate, "chat": cmd_chat, "random-weights": cmd_random_weights, "replay": cmd_replay, "doctor": cmd_doctor}[command](opts)
     except UsageError as e:
         print(f"roost: {e}\n\nusage:\n{USAGE}", file=sys.stderr)
         return 2

@@ -41,3 +41,41 @@ def test_generate_doctor_and_usage_errors(tiny_model_dirs, tmp_path):
     cfg_path.write_text(json.dumps(TINY["B"]["config"]))
     r = roost("random-weights", "--config", str(cfg_path), "--out", str(tmp_path / "m"), "--seed", "4", "--std", "0.05")
     assert r.returncode == 0 and (tmp_path / "m" / "model.safetensors").exists() and (tmp_path / "m" / "config.json").exists()
+
+
+def test_chat_console_keeps_the_conversation(tiny_model_dirs, tmp_path):
+    """Token ids in and out; every turn's prompt is the conversation so far; /reset clears it; a turn that cannot fit is
+    dropped with the refusal's name; with a tokenizer file a line is text and so is the reply."""
+    import shutil
+    model_dir = tiny_model_dirs["A"]
+    V = TINY["A"]["config"]["vocab_size"]
+    first, second = H.random_ids(9, V, 21), H.random_ids(4, V, 22)
+    too_long = " ".join(map(str, H.random_ids(600, V, 23)))        # the model has 512 positions
+    script = "\n".join([" ".join(map(str, first)), ",".join(map(str, second)), too_long, "/reset", " ".join(map(str, first)), "/exit"]) + "\n"
+    args = [sys.executable, str(ROOT / "bin" / "roost"), "chat", "--model", str(model_dir), "--dtype", "float32", "--max-output-tokens", "5",
+            "--ignore-eos", "--attention-blocks", "16"]
+    r = subprocess.run(args, input=script, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr
+    lines = [ln[2:] if ln.startswith("> ") else ln for ln in r.stdout.splitlines()]
+    replies = [ln for ln in lines if ln and ln[0].isdigit()]
+    cfg, w = plain.load_model_dir(model_dir)
+    a = plain.greedy(cfg, w, first, 5)
+    b = plain.greedy(cfg, w, first + a + second, 5)
+    assert [list(map(int, x.split())) for x in replies] == [a, b, a]
+    assert any(ln.startswith("[") and "/reset" in ln for ln in lines) and "(conversation cleared)" in lines
+
+    from tokenizers import Tokenizer, models, pre_tokenizers
+    words = {f"w{i}": i for i in range(V)}
+    tok = Tokenizer(models.WordLevel(words, unk_token="w0"))
+    tok.pre_tokenizer = pre_tokenizers.Whitespace()
+    with_tok = tmp_path / "with_tokenizer"
+    shutil.copytree(model_dir, with_tok)
+    tok.save(str(with_tok / "tokenizer.json"))
+    text = " ".join(f"w{i}" for i in first)
+    r = subprocess.run(args[:4] + [str(with_tok)] + args[5:] + ["--template", "{message}"], input=text + "\n/exit\n", capture_output=True,
+                       text=True, timeout=300)
+    assert r.returncode == 0, r.stderr
+    reply = [ln[2:] for ln in r.stdout.splitlines() if ln.startswith("> w")]
+    assert reply and reply[0].split() == [f"w{i}" for i in a]
+    r = subprocess.run(args + ["--template", "no placeholder"], input="", capture_output=True, text=True, timeout=300)
+    assert r.returncode == 2 and "usage" in r.stderr
