@@ -23,17 +23,17 @@ from .batch import AttentionPlan, BatchBuilder, HostTables, StaticTables, attent
 from .model import Model
 
 MAX_GRAPHS = 64
-GRAPH_TOKENS = 1024   # a step of more tokens runs eagerly: the device bounds it, not the host's launches
+GRAPH_TOKENS = 2048   # a step of more tokens runs eagerly: the device bounds it, not the host's launches
 
 
 def graph_tokens(n: int) -> int:
     """Tokens of the captured step that serves a step of ``n`` tokens of which some row brings more than one: 8, 16, 32,
-    then the next multiple of 64 up to 512 and of 128 beyond. A scheduler that fills a token budget asks for the
-    budget's own size step after step."""
+    then the next multiple of 64 up to 512, of 128 up to 1024 and of 256 beyond. A scheduler that fills a token budget
+    asks for the budget's own size step after step."""
     for m in (8, 16, 32):
         if n <= m:
             return m
-    granule = 64 if n <= 512 else 128
+    granule = 64 if n <= 512 else (128 if n <= 1024 else 256)
     return -(-n // granule) * granule
 
 

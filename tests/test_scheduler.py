@@ -205,4 +205,4 @@ def test_sizes_of_captured_steps_and_padding_rows():
     with pytest.raises(ValueError):
         padded_rows([(rc, 2, [1, 2, 3], [2])], 4, 1)
     from roost_b200.engine.executor import graph_tokens
-    assert [graph_tokens(n) for n in (2, 8, 9, 33, 64, 65, 505, 512, 513, 1000)] == [8, 8, 16, 64, 64, 128, 512, 512, 640, 1024]
+    assert [graph_tokens(n) for n in (2, 8, 9, 33, 64, 65, 505, 512, 513, 1000, 1025, 2000)] == [8, 8, 16, 64, 64, 128, 512, 512, 640, 1024, 1280, 2048]
