@@ -26,6 +26,21 @@ from .request import GREEDY, Request, RequestError, SamplingParameters, TokenEve
 from .scheduler import Scheduler, SchedulerOptions, StepPlan
 
 
+class _Done:
+    def synchronize(self) -> None:
+        pass
+
+
+@dataclass
+class _InFlight:
+    """A decode step that was started before the tokens of the step before it were read (see ``RoostEngine.step``)."""
+    prep: object                  # the executor's PreparedDecode
+    ids_device: torch.Tensor      # the tokens it samples, on the device
+    ids_host: torch.Tensor        # their pinned copy, valid once ``event`` has passed
+    event: object
+    fed: list | None = None       # the tokens it was fed, once the host has read them
+
+
 @dataclass
 class GenerationOptions:
     """Options of one completion, with the reference's names in snake case."""
@@ -64,11 +79,14 @@ class Completion:
 class RoostEngine:
     def __init__(self, model, *, dtype: str | torch.dtype = "bfloat16", device: str = "cuda", page_size: int = 16,
                  attention_blocks: int | None = None, kv_fraction: float = 0.9, max_sequences: int = 64, max_tokens: int = 2048,
-                 max_chunk_tokens: int | None = None, seed: int | None = None):
+                 max_chunk_tokens: int | None = None, seed: int | None = None, chain_steps: bool = True):
         """``model``: a folder with config.json and model.safetensors, or a built ``Model``. ``attention_blocks``:
         pages in each paged pool (else ``kv_fraction`` of the free device memory); ``max_tokens`` and
         ``max_sequences``: the largest token and row count of a step (the reference's worker flags of the same
-        names, src/Starlings.Roost.WorkerHost/WorkerArguments.cs:51-58)."""
+        names, src/Starlings.Roost.WorkerHost/WorkerArguments.cs:51-58). ``chain_steps``: while every live request
+        decodes, the next step is started on the device before this step's tokens have been read (the reference's
+        planner has the same option, src/Starlings.Roost.Engine/Scheduling/StepPlanner.cs:316-336); the tokens
+        are the same with it and without."""
         if isinstance(dtype, str):
             dtype = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}[dtype]
         self.model: Model = model if isinstance(model, Model) else load_model(model, dtype, device)
@@ -85,6 +103,9 @@ class RoostEngine:
         self.steps = 0
         self.last_plan: StepPlan | None = None
         self._prepared = None     # the next decode step's tables, made while the device ran the last one
+        self._inflight: _InFlight | None = None   # the next decode step, already running
+        self.chain_steps = chain_steps
+        self.chained_steps = 0    # steps that were running before the tokens of the step before them had been read
 
     # ------------------------------------------------------------------ requests
     def add_request(self, prompt_token_ids, sampling: SamplingParameters = GREEDY, *, request_id=None, stop_token_ids=(),
@@ -121,21 +142,53 @@ class RoostEngine:
         if plan.rows:
             entries = [StepEntry(r.sequence.request_id, r.tokens, [r.count - 1] if r.samples else [], r.start) for r in plan.rows]
             prepared, self._prepared = self._prepared, None
-            if prepared is not None and self.executor.matches_prepared(prepared, entries):
-                logits = self.executor.run_prepared(prepared, entries)
-            else:
-                logits = self.executor.step(entries)
+            inflight, self._inflight = self._inflight, None
             sampling_rows = [r for r in plan.rows if r.samples]
+            ids_device = ids_host = event = None
+            keep = None
+            if inflight is not None and len(sampling_rows) == len(plan.rows):
+                keep = self.executor.adoptable(inflight.prep, entries)
+                if keep is not None and any(e.tokens[0] != inflight.fed[i] for e, i in zip(entries, keep)):
+                    keep = None    # the step was fed other tokens than the plan names: it does not stand
+            if keep is not None:
+                # this step is running already (or done): it was started with the tokens on the device
+                self.executor.adopt_prepared(inflight.prep, keep)
+                self.chained_steps += 1
+                ids_device, ids_host, event = inflight.ids_device, inflight.ids_host, inflight.event
+                if len(keep) != ids_device.numel():
+                    ids_device = ids_device[torch.tensor(keep, dtype=torch.long).to(ids_device.device, non_blocking=True)]
+            else:
+                # (a step in flight that does not stand is dropped: what it wrote lies beyond its requests' committed
+                # lengths and is written again, and the pages it took stay with their requests)
+                if prepared is not None and self.executor.matches_prepared(prepared, entries):
+                    logits = self.executor.run_prepared(prepared, entries)
+                else:
+                    logits = self.executor.step(entries)
+                if sampling_rows:
+                    rows = [SamplingRow(r.sequence.request.sampling, self._seeds[r.sequence.request_id], r.sequence.generated)
+                            for r in sampling_rows]
+                    ids_device = self.sampler(logits, rows)
+                    ids_host, event = self._to_host(ids_device)
+                    keep = list(range(len(sampling_rows)))
             if sampling_rows:
-                rows = [SamplingRow(r.sequence.request.sampling, self._seeds[r.sequence.request_id], r.sequence.generated)
-                        for r in sampling_rows]
-                ids_device = self.sampler(logits, rows)
-                # While the device runs this step: the tables of the next one, should it be these rows' next tokens and
-                # nothing else (no request waiting for its prompt, none ending now). The host then only fills the
-                # tokens in when they arrive.
+                # While the device runs this step: the next one, should it be these rows' next tokens and nothing else
+                # (no request waiting for its prompt). Its tables are made now; with ``chain_steps`` it is also started
+                # now, fed with this step's tokens on the device, and the host reads this step's tokens meanwhile.
                 if len(sampling_rows) == len(plan.rows) and all(r.count == 1 for r in plan.rows) and self._decode_only():
-                    self._prepared = self.executor.prepare_decode([r.sequence.request_id for r in plan.rows])
-                ids = ids_device.cpu().tolist()
+                    prep = self.executor.prepare_decode([r.sequence.request_id for r in plan.rows])
+                    if prep is not None and self.chain_steps:
+                        nxt = self.executor.launch_prepared(prep, ids_device)
+                        rows = [SamplingRow(r.sequence.request.sampling, self._seeds[r.sequence.request_id], r.sequence.generated + 1)
+                                for r in plan.rows]
+                        nxt_ids = self.sampler(nxt, rows)
+                        self._inflight = _InFlight(prep, nxt_ids, *self._to_host(nxt_ids))
+                    else:
+                        self._prepared = prep
+                event.synchronize()
+                host = ids_host.tolist()
+                ids = [host[i] for i in keep]
+                if self._inflight is not None:
+                    self._inflight.fed = ids
                 tokens = {r.sequence.request_id: t for r, t in zip(sampling_rows, ids)}
             self.steps += 1
             if self.steps % self.STATUS_EVERY == 0:
@@ -147,6 +200,16 @@ class RoostEngine:
         return events
 
     STATUS_EVERY = 256   # steps between looks at the kernels' status words
+
+    def _to_host(self, ids_device: torch.Tensor):
+        """Starts the copy of sampled ids to pinned host memory; (the host tensor, the event that says it has arrived)."""
+        if ids_device.device.type != "cuda":
+            return ids_device, _Done()
+        host = torch.empty(ids_device.shape, dtype=ids_device.dtype, pin_memory=True)
+        host.copy_(ids_device, non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        return host, event
 
     def check_device(self) -> None:
         """Raises if a kernel gave up one of its bounded waits since the last look (its results were then not valid)."""

@@ -366,6 +366,47 @@ class StepExecutor:
         self.steps_run += 1
         return logits
 
+    def launch_prepared(self, prep: PreparedDecode, ids_device: torch.Tensor) -> torch.Tensor:
+        """Starts the prepared step with its token ids still on the device: the ids the step before has sampled, one a
+        row, in the rows' order. The tables go up, the ids are copied into their table on the device, the graph is
+        replayed. The host has read nothing: the caller may start this step before it knows the tokens of the step
+        before. Nothing is committed either; ``adopt_prepared`` does that once the caller knows which rows stand (a row
+        whose request turns out to have ended with the token before is simply dropped: what it wrote lies in pages
+        that go back to the pool, and later launches come after it on the stream)."""
+        n = len(prep.request_ids)
+        if ids_device.numel() != n or ids_device.dtype != torch.int32:
+            raise ValueError("launch_prepared: one int32 token id a row is needed")
+        g = prep.graph
+        g.static.send(prep.staged)
+        g.static.views[0][:n].copy_(ids_device)
+        g.graph.replay()
+        self.rt.kernels.launches += g.launches
+        self.last_upload_bytes = g.static.total * 4
+        return g.out[:n].clone()
+
+    def adoptable(self, prep: PreparedDecode, entries: list[StepEntry]) -> list[int] | None:
+        """The rows of a step started by ``launch_prepared`` that these entries name, when the entries are exactly such
+        a step: the same requests or some of them, in the same order, one token each at the position the step was
+        prepared for, its logits wanted. None otherwise."""
+        where = {rid: i for i, rid in enumerate(prep.request_ids)}
+        keep, last = [], -1
+        for e in entries:
+            i = where.get(e.request_id)
+            if (i is None or i <= last or len(e.tokens) != 1 or list(e.want) != [0] or e.request_id not in self.cache
+                    or self.cache.get(e.request_id).tokens != prep.starts[i] or (e.start is not None and e.start != prep.starts[i])):
+                return None
+            keep.append(i)
+            last = i
+        return keep or None
+
+    def adopt_prepared(self, prep: PreparedDecode, keep: list[int]) -> None:
+        """The step started by ``launch_prepared`` stands for the rows ``keep``: their requests now hold one token more."""
+        for i in keep:
+            self.cache.commit(prep.request_ids[i], prep.starts[i] + 1)
+        self.graph_replays += 1
+        self.prepared_replays += 1
+        self.steps_run += 1
+
     def _zero_new_state(self, rows) -> None:
         """A request's fixed-size state starts at zero when its first token arrives, as the reference's worker
         zeroes a recurrent slot at position 0 (src/Starlings.Roost.Worker/Eager/EagerWorker.cs:214-230)."""

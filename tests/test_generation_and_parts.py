@@ -540,3 +540,43 @@ def test_a_toy_routed_feed_forward_and_a_toy_position_encoding_are_registered_bu
     got = H.run_portions(ex, "c", a, [5, 2, 14])
     assert H.scaled_error(got, want_a) < bound
     assert not ex.use_graphs and ex.graph_replays == 0
+
+
+@pytest.mark.gpu
+def test_steps_started_before_the_last_tokens_were_read_give_the_same_tokens(tiny_model_dirs):
+    """While every live request decodes, the engine starts the next step with the sampled tokens still on the device.
+    Requests that end at different times (their rows of the running step are dropped), stop tokens, a request that
+    arrives in the middle (the running step stands, the newcomer joins a step later) and one that is cancelled: the
+    tokens are those of an engine that reads every step's tokens first."""
+    t = TINY["B"]
+    model = H.make_model(tiny_model_dirs["B"], torch.float32, "gpu")
+    V = t["config"]["vocab_size"]
+    prompts = [H.random_ids(n, V, 400 + n) for n in (5, 11, 17, 23, 9)]
+    opts = [GenerationOptions(max_output_tokens=m, temperature=(0.9 if i % 2 else None), top_p=0.95, seed=60 + i)
+            for i, m in enumerate((40, 9, 26, 14, 12))]
+    results = []
+    for chain in (True, False):
+        engine = RoostEngine(model, page_size=t["page_size"], attention_blocks=96, max_sequences=8, max_tokens=64, chain_steps=chain)
+        got = {}
+        ids = [engine.add_request(p, o.sampling(), stop_token_ids=o.stop_token_ids) for p, o in zip(prompts[:3], opts[:3])]
+        steps = 0
+        while engine.has_unfinished():
+            for e in engine.step():
+                if e.token is not None:
+                    got.setdefault(e.request_id, []).append(e.token)
+            steps += 1
+            if steps == 7:
+                ids.append(engine.add_request(prompts[3], opts[3].sampling()))
+            if steps == 12:
+                ids.append(engine.add_request(prompts[4], opts[4].sampling()))
+            if steps == 16:
+                engine.cancel(ids[4])
+        results.append([got.get(r, []) for r in ids[:4]])
+        assert engine.executor.cache.pools[0].free_count == 96
+        engine.executor.cache.check_invariants()
+        if chain:
+            assert engine.chained_steps > 10
+        else:
+            assert engine.chained_steps == 0
+    assert results[0] == results[1]
+    assert [len(x) for x in results[0]][1] == 9
