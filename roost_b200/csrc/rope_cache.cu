@@ -57,92 +57,6 @@ __global__ void qk_norm_rope_cache_kernel(const T* __restrict__ qkv, int64_t qkv
     __syncthreads();
   }
 
-  // Many tokens of bfloat16 with every element rotated and a head of 64, 128 or 256: a lane owns eight neighbouring
-  // elements (one 16-byte access) of a head slot, so a warp serves 32 / (head_dim / 8) slots at a time; the lane that
-  // holds the other element of each of its pairs is head_dim / 16 lanes away, and the sum of squares is reduced over
-  // the slot's lanes only. A fifth of the instructions of the element-by-element form below.
-  if constexpr (TABLE && sizeof(T) == 2) {
-    if (vector_ok && rotary_dim == head_dim && (head_dim == 64 || head_dim == 128 || head_dim == 256)) {
-      const int lanes_per_slot = head_dim / 8, slots_per_pass = 32 / lanes_per_slot;
-      const int sub = lane / lanes_per_slot, c = lane % lanes_per_slot;  // which slot of the pass, which chunk of its head
-      const int pair_lanes = lanes_per_slot / 2;                        // the lane that holds the pairs' other elements: lane ^ pair_lanes
-      const bool second = c >= pair_lanes;                              // this lane's elements are the x2 of their pairs
-      const int i0 = (c % pair_lanes) * 8;                              // first pair index of the lane
-      float wq[8], wk[8];
-#pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        wq[e] = q_w ? load_w(q_w, c * 8 + e, wdtype) : 1.0f;
-        wk[e] = k_w ? load_w(k_w, c * 8 + e, wdtype) : 1.0f;
-      }
-      float cs[8], sn[8];
-#pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        const float2 r = cos_sin[i0 + e];
-        cs[e] = r.x;
-        sn[e] = second ? r.y : -r.y;  // x1' = x1 c - x2 s; x2' = x2 c + x1 s: own * c + other * (-+s)
-      }
-      const int slot = slot_mapping ? slot_mapping[t] : -1;
-      const int64_t page = slot >= 0 ? slot / page_size : 0;
-      const int off = slot >= 0 ? slot % page_size : 0;
-      const bool cache_ok = slot >= 0 && page < pool_pages;
-      const int first_warp_slot = (blockIdx.y * warps + (threadIdx.x >> 5)) * slots_per_pass;
-      const int pass_stride = gridDim.y * warps * slots_per_pass;
-      float x_next[8];
-      auto fetch = [&](int base) {  // the lane's eight elements of the pass that starts at slot `base`
-        if (base + sub < slots_per_token) {
-          Vec<T>::load(row + (size_t)(base + sub) * head_dim + c * 8, x_next);
-        } else {
-#pragma unroll
-          for (int e = 0; e < 8; ++e) x_next[e] = 0.f;
-        }
-      };
-      fetch(first_warp_slot);
-      for (int base = first_warp_slot; base < slots_per_token; base += pass_stride) {
-        const int slot_idx = base + sub;
-        const bool live = slot_idx < slots_per_token;
-        int kind = 0, head = 0;
-        if (live) {
-          if (slot_idx < q_heads) {
-            kind = 0; head = slot_idx;
-          } else if (slot_idx < q_heads + kv_heads) {
-            kind = 1; head = slot_idx - q_heads;
-          } else {
-            kind = 2; head = slot_idx - q_heads - kv_heads;
-          }
-        }
-        float x[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) x[e] = x_next[e];
-        fetch(base + pass_stride);  // the next pass's elements travel while this pass is computed
-        float ss = 0.f;
-#pragma unroll
-        for (int e = 0; e < 8; ++e) ss += x[e] * x[e];
-        for (int o = lanes_per_slot / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-        const void* w = kind == 0 ? q_w : k_w;
-        const float inv = (kind != 2 && w != nullptr) ? 1.0f / sqrtf(ss / (float)head_dim + eps) : 1.0f;
-        float y[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) y[e] = kind == 2 ? x[e] : x[e] * inv * (kind == 0 ? wq[e] : wk[e]);
-        float out[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          const float other = __shfl_xor_sync(0xffffffffu, y[e], pair_lanes);
-          out[e] = kind == 2 ? y[e] : y[e] * cs[e] + other * sn[e];
-        }
-        if (!live) continue;
-        T* dst;
-        if (kind == 0) {
-          dst = q_out + (t * q_heads + head) * head_dim;
-        } else {
-          if (!cache_ok) continue;  // a skipped token, or a slot beyond the pool: never written
-          dst = (kind == 1 ? k_pool : v_pool) + ((page * kv_heads + head) * page_size + off) * head_dim;
-        }
-        Vec<T>::store(dst + c * 8, out);
-      }
-      return;
-    }
-  }
-
   for (int slot_idx = blockIdx.y * warps + (threadIdx.x >> 5); slot_idx < slots_per_token; slot_idx += gridDim.y * warps) {
     int kind, head;  // 0 q, 1 k, 2 v
     if (slot_idx < q_heads) {
@@ -232,6 +146,138 @@ __global__ void qk_norm_rope_cache_kernel(const T* __restrict__ qkv, int64_t qkv
   }
 }
 
+// bfloat16, every element rotated, a head of 64, 128 or 256 elements, 16-byte aligned rows, more than a few tokens.
+// A lane owns four elements of the head's first half and the four that pair with them in the second half (two 8-byte
+// accesses), so a rotation needs no exchange between lanes; D / 8 lanes serve a head slot and a warp 32 / (D / 8)
+// slots at a time; the sum of squares is reduced over the slot's lanes. A block of eight warps takes several tokens
+// in turn: the norm weights stay in registers for all of them, and the cosines and sines of the next token are
+// computed (by D / 2 of the threads, in the reference's 64-bit form) while the heads of the current one are processed.
+template <int D>
+__global__ void __launch_bounds__(256, 4) qk_norm_rope_cache_vec_kernel(
+    const __nv_bfloat16* __restrict__ qkv, int64_t qkv_stride, __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_pool,
+    __nv_bfloat16* __restrict__ v_pool, const void* __restrict__ q_w, const void* __restrict__ k_w, const double* __restrict__ inv_freq,
+    const int32_t* __restrict__ positions, const int32_t* __restrict__ slot_mapping, int tokens, int tokens_per_block, int q_heads,
+    int kv_heads, float eps, int page_size, int page_shift, int64_t pool_pages, int slots_per_token, int wdtype) {
+  constexpr int kLanes = D / 8;          // lanes of a head slot
+  constexpr int kSlots = 32 / kLanes;    // head slots of a warp's pass
+  constexpr int kHalf = D / 2;
+  constexpr int kWarps = 8;
+  __shared__ float2 cos_sin[2][kHalf];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int sub = lane / kLanes, c = lane % kLanes;   // which slot of the pass; which four pairs of its head
+  float wq_lo[4], wq_hi[4], wk_lo[4], wk_hi[4];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    wq_lo[e] = q_w ? load_w(q_w, 4 * c + e, wdtype) : 1.0f;
+    wq_hi[e] = q_w ? load_w(q_w, kHalf + 4 * c + e, wdtype) : 1.0f;
+    wk_lo[e] = k_w ? load_w(k_w, 4 * c + e, wdtype) : 1.0f;
+    wk_hi[e] = k_w ? load_w(k_w, kHalf + 4 * c + e, wdtype) : 1.0f;
+  }
+  const bool normed = q_w != nullptr;
+  const double freq = (int)threadIdx.x < kHalf ? inv_freq[threadIdx.x] : 0.0;
+  pdl_launch_dependents(3);
+  pdl_wait(3);
+  const int t0 = blockIdx.x * tokens_per_block;
+  const int t1 = min(tokens, t0 + tokens_per_block);
+  auto table = [&](int t, int buf) {
+    if ((int)threadIdx.x < kHalf) {
+      double ang = (double)positions[t] * freq;
+      ang -= 6.283185307179586476925286766559 * rint(ang * 0.15915494309189533576888376337251);
+      float sn, cs;
+      sincosf((float)ang, &sn, &cs);
+      cos_sin[buf][threadIdx.x] = make_float2(cs, sn);
+    }
+  };
+  auto unpack = [](const uint2 u, float (&v)[4]) {
+    v[0] = __uint_as_float(u.x << 16); v[1] = __uint_as_float(u.x & 0xffff0000u);
+    v[2] = __uint_as_float(u.y << 16); v[3] = __uint_as_float(u.y & 0xffff0000u);
+  };
+  auto store_half = [](__nv_bfloat16* p, const float (&v)[4]) {
+    const __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+    *reinterpret_cast<uint2*>(p) = make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b));
+  };
+  if (t0 < t1) table(t0, 0);
+  __syncthreads();
+  for (int t = t0; t < t1; ++t) {
+    const int buf = (t - t0) & 1;
+    if (t + 1 < t1) table(t + 1, buf ^ 1);
+    float cs[4], sn[4];
+    {
+      const float4 r0 = *reinterpret_cast<const float4*>(&cos_sin[buf][4 * c]);
+      const float4 r1 = *reinterpret_cast<const float4*>(&cos_sin[buf][4 * c + 2]);
+      cs[0] = r0.x; sn[0] = r0.y; cs[1] = r0.z; sn[1] = r0.w;
+      cs[2] = r1.x; sn[2] = r1.y; cs[3] = r1.z; sn[3] = r1.w;
+    }
+    const int slot = slot_mapping ? slot_mapping[t] : -1;
+    const unsigned page = slot < 0 ? 0u : (page_shift >= 0 ? (unsigned)slot >> page_shift : (unsigned)slot / (unsigned)page_size);
+    const unsigned off = slot < 0 ? 0u : (unsigned)slot - page * (unsigned)page_size;
+    const bool cache_ok = slot >= 0 && (int64_t)page < pool_pages;
+    const __nv_bfloat16* row = qkv + (size_t)t * qkv_stride;
+    // the loads of up to three passes are issued before the first is used: enough bytes in flight to keep the memory busy
+    constexpr int kAhead = 3;
+    for (int base0 = warp * kSlots; base0 < slots_per_token; base0 += kAhead * kWarps * kSlots) {
+      uint2 raw_lo[kAhead], raw_hi[kAhead];
+#pragma unroll
+      for (int p = 0; p < kAhead; ++p) {
+        const int slot_idx = base0 + p * kWarps * kSlots + sub;
+        if (slot_idx < slots_per_token) {
+          const __nv_bfloat16* src = row + (size_t)slot_idx * D + 4 * c;
+          raw_lo[p] = *reinterpret_cast<const uint2*>(src);
+          raw_hi[p] = *reinterpret_cast<const uint2*>(src + kHalf);
+        }
+      }
+#pragma unroll
+      for (int p = 0; p < kAhead; ++p) {
+        const int slot_idx = base0 + p * kWarps * kSlots + sub;
+        if (slot_idx >= slots_per_token) continue;   // whole slots only: the lanes of a slot stay together
+        __nv_bfloat16* dst;
+        if (slot_idx >= q_heads + kv_heads) {   // a value head: copied as it is
+          if (!cache_ok) continue;
+          dst = v_pool + (((size_t)page * kv_heads + (slot_idx - q_heads - kv_heads)) * page_size + off) * D + 4 * c;
+          *reinterpret_cast<uint2*>(dst) = raw_lo[p];
+          *reinterpret_cast<uint2*>(dst + kHalf) = raw_hi[p];
+          continue;
+        }
+        float lo[4], hi[4];
+        unpack(raw_lo[p], lo);
+        unpack(raw_hi[p], hi);
+        const bool is_q = slot_idx < q_heads;
+        float inv = 1.0f;
+        if (normed) {
+          float ss = 0.f;
+#pragma unroll
+          for (int e = 0; e < 4; ++e) ss += lo[e] * lo[e] + hi[e] * hi[e];
+#pragma unroll
+          for (int o = kLanes / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o, kLanes);
+          inv = 1.0f / sqrtf(ss / (float)D + eps);
+        }
+        float o_lo[4], o_hi[4];
+        if (is_q) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float x1 = lo[e] * inv * wq_lo[e], x2 = hi[e] * inv * wq_hi[e];
+            o_lo[e] = x1 * cs[e] - x2 * sn[e];
+            o_hi[e] = x2 * cs[e] + x1 * sn[e];
+          }
+          dst = q_out + ((size_t)t * q_heads + slot_idx) * D + 4 * c;
+        } else {
+          if (!cache_ok) continue;
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float x1 = lo[e] * inv * wk_lo[e], x2 = hi[e] * inv * wk_hi[e];
+            o_lo[e] = x1 * cs[e] - x2 * sn[e];
+            o_hi[e] = x2 * cs[e] + x1 * sn[e];
+          }
+          dst = k_pool + (((size_t)page * kv_heads + (slot_idx - q_heads)) * page_size + off) * D + 4 * c;
+        }
+        store_half(dst, o_lo);
+        store_half(dst + kHalf, o_hi);
+      }
+    }
+    __syncthreads();   // the next token's table is complete; this token's is free to be written again
+  }
+}
+
 }  // namespace roost
 
 using namespace roost;
@@ -264,6 +310,24 @@ extern "C" int roost_qk_norm_rope_cache(const void* qkv, int64_t qkv_stride, voi
   const size_t esize = dtype == ROOST_F32 ? 4 : 2;
   const bool vector_ok = (head_dim * esize) % 16 == 0 && (qkv_stride * esize) % 16 == 0 && (uintptr_t)qkv % 16 == 0 &&
                          (uintptr_t)q_out % 16 == 0 && (!write_kv || ((uintptr_t)k_pool % 16 == 0 && (uintptr_t)v_pool % 16 == 0));
+  // bfloat16 heads of 64, 128 or 256 elements, all rotated, from 64 tokens on: the vector kernel
+  if (dtype == ROOST_BF16 && vector_ok && rotary_dim == head_dim && tokens >= 64 && (head_dim == 64 || head_dim == 128 || head_dim == 256) &&
+      (q_w == nullptr) == (k_w == nullptr)) {
+    const int per_block = tokens >= 1024 ? 4 : (tokens >= 256 ? 2 : 1);   // measured: 1, 2 and 4 within 10 %, 8 a third slower
+    const dim3 vgrid((tokens + per_block - 1) / per_block);
+    int page_shift = -1;   // pages of a power of two of tokens: a shift instead of a division
+    for (int b = 0; b < 31 && page_size > 0; ++b)
+      if (page_size == (1 << b)) page_shift = b;
+    auto launch = [&](auto kernel) {
+      launch_kernel(kernel, vgrid, dim3(256), 0, (cudaStream_t)stream, (const __nv_bfloat16*)qkv, qkv_stride, (__nv_bfloat16*)q_out,
+                    (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, q_w, k_w, inv_freq, positions, slot_mapping, tokens, per_block, q_heads,
+                    kv_heads, eps, page_size, page_shift, pool_pages, slots, wdtype);
+    };
+    if (head_dim == 64) launch(qk_norm_rope_cache_vec_kernel<64>);
+    else if (head_dim == 128) launch(qk_norm_rope_cache_vec_kernel<128>);
+    else launch(qk_norm_rope_cache_vec_kernel<256>);
+    return check_launch("qk_norm_rope_cache");
+  }
   ROOST_DISPATCH_DTYPE(dtype, T, {
     auto kernel = many ? qk_norm_rope_cache_kernel<T, true> : qk_norm_rope_cache_kernel<T, false>;
     launch_kernel(kernel, grid, dim3(warps * 32), many ? table_bytes : 0, (cudaStream_t)stream, (const T*)qkv, qkv_stride, (T*)q_out,

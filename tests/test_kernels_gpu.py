@@ -124,6 +124,52 @@ def test_qk_norm_rope_cache(kernels, dtype, nq, nkv, d, rot, page):
     assert torch.equal(q2.reshape(T, -1), qkv[:, : nq * d])
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("T,nq,nkv,d,page,weights", [(64, 8, 2, 128, 16, "same"), (300, 5, 3, 64, 8, "float32"), (1100, 3, 1, 256, 32, "same"),
+                                                     (1030, 4, 4, 128, 16, None), (70, 2, 1, 96, 16, "same")])
+def test_qk_norm_rope_cache_of_many_tokens(kernels, dtype, T, nq, nkv, d, page, weights):
+    """Steps of many tokens (bfloat16 heads of 64, 128 or 256 take a kernel of their own): several tokens a block, some
+    tokens skipped (slot -1), slots scattered over the pool, norm weights in either dtype or none."""
+    eps, theta = 1e-6, 1e6
+    g = torch.Generator().manual_seed(T + d)
+    pages = -(-T // page) + 3
+    qkv = rand((T, (nq + 2 * nkv) * d), dtype, T, 2.0)
+    wdtype = torch.float32 if weights == "float32" else dtype
+    qw = kw = None
+    if weights is not None:
+        qw = (1 + 0.1 * torch.randn(d, generator=g)).to(wdtype).cuda()
+        kw = (1 + 0.1 * torch.randn(d, generator=g)).to(wdtype).cuda()
+    positions = torch.randint(0, 200000, (T,), generator=g, dtype=torch.int32)
+    positions[:3] = torch.tensor([0, 1, 131071], dtype=torch.int32)
+    slots = torch.randperm(page * pages, generator=g)[:T].to(torch.int32)
+    slots[torch.randperm(T, generator=g)[: T // 9]] = -1
+    inv_freq = torch.pow(torch.tensor(theta, dtype=torch.float64), -2.0 * torch.arange(d // 2, dtype=torch.float64) / d).cuda()
+    kp = torch.full((pages, nkv, page, d), 7.0, dtype=dtype).cuda()
+    vp = torch.full((pages, nkv, page, d), 7.0, dtype=dtype).cuda()
+    q = kernels.qk_norm_rope_cache(qkv, nq, nkv, d, q_w=qw, k_w=kw, eps=eps, inv_freq=inv_freq, rotary_dim=d, positions=positions.cuda(),
+                                   k_pool=kp, v_pool=vp, slot_mapping=slots.cuda(), page_size=page)
+    x = qkv.double().cpu()
+    qq = x[:, : nq * d].reshape(T, nq, d)
+    kk = x[:, nq * d : (nq + nkv) * d].reshape(T, nkv, d)
+    vv = x[:, (nq + nkv) * d :].reshape(T, nkv, d)
+    if weights is not None:
+        qq, kk = plain.qk_norm(qq, kk, qw.double().cpu(), kw.double().cpu(), eps)
+    pos = positions.tolist()
+    qq = plain.rope_neox(qq, pos, theta, d)
+    kk = plain.rope_neox(kk, pos, theta, d)
+    close(q, qq, dtype, "q normed and rotated", scale=2)
+    want_k = torch.full((pages, nkv, page, d), 7.0, dtype=torch.float64)
+    want_v = want_k.clone()
+    for t, s_ in enumerate(slots.tolist()):
+        if s_ >= 0:
+            want_k[s_ // page, :, s_ % page, :] = kk[t]
+            want_v[s_ // page, :, s_ % page, :] = vv[t]
+    close(kp, want_k, dtype, "k pages", scale=2)
+    assert torch.equal(vp.double().cpu(), want_v), "values are copied bit for bit, and no other slot is touched"
+    untouched = want_k == 7.0
+    assert torch.equal(kp.double().cpu()[untouched], want_k[untouched])
+
+
 def paged_reference(q, keys, values, positions, rows, scale, window):
     """q [T, nq, d]; keys/values: per row a [len, nkv, d] tensor; float64."""
     out = torch.zeros(q.shape[0], q.shape[1] * q.shape[2], dtype=torch.float64)
