@@ -76,6 +76,7 @@ __global__ void silu_mul_kernel(const T* __restrict__ x, T* __restrict__ out, in
 // 16-byte loads and stores (Vec in common.cuh), the row kept in registers between the sum of squares and the scaling.
 // Used when the row length is a multiple of the vector and short enough for kMaxVec vectors a thread.
 constexpr int kMaxVec = 4;
+constexpr int kNormWideRows = 1024;  // from this many rows on a bfloat16 norm gives a thread four vectors
 
 // N consecutive weights starting at element i (a multiple of N; the vector is then 8-byte aligned at least).
 template <int N>
@@ -195,6 +196,9 @@ static int launch_norm(const void* x, void* residual, const void* w, void* out, 
       const int nvec = hidden / vec;
       int threads = ((nvec + 31) / 32) * 32;
       if (threads > 512) threads = 512;
+      // many rows of bfloat16: four vectors a thread, so that a block waits less at its reduction and more rows are in
+      // flight on an SM (float32 keeps one order of summation whatever the number of rows: its bits do not depend on the batch)
+      if (dtype == ROOST_BF16 && n_out >= kNormWideRows && nvec >= 4 * 32) threads = (((nvec + 3) / 4 + 31) / 32) * 32;
       if (nvec <= threads * kMaxVec) {
         ROOST_DISPATCH_DTYPE(dtype, T,
                              launch_kernel(rms_norm_vec_kernel<T, ADD>, dim3(n_out), dim3(threads), 0, (cudaStream_t)stream,
