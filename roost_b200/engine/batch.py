@@ -103,15 +103,18 @@ def attention_work(row_starts, row_counts, group: int, window: int | None, chunk
     return prefill, decode, merge, slots
 
 
-def attention_caps(num_tokens: int, num_rows: int, kv_cap: int, group: int, chunk: int, tile_rows: int = 64) -> tuple[int, int, int]:
+def attention_caps(num_tokens: int, num_rows: int, kv_cap: int, group: int, chunk: int, tile_rows: int = 64,
+                   short_rows: bool = True) -> tuple[int, int, int]:
     """Largest (prefill, decode, merge) item counts of a step of ``num_tokens`` tokens in ``num_rows`` rows whose
-    requests hold at most ``kv_cap`` keys. A step of one token a row has work of one kind only."""
+    requests hold at most ``kv_cap`` keys. A step of one token a row has work of one kind only; so has a step without
+    ``short_rows`` (rows of at most 16 tokens, the only ones that can go to the decode kernel)."""
     chunks = -(-kv_cap // chunk)
     if num_tokens == num_rows:
         if group > 16:
             return num_rows * (-(-group // tile_rows)), 0, 0
         return 0, num_rows * chunks, num_rows
-    return -(-num_tokens * group // tile_rows) + num_rows, num_rows * chunks, num_rows
+    prefill = -(-num_tokens * group // tile_rows) + num_rows
+    return (prefill, num_rows * chunks, num_rows) if short_rows else (prefill, 0, 0)
 
 
 def _pad4(a: list) -> list:

@@ -92,14 +92,14 @@ class StepGraph:
     unclaimed (kernels/README.md:240-250); here a replay runs the very kernels of the eager path with the same
     arguments, and the tests compare both with the plain implementation."""
 
-    def __init__(self, executor: "StepExecutor", num_tokens: int, num_rows: int, kv_cap: int, plan_keys: list):
+    def __init__(self, executor: "StepExecutor", num_tokens: int, num_rows: int, kv_cap: int, short_rows: bool, plan_keys: list):
         self.ex = weakref.proxy(executor)   # the executor owns its graphs; no reference cycle keeps its cache alive
-        self.num_tokens, self.num_rows, self.kv_cap = num_tokens, num_rows, kv_cap
+        self.num_tokens, self.num_rows, self.kv_cap, self.short_rows = num_tokens, num_rows, kv_cap, short_rows
         self.plan_keys = list(plan_keys)
         builder = executor.builder
         table_caps = builder.table_caps(num_tokens, num_rows, kv_cap)
         self.n_table = len(table_caps)
-        self.plan_caps = [attention_caps(num_tokens, num_rows, kv_cap, g, chunk, rows) for (g, _w, chunk, rows) in self.plan_keys]
+        self.plan_caps = [attention_caps(num_tokens, num_rows, kv_cap, g, chunk, rows, short_rows) for (g, _w, chunk, rows) in self.plan_keys]
         caps, fills = list(table_caps), [0] * len(table_caps)
         for pc, dc, mc in self.plan_caps:
             caps += [pc * 2, dc * 4, mc * 4]
@@ -108,6 +108,10 @@ class StepGraph:
         self.static = StaticTables(executor.rt.device, caps)
         self.graph = None
         self.out = None
+
+    @property
+    def key(self) -> tuple:
+        return (self.num_tokens, self.num_rows, self.kv_cap, self.short_rows)
 
     def _arrays(self, ht: HostTables) -> list:
         arrays = list(ht.arrays)
@@ -270,7 +274,9 @@ class StepExecutor:
             if wanted > rows_cap:
                 return None
         ht = self.builder.host_tables(padded_rows(rows, tokens_cap, rows_cap), self.model.spec.vocab)
-        key = (tokens_cap, rows_cap, graph_kv_cap(ht.max_kv_len))
+        # rows of at most 16 tokens may go to the decode attention; a step without any is captured without that kernel
+        short = decode or any(len(r[2]) <= 16 for r in rows)
+        key = (tokens_cap, rows_cap, graph_kv_cap(ht.max_kv_len), short)
         g = self._touch(key)
         if g is None:
             if not decode:
@@ -284,7 +290,7 @@ class StepExecutor:
             batch = self.builder.place(ht)
             self.last_upload_bytes = batch.host_buffer.numel() * batch.host_buffer.element_size()
             logits = self.model.forward(batch, self.storage)
-            g = StepGraph(self, tokens_cap, rows_cap, key[2], sorted(batch.attention_plans, key=repr))
+            g = StepGraph(self, tokens_cap, rows_cap, key[2], short, sorted(batch.attention_plans, key=repr))
             if g.fits(ht):
                 g.capture(ht)
                 if len(self._graphs) >= MAX_GRAPHS:
@@ -336,14 +342,14 @@ class StepExecutor:
         rows = [(self.cache.extend(rid, start + 1), start, [0], [0]) for rid, start in zip(request_ids, starts)]
         cap = graph_rows(len(rows))
         ht = self.builder.host_tables(padded_rows(rows, cap, cap), self.model.spec.vocab)
-        g = self._touch((cap, cap, graph_kv_cap(ht.max_kv_len)))
+        g = self._touch((cap, cap, graph_kv_cap(ht.max_kv_len), True))
         if g is None or not g.fits(ht):
             return None
         return PreparedDecode(list(request_ids), starts, g, g.static.stage(g._pending, g.fills))
 
     def matches_prepared(self, prep: PreparedDecode, entries: list[StepEntry]) -> bool:
         return (len(entries) == len(prep.request_ids)
-                and self._graphs.get((prep.graph.num_tokens, prep.graph.num_rows, prep.graph.kv_cap)) is prep.graph
+                and self._graphs.get(prep.graph.key) is prep.graph
                 and all(e.request_id == rid and len(e.tokens) == 1 and list(e.want) == [0] and (e.start is None or e.start == st)
                         and rid in self.cache and self.cache.get(rid).tokens == st
                         for e, rid, st in zip(entries, prep.request_ids, prep.starts)))
