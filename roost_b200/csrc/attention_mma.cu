@@ -690,11 +690,14 @@ __global__ void __launch_bounds__((kTmaConsumers + 1) * 32, 2)
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   pdl_launch_dependents(4);
-  pdl_wait(4);
   __syncthreads();  // the barriers are initialised
   const int group = q_heads / kv_heads;
   const long long total = (long long)items * kv_heads;
   volatile int* abortp = &abort_flag;
+  // What the kernel before this one on the stream writes (the step's queries, and the keys and values of the step's own
+  // tokens) is first touched after pdl_wait(). The step's tables were copied to the device before the step's first
+  // kernel, and pages that hold only earlier tokens were written by earlier steps: the producer reads the first and
+  // starts copying the second while the kernel before is still running.
 
   if (warp == NW) {
     // ---- producer: all lanes walk the loops (a lane holds one block-table entry of the current 32, as the pool row its
@@ -757,25 +760,14 @@ __global__ void __launch_bounds__((kTmaConsumers + 1) * 32, 2)
         round1();
         rounds = 1;
       }
-      if (lane == 0 && k >= 2) ok = mbar_wait_limited(desc_empty(k & 1), (uint32_t)((k >> 1) - 1) & 1u, abortp, 4, &g_attention_error);
-      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-      if (!ok) break;
-      // the chunk's Q tile, then the descriptor: the barrier completes when both are in shared memory
-      if (c.b >= 0) load_q_tile<D, 16, 32>(q_smem + (k & 1) * kQBytes, q, c.q_start, q_heads, group, c.kvh, 0, c.n * group, lane);
-      asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];\n" ::"r"(desc_full(k & 1)) : "memory");
-      if (lane == 0) {
-        desc[k & 1] = c;
-        mbar_arrive(desc_full(k & 1));  // releases the descriptor to the consumers
-      }
-      if (c.b < 0) break;
       const int p_first = (c.t0 * TK) >> page_shift, p_last = c.hi >> page_shift;
       auto row_of = [&](int p, int entry) {  // first pool row of page p of the request, given its block-table entry
         const bool visible = ((p + 1) << page_shift) > c.lo && (p << page_shift) <= c.hi;
         return ((visible && entry >= 0 ? entry : fallback) * kv_heads + c.kvh) << page_shift;
       };
       int batch0 = p_first;  // the page lane 0 holds
-      int cur = row_of(batch0 + lane, first_entry);
-      for (int i = 0; i < c.ntiles && ok; ++i, ++g) {
+      int cur = c.b >= 0 ? row_of(batch0 + lane, first_entry) : 0;
+      auto issue = [&](int i) {  // the copies of tile i of the chunk
         if (i == 2 && rounds == 1) {
           round2();
           rounds = 2;
@@ -806,7 +798,30 @@ __global__ void __launch_bounds__((kTmaConsumers + 1) * 32, 2)
           }
         }
         ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        ++g;
+      };
+      int issued = 0;
+      if (k == 0) {
+        // the CTA's first chunk, when it lies wholly before the step's own tokens: its first tiles are on their way
+        // before the kernel in front has finished
+        if (c.b >= 0 && c.hi < c.kv_len - c.n) {
+          const int early = c.ntiles < STAGES ? c.ntiles : STAGES;
+          for (; issued < early && ok; ++issued) issue(issued);
+        }
+        pdl_wait(4);
       }
+      if (lane == 0 && k >= 2) ok = mbar_wait_limited(desc_empty(k & 1), (uint32_t)((k >> 1) - 1) & 1u, abortp, 4, &g_attention_error);
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      if (!ok) break;
+      // the chunk's Q tile, then the descriptor: the barrier completes when both are in shared memory
+      if (c.b >= 0) load_q_tile<D, 16, 32>(q_smem + (k & 1) * kQBytes, q, c.q_start, q_heads, group, c.kvh, 0, c.n * group, lane);
+      asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];\n" ::"r"(desc_full(k & 1)) : "memory");
+      if (lane == 0) {
+        desc[k & 1] = c;
+        mbar_arrive(desc_full(k & 1));  // releases the descriptor to the consumers
+      }
+      if (c.b < 0) break;
+      for (int i = issued; i < c.ntiles && ok; ++i) issue(i);
       if (rounds < 2) round2();
       if (rounds < 3) round3();
     }
@@ -818,6 +833,7 @@ __global__ void __launch_bounds__((kTmaConsumers + 1) * 32, 2)
   }
 
   // ---- consumers
+  pdl_wait(4);
   bool ok = true;
   int g0 = 0;  // tiles of the chunks before this one
   for (int k = 0; ok; ++k) {
