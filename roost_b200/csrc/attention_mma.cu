@@ -956,9 +956,9 @@ template <int D>
 __global__ void attention_merge_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                        const int4* __restrict__ merge_work, int q_heads, int kv_heads) {
   pdl_launch_dependents(5);
-  pdl_wait(5);
-  const int4 w = merge_work[blockIdx.x];
+  const int4 w = merge_work[blockIdx.x];  // the step's work lists are on the device before the step's first kernel runs
   const int b = w.x, slot0 = w.y, chunks = w.z & 0xffffff, rows_total = w.z >> 24, q_start = w.w;
+  pdl_wait(5);
   if (b < 0) return;  // padding of a fixed-size work list
   const int kvh = blockIdx.y;
   const int group = q_heads / kv_heads;

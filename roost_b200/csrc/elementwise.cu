@@ -100,16 +100,27 @@ __device__ __forceinline__ void load_w_vec(const void* w, int i, int wdtype, flo
   }
 }
 
-template <typename T, bool ADD>
+// EARLY_W (steps of few rows, where the kernel's latency is its cost): the weights are in registers before the wait for
+// the kernel in front; otherwise they are read when they are used, which keeps the registers for more rows in flight.
+template <typename T, bool ADD, bool EARLY_W>
 __global__ void rms_norm_vec_kernel(const T* __restrict__ x, T* residual, const void* __restrict__ w, T* __restrict__ out,
                                     const int32_t* __restrict__ rows, int hidden, float eps, int wdtype) {
   constexpr int N = Vec<T>::N;
   __shared__ float scratch[32];
   pdl_launch_dependents(1);
-  pdl_wait(1);
+  // the weights and the list of rows do not come from the kernel in front: they are read while it finishes
   const int i_out = blockIdx.x;
   const size_t r = rows ? (size_t)rows[i_out] : (size_t)i_out;
   const int nvec = hidden / N;
+  float wv[EARLY_W ? kMaxVec : 1][N];
+  if constexpr (EARLY_W) {
+#pragma unroll
+    for (int k = 0; k < kMaxVec; ++k) {
+      const int vi = threadIdx.x + k * blockDim.x;
+      if (vi < nvec) load_w_vec<N>(w, vi * N, wdtype, wv[k]);
+    }
+  }
+  pdl_wait(1);
   float v[kMaxVec][N];
   float ss = 0.f;
 #pragma unroll
@@ -134,10 +145,10 @@ __global__ void rms_norm_vec_kernel(const T* __restrict__ x, T* residual, const 
   for (int k = 0; k < kMaxVec; ++k) {
     const int vi = threadIdx.x + k * blockDim.x;
     if (vi < nvec) {
-      float o[N], wv[N];
-      load_w_vec<N>(w, vi * N, wdtype, wv);
+      float o[N];
+      if constexpr (!EARLY_W) load_w_vec<N>(w, vi * N, wdtype, wv[0]);
 #pragma unroll
-      for (int e = 0; e < N; ++e) o[e] = v[k][e] * inv * wv[e];
+      for (int e = 0; e < N; ++e) o[e] = v[k][e] * inv * wv[EARLY_W ? k : 0][e];
       Vec<T>::store(out + (size_t)i_out * hidden + (size_t)vi * N, o);
     }
   }
@@ -200,9 +211,11 @@ static int launch_norm(const void* x, void* residual, const void* w, void* out, 
       // flight on an SM (float32 keeps one order of summation whatever the number of rows: its bits do not depend on the batch)
       if (dtype == ROOST_BF16 && n_out >= kNormWideRows && nvec >= 4 * 32) threads = (((nvec + 3) / 4 + 31) / 32) * 32;
       if (nvec <= threads * kMaxVec) {
-        ROOST_DISPATCH_DTYPE(dtype, T,
-                             launch_kernel(rms_norm_vec_kernel<T, ADD>, dim3(n_out), dim3(threads), 0, (cudaStream_t)stream,
-                                           (const T*)x, (T*)residual, w, (T*)out, rows, hidden, eps, wdtype));
+        ROOST_DISPATCH_DTYPE(dtype, T, {
+          auto kernel = n_out <= 64 ? rms_norm_vec_kernel<T, ADD, true> : rms_norm_vec_kernel<T, ADD, false>;
+          launch_kernel(kernel, dim3(n_out), dim3(threads), 0, (cudaStream_t)stream, (const T*)x, (T*)residual, w, (T*)out, rows, hidden, eps,
+                        wdtype);
+        });
         return check_launch("rms_norm");
       }
     }
