@@ -222,10 +222,10 @@ def timed_e2e(model, batch: int, context: int, steps: int, warmup: int):
     while any(s.computed < s.prompt_len for s in engine.scheduler.sequences()) or \
             any(s.generated == 0 for s in engine.scheduler.sequences()):
         engine.step()
-    # The prefill draws about 750 W, and decode steps after it run up to 3 % slower for some seconds, the SM and memory
-    # clocks reading the same all the while (measured through this entry point: 4.78 ms a step right after the
-    # prefill, 4.72 ms a second later, 4.62 ms ten seconds later). The device-timed figure above is taken with no
-    # prefill before it, so this one lets the device settle before its warm-up steps too.
+    # After some seconds of load (always after this prefill, at about 750 W) the device runs the same decode step about
+    # 3 % slower (4.68 against 4.55 ms), the SM and memory clocks reading the same; some seconds of idling bring the
+    # faster state back. The device-timed figure above is taken at the start of the process, so this one lets the
+    # device idle before its warm-up steps too.
     torch.cuda.synchronize()
     time.sleep(E2E_SETTLE_S)
     for _ in range(warmup - 1):
