@@ -82,7 +82,7 @@ def attention_work(row_starts, row_counts, group: int, window: int | None, chunk
         rows, kv_len = n * group, start + n
         first_token, token = token, token + n
         if start < 0:
-            continue   # a padding row (see PAD_ROW): no keys, no work
+            continue   # a padding row (see pad_row): no keys, no work
         if rows <= 16:
             lo = max(0, start - window + 1) if window else 0
             first = (lo // chunk) * chunk
