@@ -67,8 +67,8 @@ class Runtime:
 class Part:
     spec = None
     # False for a part whose call reads device values on the host or launches a number of kernels that depends on the
-    # data (routing written in Python, say): a model with such a part runs its decode steps eagerly instead of
-    # replaying a captured CUDA graph. A class that does not derive from Part may set the attribute all the same.
+    # data (routing written in Python, say): a model with such a part runs its steps eagerly instead of
+    # replaying captured CUDA graphs. A class that does not derive from Part may set the attribute all the same.
     capturable = True
 
     @classmethod
@@ -96,7 +96,9 @@ class Mixer(Part):
     def __call__(self, x: torch.Tensor, batch, cache, write_cache: bool = True) -> torch.Tensor:
         """x: [T, hidden] normed input of this step's tokens. ``batch`` is the step's ``StepBatch``; ``cache``
         is this run's view of its cache group (None when ``cache_need`` is None). With ``write_cache`` False
-        the run reads another run's cache and must not write it."""
+        the run reads another run's cache and must not write it. In a captured step the batch may end in padding
+        rows: tokens at position -1 of a row that holds no keys (``kv_lens`` 0, an empty page range, slot -1); nothing is
+        written to the cache for them and nobody reads their output."""
         raise NotImplementedError
 
 
