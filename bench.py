@@ -350,6 +350,7 @@ def main() -> int:
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true")
+    ap.add_argument("--point-batches", default="1,64", help="batch sizes of the extra decode points (the 32B configuration names 1, 8 and 32)")
     ap.add_argument("--skip-e2e", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -373,8 +374,8 @@ def main() -> int:
     pre_flops = prefill_flops(cfg, args.prefill_tokens)
     points = {}
     if not args.skip_points:
-        for name, b in (("decode_b1", 1), ("decode_b64", 64)):
-            points[name] = round(timed_decode(model, b, args.context, max(8, args.steps // 2), warmup)[0], 1)
+        for b in [int(x) for x in args.point_batches.split(",") if x.strip()]:
+            points[f"decode_b{b}"] = round(timed_decode(model, b, args.context, max(8, args.steps // 2), warmup)[0], 1)
     e2e = None
     if not args.skip_e2e:
         v, bi, bo = timed_e2e(model, args.batch, args.context, args.steps, warmup)
