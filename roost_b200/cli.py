@@ -14,6 +14,8 @@ and exits with 2.
                    [--top-p P] [--top-k K] [--min-p P] [--seed S] [--stop-ids a,b] [--ignore-eos] [engine options]
     roost chat --model DIR [--tokenizer tokenizer.json] [--template TEXT] [--max-output-tokens N] [sampling options as
                for generate] [engine options]                       a console: /reset clears the conversation, /exit quits
+    roost bench --model DIR [--batch N] [--prompt-tokens P] [--new-tokens K] [--seed S] [engine options]
+                                                      prefill and decode tokens a second of this model, one JSON line
     roost random-weights --config config.json --out DIR [--seed S] [--std X] [--norm-std X]
     roost replay --model DIR --dtype bfloat16|float32 --out DIR --max-tokens N      (bin/trace_run)
     roost doctor [--model DIR] [--kernels DIR] [--no-gpu] [--min-free-memory-gib N]
@@ -35,6 +37,7 @@ _COMMANDS = {
                                    "--top-k", "--min-p", "--seed", "--stop-ids"}, {"--ignore-eos"}),
     "chat": (_ENGINE_VALUED | {"--model", "--tokenizer", "--template", "--max-output-tokens", "--temperature", "--top-p", "--top-k",
                                "--min-p", "--seed", "--stop-ids"}, {"--ignore-eos"}),
+    "bench": (_ENGINE_VALUED | {"--model", "--batch", "--prompt-tokens", "--new-tokens", "--seed"}, set()),
     "random-weights": ({"--config", "--out", "--seed", "--std", "--norm-std"}, set()),
     "replay": ({"--model", "--dtype", "--out", "--max-tokens", "--page-size"}, set()),
     "doctor": ({"--model", "--kernels", "--min-free-memory-gib"}, {"--no-gpu"}),
@@ -223,6 +226,56 @@ def cmd_chat(opts, lines=None, out=None) -> int:
         history += turn + reply
 
 
+def cmd_bench(opts) -> int:
+    """Times this model through the entry point: ``--batch`` requests of ``--prompt-tokens`` seeded random tokens each
+    are prefilled (under the step's token budget) and then decode ``--new-tokens`` greedy tokens each. The first pass
+    warms up (library handles, captured steps); the second is timed by wall clock with the device drained at both ends."""
+    import random
+    import time
+    model = _need(opts, "--model")
+    dtype = opts.get("--dtype", "bfloat16")
+    if dtype not in ("bfloat16", "float32"):
+        raise UsageError("--dtype is bfloat16 or float32")
+    batch, prompt_tokens, new_tokens = _int(opts, "--batch", 8), _int(opts, "--prompt-tokens", 512), _int(opts, "--new-tokens", 64)
+    if min(batch, prompt_tokens, new_tokens) <= 0:
+        raise UsageError("--batch, --prompt-tokens and --new-tokens must be positive")
+    engine_opts = dict(page_size=_int(opts, "--page-size", 16), attention_blocks=_int(opts, "--attention-blocks"),
+                       max_sequences=_int(opts, "--max-sequences", max(batch, 1)), max_tokens=_int(opts, "--max-tokens", 2048),
+                       max_chunk_tokens=_int(opts, "--max-chunk-tokens"))
+    seed = _int(opts, "--seed", 0)
+    _apply_common(opts)
+    import torch
+
+    from .engine.engine import GenerationOptions, RoostEngine
+    engine = RoostEngine(model, dtype=dtype, **engine_opts)
+    rng = random.Random(seed)
+    vocab = engine.model.spec.vocab
+    prompts = [[rng.randrange(vocab) for _ in range(prompt_tokens)] for _ in range(batch)]
+    sampling = GenerationOptions(max_output_tokens=new_tokens, ignore_eos=True).sampling()
+    result = {}
+    for timed in (False, True):
+        for p in prompts:
+            engine.add_request(p, sampling)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        while any(s.generated == 0 for s in engine.scheduler.sequences()):     # until every request has its first token
+            engine.step()
+        torch.cuda.synchronize()
+        t1 = time.perf_counter()
+        produced = 0
+        while engine.has_unfinished():
+            produced += sum(1 for e in engine.step() if e.token is not None)
+        torch.cuda.synchronize()
+        t2 = time.perf_counter()
+        if timed:
+            result = {"model": str(model), "dtype": dtype, "batch": batch, "prompt_tokens": prompt_tokens, "new_tokens": new_tokens,
+                      "prefill_tokens_per_s": round(batch * prompt_tokens / (t1 - t0), 1), "prefill_s": round(t1 - t0, 4),
+                      "decode_tokens_per_s": round(produced / (t2 - t1), 1) if t2 > t1 and produced else None,
+                      "decode_ms_per_step": round((t2 - t1) / max(new_tokens - 1, 1) * 1e3, 3), **engine.stats()}
+    print(json.dumps(result))
+    return 0
+
+
 def cmd_random_weights(opts) -> int:
     from .weights.random_init import write_random_model
     with open(_need(opts, "--config")) as f:
@@ -304,7 +357,7 @@ def main(argv=None) -> int:
     argv = list(sys.argv[1:] if argv is None else argv)
     try:
         command, opts = parse(argv)
-        return {"generate": cmd_generate, "chat": cmd_chat, "random-weights": cmd_random_weights, "replay": cmd_replay, "doctor": cmd_doctor}[command](opts)
+        return {"generate": cmd_generate, "chat": cmd_chat, "bench": cmd_bench, "random-weights": cmd_random_weights, "replay": cmd_replay, "doctor": cmd_doctor}[command](opts)
     except UsageError as e:
         print(f"roost: {e}\n\nusage:\n{USAGE}", file=sys.stderr)
         return 2

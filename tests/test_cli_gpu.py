@@ -31,6 +31,10 @@ def test_generate_doctor_and_usage_errors(tiny_model_dirs, tmp_path):
     assert r.returncode == 0 and len(r.stdout.strip().splitlines()) == 2
     r = roost("doctor", "--model", str(model_dir))
     assert r.returncode == 0 and "ok   weights" in r.stdout and "ok   gpu" in r.stdout
+    r = roost("bench", "--model", str(model_dir), "--batch", "3", "--prompt-tokens", "20", "--new-tokens", "5", "--attention-blocks", "16")
+    assert r.returncode == 0, r.stderr
+    line = json.loads(r.stdout.strip().splitlines()[-1])
+    assert line["batch"] == 3 and line["prefill_tokens_per_s"] > 0 and line["decode_tokens_per_s"] > 0 and line["preemptions"] == 0
     r = roost("doctor", "--model", str(tmp_path))
     assert r.returncode == 1 and "FAIL" in r.stdout
     for bad in (["generate", "--model", "x", "--bogus", "1"], ["generate", "--model"], ["generate", "--model", "a", "--model", "b"],
