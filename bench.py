@@ -328,7 +328,7 @@ def serving_main(args) -> int:
 
 def reference_arm() -> int:
     print(json.dumps({"impl": "reference", "unavailable": "starlinghq/roost is a C#/.NET 10 program with no Python package "
-                      "(pip install of /root/reference finds no setup.py or pyproject.toml) and no .NET SDK or runtime is on this image"}))
+                      "(pip install of the reference's source tree finds no setup.py or pyproject.toml) and no .NET SDK or runtime is on this image"}))
     return 0
 
 

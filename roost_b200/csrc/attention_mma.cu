@@ -707,7 +707,7 @@ __global__ void __launch_bounds__((kTmaConsumers + 1) * 32, 2)
     const int page_shift = 31 - __clz(page_size);  // a power of two here
     bool ok = true;
     int g = 0;  // tiles issued so far
-    // the chunk being fetched: work item (round 1), row facts (round 2), chunk and block-table entries (round 3)
+    // the chunk being fetched: work item (first fetch), row facts (second), chunk and block-table entries (third)
     long long nf = blockIdx.x;
     int4 nw = make_int4(-1, 0, 0, 0);
     int nq0 = 0, nq1 = 0, nkvl = 0, ntbl = 0;
