@@ -951,6 +951,8 @@ __global__ void __launch_bounds__((kTmaConsumers + 1) * 32, 2)
   }
 }
 
+constexpr int kMergeAhead = 9;  // chunks whose partial results a merge thread loads in one go (a context of 4096 to 4608 keys)
+
 // merge_work[i] = (batch row, first partial slot, number of chunks | packed rows << 24, the row's first token)
 template <int D>
 __global__ void attention_merge_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict__ part_o, const float* __restrict__ part_ml,
@@ -965,6 +967,54 @@ __global__ void attention_merge_kernel(__nv_bfloat16* __restrict__ out, const fl
   const size_t stride = (size_t)kv_heads * 16;  // partial rows from one chunk's slot to the next
   for (int row = blockIdx.z; row < rows_total; row += gridDim.z) {
     const size_t pr0 = ((size_t)slot0 * kv_heads + kvh) * 16 + row;
+    const size_t out_at = ((size_t)(q_start + row / group) * q_heads + kvh * group + row % group) * D;
+    if (chunks <= kMergeAhead) {
+      // the usual case: every partial maximum, sum and output value this thread needs is loaded at once (one trip to
+      // memory instead of two), then combined in chunk order
+      float pm[kMergeAhead], pl[kMergeAhead], po[(D + 127) / 128][kMergeAhead];
+#pragma unroll
+      for (int c = 0; c < kMergeAhead; ++c) {
+        if (c < chunks) {
+          const size_t pr = pr0 + c * stride;
+          const float2 ml = *reinterpret_cast<const float2*>(part_ml + pr * 2);
+          pm[c] = ml.x;
+          pl[c] = ml.y;
+#pragma unroll
+          for (int j = 0; j < (D + 127) / 128; ++j) {
+            const int col = threadIdx.x + j * 128;
+            po[j][c] = col < D ? part_o[pr * D + col] : 0.f;
+          }
+        } else {
+          pm[c] = -INFINITY;
+          pl[c] = 0.f;
+#pragma unroll
+          for (int j = 0; j < (D + 127) / 128; ++j) po[j][c] = 0.f;
+        }
+      }
+      float m = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < kMergeAhead; ++c) m = fmaxf(m, pm[c]);
+      const float msafe = m == -INFINITY ? 0.f : m;
+      float l = 0.f, o[(D + 127) / 128];
+#pragma unroll
+      for (int j = 0; j < (D + 127) / 128; ++j) o[j] = 0.f;
+#pragma unroll
+      for (int c = 0; c < kMergeAhead; ++c) {  // chunk order: the sums do not depend on how the chunks were scheduled
+        if (c < chunks) {
+          const float f = exp2f(pm[c] - msafe);
+          l += pl[c] * f;
+#pragma unroll
+          for (int j = 0; j < (D + 127) / 128; ++j) o[j] += po[j][c] * f;
+        }
+      }
+      const float inv = l > 0.f ? 1.0f / l : 0.f;
+#pragma unroll
+      for (int j = 0; j < (D + 127) / 128; ++j) {
+        const int col = threadIdx.x + j * 128;
+        if (col < D) out[out_at + col] = __float2bfloat16_rn(o[j] * inv);
+      }
+      continue;
+    }
     float m = -INFINITY;
 #pragma unroll 8
     for (int c = 0; c < chunks; ++c) m = fmaxf(m, part_ml[(pr0 + c * stride) * 2]);
@@ -979,7 +1029,7 @@ __global__ void attention_merge_kernel(__nv_bfloat16* __restrict__ out, const fl
         o += part_o[pr * D + col] * f;
       }
       const float inv = l > 0.f ? 1.0f / l : 0.f;
-      out[((size_t)(q_start + row / group) * q_heads + kvh * group + row % group) * D + col] = __float2bfloat16_rn(o * inv);
+      out[out_at + col] = __float2bfloat16_rn(o * inv);
     }
   }
 }
