@@ -17,7 +17,7 @@
 extern "C" {
 #endif
 
-#define ROOST_ABI_VERSION 3
+#define ROOST_ABI_VERSION 4
 
 #define ROOST_OK 0
 #define ROOST_ERR_INVALID 1      /* an argument is out of range or inconsistent; nothing was launched */
@@ -58,12 +58,19 @@ int roost_silu_mul(const void* x, void* out, int tokens, int inter, int block, i
  * = no rotation), then q to q_out[t, h, :], k and v into their page slot:
  * pool[(page * kv_heads + h) * page_size + offset][:] with slot = page * page_size + offset from slot_mapping
  * (a negative slot is skipped). qkv rows hold [q heads | k heads | v heads] with row stride qkv_stride
- * elements; with write_kv 0 only the q part is read. */
+ * elements; with write_kv 0 only the q part is read. cos_sin: null, or the table roost_rope_table made for these
+ * positions and this inv_freq (tokens x rotary_dim/2 pairs). */
 int roost_qk_norm_rope_cache(const void* qkv, int64_t qkv_stride, void* q_out, void* k_pool, void* v_pool,
                              const void* q_w, const void* k_w, const double* inv_freq, const int32_t* positions,
-                             const int32_t* slot_mapping, int tokens, int q_heads, int kv_heads, int head_dim,
-                             int rotary_dim, float eps, int page_size, int64_t pool_pages, int write_kv, int dtype,
-                             int wdtype, roost_stream_t stream);
+                             const int32_t* slot_mapping, const float* cos_sin, int tokens, int q_heads, int kv_heads,
+                             int head_dim, int rotary_dim, float eps, int page_size, int64_t pool_pages, int write_kv,
+                             int dtype, int wdtype, roost_stream_t stream);
+
+/* The cosines and sines of a step's rotations: cos_sin[(t * half + i) * 2 + {0, 1}] = (cos, sin)(positions[t] * inv_freq[i])
+ * for i < half, the angle formed in 64-bit and reduced to [-pi, pi] before the 32-bit sincosf. They depend on the
+ * positions only, so a step computes them once and hands them to roost_qk_norm_rope_cache of every layer (its cos_sin
+ * argument; null there computes the same values in place). */
+int roost_rope_table(const int32_t* positions, const double* inv_freq, int tokens, int half, float* cos_sin, roost_stream_t stream);
 
 /* Causal grouped-query attention over a paged cache, one query token per block and key/value head; 32-bit
  * arithmetic throughout. Token t belongs to batch row token_row[t] and sits at absolute position

@@ -34,8 +34,8 @@ __global__ void qk_norm_rope_cache_kernel(const T* __restrict__ qkv, int64_t qkv
                                           T* __restrict__ k_pool, T* __restrict__ v_pool, const void* __restrict__ q_w,
                                           const void* __restrict__ k_w, const double* __restrict__ inv_freq,
                                           const int32_t* __restrict__ positions, const int32_t* __restrict__ slot_mapping,
-                                          int q_heads, int kv_heads, int head_dim, int rotary_dim, float eps, int page_size,
-                                          int64_t pool_pages, int slots_per_token, int wdtype, bool vector_ok) {
+                                          const float2* __restrict__ step_table, int q_heads, int kv_heads, int head_dim, int rotary_dim,
+                                          float eps, int page_size, int64_t pool_pages, int slots_per_token, int wdtype, bool vector_ok) {
   extern __shared__ float2 cos_sin[];  // [rotary_dim / 2]
   const int lane = threadIdx.x & 31;
   const int warps = blockDim.x >> 5;
@@ -44,8 +44,9 @@ __global__ void qk_norm_rope_cache_kernel(const T* __restrict__ qkv, int64_t qkv
   const size_t t = blockIdx.x;
   const T* row = qkv + t * qkv_stride;
   const int half = rotary_dim / 2;
-  const double pos = half > 0 ? (double)positions[t] : 0.0;
-  auto rotation = [&](int i) {  // (cos, sin) of the pair i
+  const double pos = half > 0 && step_table == nullptr ? (double)positions[t] : 0.0;
+  auto rotation = [&](int i) {  // (cos, sin) of the pair i: from the step's table, or computed here
+    if (step_table != nullptr) return step_table[t * half + i];
     double ang = pos * inv_freq[i];
     ang -= 6.283185307179586476925286766559 * rint(ang * 0.15915494309189533576888376337251);
     float sn, cs;
@@ -156,8 +157,9 @@ template <int D>
 __global__ void __launch_bounds__(256, 4) qk_norm_rope_cache_vec_kernel(
     const __nv_bfloat16* __restrict__ qkv, int64_t qkv_stride, __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_pool,
     __nv_bfloat16* __restrict__ v_pool, const void* __restrict__ q_w, const void* __restrict__ k_w, const double* __restrict__ inv_freq,
-    const int32_t* __restrict__ positions, const int32_t* __restrict__ slot_mapping, int tokens, int tokens_per_block, int q_heads,
-    int kv_heads, float eps, int page_size, int page_shift, int64_t pool_pages, int slots_per_token, int wdtype) {
+    const int32_t* __restrict__ positions, const int32_t* __restrict__ slot_mapping, const float2* __restrict__ step_table, int tokens,
+    int tokens_per_block, int q_heads, int kv_heads, float eps, int page_size, int page_shift, int64_t pool_pages, int slots_per_token,
+    int wdtype) {
   constexpr int kLanes = D / 8;          // lanes of a head slot
   constexpr int kSlots = 32 / kLanes;    // head slots of a warp's pass
   constexpr int kHalf = D / 2;
@@ -174,13 +176,15 @@ __global__ void __launch_bounds__(256, 4) qk_norm_rope_cache_vec_kernel(
     wk_hi[e] = k_w ? load_w(k_w, kHalf + 4 * c + e, wdtype) : 1.0f;
   }
   const bool normed = q_w != nullptr;
-  const double freq = (int)threadIdx.x < kHalf ? inv_freq[threadIdx.x] : 0.0;
+  const double freq = (int)threadIdx.x < kHalf && step_table == nullptr ? inv_freq[threadIdx.x] : 0.0;
   pdl_launch_dependents(3);
   pdl_wait(3);
   const int t0 = blockIdx.x * tokens_per_block;
   const int t1 = min(tokens, t0 + tokens_per_block);
   auto table = [&](int t, int buf) {
-    if ((int)threadIdx.x < kHalf) {
+    if ((int)threadIdx.x < kHalf && step_table != nullptr) {
+      cos_sin[buf][threadIdx.x] = step_table[(size_t)t * kHalf + threadIdx.x];
+    } else if ((int)threadIdx.x < kHalf) {
       double ang = (double)positions[t] * freq;
       ang -= 6.283185307179586476925286766559 * rint(ang * 0.15915494309189533576888376337251);
       float sn, cs;
@@ -284,14 +288,15 @@ using namespace roost;
 
 extern "C" int roost_qk_norm_rope_cache(const void* qkv, int64_t qkv_stride, void* q_out, void* k_pool, void* v_pool,
                                         const void* q_w, const void* k_w, const double* inv_freq,
-                                        const int32_t* positions, const int32_t* slot_mapping, int tokens, int q_heads,
-                                        int kv_heads, int head_dim, int rotary_dim, float eps, int page_size,
+                                        const int32_t* positions, const int32_t* slot_mapping, const float* cos_sin, int tokens,
+                                        int q_heads, int kv_heads, int head_dim, int rotary_dim, float eps, int page_size,
                                         int64_t pool_pages, int write_kv, int dtype, int wdtype, roost_stream_t stream) {
   ROOST_REQUIRE(tokens >= 0 && q_heads > 0 && kv_heads >= 0 && head_dim > 0, "qk_norm_rope_cache: sizes must be positive");
   ROOST_REQUIRE(rotary_dim >= 0 && rotary_dim <= head_dim && rotary_dim % 2 == 0,
                 "qk_norm_rope_cache: rotary_dim must be even and at most head_dim");
   ROOST_REQUIRE(rotary_dim == 0 || inv_freq != nullptr, "qk_norm_rope_cache: inv_freq is null");
   ROOST_REQUIRE(rotary_dim == 0 || positions != nullptr, "qk_norm_rope_cache: positions is null");
+  ROOST_REQUIRE(cos_sin == nullptr || (uintptr_t)cos_sin % 16 == 0, "qk_norm_rope_cache: the table of cosines and sines must start on a 16-byte boundary");
   ROOST_REQUIRE((q_w == nullptr) == (k_w == nullptr) || !write_kv, "qk_norm_rope_cache: q and k norm weights come together");
   if (write_kv) {
     ROOST_REQUIRE(k_pool && v_pool && slot_mapping && page_size > 0 && pool_pages > 0 && kv_heads > 0,
@@ -320,8 +325,8 @@ extern "C" int roost_qk_norm_rope_cache(const void* qkv, int64_t qkv_stride, voi
       if (page_size == (1 << b)) page_shift = b;
     auto launch = [&](auto kernel) {
       launch_kernel(kernel, vgrid, dim3(256), 0, (cudaStream_t)stream, (const __nv_bfloat16*)qkv, qkv_stride, (__nv_bfloat16*)q_out,
-                    (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, q_w, k_w, inv_freq, positions, slot_mapping, tokens, per_block, q_heads,
-                    kv_heads, eps, page_size, page_shift, pool_pages, slots, wdtype);
+                    (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, q_w, k_w, inv_freq, positions, slot_mapping, (const float2*)cos_sin, tokens,
+                    per_block, q_heads, kv_heads, eps, page_size, page_shift, pool_pages, slots, wdtype);
     };
     if (head_dim == 64) launch(qk_norm_rope_cache_vec_kernel<64>);
     else if (head_dim == 128) launch(qk_norm_rope_cache_vec_kernel<128>);
@@ -331,10 +336,38 @@ extern "C" int roost_qk_norm_rope_cache(const void* qkv, int64_t qkv_stride, voi
   ROOST_DISPATCH_DTYPE(dtype, T, {
     auto kernel = many ? qk_norm_rope_cache_kernel<T, true> : qk_norm_rope_cache_kernel<T, false>;
     launch_kernel(kernel, grid, dim3(warps * 32), many ? table_bytes : 0, (cudaStream_t)stream, (const T*)qkv, qkv_stride, (T*)q_out,
-                  (T*)k_pool, (T*)v_pool, q_w, k_w, inv_freq, positions, slot_mapping, q_heads, kv_heads, head_dim, rotary_dim, eps,
-                  page_size, pool_pages, slots, wdtype, vector_ok);
+                  (T*)k_pool, (T*)v_pool, q_w, k_w, inv_freq, positions, slot_mapping, (const float2*)cos_sin, q_heads, kv_heads, head_dim,
+                  rotary_dim, eps, page_size, pool_pages, slots, wdtype, vector_ok);
   });
   return check_launch("qk_norm_rope_cache");
+}
+
+namespace roost {
+__global__ void rope_table_kernel(const int32_t* __restrict__ positions, const double* __restrict__ inv_freq, int tokens, int half,
+                                  float2* __restrict__ cos_sin) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int64_t n = (int64_t)tokens * half;
+  for (int64_t j = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; j < n; j += (int64_t)gridDim.x * blockDim.x) {
+    double ang = (double)positions[j / half] * inv_freq[j % half];
+    ang -= 6.283185307179586476925286766559 * rint(ang * 0.15915494309189533576888376337251);
+    float sn, cs;
+    sincosf((float)ang, &sn, &cs);
+    cos_sin[j] = make_float2(cs, sn);
+  }
+}
+}  // namespace roost
+
+extern "C" int roost_rope_table(const int32_t* positions, const double* inv_freq, int tokens, int half, float* cos_sin,
+                                roost_stream_t stream) {
+  ROOST_REQUIRE(tokens >= 0 && half > 0, "rope_table: tokens and half must be positive");
+  ROOST_REQUIRE(positions && inv_freq && cos_sin, "rope_table: positions, inv_freq and the table are needed");
+  if (tokens == 0) return ROOST_OK;
+  const int64_t n = (int64_t)tokens * half;
+  const int blocks = (int)((n + 127) / 128 > 4096 ? 4096 : (n + 127) / 128);
+  launch_kernel(rope_table_kernel, dim3(blocks), dim3(128), 0, (cudaStream_t)stream, positions, inv_freq, tokens, half,
+                reinterpret_cast<float2*>(cos_sin));
+  return check_launch("rope_table");
 }
 
 ROOST_TRACE_TU(rope_cache)

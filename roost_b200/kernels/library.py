@@ -13,7 +13,7 @@ import torch
 
 from . import build
 
-ABI_VERSION = 3
+ABI_VERSION = 4
 F32, BF16 = 0, 1
 
 
@@ -61,8 +61,9 @@ _SIGNATURES = {
     "roost_silu_mul": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "roost_gemm_tcgen05_swiglu": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_void_p],
     "roost_qk_norm_rope_cache": [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                                 c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int64, c_int, c_int, c_int,
+                                 c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int64, c_int, c_int, c_int,
                                  c_void_p],
+    "roost_rope_table": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p],
     "roost_paged_attention_generic": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                       c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p],
     "roost_attention_mma_supported": [c_int],
@@ -169,10 +170,19 @@ class KernelLibrary:
         self._call("roost_gemm_tcgen05_swiglu", _ptr(a), _ptr(w), _ptr(out), M, N, K, a.stride(0), w.stride(0), out.stride(0), _stream())
         return out
 
+    def rope_table(self, positions: torch.Tensor, inv_freq: torch.Tensor) -> torch.Tensor:
+        """(cos, sin) of positions[t] * inv_freq[i] as float32 [T, half, 2]: a step computes it once for all its layers."""
+        _need(positions, "positions", torch.int32); _need(inv_freq, "inv_freq", torch.float64)
+        T, half = positions.numel(), inv_freq.numel()
+        out = torch.empty((T, half, 2), dtype=torch.float32, device=positions.device)
+        self._call("roost_rope_table", _ptr(positions), _ptr(inv_freq), T, half, _ptr(out), _stream())
+        return out
+
     def qk_norm_rope_cache(self, qkv, q_heads, kv_heads, head_dim, *, q_w, k_w, eps, inv_freq, rotary_dim, positions,
-                           k_pool=None, v_pool=None, slot_mapping=None, page_size=0, write_kv=True) -> torch.Tensor:
+                           k_pool=None, v_pool=None, slot_mapping=None, page_size=0, write_kv=True, cos_sin=None) -> torch.Tensor:
         """qkv: [T, (q_heads + 2 kv_heads) * head_dim] (or [T, q_heads * head_dim] with write_kv False). Returns
-        q: [T, q_heads, head_dim], normed and rotated; k and v go into the pools."""
+        q: [T, q_heads, head_dim], normed and rotated; k and v go into the pools. ``cos_sin``: the step's table from
+        ``rope_table`` for these positions and this ``inv_freq`` (else the kernel computes the same values itself)."""
         _need(qkv, "qkv")
         T = qkv.shape[0]
         width = (q_heads + (2 * kv_heads if write_kv else 0)) * head_dim
@@ -190,8 +200,14 @@ class KernelLibrary:
             _need(inv_freq, "inv_freq", torch.float64); _need(positions, "positions", torch.int32)
             if inv_freq.numel() != rotary_dim // 2:
                 raise KernelError("qk_norm_rope_cache: inv_freq must have rotary_dim / 2 entries")
+            if cos_sin is not None:
+                _need(cos_sin, "cos_sin", torch.float32)
+                if tuple(cos_sin.shape) != (T, rotary_dim // 2, 2):
+                    raise KernelError(f"qk_norm_rope_cache: the table is {tuple(cos_sin.shape)}; expected {(T, rotary_dim // 2, 2)}")
+        else:
+            cos_sin = None
         self._call("roost_qk_norm_rope_cache", _ptr(qkv), qkv.stride(0), _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(q_w),
-                   _ptr(k_w), _ptr(inv_freq), _ptr(positions), _ptr(slot_mapping), T, q_heads, kv_heads, head_dim,
+                   _ptr(k_w), _ptr(inv_freq), _ptr(positions), _ptr(slot_mapping), _ptr(cos_sin), T, q_heads, kv_heads, head_dim,
                    rotary_dim, eps, page_size, pages, 1 if write_kv else 0, dtype_code(qkv.dtype), wd, _stream())
         return q
 

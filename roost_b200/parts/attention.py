@@ -75,10 +75,11 @@ class PagedAttention(Mixer):
         eps = s.qk_norm.eps if s.qk_norm is not None else 1.0
         qw = self.q_norm.weight if self.q_norm is not None else None
         kw = self.k_norm.weight if self.k_norm is not None else None
+        table = batch.rotation_table(k, inv_freq) if rotary_dim else None
         if write_cache:
             qkv = self.qkv(x)
             q = k.qk_norm_rope_cache(qkv, s.num_heads, s.num_kv_heads, s.head_dim, q_w=qw, k_w=kw, eps=eps,
-                                     inv_freq=inv_freq, rotary_dim=rotary_dim, positions=batch.positions,
+                                     inv_freq=inv_freq, rotary_dim=rotary_dim, positions=batch.positions, cos_sin=table,
                                      k_pool=cache.k_pool, v_pool=cache.v_pool, slot_mapping=tables.slot_mapping,
                                      page_size=cache.page_size, write_kv=True)
         else:
@@ -86,7 +87,7 @@ class PagedAttention(Mixer):
                 self.q_only = Linear(self.rt, self.q_width, s.hidden)
                 self.q_only.load(self.qkv.weight[: self.q_width])
             q = k.qk_norm_rope_cache(self.q_only(x), s.num_heads, s.num_kv_heads, s.head_dim, q_w=qw, k_w=kw, eps=eps,
-                                     inv_freq=inv_freq, rotary_dim=rotary_dim, positions=batch.positions, write_kv=False)
+                                     inv_freq=inv_freq, rotary_dim=rotary_dim, positions=batch.positions, write_kv=False, cos_sin=table)
         o = self.attend(q, batch, cache, tables)
         return self.out(o)
 

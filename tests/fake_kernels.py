@@ -39,7 +39,7 @@ class FakeKernels:
         return (g / (1 + torch.exp(-g)) * u).to(x.dtype)
 
     def qk_norm_rope_cache(self, qkv, q_heads, kv_heads, head_dim, *, q_w, k_w, eps, inv_freq, rotary_dim, positions,
-                           k_pool=None, v_pool=None, slot_mapping=None, page_size=0, write_kv=True):
+                           k_pool=None, v_pool=None, slot_mapping=None, page_size=0, write_kv=True, cos_sin=None):
         T = qkv.shape[0]
         d = head_dim
         q = qkv[:, : q_heads * d].reshape(T, q_heads, d).float()

@@ -118,6 +118,10 @@ def test_qk_norm_rope_cache(kernels, dtype, nq, nkv, d, rot, page):
             want_v[s // page, :, s % page, :] = vv[t]
     close(kp, want_k, dtype, "k pages", scale=2)
     assert torch.equal(vp.double().cpu(), want_v), "values are copied bit for bit, and no other slot is touched"
+    kp2, vp2 = torch.full_like(kp, 7.0), torch.full_like(vp, 7.0)
+    q_t = kernels.qk_norm_rope_cache(qkv, nq, nkv, d, q_w=qw, k_w=kw, eps=eps, inv_freq=inv_freq, rotary_dim=rot, positions=positions,
+                                     k_pool=kp2, v_pool=vp2, slot_mapping=slots, page_size=page, cos_sin=kernels.rope_table(positions, inv_freq))
+    assert torch.equal(q_t, q) and torch.equal(kp2, kp) and torch.equal(vp2, vp), "the step's table gives the same bits"
     # q only (a run that reads another run's cache), no norm, no rotation
     q2 = kernels.qk_norm_rope_cache(qkv[:, : nq * d].contiguous(), nq, nkv, d, q_w=None, k_w=None, eps=eps, inv_freq=None, rotary_dim=0,
                                     positions=positions, write_kv=False)
@@ -168,6 +172,12 @@ def test_qk_norm_rope_cache_of_many_tokens(kernels, dtype, T, nq, nkv, d, page, 
     assert torch.equal(vp.double().cpu(), want_v), "values are copied bit for bit, and no other slot is touched"
     untouched = want_k == 7.0
     assert torch.equal(kp.double().cpu()[untouched], want_k[untouched])
+    # with the step's table of cosines and sines (computed once for all layers) the bits are the same
+    kp2, vp2 = torch.full_like(kp, 7.0), torch.full_like(vp, 7.0)
+    table = kernels.rope_table(positions.cuda(), inv_freq)
+    q2 = kernels.qk_norm_rope_cache(qkv, nq, nkv, d, q_w=qw, k_w=kw, eps=eps, inv_freq=inv_freq, rotary_dim=d, positions=positions.cuda(),
+                                    k_pool=kp2, v_pool=vp2, slot_mapping=slots.cuda(), page_size=page, cos_sin=table)
+    assert torch.equal(q2, q) and torch.equal(kp2, kp) and torch.equal(vp2, vp)
 
 
 def paged_reference(q, keys, values, positions, rows, scale, window):
