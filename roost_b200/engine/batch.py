@@ -138,6 +138,16 @@ def plan_attention(row_starts, row_counts, group: int, window: int | None, chunk
     return plan
 
 
+def graph_kv_cap(kv_len: int) -> int:
+    """The bound on the requests' lengths a captured decode step is made for: the next multiple of 1024 up to 8192
+    tokens, of 4096 up to 32768, of 16384 beyond. It sizes the step's page tables and attention work lists, whose unused
+    entries cost an upload of a few bytes each and nothing on the device."""
+    for limit, granule in ((8192, 1024), (32768, 4096)):
+        if kv_len <= limit:
+            return max(granule, -(-kv_len // granule) * granule)
+    return -(-kv_len // 16384) * 16384
+
+
 ROTATION_TABLE_MIN_TOKENS = 64   # from this many tokens on a step computes its cosines and sines once for all layers
 
 
@@ -158,6 +168,7 @@ class StepBatch:
     row_counts: list = field(default_factory=list)       # tokens of each row
     max_position: int = 0
     max_kv_len: int = 0
+    kv_cap: int = 0              # the bound on the requests' lengths a captured step of this size is made for
     all_single: bool = False     # every row brings exactly one token
     host_buffer: object = None   # the pinned staging buffer, kept until the step is done
     attention_plans: dict = field(default_factory=dict)   # (group size, window, chunk) -> AttentionPlan, made by the first mixer that asks
@@ -335,7 +346,7 @@ class BatchBuilder:
         return StepBatch(num_tokens=ht.num_tokens, num_rows=ht.num_rows, num_selected=ht.num_selected, ids=d_ids, positions=d_pos,
                          token_row=d_trow, q_indptr=d_qi, kv_lens=d_kvl, selected=d_sel, groups=groups, row_starts=ht.row_starts,
                          row_counts=ht.row_counts, max_position=ht.max_position, max_kv_len=ht.max_kv_len,
-                         all_single=all(n == 1 for n in ht.row_counts), host_buffer=host_buffer)
+                         kv_cap=graph_kv_cap(ht.max_kv_len), all_single=all(n == 1 for n in ht.row_counts), host_buffer=host_buffer)
 
     def build(self, rows: list[tuple], vocab: int) -> StepBatch:
         return self.place(self.host_tables(rows, vocab))

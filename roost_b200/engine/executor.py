@@ -19,7 +19,8 @@ import numpy as np
 
 from ..cache.manager import CacheManager, OutOfPages, build_groups
 from ..cache.storage import CacheStorage
-from .batch import AttentionPlan, BatchBuilder, HostTables, StaticTables, attention_caps, attention_work, padded_rows
+from .batch import (AttentionPlan, BatchBuilder, HostTables, StaticTables, attention_caps, attention_work, graph_kv_cap,
+                    padded_rows)
 from .model import Model
 
 MAX_GRAPHS = 64
@@ -49,16 +50,6 @@ def graph_rows(n: int) -> int:
             if n <= m:
                 return m
         b *= 2
-
-
-def graph_kv_cap(kv_len: int) -> int:
-    """The bound on the requests' lengths a captured decode step is made for: the next multiple of 1024 up to 8192
-    tokens, of 4096 up to 32768, of 16384 beyond. It sizes the step's page tables and attention work lists, whose unused
-    entries cost an upload of a few bytes each and nothing on the device."""
-    for limit, granule in ((8192, 1024), (32768, 4096)):
-        if kv_len <= limit:
-            return max(granule, -(-kv_len // granule) * granule)
-    return -(-kv_len // 16384) * 16384
 
 
 @dataclass

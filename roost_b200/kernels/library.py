@@ -109,7 +109,8 @@ class KernelLibrary:
             fn = getattr(self._lib, name)
             fn.argtypes = args
             fn.restype = c_int
-        self.decode_chunk = 512  # keys per CTA of the split decode attention; fixed, so results do not depend on the batch
+        self.decode_chunk = 512  # keys per work item of the split decode attention (see decode_chunk_for)
+        self._decode_ctas = 0
         self.launches = 0  # kernels launched through this handle (a host-side count of entry-point calls that launch)
 
     def _call(self, name: str, *args, launches: int = 1):
@@ -118,6 +119,17 @@ class KernelLibrary:
             msg = self._lib.roost_last_error().decode(errors="replace")
             raise KernelError(f"{name}: {msg} (status {status})")
         self.launches += launches
+
+    def decode_chunk_for(self, rows: int, kv_cap: int, kv_heads: int) -> int:
+        """Keys per work item of the split decode attention for a step of ``rows`` rows whose requests hold at most
+        ``kv_cap`` keys (the bound of the captured step, so that every replay of it agrees). The persistent decode
+        kernel runs two CTAs an SM; when ``decode_chunk`` keys an item give more items than CTAs but at most twice as
+        many, the second round would be half empty, and items of twice the keys run as one full round instead (batch 8
+        at 4096 keys: 4.42 against 4.51 ms a step). A row's bits then depend on the step's size class, within rounding."""
+        if not self._decode_ctas:
+            self._decode_ctas = 2 * torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+        items = rows * kv_heads * (-(-max(kv_cap, 1) // self.decode_chunk))
+        return 2 * self.decode_chunk if self._decode_ctas < items <= 2 * self._decode_ctas else self.decode_chunk
 
     # ------------------------------------------------------------------ ops
     def embedding(self, table: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:

@@ -98,7 +98,9 @@ class PagedAttention(Mixer):
         if q.dtype == torch.bfloat16 and getattr(k, "attention_mma_supported", lambda d: False)(s.head_dim):
             group = s.num_heads // s.num_kv_heads
             tile_rows = k.attention_prefill_tile_rows(s.num_heads, cache.k_pool, cache.v_pool, batch.num_tokens * group)
-            plan = batch.attention_plan(group, s.window, k.decode_chunk, tile_rows)
+            chunk_for = getattr(k, "decode_chunk_for", None)
+            chunk = chunk_for(batch.num_rows, batch.kv_cap, s.num_kv_heads) if chunk_for and batch.kv_cap else k.decode_chunk
+            plan = batch.attention_plan(group, s.window, chunk, tile_rows)
             return k.attention_mma(q, cache.k_pool, cache.v_pool, batch.q_indptr, batch.kv_lens, tables.kv_indptr,
                                    tables.kv_indices, plan, s.scale, s.window)
         return k.paged_attention_generic(q, cache.k_pool, cache.v_pool, batch.positions, batch.token_row,
