@@ -17,7 +17,7 @@
 extern "C" {
 #endif
 
-#define ROOST_ABI_VERSION 4
+#define ROOST_ABI_VERSION 5
 
 #define ROOST_OK 0
 #define ROOST_ERR_INVALID 1      /* an argument is out of range or inconsistent; nothing was launched */
@@ -178,6 +178,11 @@ int roost_gemm_stream_swiglu(const void* x, const void* w, void* out, int m, int
 
 /* ids[r] = index of the largest logit of row r, ties to the lowest index, NaN never chosen (-1 if none). */
 int roost_argmax(const float* logits, int64_t stride, int rows, int vocab, int32_t* ids, roost_stream_t stream);
+/* The same result with a row split over `splits` (1 to 32) blocks, for vocabularies that one SM reads too slowly.
+ * part_v, part_i: rows * splits entries of scratch; counters: rows words that are zero before the first call (the
+ * kernel leaves them zero). */
+int roost_argmax_split(const float* logits, int64_t stride, int rows, int vocab, int32_t* ids, int splits, float* part_v,
+                       int32_t* part_i, uint32_t* counters, roost_stream_t stream);
 
 /* Temperature / top-k / top-p / min-p sampling with a Philox4x32-10 draw per row; see sampling.cu.
  * workspace: rows * vocab floats. temperature <= 0 is greedy. */

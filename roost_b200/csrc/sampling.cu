@@ -126,6 +126,45 @@ __global__ void __launch_bounds__(kThreads) argmax_kernel(const float* __restric
   if (threadIdx.x == 0) ids[r] = best;
 }
 
+// A row of a large vocabulary split over several blocks, so that one SM's bandwidth does not bound it: a block finds the
+// best of its span and leaves it in part_v / part_i; the block that arrives last at the row's counter (after a fence)
+// combines the spans in index order, writes the row's id and sets the counter back to zero for the next call.
+__global__ void __launch_bounds__(kThreads) argmax_split_kernel(const float* __restrict__ logits, long long stride, int vocab,
+                                                               int* __restrict__ ids, float* part_v, int* part_i, unsigned* counters) {
+  __shared__ float sf[32];
+  __shared__ int si[32];
+  __shared__ int last;
+  const int r = blockIdx.x, s = blockIdx.y, splits = gridDim.y;
+  const int span = (((vocab + splits - 1) / splits) + 3) & ~3;
+  const int lo = min(vocab, s * span), hi = min(vocab, lo + span);
+  const int best = block_argmax(logits + (size_t)r * stride + lo, hi - lo, false, sf, si);
+  if (threadIdx.x == 0) {
+    part_v[r * splits + s] = sf[0];
+    part_i[r * splits + s] = best < 0 ? -1 : best + lo;
+    __threadfence();
+    last = atomicAdd(&counters[r], 1u) == (unsigned)(splits - 1);
+  }
+  __syncthreads();
+  if (!last || threadIdx.x >= 32) return;
+  __threadfence();
+  const int lane = threadIdx.x;
+  float bv = lane < splits ? __ldcg(part_v + r * splits + lane) : 0.f;
+  int bi = lane < splits ? __ldcg(part_i + r * splits + lane) : -1;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (!better(bv, bi, ov, oi)) {
+      bv = ov;
+      bi = oi;
+    }
+  }
+  if (lane == 0) {
+    ids[r] = bi;
+    counters[r] = 0u;
+  }
+}
+
 // A kept prefix of the order is (xb, c): every key > xb, plus the first c tokens (by index) whose key == xb.
 // Keys are the bit patterns of the probabilities; removed tokens hold -1 and are skipped.
 
@@ -368,6 +407,17 @@ __global__ void __launch_bounds__(kThreads)
 }  // namespace roost
 
 using namespace roost;
+
+extern "C" int roost_argmax_split(const float* logits, int64_t stride, int rows, int vocab, int32_t* ids, int splits, float* part_v,
+                                  int32_t* part_i, uint32_t* counters, roost_stream_t stream) {
+  ROOST_REQUIRE(rows >= 0 && vocab > 0 && stride >= vocab, "argmax: rows, vocab and stride must be consistent");
+  ROOST_REQUIRE(splits >= 1 && splits <= 32, "argmax: between 1 and 32 spans a row");
+  ROOST_REQUIRE(part_v && part_i && counters, "argmax: the workspace of the spans is missing");
+  if (rows == 0) return ROOST_OK;
+  if (rows > 65535 * 32) return fail(ROOST_ERR_UNSUPPORTED, "argmax: too many rows");
+  argmax_split_kernel<<<dim3(rows, splits), kThreads, 0, (cudaStream_t)stream>>>(logits, (long long)stride, vocab, ids, part_v, part_i, counters);
+  return check_launch("argmax");
+}
 
 extern "C" int roost_argmax(const float* logits, int64_t stride, int rows, int vocab, int32_t* ids, roost_stream_t stream) {
   ROOST_REQUIRE(rows >= 0 && vocab > 0 && stride >= vocab, "argmax: rows, vocab and stride must be consistent");

@@ -13,7 +13,7 @@ import torch
 
 from . import build
 
-ABI_VERSION = 4
+ABI_VERSION = 5
 F32, BF16 = 0, 1
 
 
@@ -91,6 +91,7 @@ _SIGNATURES = {
     "roost_gemm_stream_swiglu": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int, c_void_p, c_void_p,
                                  c_void_p],
     "roost_argmax": [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p],
+    "roost_argmax_split": [c_void_p, c_int64, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
     "roost_sample": [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                      c_void_p, c_void_p],
 }
@@ -396,6 +397,17 @@ class KernelLibrary:
         _need(logits, "logits", torch.float32)
         R, V = logits.shape
         ids = torch.empty((R,), dtype=torch.int32, device=logits.device)
+        splits = min(16, V // 8192)     # a block a span of 8192 logits or more, up to 16 blocks a row
+        if splits > 1:
+            ws = getattr(self, "_argmax_ws", None)
+            if ws is None or ws[2].numel() < R or ws[2].device != logits.device:
+                cap = max(64, R)
+                ws = self._argmax_ws = (torch.empty(cap * 16, dtype=torch.float32, device=logits.device),
+                                        torch.empty(cap * 16, dtype=torch.int32, device=logits.device),
+                                        torch.zeros(cap, dtype=torch.int32, device=logits.device))
+            self._call("roost_argmax_split", _ptr(logits), logits.stride(0), R, V, _ptr(ids), splits, _ptr(ws[0]), _ptr(ws[1]), _ptr(ws[2]),
+                       _stream())
+            return ids
         self._call("roost_argmax", _ptr(logits), logits.stride(0), R, V, _ptr(ids), _stream())
         return ids
 

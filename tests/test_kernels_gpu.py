@@ -284,6 +284,28 @@ def test_argmax_ties_and_nan(kernels):
     z[3, V - 1] = 60.0
     ids = kernels.argmax(z.cuda()).cpu().tolist()
     assert ids == [77, 6, -1, V - 1]
+    # a vocabulary large enough for a row to be split over sixteen blocks: ties across spans, maxima at span edges,
+    # a row of NaN, and the counters left clean for a second call with other values
+    V = 151936
+    span = (((V + 15) // 16) + 3) & ~3
+    for seed in (1, 2):
+        z = torch.randn(9, V, generator=torch.Generator().manual_seed(seed))
+        z[0, 77] = 50.0
+        z[0, 9 * span + 1] = 50.0      # the same value in a later span: the lower index wins
+        z[1, 5] = float("nan")
+        z[1, 3 * span] = 40.0          # first element of a span
+        z[2] = float("nan")
+        z[3, V - 1] = 60.0             # last element of the last span
+        z[4, span - 1] = 45.0          # last element of the first span
+        z[4, span] = 45.0
+        z[5, 12 * span + 7] = 33.0
+        want = []
+        for r in range(9):
+            row = z[r]
+            ok = ~torch.isnan(row)
+            want.append(int(torch.where(ok, row, torch.tensor(-float("inf"))).argmax()) if ok.any() else -1)
+        assert want[:6] == [77, 3 * span, -1, V - 1, span - 1, 12 * span + 7]
+        assert kernels.argmax(z.cuda()).cpu().tolist() == want
 
 
 @pytest.mark.parametrize("vocab", [387, 5000])
