@@ -7,7 +7,7 @@ no CUDA device is present, ``load()`` raises and nothing in the engine runs.
 from __future__ import annotations
 
 import ctypes
-from ctypes import c_char_p, c_double, c_float, c_int, c_int64, c_void_p
+from ctypes import c_char_p, c_float, c_int, c_int64, c_void_p
 
 import torch
 

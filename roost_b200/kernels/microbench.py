@@ -13,7 +13,6 @@ under ``profiles/`` were taken with (``--iters 2 --warmup 1`` under a profiler).
 from __future__ import annotations
 
 import argparse
-import math
 import sys
 
 

@@ -12,7 +12,7 @@ from __future__ import annotations
 import torch
 
 from ..config.spec import AttentionSpec
-from .base import MIXERS, NORMS, POSITIONS, CacheNeed, Mixer, ParamDecl, Runtime, register_mixer
+from .base import NORMS, POSITIONS, CacheNeed, Mixer, ParamDecl, Runtime, register_mixer
 from .linear import Linear
 
 
