@@ -31,7 +31,12 @@ typedef void* roost_stream_t;
 
 int roost_abi_version(void);
 /* Programmatic dependent launch for the library's kernels (off by default): a kernel may start its preamble, and the
- * weight-streaming product its first loads of weights, while the kernel before it on the stream is finishing. */
+ * weight-streaming product its first loads of weights, while the kernel before it on the stream is finishing.
+ * With it on, a kernel reads before it waits for the kernel in front: weights (norm weights, the products' weight
+ * matrices), index tables (the `rows` of the norms, the work lists of the attention kernels, q_indptr, kv_lens,
+ * kv_indptr, kv_indices) and pages of the cache that hold only tokens of earlier steps. A caller must therefore not
+ * have those written by the kernel launched directly before the call that reads them (a copy in between is enough);
+ * activations and the pages of the step's own tokens are read after the wait. */
 void roost_set_pdl(int on);
 /* Message of the last non-OK status on this thread. */
 const char* roost_last_error(void);
