@@ -16,7 +16,9 @@ and exits with 2.
                for generate] [engine options]                       a console: /reset clears the conversation, /exit quits
     roost bench --model DIR [--batch N] [--prompt-tokens P] [--new-tokens K] [--seed S] [engine options]
                                                       prefill and decode tokens a second of this model, one JSON line
-    roost random-weights --config config.json --out DIR [--seed S] [--std X] [--norm-std X]
+    roost random-weights --config config.json --out DIR [--seed S] [--std X] [--norm-std X] [--mode normal|reference]
+                                                      reference: the reference's own seeded generator (its tiny model's seed
+                                                      unless --seed is given), so that its pinned tokens can be reproduced
     roost replay --model DIR --dtype bfloat16|float32 --out DIR --max-tokens N      (bin/trace_run)
     roost doctor [--model DIR] [--kernels DIR] [--no-gpu] [--min-free-memory-gib N]
   engine options: [--dtype bfloat16|float32] [--device N] [--kernels DIR] [--page-size N] [--attention-blocks N]
@@ -38,7 +40,7 @@ _COMMANDS = {
     "chat": (_ENGINE_VALUED | {"--model", "--tokenizer", "--template", "--max-output-tokens", "--temperature", "--top-p", "--top-k",
                                "--min-p", "--seed", "--stop-ids"}, {"--ignore-eos"}),
     "bench": (_ENGINE_VALUED | {"--model", "--batch", "--prompt-tokens", "--new-tokens", "--seed"}, set()),
-    "random-weights": ({"--config", "--out", "--seed", "--std", "--norm-std"}, set()),
+    "random-weights": ({"--config", "--out", "--seed", "--std", "--norm-std", "--mode"}, set()),
     "replay": ({"--model", "--dtype", "--out", "--max-tokens", "--page-size"}, set()),
     "doctor": ({"--model", "--kernels", "--min-free-memory-gib"}, {"--no-gpu"}),
 }
@@ -277,10 +279,16 @@ def cmd_bench(opts) -> int:
 
 
 def cmd_random_weights(opts) -> int:
-    from .weights.random_init import write_random_model
+    from .weights.random_init import REFERENCE_TINY_SEED, write_random_model
+    mode = opts.get("--mode", "normal")
+    if mode not in ("normal", "reference"):
+        raise UsageError("--mode is normal or reference")
+    if mode == "reference" and ("--std" in opts or "--norm-std" in opts):
+        raise UsageError("--std and --norm-std do not apply to --mode reference: the reference's generator fixes the amplitudes")
     with open(_need(opts, "--config")) as f:
         config = json.load(f)
-    out = write_random_model(_need(opts, "--out"), config, _int(opts, "--seed", 0), _float(opts, "--std", 0.02), _float(opts, "--norm-std", 0.0))
+    seed = _int(opts, "--seed", REFERENCE_TINY_SEED if mode == "reference" else 0)
+    out = write_random_model(_need(opts, "--out"), config, seed, _float(opts, "--std", 0.02), _float(opts, "--norm-std", 0.0), mode=mode)
     print(out)
     return 0
 

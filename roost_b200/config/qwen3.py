@@ -175,6 +175,37 @@ class Qwen3Config:
             d["eos_token_id"] = list(self.eos_token_ids) if len(self.eos_token_ids) > 1 else self.eos_token_ids[0]
         return d
 
+    # ------------------------------------------------------------------ the reference's weight slots
+    def reference_slots(self, tied: bool | None = None) -> list:
+        """(slot name, slot shape, checkpoint tensors that hold the slot's rows in order) for every weight, with the
+        slot names and shapes of the reference's own Qwen3-shaped model definition
+        (src/Starlings.Roost.Models.Tiny/RoostTiny.cs:26-38): ``embed``, per layer ``l{i}.input_norm``, ``q_proj``,
+        ``k_proj``, ``v_proj``, ``q_norm``, ``k_norm``, ``o_proj``, ``post_norm``, ``gate_up`` (one slot of 2 x
+        intermediate rows: gate_proj then up_proj), ``down``, then ``final_norm`` and ``lm_head``. The reference's seeded
+        generator draws a slot's values from the slot's name, so the names are part of the weights."""
+        tie = self.tie_word_embeddings if tied is None else tied
+        H, d, I = self.hidden_size, self.head_dim, self.intermediate_size
+        Q, KV = self.num_attention_heads * d, self.num_key_value_heads * d
+        slots = [("embed", (self.vocab_size, H), ("model.embed_tokens.weight",))]
+        for i in range(self.num_hidden_layers):
+            p, a = f"model.layers.{i}.", f"model.layers.{i}.self_attn."
+            slots += [
+                (f"l{i}.input_norm", (H,), (p + "input_layernorm.weight",)),
+                (f"l{i}.q_proj", (Q, H), (a + "q_proj.weight",)),
+                (f"l{i}.k_proj", (KV, H), (a + "k_proj.weight",)),
+                (f"l{i}.v_proj", (KV, H), (a + "v_proj.weight",)),
+                (f"l{i}.q_norm", (d,), (a + "q_norm.weight",)),
+                (f"l{i}.k_norm", (d,), (a + "k_norm.weight",)),
+                (f"l{i}.o_proj", (H, Q), (a + "o_proj.weight",)),
+                (f"l{i}.post_norm", (H,), (p + "post_attention_layernorm.weight",)),
+                (f"l{i}.gate_up", (2 * I, H), (p + "mlp.gate_proj.weight", p + "mlp.up_proj.weight")),
+                (f"l{i}.down", (H, I), (p + "mlp.down_proj.weight",)),
+            ]
+        slots.append(("final_norm", (H,), ("model.norm.weight",)))
+        if not tie:
+            slots.append(("lm_head", (self.vocab_size, H), ("lm_head.weight",)))
+        return slots
+
     # ------------------------------------------------------------------ the model as parts
     def to_spec(self, tied: bool | None = None) -> ModelSpec:
         """Blocks, run order and checkpoint names. ``tied`` overrides ``tie_word_embeddings`` when the

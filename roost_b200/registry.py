@@ -23,13 +23,16 @@ class Architecture:
     model_types: tuple
     read_config: Callable          # ConfigReader -> typed configuration
     to_spec: Callable              # (configuration, tied: bool | None) -> ModelSpec
+    # configuration -> [(slot name, shape, checkpoint tensors)]: the weight slots as the reference's model definition of
+    # this architecture names them, for its seeded weight generator; None when the reference defines no such model
+    reference_slots: Callable | None = None
 
 
 _ARCHITECTURES: dict[str, Architecture] = {}
 
 
-def register_architecture(name: str, *, model_types=(), read_config, to_spec) -> None:
-    _ARCHITECTURES[name] = Architecture(name, tuple(model_types), read_config, to_spec)
+def register_architecture(name: str, *, model_types=(), read_config, to_spec, reference_slots=None) -> None:
+    _ARCHITECTURES[name] = Architecture(name, tuple(model_types), read_config, to_spec, reference_slots)
 
 
 def registered() -> list[str]:
@@ -53,7 +56,7 @@ def resolve(reader: ConfigReader) -> Architecture:
 def _register_builtin() -> None:
     from .config import qwen3
     register_architecture(qwen3.ARCHITECTURE, model_types=(qwen3.MODEL_TYPE,), read_config=qwen3.Qwen3Config.from_reader,
-                          to_spec=lambda cfg, tied=None: cfg.to_spec(tied))
+                          to_spec=lambda cfg, tied=None: cfg.to_spec(tied), reference_slots=lambda cfg: cfg.reference_slots())
 
 
 _register_builtin()

@@ -5,13 +5,19 @@ do not depend on the order tensors are written in, nor on which other tensors ex
 reference's seeded tiny weights, src/Starlings.Roost.Models.Tiny/TinyWeights.cs:22-32). Matrices and the
 embedding are N(0, std); norm weights are 1, or 1 + N(0, norm_std). Values are drawn in float32 and rounded
 to the config's ``torch_dtype``.
+
+A second mode, ``reference``, draws every tensor exactly as the reference's own generator does for a model of the same
+sizes (``reference_tensors``): with the reference's seed and its roost-tiny sizes the folder holds the very weights the
+reference's tests run, so its pinned greedy tokens can be asked of this engine.
 """
 from __future__ import annotations
 
 import hashlib
 import json
+import math
 from pathlib import Path
 
+import numpy as np
 import torch
 
 from ..config.reader import ConfigReader
@@ -54,11 +60,63 @@ def random_tensors(config: dict, seed: int, std: float = 0.02, norm_std: float =
     return out
 
 
-def write_random_model(model_dir, config: dict, seed: int, std: float = 0.02, norm_std: float = 0.0) -> Path:
-    """Writes ``config`` as config.json and seeded random weights as model.safetensors; returns the folder."""
+REFERENCE_TINY_SEED = 0x524F4F53540001   # the seed of the reference's dense tiny model (src/Starlings.Roost.Models.Tiny/TinyConfig.cs:63-66)
+_U64 = (1 << 64) - 1
+
+
+def reference_slot_values(model_seed: int, slot: str, shape: tuple) -> np.ndarray:
+    """The values of one weight slot as the reference's generator draws them, in float64 before rounding to the stored
+    dtype (src/Starlings.Roost.Models.Tiny/TinyWeights.cs:45-78,155-162): the generator's state starts at the model seed
+    xor the 64-bit FNV-1a hash of the slot name's characters; draw i is SplitMix64 of state + (i + 1) * 0x9E3779B97F4A7C15;
+    u = (draw >> 11) * 2^-53; the value is 1 + (2u - 1) * 0.1 for a slot whose name ends in "norm", (2u - 1) for "embed",
+    (2u - 1) * 1.5 / sqrt(last dimension) for every other slot."""
+    h = 0xCBF29CE484222325
+    for ch in slot:
+        h = ((h ^ ord(ch)) * 0x100000001B3) & _U64
+    state = np.uint64((model_seed ^ h) & _U64)
+    count = int(np.prod(shape))
+    with np.errstate(over="ignore"):     # arithmetic modulo 2^64 is the generator's definition
+        z = state + np.arange(1, count + 1, dtype=np.uint64) * np.uint64(0x9E3779B97F4A7C15)
+        z = (z ^ (z >> np.uint64(30))) * np.uint64(0xBF58476D1CE4E5B9)
+        z = (z ^ (z >> np.uint64(27))) * np.uint64(0x94D049BB133111EB)
+        z ^= z >> np.uint64(31)
+    u = (z >> np.uint64(11)).astype(np.float64) * 2.0 ** -53
+    if slot.endswith("norm"):
+        offset, amplitude = 1.0, 0.1
+    elif slot == "embed":
+        offset, amplitude = 0.0, 1.0
+    else:
+        offset, amplitude = 0.0, 1.5 / math.sqrt(shape[-1])
+    return (offset + (2.0 * u - 1.0) * amplitude).reshape(shape)
+
+
+def reference_tensors(config: dict, model_seed: int = REFERENCE_TINY_SEED) -> dict[str, torch.Tensor]:
+    """Checkpoint tensors drawn by the reference's generator, slot by slot under the reference's slot names, each rounded
+    to float32 and then to the config's ``torch_dtype`` as the reference rounds (TinyWeights.cs:86-91); a slot that
+    spans several checkpoint tensors (gate_up) is cut into them by rows."""
+    reader = ConfigReader(config, "config")
+    arch = registry.resolve(reader)
+    if arch.reference_slots is None:
+        raise ValueError(f"the reference defines no model of architecture {arch.name}: its generator's slot names are not known")
+    cfg = arch.read_config(reader)
+    dtype = _DTYPES[arch.to_spec(cfg, None).stored_dtype]
+    out = {}
+    for slot, shape, names in arch.reference_slots(cfg):
+        t = torch.from_numpy(reference_slot_values(model_seed, slot, shape).astype(np.float32)).to(dtype)
+        rows = shape[0] // len(names)
+        for i, n in enumerate(names):
+            out[n] = t[i * rows : (i + 1) * rows].clone() if len(names) > 1 else t
+    return out
+
+
+def write_random_model(model_dir, config: dict, seed: int, std: float = 0.02, norm_std: float = 0.0, mode: str = "normal") -> Path:
+    """Writes ``config`` as config.json and seeded random weights as model.safetensors; returns the folder. ``mode``
+    "normal": N(0, std) matrices; "reference": the reference's generator with ``seed`` as its model seed."""
+    if mode not in ("normal", "reference"):
+        raise ValueError(f"random-weights mode '{mode}' is neither normal nor reference")
     model_dir = Path(model_dir)
     model_dir.mkdir(parents=True, exist_ok=True)
-    tensors = random_tensors(config, seed, std, norm_std)
+    tensors = random_tensors(config, seed, std, norm_std) if mode == "normal" else reference_tensors(config, seed)
     (model_dir / "config.json").write_text(json.dumps(config, indent=2) + "\n")
     write_safetensors(model_dir / "model.safetensors", tensors, metadata={"format": "pt", "seed": seed})
     return model_dir
