@@ -350,9 +350,10 @@ def cmd_doctor(opts) -> int:
             spec = arch.to_spec(cfg, tied)
             want = loader.expected_tensors(parameter_declarations(spec), spec.weight_names)
             have = {}
+            weight_map = loader.checkpoint_index(opts["--model"])
             for f in loader.checkpoint_files(opts["--model"]):
                 with SafetensorsFile(f) as st:
-                    have.update({n: tuple(e.shape) for n, e in st.entries.items()})
+                    have.update({n: tuple(e.shape) for n, e in st.entries.items() if weight_map is None or weight_map.get(n) == f.name})
             missing = [n for n in want if n not in have]
             wrong = [n for n in want if n in have and have[n] != want[n]]
             line("weights", not missing and not wrong, f"{len(want)} tensors wanted, {len(missing)} missing, {len(wrong)} of another shape")

@@ -101,6 +101,51 @@ def test_concatenation_and_tied_head(tmp_path):
         loader.checkpoint_files(tmp_path / "nowhere")
 
 
+def test_a_checkpoint_in_two_shards_is_read_through_its_index(tmp_path):
+    """model.safetensors.index.json names a shard for every tensor; the loader reads each tensor from the shard the index
+    names and gives the same parameters as the one-file form. A tensor a shard holds without the index naming it, and a
+    tensor the index names for a shard that lacks it, are told in the same one error as the tensors the model misses."""
+    spec, decls = _spec(TINY_B)
+    tensors = random_tensors(TINY_B, 5)
+    one = tmp_path / "one"
+    one.mkdir()
+    write_safetensors(one / "model.safetensors", tensors)
+    want = loader.load_checkpoint(one, decls, spec.weight_names)
+    names = list(tensors)
+    first, second = names[::2], names[1::2]          # neighbours of a concatenated parameter land in different shards
+    two = tmp_path / "two"
+    two.mkdir()
+    shards = {"model-00001-of-00002.safetensors": first, "model-00002-of-00002.safetensors": second}
+    weight_map = {}
+    for shard, held in shards.items():
+        write_safetensors(two / shard, {n: tensors[n] for n in held})
+        weight_map.update({n: shard for n in held})
+    (two / "model.safetensors.index.json").write_text(json.dumps({"metadata": {"total_size": 0}, "weight_map": weight_map}))
+    assert [f.name for f in loader.checkpoint_files(two)] == sorted(shards)
+    assert loader.checkpoint_has(two, "lm_head.weight") and not loader.checkpoint_has(two, "model.layers.0.self_attn.q_proj.bias")
+    got = loader.load_checkpoint(two, decls, spec.weight_names)
+    assert got.keys() == want.keys()
+    for scope in want:
+        for local in want[scope]:
+            assert torch.equal(got[scope][local], want[scope][local]), (scope, local)
+    # the index forgets one tensor (it is still in its shard) and names another for the wrong shard
+    forgotten, misplaced = "model.layers.1.mlp.down_proj.weight", "model.norm.weight"
+    bad = dict(weight_map)
+    del bad[forgotten]
+    bad[misplaced] = [s for s in shards if s != weight_map[misplaced]][0]
+    (two / "model.safetensors.index.json").write_text(json.dumps({"weight_map": bad}))
+    with pytest.raises(loader.WeightError) as e:
+        loader.load_checkpoint(two, decls, spec.weight_names)
+    err = e.value
+    assert sorted(err.missing) == sorted([forgotten, misplaced])
+    assert len(err.index_faults) == 3 and "shard index" in str(err)
+    assert any(forgotten in f and "does not name it" in f for f in err.index_faults)
+    assert any(misplaced in f and "does not hold it" in f for f in err.index_faults)
+    (two / "model.safetensors.index.json").write_text(json.dumps({"weights": {}}))
+    with pytest.raises(loader.WeightError, match="weight_map"):
+        loader.load_checkpoint(two, decls, spec.weight_names)
+
+
 def test_random_weights_mode_is_seeded_and_order_independent(tmp_path):
     a = random_tensors(TINY_B, seed=1, std=0.02, norm_std=0.1)
     b = random_tensors(TINY_B, seed=1, std=0.02, norm_std=0.1)
