@@ -12,8 +12,8 @@ and exits with 2.
 
     roost generate --model DIR (--prompt-ids 1,2,3 | --prompt-file FILE) [--max-output-tokens N] [--temperature T]
                    [--top-p P] [--top-k K] [--min-p P] [--seed S] [--stop-ids a,b] [--ignore-eos] [engine options]
-    roost chat --model DIR [--tokenizer tokenizer.json] [--template TEXT] [--max-output-tokens N] [sampling options as
-               for generate] [engine options]                       a console: /reset clears the conversation, /exit quits
+    roost chat --model DIR [--tokenizer tokenizer.json] [--template TEXT] [--stop-strings TEXT|JSON-LIST] [--max-output-tokens N]
+               [sampling options as for generate] [engine options]  a console: /reset clears the conversation, /exit quits
     roost bench --model DIR [--batch N] [--prompt-tokens P] [--new-tokens K] [--seed S] [engine options]
                                                       prefill and decode tokens a second of this model, one JSON line
     roost random-weights --config config.json --out DIR [--seed S] [--std X] [--norm-std X] [--mode normal|reference]
@@ -22,7 +22,7 @@ and exits with 2.
     roost replay --model DIR --dtype bfloat16|float32 --out DIR --max-tokens N      (bin/trace_run)
     roost doctor [--model DIR] [--kernels DIR] [--no-gpu] [--min-free-memory-gib N]
   engine options: [--dtype bfloat16|float32] [--device N] [--kernels DIR] [--page-size N] [--attention-blocks N]
-                  [--max-tokens N] [--max-sequences N] [--max-chunk-tokens N]
+                  [--kv-fraction F] [--max-tokens N] [--max-sequences N] [--max-chunk-tokens N]
 """
 from __future__ import annotations
 
@@ -32,12 +32,12 @@ import sys
 
 USAGE = __doc__.split("\n\n", 2)[2]
 
-_ENGINE_VALUED = {"--dtype", "--device", "--kernels", "--page-size", "--attention-blocks", "--max-tokens", "--max-sequences",
-                  "--max-chunk-tokens"}
+_ENGINE_VALUED = {"--dtype", "--device", "--kernels", "--page-size", "--attention-blocks", "--kv-fraction", "--max-tokens",
+                  "--max-sequences", "--max-chunk-tokens"}
 _COMMANDS = {
     "generate": (_ENGINE_VALUED | {"--model", "--prompt-ids", "--prompt-file", "--max-output-tokens", "--temperature", "--top-p",
                                    "--top-k", "--min-p", "--seed", "--stop-ids"}, {"--ignore-eos"}),
-    "chat": (_ENGINE_VALUED | {"--model", "--tokenizer", "--template", "--max-output-tokens", "--temperature", "--top-p", "--top-k",
+    "chat": (_ENGINE_VALUED | {"--model", "--tokenizer", "--template", "--stop-strings", "--max-output-tokens", "--temperature", "--top-p", "--top-k",
                                "--min-p", "--seed", "--stop-ids"}, {"--ignore-eos"}),
     "bench": (_ENGINE_VALUED | {"--model", "--batch", "--prompt-tokens", "--new-tokens", "--seed"}, set()),
     "random-weights": ({"--config", "--out", "--seed", "--std", "--norm-std", "--mode"}, set()),
@@ -107,6 +107,32 @@ def _need(opts, key):
     return opts[key]
 
 
+def _kv_fraction(opts) -> float:
+    """--kv-fraction: the share of the device memory free after the weights that the cache pools take when
+    --attention-blocks does not size them."""
+    f = _float(opts, "--kv-fraction", 0.9)
+    if not 0 < f <= 1:
+        raise UsageError("--kv-fraction must lie in (0, 1]")
+    return f
+
+
+def _stop_strings(opts) -> tuple:
+    """--stop-strings: one string, or a JSON list of strings."""
+    if "--stop-strings" not in opts:
+        return ()
+    text = opts["--stop-strings"]
+    if text.lstrip().startswith("["):
+        try:
+            stops = json.loads(text)
+        except json.JSONDecodeError:
+            raise UsageError("--stop-strings: not a JSON list") from None
+    else:
+        stops = [text]
+    if not isinstance(stops, list) or not all(isinstance(x, str) and x for x in stops):
+        raise UsageError("--stop-strings needs non-empty strings")
+    return tuple(stops)
+
+
 def _apply_common(opts) -> None:
     if "--device" in opts:
         os.environ["CUDA_VISIBLE_DEVICES"] = str(_int(opts, "--device"))
@@ -129,7 +155,7 @@ def cmd_generate(opts) -> int:
     if dtype not in ("bfloat16", "float32"):
         raise UsageError("--dtype is bfloat16 or float32")
     # every option is read before anything is loaded, so a bad value is a usage error whatever the model is
-    engine_opts = dict(page_size=_int(opts, "--page-size", 16), attention_blocks=_int(opts, "--attention-blocks"),
+    engine_opts = dict(page_size=_int(opts, "--page-size", 16), attention_blocks=_int(opts, "--attention-blocks"), kv_fraction=_kv_fraction(opts),
                        max_sequences=_int(opts, "--max-sequences", 64), max_tokens=_int(opts, "--max-tokens", 2048),
                        max_chunk_tokens=_int(opts, "--max-chunk-tokens"))
     gen_opts = dict(max_output_tokens=_int(opts, "--max-output-tokens", 16), temperature=_float(opts, "--temperature"),
@@ -159,7 +185,7 @@ def cmd_chat(opts, lines=None, out=None) -> int:
     dtype = opts.get("--dtype", "bfloat16")
     if dtype not in ("bfloat16", "float32"):
         raise UsageError("--dtype is bfloat16 or float32")
-    engine_opts = dict(page_size=_int(opts, "--page-size", 16), attention_blocks=_int(opts, "--attention-blocks"),
+    engine_opts = dict(page_size=_int(opts, "--page-size", 16), attention_blocks=_int(opts, "--attention-blocks"), kv_fraction=_kv_fraction(opts),
                        max_sequences=_int(opts, "--max-sequences", 1), max_tokens=_int(opts, "--max-tokens", 2048),
                        max_chunk_tokens=_int(opts, "--max-chunk-tokens"))
     gen_opts = dict(max_output_tokens=_int(opts, "--max-output-tokens", 256), temperature=_float(opts, "--temperature"),
@@ -169,6 +195,7 @@ def cmd_chat(opts, lines=None, out=None) -> int:
     template = opts.get("--template", CHAT_TEMPLATE)
     if "{message}" not in template:
         raise UsageError("--template needs the placeholder {message}")
+    stops = _stop_strings(opts)
     tokenizer_path = opts.get("--tokenizer") or os.path.join(model, "tokenizer.json")
     tokenizer = None
     if os.path.exists(tokenizer_path):
@@ -179,9 +206,12 @@ def cmd_chat(opts, lines=None, out=None) -> int:
         tokenizer = Tokenizer.from_file(tokenizer_path)
     elif "--tokenizer" in opts:
         raise UsageError(f"--tokenizer: {tokenizer_path} does not exist")
+    if stops and tokenizer is None:
+        raise UsageError("--stop-strings are matched on text: a tokenizer is needed")
     _apply_common(opts)
     from .engine.engine import GenerationOptions, RoostEngine
     from .engine.request import RequestError
+    from .engine.text import IncrementalDetokenizer, StopMatcher
     out = out or sys.stdout
     engine = RoostEngine(model, dtype=dtype, **engine_opts)
     go = GenerationOptions(**gen_opts)
@@ -208,19 +238,28 @@ def cmd_chat(opts, lines=None, out=None) -> int:
                 print("[InvalidOption] a turn is token ids separated by commas or spaces", file=out, flush=True)
                 continue
         reply: list[int] = []
-        shown = ""
+        # text mode: the reply is detokenised as it grows (a token may end inside a character) and watched for the stop
+        # strings, which end the turn and are not printed (src/Starlings.Generation.Roost/RoostChatClient.cs:366-378)
+        detok = IncrementalDetokenizer(tokenizer, skip_special_tokens=True) if tokenizer is not None else None
+        matcher = StopMatcher(stops)
         try:
-            for update in engine.stream_completion(history + turn, go):
+            stream = engine.stream_completion(history + turn, go)
+            for update in stream:
                 if update.token is None:
                     continue
                 reply.append(update.token)
                 if tokenizer is None:
                     print(("" if len(reply) == 1 else " ") + str(update.token), end="", file=out, flush=True)
-                else:   # decode the whole reply and print what is new: a token may end inside a character
-                    whole = tokenizer.decode(reply, skip_special_tokens=True)
-                    if not whole.endswith("\ufffd"):
-                        print(whole[len(shown):], end="", file=out, flush=True)
-                        shown = whole
+                    continue
+                emit, matched = matcher.push(detok.push(update.token))
+                print(emit, end="", file=out, flush=True)
+                if matched is not None:
+                    stream.close()     # cancels the request
+                    break
+            else:
+                if tokenizer is not None:
+                    emit, _ = matcher.push(detok.flush())
+                    print(emit + matcher.flush(), end="", file=out, flush=True)
         except RequestError as e:
             print(f"\n[{e.kind}] {e} (type /reset to start over)", file=out, flush=True)
             continue
@@ -241,7 +280,7 @@ def cmd_bench(opts) -> int:
     batch, prompt_tokens, new_tokens = _int(opts, "--batch", 8), _int(opts, "--prompt-tokens", 512), _int(opts, "--new-tokens", 64)
     if min(batch, prompt_tokens, new_tokens) <= 0:
         raise UsageError("--batch, --prompt-tokens and --new-tokens must be positive")
-    engine_opts = dict(page_size=_int(opts, "--page-size", 16), attention_blocks=_int(opts, "--attention-blocks"),
+    engine_opts = dict(page_size=_int(opts, "--page-size", 16), attention_blocks=_int(opts, "--attention-blocks"), kv_fraction=_kv_fraction(opts),
                        max_sequences=_int(opts, "--max-sequences", max(batch, 1)), max_tokens=_int(opts, "--max-tokens", 2048),
                        max_chunk_tokens=_int(opts, "--max-chunk-tokens"))
     seed = _int(opts, "--seed", 0)

@@ -1201,6 +1201,13 @@ extern "C" void roost_attention_set_decode_tma(int on) { g_decode_tma = on != 0;
 
 // 0, or the code of the first wait a decode kernel gave up since the last call (1, 3: a free stage; 2: a tile's copies;
 // 4, 5: the chunk descriptors).
+namespace roost {
+int* attention_error_address() {
+  int* p = nullptr;
+  return cudaGetSymbolAddress((void**)&p, g_attention_error) == cudaSuccess ? p : nullptr;
+}
+}  // namespace roost
+
 extern "C" int roost_attention_status(void) {
   int code = 0;
   if (cudaMemcpyFromSymbol(&code, g_attention_error, sizeof(int)) != cudaSuccess) return -1;

@@ -496,6 +496,11 @@ int launch_prefill_tc(const void* q, long long tokens, void* out, const void* k_
 
 void set_prefill_tc(bool on) { g_prefill_tc = on; }
 
+int* attention_tc_error_address() {
+  int* p = nullptr;
+  return cudaGetSymbolAddress((void**)&p, g_attention_tc_error) == cudaSuccess ? p : nullptr;
+}
+
 int prefill_tc_status() {
   int code = 0;
   if (cudaMemcpyFromSymbol(&code, g_attention_tc_error, sizeof(int)) != cudaSuccess) return -1;

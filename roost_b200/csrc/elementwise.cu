@@ -174,9 +174,43 @@ __global__ void silu_mul_vec_kernel(const T* __restrict__ x, T* __restrict__ out
   Vec<T>::store(out + t * inter + (size_t)vi * N, o);
 }
 
+// The error words of the kernels that wait with a limit (defined beside those kernels).
+int* gemm_tcgen05_error_address();
+int* attention_error_address();
+int* attention_tc_error_address();
+
+__global__ void status_snapshot_kernel(const int* a, const int* b, const int* c, int* out) {
+  pdl_wait();   // the kernels before this one on the stream have finished: what they recorded is seen
+  if (threadIdx.x == 0) {
+    out[0] = *a;
+    out[1] = *b;
+    out[2] = *c;
+    out[3] = 1;   // says that the snapshot was written
+    __threadfence_system();
+  }
+}
+
 }  // namespace roost
 
 using namespace roost;
+
+extern "C" int roost_status_snapshot(int32_t* out, int out_is_host, roost_stream_t stream) {
+  ROOST_REQUIRE(out != nullptr, "status_snapshot: no destination");
+  int* dst = out;
+  if (out_is_host) {
+    void* mapped = nullptr;
+    if (cudaHostGetDevicePointer(&mapped, out, 0) != cudaSuccess || mapped == nullptr) {
+      cudaGetLastError();
+      return fail(ROOST_ERR_INVALID, "status_snapshot: the host destination is not page-locked memory the device can write");
+    }
+    dst = static_cast<int*>(mapped);
+  }
+  const int *a = gemm_tcgen05_error_address(), *b = attention_error_address(), *c = attention_tc_error_address();
+  if (!a || !b || !c) return fail(ROOST_ERR_CUDA, "status_snapshot: an error word has no device address");
+  cudaError_t e = launch_kernel(status_snapshot_kernel, dim3(1), dim3(32), 0, (cudaStream_t)stream, a, b, c, dst);
+  if (e != cudaSuccess) return fail(ROOST_ERR_CUDA, std::string("status_snapshot: ") + cudaGetErrorString(e));
+  return ROOST_OK;
+}
 
 extern "C" int roost_abi_version(void) { return ROOST_ABI_VERSION; }
 extern "C" void roost_set_pdl(int on) { g_pdl_enabled = on != 0; }

@@ -838,6 +838,13 @@ extern "C" int roost_gemm_tcgen05_supported(int m, int n, int k, int64_t lda, in
 // The error code a kernel recorded when it gave a wait up (0: none), cleared by the call. 1: producer waiting for a free
 // stage, 2: issuer waiting for a free accumulator, 3: issuer waiting for a stage's data, 4: epilogue waiting for an
 // accumulator. Synchronises the device.
+namespace roost {
+int* gemm_tcgen05_error_address() {
+  int* p = nullptr;
+  return cudaGetSymbolAddress((void**)&p, g_gemm_tcgen05_error) == cudaSuccess ? p : nullptr;
+}
+}  // namespace roost
+
 extern "C" int roost_gemm_tcgen05_status(void) {
   int code = 0;
   if (cudaMemcpyFromSymbol(&code, g_gemm_tcgen05_error, sizeof(int)) != cudaSuccess) return -1;

@@ -17,7 +17,7 @@
 extern "C" {
 #endif
 
-#define ROOST_ABI_VERSION 5
+#define ROOST_ABI_VERSION 6
 
 #define ROOST_OK 0
 #define ROOST_ERR_INVALID 1      /* an argument is out of range or inconsistent; nothing was launched */
@@ -40,6 +40,13 @@ int roost_abi_version(void);
 void roost_set_pdl(int on);
 /* Message of the last non-OK status on this thread. */
 const char* roost_last_error(void);
+
+/* Writes, in stream order and without synchronising, the error words of the kernels that wait with a limit into
+ * out[0..2] (the tcgen05 products, the decode attention, the tcgen05 prefill attention; 0: no wait was given up since
+ * the words were last cleared by roost_gemm_tcgen05_status() / roost_attention_status()) and 1 into out[3]. out is
+ * device memory, or with out_is_host page-locked host memory (refused when the device cannot write it): a caller that
+ * copies a step's results to the host anyway learns of a given-up wait with them, at no extra synchronisation. */
+int roost_status_snapshot(int32_t* out, int out_is_host, roost_stream_t stream);
 
 /* out[t,:] = table[ids[t],:]; an id outside [0, vocab) gives a zero row. */
 int roost_embedding(const void* table, const int32_t* ids, void* out, int tokens, int hidden, int vocab, int dtype,

@@ -24,6 +24,7 @@ from .executor import StepEntry, StepExecutor
 from .model import Model, load_model
 from .request import GREEDY, Request, RequestError, SamplingParameters, TokenEvent
 from .scheduler import Scheduler, SchedulerOptions, StepPlan
+from .text import (IncrementalDetokenizer, StopMatcher, TextCompletion, TextUpdate, encode, render_chat)
 
 
 class _Done:
@@ -36,7 +37,7 @@ class _InFlight:
     """A decode step that was started before the tokens of the step before it were read (see ``RoostEngine.step``)."""
     prep: object                  # the executor's PreparedDecode
     ids_device: torch.Tensor      # the tokens it samples, on the device
-    ids_host: torch.Tensor        # their pinned copy, valid once ``event`` has passed
+    ids_host: torch.Tensor        # their pinned copy (followed by the kernels' status words), valid once ``event`` has passed
     event: object
     fed: list | None = None       # the tokens it was fed, once the host has read them
 
@@ -85,8 +86,9 @@ class RoostEngine:
         ``max_sequences``: the largest token and row count of a step (the reference's worker flags of the same
         names, src/Starlings.Roost.WorkerHost/WorkerArguments.cs:51-58). ``chain_steps``: while every live request
         decodes, the next step is started on the device before this step's tokens have been read (the reference's
-        planner has the same option, src/Starlings.Roost.Engine/Scheduling/StepPlanner.cs:316-336); the tokens
-        are the same with it and without."""
+        planner keeps plans in flight while it makes later ones, ``_inFlight``,
+        src/Starlings.Roost.Engine/Scheduling/StepPlanner.cs:102,345,951; it does not start a step on tokens the host has
+        not seen, which is this engine's own addition); the tokens are the same with it and without."""
         if isinstance(dtype, str):
             dtype = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}[dtype]
         self.model: Model = model if isinstance(model, Model) else load_model(model, dtype, device)
@@ -105,6 +107,7 @@ class RoostEngine:
         self._prepared = None     # the next decode step's tables, made while the device ran the last one
         self._inflight: _InFlight | None = None   # the next decode step, already running
         self.chain_steps = chain_steps
+        self._status_with_tokens = hasattr(self.model.rt.kernels, "status_snapshot") and self.model.rt.device.type == "cuda"
         self.chained_steps = 0    # steps that were running before the tokens of the step before them had been read
 
     # ------------------------------------------------------------------ requests
@@ -140,73 +143,94 @@ class RoostEngine:
             return []
         tokens = {}
         if plan.rows:
-            entries = [StepEntry(r.sequence.request_id, r.tokens, [r.count - 1] if r.samples else [], r.start) for r in plan.rows]
-            prepared, self._prepared = self._prepared, None
-            inflight, self._inflight = self._inflight, None
-            sampling_rows = [r for r in plan.rows if r.samples]
-            ids_device = ids_host = event = None
-            keep = None
-            if inflight is not None and len(sampling_rows) == len(plan.rows):
-                keep = self.executor.adoptable(inflight.prep, entries)
-                if keep is not None and any(e.tokens[0] != inflight.fed[i] for e, i in zip(entries, keep)):
-                    keep = None    # the step was fed other tokens than the plan names: it does not stand
-            if keep is not None:
-                # this step is running already (or done): it was started with the tokens on the device
-                self.executor.adopt_prepared(inflight.prep, keep)
-                self.chained_steps += 1
-                ids_device, ids_host, event = inflight.ids_device, inflight.ids_host, inflight.event
-                if len(keep) != ids_device.numel():
-                    ids_device = ids_device[torch.tensor(keep, dtype=torch.long).to(ids_device.device, non_blocking=True)]
-            else:
-                # (a step in flight that does not stand is dropped: what it wrote lies beyond its requests' committed
-                # lengths and is written again, and the pages it took stay with their requests)
-                if prepared is not None and self.executor.matches_prepared(prepared, entries):
-                    logits = self.executor.run_prepared(prepared, entries)
-                else:
-                    logits = self.executor.step(entries)
-                if sampling_rows:
-                    rows = [SamplingRow(r.sequence.request.sampling, self._seeds[r.sequence.request_id], r.sequence.generated)
-                            for r in sampling_rows]
-                    ids_device = self.sampler(logits, rows)
-                    ids_host, event = self._to_host(ids_device)
-                    keep = list(range(len(sampling_rows)))
-            if sampling_rows:
-                # While the device runs this step: the next one, should it be these rows' next tokens and nothing else
-                # (no request waiting for its prompt). Its tables are made now; with ``chain_steps`` it is also started
-                # now, fed with this step's tokens on the device, and the host reads this step's tokens meanwhile.
-                if len(sampling_rows) == len(plan.rows) and all(r.count == 1 for r in plan.rows) and self._decode_only():
-                    prep = self.executor.prepare_decode([r.sequence.request_id for r in plan.rows])
-                    if prep is not None and self.chain_steps:
-                        nxt = self.executor.launch_prepared(prep, ids_device)
-                        rows = [SamplingRow(r.sequence.request.sampling, self._seeds[r.sequence.request_id], r.sequence.generated + 1)
-                                for r in plan.rows]
-                        nxt_ids = self.sampler(nxt, rows)
-                        self._inflight = _InFlight(prep, nxt_ids, *self._to_host(nxt_ids))
-                    else:
-                        self._prepared = prep
-                event.synchronize()
-                host = ids_host.tolist()
-                ids = [host[i] for i in keep]
-                if self._inflight is not None:
-                    self._inflight.fed = ids
-                tokens = {r.sequence.request_id: t for r, t in zip(sampling_rows, ids)}
-            self.steps += 1
-            if self.steps % self.STATUS_EVERY == 0:
-                self.check_device()
+            try:
+                tokens = self._run(plan)
+            except Exception:
+                # nothing of this plan is applied: its rows are planned again from where the cache stands, a step that
+                # was started ahead is dropped, and the error goes to the caller with the engine still usable
+                self._prepared = self._inflight = None
+                self.scheduler.rollback(plan)
+                raise
         events = self.scheduler.apply(plan, tokens)
         for e in events:
             if e.finish_reason is not None:
                 self._seeds.pop(e.request_id, None)
         return events
 
-    STATUS_EVERY = 256   # steps between looks at the kernels' status words
+    def _run(self, plan: StepPlan) -> dict:
+        """Runs the plan's rows through the step function and the sampler; request id -> sampled token."""
+        tokens = {}
+        entries = [StepEntry(r.sequence.request_id, r.tokens, [r.count - 1] if r.samples else [], r.start) for r in plan.rows]
+        prepared, self._prepared = self._prepared, None
+        inflight, self._inflight = self._inflight, None
+        sampling_rows = [r for r in plan.rows if r.samples]
+        ids_device = ids_host = event = None
+        keep = None
+        if inflight is not None and len(sampling_rows) == len(plan.rows):
+            keep = self.executor.adoptable(inflight.prep, entries)
+            if keep is not None and any(e.tokens[0] != inflight.fed[i] for e, i in zip(entries, keep)):
+                keep = None    # the step was fed other tokens than the plan names: it does not stand
+        if keep is not None:
+            # this step is running already (or done): it was started with the tokens on the device
+            self.executor.adopt_prepared(inflight.prep, keep)
+            self.chained_steps += 1
+            ids_device, ids_host, event = inflight.ids_device, inflight.ids_host, inflight.event
+            if len(keep) != ids_device.numel():
+                ids_device = ids_device[torch.tensor(keep, dtype=torch.long).to(ids_device.device, non_blocking=True)]
+        else:
+            # (a step in flight that does not stand is dropped: what it wrote lies beyond its requests' committed
+            # lengths and is written again, and the pages it took stay with their requests)
+            if prepared is not None and self.executor.matches_prepared(prepared, entries):
+                logits = self.executor.run_prepared(prepared, entries)
+            else:
+                logits = self.executor.step(entries)
+            if sampling_rows:
+                rows = [SamplingRow(r.sequence.request.sampling, self._seeds[r.sequence.request_id], r.sequence.generated)
+                        for r in sampling_rows]
+                ids_device = self.sampler(logits, rows)
+                ids_host, event = self._to_host(ids_device)
+                keep = list(range(len(sampling_rows)))
+        if sampling_rows:
+            # While the device runs this step: the next one, should it be these rows' next tokens and nothing else
+            # (no request waiting for its prompt). Its tables are made now; with ``chain_steps`` it is also started
+            # now, fed with this step's tokens on the device, and the host reads this step's tokens meanwhile.
+            if len(sampling_rows) == len(plan.rows) and all(r.count == 1 for r in plan.rows) and self._decode_only():
+                prep = self.executor.prepare_decode([r.sequence.request_id for r in plan.rows])
+                if prep is not None and self.chain_steps:
+                    nxt = self.executor.launch_prepared(prep, ids_device)
+                    rows = [SamplingRow(r.sequence.request.sampling, self._seeds[r.sequence.request_id], r.sequence.generated + 1)
+                            for r in plan.rows]
+                    nxt_ids = self.sampler(nxt, rows)
+                    self._inflight = _InFlight(prep, nxt_ids, *self._to_host(nxt_ids))
+                else:
+                    self._prepared = prep
+            event.synchronize()
+            host = ids_host.tolist()
+            if any(host[-4:-1]):
+                self.check_device()   # a kernel gave up a bounded wait: this step's tokens are not valid (raises)
+            ids = [host[i] for i in keep]
+            if self._inflight is not None:
+                self._inflight.fed = ids
+            tokens = {r.sequence.request_id: t for r, t in zip(sampling_rows, ids)}
+        self.steps += 1
+        if not self._status_with_tokens and self.steps % self.STATUS_EVERY == 0:
+            self.check_device()
+        return tokens
+
+    STATUS_EVERY = 256   # steps between looks at the kernels' status words when no step reads them with its tokens
 
     def _to_host(self, ids_device: torch.Tensor):
-        """Starts the copy of sampled ids to pinned host memory; (the host tensor, the event that says it has arrived)."""
+        """Starts the copy of sampled ids to pinned host memory; (the host tensor, the event that says it has arrived).
+        The host tensor ends in four more words: the kernels' error words as they stand after this step's kernels (0: no
+        bounded wait was given up) and a 1, written by the device in stream order, so that the wait for the tokens is
+        also the look at the status and no generation returns tokens of a step whose kernels gave up."""
+        n = ids_device.numel()
         if ids_device.device.type != "cuda":
-            return ids_device, _Done()
-        host = torch.empty(ids_device.shape, dtype=ids_device.dtype, pin_memory=True)
-        host.copy_(ids_device, non_blocking=True)
+            return torch.cat([ids_device.reshape(-1).to(torch.int32), torch.tensor([0, 0, 0, 1], dtype=torch.int32)]), _Done()
+        host = torch.zeros(n + 4, dtype=ids_device.dtype, pin_memory=True)
+        host[:n].copy_(ids_device.reshape(-1), non_blocking=True)
+        if self._status_with_tokens:
+            self.model.rt.kernels.status_snapshot(host[n:])
         event = torch.cuda.Event()
         event.record()
         return host, event
@@ -251,23 +275,100 @@ class RoostEngine:
         rid = self.add_request(prompt_token_ids, o.sampling(), stop_token_ids=o.stop_token_ids)
         produced = 0
         done = False
-        while not done:
-            if not self.has_unfinished():
-                break
-            for e in self.step():
-                if e.request_id != rid:
-                    continue
-                if e.token is not None:
-                    produced += 1
-                done = e.finish_reason is not None
-                yield CompletionUpdate(rid, e.token, e.finish_reason, len(prompt_token_ids), produced)
+        try:
+            while not done:
+                if not self.has_unfinished():
+                    break
+                for e in self.step():
+                    if e.request_id != rid:
+                        continue
+                    if e.token is not None:
+                        produced += 1
+                    done = e.finish_reason is not None
+                    yield CompletionUpdate(rid, e.token, e.finish_reason, len(prompt_token_ids), produced)
+        finally:
+            if not done:
+                self.cancel(rid)   # the caller stopped listening (a stop string matched, say): out of the next step
 
-    def complete_text(self, tokenizer, prompt: str, options: GenerationOptions | None = None) -> str:
-        """Text in, text out, for a caller that brings a tokenizer (``encode(str) -> ids``, ``decode(ids) -> str``)."""
-        ids = tokenizer.encode(prompt)
-        ids = getattr(ids, "ids", ids)
-        out = self.generate([list(ids)], options)[0]
-        return tokenizer.decode(out.token_ids)
+    # ------------------------------------------------------------------ text in, text out (the caller brings the tokenizer)
+    def stream_text(self, tokenizer, prompt: str, options: GenerationOptions | None = None, stop=(),
+                    encode_options: dict | None = None, decode_options: dict | None = None) -> Iterator[TextUpdate]:
+        """A raw completion (no chat template) as text deltas, with stop strings: they are matched on the detokenised
+        text on the host as the tokens arrive, text that could be the start of one is held back until it is decided,
+        the match is cut from the output, the request is cancelled and the completion ends with "stop"
+        (src/Starlings.Generation.Roost/RoostChatClient.cs:366-378). The last update carries the finish reason and the
+        usage counts. ``tokenizer``: ``encode(str) -> ids`` (or an object with ``.ids``) and ``decode(ids) -> str``."""
+        matcher = StopMatcher(stop)
+        ids = encode(tokenizer, prompt, **(encode_options or {}))
+        if not ids:
+            raise RequestError("InvalidOption", "the prompt has no tokens")
+        detok = IncrementalDetokenizer(tokenizer, **(decode_options or {}))
+        o = options or GenerationOptions()
+        rid = self.add_request(ids, o.sampling(), stop_token_ids=o.stop_token_ids)
+        produced, reason, live = 0, None, True
+        try:
+            while reason is None:
+                if not self.has_unfinished():
+                    break
+                for e in self.step():
+                    if e.request_id != rid:
+                        continue
+                    stop_token = e.finish_reason == "stop"
+                    if e.token is not None:
+                        produced += 1
+                        # a stop token ends the text: it is not part of it
+                        emit, matched = matcher.push("" if stop_token else detok.push(e.token))
+                        if matched is not None:
+                            if emit:
+                                yield TextUpdate(emit)
+                            reason = "stop"
+                            live = e.finish_reason is None
+                            break
+                        if emit:
+                            yield TextUpdate(emit)
+                    if e.finish_reason is not None:
+                        live = False
+                        if not stop_token:
+                            tail, matched = matcher.push(detok.flush())
+                            tail += matcher.flush()
+                            if tail:
+                                yield TextUpdate(tail)
+                            reason = "stop" if matched is not None else e.finish_reason
+                        else:
+                            tail = matcher.flush()
+                            if tail:
+                                yield TextUpdate(tail)
+                            reason = "stop"
+                        break
+        finally:
+            if live:
+                self.cancel(rid)     # stopped on a string, or abandoned by the caller: out of the next step
+        yield TextUpdate("", reason, matcher.matched, len(ids), produced)
+
+    def complete_text(self, tokenizer, prompt: str, options: GenerationOptions | None = None, stop=(), **kw) -> TextCompletion:
+        """Text in, text out; see ``stream_text``. The result's ``text`` excludes a matched stop string."""
+        text, last = [], None
+        for u in self.stream_text(tokenizer, prompt, options, stop, **kw):
+            text.append(u.text)
+            last = u
+        return TextCompletion("".join(text), last.finish_reason, last.stop_string, last.prompt_tokens, last.completion_tokens)
+
+    def stream_chat(self, tokenizer, messages, options: GenerationOptions | None = None, stop=(), turn: str | None = None,
+                    reply: str | None = None, **kw) -> Iterator[TextUpdate]:
+        """The reply to a conversation (a list of {"role", "content"}) as text deltas: the messages are rendered in the
+        turn format the Qwen3 checkpoints are tuned on (``text.render_chat``; ``turn`` and ``reply`` give another) and
+        completed like ``stream_text``; the end-of-turn mark is a stop string unless the caller names its own."""
+        from .text import CHATML_REPLY, CHATML_TURN
+        prompt = render_chat(messages, turn or CHATML_TURN, reply if reply is not None else CHATML_REPLY)
+        return self.stream_text(tokenizer, prompt, options, tuple(stop) or ("<|im_end|>",), **kw)
+
+    def chat(self, tokenizer, messages, options: GenerationOptions | None = None, stop=(), **kw) -> TextCompletion:
+        """The assistant's reply to ``messages`` as one text; see ``stream_chat``."""
+        text, last = [], None
+        for u in self.stream_chat(tokenizer, messages, options, stop, **kw):
+            text.append(u.text)
+            last = u
+        return TextCompletion("".join(text), last.finish_reason, last.stop_string, last.prompt_tokens, last.completion_tokens)
 
     # ------------------------------------------------------------------ figures
     def stats(self) -> dict:

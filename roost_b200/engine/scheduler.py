@@ -185,6 +185,23 @@ class Scheduler:
         self.cache.extend(s.request_id, target)
         return True
 
+    def rollback(self, plan: StepPlan) -> None:
+        """The plan's step raised: its rows are taken back, so that the next plan names them again. A request whose
+        cache still stands where the row began keeps it (and the pages taken for the row: the next plan needs them
+        again); one whose cache the failed step had already moved on is treated like a preempted request: it keeps its
+        tokens, loses its pages and is recomputed from position 0, since what the step wrote cannot be trusted and pages
+        a window has passed cannot be had back. A request preempted or aborted while the plan was made stays so."""
+        for row in plan.rows:
+            s = row.sequence
+            if s not in self._seqs:
+                continue
+            held = self.cache.get(s.request_id).tokens if s.request_id in self.cache else 0
+            if held == row.start:
+                s.computed = row.start
+            else:
+                self.cache.free(s.request_id)
+                s.computed = 0
+
     def _preempt(self, v: Sequence) -> None:
         """The victim keeps every token, loses its pages and is recomputed from position 0."""
         self.cache.free(v.request_id)

@@ -13,7 +13,7 @@ import torch
 
 from . import build
 
-ABI_VERSION = 5
+ABI_VERSION = 6
 F32, BF16 = 0, 1
 
 
@@ -55,6 +55,7 @@ def _need(t: torch.Tensor, name: str, dtype=None):
 
 
 _SIGNATURES = {
+    "roost_status_snapshot": [c_void_p, c_int, c_void_p],
     "roost_embedding": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "roost_rms_norm": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_int, c_void_p],
     "roost_add_rms_norm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_int, c_void_p],
@@ -378,10 +379,25 @@ class KernelLibrary:
         """The code of a bounded wait the copy-engine decode kernel gave up since the last call (0: none); synchronises."""
         return int(self._lib.roost_attention_status())
 
+    def status_snapshot(self, out: torch.Tensor) -> None:
+        """Writes the kernels' error words into ``out`` (four int32: three codes, then 1) in stream order, without
+        synchronising. ``out`` is on the device or in pinned host memory: an engine that copies a step's tokens to the
+        host puts the words beside them and reads both after the one wait it makes anyway."""
+        if out.dtype != torch.int32 or out.numel() < 4 or not out.is_contiguous():
+            raise KernelError("status_snapshot: four contiguous int32 are needed")
+        if not out.is_cuda and not out.is_pinned():
+            raise KernelError("status_snapshot: a host destination must be pinned memory")
+        self._call("roost_status_snapshot", _ptr(out), 0 if out.is_cuda else 1, _stream())
+
     def check_device_status(self) -> None:
-        """Raises when a kernel gave up one of its bounded waits since the last call (its results are then not valid)."""
+        """Raises when a kernel gave up one of its bounded waits since the last call (its results are then not valid).
+        Synchronises, clears the error words and lowers the flags a weight-streaming product that gave up may have left
+        raised, so that the launches after the error start clean."""
         gemm, attn = self.gemm_tcgen05_status(), self.attention_status()
         if gemm or attn:
+            ws = getattr(self, "_stream_ws", None)
+            if ws is not None:
+                ws[1].zero_()
             raise KernelError(f"a kernel gave up a bounded wait (tcgen05 product: code {gemm}, decode attention: code {attn}); "
                               "the step's results are not valid")
 
