@@ -9,7 +9,10 @@ that each hold ``--context`` tokens, timed on the device with CUDA events; ``e2e
 Python entry point (``RoostEngine.step``: host token ids in from pinned memory, sampled ids back to the host,
 every step). ``prefill`` is one 2,048-token prompt; ``roofline`` the decode step's bytes (every weight once and
 the live requests' cache) over its time against the measured copy bandwidth; ``points`` decode at batch 1 and
-64. Weights are seeded random values, token ids seeded uniform-random, and the contexts of the device-timed
+64 at the same context and at batch 1, 8 and 64 with 1,024-token contexts (tokens a second; ``points_detail`` has each
+point's step time and roofline fraction); ``other_sizes`` the same figures at the Qwen3-0.6B and -32B layer sizes and
+the 0.6B serving workload. After every timed region the kernels' status words are read: a bounded wait given up inside
+it fails the run instead of printing a fast, wrong number. Weights are seeded random values, token ids seeded uniform-random, and the contexts of the device-timed
 decode runs are filled with random keys and values instead of being prefilled (their values do not change the
 work of a decode step); the e2e run prefills its contexts for real through the engine.
 
@@ -170,6 +173,7 @@ def timed_decode(model, batch: int, context: int, steps: int, warmup: int):
         torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / steps
     launches = k.launches - launches0
+    k.check_device_status()   # a bounded wait given up inside the timed region would make the figure a fast, wrong one: fail instead
     ex.close()
     del ex
     gc.collect()
@@ -195,6 +199,7 @@ def timed_prefill(model, tokens_n: int, warmup: int = 3, iters: int = 6):
         ex.finish("p")
         if i >= warmup:
             times.append(e0.elapsed_time(e1))
+    model.rt.kernels.check_device_status()
     ex.close()
     del ex
     gc.collect()
@@ -239,9 +244,10 @@ def timed_e2e(model, batch: int, context: int, steps: int, warmup: int):
         assert len(events) == batch, "a request left the batch inside the timed region"
         produced += sum(1 for e in events if e.token is not None)
         h2d += engine.executor.last_upload_bytes
-        d2h += 4 * len(events)
+        d2h += 4 * (len(events) + 4)     # the sampled ids and the kernels' four status words, one pinned copy
     torch.cuda.synchronize()
     dt = time.perf_counter() - t0
+    engine.check_device()
     engine.executor.close()
     del engine
     gc.collect()
@@ -287,6 +293,7 @@ def timed_serving(model, requests: int, budget: int, new_tokens: int, max_prompt
             produced += sum(1 for e in events if e.token is not None)
         torch.cuda.synchronize()
         dt = time.perf_counter() - t0
+        engine.check_device()
         stats = engine.stats()
         stats["steps"] -= steps0
         replays = engine.executor.prepared_replays - replays0
@@ -351,7 +358,10 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--point-batches", default="1,64", help="batch sizes of the extra decode points (the 32B configuration names 1, 8 and 32)")
+    ap.add_argument("--point-contexts", default="1024", help="further context lengths of the decode points (the 8B configuration starts at 1,024)")
+    ap.add_argument("--point-context-batches", default="1,8,64", help="batch sizes measured at each of --point-contexts")
     ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--skip-other-sizes", action="store_true", help="leave out the 0.6B and 32B figures that the 8B line carries")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -368,14 +378,17 @@ def main() -> int:
     args.layers = args.layers or sizes["num_hidden_layers"]
     model, cfg = build_model(args.layers, torch.bfloat16, sizes=sizes)
     tps, ms, launches, clocks = timed_decode(model, args.batch, args.context, args.steps, warmup)
-    decode_bytes = matrix_bytes(cfg) + args.batch * args.context * kv_bytes_per_token(cfg)
-    achieved = decode_bytes / (ms / 1e3) / 1e9
+    roof = decode_roofline(cfg, args.batch, args.context, ms, pk)
     pre_ms = timed_prefill(model, args.prefill_tokens)
-    pre_flops = prefill_flops(cfg, args.prefill_tokens)
-    points = {}
+    points, detail = {}, {}
     if not args.skip_points:
-        for b in [int(x) for x in args.point_batches.split(",") if x.strip()]:
-            points[f"decode_b{b}"] = round(timed_decode(model, b, args.context, max(8, args.steps // 2), warmup)[0], 1)
+        # the rest of the metric at these sizes: the other batches at this context, and every batch at 1,024 tokens
+        todo = [(b, args.context) for b in _ints(args.point_batches)] + [(b, c) for c in _ints(args.point_contexts) for b in _ints(args.point_context_batches)]
+        for b, c in todo:
+            name = f"decode_b{b}" + ("" if c == args.context else f"_ctx{c}")
+            p_tps, p_ms, _, _ = timed_decode(model, b, c, max(8, args.steps // 2), warmup)
+            points[name] = round(p_tps, 1)
+            detail[name] = {"ms_per_step": round(p_ms, 4), "roofline_frac": decode_roofline(cfg, b, c, p_ms, pk)["frac"]}
     e2e = None
     if not args.skip_e2e:
         v, bi, bo = timed_e2e(model, args.batch, args.context, args.steps, warmup)
@@ -391,16 +404,61 @@ def main() -> int:
                    "q_heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
                    "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"], "page_size": PAGE,
                    "l2": "inputs larger than L2: each step streams all weights (>10 GB) from HBM", "peaks": pk_kind},
-        "prefill": {"value": round(args.prefill_tokens / (pre_ms / 1e3), 1), "tokens": args.prefill_tokens, "ms": round(pre_ms, 3),
-                    "frac": round(pre_flops / (pre_ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)},
-        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
-                     "frac": round(achieved / pk["hbm_gbs"], 4)},
-        "points": points, "clocks": clocks, "gpu_launches": launches,
+        "prefill": prefill_record(cfg, args.prefill_tokens, pre_ms, pk),
+        "roofline": roof,
+        "points": points, "points_detail": detail, "clocks": clocks, "gpu_launches": launches,
     }
     if e2e is not None:
         line["e2e"] = e2e
+    del model
+    gc.collect()
+    torch.cuda.empty_cache()
+    if args.sizes == "8b" and not args.skip_other_sizes:
+        # the baseline's other two configurations, each measured the same way (device-timed decode, one prefill), and the
+        # serving workload of the smallest; the largest last, alone on the device (its weights are 65 GB)
+        line["other_sizes"] = {name: other_sizes_record(name, args, warmup, pk) for name in ("0.6b", "32b")}
     print(json.dumps(line))
     return 0
+
+
+def _ints(text: str) -> list:
+    return [int(x) for x in text.split(",") if x.strip()]
+
+
+def decode_roofline(cfg: dict, batch: int, context: int, ms: float, pk: dict) -> dict:
+    """The decode step against the copy bandwidth: the bytes it has to read (every weight once, the live requests' keys
+    and values) over its time."""
+    achieved = (matrix_bytes(cfg) + batch * context * kv_bytes_per_token(cfg)) / (ms / 1e3) / 1e9
+    return {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": round(achieved / pk["hbm_gbs"], 4)}
+
+
+def prefill_record(cfg: dict, tokens: int, ms: float, pk: dict) -> dict:
+    """``frac`` is against the burst rate of a cuBLAS product timed alone; ``frac_sustained`` against the rate of a
+    seconds-long loop under the power cap (the state a 36-layer step is in)."""
+    rate = prefill_flops(cfg, tokens) / (ms / 1e3)
+    rec = {"value": round(tokens / (ms / 1e3), 1), "tokens": tokens, "ms": round(ms, 3), "frac": round(rate / (pk["bf16_tflops"] * 1e12), 4)}
+    if pk.get("bf16_tflops_sustained"):
+        rec["frac_sustained"] = round(rate / (pk["bf16_tflops_sustained"] * 1e12), 4)
+    return rec
+
+
+def other_sizes_record(name: str, args, warmup: int, pk: dict) -> dict:
+    import torch
+    sizes = SIZES[name]
+    model, cfg = build_model(sizes["num_hidden_layers"], torch.bfloat16, sizes=sizes)
+    steps = max(8, args.steps // 2)
+    rec = {"layers": sizes["num_hidden_layers"]}
+    for b in (1, 8, 32 if name == "32b" else 64):
+        tps, ms, _, _ = timed_decode(model, b, args.context, steps, warmup)
+        rec[f"decode_b{b}"] = {"value": round(tps, 1), "ms_per_step": round(ms, 4), "roofline_frac": decode_roofline(cfg, b, args.context, ms, pk)["frac"]}
+    rec["prefill"] = prefill_record(cfg, args.prefill_tokens, timed_prefill(model, args.prefill_tokens, warmup=2, iters=3), pk)
+    if name == "0.6b":
+        r = timed_serving(model, args.requests, args.budget, args.new_tokens, args.max_prompt)
+        rec["serving"] = {k: r[k] for k in ("output_tokens_per_s", "total_tokens_per_s", "steps", "mixed_ms_per_step", "decode_ms_per_step", "preemptions")}
+    del model
+    gc.collect()
+    torch.cuda.empty_cache()
+    return rec
 
 
 if __name__ == "__main__":

@@ -466,13 +466,18 @@ __global__ void __launch_bounds__(128) attention_prefill_kernel(const __nv_bfloa
 // ------------------------------------------------------------------------------------------------ decode
 // work[i] = (batch row, first key of the chunk, one past its last key, partial slot or -1 for a row with one chunk)
 // Partial results of slot s and key/value head h: part_o[(s * kv_heads + h) * 16 + row][D], part_ml[...][2].
+// slot_limit: partial slots the workspace holds. An item that names a slot at or beyond it is skipped and code 9 is
+// recorded for roost_attention_status(): a work list that does not match the workspace must not write past it.
+__device__ int g_attention_error = 0;   // 0, or the code of the first fault a decode kernel met since it was last read
+constexpr int kNoSlotLimit = 0x7fffffff;
 template <int D, int NWARPS>
 __global__ void __launch_bounds__(NWARPS * 32)
     attention_decode_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ k_pool,
                             const __nv_bfloat16* __restrict__ v_pool, const int32_t* __restrict__ q_indptr,
                             const int32_t* __restrict__ kv_lens, const int32_t* __restrict__ kv_indptr,
                             const int32_t* __restrict__ kv_indices, const int4* __restrict__ work, float* __restrict__ part_o,
-                            float* __restrict__ part_ml, int q_heads, int kv_heads, int page_size, int page_shift, float scale_log2, int window) {
+                            float* __restrict__ part_ml, int q_heads, int kv_heads, int page_size, int page_shift, float scale_log2, int window,
+                            int slot_limit) {
   constexpr int BN = kDecodeTileKeys, STAGES = kDecodeStages;
   extern __shared__ __align__(128) unsigned char smem_raw[];
   const uint32_t smem = (uint32_t)__cvta_generic_to_shared(smem_raw);
@@ -489,6 +494,10 @@ __global__ void __launch_bounds__(NWARPS * 32)
   const int4 w = work[blockIdx.x];
   const int b = w.x, kv_begin = w.y, kv_end = w.z, slot = w.w;
   if (b < 0) return;  // padding of a fixed-size work list
+  if (slot >= slot_limit) {
+    if (tid == 0) atomicCAS(&g_attention_error, 0, 9);
+    return;
+  }
   const int kvh = blockIdx.y;
   const int group = q_heads / kv_heads;
   const int q_start = q_indptr[b];
@@ -626,7 +635,6 @@ __global__ void __launch_bounds__(NWARPS * 32)
 constexpr int kTmaTileKeys = 32;
 constexpr int kTmaConsumers = 4;
 constexpr int kTmaMergeRows = 2;  // packed rows merged per pass
-__device__ int g_attention_error = 0;
 
 // A tile of TK keys as the copies leave it: [page of RPC rows][K, V][D / 64 column blocks][RPC][64 bfloat16], 128-byte
 // swizzle, 1024-byte aligned. offset() is relative to the tile's keys; the values follow at kValues.
@@ -956,12 +964,16 @@ constexpr int kMergeAhead = 9;  // chunks whose partial results a merge thread l
 // merge_work[i] = (batch row, first partial slot, number of chunks | packed rows << 24, the row's first token)
 template <int D>
 __global__ void attention_merge_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                       const int4* __restrict__ merge_work, int q_heads, int kv_heads) {
+                                       const int4* __restrict__ merge_work, int q_heads, int kv_heads, int slot_limit) {
   pdl_launch_dependents(5);
   const int4 w = merge_work[blockIdx.x];  // the step's work lists are on the device before the step's first kernel runs
   const int b = w.x, slot0 = w.y, chunks = w.z & 0xffffff, rows_total = w.z >> 24, q_start = w.w;
   pdl_wait(5);
   if (b < 0) return;  // padding of a fixed-size work list
+  if (slot0 < 0 || chunks > slot_limit - slot0) {  // the row's partial slots do not all lie in the workspace: see the decode kernel
+    if (threadIdx.x == 0) atomicCAS(&g_attention_error, 0, 9);
+    return;
+  }
   const int kvh = blockIdx.y;
   const int group = q_heads / kv_heads;
   const size_t stride = (size_t)kv_heads * 16;  // partial rows from one chunk's slot to the next
@@ -1134,11 +1146,11 @@ template <int D>
 static int launch_decode(const void* q, void* out, const void* k_pool, const void* v_pool, const int32_t* q_indptr, const int32_t* kv_lens,
                          const int32_t* kv_indptr, const int32_t* kv_indices, const int32_t* work, int items, const int32_t* merge_work,
                          int merge_items, int merge_rows, float* part_o, float* part_ml, int q_heads, int kv_heads, int page_size,
-                         long long pool_pages, float scale, int window, cudaStream_t s) {
+                         long long pool_pages, float scale, int window, cudaStream_t s, int slot_limit = kNoSlotLimit) {
   int rc = ROOST_OK;
   bool launched = false;
   if constexpr (D == 64 || D == 128) {
-    if (decode_tma_serves(D, page_size, pool_pages, kv_heads, k_pool, v_pool)) {
+    if (slot_limit == kNoSlotLimit && decode_tma_serves(D, page_size, pool_pages, kv_heads, k_pool, v_pool)) {
       rc = launch_decode_tma<D>(q, out, k_pool, v_pool, q_indptr, kv_lens, kv_indptr, kv_indices, work, items, part_o, part_ml, q_heads,
                                 kv_heads, page_size, pool_pages, scale, window, s);
       launched = true;
@@ -1148,20 +1160,22 @@ static int launch_decode(const void* q, void* out, const void* k_pool, const voi
     constexpr int NW = 4;
     const size_t smem = (size_t)16 * D * 2 + (size_t)NW * kDecodeStages * 2 * kDecodeTileKeys * D * 2;
     auto kernel = attention_decode_kernel<D, NW>;
-    static bool attr_set = false;
-    if (smem > 48 * 1024 && !attr_set) {
+    static bool attr_set[64] = {};   // per device: the attribute belongs to the kernel as loaded on that device
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (smem > 48 * 1024 && (dev < 0 || dev >= 64 || !attr_set[dev])) {
       cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-      attr_set = true;
+      if (dev >= 0 && dev < 64) attr_set[dev] = true;
     }
     launch_kernel(kernel, dim3(items, kv_heads), dim3(NW * 32), smem, s, (const __nv_bfloat16*)q, (__nv_bfloat16*)out,
                   (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, q_indptr, kv_lens, kv_indptr, kv_indices, (const int4*)work, part_o,
-                  part_ml, q_heads, kv_heads, page_size, page_shift_of(page_size), scale * kLog2e, window);
+                  part_ml, q_heads, kv_heads, page_size, page_shift_of(page_size), scale * kLog2e, window, slot_limit);
     rc = check_launch("attention_decode");
   }
   if (rc != ROOST_OK || merge_items == 0) return rc;
   const int rows = merge_rows < 1 ? 1 : (merge_rows > 16 ? 16 : merge_rows);  // blocks along z; each walks the rows beyond
   launch_kernel(attention_merge_kernel<D>, dim3(merge_items, kv_heads, rows), dim3(D < 128 ? D : 128), 0, s, (__nv_bfloat16*)out,
-                (const float*)part_o, (const float*)part_ml, (const int4*)merge_work, q_heads, kv_heads);
+                (const float*)part_o, (const float*)part_ml, (const int4*)merge_work, q_heads, kv_heads, slot_limit);
   return check_launch("attention_merge");
 }
 
@@ -1332,13 +1346,16 @@ extern "C" int roost_attention_decode_static(const void* q, void* out, const voi
   float* scratch = nullptr;
   const int rc = static_scratch(&scratch);
   if (rc != ROOST_OK) return rc;
+  // `slots` is also the limit the kernels hold the work lists to: an item that names a slot at or beyond it is skipped
+  // (its output rows stay unwritten) and roost_attention_status() reports code 9, so a work list that disagrees with
+  // `slots` cannot make the kernels write past the library's array into whatever lies behind it.
   // Nothing in the array has to start at zero: the decode kernel writes every element of a slot that the merge kernel
   // reads (all rows below the request's packed-row count, for every key/value head), so what an earlier call left
   // behind is never read.
   ROOST_DISPATCH_HEAD_DIM(head_dim, D, return launch_decode<D>(q, out, k_pool, v_pool, q_indptr, kv_lens, kv_indptr, kv_indices, work, items,
                                                                 merge_work, merge_items, 16, scratch, scratch + o_padded, q_heads, kv_heads,
                                                                 page_size, /*pool_pages unknown: the cp.async kernel*/ 0, scale, window,
-                                                                (cudaStream_t)stream));
+                                                                (cudaStream_t)stream, /*slot_limit*/ slots));
   return ROOST_OK;
 }
 

@@ -108,7 +108,8 @@ int roost_paged_attention_generic(const void* q, void* out, const void* k_pool, 
  * on 128-byte boundaries, decode streams keys and values through the copy engine (TMA) unless
  * roost_attention_set_decode_tma(0) was called; 0 when not known (the cp.async kernel runs). It copies whole pages:
  * every slot of a page a block table names must be readable, whatever it holds.
- * roost_attention_status(): 0, or the code of a wait the copy-engine kernel gave up (read and cleared). */
+ * roost_attention_status(): 0, or the code of a wait the copy-engine kernel gave up, or 9 when a work item named a
+ * partial slot beyond the workspace of roost_attention_decode_static (read and cleared). */
 int roost_attention_mma_supported(int head_dim);
 int roost_attention_prefill_tile_rows(int head_dim, int q_heads, int kv_heads, int page_size, long long pool_pages, const void* k_pool,
                                       const void* v_pool, long long packed_rows);
@@ -137,7 +138,9 @@ int roost_attention_status(void);
  * make that first call outside any stream capture. All calls share the one array and it keeps what the last call
  * wrote; nothing in it needs clearing, because a call writes every element it later reads. Two calls that overlap
  * on the GPU (different streams, or one stream's call still running when another is launched elsewhere) race on the
- * array: order them on one stream or with events. */
+ * array: order them on one stream or with events. `slots` must exceed every slot id the work lists name: an item that
+ * names a slot at or beyond it is skipped, its output rows stay unwritten and roost_attention_status() returns 9, so that
+ * a wrong work list cannot write past the library's array. */
 int roost_attention_decode_static_capacity_floats(void);
 int roost_attention_decode_static(const void* q, void* out, const void* k_pool, const void* v_pool, const int32_t* q_indptr,
                                   const int32_t* kv_lens, const int32_t* kv_indptr, const int32_t* kv_indices,
@@ -150,12 +153,6 @@ int roost_attention_decode_static(const void* q, void* out, const void* k_pool, 
 int roost_gemm_simt(const void* a, const void* w, void* out, int m, int n, int k, int64_t lda, int64_t ldw,
                     int64_t ldo, int in_dtype, int out_dtype, roost_stream_t stream);
 
-/* out[m,n] = sum_k x[m,k] * w[n,k] for 1 <= m <= 32 rows of bfloat16 x: weight-streaming, 32-bit accumulation
- * (gemm_skinny.cu). roost_gemm_skinny_supported tells whether the sizes are served (n a multiple of 16, k a multiple
- * of 32 and at least 256, rows of x and w on 16-byte boundaries). out_dtype: 1 bfloat16, 0 float32. */
-int roost_gemm_skinny_supported(int m, int n, int k, int64_t ldx, int64_t ldw);
-int roost_gemm_skinny(const void* x, const void* w, void* out, int m, int n, int k, int64_t ldx, int64_t ldw, int64_t ldo,
-                      int out_dtype, roost_stream_t stream);
 
 /* out[m,n] = sum_k a[m,k] * w[n,k], bfloat16 operands, 32-bit accumulation in tensor memory (tcgen05.mma fed by TMA;
  * gemm_tcgen05.cu). k and the row strides must be multiples of 8. out_dtype: 1 bfloat16, 0 float32. Every wait inside

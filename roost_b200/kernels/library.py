@@ -76,8 +76,6 @@ _SIGNATURES = {
                                c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, ctypes.c_longlong, c_float, c_int,
                                c_void_p],
     "roost_gemm_simt": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int, c_int, c_void_p],
-    "roost_gemm_skinny_supported": [c_int, c_int, c_int, c_int64, c_int64],
-    "roost_gemm_skinny": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int, c_void_p],
     "roost_gemm_tcgen05_supported": [c_int, c_int, c_int, c_int64, c_int64],
     "roost_gemm_tcgen05": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int, c_void_p],
     "roost_gemm_tcgen05_status": [],
@@ -291,22 +289,6 @@ class KernelLibrary:
                    dtype_code(a.dtype), dtype_code(out_dtype), _stream())
         return out
 
-    def gemm_skinny_supported(self, m: int, n: int, k: int, ldx: int, ldw: int) -> bool:
-        return bool(self._lib.roost_gemm_skinny_supported(m, n, k, ldx, ldw))
-
-    def gemm_skinny(self, x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
-        """x [M <= 32, K] times w [N, K] transposed, bfloat16 operands streamed once, 32-bit accumulation."""
-        _need(x, "x", torch.bfloat16); _need(w, "w", torch.bfloat16)
-        M, K = x.shape
-        N, K2 = w.shape
-        if K != K2:
-            raise KernelError(f"gemm_skinny: x has {K} columns, w has {K2}")
-        out_dtype = out_dtype or torch.bfloat16
-        out = torch.empty((M, N), dtype=out_dtype, device=x.device)
-        self._call("roost_gemm_skinny", _ptr(x), _ptr(w), _ptr(out), M, N, K, x.stride(0), w.stride(0), out.stride(0),
-                   dtype_code(out_dtype), _stream())
-        return out
-
     def gemm_tcgen05_supported(self, m: int, n: int, k: int, lda: int, ldw: int) -> bool:
         return bool(self._lib.roost_gemm_tcgen05_supported(m, n, k, lda, ldw))
 
@@ -457,6 +439,10 @@ def load() -> KernelLibrary:
             raise KernelError(f"the GPU has compute capability {major}.{minor}; the kernel library is built for sm_100a only")
         _LIB = KernelLibrary(build.library_path())
         import os
+        # The bfloat16 products that go to cuBLAS through torch accumulate in 32-bit, as the reference asks of its library
+        # (CUBLAS_COMPUTE_32F, kernels/src/gemm.cu:247-249). torch's default also lets a split-k product add its partial
+        # sums up in bfloat16; that is switched off here, so that every sum of the bfloat16 path is a 32-bit sum.
+        torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
         # programmatic dependent launch is on unless ROOST_PDL=0: the library's kernels overlap their preambles, and the
         # weight-streaming product its first loads of weights, with the tail of the kernel before them
         _LIB.set_pdl(os.environ.get("ROOST_PDL", "1") != "0")

@@ -4,6 +4,7 @@
     python -m roost_b200.kernels.microbench attention-prefill --tokens 8192
     python -m roost_b200.kernels.microbench gemm-small --rows 8
     python -m roost_b200.kernels.microbench gemm-large --rows 2048
+    python -m roost_b200.kernels.microbench sample --vocab 151936 --sample-rows 1,8,64
 
 Each case prints one line per measurement: the time of one call, the achieved bandwidth or arithmetic rate, and what
 the same bytes or operations would take at the device's measured peaks when a peak is given. The inputs are larger
@@ -130,9 +131,36 @@ def gemm_large(k, a) -> None:
         print(f"gemm-large rows={a.rows} n={n} k={kk} cuBLAS: {us:.1f} us, {flops / us / 1e6:.0f} TFLOP/s; status {k.gemm_tcgen05_status()}", flush=True)
 
 
+def sample(k, a) -> None:
+    """The argmax and the sampling kernel over rows of a vocabulary's logits, at the batch sizes of the benchmark."""
+    import torch
+    V = a.vocab
+    for rows in [int(x) for x in a.sample_rows.split(",")]:
+        copies = max(2, int(300e6 // (rows * V * 4)))       # rotate through more than L2 holds
+        logits = [torch.randn(rows, V, device="cuda") * 3 for _ in range(copies)]
+        ws = torch.empty(rows, V, device="cuda")
+        t = torch.full((rows,), a.temperature, device="cuda")
+        tk = torch.full((rows,), a.top_k, dtype=torch.int32, device="cuda")
+        tp = torch.full((rows,), a.top_p, device="cuda")
+        mp = torch.zeros(rows, device="cuda")
+        seeds = torch.arange(rows, dtype=torch.int64, device="cuda") + 99
+        offs = torch.zeros(rows, dtype=torch.int64, device="cuda")
+        turn = [0]
+
+        def next_logits():
+            turn[0] = (turn[0] + 1) % copies
+            return logits[turn[0]]
+
+        us_arg = _time(lambda: k.argmax(next_logits()), a.warmup, a.iters)
+        us_smp = _time(lambda: k.sample(next_logits(), t, tk, tp, mp, seeds, offs, ws), a.warmup, a.iters)
+        nbytes = rows * V * 4
+        print(f"sample rows={rows} vocab={V} temperature={a.temperature} top_k={a.top_k} top_p={a.top_p}: argmax {us_arg:.1f} us "
+              f"({nbytes / us_arg / 1e6:.2f} TB/s), sampler {us_smp:.1f} us ({nbytes / us_smp / 1e6:.3f} TB/s of one pass over the logits)", flush=True)
+
+
 def main(argv=None) -> int:
     p = argparse.ArgumentParser(prog="python -m roost_b200.kernels.microbench", description=__doc__.split("\n")[0])
-    p.add_argument("case", choices=["attention-decode", "attention-prefill", "gemm-small", "gemm-large"])
+    p.add_argument("case", choices=["attention-decode", "attention-prefill", "gemm-small", "gemm-large", "sample"])
     p.add_argument("--batch", type=int, default=8)
     p.add_argument("--context", type=int, default=4096)
     p.add_argument("--tokens", type=int, default=2048)
@@ -148,12 +176,17 @@ def main(argv=None) -> int:
     p.add_argument("--cp-async", action="store_true", help="decode attention through the cp.async kernel instead of TMA")
     p.add_argument("--mma-sync", action="store_true", help="prefill attention through the mma.sync kernel instead of tcgen05")
     p.add_argument("--sequential-pages", action="store_true")
+    p.add_argument("--vocab", type=int, default=151936)
+    p.add_argument("--sample-rows", default="1,8,64")
+    p.add_argument("--temperature", type=float, default=0.8)
+    p.add_argument("--top-k", type=int, default=0)
+    p.add_argument("--top-p", type=float, default=0.9)
     p.add_argument("--iters", type=int, default=10)
     p.add_argument("--warmup", type=int, default=3)
     a = p.parse_args(argv)
     from . import library
     k = library.load()
-    {"attention-decode": attention_decode, "attention-prefill": attention_prefill, "gemm-small": gemm_small, "gemm-large": gemm_large}[a.case](k, a)
+    {"attention-decode": attention_decode, "attention-prefill": attention_prefill, "gemm-small": gemm_small, "gemm-large": gemm_large, "sample": sample}[a.case](k, a)
     return 0
 
 

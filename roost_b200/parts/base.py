@@ -54,10 +54,10 @@ class Runtime:
         self.dtype = dtype
         self.device = torch.device(device)
         self.kernels = kernels
-        # products of at most 64 rows: "auto" | "library" | "stream" | "skinny" (parts/linear.py)
+        # products of at most 64 rows: "auto" | "library" | "stream" (parts/linear.py)
         self.small_gemm = os.environ.get("ROOST_SMALL_GEMM", "auto")
-        if self.small_gemm not in ("auto", "library", "stream", "skinny"):
-            raise ValueError(f"ROOST_SMALL_GEMM={self.small_gemm!r} is not one of auto, library, stream, skinny")
+        if self.small_gemm not in ("auto", "library", "stream"):
+            raise ValueError(f"ROOST_SMALL_GEMM={self.small_gemm!r} is not one of auto, library, stream")
 
     @property
     def full_precision(self) -> bool:

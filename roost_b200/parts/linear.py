@@ -5,7 +5,7 @@ with 32-bit accumulation goes to cuBLAS through torch, the place where the refer
 library (kernels/src/gemm.cu:235), except where a kernel of this library is faster. ``Runtime.small_gemm`` decides for
 products of at most 64 rows (decode steps): "auto" streams the weights through the TMA/tcgen05 kernel where that was
 measured faster than cuBLAS on a B200 (at most 16 rows and a reduction length of 8192 or more, or the vocabulary-sized
-head) and leaves the rest to cuBLAS; "stream" and "skinny" force one of the library's kernels, "library" forces cuBLAS.
+head) and leaves the rest to cuBLAS; "stream" forces the library's kernel wherever it serves, "library" forces cuBLAS.
 """
 from __future__ import annotations
 
@@ -40,9 +40,6 @@ class Linear:
             if policy == "stream" or (policy == "auto" and M <= 16 and (self.in_features >= 8192 or self.out_features >= 65536)):
                 if k.gemm_stream_supported(M, self.out_features, self.in_features, x.stride(0), self.weight.stride(0)):
                     return k.gemm_stream(x, self.weight, out_dtype)   # weights streamed once by TMA, tcgen05 products
-            if policy == "skinny" and M <= 32 and k.gemm_skinny_supported(M, self.out_features, self.in_features, x.stride(0),
-                                                                          self.weight.stride(0)):
-                return k.gemm_skinny(x, self.weight, out_dtype)
         if out_dtype == torch.bfloat16:
             k.launches += 1
             return torch.matmul(x, self.weight.t())

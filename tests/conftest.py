@@ -41,7 +41,15 @@ TINY_C = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden
               num_attention_heads=3, num_key_value_heads=3, head_dim=48, intermediate_size=100, vocab_size=131,
               rope_theta=50000.0, rms_norm_eps=1e-6, tie_word_embeddings=True, max_position_embeddings=300,
               torch_dtype="float32", hidden_act="silu", sliding_window=24, use_sliding_window=True, max_window_layers=1)
+# A fourth one that the tensor-core attention kernels serve in bfloat16 (head size 64, pages of 16 rows: the copy-engine
+# decode kernel and the tcgen05 prefill kernel) with a sliding-window layer, so that those kernels meet block tables whose
+# leading pages a window has passed and given back.
+TINY_D = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=2, hidden_size=120,
+              num_attention_heads=4, num_key_value_heads=2, head_dim=64, intermediate_size=200, vocab_size=301,
+              rope_theta=100000.0, rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=2048,
+              torch_dtype="bfloat16", hidden_act="silu", sliding_window=48, layer_types=["sliding_attention", "full_attention"])
 TINY = {"C": dict(config=TINY_C, seed=2, std=0.1, norm_std=0.05, page_size=4),
+        "D": dict(config=TINY_D, seed=3, std=0.07, norm_std=0.1, page_size=16),
         "A": dict(config=TINY_A, seed=0, std=0.08, norm_std=0.0, page_size=16),
         "B": dict(config=TINY_B, seed=1, std=0.06, norm_std=0.1, page_size=8)}
 

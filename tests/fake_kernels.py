@@ -95,9 +95,6 @@ class FakeKernels:
     def gemm_stream_supported(self, *a):
         return False
 
-    def gemm_skinny_supported(self, *a):
-        return False
-
     def gemm_stream_swiglu_supported(self, *a):
         return False
 

@@ -185,8 +185,9 @@ def normalise_config(cfg: dict) -> dict:
     return cfg
 
 
-def forward_logits(cfg: dict, w: dict[str, torch.Tensor], ids, schedule=None) -> torch.Tensor:
-    """Logits [T, vocab] at every position of one whole sequence
+def forward_logits(cfg: dict, w: dict[str, torch.Tensor], ids, schedule=None, rows=None) -> torch.Tensor:
+    """Logits [T, vocab] at every position of one whole sequence (or, with ``rows``, at those positions only: the
+    final norm and the head are per position, so the other positions' logits need not be formed)
     (src/Starlings.Roost.Models.Tiny/RoostTiny.cs:39-56; the shape of the reference's TinyReference,
     tests/Starlings.Roost.Models.Tiny.Tests/Support/TinyReference.cs:22-102).
 
@@ -211,6 +212,8 @@ def forward_logits(cfg: dict, w: dict[str, torch.Tensor], ids, schedule=None) ->
         h = h + mix
         y = rms_norm(h, w[p + "post_attention_layernorm.weight"], eps)
         h = h + swiglu_mlp(y, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"])
+    if rows is not None:
+        h = h[torch.as_tensor(list(rows), dtype=torch.long, device=h.device)]
     final = rms_norm(h, w["model.norm.weight"], eps)
     head = w["lm_head.weight"] if "lm_head.weight" in w and not cfg.get("tie_word_embeddings", False) else w["model.embed_tokens.weight"]
     return final @ head.T

@@ -23,7 +23,7 @@ def backend(request):
     return request.param
 
 
-@pytest.fixture(params=["A", "B", "C"])
+@pytest.fixture(params=["A", "B", "C", "D"])
 def tiny(request, tiny_model_dirs):
     return request.param, tiny_model_dirs[request.param], TINY[request.param]
 
@@ -106,6 +106,7 @@ def test_mixed_batches_with_pages_used_again(tiny, backend):
     live_max = max(sum(-(-n // P) for n in lengths[i : i + 4]) for i in range(len(lengths)))
     num_pages = max(live_max, max(sum(sorted(-(-n // P) for n in lengths)[-4:]), live_max))
     ex, dtype = make_executor(tiny, backend, num_pages=num_pages)
+    ex.storage.poison()      # every slot holds NaN until a request writes it: a read of a slot nobody wrote shows in the logits
     reqs = {f"q{i}": H.random_ids(n, t["config"]["vocab_size"], seed=50 + i) for i, n in enumerate(lengths)}
     taken = set()
     orig_extend = ex.cache.extend
@@ -166,7 +167,7 @@ def test_a_step_that_does_not_fit_changes_nothing(tiny, backend):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("policy", ["stream", "skinny", "library"])
+@pytest.mark.parametrize("policy", ["stream", "library"])
 def test_every_small_product_kernel_serves_the_engine(tiny_model_dirs, policy):
     """Decode steps through each of the kernels a product of few rows can run on (the default picks by size)."""
     name, t = "B", TINY["B"]

@@ -1,5 +1,6 @@
 """Each kernel alone against a plain torch float64 restatement of the same op, at sizes other than the engine's
 tiny models: widths and vocabularies that are no power of two, head sizes in steps of 16, odd group sizes."""
+import functools
 import math
 
 import pytest
@@ -215,6 +216,28 @@ def build_paged(keys, values, page, dtype, num_pages, seed):
     return pool[0], pool[1], torch.tensor(indptr, dtype=torch.int32).cuda(), torch.tensor(indices, dtype=torch.int32).cuda()
 
 
+def release_passed_pages(kp, vp, indptr, indices, lens, news, window, page):
+    """What the cache manager's commit leaves of a windowed request before a step: every page wholly below
+    (tokens held before the step) - window has gone back to the pool, its block-table entry is -1 and, here, its
+    slots hold NaN (the pool's next user may have written anything). Returns how many pages were released."""
+    released = 0
+    if not window:
+        return 0
+    table = indices.cpu().clone()
+    ptr = indptr.cpu().tolist()
+    for b, (n, m) in enumerate(zip(lens, news)):
+        start = n - m
+        gone = (start - window) // page if start > window else 0
+        for i in range(gone):
+            pg = int(table[ptr[b] + i])
+            kp[pg] = float("nan")
+            vp[pg] = float("nan")
+            table[ptr[b] + i] = -1
+            released += 1
+    indices.copy_(table)
+    return released
+
+
 ATTN_SHAPES = [(4, 2, 16, 16), (6, 1, 32, 8), (8, 2, 128, 16), (5, 5, 48, 4), (14, 2, 64, 32), (3, 1, 80, 16), (2, 1, 256, 16)]
 
 
@@ -235,6 +258,8 @@ def test_paged_attention_mixed_rows(kernels, dtype, window, nq, nkv, d, page):
     T = len(positions)
     q = (torch.randn(T, nq, d, generator=g) * 1.5).to(dtype)
     kp, vp, indptr, indices = build_paged(keys, values, page, dtype, num_pages=sum(-(-n // page) for n in lens) + 3, seed=12)
+    if window:
+        assert release_passed_pages(kp, vp, indptr, indices, lens, news, window, page) > 0
     scale = 1 / math.sqrt(d)
     out = kernels.paged_attention_generic(q.cuda(), kp, vp, torch.tensor(positions, dtype=torch.int32).cuda(),
                                           torch.tensor(rows, dtype=torch.int32).cuda(), indptr, indices, scale, window)
@@ -308,7 +333,7 @@ def test_argmax_ties_and_nan(kernels):
         assert kernels.argmax(z.cuda()).cpu().tolist() == want
 
 
-@pytest.mark.parametrize("vocab", [387, 5000])
+@pytest.mark.parametrize("vocab", [387, 5000, 151936])
 def test_sampler_matches_the_plain_sampler(kernels, vocab):
     """Rows with different settings in one launch; a row is compared when the plain sampler's draw is not within
     1e-4 of the kept mass from an edge of the chosen token's interval."""
@@ -316,7 +341,7 @@ def test_sampler_matches_the_plain_sampler(kernels, vocab):
     settings = [(0.0, 0, 1.0, 0.0), (1.0, 0, 1.0, 0.0), (0.8, 0, 0.9, 0.0), (0.7, 20, 1.0, 0.0), (1.3, 50, 0.8, 0.0),
                 (1.0, 0, 1.0, 0.05), (0.9, 40, 0.95, 0.02), (0.5, 1, 1.0, 0.0), (2.0, 0, 0.5, 0.0), (1.0, 3, 0.2, 0.0)]
     rows = []
-    for rep in range(4):
+    for rep in range(4 if vocab < 100000 else 1):     # the plain sampler sorts a row in Python: one pass at the real vocabulary
         for s in settings:
             rows.append(s)
     R = len(rows)
@@ -367,15 +392,18 @@ MMA_SHAPES = [(4, 2, 16, 16), (6, 1, 32, 8), (8, 2, 128, 16), (14, 2, 64, 32), (
               (8, 2, 64, 32), (4, 1, 128, 64)]
 
 
+@pytest.mark.parametrize("chunk", [512, 1024])
 @pytest.mark.parametrize("window", [None, 37, 300])
 @pytest.mark.parametrize("nq,nkv,d,page", MMA_SHAPES)
-def test_attention_mma_mixed_rows(kernels, window, nq, nkv, d, page):
+def test_attention_mma_mixed_rows(kernels, window, nq, nkv, d, page, chunk):
     """A whole prompt, a portion in the middle of a request, a two-token portion after a long history, single decoded
-    tokens after short and long histories (several chunks of the split decode kernel), all in one launch."""
+    tokens after short and long histories (several chunks of the split decode kernel, for both chunk sizes the engine
+    uses), all in one launch. Under a window the pages the window has passed are gone (entry -1, slots NaN), as the cache
+    manager leaves them."""
     dtype = torch.bfloat16
     g = torch.Generator().manual_seed(21)
-    lens = [45, 233, 700, 19, 1000, 257]
-    news = [45, 121, 2, 1, 1, 1]
+    lens = [45, 233, 700, 19, 1000, 257, 2300]
+    news = [45, 121, 2, 1, 1, 1, 1]
     keys = [torch.randn(n, nkv, d, generator=g).to(dtype).double() for n in lens]
     values = [torch.randn(n, nkv, d, generator=g).to(dtype).double() for n in lens]
     positions, rows = [], []
@@ -384,8 +412,12 @@ def test_attention_mma_mixed_rows(kernels, window, nq, nkv, d, page):
         rows += [b] * m
     q = (torch.randn(len(positions), nq, d, generator=g) * 1.5).to(dtype)
     kp, vp, indptr, indices = build_paged(keys, values, page, dtype, num_pages=sum(-(-n // page) for n in lens) + 5, seed=22)
+    if window:
+        assert release_passed_pages(kp, vp, indptr, indices, lens, news, window, page) > 0
     scale = 1 / math.sqrt(d)
-    out, plan = run_mma(kernels, q, kp, vp, lens, news, indptr, indices, scale, window)
+    run = functools.partial(run_mma, chunk=chunk)      # every run below uses this test's chunk size
+
+    out, plan = run(kernels, q, kp, vp, lens, news, indptr, indices, scale, window)
     assert plan.prefill_items > 0 and (nq // nkv > 16 or (plan.decode_items > 0 and (plan.merge_items > 0 or window is not None)))
     want = paged_reference(q.double(), keys, values, positions, rows, scale, window)
     assert not torch.isnan(out.float()).any(), "a slot outside the rows' visible keys was read"
@@ -399,7 +431,7 @@ def test_attention_mma_mixed_rows(kernels, window, nq, nkv, d, page):
     # the decode rows again through the cp.async kernel (where the copy-engine kernel served them above)
     kernels.attention_set_decode_tma(False)
     try:
-        plain_copy, _ = run_mma(kernels, q, kp, vp, lens, news, indptr, indices, scale, window)
+        plain_copy, _ = run(kernels, q, kp, vp, lens, news, indptr, indices, scale, window)
     finally:
         kernels.attention_set_decode_tma(True)
     assert kernels.attention_status() == 0, "a bounded wait inside the decode kernel was given up"
@@ -408,7 +440,7 @@ def test_attention_mma_mixed_rows(kernels, window, nq, nkv, d, page):
     # the prompt portions again through the mma.sync kernel (where the tcgen05 kernel served them above)
     kernels.attention_set_prefill_tc(False)
     try:
-        legacy, _ = run_mma(kernels, q, kp, vp, lens, news, indptr, indices, scale, window)
+        legacy, _ = run(kernels, q, kp, vp, lens, news, indptr, indices, scale, window)
     finally:
         kernels.attention_set_prefill_tc(True)
     assert kernels.attention_status() == 0, "a bounded wait inside an attention kernel was given up"
@@ -419,29 +451,33 @@ def test_attention_mma_mixed_rows(kernels, window, nq, nkv, d, page):
     assert torch.equal(legacy, out) != tc_serves, "the tcgen05 kernel serves exactly these sizes (its tiles round differently)"
     if tc_serves:
         # two row groups a CTA (work items of 256 packed rows) compute every row as one group does
-        both, both_plan = run_mma(kernels, q, kp, vp, lens, news, indptr, indices, scale, window, tile_rows=256)
+        both, both_plan = run(kernels, q, kp, vp, lens, news, indptr, indices, scale, window, tile_rows=256)
         assert both_plan.prefill_items < plan.prefill_items
         assert torch.equal(both, out), "one and two row groups a CTA differ"
     if d <= 128:
         # work items of 128 packed rows (two row tiles a warp) compute every row with the same operations in the same order
         kernels.attention_set_prefill_tc(False)
         try:
-            wide, wide_plan = run_mma(kernels, q, kp, vp, lens, news, indptr, indices, scale, window, tile_rows=128)
-            narrow, narrow_plan = run_mma(kernels, q, kp, vp, lens, news, indptr, indices, scale, window, tile_rows=64)
+            wide, wide_plan = run(kernels, q, kp, vp, lens, news, indptr, indices, scale, window, tile_rows=128)
+            narrow, narrow_plan = run(kernels, q, kp, vp, lens, news, indptr, indices, scale, window, tile_rows=64)
         finally:
             kernels.attention_set_prefill_tc(True)
         assert wide_plan.prefill_items < narrow_plan.prefill_items or nq // nkv * max(news) <= 64
         assert torch.equal(wide, narrow), "64-row and 128-row prefill tiles differ"
 
 
-@pytest.mark.parametrize("case", ["far key", "first key", "page edge", "chunk edge", "window edge in", "window edge out"])
+@pytest.mark.parametrize("case", ["far key", "first key", "page edge", "chunk edge 511", "chunk edge 512", "chunk edge 1023", "chunk edge 1024",
+                                  "window edge in", "window edge out"])
 @pytest.mark.parametrize("queries", [1, 40])
-def test_attention_mma_finds_the_one_key_that_matters(kernels, case, queries):
+@pytest.mark.parametrize("chunk", [512, 1024])
+def test_attention_mma_finds_the_one_key_that_matters(kernels, case, queries, chunk):
     dtype = torch.bfloat16
-    nq, nkv, d, page, n = 4, 2, 64, 16, 700
+    nq, nkv, d, page, n = 4, 2, 64, 16, 1300
     window = 50 if case.startswith("window") else None
     last = n - 1
-    target = {"far key": 3, "first key": 0, "page edge": 16 * 20 - 1, "chunk edge": 256, "window edge in": last - 49, "window edge out": last - 50}[case]
+    # the last and the first key of a chunk of the split decode kernel, for both chunk sizes the engine uses
+    target = {"far key": 3, "first key": 0, "page edge": 16 * 20 - 1, "chunk edge 511": 511, "chunk edge 512": 512, "chunk edge 1023": 1023,
+              "chunk edge 1024": 1024, "window edge in": last - 49, "window edge out": last - 50}[case]
     g = torch.Generator().manual_seed(23)
     keys = torch.randn(n, nkv, d, generator=g) * 0.1
     values = torch.randn(n, nkv, d, generator=g)
@@ -451,7 +487,9 @@ def test_attention_mma_finds_the_one_key_that_matters(kernels, case, queries):
     q[-1, :] = direction * 16.0
     keys_d, values_d = keys.to(dtype).double(), values.to(dtype).double()
     kp, vp, indptr, indices = build_paged([keys_d], [values_d], page, dtype, num_pages=-(-n // page) + 2, seed=24)
-    out, _ = run_mma(kernels, q.to(dtype), kp, vp, [n], [queries], indptr, indices, 1 / math.sqrt(d), window)
+    if window:
+        assert release_passed_pages(kp, vp, indptr, indices, [n], [queries], window, page) > 0
+    out, _ = run_mma(kernels, q.to(dtype), kp, vp, [n], [queries], indptr, indices, 1 / math.sqrt(d), window, chunk=chunk)
     positions = list(range(n - queries, n))
     want = paged_reference(q.to(dtype).double(), [keys_d], [values_d], positions, [0] * queries, 1 / math.sqrt(d), window)
     close(out, want, dtype, f"{case} x{queries}", scale=4)
@@ -460,39 +498,28 @@ def test_attention_mma_finds_the_one_key_that_matters(kernels, case, queries):
     assert hit == (case != "window edge out"), f"{case}: the last query's output {'is' if hit else 'is not'} the target's value"
 
 
-def test_attention_mma_rows_do_not_depend_on_the_batch(kernels):
-    """A decode row alone and the same row among others: the same bits (the chunk size is fixed, so is every sum's order)."""
+@pytest.mark.parametrize("chunk", [512, 1024])
+def test_attention_mma_rows_do_not_depend_on_the_batch(kernels, chunk):
+    """A decode row alone and the same row among others: the same bits (for a given chunk size every sum's order is fixed)."""
     dtype = torch.bfloat16
     nq, nkv, d, page = 8, 2, 128, 16
     g = torch.Generator().manual_seed(25)
-    lens = [900, 300, 1200]
+    lens = [900, 300, 2500]
     keys = [torch.randn(n, nkv, d, generator=g).to(dtype).double() for n in lens]
     values = [torch.randn(n, nkv, d, generator=g).to(dtype).double() for n in lens]
     q = torch.randn(3, nq, d, generator=g).to(dtype)
-    kp, vp, indptr, indices = build_paged(keys, values, page, dtype, num_pages=200, seed=26)
-    together, _ = run_mma(kernels, q, kp, vp, lens, [1, 1, 1], indptr, indices, 0.1, None)
+    kp, vp, indptr, indices = build_paged(keys, values, page, dtype, num_pages=300, seed=26)
+    together, plan = run_mma(kernels, q, kp, vp, lens, [1, 1, 1], indptr, indices, 0.1, None, chunk=chunk)
+    assert plan.merge_items >= 1
     alone, _ = run_mma(kernels, q[2:3], kp, vp, lens[2:], [1], torch.tensor([0, int(indptr[3] - indptr[2])], dtype=torch.int32).cuda(),
-                       indices[int(indptr[2]):].contiguous(), 0.1, None)
+                       indices[int(indptr[2]):].contiguous(), 0.1, None, chunk=chunk)
     assert torch.equal(together[2:3], alone)
-
-
-@pytest.mark.parametrize("m,n,k", [(1, 6144, 4096), (8, 4096, 12288), (5, 272, 320), (20, 64, 256), (32, 1024, 1056), (17, 9504, 512)])
-@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
-def test_gemm_skinny(kernels, m, n, k, out_dtype):
-    assert kernels.gemm_skinny_supported(m, n, k, k, k)
-    a = rand((m, k), torch.bfloat16, 31)
-    w = rand((n, k), torch.bfloat16, 32)
-    want = a.double().cpu() @ w.double().cpu().T
-    got = kernels.gemm_skinny(a, w, out_dtype)
-    if out_dtype == torch.float32:
-        close(got, want, torch.float32, "gemm_skinny f32 out", scale=k * 2.0 ** -23 / 2e-6)
-    else:
-        close(got, want, torch.bfloat16, "gemm_skinny", scale=math.sqrt(k) / 8)
-    # a row's bits do not depend on which other rows are in the product
-    r = m // 2
-    assert torch.equal(kernels.gemm_skinny(a[r : r + 1].contiguous(), w, out_dtype), got[r : r + 1])
-    assert not kernels.gemm_skinny_supported(33, n, k, k, k) and not kernels.gemm_skinny_supported(m, n + 1, k, k, k)
-    assert not kernels.gemm_skinny_supported(m, n, k + 8, k + 8, k + 8) and not kernels.gemm_skinny_supported(m, n, 128, 128, 128)
+    # the two chunk sizes give the same row within rounding (a step's size class picks one of them)
+    other, _ = run_mma(kernels, q, kp, vp, lens, [1, 1, 1], indptr, indices, 0.1, None, chunk=1536 - chunk)
+    positions = [n - 1 for n in lens]
+    want = paged_reference(q.double(), keys, values, positions, [0, 1, 2], 0.1, None)
+    close(together, want, dtype, f"chunk {chunk}", scale=2)
+    close(other, together.double(), dtype, "one chunk size against the other", scale=2)
 
 
 @pytest.mark.parametrize("m,n,k", [(128, 256, 64), (300, 272, 96), (1, 256, 64), (77, 18992, 1024), (2048, 6144, 4096), (513, 512, 12288)])
