@@ -167,6 +167,9 @@ __global__ void __launch_bounds__(256, 4) qk_norm_rope_cache_vec_kernel(
   __shared__ float2 cos_sin[2][kHalf];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int sub = lane / kLanes, c = lane % kLanes;   // which slot of the pass; which four pairs of its head
+  // The lanes of this thread's head slot. A pass may hold a key head beside a value head (or beside no head at all): the
+  // slots of a warp then take different branches, and an exchange may name only the lanes that take it together.
+  const unsigned slot_lanes = kLanes == 32 ? 0xffffffffu : ((1u << kLanes) - 1u) << (sub * kLanes);
   float wq_lo[4], wq_hi[4], wk_lo[4], wk_hi[4];
 #pragma unroll
   for (int e = 0; e < 4; ++e) {
@@ -252,7 +255,7 @@ __global__ void __launch_bounds__(256, 4) qk_norm_rope_cache_vec_kernel(
 #pragma unroll
           for (int e = 0; e < 4; ++e) ss += lo[e] * lo[e] + hi[e] * hi[e];
 #pragma unroll
-          for (int o = kLanes / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o, kLanes);
+          for (int o = kLanes / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(slot_lanes, ss, o, kLanes);
           inv = 1.0f / sqrtf(ss / (float)D + eps);
         }
         float o_lo[4], o_hi[4];

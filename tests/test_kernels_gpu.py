@@ -131,7 +131,11 @@ def test_qk_norm_rope_cache(kernels, dtype, nq, nkv, d, rot, page):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("T,nq,nkv,d,page,weights", [(64, 8, 2, 128, 16, "same"), (300, 5, 3, 64, 8, "float32"), (1100, 3, 1, 256, 32, "same"),
-                                                     (1030, 4, 4, 128, 16, None), (70, 2, 1, 96, 16, "same")])
+                                                     (1030, 4, 4, 128, 16, None), (70, 2, 1, 96, 16, "same"),
+                                                     # head slots that share a warp's pass and take different branches: key
+                                                     # heads beside value heads, a query head beside a key head, a value head
+                                                     # and an empty slot
+                                                     (150, 4, 2, 64, 16, "same"), (70, 5, 1, 64, 16, "float32"), (90, 3, 1, 128, 16, "same")])
 def test_qk_norm_rope_cache_of_many_tokens(kernels, dtype, T, nq, nkv, d, page, weights):
     """Steps of many tokens (bfloat16 heads of 64, 128 or 256 take a kernel of their own): several tokens a block, some
     tokens skipped (slot -1), slots scattered over the pool, norm weights in either dtype or none."""
@@ -345,7 +349,9 @@ def test_sampler_matches_the_plain_sampler(kernels, vocab):
         for s in settings:
             rows.append(s)
     R = len(rows)
-    logits = torch.randn(R, vocab, generator=g) * 3
+    # at the real vocabulary a flatter row gives every token an interval of a few millionths of the mass, within the
+    # margin below of its edges: the rows are made more peaked there so that most draws can be compared
+    logits = torch.randn(R, vocab, generator=g) * (3 if vocab < 100000 else 6)
     logits[3, 10] = float("-inf")
     logits[4, 11] = float("nan")
     logits[5, 40:44] = logits[5, 40]            # ties in the middle of the order
@@ -370,7 +376,7 @@ def test_sampler_matches_the_plain_sampler(kernels, vocab):
         if detail["margin"] > 1e-4:
             assert got[r] == want, f"row {r} {rows[r]}: got {got[r]}, want {want} (margin {detail['margin']:.2e})"
             compared += 1
-    assert compared >= R * 0.8
+    assert compared >= R * (0.8 if vocab < 100000 else 0.7), compared
     # a row's token does not depend on the batch it is in
     one = kernels.sample(logits[7:8].cuda(), t[7:8].cuda(), k[7:8].cuda(), p[7:8].cuda(), mp[7:8].cuda(), seeds[7:8].cuda(), offsets[7:8].cuda())
     assert one.cpu().tolist() == [got[7]]
