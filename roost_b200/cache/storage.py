@@ -3,7 +3,8 @@
 A paged group is one tensor [runs, 2, pages, kv_heads, page_size, head_dim] in the compute dtype: a page id
 addresses the page of every run in the group, as the reference's "bytes per block across all layers" does
 (src/Starlings.Roost.Abstractions/State/StateGroups.cs:83-84); within a page the layout is head-major so that
-one head's keys of a page are contiguous. A state group is one tensor [runs, slots, *state_shape].
+one head's keys of a page are contiguous. A state group is one tensor [runs, slots + 1, *state_shape]: the last slot
+belongs to no request and takes what the padding rows of a captured step write.
 """
 from __future__ import annotations
 
@@ -36,7 +37,8 @@ class CacheStorage:
                 for li, run in enumerate(g.runs):
                     self._view_of_run[run] = CacheView(group=gi, kind="paged", page_size=g.page_size, k_pool=t[li, 0], v_pool=t[li, 1])
             else:
-                t = torch.zeros((max(len(g.runs), 1), cap, *g.state_shape), dtype=g.state_dtype, device=device)
+                # one slot more than the pool hands out: the scratch slot that the padding rows of a captured step name
+                t = torch.zeros((max(len(g.runs), 1), cap + 1, *g.state_shape), dtype=g.state_dtype, device=device)
                 for li, run in enumerate(g.runs):
                     self._view_of_run[run] = CacheView(group=gi, kind="state", state=t[li])
             self.tensors.append(t)

@@ -22,7 +22,7 @@ from ..cache.block_pool import NULL_PAGE
 def pad_row(tokens: int) -> tuple:
     """A row that only fills a captured step up to the rows and tokens it was captured for: ``tokens`` tokens (id 0,
     possibly none) at position -1 of no request. It holds no keys (kv_len 0, an empty page range), writes no key or
-    value (slot -1, which the cache write skips), gets no attention work and wants no logits. A token's values never
+    value (slot -1, which the cache write skips), gets no work from any mixer and wants no logits. A token's values never
     mix with another row's, so whatever a padding row carries stays in it."""
     return (None, -1, [0] * tokens, [])
 
@@ -46,101 +46,37 @@ def padded_rows(rows: list, tokens_cap: int, rows_cap: int) -> list:
 class GroupTables:
     """Per cache group. Paged: ``slot_mapping[t]`` = page * page_size + offset for token t, ``kv_indices``
     the rows' block tables back to back (a page given back to the pool stays as -1), ``kv_indptr`` their
-    bounds. State: ``state_slots[b]`` the row's slot."""
+    bounds. State: ``state_slots[b]`` the row's slot (a padding row names the group's scratch slot, which belongs to no
+    request), ``fresh[b]`` 1 when the row brings its request's first token: the slot is zeroed before the step's blocks
+    run."""
     slot_mapping: torch.Tensor | None = None
     kv_indptr: torch.Tensor | None = None
     kv_indices: torch.Tensor | None = None
     state_slots: torch.Tensor | None = None
+    fresh: torch.Tensor | None = None
 
 
-@dataclass
-class AttentionPlan:
-    """How the tensor-core attention kernels divide a step's rows (see csrc/attention_mma.cu): rows with at most 16
-    packed rows (tokens x query heads per key/value head) go to the decode kernel in chunks of a fixed number of
-    keys, the others to the prefill kernel in tiles of ``prefill_tile_rows`` packed rows. Item counts may include
-    padding entries (batch row -1), which the kernels skip."""
-    prefill_items: int = 0
-    prefill_tile_rows: int = 64
-    merge_rows: int = 16         # the most packed rows a split row has (the merge kernel's blocks along z)
-    decode_items: int = 0
-    merge_items: int = 0
-    slots: int = 0
-    prefill_work: torch.Tensor | None = None
-    decode_work: torch.Tensor | None = None
-    merge_work: torch.Tensor | None = None
-
-
-def attention_work(row_starts, row_counts, group: int, window: int | None, chunk: int, tile_rows: int = 64):
-    """(prefill pairs, decode quadruples, merge quadruples, slots) as flat int lists. ``chunk`` is a multiple of 64: a
-    chunk starts on a boundary of the decode kernels' key tiles."""
-    if chunk <= 0 or chunk % 64:
-        raise ValueError(f"decode chunk {chunk} is not a positive multiple of 64")
-    prefill, decode, merge, tiles = [], [], [], []
-    slots = 0
-    token = 0    # the row's first token among the step's tokens
-    for b, (start, n) in enumerate(zip(row_starts, row_counts)):
-        rows, kv_len = n * group, start + n
-        first_token, token = token, token + n
-        if start < 0:
-            continue   # a padding row (see pad_row): no keys, no work
-        if rows <= 16:
-            lo = max(0, start - window + 1) if window else 0
-            first = (lo // chunk) * chunk
-            begins = range(first, kv_len, chunk)
-            if len(begins) == 1:
-                decode += [b, first, min(first + chunk, kv_len), -1]
-            else:
-                merge += [b, slots, len(begins) | (rows << 24), first_token]
-                for c in begins:
-                    decode += [b, c, min(c + chunk, kv_len), slots]
-                    slots += 1
-        else:
-            for r0 in range(0, rows, tile_rows):
-                tiles.append((start + min(rows, r0 + tile_rows) // group, b, r0))
-    # the tiles with the longest history run longest: they go first, so that the last wave of CTAs is the lightest
-    for _, b, r0 in sorted(tiles, key=lambda t: -t[0]):
-        prefill += [b, r0]
-    return prefill, decode, merge, slots
-
-
-def attention_caps(num_tokens: int, num_rows: int, kv_cap: int, group: int, chunk: int, tile_rows: int = 64,
-                   short_rows: bool = True) -> tuple[int, int, int]:
-    """Largest (prefill, decode, merge) item counts of a step of ``num_tokens`` tokens in ``num_rows`` rows whose
-    requests hold at most ``kv_cap`` keys. A step of one token a row has work of one kind only; so has a step without
-    ``short_rows`` (rows of at most 16 tokens, the only ones that can go to the decode kernel)."""
-    chunks = -(-kv_cap // chunk)
-    if num_tokens == num_rows:
-        if group > 16:
-            return num_rows * (-(-group // tile_rows)), 0, 0
-        return 0, num_rows * chunks, num_rows
-    prefill = -(-num_tokens * group // tile_rows) + num_rows
-    return (prefill, num_rows * chunks, num_rows) if short_rows else (prefill, 0, 0)
-
-
-def _pad4(a: list) -> list:
-    return a + [0] * (-len(a) % 4)
-
-
-def plan_attention(row_starts, row_counts, group: int, window: int | None, chunk: int, device, tile_rows: int = 64) -> AttentionPlan:
-    prefill, decode, merge, slots = attention_work(row_starts, row_counts, group, window, chunk, tile_rows)
-    plan = AttentionPlan(prefill_items=len(prefill) // 2, prefill_tile_rows=tile_rows, decode_items=len(decode) // 4, merge_items=len(merge) // 4, slots=slots,
-                         merge_rows=max((z >> 24 for z in merge[2::4]), default=1))
-    flat = _pad4(prefill) + _pad4(decode) + _pad4(merge)
-    if flat:
-        host = torch.tensor(flat, dtype=torch.int32)
-        if torch.device(device).type == "cuda":
-            host = host.pin_memory()
-        dev = host.to(device, non_blocking=True)
-        a = len(_pad4(prefill))
-        b_ = a + len(_pad4(decode))
-        plan.prefill_work, plan.decode_work, plan.merge_work = dev[:a], dev[a:b_], dev[b_:]
-        plan.host = host
-    return plan
+def upload_tables(arrays: list, device) -> tuple[list, torch.Tensor | None]:
+    """int32 arrays in one pinned buffer (each starting on a 16-byte boundary), copied to the device in one transfer;
+    (one device tensor per array, the pinned buffer, to be kept until the copy has run)."""
+    offsets, total = [], 0
+    for a in arrays:
+        offsets.append(total)
+        total += -(-a.size // 4) * 4
+    if total == 0:
+        return [None] * len(arrays), None
+    device = torch.device(device)
+    host = torch.zeros(total, dtype=torch.int32, pin_memory=device.type == "cuda")
+    hv = host.numpy()
+    for a, o in zip(arrays, offsets):
+        hv[o : o + a.size] = a
+    dev = host.to(device, non_blocking=True)
+    return [dev[o : o + a.size] if a.size else None for a, o in zip(arrays, offsets)], host
 
 
 def graph_kv_cap(kv_len: int) -> int:
     """The bound on the requests' lengths a captured decode step is made for: the next multiple of 1024 up to 8192
-    tokens, of 4096 up to 32768, of 16384 beyond. It sizes the step's page tables and attention work lists, whose unused
+    tokens, of 4096 up to 32768, of 16384 beyond. It sizes the step's page tables and the mixers' work lists, whose unused
     entries cost an upload of a few bytes each and nothing on the device."""
     for limit, granule in ((8192, 1024), (32768, 4096)):
         if kv_len <= limit:
@@ -171,7 +107,9 @@ class StepBatch:
     kv_cap: int = 0              # the bound on the requests' lengths a captured step of this size is made for
     all_single: bool = False     # every row brings exactly one token
     host_buffer: object = None   # the pinned staging buffer, kept until the step is done
-    attention_plans: dict = field(default_factory=dict)   # (group size, window, chunk) -> AttentionPlan, made by the first mixer that asks
+    # key -> (the mixer that made it, what it bound): per-step work lists of mixers whose kernels want them, made by the
+    # first run that asks and shared by every run that asks under the same key (see ``Mixer.step_work_arrays``)
+    work: dict = field(default_factory=dict)
     rotation_tables: dict = field(default_factory=dict)   # frequency table -> the step's cosines and sines, made by the first layer that asks
 
     def rotation_table(self, kernels, inv_freq: torch.Tensor):
@@ -189,13 +127,17 @@ class StepBatch:
             table = self.rotation_tables[key] = make(self.positions, inv_freq)
         return table
 
-    def attention_plan(self, group: int, window: int | None, chunk: int, tile_rows: int = 64) -> AttentionPlan:
-        key = (group, window, chunk, tile_rows)
-        plan = self.attention_plans.get(key)
-        if plan is None:
-            plan = plan_attention(self.row_starts, self.row_counts, group, window, chunk, self.ids.device, tile_rows)
-            self.attention_plans[key] = plan
-        return plan
+    def step_work(self, mixer, key):
+        """What ``mixer`` bound for this step under ``key``: its work lists, derived on the host from the rows' starts
+        and counts, uploaded in one copy and bound by ``mixer.step_work_bind``. In a captured step the lists are there
+        already, at fixed addresses (the executor's ``StepGraph`` refills them before every replay)."""
+        entry = self.work.get(key)
+        if entry is None:
+            arrays = mixer.step_work_arrays(key, self.row_starts, self.row_counts)
+            tensors, host = upload_tables(arrays, self.ids.device)
+            bound = mixer.step_work_bind(key, tensors, host_arrays=arrays)
+            entry = self.work[key] = (mixer, bound, host)
+        return entry[1]
 
 
 @dataclass
@@ -327,7 +269,9 @@ class BatchBuilder:
                     at += n
                 arrays += [slot, indptr, np.asarray(indices, np.int32)]
             else:
-                arrays.append(np.asarray([rc.slots[gi] if rc is not None else 0 for rc, *_ in rows], np.int32))
+                scratch = self.cm.pools[gi].capacity       # the slot beyond the pool's: padding rows' state goes there
+                arrays.append(np.asarray([rc.slots[gi] if rc is not None else scratch for rc, *_ in rows], np.int32))
+                arrays.append(np.asarray([1 if rc is not None and start == 0 else 0 for rc, start, *_ in rows], np.int32))
         return HostTables(arrays=arrays, num_tokens=T, num_rows=B, num_selected=len(selected), row_starts=[r[1] for r in rows],
                           row_counts=[len(r[2]) for r in rows], max_position=max(int(pos.max()), 0) if T else 0,
                           max_kv_len=int(kv_lens.max()) if B else 0)
@@ -341,8 +285,8 @@ class BatchBuilder:
                 groups.append(GroupTables(slot_mapping=rest[0], kv_indptr=rest[1], kv_indices=rest[2]))
                 rest = rest[3:]
             else:
-                groups.append(GroupTables(state_slots=rest[0]))
-                rest = rest[1:]
+                groups.append(GroupTables(state_slots=rest[0], fresh=rest[1]))
+                rest = rest[2:]
         return StepBatch(num_tokens=ht.num_tokens, num_rows=ht.num_rows, num_selected=ht.num_selected, ids=d_ids, positions=d_pos,
                          token_row=d_trow, q_indptr=d_qi, kv_lens=d_kvl, selected=d_sel, groups=groups, row_starts=ht.row_starts,
                          row_counts=ht.row_counts, max_position=ht.max_position, max_kv_len=ht.max_kv_len,
@@ -376,7 +320,7 @@ class BatchBuilder:
             if g.kind == "paged":
                 caps += [T, B + 1, B * (-(-kv_cap // g.page_size))]
             else:
-                caps.append(B)
+                caps += [B, B]
         return caps
 
     def static_batch(self, ht: HostTables, static: StaticTables, n_table_sections: int) -> StepBatch:

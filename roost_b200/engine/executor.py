@@ -19,8 +19,7 @@ import numpy as np
 
 from ..cache.manager import CacheManager, OutOfPages, build_groups
 from ..cache.storage import CacheStorage
-from .batch import (AttentionPlan, BatchBuilder, HostTables, StaticTables, attention_caps, attention_work, graph_kv_cap,
-                    padded_rows)
+from .batch import BatchBuilder, HostTables, StaticTables, graph_kv_cap, padded_rows
 from .model import Model
 
 MAX_GRAPHS = 64
@@ -78,23 +77,30 @@ class StepGraph:
     """A captured CUDA graph of one step for a fixed number of tokens and rows and a bound on the requests' lengths.
     The step's tables live at fixed device addresses; a replay uploads the new tables and launches the whole forward
     pass with one call, so the host's per-kernel launch cost (hundreds of launches a step) no longer bounds small
-    batches and small models. A step with fewer rows or tokens is filled up with padding rows (``batch.pad_row``), its
-    work lists with items the kernels skip. The reference's one graph experiment did not replay bit-identically and is
-    unclaimed (kernels/README.md:240-250); here a replay runs the very kernels of the eager path with the same
-    arguments, and the tests compare both with the plain implementation."""
+    batches and small models. A step with fewer rows or tokens is filled up with padding rows (``batch.pad_row``), the
+    mixers' work lists with items their kernels skip. The reference's one graph experiment did not replay bit-identically
+    and is unclaimed (kernels/README.md:240-250); here a replay runs the very kernels of the eager path with the same
+    arguments, and the tests compare both with the plain implementation.
 
-    def __init__(self, executor: "StepExecutor", num_tokens: int, num_rows: int, kv_cap: int, short_rows: bool, plan_keys: list):
+    ``work``: (key, mixer) of every set of per-step work lists the eager run of this step asked its batch for. The graph
+    gives each list a fixed section beside the step's tables (sized by ``mixer.step_work_caps``), refills the sections
+    from ``mixer.step_work_arrays`` before every replay and hands the mixer its sections once, at capture."""
+
+    def __init__(self, executor: "StepExecutor", num_tokens: int, num_rows: int, kv_cap: int, step_class: tuple, work: list):
         self.ex = weakref.proxy(executor)   # the executor owns its graphs; no reference cycle keeps its cache alive
-        self.num_tokens, self.num_rows, self.kv_cap, self.short_rows = num_tokens, num_rows, kv_cap, short_rows
-        self.plan_keys = list(plan_keys)
+        self.num_tokens, self.num_rows, self.kv_cap, self.step_class = num_tokens, num_rows, kv_cap, step_class
+        self.work = list(work)
         builder = executor.builder
         table_caps = builder.table_caps(num_tokens, num_rows, kv_cap)
         self.n_table = len(table_caps)
-        self.plan_caps = [attention_caps(num_tokens, num_rows, kv_cap, g, chunk, rows, short_rows) for (g, _w, chunk, rows) in self.plan_keys]
         caps, fills = list(table_caps), [0] * len(table_caps)
-        for pc, dc, mc in self.plan_caps:
-            caps += [pc * 2, dc * 4, mc * 4]
-            fills += [-1, -1, -1]    # padding items name batch row -1, which the kernels skip
+        self.work_sections = []             # per set of lists: the indices of its sections
+        for key, mixer in self.work:
+            sizes = mixer.step_work_caps(key, num_tokens, num_rows, kv_cap, step_class)
+            self.work_sections.append(list(range(len(caps), len(caps) + len(sizes))))
+            for cap, fill in sizes:
+                caps.append(cap)
+                fills.append(fill)
         self.fills = fills
         self.static = StaticTables(executor.rt.device, caps)
         self.graph = None
@@ -102,13 +108,12 @@ class StepGraph:
 
     @property
     def key(self) -> tuple:
-        return (self.num_tokens, self.num_rows, self.kv_cap, self.short_rows)
+        return (self.num_tokens, self.num_rows, self.kv_cap, self.step_class)
 
     def _arrays(self, ht: HostTables) -> list:
         arrays = list(ht.arrays)
-        for (g, w, chunk, rows) in self.plan_keys:
-            prefill, decode, merge, _ = attention_work(ht.row_starts, ht.row_counts, g, w, chunk, rows)
-            arrays += [np.asarray(prefill, np.int32), np.asarray(decode, np.int32), np.asarray(merge, np.int32)]
+        for key, mixer in self.work:
+            arrays += [np.asarray(a, np.int32) for a in mixer.step_work_arrays(key, ht.row_starts, ht.row_counts)]
         return arrays
 
     def fits(self, ht: HostTables) -> bool:
@@ -131,26 +136,23 @@ class StepGraph:
 
     def capture(self, ht: HostTables) -> None:
         """Records the step over the fixed tables (after ``fits(ht)`` returned True). Nothing runs: the step's own result
-        comes from the eager run before it, which also told which attention plans the model's mixers ask for."""
+        comes from the eager run before it, which also told which work lists the model's mixers ask for."""
         ex = self.ex
         self.static.upload(self._pending, self.fills)
         batch = ex.builder.static_batch(ht, self.static, self.n_table)
-        views = self.static.views[self.n_table:]
-        for i, (key, (pc, dc, mc)) in enumerate(zip(self.plan_keys, self.plan_caps)):
-            batch.attention_plans[key] = AttentionPlan(prefill_items=pc, prefill_tile_rows=key[3], decode_items=dc, merge_items=mc, slots=dc,
-                                                       merge_rows=min(16, key[0]) if self.num_tokens == self.num_rows else 16,
-                                                       prefill_work=views[3 * i], decode_work=views[3 * i + 1],
-                                                       merge_work=views[3 * i + 2])
+        captured = (self.num_tokens, self.num_rows, self.kv_cap, self.step_class)
+        for (key, mixer), sections in zip(self.work, self.work_sections):
+            batch.work[key] = (mixer, mixer.step_work_bind(key, [self.static.views[i] for i in sections], captured=captured), None)
         graph = torch.cuda.CUDAGraph()
         before = ex.rt.kernels.launches
         # one memory pool for all of an executor's graphs: they never run at the same time, so what one capture used
         # and freed serves the next
         with torch.cuda.graph(graph, pool=ex.graph_pool()):
-            out = ex.model.forward(batch, ex.storage)
+            out = ex.forward(batch)
         self.launches = ex.rt.kernels.launches - before   # kernels one replay launches
         ex.rt.kernels.launches = before
-        if sorted(batch.attention_plans, key=repr) != sorted(self.plan_keys, key=repr):
-            raise RuntimeError("the captured step asked for other attention plans than the eager step before it")
+        if sorted(batch.work, key=repr) != sorted((k for k, _ in self.work), key=repr):
+            raise RuntimeError("the captured step asked for other work lists than the eager step before it")
         self.graph, self.out, self.batch = graph, out, batch
 
 
@@ -179,11 +181,13 @@ class StepExecutor:
         self.builder = BatchBuilder(self.rt.device, self.cache)
         self.steps_run = 0
         self.last_upload_bytes = 0
-        # decode steps are replayed from captured graphs when every run keeps paged keys and values only (a mixer with
-        # state of its own may be written in Python and may not be idempotent, so such models run eagerly) and every
-        # part says that its call can be captured
+        # steps are replayed from captured graphs when every part says that its call can be captured and every mixer
+        # with state of its own says that it reads the step's device tables only (``Mixer.state_capturable``; a mixer
+        # written in Python over host values is right as it is and keeps its model's steps eager)
+        self.mixers = [b.mixer for b in model.blocks]
+        state_runs = {r for g in self.groups if g.kind == "state" for r in g.runs}
         self.use_graphs = (use_graphs and self.rt.device.type == "cuda"
-                           and all(g.kind == "paged" or not g.runs for g in self.groups)
+                           and all(getattr(model.blocks[model.spec.schedule[r].block].mixer, "state_capturable", False) for r in state_runs)
                            and all(getattr(p, "capturable", True) for p in model.parts()))
         self._graphs: dict = {}
         self._graph_pool = None
@@ -242,8 +246,7 @@ class StepExecutor:
             raise
         if logits is None:
             self.last_upload_bytes = batch.host_buffer.numel() * batch.host_buffer.element_size()
-            self._zero_new_state(rows)
-            logits = self.model.forward(batch, self.storage)
+            logits = self.forward(batch)
         for (e, _, end) in plan:
             self.cache.commit(e.request_id, end)
         self.steps_run += 1
@@ -265,9 +268,9 @@ class StepExecutor:
             if wanted > rows_cap:
                 return None
         ht = self.builder.host_tables(padded_rows(rows, tokens_cap, rows_cap), self.model.spec.vocab)
-        # rows of at most 16 tokens may go to the decode attention; a step without any is captured without that kernel
-        short = decode or any(len(r[2]) <= 16 for r in rows)
-        key = (tokens_cap, rows_cap, graph_kv_cap(ht.max_kv_len), short)
+        # what the mixers say about the step's rows decides which of their kernels a step needs at all (a step without
+        # short rows is captured without the kernel that serves them): it is part of the captured step's identity
+        key = (tokens_cap, rows_cap, graph_kv_cap(ht.max_kv_len), self.step_class([len(r[2]) for r in rows]))
         g = self._touch(key)
         if g is None:
             if not decode:
@@ -276,12 +279,12 @@ class StepExecutor:
                 self._seen[key] = self._seen.get(key, 0) + 1
                 if self._seen[key] < 2:
                     return None
-            # the eager run of the padded step gives this step's result and tells which attention plans the mixers ask
+            # the eager run of the padded step gives this step's result and tells which work lists the mixers ask
             # for; the capture that follows records the same launches over fixed tables without running them
             batch = self.builder.place(ht)
             self.last_upload_bytes = batch.host_buffer.numel() * batch.host_buffer.element_size()
-            logits = self.model.forward(batch, self.storage)
-            g = StepGraph(self, tokens_cap, rows_cap, key[2], short, sorted(batch.attention_plans, key=repr))
+            logits = self.forward(batch)
+            g = StepGraph(self, tokens_cap, rows_cap, key[2], key[3], [(k, batch.work[k][0]) for k in sorted(batch.work, key=repr)])
             if g.fits(ht):
                 g.capture(ht)
                 if len(self._graphs) >= MAX_GRAPHS:
@@ -293,6 +296,14 @@ class StepExecutor:
         self.last_upload_bytes = g.static.total * 4
         self.graph_replays += 1
         return g.run(wanted)
+
+    def step_class(self, row_counts: list) -> tuple:
+        out = ()
+        for m in self.mixers:
+            c = m.step_class(row_counts) if hasattr(m, "step_class") else ()
+            if c and c not in out:
+                out += (c,)
+        return tuple(x for c in out for x in c)
 
     def _touch(self, key):
         """The captured step of this key, marked as the most recently used (the least recently used one goes when there
@@ -310,7 +321,7 @@ class StepExecutor:
     # ------------------------------------------------------------------ a decode step prepared ahead of its tokens
     def prepare_decode(self, request_ids: list) -> PreparedDecode | None:
         """Everything of the next decode step of these requests (one token each, logits wanted) that does not depend on
-        the tokens' values: pages, tables, attention work lists. A caller makes it while the device still runs the step
+        the tokens' values: pages, tables, the mixers' work lists. A caller makes it while the device still runs the step
         before, and hands it to ``run_prepared`` with the tokens once they are known; when the next step turns out to be
         another one, the preparation is simply dropped (the pages it took belong to their requests and go back with
         them). None when the step cannot be prepared: no captured graph serves it yet, or pages are short."""
@@ -333,7 +344,7 @@ class StepExecutor:
         rows = [(self.cache.extend(rid, start + 1), start, [0], [0]) for rid, start in zip(request_ids, starts)]
         cap = graph_rows(len(rows))
         ht = self.builder.host_tables(padded_rows(rows, cap, cap), self.model.spec.vocab)
-        g = self._touch((cap, cap, graph_kv_cap(ht.max_kv_len), True))
+        g = self._touch((cap, cap, graph_kv_cap(ht.max_kv_len), self.step_class([1] * len(rows))))
         if g is None or not g.fits(ht):
             return None
         return PreparedDecode(list(request_ids), starts, g, g.static.stage(g._pending, g.fills))
@@ -404,16 +415,21 @@ class StepExecutor:
         self.prepared_replays += 1
         self.steps_run += 1
 
-    def _zero_new_state(self, rows) -> None:
-        """A request's fixed-size state starts at zero when its first token arrives, as the reference's worker
-        zeroes a recurrent slot at position 0 (src/Starlings.Roost.Worker/Eager/EagerWorker.cs:214-230)."""
+    def forward(self, batch) -> torch.Tensor:
+        """The model's forward pass over a step's batch, after the fixed-size state of every request whose first token
+        the step brings has been set to zero, as the reference's worker zeroes a recurrent slot at position 0
+        (src/Starlings.Roost.Worker/Eager/EagerWorker.cs:214-230). The zeroing reads the step's device tables only
+        (``state_slots``, ``fresh``), so it is part of a captured step like everything after it; a padding row names the
+        group's scratch slot."""
         for gi, g in enumerate(self.groups):
             if g.kind != "state" or not g.runs:
                 continue
-            fresh = [rc.slots[gi] for rc, start, _, _ in rows if start == 0]
-            if fresh:
-                idx = torch.tensor(fresh, dtype=torch.long, device=self.rt.device)
-                self.storage.tensors[gi].index_fill_(1, idx, 0)
+            tables = batch.groups[gi]
+            state = self.storage.tensors[gi]                        # [runs, slots + 1, *shape]
+            slots = tables.state_slots.long()
+            keep = (1 - tables.fresh).to(state.dtype).view(1, -1, *([1] * (state.dim() - 2)))
+            state.index_copy_(1, slots, state.index_select(1, slots) * keep)
+        return self.model.forward(batch, self.storage)
 
     def close(self) -> None:
         """Drops the captured graphs and the cache's device memory."""

@@ -56,7 +56,7 @@ def _graph_time(fns: list, warmup: int, iters: int) -> float:
 def attention_decode(k, a) -> None:
     import torch
 
-    from ..engine.batch import plan_attention
+    from ..parts.attention_work import plan_attention
     nq, nkv, d, page = a.q_heads, a.kv_heads, a.head_dim, a.page_size
     pages_per = -(-a.context // page)
     npages = pages_per * a.batch
@@ -80,7 +80,7 @@ def attention_decode(k, a) -> None:
 def attention_prefill(k, a) -> None:
     import torch
 
-    from ..engine.batch import plan_attention
+    from ..parts.attention_work import plan_attention
     nq, nkv, d, page = a.q_heads, a.kv_heads, a.head_dim, a.page_size
     T = a.tokens
     pages_per = -(-T // page)

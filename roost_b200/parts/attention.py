@@ -11,9 +11,14 @@ from __future__ import annotations
 
 import torch
 
+import numpy as np
+
 from ..config.spec import AttentionSpec
+from .attention_work import AttentionPlan, attention_caps, attention_work
 from .base import NORMS, POSITIONS, CacheNeed, Mixer, ParamDecl, Runtime, register_mixer
 from .linear import Linear
+
+SHORT_ROW_TOKENS = 16   # rows of at most this many tokens may go to the split decode kernel
 
 
 class PagedAttention(Mixer):
@@ -100,11 +105,42 @@ class PagedAttention(Mixer):
             tile_rows = k.attention_prefill_tile_rows(s.num_heads, cache.k_pool, cache.v_pool, batch.num_tokens * group)
             chunk_for = getattr(k, "decode_chunk_for", None)
             chunk = chunk_for(batch.num_rows, batch.kv_cap, s.num_kv_heads) if chunk_for and batch.kv_cap else k.decode_chunk
-            plan = batch.attention_plan(group, s.window, chunk, tile_rows)
+            plan = batch.step_work(self, ("paged_attention", group, s.window, chunk, tile_rows))
             return k.attention_mma(q, cache.k_pool, cache.v_pool, batch.q_indptr, batch.kv_lens, tables.kv_indptr,
                                    tables.kv_indices, plan, s.scale, s.window)
         return k.paged_attention_generic(q, cache.k_pool, cache.v_pool, batch.positions, batch.token_row,
                                          tables.kv_indptr, tables.kv_indices, s.scale, s.window)
+
+
+    # ---- the tensor-core kernels' work lists, as the step's batch asks for them
+    def step_class(self, row_counts):
+        return ("short_rows", any(n <= SHORT_ROW_TOKENS for n in row_counts))
+
+    def step_work_arrays(self, key, row_starts, row_counts):
+        _, group, window, chunk, tile_rows = key
+        prefill, decode, merge, _ = attention_work(row_starts, row_counts, group, window, chunk, tile_rows)
+        return [np.asarray(prefill, np.int32), np.asarray(decode, np.int32), np.asarray(merge, np.int32)]
+
+    def step_work_caps(self, key, num_tokens, num_rows, kv_cap, step_class):
+        _, group, _, chunk, tile_rows = key
+        short = dict([step_class[i : i + 2] for i in range(0, len(step_class), 2)]).get("short_rows", True)
+        pc, dc, mc = attention_caps(num_tokens, num_rows, kv_cap, group, chunk, tile_rows, short)
+        return [(pc * 2, -1), (dc * 4, -1), (mc * 4, -1)]     # padding items name batch row -1, which the kernels skip
+
+    def step_work_bind(self, key, tensors, host_arrays=None, captured=None):
+        _, group, _, _, tile_rows = key
+        prefill, decode, merge = tensors
+        if captured is not None:       # every list at its capacity; a step of one token a row splits rows of `group` packed rows
+            num_tokens, num_rows, kv_cap, step_class = captured
+            (pc, _), (dc, _), (mc, _) = self.step_work_caps(key, num_tokens, num_rows, kv_cap, step_class)
+            return AttentionPlan(prefill_items=pc // 2, prefill_tile_rows=tile_rows, decode_items=dc // 4, merge_items=mc // 4, slots=dc // 4,
+                                 merge_rows=min(16, group) if num_tokens == num_rows else 16, prefill_work=prefill, decode_work=decode,
+                                 merge_work=merge)
+        hp, hd, hm = host_arrays
+        slots = int((hd[3::4] >= 0).sum())      # every chunk of a split row has a partial slot of its own
+        return AttentionPlan(prefill_items=hp.size // 2, prefill_tile_rows=tile_rows, decode_items=hd.size // 4, merge_items=hm.size // 4,
+                             slots=slots, merge_rows=int((hm[2::4] >> 24).max()) if hm.size else 1, prefill_work=prefill,
+                             decode_work=decode, merge_work=merge)
 
 
 register_mixer("paged_attention", PagedAttention)

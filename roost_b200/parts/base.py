@@ -90,8 +90,39 @@ class Norm(Part):
 
 
 class Mixer(Part):
+    # True for a mixer with state of its own whose call reads the step's device tables only (``state_slots``, ``token_row``,
+    # ``positions``, ``q_indptr`` ...), never host values: a step is the same sequence of launches whatever its rows are,
+    # so the executor may capture it. The default keeps such a model's steps eager (a mixer written as a Python loop over
+    # the rows is then right as it is).
+    state_capturable = False
+
     def cache_need(self) -> CacheNeed | None:
         return None
+
+    # ---- per-step work lists (optional). A mixer whose kernels want lists derived on the host from the step's rows
+    # (how the rows are divided among kernels and CTAs) asks the batch for them in its call: ``batch.step_work(self,
+    # key)``. The batch calls back here. Neither the batch nor the executor knows what the lists hold: a captured step
+    # sizes its fixed tables with ``step_work_caps``, refills them with ``step_work_arrays`` before every replay and lets
+    # the mixer bind them once, at capture, with ``step_work_bind``. ``key`` is any hashable that starts with the mixer's
+    # kind; runs that ask under the same key share one set of lists.
+    def step_class(self, row_counts: list) -> tuple:
+        """What about a step's rows decides which lists the step needs at all (part of a captured step's identity)."""
+        return ()
+
+    def step_work_arrays(self, key, row_starts: list, row_counts: list) -> list:
+        """The step's lists as int32 numpy arrays. A padding row has start -1."""
+        raise NotImplementedError
+
+    def step_work_caps(self, key, num_tokens: int, num_rows: int, kv_cap: int, step_class: tuple) -> list:
+        """(capacity, fill value) of each list for a captured step of these sizes; entries beyond a step's own are set to
+        the fill value, which the kernels must skip."""
+        raise NotImplementedError
+
+    def step_work_bind(self, key, tensors: list, host_arrays: list | None = None, captured: tuple | None = None):
+        """What the mixer's call gets back from ``batch.step_work``: built from the lists on the device and either the
+        host arrays they were copied from (an eager step) or, in a captured step whose tables have their full capacity,
+        ``captured`` = (num_tokens, num_rows, kv_cap, step_class)."""
+        raise NotImplementedError
 
     def __call__(self, x: torch.Tensor, batch, cache, write_cache: bool = True) -> torch.Tensor:
         """x: [T, hidden] normed input of this step's tokens. ``batch`` is the step's ``StepBatch``; ``cache``

@@ -268,6 +268,32 @@ class ToyRunningMean(Mixer):
         return out.to(x.dtype)
 
 
+class ToyRunningMeanOnDevice(ToyRunningMean):
+    """The same mixer written over the step's device tables alone (``token_row``, ``positions``, ``q_indptr``,
+    ``state_slots``): no value is read on the host and the launches do not depend on the rows, so the mixer may say
+    ``state_capturable`` and its model's steps are captured and replayed like any other's. The scan over a row's tokens
+    is a product with a [T, T] matrix of decay powers between tokens of the same row."""
+    state_capturable = True
+
+    def __call__(self, x, batch, cache, write_cache=True):
+        d = self.spec.decay
+        u = self.proj(x).float()                                           # [T, H]
+        tables = batch.groups[cache.group]
+        row = batch.token_row.long()
+        pos = batch.positions.float()
+        first = batch.q_indptr[:-1].long().clamp(max=max(batch.num_tokens - 1, 0))
+        idx = torch.arange(batch.num_tokens, device=u.device)
+        same = (row[:, None] == row[None, :]) & (idx[None, :] <= idx[:, None])
+        w = torch.where(same, (1 - d) * torch.pow(torch.tensor(d, device=u.device), (pos[:, None] - pos[None, :]).clamp(min=0)), torch.zeros((), device=u.device))
+        slots = tables.state_slots.long()
+        before = cache.state.index_select(0, slots)                        # [B, H]
+        carried = torch.pow(torch.tensor(d, device=u.device), pos - pos[first][row] + 1)[:, None] * before[row]
+        out = w @ u + carried
+        last = (batch.q_indptr[1:].long() - 1).clamp(min=0)
+        cache.state.index_copy_(0, slots, out.index_select(0, last))      # padding rows write the scratch slot
+        return out.to(x.dtype)
+
+
 def toy_plain(x, w, decay):
     u = x @ w.T
     s = torch.zeros(w.shape[0], dtype=torch.float64)
@@ -278,8 +304,9 @@ def toy_plain(x, w, decay):
     return torch.stack(out)
 
 
-def test_a_toy_mixer_with_its_own_state_is_registered_built_and_stepped(backend):
-    register_mixer("toy_running_mean", ToyRunningMean)
+@pytest.mark.parametrize("written", ["as a loop over the rows", "over the device tables"])
+def test_a_toy_mixer_with_its_own_state_is_registered_built_and_stepped(backend, written):
+    register_mixer("toy_running_mean", ToyRunningMean if written == "as a loop over the rows" else ToyRunningMeanOnDevice)
     rt = runtime(backend)
     H_, V, I = 32, 50, 48
     norm = NormSpec(size=H_, eps=1e-6)
@@ -328,6 +355,28 @@ def test_a_toy_mixer_with_its_own_state_is_registered_built_and_stepped(backend)
     # a slot that is used again starts from zero: the next request does not see the last one's state
     got = H.run_portions(ex, "c", b, [4, 2, 9])
     assert H.scaled_error(got, plain_forward(b)) < bound
+    assert ex.cache.pools[1].free_count == 3
+    # The mixer written as a Python loop keeps its model's steps eager; the one written over the device tables lets them
+    # be captured: single-token steps replay a graph (the fresh slot is zeroed inside it, padding rows write the scratch
+    # slot), three requests beside each other in the captured step of three rows, one of them ending early.
+    captured = backend[0] == "gpu" and written == "over the device tables"
+    assert ex.use_graphs == captured
+    replays0 = ex.graph_replays
+    got = H.run_tail_decoded(ex, "d", a, tail=12)
+    assert H.scaled_error(got, plain_forward(a)) < bound
+    seqs = {"x": a[:9], "y": b[:14], "z": a[5:17]}
+    outs = {r: [] for r in seqs}
+    for i in range(14):
+        live = [r for r, ids in seqs.items() if i < len(ids)]
+        logits = ex.step([StepEntry(r, [seqs[r][i]], [0]) for r in live])
+        for r, row in zip(live, logits):
+            outs[r].append(row)
+        for r in live:
+            if i == len(seqs[r]) - 1:
+                ex.finish(r)
+    for r, ids in seqs.items():
+        assert H.scaled_error(torch.stack(outs[r]), plain_forward(ids)) < bound, r
+    assert (ex.graph_replays - replays0 >= 15) == captured
     assert ex.cache.pools[1].free_count == 3
 
 

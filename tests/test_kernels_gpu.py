@@ -384,7 +384,7 @@ def test_sampler_matches_the_plain_sampler(kernels, vocab):
 
 # ------------------------------------------------------------------------------------------ tensor-core attention (bfloat16)
 def run_mma(kernels, q, kp, vp, lens, news, indptr, indices, scale, window, chunk=None, tile_rows=None):
-    from roost_b200.engine.batch import plan_attention
+    from roost_b200.parts.attention_work import plan_attention
     nq, nkv = q.shape[1], kp.shape[1]
     starts = [n - m for n, m in zip(lens, news)]
     plan = plan_attention(starts, news, nq // nkv, window, chunk or kernels.decode_chunk, "cuda",

@@ -178,7 +178,8 @@ def test_sizes_of_captured_steps_and_padding_rows():
     import numpy as np
 
     from roost_b200.cache.manager import CacheManager, build_groups
-    from roost_b200.engine.batch import BatchBuilder, attention_work, pad_row, padded_rows
+    from roost_b200.engine.batch import BatchBuilder, pad_row, padded_rows
+    from roost_b200.parts.attention_work import attention_work
     from roost_b200.engine.executor import graph_kv_cap, graph_rows
     from roost_b200.parts import CacheNeed
     assert [graph_rows(n) for n in (1, 5, 8, 9, 12, 13, 17, 33, 64, 65, 100)] == [1, 5, 8, 12, 12, 16, 24, 48, 64, 96, 128]
@@ -190,8 +191,9 @@ def test_sizes_of_captured_steps_and_padding_rows():
     rows = padded_rows([(rc, 5, [9], [0])], 3, 3)
     assert rows[1:] == [pad_row(1), pad_row(1)]
     ht = BatchBuilder("cpu", cm).host_tables(rows, vocab=16)
-    ids, pos, trow, q_indptr, kv_lens, selected, slot, indptr, indices, state_slots = ht.arrays
-    assert state_slots.tolist()[1:] == [0, 0] and selected.tolist() == [0]
+    ids, pos, trow, q_indptr, kv_lens, selected, slot, indptr, indices, state_slots, fresh = ht.arrays
+    # padding rows name the scratch slot beyond the pool's four; no row of this step brings a request's first token
+    assert state_slots.tolist()[1:] == [4, 4] and fresh.tolist() == [0, 0, 0] and selected.tolist() == [0]
     assert pos.tolist() == [5, -1, -1] and kv_lens.tolist() == [6, 0, 0] and q_indptr.tolist() == [0, 1, 2, 3]
     assert slot.tolist()[1:] == [-1, -1] and slot[0] >= 0 and indptr.tolist() == [0, 2, 2, 2] and len(indices) == 2
     assert ht.max_position == 5 and ht.max_kv_len == 6 and ht.row_starts == [5, -1, -1]

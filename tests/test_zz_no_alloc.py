@@ -24,7 +24,7 @@ def _p(t):
 
 
 def test_decode_attention_without_a_workspace_matches_the_one_with(kernels):
-    from roost_b200.engine.batch import plan_attention
+    from roost_b200.parts.attention_work import plan_attention
     from tests.test_kernels_gpu import build_paged, close, paged_reference
 
     lib = ctypes.CDLL(kernels.path)
