@@ -284,10 +284,11 @@ class ToyRunningMeanOnDevice(ToyRunningMean):
         first = batch.q_indptr[:-1].long().clamp(max=max(batch.num_tokens - 1, 0))
         idx = torch.arange(batch.num_tokens, device=u.device)
         same = (row[:, None] == row[None, :]) & (idx[None, :] <= idx[:, None])
-        w = torch.where(same, (1 - d) * torch.pow(torch.tensor(d, device=u.device), (pos[:, None] - pos[None, :]).clamp(min=0)), torch.zeros((), device=u.device))
+        # (a scalar base: a tensor made from a host value inside a captured step would be a copy from pageable memory)
+        w = torch.where(same, (1 - d) * torch.pow(d, (pos[:, None] - pos[None, :]).clamp(min=0)), torch.zeros((), device=u.device))
         slots = tables.state_slots.long()
         before = cache.state.index_select(0, slots)                        # [B, H]
-        carried = torch.pow(torch.tensor(d, device=u.device), pos - pos[first][row] + 1)[:, None] * before[row]
+        carried = torch.pow(d, pos - pos[first][row] + 1)[:, None] * before[row]
         out = w @ u + carried
         last = (batch.q_indptr[1:].long() - 1).clamp(min=0)
         cache.state.index_copy_(0, slots, out.index_select(0, last))      # padding rows write the scratch slot
