@@ -1066,7 +1066,10 @@ static int page_shift_of(int page_size) {
 // grid fills the device several times over; with less work the smaller tiles spread it over more SMs. Both compute a row
 // with the same operations in the same order, so the choice does not show in the result.
 constexpr int kPrefillWideMinRows = 65536;  // packed rows x key/value heads from which 128-row tiles are used
-constexpr int kPrefillTwoGroupsMinRows = 131072;  // ... from which the tcgen05 kernel takes 256 rows a CTA
+// ... from which a work item of the tcgen05 kernel is two row groups (256 packed rows): one group's products then run
+// while the other's softmax does, which pays once the longest item is long enough (measured at 32/8 heads of 128: 1024
+// tokens 22 against 28 us with one group, 2048 tokens 59 against 50 us, 4096 tokens 182 against 147 us)
+constexpr int kPrefillTwoGroupsMinRows = 49152;
 
 template <int D, int MT>
 static int launch_prefill(const void* q, void* out, const void* k_pool, const void* v_pool, const int32_t* q_indptr, const int32_t* kv_lens,
