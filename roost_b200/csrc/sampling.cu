@@ -11,10 +11,11 @@
 //     * 2^-24 (src/Starlings.Roost.Ops/CpuPhilox.cs:15-44); the chosen token is the first of the order whose
 //     running kept mass exceeds u * (kept mass), the last kept token if rounding leaves none.
 // A prefix of the order is the set {p > x} plus the first c tokens (by index) with p == x, so every step is a
-// search for x over the bit patterns of p (non-negative floats order like their bits), 32 passes over the row
-// with a block-wide sum each, and a count of ties. The sums run in a fixed order, so a row gives the same
-// token in any batch and on any run. Sums differ in rounding from the reference's sequential sums over a
-// sorted array: a draw within rounding of an interval's edge may fall to the neighbouring token.
+// search for x over the bit patterns of the weights (non-negative floats order like their bits): three passes
+// over the row, one per digit of the key, each a histogram of integer masses and a suffix sum (search_key
+// below), and a count of ties. Integer sums do not depend on their order, so a row gives the same token in
+// any batch and on any run. The masses are rounded to 2^-40 of the largest weight where the reference sums
+// doubles over a sorted array: a draw within rounding of an interval's edge may fall to the neighbouring token.
 #include "common.cuh"
 
 namespace roost {
@@ -166,54 +167,156 @@ __global__ void __launch_bounds__(kThreads) argmax_split_kernel(const float* __r
 }
 
 // A kept prefix of the order is (xb, c): every key > xb, plus the first c tokens (by index) whose key == xb.
-// Keys are the bit patterns of the probabilities; removed tokens hold -1 and are skipped.
+// Keys are the bit patterns of the weights e = exp((z - max) / T), which order like the probabilities e / total;
+// removed tokens hold -1 and are skipped. A weight's mass is the integer round(e * 2^40): integer sums do not depend on
+// the order of their terms, so every mass below is exact, the same in any batch and on any run, and histograms may be
+// filled with atomic adds. (A weight below 2^-41 has mass 0: all of them together are less than 2^-23 of the largest.)
+// a key's 30 significant bits, searched digit by digit, high to low: 11, 11 and 8 bits
+__device__ __forceinline__ constexpr int digit_bits(int level) { return level == 2 ? 8 : 11; }
+__device__ __forceinline__ constexpr int digit_shift(int level) { return level == 0 ? 19 : (level == 1 ? 8 : 0); }
+constexpr int kBuckets = 2048;
 
-// Mass of {key > xb}; the count of the same set is left in *count.
-__device__ __forceinline__ float mass_gt(const float* p, int n, unsigned xb, int& count, float* sf, int* si) {
-  float m = 0.f;
-  int c = 0;
-  for (int v = threadIdx.x; v < n; v += kThreads) {
-    const float x = p[v];
-    if (x >= 0.f && __float_as_uint(x) > xb) {
-      m += x;
-      ++c;
+struct SearchScratch {
+  unsigned long long mass[kBuckets];
+  unsigned cnt[kBuckets];
+  unsigned long long warp_mass[32];
+  unsigned warp_cnt[32];
+  unsigned long long found_above_mass;
+  unsigned found_above_cnt, found_digit;
+  unsigned long long found_mass;   // of the digit itself
+  unsigned found_cnt;
+};
+
+__device__ __forceinline__ unsigned long long weight_mass(float e) { return __float2ull_rn(e * 1099511627776.0f); }
+
+// The largest key b such that the measure of {keys >= b} within the prefix (xb, c) reaches `target` (is at least it, or
+// with `strict` exceeds it); the measure is the mass, or with `by_count` the number of tokens. Three passes over the row,
+// one per digit: a histogram of the measure over the digit among the tokens that share the digits chosen so far, a
+// suffix sum over the buckets, and the bucket where the sum crosses the target. Leaves in `above_mass` / `above_cnt`
+// the mass and count of {keys > b} within the prefix and in `ties` the number of tokens whose key is b (of which the
+// prefix holds c when b == xb). Requires that the whole prefix reaches the target.
+__device__ unsigned search_key(const float* __restrict__ p, int n, unsigned xb, int c, unsigned long long target, bool strict, bool by_count,
+                               SearchScratch& h, unsigned long long& above_mass, unsigned& above_cnt, unsigned& ties) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  unsigned prefix = 0u;                 // the digits chosen so far, in place
+  unsigned prefix_mask = 0u;
+  unsigned long long acc_mass = 0ull;   // measure of the keys above every bucket chosen so far
+  unsigned acc_cnt = 0u;
+  const unsigned long long xb_mass = weight_mass(__uint_as_float(xb));
+  for (int level = 0; level < 3; ++level) {
+    const int shift = digit_shift(level), buckets = 1 << digit_bits(level);
+    for (int i = threadIdx.x; i < buckets; i += kThreads) {
+      h.mass[i] = 0ull;
+      h.cnt[i] = 0u;
     }
-  }
-  count = block_sum_i(c, si);
-  return block_sum_f(m, sf);
-}
-
-__device__ __forceinline__ int count_ge(const float* p, int n, unsigned b, int* si) {
-  int c = 0;
-  for (int v = threadIdx.x; v < n; v += kThreads) {
-    const float x = p[v];
-    if (x >= 0.f && __float_as_uint(x) >= b) ++c;
-  }
-  return block_sum_i(c, si);
-}
-
-__device__ __forceinline__ int count_eq(const float* p, int n, unsigned xb, int* si) {
-  int c = 0;
-  for (int v = threadIdx.x; v < n; v += kThreads) {
-    const float x = p[v];
-    if (x >= 0.f && __float_as_uint(x) == xb) ++c;
-  }
-  return block_sum_i(c, si);
-}
-
-// Mass of {key >= b} within the prefix (xb, c).
-__device__ __forceinline__ float mass_ge_within(const float* p, int n, unsigned b, unsigned xb, int c, float* sf) {
-  float m = 0.f;
-  for (int v = threadIdx.x; v < n; v += kThreads) {
-    const float x = p[v];
-    if (x >= 0.f) {
-      const unsigned k = __float_as_uint(x);
-      if (k >= b && k > xb) m += x;
+    __syncthreads();
+    constexpr int kAhead = 8;   // loads in flight a thread: the pass is bound by their latency, not by their bytes
+    for (int base = 0; base < n; base += kThreads * kAhead) {   // whole warps go round together: the exchange below names all lanes
+      float xs[kAhead];
+#pragma unroll
+      for (int j = 0; j < kAhead; ++j) {
+        const int v = base + j * kThreads + (int)threadIdx.x;
+        xs[j] = v < n ? p[v] : -1.f;
+      }
+#pragma unroll
+      for (int j = 0; j < kAhead; ++j) {
+        const float x = xs[j];
+        unsigned digit = 0xffffffffu;   // no token of this search
+        unsigned long long w = 0ull;
+        if (x >= 0.f) {
+          const unsigned k = __float_as_uint(x);
+          if ((k & prefix_mask) == prefix && k > xb) {   // the tokens at xb are counted below, c of them
+            digit = (k >> shift) & (unsigned)(buckets - 1);
+            w = weight_mass(x);
+          }
+        }
+        // a row whose tokens crowd into one bucket (equal logits) would queue a hundred thousand adds on one address:
+        // a warp whose lanes all name the same bucket adds once
+        if (__match_any_sync(0xffffffffu, digit) == 0xffffffffu) {
+          if (digit != 0xffffffffu) {
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) w += __shfl_xor_sync(0xffffffffu, w, o);
+            if (lane == 0) {
+              atomicAdd(&h.mass[digit], w);
+              atomicAdd(&h.cnt[digit], 32u);
+            }
+          }
+        } else if (digit != 0xffffffffu) {
+          atomicAdd(&h.mass[digit], w);
+          atomicAdd(&h.cnt[digit], 1u);
+        }
+      }
     }
+    if (threadIdx.x == 0 && c > 0 && (xb & prefix_mask) == prefix) {
+      const unsigned digit = (xb >> shift) & (unsigned)(buckets - 1);
+      atomicAdd(&h.mass[digit], xb_mass * (unsigned long long)c);
+      atomicAdd(&h.cnt[digit], (unsigned)c);
+    }
+    __syncthreads();
+    // suffix sums, high digits first: thread t holds buckets [per t, per (t + 1)) counted from the top
+    const int per = (buckets + kThreads - 1) / kThreads;
+    unsigned long long my_mass = 0ull;
+    unsigned my_cnt = 0u;
+    for (int i = 0; i < per; ++i) {
+      const int bkt = buckets - 1 - ((int)threadIdx.x * per + i);
+      if (bkt >= 0) {
+        my_mass += h.mass[bkt];
+        my_cnt += h.cnt[bkt];
+      }
+    }
+    unsigned long long inc_mass = my_mass;   // inclusive scan over the warp, then over the warps
+    unsigned inc_cnt = my_cnt;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const unsigned long long tm = __shfl_up_sync(0xffffffffu, inc_mass, o);
+      const unsigned tc = __shfl_up_sync(0xffffffffu, inc_cnt, o);
+      if (lane >= o) {
+        inc_mass += tm;
+        inc_cnt += tc;
+      }
+    }
+    if (lane == 31) {
+      h.warp_mass[warp] = inc_mass;
+      h.warp_cnt[warp] = inc_cnt;
+    }
+    __syncthreads();
+    unsigned long long before_mass = acc_mass + inc_mass - my_mass;
+    unsigned before_cnt = acc_cnt + inc_cnt - my_cnt;
+    for (int w2 = 0; w2 < warp; ++w2) {
+      before_mass += h.warp_mass[w2];
+      before_cnt += h.warp_cnt[w2];
+    }
+    // the bucket where the running measure (from the top) first reaches the target
+    for (int i = 0; i < per; ++i) {
+      const int bkt = buckets - 1 - ((int)threadIdx.x * per + i);
+      if (bkt < 0) break;
+      const unsigned long long bm = h.mass[bkt];
+      const unsigned bc = h.cnt[bkt];
+      const unsigned long long before = by_count ? (unsigned long long)before_cnt : before_mass;
+      const unsigned long long with = before + (by_count ? (unsigned long long)bc : bm);
+      const bool was = strict ? before > target : before >= target;
+      const bool is = strict ? with > target : with >= target;
+      if (!was && is) {
+        h.found_digit = (unsigned)bkt;
+        h.found_above_mass = before_mass;
+        h.found_above_cnt = before_cnt;
+        h.found_mass = bm;
+        h.found_cnt = bc;
+      }
+      before_mass += bm;
+      before_cnt += bc;
+    }
+    __syncthreads();
+    prefix |= h.found_digit << shift;
+    prefix_mask |= (unsigned)(buckets - 1) << shift;
+    acc_mass = h.found_above_mass;
+    acc_cnt = h.found_above_cnt;
+    ties = h.found_cnt;
+    __syncthreads();
   }
-  m = block_sum_f(m, sf);
-  if (b <= xb) m += (float)c * __uint_as_float(xb);
-  return m;
+  above_mass = acc_mass;
+  above_cnt = acc_cnt;
+  return prefix;
 }
 
 // Index of the (r+1)-th token (by index) whose key equals xb; -1 if there are fewer.
@@ -266,6 +369,9 @@ __global__ void __launch_bounds__(kThreads)
   __shared__ float sf[32];
   __shared__ int si[32];
   __shared__ int s_result;
+  __shared__ SearchScratch h;
+  __shared__ unsigned long long s_total;
+  __shared__ unsigned s_allowed, s_zero;
   const int r = blockIdx.x;
   const float* z = logits + (size_t)r * stride;
   float* p = workspace + (size_t)r * vocab;
@@ -278,128 +384,111 @@ __global__ void __launch_bounds__(kThreads)
     return;
   }
 
-  // probabilities; removed tokens are marked -1
-  float part = 0.f;
-  int allowed = 0;
+  // the weights e = exp((z - max) / T), at most 1; removed tokens are marked -1
+  if (threadIdx.x == 0) {
+    s_total = 0ull;
+    s_allowed = 0u;
+    s_zero = 0u;
+  }
+  __syncthreads();
+  unsigned long long part = 0ull;
+  unsigned allowed_mine = 0u, zero_mine = 0u;
   for (int v = threadIdx.x; v < vocab; v += kThreads) {
     const float x = z[v];
     float e = -1.f;
     if (x == x && x != -INFINITY) {
       e = expf((x - zmax) / temp);
-      part += e;
-      ++allowed;
+      part += weight_mass(e);
+      ++allowed_mine;
+      zero_mine += e == 0.f ? 1u : 0u;
     }
     p[v] = e;
   }
-  const float total = block_sum_f(part, sf);
-  allowed = block_sum_i(allowed, si);
-  for (int v = threadIdx.x; v < vocab; v += kThreads) {
-    const float e = p[v];
-    if (e >= 0.f) p[v] = e / total;
-  }
+  atomicAdd(&s_total, part);
+  atomicAdd(&s_allowed, allowed_mine);
+  atomicAdd(&s_zero, zero_mine);
   __syncthreads();
-  const float pmax = 1.0f / total;  // exp(0) / total
+  const int allowed = (int)s_allowed;
 
-  // the whole allowed set as a prefix: every key above 0, and all tokens whose probability underflowed to 0
+  // the whole allowed set as a prefix: every key above 0, and all tokens whose weight underflowed to 0
   unsigned keep_xb = 0u;
-  int keep_c = count_eq(p, vocab, 0u, si);
-  constexpr int kTopBit = 29;  // probabilities are at most 1 = 0x3F800000, so bits 31 and 30 of a key are 0
+  int keep_c = (int)s_zero;
+  unsigned long long kept_mass = s_total;   // mass of the prefix (keep_xb, keep_c)
+  unsigned long long above_mass;
+  unsigned above_cnt, ties;
 
   // top-k: the k-th largest key is the largest b with count(key >= b) >= k
   const int k = top_k[r];
   if (k > 0 && k < allowed) {
-    unsigned b = 0u;
-    for (int bit = kTopBit; bit >= 0; --bit) {
-      const unsigned trial = b | (1u << bit);
-      if (count_ge(p, vocab, trial, si) >= k) b = trial;
-    }
-    int above;
-    mass_gt(p, vocab, b, above, sf, si);
+    const unsigned b = search_key(p, vocab, keep_xb, keep_c, (unsigned long long)k, false, true, h, above_mass, above_cnt, ties);
     keep_xb = b;
-    keep_c = k - above;
+    keep_c = k - (int)above_cnt;
+    kept_mass = above_mass + (unsigned long long)keep_c * weight_mass(__uint_as_float(b));
   }
 
   // top-p: the crossing token's key is the largest b with (kept mass of keys >= b) >= top_p * kept mass
   const float tp = top_p[r];
-  if (tp < 1.0f) {
-    const float kept_total = mass_ge_within(p, vocab, 0u, keep_xb, keep_c, sf);
-    const float bar = tp * kept_total;
-    unsigned b = 0u;
-    for (int bit = kTopBit; bit >= 0; --bit) {
-      const unsigned trial = b | (1u << bit);
-      if (mass_ge_within(p, vocab, trial, keep_xb, keep_c, sf) >= bar) b = trial;
-    }
-    if (b < keep_xb) b = keep_xb;
-    int gt_count;
-    const float gt_mass = mass_gt(p, vocab, b, gt_count, sf, si);
-    const float x = __uint_as_float(b);
-    const int ties = (b == keep_xb) ? keep_c : count_eq(p, vocab, b, si);
+  if (tp < 1.0f && kept_mass > 0ull) {
+    unsigned long long bar = (unsigned long long)ceil((double)tp * (double)kept_mass);
+    if (bar > kept_mass) bar = kept_mass;
+    if (bar < 1ull) bar = 1ull;
+    const unsigned b = search_key(p, vocab, keep_xb, keep_c, bar, false, false, h, above_mass, above_cnt, ties);
+    const unsigned long long x = weight_mass(__uint_as_float(b));
+    const int have = (b == keep_xb) ? keep_c : (int)ties;
     int need = 1;
-    if (x > 0.f) {
-      need = (int)ceilf((bar - gt_mass) / x);
+    if (x > 0ull && bar > above_mass) {
+      const unsigned long long q = (bar - above_mass + x - 1ull) / x;
+      need = q > (unsigned long long)have ? have : (int)q;
       if (need < 1) need = 1;
     }
-    if (need > ties) need = ties;
+    if (need > have) need = have;
     keep_xb = b;
     keep_c = need;
+    kept_mass = above_mass + (unsigned long long)need * x;
   }
 
-  // min-p: drop p < min_p * p_max; what stays is {key > bits(floor) - 1} when the prefix reached below the floor
+  // min-p: drop e < min_p (the largest weight is 1); what stays is {key > bits(min_p) - 1} when the prefix reached below
   const float mp = min_p[r];
-  if (mp > 0.f) {
-    const float floor_p = mp * pmax;
-    if (__uint_as_float(keep_xb) < floor_p) {
-      keep_xb = __float_as_uint(floor_p) - 1u;
-      keep_c = 0;
-    }
+  bool recount = false;
+  if (mp > 0.f && __uint_as_float(keep_xb) < mp) {
+    keep_xb = __float_as_uint(mp) - 1u;
+    keep_c = 0;
+    recount = true;
   }
 
   // the draw: the chosen token's key is the largest b with (kept mass of keys >= b) > u * kept mass
-  int above;
-  mass_gt(p, vocab, keep_xb, above, sf, si);
   int chosen = -1;
-  if (above == 0 && keep_c == 0) {
-    chosen = imax;  // min-p above 1 left nothing: the reference keeps the first token of the order
+  if (recount) {
+    // the mass above the new floor: one pass
+    unsigned long long m = 0ull;
+    for (int v = threadIdx.x; v < vocab; v += kThreads) {
+      const float x = p[v];
+      if (x >= 0.f && __float_as_uint(x) > keep_xb) m += weight_mass(x);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) s_total = 0ull;
+    __syncthreads();
+    atomicAdd(&s_total, m);
+    __syncthreads();
+    kept_mass = s_total;
+  }
+  if (kept_mass == 0ull) {
+    chosen = imax;  // min-p above 1 left nothing (or every kept weight's mass is 0): the reference keeps the first token of the order
   } else {
-    const float mass = mass_ge_within(p, vocab, 0u, keep_xb, keep_c, sf);
     const unsigned r0 = philox4x32_10(offsets[2 * r], offsets[2 * r + 1], 0u, 0u, seeds[2 * r], seeds[2 * r + 1]);
-    const float u = (float)(r0 >> 8) * (1.0f / 16777216.0f);
-    const float target = u * mass;
-    if (mass > target) {
-      unsigned b = 0u;
-      for (int bit = kTopBit; bit >= 0; --bit) {
-        const unsigned trial = b | (1u << bit);
-        if (mass_ge_within(p, vocab, trial, keep_xb, keep_c, sf) > target) b = trial;
-      }
-      if (b < keep_xb) b = keep_xb;
-      int gt_count;
-      const float gt_mass = mass_gt(p, vocab, b, gt_count, sf, si);
-      const float x = __uint_as_float(b);
-      const int ties = (b == keep_xb) ? keep_c : count_eq(p, vocab, b, si);
-      if (ties > 0) {
-        int rnk = 0;
-        if (x > 0.f) {
-          rnk = (int)floorf((target - gt_mass) / x);
-          if (rnk < 0) rnk = 0;
-        }
-        if (rnk > ties - 1) rnk = ties - 1;
-        chosen = nth_equal(p, vocab, b, rnk, si, &s_result);
-      }
+    const double u = (double)(r0 >> 8) * (1.0 / 16777216.0);
+    unsigned long long target = (unsigned long long)(u * (double)kept_mass);   // below kept_mass, since u < 1
+    if (target >= kept_mass) target = kept_mass - 1ull;
+    const unsigned b = search_key(p, vocab, keep_xb, keep_c, target, true, false, h, above_mass, above_cnt, ties);
+    const unsigned long long x = weight_mass(__uint_as_float(b));
+    const int have = (b == keep_xb) ? keep_c : (int)ties;
+    int rnk = 0;
+    if (x > 0ull && target >= above_mass) {
+      const unsigned long long q = (target - above_mass) / x;   // tokens of this key wholly at or below the target
+      rnk = q > (unsigned long long)(have - 1) ? have - 1 : (int)q;
     }
-    if (chosen < 0) {
-      // rounding left none: the last kept token, i.e. the smallest kept key and its last kept tie
-      unsigned b = keep_xb;
-      int ties = keep_c;
-      if (ties == 0) {
-        b = 0u;  // the smallest key above keep_xb is the largest b with count(key >= b) >= above
-        for (int bit = kTopBit; bit >= 0; --bit) {
-          const unsigned trial = b | (1u << bit);
-          if (count_ge(p, vocab, trial, si) >= above) b = trial;
-        }
-        ties = count_eq(p, vocab, b, si);
-      }
-      chosen = ties > 0 ? nth_equal(p, vocab, b, ties - 1, si, &s_result) : imax;
-    }
+    if (have > 0) chosen = nth_equal(p, vocab, b, rnk, si, &s_result);
+    if (chosen < 0) chosen = imax;
   }
   if (threadIdx.x == 0) ids[r] = chosen;
 }

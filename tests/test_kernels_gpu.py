@@ -355,6 +355,9 @@ def test_sampler_matches_the_plain_sampler(kernels, vocab):
     logits[3, 10] = float("-inf")
     logits[4, 11] = float("nan")
     logits[5, 40:44] = logits[5, 40]            # ties in the middle of the order
+    logits[1] = 1.25                            # every token the same: one bucket holds the whole row, the draw is a rank among ties
+    logits[8, ::2] = 2.0                        # two values, half the row each
+    logits[8, 1::2] = 1.0
     seeds = torch.arange(R, dtype=torch.int64) * 7919 + 12345
     offsets = torch.arange(R, dtype=torch.int64) % 5
     t = torch.tensor([r[0] for r in rows], dtype=torch.float32)
