@@ -174,22 +174,6 @@ __global__ void silu_mul_vec_kernel(const T* __restrict__ x, T* __restrict__ out
   Vec<T>::store(out + t * inter + (size_t)vi * N, o);
 }
 
-// out[row] = sum of the squares of a row, for the first product of a step that norms its operand itself.
-template <typename T>
-__global__ void row_ssq_kernel(const T* __restrict__ x, float* __restrict__ out, int hidden) {
-  __shared__ float scratch[32];
-  pdl_launch_dependents();
-  pdl_wait();
-  const size_t r = blockIdx.x;
-  float ss = 0.f;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-    const float v = to_float(x[r * hidden + i]);
-    ss += v * v;
-  }
-  ss = block_sum(ss, scratch);
-  if (threadIdx.x == 0) out[r] = ss;
-}
-
 // The error words of the kernels that wait with a limit (defined beside those kernels).
 int* gemm_tcgen05_error_address();
 int* attention_error_address();
@@ -226,15 +210,6 @@ extern "C" int roost_status_snapshot(int32_t* out, int out_is_host, roost_stream
   cudaError_t e = launch_kernel(status_snapshot_kernel, dim3(1), dim3(32), 0, (cudaStream_t)stream, a, b, c, dst);
   if (e != cudaSuccess) return fail(ROOST_ERR_CUDA, std::string("status_snapshot: ") + cudaGetErrorString(e));
   return ROOST_OK;
-}
-
-extern "C" int roost_row_ssq(const void* x, float* out, int rows, int hidden, int dtype, roost_stream_t stream) {
-  ROOST_REQUIRE(rows >= 0 && hidden > 0 && x != nullptr && out != nullptr, "row_ssq: sizes and pointers must be given");
-  if (rows == 0) return ROOST_OK;
-  ROOST_DISPATCH_DTYPE(dtype, T, {
-    launch_kernel(row_ssq_kernel<T>, dim3(rows), dim3(256), 0, (cudaStream_t)stream, (const T*)x, out, hidden);
-  });
-  return check_launch("row_ssq");
 }
 
 extern "C" int roost_abi_version(void) { return ROOST_ABI_VERSION; }

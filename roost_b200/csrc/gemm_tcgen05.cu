@@ -465,61 +465,24 @@ struct StreamCfg {
 };
 constexpr int kStreamMaxCtas = 256;
 
-// Eight consecutive norm weights starting at element i (a multiple of 8) as floats.
-__device__ __forceinline__ void load_w8(const void* w, int i, int wdtype, float (&o)[8]) {
-  if (wdtype == ROOST_F32) {
-    const float4 a = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(w) + i)[0];
-    const float4 b = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(w) + i)[1];
-    o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w; o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
-  } else {
-    const uint4 u = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(w) + i);
-    const uint32_t p[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      o[2 * e] = __uint_as_float(p[e] << 16);
-      o[2 * e + 1] = __uint_as_float(p[e] & 0xffff0000u);
-    }
-  }
-}
-
-// What a weight-streaming product may take over from the kernels around it (decode steps, where a kernel's start and end
-// cost as much as its bytes). ssq_in: x is a residual stream h and the product wants its RMS norm: x's tiles are scaled in
-// shared memory, as they arrive, by 1 / sqrt(mean(h^2) + eps) and the norm's weight, rounded to bfloat16 like the norm
-// kernel's output; the rows' sums of squares come in `ssq_parts` partial sums a row ([part][m], added in order).
-// residual: the product is added to this [m, n] tensor (row stride ldo) in place, rounded once, instead of being
-// written to out; ssq_out then receives, per tile of 128 columns, the new rows' sums of squares ([tile][m]) for the
-// next product's ssq_in.
-struct StreamFuse {
-  const float* ssq_in;
-  int ssq_parts;
-  const void* norm_w;
-  int norm_wdtype;
-  float eps;
-  void* residual;
-  float* ssq_out;
-};
-
 template <typename TOut, bool SWIGLU>
-__global__ void __launch_bounds__(256, 1)
+__global__ void __launch_bounds__(192, 1)
     gemm_stream_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_constant__ CUtensorMap tma_x, TOut* __restrict__ out, int M,
-                       int N, int K, int64_t ldo, int ntok, float* ws, int* flags, const StreamFuse fuse) {
+                       int N, int K, int64_t ldo, int ntok, float* ws, int* flags) {
   using Cfg = StreamCfg<SWIGLU>;
   constexpr int STAGES_S = Cfg::kStages;
   constexpr uint32_t kStageSWBytes = Cfg::kStageW, kStageSBytes = Cfg::kStage;
   constexpr int WR = Cfg::kWRows;
   extern __shared__ unsigned char smem_raw[];
   const uint32_t smem_base = ((uint32_t)__cvta_generic_to_shared(smem_raw) + 1023u) & ~1023u;
-  __shared__ __align__(8) uint64_t bars[3 * STAGES_S + 4];
+  __shared__ __align__(8) uint64_t bars[2 * STAGES_S + 4];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
-  __shared__ float ssq_red[4][16];   // the epilogue warps' partial sums of squares of sixteen rows
   const uint32_t bar0 = (uint32_t)__cvta_generic_to_shared(bars);
   auto full_bar = [&](int s) { return bar0 + 8u * s; };
   auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES_S + s); };
   auto acc_full_bar = [&](int a) { return bar0 + 8u * (2 * STAGES_S + a); };
   auto acc_empty_bar = [&](int a) { return bar0 + 8u * (2 * STAGES_S + 2 + a); };
-  auto normed_bar = [&](int s) { return bar0 + 8u * (2 * STAGES_S + 4 + s); };   // the stage's x tile has been normed in place
-  const bool norm_x = fuse.ssq_in != nullptr;
   constexpr uint32_t kCols = 2 * Cfg::kAccCols;  // two tiles' accumulators
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -537,7 +500,6 @@ __global__ void __launch_bounds__(256, 1)
     for (int s = 0; s < STAGES_S; ++s) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
-      mbar_init(normed_bar(s), 2);   // the two warps that norm a tile
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(acc_full_bar(a), 1);
@@ -610,7 +572,7 @@ __global__ void __launch_bounds__(256, 1)
         tcgen05_fence_after();
         const uint32_t tmem_d = tmem_base + (uint32_t)acc * Cfg::kAccCols;
         for (long long u = s0; u < s1; ++u) {
-          if (!(ok = mbar_wait(norm_x ? normed_bar(stage) : full_bar(stage), phase, abortp, 3))) break;
+          if (!(ok = mbar_wait(full_bar(stage), phase, abortp, 3))) break;
           tcgen05_fence_after();
 #ifdef ROOST_TRACE
           if (u == u0) tr_mma[0] = trace_now();
@@ -638,57 +600,6 @@ __global__ void __launch_bounds__(256, 1)
       tr_mma[1] = trace_now();
       trace_flush(6 * 4 + 3, blockIdx.x * 8, tr_mma, 2);
 #endif
-    }
-  } else if (warp >= 6) {
-    // ---- the norm of x, tile by tile as the copies land (two warps, half of a tile's chunks each): x's rows are rows of a
-    // residual stream, and the product wants them scaled by 1 / sqrt(mean(h^2) + eps) and the norm's weight, rounded to
-    // bfloat16 as the norm kernel rounds its output. A tile is ntok rows of 64 elements, 128 bytes a row, sixteen-byte
-    // chunks swizzled by the row as the copy engine wrote them.
-    if (norm_x) {
-      float inv[2];   // of rows lane and lane + 32
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const int r = lane + 32 * h;
-        float ss = 0.f;
-        if (r < M)
-          for (int p = 0; p < fuse.ssq_parts; ++p) ss += fuse.ssq_in[(size_t)p * M + r];
-        inv[h] = r < M ? 1.0f / sqrtf(ss / (float)K + fuse.eps) : 0.f;
-      }
-      bool ok = true;
-      long long ui = 0;
-      const int tl = (warp - 6) * 32 + lane;   // 0..63 among the two warps: each takes half of a tile's chunks
-      for (long long u = u0; u < u1 && ok; ++u, ++ui) {
-        const int stage = (int)(ui % STAGES_S);
-        const uint32_t phase = (uint32_t)(ui / STAGES_S) & 1u;
-        const int kb = (int)(u % kbs);
-        if (!(ok = mbar_wait(full_bar(stage), phase, abortp, 8))) break;
-        const uint32_t sx = smem_base + stage * kStageSBytes + kStageSWBytes;
-        for (int q = tl; q < ntok * 8; q += 64) {   // (ntok * 8 is a multiple of 64: whole warps go round together)
-          const int r = q >> 3, ch = q & 7;
-          const uint32_t addr = sx + (uint32_t)r * 128u + (uint32_t)((ch ^ (r & 7)) << 4);
-          uint32_t v[4];
-          asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];\n" : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]) : "r"(addr));
-          const float scale = __shfl_sync(0xffffffffu, r < 32 ? inv[0] : inv[1], r & 31);
-          const int col = kb * BK + ch * 8;
-          float wn[8];   // the norm's weights of these eight columns (k is a multiple of 8: all of them exist, or none)
-          if (col < K) {
-            load_w8(fuse.norm_w, col, fuse.norm_wdtype, wn);
-          } else {
-#pragma unroll
-            for (int e = 0; e < 8; ++e) wn[e] = 0.f;
-          }
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float lo = __uint_as_float(v[e] << 16), hi = __uint_as_float(v[e] & 0xffff0000u);
-            const __nv_bfloat162 o = __floats2bfloat162_rn(lo * scale * wn[2 * e], hi * scale * wn[2 * e + 1]);
-            v[e] = *reinterpret_cast<const uint32_t*>(&o);
-          }
-          asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};\n" ::"r"(addr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]) : "memory");
-        }
-        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // the stores are visible to the tensor cores' reads
-        __syncwarp();
-        if (lane == 0) mbar_arrive(normed_bar(stage));
-      }
     }
   } else {
     const int lane_group = warp & 3;
@@ -780,20 +691,6 @@ __global__ void __launch_bounds__(256, 1)
             }
           }
         }
-        // the rows of the residual stream this thread's column is added to, fetched while the tensor cores still work
-        float hres[QMAX][16];
-        if (fuse.residual != nullptr) {
-#pragma unroll
-          for (int q = 0; q < QMAX; ++q) {
-            if (q * 16 < ntok) {
-#pragma unroll
-              for (int i = 0; i < 16; ++i) {
-                const int m = q * 16 + i;
-                hres[q][i] = (m < M && n < n_out) ? to_float(reinterpret_cast<const TOut*>(fuse.residual)[(size_t)m * ldo + n]) : 0.f;
-              }
-            }
-          }
-        }
 #ifdef ROOST_TRACE
         tr_epi[0] = trace_now();
 #endif
@@ -808,7 +705,6 @@ __global__ void __launch_bounds__(256, 1)
             uint32_t v[P][16];
 #pragma unroll
             for (int p = 0; p < P; ++p) tcgen05_ld_32x32b_x16(taddr + p * 64 + q * 16, v[p]);
-            float sq[16];   // of this thread's column, a row each
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
               const int m = q * 16 + i;
@@ -816,33 +712,7 @@ __global__ void __launch_bounds__(256, 1)
 #pragma unroll
               for (int p = 0; p < P; ++p) val[p] = contributors > 0 ? __uint_as_float(v[p][i]) + psum[p][q][i] : __uint_as_float(v[p][i]);
               const float res = SWIGLU ? silu_f(val[0]) * val[P - 1] : val[0];
-              sq[i] = 0.f;
-              if (m < M && n < n_out) {
-                if (fuse.residual != nullptr) {   // the product goes onto the residual stream: one rounding of the sum
-                  const TOut sum = from_float<TOut>(hres[q][i] + res);
-                  reinterpret_cast<TOut*>(fuse.residual)[(size_t)m * ldo + n] = sum;
-                  sq[i] = to_float(sum) * to_float(sum);
-                } else {
-                  out[(size_t)m * ldo + n] = from_float<TOut>(res);
-                }
-              }
-            }
-            if (fuse.ssq_out != nullptr) {
-              // the tile's share of the new rows' sums of squares: over the warp, then over the four warps in order
-#pragma unroll
-              for (int i = 0; i < 16; ++i) {
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) sq[i] += __shfl_xor_sync(0xffffffffu, sq[i], o);
-              }
-              asm volatile("bar.sync 1, 128;\n" ::: "memory");   // the scratch of the sixteen rows before is read
-              if (lane == 0) {
-#pragma unroll
-                for (int i = 0; i < 16; ++i) ssq_red[warp - 2][i] = sq[i];
-              }
-              asm volatile("bar.sync 1, 128;\n" ::: "memory");
-              if (etid < 16 && q * 16 + etid < M) {
-                fuse.ssq_out[(size_t)t * M + q * 16 + etid] = (ssq_red[0][etid] + ssq_red[1][etid]) + (ssq_red[2][etid] + ssq_red[3][etid]);
-              }
+              if (m < M && n < n_out) out[(size_t)m * ldo + n] = from_float<TOut>(res);
             }
           }
         }
@@ -932,7 +802,7 @@ static int launch_tcgen05_pair(const CUtensorMap& ma, const CUtensorMap& mb, voi
 
 template <typename TOut, bool SWIGLU>
 static int launch_stream(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int m, int n, int k, int64_t ldo, int ntok, float* ws,
-                         int* flags, const StreamFuse& fuse, cudaStream_t s) {
+                         int* flags, cudaStream_t s) {
   using Cfg = StreamCfg<SWIGLU>;
   static int sms = 0;
   static bool attr_set = false;
@@ -948,7 +818,7 @@ static int launch_stream(const CUtensorMap& mw, const CUtensorMap& mx, void* out
   const long long units = (long long)((n + Cfg::kWRows - 1) / Cfg::kWRows) * ((k + BK - 1) / BK);
   long long grid = sms < kStreamMaxCtas ? sms : kStreamMaxCtas;
   if (units < grid) grid = units;
-  launch_kernel(kernel, dim3((int)grid), dim3(256), smem, s, mw, mx, (TOut*)out, m, n, k, ldo, ntok, ws, flags, fuse);
+  launch_kernel(kernel, dim3((int)grid), dim3(192), smem, s, mw, mx, (TOut*)out, m, n, k, ldo, ntok, ws, flags);
   return check_launch("gemm_stream");
 }
 
@@ -1033,28 +903,8 @@ extern "C" int roost_gemm_stream_supported(int m, int n, int k, int64_t ldx, int
   return m >= 1 && m <= 64 && n >= 1 && k >= 8 && k % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0;
 }
 
-// Checks the optional fusions of a weight-streaming product and packs them for the kernel.
-static int stream_fuse(const char* who, const float* ssq_in, int ssq_parts, const void* norm_w, int norm_wdtype, float eps, void* residual,
-                       float* ssq_out, int out_dtype, StreamFuse* f) {
-  if (ssq_in != nullptr) {
-    if (ssq_parts < 1 || norm_w == nullptr || !(eps > 0.f) || (norm_wdtype != ROOST_F32 && norm_wdtype != ROOST_BF16)) {
-      return fail(ROOST_ERR_INVALID, std::string(who) + ": the norm of x needs its partial sums, its weight (float32 or bfloat16) and a positive eps");
-    }
-    if ((uintptr_t)norm_w % 16 != 0) return fail(ROOST_ERR_INVALID, std::string(who) + ": the norm weight must start on a 16-byte boundary");
-  }
-  if (ssq_out != nullptr && residual == nullptr) return fail(ROOST_ERR_INVALID, std::string(who) + ": sums of squares are those of the residual stream the product is added to");
-  if (residual != nullptr && out_dtype != ROOST_BF16) return fail(ROOST_ERR_UNSUPPORTED, std::string(who) + ": the residual stream is bfloat16");
-  *f = StreamFuse{ssq_in, ssq_parts, norm_w, norm_wdtype, eps, residual, ssq_out};
-  return ROOST_OK;
-}
-
 extern "C" int roost_gemm_stream(const void* x, const void* w, void* out, int m, int n, int k, int64_t ldx, int64_t ldw, int64_t ldo,
-                                 int out_dtype, float* ws, int32_t* flags, const float* ssq_in, int ssq_parts, const void* norm_w,
-                                 int norm_wdtype, float eps, void* residual, float* ssq_out, roost_stream_t stream) {
-  StreamFuse fuse;
-  const int frc = stream_fuse("gemm_stream", ssq_in, ssq_parts, norm_w, norm_wdtype, eps, residual, ssq_out, out_dtype, &fuse);
-  if (frc != ROOST_OK) return frc;
-  ROOST_REQUIRE(out != nullptr || residual != nullptr, "gemm_stream: neither out nor a residual stream to add to");
+                                 int out_dtype, float* ws, int32_t* flags, roost_stream_t stream) {
   ROOST_REQUIRE(out_dtype == ROOST_BF16 || out_dtype == ROOST_F32, "gemm_stream: the output is bfloat16 (1) or float32 (0)");
   ROOST_REQUIRE(ldx >= k && ldw >= k && ldo >= n, "gemm_stream: a leading dimension is smaller than its row");
   ROOST_REQUIRE(ws != nullptr && flags != nullptr, "gemm_stream: the workspace is missing");
@@ -1068,8 +918,8 @@ extern "C" int roost_gemm_stream(const void* x, const void* w, void* out, int m,
   if (rc != ROOST_OK) return rc;
   rc = make_map(&mx, x, m, k, ldx, ntok);
   if (rc != ROOST_OK) return rc;
-  if (out_dtype == ROOST_BF16) return launch_stream<__nv_bfloat16, false>(mw, mx, out, m, n, k, ldo, ntok, ws, flags, fuse, (cudaStream_t)stream);
-  return launch_stream<float, false>(mw, mx, out, m, n, k, ldo, ntok, ws, flags, fuse, (cudaStream_t)stream);
+  if (out_dtype == ROOST_BF16) return launch_stream<__nv_bfloat16, false>(mw, mx, out, m, n, k, ldo, ntok, ws, flags, (cudaStream_t)stream);
+  return launch_stream<float, false>(mw, mx, out, m, n, k, ldo, ntok, ws, flags, (cudaStream_t)stream);
 }
 
 extern "C" int roost_gemm_stream_swiglu_supported(int m, int n, int k, int64_t ldx, int64_t ldw) {
@@ -1079,11 +929,7 @@ extern "C" int roost_gemm_stream_swiglu_supported(int m, int n, int k, int64_t l
 // out[m, j] = silu(gate_j) * up_j for w's rows in blocks of 256 (128 gate rows, then the 128 up rows of the same outputs);
 // out has n / 2 columns.
 extern "C" int roost_gemm_stream_swiglu(const void* x, const void* w, void* out, int m, int n, int k, int64_t ldx, int64_t ldw, int64_t ldo,
-                                        int out_dtype, float* ws, int32_t* flags, const float* ssq_in, int ssq_parts, const void* norm_w,
-                                        int norm_wdtype, float eps, roost_stream_t stream) {
-  StreamFuse fuse;
-  const int frc = stream_fuse("gemm_stream_swiglu", ssq_in, ssq_parts, norm_w, norm_wdtype, eps, nullptr, nullptr, out_dtype, &fuse);
-  if (frc != ROOST_OK) return frc;
+                                        int out_dtype, float* ws, int32_t* flags, roost_stream_t stream) {
   ROOST_REQUIRE(out_dtype == ROOST_BF16 || out_dtype == ROOST_F32, "gemm_stream_swiglu: the output is bfloat16 (1) or float32 (0)");
   ROOST_REQUIRE(ldx >= k && ldw >= k && ldo >= n / 2, "gemm_stream_swiglu: a leading dimension is smaller than its row");
   ROOST_REQUIRE(ws != nullptr && flags != nullptr, "gemm_stream_swiglu: the workspace is missing");
@@ -1097,8 +943,8 @@ extern "C" int roost_gemm_stream_swiglu(const void* x, const void* w, void* out,
   if (rc != ROOST_OK) return rc;
   rc = make_map(&mx, x, m, k, ldx, ntok);
   if (rc != ROOST_OK) return rc;
-  if (out_dtype == ROOST_BF16) return launch_stream<__nv_bfloat16, true>(mw, mx, out, m, n, k, ldo, ntok, ws, flags, fuse, (cudaStream_t)stream);
-  return launch_stream<float, true>(mw, mx, out, m, n, k, ldo, ntok, ws, flags, fuse, (cudaStream_t)stream);
+  if (out_dtype == ROOST_BF16) return launch_stream<__nv_bfloat16, true>(mw, mx, out, m, n, k, ldo, ntok, ws, flags, (cudaStream_t)stream);
+  return launch_stream<float, true>(mw, mx, out, m, n, k, ldo, ntok, ws, flags, (cudaStream_t)stream);
 }
 
 ROOST_TRACE_TU(gemm_tcgen05)

@@ -17,7 +17,7 @@
 extern "C" {
 #endif
 
-#define ROOST_ABI_VERSION 7
+#define ROOST_ABI_VERSION 6
 
 #define ROOST_OK 0
 #define ROOST_ERR_INVALID 1      /* an argument is out of range or inconsistent; nothing was launched */
@@ -173,28 +173,17 @@ int roost_gemm_tcgen05_swiglu(const void* a, const void* w, void* out, int m, in
  * CTA per SM, the products on tcgen05 with w's rows as the 128-row operand, the work split into equal contiguous ranges
  * of (128 rows x 64 k) units with a fixed-order fix-up of tiles shared by neighbouring CTAs (gemm_tcgen05.cu).
  * ws: roost_gemm_stream_workspace_floats() floats, flags: roost_gemm_stream_workspace_flags() int32, zero before the first
- * call and left zero by every call.
- * Two things a decode step's neighbouring kernels would do may be folded in (each optional: null pointers leave it out).
- * ssq_in: x is a residual stream and the product wants its RMS norm: every tile of x is scaled in shared memory by
- * 1 / sqrt(sum(x_row^2) / k + eps) and norm_w (k weights of dtype norm_wdtype), rounded to bfloat16 as the norm kernel
- * rounds its output; the rows' sums of squares are given as ssq_parts partial sums a row, ssq_in[part * m + row], added
- * in order. residual: the product is added to residual[row * ldo + col] in place (bfloat16, one rounding of the sum)
- * and out is not written; ssq_out[tile * m + row] then receives, for every tile of 128 columns, the new rows' sums of
- * squares: the next product's ssq_in, with ceil(n / 128) parts. roost_row_ssq gives the sums of a tensor no product wrote. */
+ * call and left zero by every call. */
 int roost_gemm_stream_workspace_floats(void);
 int roost_gemm_stream_workspace_flags(void);
 int roost_gemm_stream_supported(int m, int n, int k, int64_t ldx, int64_t ldw);
 int roost_gemm_stream(const void* x, const void* w, void* out, int m, int n, int k, int64_t ldx, int64_t ldw, int64_t ldo,
-                      int out_dtype, float* ws, int32_t* flags, const float* ssq_in, int ssq_parts, const void* norm_w, int norm_wdtype,
-                      float eps, void* residual, float* ssq_out, roost_stream_t stream);
-/* out[row] = sum over the row's `hidden` elements of x^2, in 32-bit (one part of a product's ssq_in). */
-int roost_row_ssq(const void* x, float* out, int rows, int hidden, int dtype, roost_stream_t stream);
+                      int out_dtype, float* ws, int32_t* flags, roost_stream_t stream);
 /* The same with the SwiGLU of the fused product: w's rows in blocks of 256 (128 gate rows, then the 128 up rows of the
  * same outputs), out[m, j] = silu(gate_j) * up_j with n / 2 columns; at most 32 rows of x, n a multiple of 256. */
 int roost_gemm_stream_swiglu_supported(int m, int n, int k, int64_t ldx, int64_t ldw);
 int roost_gemm_stream_swiglu(const void* x, const void* w, void* out, int m, int n, int k, int64_t ldx, int64_t ldw, int64_t ldo,
-                             int out_dtype, float* ws, int32_t* flags, const float* ssq_in, int ssq_parts, const void* norm_w,
-                             int norm_wdtype, float eps, roost_stream_t stream);
+                             int out_dtype, float* ws, int32_t* flags, roost_stream_t stream);
 
 /* ids[r] = index of the largest logit of row r, ties to the lowest index, NaN never chosen (-1 if none). */
 int roost_argmax(const float* logits, int64_t stride, int rows, int vocab, int32_t* ids, roost_stream_t stream);

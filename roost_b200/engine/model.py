@@ -13,7 +13,7 @@ import torch
 
 from ..config.reader import ConfigReader
 from ..config.spec import ModelSpec
-from ..parts.base import BLOCKS, NORMS, ParamDecl, Runtime, StreamStats
+from ..parts.base import BLOCKS, NORMS, ParamDecl, Runtime
 from ..parts.linear import Linear
 from .. import registry
 from ..weights import loader as weight_loader
@@ -117,9 +117,7 @@ class Model:
             h, residual = self.blocks[e.block](h, residual, batch, storage.view(owner), write_cache=e.reads_cache_of is None)
         if batch.num_selected == 0:
             return torch.empty((0, self.spec.vocab), dtype=torch.float32, device=self.rt.device)
-        if isinstance(h, StreamStats):     # the last block has added its output to the stream already
-            final = self.final_norm(residual, rows=batch.selected)
-        elif residual is None:
+        if residual is None:
             final = self.final_norm(h, rows=batch.selected)
         else:
             final, _ = self.final_norm.add_norm(h, residual, rows=batch.selected)

@@ -13,7 +13,7 @@ import torch
 
 from . import build
 
-ABI_VERSION = 7
+ABI_VERSION = 6
 F32, BF16 = 0, 1
 
 
@@ -85,11 +85,10 @@ _SIGNATURES = {
     "roost_gemm_stream_workspace_flags": [],
     "roost_gemm_stream_supported": [c_int, c_int, c_int, c_int64, c_int64],
     "roost_gemm_stream": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int, c_void_p, c_void_p,
-                          c_void_p, c_int, c_void_p, c_int, c_float, c_void_p, c_void_p, c_void_p],
-    "roost_row_ssq": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+                          c_void_p],
     "roost_gemm_stream_swiglu_supported": [c_int, c_int, c_int, c_int64, c_int64],
     "roost_gemm_stream_swiglu": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int, c_void_p, c_void_p,
-                                 c_void_p, c_int, c_void_p, c_int, c_float, c_void_p],
+                                 c_void_p],
     "roost_argmax": [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p],
     "roost_argmax_split": [c_void_p, c_int64, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
     "roost_sample": [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -322,31 +321,8 @@ class KernelLibrary:
                                     torch.zeros(self._lib.roost_gemm_stream_workspace_flags(), dtype=torch.int32, device=device))
         return ws
 
-    @staticmethod
-    def _pre_norm_args(pre_norm, m: int, k: int, who: str):
-        """(ssq pointer, parts, weight pointer, weight dtype code, eps) of a product that norms its operand itself."""
-        if pre_norm is None:
-            return None, 0, None, F32, 0.0
-        ssq, weight, eps = pre_norm
-        _need(ssq, "ssq", torch.float32); _need(weight, "norm weight")
-        if ssq.dim() != 2 or ssq.shape[1] != m or weight.numel() != k:
-            raise KernelError(f"{who}: the sums of squares are {tuple(ssq.shape)} and the norm weight has {weight.numel()} elements for x of {(m, k)}")
-        return _ptr(ssq), ssq.shape[0], _ptr(weight), dtype_code(weight.dtype), float(eps)
-
-    def row_ssq(self, x: torch.Tensor) -> torch.Tensor:
-        """Sums of squares of x's rows as one part [1, rows] of a product's ``pre_norm``."""
-        _need(x, "x")
-        rows, hidden = x.shape
-        out = torch.empty((1, rows), dtype=torch.float32, device=x.device)
-        self._call("roost_row_ssq", _ptr(x), _ptr(out), rows, hidden, dtype_code(x.dtype), _stream())
-        return out
-
-    def gemm_stream(self, x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None, pre_norm=None, add_to=None):
-        """x [M <= 64, K] times w [N, K] transposed: the weight-streaming tcgen05 product of decode steps.
-        ``pre_norm`` = (ssq [parts, M] float32, norm weight [K], eps): x is a residual stream and the product takes its
-        RMS norm, scaling x's tiles as they arrive (no norm kernel, no normed copy of x in memory). ``add_to`` = a
-        bfloat16 residual stream [M, N]: the product is added to it in place and the call returns (the stream, the sums
-        of squares of its new rows [ceil(N / 128), M] for the next product's ``pre_norm``)."""
+    def gemm_stream(self, x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+        """x [M <= 64, K] times w [N, K] transposed: the weight-streaming tcgen05 product of decode steps."""
         _need(x, "x", torch.bfloat16); _need(w, "w", torch.bfloat16)
         M, K = x.shape
         N, K2 = w.shape
@@ -354,27 +330,17 @@ class KernelLibrary:
             raise KernelError(f"gemm_stream: x has {K} columns, w has {K2}")
         ws = self._stream_workspace(x.device)
         out_dtype = out_dtype or torch.bfloat16
-        ssq_in, parts, nw, nwd, eps = self._pre_norm_args(pre_norm, M, K, "gemm_stream")
-        if add_to is not None:
-            _need(add_to, "residual", torch.bfloat16)
-            if tuple(add_to.shape) != (M, N) or out_dtype != torch.bfloat16:
-                raise KernelError(f"gemm_stream: the residual stream is {tuple(add_to.shape)}; the product is {(M, N)} bfloat16")
-            ssq_out = torch.empty((-(-N // 128), M), dtype=torch.float32, device=x.device)
-            self._call("roost_gemm_stream", _ptr(x), _ptr(w), None, M, N, K, x.stride(0), w.stride(0), add_to.stride(0), BF16, _ptr(ws[0]),
-                       _ptr(ws[1]), ssq_in, parts, nw, nwd, eps, _ptr(add_to), _ptr(ssq_out), _stream())
-            return add_to, ssq_out
         out = torch.empty((M, N), dtype=out_dtype, device=x.device)
         self._call("roost_gemm_stream", _ptr(x), _ptr(w), _ptr(out), M, N, K, x.stride(0), w.stride(0), out.stride(0),
-                   dtype_code(out_dtype), _ptr(ws[0]), _ptr(ws[1]), ssq_in, parts, nw, nwd, eps, None, None, _stream())
+                   dtype_code(out_dtype), _ptr(ws[0]), _ptr(ws[1]), _stream())
         return out
 
     def gemm_stream_swiglu_supported(self, m: int, n: int, k: int, ldx: int, ldw: int) -> bool:
         return bool(self._lib.roost_gemm_stream_swiglu_supported(m, n, k, ldx, ldw))
 
-    def gemm_stream_swiglu(self, x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None, pre_norm=None) -> torch.Tensor:
+    def gemm_stream_swiglu(self, x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
         """silu(x Wg^T) * (x Wu^T) for x [M <= 32, K] and w [2I, K] with gate and up rows interleaved in blocks of 128:
-        the weight-streaming product with the activation applied to its accumulators; returns [M, I]. ``pre_norm`` as
-        in ``gemm_stream``."""
+        the weight-streaming product with the activation applied to its accumulators; returns [M, I]."""
         _need(x, "x", torch.bfloat16); _need(w, "w", torch.bfloat16)
         M, K = x.shape
         N, K2 = w.shape
@@ -382,10 +348,9 @@ class KernelLibrary:
             raise KernelError(f"gemm_stream_swiglu: x has {K} columns, w has {K2}")
         ws = self._stream_workspace(x.device)
         out_dtype = out_dtype or torch.bfloat16
-        ssq_in, parts, nw, nwd, eps = self._pre_norm_args(pre_norm, M, K, "gemm_stream_swiglu")
         out = torch.empty((M, N // 2), dtype=out_dtype, device=x.device)
         self._call("roost_gemm_stream_swiglu", _ptr(x), _ptr(w), _ptr(out), M, N, K, x.stride(0), w.stride(0), out.stride(0),
-                   dtype_code(out_dtype), _ptr(ws[0]), _ptr(ws[1]), ssq_in, parts, nw, nwd, eps, _stream())
+                   dtype_code(out_dtype), _ptr(ws[0]), _ptr(ws[1]), _stream())
         return out
 
     def attention_set_decode_tma(self, on: bool) -> None:

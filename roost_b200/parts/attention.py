@@ -71,12 +71,7 @@ class PagedAttention(Mixer):
         s = self.spec
         return CacheNeed(kind="paged", kv_heads=s.num_kv_heads, head_dim=s.head_dim, window=s.window)
 
-    fuses_norm = True
-
-    def fusable(self, tokens: int) -> bool:
-        return self.qkv.fusable(tokens) and self.out.fusable(tokens)
-
-    def __call__(self, x, batch, cache, write_cache: bool = True, pre_norm=None, add_to=None):
+    def __call__(self, x, batch, cache, write_cache: bool = True):
         s, k = self.spec, self.rt.kernels
         tables = batch.groups[cache.group]
         inv_freq, rotary_dim = self.position.rotation() if self.position is not None else (None, 0)
@@ -87,7 +82,7 @@ class PagedAttention(Mixer):
         kw = self.k_norm.weight if self.k_norm is not None else None
         table = batch.rotation_table(k, inv_freq) if rotary_dim else None
         if write_cache:
-            qkv = self.qkv(x, pre_norm=pre_norm)
+            qkv = self.qkv(x)
             q = k.qk_norm_rope_cache(qkv, s.num_heads, s.num_kv_heads, s.head_dim, q_w=qw, k_w=kw, eps=eps,
                                      inv_freq=inv_freq, rotary_dim=rotary_dim, positions=batch.positions, cos_sin=table,
                                      k_pool=cache.k_pool, v_pool=cache.v_pool, slot_mapping=tables.slot_mapping,
@@ -96,10 +91,10 @@ class PagedAttention(Mixer):
             if self.q_only is None:
                 self.q_only = Linear(self.rt, self.q_width, s.hidden)
                 self.q_only.load(self.qkv.weight[: self.q_width])
-            q = k.qk_norm_rope_cache(self.q_only(x, pre_norm=pre_norm), s.num_heads, s.num_kv_heads, s.head_dim, q_w=qw, k_w=kw, eps=eps,
+            q = k.qk_norm_rope_cache(self.q_only(x), s.num_heads, s.num_kv_heads, s.head_dim, q_w=qw, k_w=kw, eps=eps,
                                      inv_freq=inv_freq, rotary_dim=rotary_dim, positions=batch.positions, write_kv=False, cos_sin=table)
         o = self.attend(q, batch, cache, tables)
-        return self.out(o, add_to=add_to)
+        return self.out(o)
 
     def attend(self, q, batch, cache, tables):
         """bfloat16 with a head size the tensor-core kernels serve goes to them; float32 and every other head size

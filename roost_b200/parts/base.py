@@ -44,18 +44,6 @@ class CacheNeed:
     state_dtype: torch.dtype = torch.float32
 
 
-@dataclass
-class StreamStats:
-    """Stands in the place of a block's branch output when that output has already been added to the residual stream:
-    ``ssq`` holds the sums of squares of the stream's rows, [parts, rows] float32 (the parts are added in order), which is
-    all the next norm needs of the stream besides the stream itself. A block that takes no part in the fusion norms
-    the stream with its norm kernel and ignores the sums."""
-    ssq: torch.Tensor
-
-
-FUSED_STEP_MAX_TOKENS = 16   # steps of at most this many tokens may fold norms and residual sums into their products
-
-
 class Runtime:
     """What every part is built with: the compute dtype of activations (and of the cache), the device, and
     the kernel library handle (None only for declaring parameters on a machine without a GPU)."""
@@ -70,9 +58,6 @@ class Runtime:
         self.small_gemm = os.environ.get("ROOST_SMALL_GEMM", "auto")
         if self.small_gemm not in ("auto", "library", "stream"):
             raise ValueError(f"ROOST_SMALL_GEMM={self.small_gemm!r} is not one of auto, library, stream")
-        # decode steps fold each norm into the product after it and each residual sum into the product before it
-        # (parts/block.py); ROOST_FUSE_DECODE=0 keeps every kernel of its own, for comparison
-        self.fuse_decode = os.environ.get("ROOST_FUSE_DECODE", "1") != "0"
 
     @property
     def full_precision(self) -> bool:
@@ -105,17 +90,6 @@ class Norm(Part):
 
 
 class Mixer(Part):
-    # True for a mixer whose call takes ``pre_norm`` and ``add_to`` (see ``fusable``): its first product can norm the
-    # residual stream it is given and its last product can add its result to that stream.
-    fuses_norm = False
-
-    def fusable(self, tokens: int) -> bool:
-        """Whether a step of ``tokens`` tokens may call this mixer with ``pre_norm`` = (sums of squares [parts, tokens],
-        norm weight, eps) in place of a normed input (``x`` is then the residual stream itself) and ``add_to`` = the
-        residual stream, to which the result is added in place; the call then returns (the stream, the sums of squares
-        of its new rows)."""
-        return False
-
     # True for a mixer with state of its own whose call reads the step's device tables only (``state_slots``, ``token_row``,
     # ``positions``, ``q_indptr`` ...), never host values: a step is the same sequence of launches whatever its rows are,
     # so the executor may capture it. The default keeps such a model's steps eager (a mixer written as a Python loop over
@@ -160,11 +134,6 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
-    fuses_norm = False     # as for a mixer
-
-    def fusable(self, tokens: int) -> bool:
-        return False
-
     def __call__(self, x: torch.Tensor, batch) -> torch.Tensor:
         raise NotImplementedError
 

@@ -5,7 +5,7 @@ activation dtype and every sum is formed in 32-bit and rounded once."""
 from __future__ import annotations
 
 from ..config.spec import BlockSpec
-from .base import FEED_FORWARDS, FUSED_STEP_MAX_TOKENS, MIXERS, NORMS, Block, Runtime, StreamStats, register_block
+from .base import FEED_FORWARDS, MIXERS, NORMS, Block, Runtime, register_block
 
 
 class PreNormBlock(Block):
@@ -26,27 +26,10 @@ class PreNormBlock(Block):
         return {"input_norm": (NORMS, spec.input_norm), "mixer": (MIXERS, spec.mixer),
                 "post_mixer_norm": (NORMS, spec.post_mixer_norm), "feed_forward": (FEED_FORWARDS, spec.feed_forward)}
 
-    def fused(self, tokens: int) -> bool:
-        """A step of few tokens (a decode step) runs the block as four products and the mixer's own kernels: each norm is
-        folded into the product after it, each residual sum into the product before it, where every part can."""
-        return (tokens <= FUSED_STEP_MAX_TOKENS and getattr(self.input_norm, "stream_fusable", False)
-                and getattr(self.post_mixer_norm, "stream_fusable", False) and getattr(self.mixer, "fuses_norm", False)
-                and getattr(self.feed_forward, "fuses_norm", False) and self.mixer.fusable(tokens) and self.feed_forward.fusable(tokens))
-
     def __call__(self, h, residual, batch, cache, write_cache: bool = True):
         """``h`` is the previous branch output (or the embedding), ``residual`` the stream before it was added
-        (None at the first block). Returns the feed-forward's output and the stream it is still to be added to; or,
-        from a fused step, ``StreamStats`` and the stream with everything added."""
-        if (residual is None or isinstance(h, StreamStats)) and self.fused(batch.num_tokens):
-            if residual is None:
-                residual, h = h, StreamStats(self.rt.kernels.row_ssq(h))
-            eps1, eps2 = self.input_norm.spec.eps, self.post_mixer_norm.spec.eps
-            residual, ssq = self.mixer(residual, batch, cache, write_cache, pre_norm=(h.ssq, self.input_norm.weight, eps1), add_to=residual)
-            residual, ssq = self.feed_forward(residual, batch, pre_norm=(ssq, self.post_mixer_norm.weight, eps2), add_to=residual)
-            return StreamStats(ssq), residual
-        if isinstance(h, StreamStats):      # the block before has added its output to the stream already
-            x = self.input_norm(residual)
-        elif residual is None:
+        (None at the first block). Returns the feed-forward's output and the stream it is still to be added to."""
+        if residual is None:
             residual = h
             x = self.input_norm(h)
         else:

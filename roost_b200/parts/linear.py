@@ -28,21 +28,10 @@ class Linear:
             raise ValueError(f"linear: weight is {tuple(weight.shape)}; expected {(self.out_features, self.in_features)}")
         self.weight = weight.to(self.rt.dtype).contiguous()
 
-    def fusable(self, rows: int) -> bool:
-        """Whether a product of ``rows`` rows can take ``pre_norm`` and ``add_to``: the weight-streaming kernel serves it."""
-        k = self.rt.kernels
-        return (not self.rt.full_precision and self.rt.fuse_decode and hasattr(k, "row_ssq")
-                and k.gemm_stream_supported(rows, self.out_features, self.in_features, self.in_features, self.in_features))
-
-    def __call__(self, x: torch.Tensor, out_dtype: torch.dtype | None = None, pre_norm=None, add_to=None):
-        """``pre_norm`` = (sums of squares [parts, rows], norm weight, eps): x is a residual stream and the product takes
-        its RMS norm; ``add_to`` = a residual stream the product is added to in place, the call then returns (the
-        stream, the sums of squares of its new rows). Both only where ``fusable`` says so."""
+    def __call__(self, x: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
         global _MM_OUT_DTYPE
         k = self.rt.kernels
         out_dtype = out_dtype or self.rt.dtype
-        if pre_norm is not None or add_to is not None:
-            return k.gemm_stream(x, self.weight, out_dtype, pre_norm=pre_norm, add_to=add_to)
         if self.rt.full_precision:
             return k.gemm_simt(x, self.weight, torch.float32)
         M = x.shape[0]

@@ -45,19 +45,8 @@ class GatedMlp(FeedForward):
         self.gate_up.load(w)
         self.down.load(params["down"])
 
-    fuses_norm = True
-
-    def fusable(self, tokens: int) -> bool:
-        k, w = self.rt.kernels, self.gate_up.weight
-        return (bool(self.interleave) and self.down.fusable(tokens) and hasattr(k, "gemm_stream_swiglu")
-                and k.gemm_stream_swiglu_supported(tokens, w.shape[0], w.shape[1], w.shape[1], w.stride(0)))
-
-    def __call__(self, x, batch=None, pre_norm=None, add_to=None):
+    def __call__(self, x, batch=None):
         k = self.rt.kernels
-        if pre_norm is not None or add_to is not None:
-            # a decode step: the gate/up product norms the residual stream it reads and applies the activation to its
-            # accumulators, the down projection adds its result to the stream
-            return self.down(k.gemm_stream_swiglu(x, self.gate_up.weight, pre_norm=pre_norm), add_to=add_to)
         if self.interleave and x.shape[0] >= self.fused_min_rows and x.is_contiguous():
             return self.down(k.gemm_tcgen05_swiglu(x, self.gate_up.weight))
         if (self.interleave and x.shape[0] <= self.fused_max_stream_rows and x.is_contiguous()

@@ -10,8 +10,6 @@ from .base import Norm, ParamDecl, Runtime, register_norm
 
 
 class RmsNorm(Norm):
-    stream_fusable = True    # a product can take this norm over: it is fully described by ``weight`` and ``spec.eps``
-
     def __init__(self, spec: NormSpec, runtime: Runtime):
         if spec.size <= 0 or spec.eps <= 0:
             raise ValueError(f"rms_norm: size {spec.size} and eps {spec.eps} must be positive")

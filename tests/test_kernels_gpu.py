@@ -611,65 +611,3 @@ def test_gemm_stream(kernels, m, n, k, out_dtype):
     r = m // 2
     assert torch.equal(kernels.gemm_stream(a[r : r + 1].contiguous(), w, out_dtype), got[r : r + 1]), "a row depends on its batch"
     assert not kernels.gemm_stream_supported(65, n, k, k, k) and not kernels.gemm_stream_supported(m, n, k + 4, k + 4, k + 4)
-
-
-@pytest.mark.parametrize("m,n,k", [(1, 272, 96), (8, 6144, 4096), (8, 4096, 12288), (5, 1024, 1000), (16, 4096, 4096), (23, 384, 512)])
-@pytest.mark.parametrize("wdtype", [torch.bfloat16, torch.float32])
-def test_gemm_stream_takes_over_the_norm_before_it_and_the_residual_sum_after_it(kernels, m, n, k, wdtype):
-    """The weight-streaming product with the work of its neighbours folded in: the RMS norm of its operand (x's tiles scaled
-    in shared memory from the rows' sums of squares, given in several parts) and the residual sum with the sums of squares
-    of the new rows, tile by tile, for the next product. Compared with the norm kernel followed by the plain product and a
-    separate sum; the sums of squares must be those of the stored (rounded) rows."""
-    eps = 1e-5
-    h = rand((m, k), torch.bfloat16, 61, 2.0)
-    w = rand((n, k), torch.bfloat16, 62, 1 / math.sqrt(k))
-    nw = (1 + 0.2 * torch.randn(k, generator=torch.Generator().manual_seed(63))).to(wdtype).cuda()
-    # the rows' sums of squares in three uneven parts, as three tiles of a product before would leave them
-    hf = h.float()
-    cuts = [0, k // 3, k // 2, k]
-    ssq = torch.stack([(hf[:, a:b] ** 2).sum(1) for a, b in zip(cuts, cuts[1:])]).contiguous()
-    got = kernels.gemm_stream(h, w, pre_norm=(ssq, nw, eps))
-    assert kernels.gemm_tcgen05_status() == 0, "a bounded wait inside the kernel was given up"
-    normed = kernels.rms_norm(h, nw, eps)
-    two = kernels.gemm_stream(normed, w)
-    want = plain.rms_norm(h.double().cpu(), nw.double().cpu(), eps) @ w.double().cpu().T
-    close(got, want, torch.bfloat16, "product of the normed operand", scale=2)
-    close(got, two.double(), torch.bfloat16, "against the norm kernel and the plain product", scale=2)
-    assert torch.equal(kernels.gemm_stream(h, w, pre_norm=(ssq, nw, eps)), got), "the product is not repeatable"
-    assert torch.equal(kernels.gemm_stream(h, w, pre_norm=(kernels.row_ssq(h), nw, eps))[m // 2], kernels.gemm_stream(
-        h[m // 2 : m // 2 + 1].contiguous(), w, pre_norm=(kernels.row_ssq(h[m // 2 : m // 2 + 1].contiguous()), nw, eps))[0]), "a row depends on its batch"
-    close(kernels.row_ssq(h)[0], (h.double().cpu() ** 2).sum(1), torch.float32, "row_ssq", scale=4)
-    # the residual sum: out-of-place reference first
-    res = rand((m, n), torch.bfloat16, 64, 1.5)
-    want_sum = (res.double().cpu() + h.double().cpu() @ w.double().cpu().T)
-    stream = res.clone()
-    same, ssq_out = kernels.gemm_stream(h, w, add_to=stream)
-    assert same is stream and ssq_out.shape == (-(-n // 128), m)
-    close(stream, want_sum, torch.bfloat16, "residual stream with the product added", scale=2)
-    stored = stream.float()
-    want_ssq = torch.stack([(stored[:, t * 128 : (t + 1) * 128] ** 2).sum(1) for t in range(-(-n // 128))])
-    close(ssq_out, want_ssq.double(), torch.float32, "sums of squares of the stored rows, tile by tile", scale=8)
-    # both at once, as the gate/up product and the down projection of a decode step use them
-    if n == k:
-        stream2 = h.clone()
-        _, ssq2 = kernels.gemm_stream(h, w, pre_norm=(ssq, nw, eps), add_to=stream2)
-        close(stream2, h.double().cpu() + want, torch.bfloat16, "norm in, residual out", scale=2)
-    with pytest.raises(Exception):
-        kernels.gemm_stream(h, w, pre_norm=(ssq[:, :-1].contiguous() if m > 1 else ssq[:, :0].contiguous(), nw, eps))
-
-
-@pytest.mark.parametrize("m,inter,k", [(8, 384, 96), (8, 12288, 4096), (3, 3072, 1024)])
-def test_gemm_stream_swiglu_takes_over_the_norm_before_it(kernels, m, inter, k):
-    eps = 1e-6
-    h = rand((m, k), torch.bfloat16, 71, 2.0)
-    gate = rand((inter, k), torch.bfloat16, 72, 1 / math.sqrt(k))
-    up = rand((inter, k), torch.bfloat16, 73, 1 / math.sqrt(k))
-    w = torch.stack([gate.reshape(inter // 128, 128, k), up.reshape(inter // 128, 128, k)], dim=1).reshape(2 * inter, k).contiguous()
-    nw = (1 + 0.2 * torch.randn(k, generator=torch.Generator().manual_seed(74))).to(torch.bfloat16).cuda()
-    got = kernels.gemm_stream_swiglu(h, w, pre_norm=(kernels.row_ssq(h), nw, eps))
-    assert kernels.gemm_tcgen05_status() == 0
-    x = plain.rms_norm(h.double().cpu(), nw.double().cpu(), eps)
-    want = plain.silu_and_mul(x @ gate.double().cpu().T, x @ up.double().cpu().T)
-    close(got, want, torch.bfloat16, "gemm_stream_swiglu of the normed operand", scale=2)
-    two = kernels.gemm_stream_swiglu(kernels.rms_norm(h, nw, eps), w)
-    close(got, two.double(), torch.bfloat16, "against the norm kernel and the plain product", scale=2)
