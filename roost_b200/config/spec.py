@@ -64,6 +64,24 @@ class GatedMlpSpec(FeedForwardSpec):
 
 
 @dataclass(frozen=True)
+class EmbeddingSpec:
+    """How token ids become the first hidden states. ``table``: a row copy, no scaling
+    (src/Starlings.Roost.Ops/CpuOps.cs:441-458)."""
+    kind: str = "table"
+    vocab: int = 0
+    hidden: int = 0
+
+
+@dataclass(frozen=True)
+class HeadSpec:
+    """How the final hidden states of the wanted rows become logits. ``linear``: a product with a [vocab, hidden] matrix
+    into 32-bit logits, no soft cap (src/Starlings.Roost.Ops/CpuOps.cs:465-495)."""
+    kind: str = "linear"
+    vocab: int = 0
+    hidden: int = 0
+
+
+@dataclass(frozen=True)
 class BlockSpec:
     """One layer's parts and their arrangement. ``pre_norm``: h += mixer(norm1(h)); h += ff(norm2(h))."""
     mixer: MixerSpec
@@ -94,11 +112,19 @@ class ModelSpec:
     max_positions: int
     stop_token_ids: tuple[int, ...] = ()
     stored_dtype: str = "bfloat16"
+    # the two ends of the model as parts of their own kinds (None: a table embedding and a linear head of the model's
+    # vocabulary and width)
+    embedding: EmbeddingSpec | None = None
+    head: HeadSpec | None = None
     # checkpoint tensor names: scope -> {part-local parameter name -> tuple of checkpoint names whose rows
     # are concatenated in order}. Scopes: "embed", "final_norm", "lm_head", "blocks.<i>.<part>".
     weight_names: dict = field(default_factory=dict, compare=False, hash=False)
 
     def __post_init__(self):
+        if self.embedding is None:
+            object.__setattr__(self, "embedding", EmbeddingSpec(vocab=self.vocab, hidden=self.hidden))
+        if self.head is None:
+            object.__setattr__(self, "head", HeadSpec(vocab=self.vocab, hidden=self.hidden))
         for n, e in enumerate(self.schedule):
             if not 0 <= e.block < len(self.blocks):
                 raise ValueError(f"schedule entry {n} names block {e.block}; the model has {len(self.blocks)}")

@@ -1,8 +1,8 @@
 """A model: blocks built from a ``ModelSpec``, run in the order of its schedule.
 
-The forward pass of one step is: embedding gather; every schedule entry's block over the step's tokens with
-that entry's cache; the final norm of the selected rows (the last residual sum fused into it); the output
-projection to 32-bit logits (src/Starlings.Roost.Models.Tiny/RoostTiny.cs:39-56). Logits are float32 whatever
+The forward pass of one step is: the embedding part; every schedule entry's block over the step's tokens with
+that entry's cache; the final norm of the selected rows (the last residual sum fused into it); the head part, which
+gives 32-bit logits (src/Starlings.Roost.Models.Tiny/RoostTiny.cs:39-56). Logits are float32 whatever
 the activation dtype is, as the reference's LmHead (src/Starlings.Roost.Ops/CpuOps.cs:465-495).
 """
 from __future__ import annotations
@@ -13,7 +13,7 @@ import torch
 
 from ..config.reader import ConfigReader
 from ..config.spec import ModelSpec
-from ..parts.base import BLOCKS, NORMS, ParamDecl, Runtime
+from ..parts.base import BLOCKS, EMBEDDINGS, HEADS, NORMS, ParamDecl, Runtime
 from ..parts.linear import Linear
 from .. import registry
 from ..weights import loader as weight_loader
@@ -21,7 +21,7 @@ from ..weights import loader as weight_loader
 
 def parameter_declarations(spec: ModelSpec) -> dict[str, dict[str, ParamDecl]]:
     """scope -> local parameter -> declaration, from the part classes alone (no device needed)."""
-    decls: dict[str, dict[str, ParamDecl]] = {"embed": {"table": ParamDecl(shape=(spec.vocab, spec.hidden))}}
+    decls: dict[str, dict[str, ParamDecl]] = {"embed": EMBEDDINGS.get(spec.embedding.kind).parameters(spec.embedding)}
     for i, b in enumerate(spec.blocks):
         block_cls = BLOCKS.get(b.kind)
         for part_name, (reg, part_spec) in block_cls.sub_specs(b).items():
@@ -30,7 +30,7 @@ def parameter_declarations(spec: ModelSpec) -> dict[str, dict[str, ParamDecl]]:
                 decls[f"blocks.{i}.{part_name}"] = params
     decls["final_norm"] = NORMS.get(spec.final_norm.kind).parameters(spec.final_norm)
     if not spec.tie_embeddings:
-        decls["lm_head"] = {"weight": ParamDecl(shape=(spec.vocab, spec.hidden))}
+        decls["lm_head"] = HEADS.get(spec.head.kind).parameters(spec.head)
     return decls
 
 
@@ -40,8 +40,8 @@ class Model:
         self.rt = runtime
         self.blocks = [BLOCKS.build(b, runtime) for b in spec.blocks]
         self.final_norm = NORMS.build(spec.final_norm, runtime)
-        self.embed_table: torch.Tensor | None = None
-        self.lm_head = Linear(runtime, spec.vocab, spec.hidden)
+        self.embedding = EMBEDDINGS.build(spec.embedding, runtime)
+        self.head = HEADS.build(spec.head, runtime)
         # what each run keeps between steps (None: nothing, or another run's cache)
         self.cache_needs = []
         for n, e in enumerate(spec.schedule):
@@ -67,18 +67,23 @@ class Model:
     def load(self, params: dict[str, dict[str, torch.Tensor]]) -> None:
         decls = parameter_declarations(self.spec)
         placed = {scope: {k: self._place(v, decls[scope][k]) for k, v in p.items()} for scope, p in params.items()}
-        self.embed_table = placed["embed"]["table"].to(self.rt.dtype).contiguous()
+        self.embedding.load(placed["embed"])
         for i, block in enumerate(self.blocks):
             for name, part in block.sub_parts().items():
                 part.load(placed.get(f"blocks.{i}.{name}", {}))
         self.final_norm.load(placed["final_norm"])
         if self.spec.tie_embeddings:
-            self.lm_head.weight = self.embed_table
+            shared = self.embedding.tied_weight()
+            if shared is None:
+                raise ValueError(f"the model ties its head to its embedding, but an embedding of kind '{self.spec.embedding.kind}' has no matrix to share")
+            self.head.load({"weight": shared})
         else:
-            self.lm_head.load(placed["lm_head"]["weight"])
+            self.head.load(placed["lm_head"])
 
     def parts(self):
-        """Every part of every block, for questions asked of all of them."""
+        """Every part of the model, for questions asked of all of them."""
+        yield self.embedding
+        yield self.head
         for b in self.blocks:
             yield b
             yield from b.sub_parts().values()
@@ -92,17 +97,14 @@ class Model:
                 seen.add(t.data_ptr())
                 total += t.numel() * t.element_size()
 
-        add(self.embed_table)
-        add(self.lm_head.weight)
-        for b in self.blocks:
-            for part in b.sub_parts().values():
-                for v in vars(part).values():
-                    if isinstance(v, torch.Tensor):
-                        add(v)
-                    elif isinstance(v, Linear):
-                        add(v.weight)
-                    elif hasattr(v, "weight") and isinstance(getattr(v, "weight"), torch.Tensor):
-                        add(v.weight)
+        for part in [self.embedding, self.head] + [p for b in self.blocks for p in b.sub_parts().values()]:
+            for v in vars(part).values():
+                if isinstance(v, torch.Tensor):
+                    add(v)
+                elif isinstance(v, Linear):
+                    add(v.weight)
+                elif hasattr(v, "weight") and isinstance(getattr(v, "weight"), torch.Tensor):
+                    add(v.weight)
         add(self.final_norm.weight)
         return total
 
@@ -110,7 +112,7 @@ class Model:
     def forward(self, batch, storage) -> torch.Tensor:
         """Logits [selected, vocab] in float32 for ``batch.selected`` (an empty tensor when nothing is wanted)."""
         k = self.rt.kernels
-        h = k.embedding(self.embed_table, batch.ids)
+        h = self.embedding(batch.ids, batch)
         residual = None
         for n, e in enumerate(self.spec.schedule):
             owner = n if e.reads_cache_of is None else e.reads_cache_of
@@ -121,7 +123,7 @@ class Model:
             final = self.final_norm(h, rows=batch.selected)
         else:
             final, _ = self.final_norm.add_norm(h, residual, rows=batch.selected)
-        return self.lm_head(final, out_dtype=torch.float32)
+        return self.head(final, batch)
 
 
 def read_model_config(model_dir):

@@ -138,6 +138,26 @@ class FeedForward(Part):
         raise NotImplementedError
 
 
+class Embedding(Part):
+    """Token ids to the first hidden states. Declares its parameters under the scope "embed"; ``tied_weight`` is what a
+    head that shares the embedding's matrix is loaded with (None when the part has nothing to share)."""
+
+    def __call__(self, ids: torch.Tensor, batch) -> torch.Tensor:
+        """ids: int32 [T]; returns [T, hidden] in the activation dtype."""
+        raise NotImplementedError
+
+    def tied_weight(self) -> torch.Tensor | None:
+        return None
+
+
+class Head(Part):
+    """The final hidden states of the wanted rows to float32 logits [rows, vocab]. Declares its parameters under the scope
+    "lm_head"; with tied embeddings it declares none and is loaded with {"weight": the embedding's ``tied_weight``}."""
+
+    def __call__(self, final: torch.Tensor, batch) -> torch.Tensor:
+        raise NotImplementedError
+
+
 class Block(Part):
     mixer: Mixer
 
@@ -172,6 +192,8 @@ POSITIONS = _Registry("position encoding")
 MIXERS = _Registry("mixer")
 FEED_FORWARDS = _Registry("feed-forward")
 BLOCKS = _Registry("block arrangement")
+EMBEDDINGS = _Registry("embedding")
+HEADS = _Registry("head")
 
 
 def register_norm(kind, cls):
@@ -192,3 +214,11 @@ def register_feed_forward(kind, cls):
 
 def register_block(kind, cls):
     BLOCKS.register(kind, cls)
+
+
+def register_embedding(kind, cls):
+    EMBEDDINGS.register(kind, cls)
+
+
+def register_head(kind, cls):
+    HEADS.register(kind, cls)

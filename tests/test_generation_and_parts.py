@@ -592,6 +592,109 @@ def test_a_toy_routed_feed_forward_and_a_toy_position_encoding_are_registered_bu
     assert not ex.use_graphs and ex.graph_replays == 0
 
 
+# ------------------------------------------------------------------------------------------ toy ends of a model
+@dataclass(frozen=True)
+class ToyScaledEmbeddingSpec:
+    kind: str = "toy_scaled_table"
+    vocab: int = 0
+    hidden: int = 0
+    scale: float = 1.0
+
+
+@dataclass(frozen=True)
+class ToyCappedHeadSpec:
+    kind: str = "toy_capped_linear"
+    vocab: int = 0
+    hidden: int = 0
+    cap: float = 30.0
+
+
+def test_a_toy_embedding_and_a_toy_head_are_registered_built_and_stepped(backend):
+    """The two ends of a model are parts like the others: an embedding that scales its rows and a head that caps its logits
+    (cap * tanh(z / cap)), defined here, registered and run through the executor, the head tied to the toy embedding's
+    table; nothing in the package changes."""
+    from roost_b200.parts import Embedding, Head, register_embedding, register_head
+
+    class ToyScaledEmbedding(Embedding):
+        def __init__(self, spec, rt):
+            self.spec, self.rt, self.table = spec, rt, None
+
+        @classmethod
+        def parameters(cls, spec):
+            return {"table": ParamDecl(shape=(spec.vocab, spec.hidden))}
+
+        def load(self, params):
+            self.table = params["table"].to(self.rt.dtype).contiguous()
+
+        def tied_weight(self):
+            return self.table
+
+        def __call__(self, ids, batch=None):
+            return (self.rt.kernels.embedding(self.table, ids).float() * self.spec.scale).to(self.rt.dtype)
+
+    class ToyCappedHead(Head):
+        def __init__(self, spec, rt):
+            self.spec, self.rt = spec, rt
+            self.linear = Linear(rt, spec.vocab, spec.hidden)
+
+        @classmethod
+        def parameters(cls, spec):
+            return {"weight": ParamDecl(shape=(spec.vocab, spec.hidden))}
+
+        def load(self, params):
+            self.linear.load(params["weight"])
+
+        def __call__(self, final, batch=None):
+            z = self.linear(final, out_dtype=torch.float32)
+            return self.spec.cap * torch.tanh(z / self.spec.cap)
+
+    register_embedding("toy_scaled_table", ToyScaledEmbedding)
+    register_head("toy_capped_linear", ToyCappedHead)
+    rt = runtime(backend)
+    H_, V, I = 32, 70, 48
+    norm = NormSpec(size=H_, eps=1e-6)
+    attn = AttentionSpec(hidden=H_, num_heads=2, num_kv_heads=1, head_dim=16, scale=0.25, qk_norm=None,
+                         position=PositionSpec(rotary_dim=16, theta=100.0))
+    block = BlockSpec(mixer=attn, feed_forward=GatedMlpSpec(hidden=H_, intermediate=I), input_norm=norm, post_mixer_norm=norm)
+    scale, cap = math.sqrt(H_), 4.0
+    spec = ModelSpec(architecture="ToyEndsForTests", hidden=H_, vocab=V, blocks=(block,), schedule=(RunEntry(0),), final_norm=norm,
+                     tie_embeddings=True, max_positions=0, embedding=ToyScaledEmbeddingSpec(vocab=V, hidden=H_, scale=scale),
+                     head=ToyCappedHeadSpec(vocab=V, hidden=H_, cap=cap))
+    model = Model(spec, rt)
+    g = torch.Generator().manual_seed(8)
+    params = {}
+    for scope, decl in parameter_declarations(spec).items():
+        params[scope] = {k: (torch.ones(d.shape) if d.role == "vector" else torch.randn(d.shape, generator=g) * 0.3).to(rt.dtype) for k, d in decl.items()}
+    assert "lm_head" not in params
+    model.load(params)
+    ex = StepExecutor(model, page_size=4, num_pages=24, max_requests=2)
+
+    def plain_forward(ids):
+        P = {s_: {k: v.double() for k, v in p.items()} for s_, p in params.items()}
+        h = P["embed"]["table"][torch.tensor(ids)] * scale
+        if not rt.full_precision:
+            h = h.to(torch.bfloat16).double()
+        pos = list(range(len(ids)))
+        x = plain.rms_norm(h, P["blocks.0.input_norm"]["weight"], 1e-6)
+        qkv = P["blocks.0.mixer"]["qkv"]
+        q = plain.rope_neox((x @ qkv[:32].T).reshape(-1, 2, 16), pos, 100.0)
+        k = plain.rope_neox((x @ qkv[32:48].T).reshape(-1, 1, 16), pos, 100.0)
+        v = (x @ qkv[48:].T).reshape(-1, 1, 16)
+        h = h + plain.causal_gqa_attention(q, k, v, 0.25).reshape(-1, 32) @ P["blocks.0.mixer"]["out"].T
+        y = plain.rms_norm(h, P["blocks.0.post_mixer_norm"]["weight"], 1e-6)
+        gu = P["blocks.0.feed_forward"]["gate_up"]
+        h = h + plain.swiglu_mlp(y, gu[:I], gu[I:], P["blocks.0.feed_forward"]["down"])
+        z = plain.rms_norm(h, P["final_norm"]["weight"], 1e-6) @ P["embed"]["table"].T
+        return cap * torch.tanh(z / cap)
+
+    ids = H.random_ids(19, V, 5)
+    want = plain_forward(ids)
+    assert float(want.abs().max()) > 0.8 * cap, "the test's logits must reach the cap for the cap to show"
+    bound = 2e-5 if rt.full_precision else H.BF16_BOUND
+    assert H.scaled_error(H.run_whole(ex, "w", ids), want) < bound
+    assert H.scaled_error(H.run_tail_decoded(ex, "t", ids, tail=8), want) < bound
+
+
 @pytest.mark.gpu
 def test_steps_started_before_the_last_tokens_were_read_give_the_same_tokens(tiny_model_dirs):
     """While every live request decodes, the engine starts the next step with the sampled tokens still on the device.
