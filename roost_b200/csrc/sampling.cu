@@ -16,6 +16,8 @@
 // below), and a count of ties. Integer sums do not depend on their order, so a row gives the same token in
 // any batch and on any run. The masses are rounded to 2^-40 of the largest weight where the reference sums
 // doubles over a sorted array: a draw within rounding of an interval's edge may fall to the neighbouring token.
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 
 namespace roost {
@@ -493,6 +495,374 @@ __global__ void __launch_bounds__(kThreads)
   if (threadIdx.x == 0) ids[r] = chosen;
 }
 
+// ------------------------------------------------------------------------------------------------ a row on a cluster of CTAs
+// One SM reads a row of a large vocabulary at about 30 GB/s, and a search makes several passes over it: a block a row
+// takes 460 us at 151,936 tokens. Here a cluster of eight CTAs takes a row: each keeps an eighth of the row's weights in
+// shared memory, so every pass after the first reads shared memory, and the CTAs combine what they find through each
+// other's shared memory: histograms are reduced bucket range by bucket range (CTA c owns an eighth of the buckets), the
+// range that holds the crossing is found from the eight range totals, and its owner finds the bucket and tells the
+// others. Every sum is an integer sum, so the result is the single block's, bit for bit.
+namespace cg = cooperative_groups;
+constexpr int kClusterCtas = 8;
+constexpr int kSliceFloats = 24576;   // of a row, in a CTA's shared memory (96 KB): rows of up to 196,608 tokens
+
+struct ClusterScratch {
+  SearchScratch h;                                   // this CTA's histogram of its slice
+  unsigned long long own_mass[kBuckets / kClusterCtas];   // the cluster's totals of the buckets this CTA owns
+  unsigned own_cnt[kBuckets / kClusterCtas];
+  unsigned long long own_total_mass;
+  unsigned own_total_cnt;
+  unsigned long long pub_u64[2][2];                  // all-reduce slots, used in turn
+  unsigned pub_u32[2][2];
+  float am_val;                                      // this CTA's best logit and its index
+  int am_idx;
+  unsigned long long found_above_mass, found_mass;   // what the owner of the crossing bucket tells the others
+  unsigned found_above_cnt, found_cnt, found_digit;
+  int crossing_rank;
+  unsigned long long crossing_above_mass;
+  unsigned crossing_above_cnt;
+  unsigned ties_local;
+};
+
+__device__ __forceinline__ unsigned long long warp_sum_u64(unsigned long long v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// Sums (a, b) over the cluster; every thread of every CTA calls it and gets the totals.
+__device__ void cluster_sum2(cg::cluster_group& cluster, ClusterScratch& cs, int& turn, unsigned long long& a, unsigned& b) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  a = warp_sum_u64(a);
+  b = (unsigned)warp_sum_i((int)b);
+  __syncthreads();
+  if (lane == 0) {
+    cs.h.warp_mass[warp] = a;
+    cs.h.warp_cnt[warp] = b;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    unsigned long long ta = 0ull;
+    unsigned tb = 0u;
+    for (int w = 0; w < kThreads / 32; ++w) {
+      ta += cs.h.warp_mass[w];
+      tb += cs.h.warp_cnt[w];
+    }
+    cs.pub_u64[turn][0] = ta;
+    cs.pub_u32[turn][0] = tb;
+  }
+  cluster.sync();
+  unsigned long long ta = 0ull;
+  unsigned tb = 0u;
+  for (int r = 0; r < kClusterCtas; ++r) {
+    const ClusterScratch* o = cluster.map_shared_rank(&cs, r);
+    ta += o->pub_u64[turn][0];
+    tb += o->pub_u32[turn][0];
+  }
+  a = ta;
+  b = tb;
+  turn ^= 1;
+}
+
+// search_key over the cluster: the same definition and the same result, the row's weights in the CTAs' slices.
+__device__ unsigned cluster_search_key(cg::cluster_group& cluster, ClusterScratch& cs, const float* __restrict__ slice, int n_local, unsigned xb,
+                                       int c, unsigned long long target, bool strict, bool by_count, unsigned long long& above_mass,
+                                       unsigned& above_cnt, unsigned& ties) {
+  const int rank = (int)cluster.block_rank();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  unsigned prefix = 0u, prefix_mask = 0u;
+  unsigned long long acc_mass = 0ull;
+  unsigned acc_cnt = 0u;
+  const unsigned long long xb_mass = weight_mass(__uint_as_float(xb));
+  auto reaches = [&](unsigned long long mass, unsigned cnt) {
+    const unsigned long long m = by_count ? (unsigned long long)cnt : mass;
+    return strict ? m > target : m >= target;
+  };
+  for (int level = 0; level < 3; ++level) {
+    const int shift = digit_shift(level), buckets = 1 << digit_bits(level), own = buckets / kClusterCtas;
+    for (int i = threadIdx.x; i < buckets; i += kThreads) {
+      cs.h.mass[i] = 0ull;
+      cs.h.cnt[i] = 0u;
+    }
+    __syncthreads();
+    for (int v = threadIdx.x; v < n_local; v += kThreads) {
+      const float x = slice[v];
+      if (x < 0.f) continue;
+      const unsigned k = __float_as_uint(x);
+      if ((k & prefix_mask) != prefix || k <= xb) continue;   // the tokens at xb are counted below, c of them
+      const unsigned digit = (k >> shift) & (unsigned)(buckets - 1);
+      atomicAdd(&cs.h.mass[digit], weight_mass(x));
+      atomicAdd(&cs.h.cnt[digit], 1u);
+    }
+    if (rank == 0 && threadIdx.x == 0 && c > 0 && (xb & prefix_mask) == prefix) {
+      const unsigned digit = (xb >> shift) & (unsigned)(buckets - 1);
+      atomicAdd(&cs.h.mass[digit], xb_mass * (unsigned long long)c);
+      atomicAdd(&cs.h.cnt[digit], (unsigned)c);
+    }
+    cluster.sync();
+    // the cluster's totals of the buckets this CTA owns, and their sum
+    unsigned long long mine_mass = 0ull;
+    unsigned mine_cnt = 0u;
+    if ((int)threadIdx.x < own) {
+      const int bkt = rank * own + (int)threadIdx.x;
+      for (int r = 0; r < kClusterCtas; ++r) {
+        const ClusterScratch* o = cluster.map_shared_rank(&cs, r);
+        mine_mass += o->h.mass[bkt];
+        mine_cnt += o->h.cnt[bkt];
+      }
+      cs.own_mass[threadIdx.x] = mine_mass;
+      cs.own_cnt[threadIdx.x] = mine_cnt;
+    }
+    {
+      unsigned long long wm = warp_sum_u64(mine_mass);
+      unsigned wc = (unsigned)warp_sum_i((int)mine_cnt);
+      if (lane == 0) {
+        cs.h.warp_mass[warp] = wm;
+        cs.h.warp_cnt[warp] = wc;
+      }
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        unsigned long long tm = 0ull;
+        unsigned tc = 0u;
+        for (int w = 0; w < (own + 31) / 32; ++w) {
+          tm += cs.h.warp_mass[w];
+          tc += cs.h.warp_cnt[w];
+        }
+        cs.own_total_mass = tm;
+        cs.own_total_cnt = tc;
+      }
+    }
+    cluster.sync();
+    // the range of buckets in which the running measure (from the top) first reaches the target: the same in every CTA
+    if (threadIdx.x == 0) {
+      unsigned long long m = acc_mass;
+      unsigned n = acc_cnt;
+      int at = 0;
+      for (int r = kClusterCtas - 1; r >= 0; --r) {
+        const ClusterScratch* o = cluster.map_shared_rank(&cs, r);
+        const unsigned long long rm = o->own_total_mass;
+        const unsigned rc = o->own_total_cnt;
+        if (reaches(m + rm, n + rc)) {
+          at = r;
+          break;
+        }
+        m += rm;
+        n += rc;
+      }
+      cs.crossing_rank = at;
+      cs.crossing_above_mass = m;
+      cs.crossing_above_cnt = n;
+    }
+    __syncthreads();
+    const int owner = cs.crossing_rank;
+    if (rank == owner) {
+      // the bucket within this CTA's range: a scan from the range's top bucket down, one bucket a thread
+      const int t = (int)threadIdx.x;
+      const bool in = t < own;
+      const int bkt = rank * own + (own - 1 - t);
+      const unsigned long long bm = in ? cs.own_mass[own - 1 - t] : 0ull;
+      const unsigned bc = in ? cs.own_cnt[own - 1 - t] : 0u;
+      unsigned long long inc_m = bm;
+      unsigned inc_c = bc;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const unsigned long long tm = __shfl_up_sync(0xffffffffu, inc_m, o);
+        const unsigned tc = __shfl_up_sync(0xffffffffu, inc_c, o);
+        if (lane >= o) {
+          inc_m += tm;
+          inc_c += tc;
+        }
+      }
+      __syncthreads();
+      if (lane == 31) {
+        cs.h.warp_mass[warp] = inc_m;
+        cs.h.warp_cnt[warp] = inc_c;
+      }
+      __syncthreads();
+      unsigned long long before_m = cs.crossing_above_mass + inc_m - bm;
+      unsigned before_c = cs.crossing_above_cnt + inc_c - bc;
+      for (int w = 0; w < warp; ++w) {
+        before_m += cs.h.warp_mass[w];
+        before_c += cs.h.warp_cnt[w];
+      }
+      if (in && !reaches(before_m, before_c) && reaches(before_m + bm, before_c + bc)) {
+        cs.found_digit = (unsigned)bkt;
+        cs.found_above_mass = before_m;
+        cs.found_above_cnt = before_c;
+        cs.found_mass = bm;
+        cs.found_cnt = bc;
+      }
+    }
+    cluster.sync();
+    const ClusterScratch* o = cluster.map_shared_rank(&cs, owner);
+    prefix |= o->found_digit << shift;
+    prefix_mask |= (unsigned)(buckets - 1) << shift;
+    acc_mass = o->found_above_mass;
+    acc_cnt = o->found_above_cnt;
+    ties = o->found_cnt;
+  }
+  cluster.sync();   // the owner's word has been read by everyone before a later search writes it again
+  above_mass = acc_mass;
+  above_cnt = acc_cnt;
+  return prefix;
+}
+
+__global__ void __cluster_dims__(kClusterCtas, 1, 1) __launch_bounds__(kThreads)
+    sample_cluster_kernel(const float* __restrict__ logits, long long stride, int vocab, const float* __restrict__ temperature,
+                          const int* __restrict__ top_k, const float* __restrict__ top_p, const float* __restrict__ min_p,
+                          const unsigned* __restrict__ seeds, const unsigned* __restrict__ offsets, int* __restrict__ ids) {
+  extern __shared__ float slice[];
+  __shared__ float sf[32];
+  __shared__ int si[32];
+  __shared__ int s_result;
+  __shared__ ClusterScratch cs;
+  cg::cluster_group cluster = cg::this_cluster();
+  const int rank = (int)cluster.block_rank();
+  const int r = blockIdx.x / kClusterCtas;
+  const int span = (((vocab + kClusterCtas - 1) / kClusterCtas) + 3) & ~3;
+  const int lo = min(vocab, rank * span), n_local = min(vocab, lo + span) - lo;
+  const float* z = logits + (size_t)r * stride + lo;
+  const float temp = temperature[r];
+  int turn = 0;
+
+  // the row's best logit: every CTA's best, combined in rank order
+  const int local_best = block_argmax(z, n_local, true, sf, si);
+  if (threadIdx.x == 0) {
+    cs.am_val = sf[0];
+    cs.am_idx = local_best < 0 ? -1 : local_best + lo;
+  }
+  cluster.sync();
+  float zmax = 0.f;
+  int imax = -1;
+  for (int c = 0; c < kClusterCtas; ++c) {
+    const ClusterScratch* o = cluster.map_shared_rank(&cs, c);
+    const float ov = o->am_val;
+    const int oi = o->am_idx;
+    if (!better(zmax, imax, ov, oi)) {
+      zmax = ov;
+      imax = oi;
+    }
+  }
+  if (temp <= 0.f || imax < 0) {
+    if (rank == 0 && threadIdx.x == 0) ids[r] = imax;
+    cluster.sync();   // nobody leaves while another CTA still reads its shared memory
+    return;
+  }
+
+  // the weights e = exp((z - max) / T) of this CTA's slice, at most 1; removed tokens are marked -1
+  unsigned long long total = 0ull;
+  unsigned allowed_u = 0u, zeros_mine = 0u;
+  for (int v = threadIdx.x; v < n_local; v += kThreads) {
+    const float x = z[v];
+    float e = -1.f;
+    if (x == x && x != -INFINITY) {
+      e = expf((x - zmax) / temp);
+      total += weight_mass(e);
+      ++allowed_u;
+      zeros_mine += e == 0.f ? 1u : 0u;
+    }
+    slice[v] = e;
+  }
+  cluster_sum2(cluster, cs, turn, total, allowed_u);
+  unsigned long long zeros64 = zeros_mine;
+  unsigned dummy = 0u;
+  cluster_sum2(cluster, cs, turn, zeros64, dummy);
+  const int allowed = (int)allowed_u;
+
+  unsigned keep_xb = 0u;
+  int keep_c = (int)zeros64;
+  unsigned long long kept_mass = total;
+  unsigned long long above_mass;
+  unsigned above_cnt, ties;
+
+  const int k = top_k[r];
+  if (k > 0 && k < allowed) {
+    const unsigned b = cluster_search_key(cluster, cs, slice, n_local, keep_xb, keep_c, (unsigned long long)k, false, true, above_mass, above_cnt, ties);
+    keep_xb = b;
+    keep_c = k - (int)above_cnt;
+    kept_mass = above_mass + (unsigned long long)keep_c * weight_mass(__uint_as_float(b));
+  }
+
+  const float tp = top_p[r];
+  if (tp < 1.0f && kept_mass > 0ull) {
+    unsigned long long bar = (unsigned long long)ceil((double)tp * (double)kept_mass);
+    if (bar > kept_mass) bar = kept_mass;
+    if (bar < 1ull) bar = 1ull;
+    const unsigned b = cluster_search_key(cluster, cs, slice, n_local, keep_xb, keep_c, bar, false, false, above_mass, above_cnt, ties);
+    const unsigned long long x = weight_mass(__uint_as_float(b));
+    const int have = (b == keep_xb) ? keep_c : (int)ties;
+    int need = 1;
+    if (x > 0ull && bar > above_mass) {
+      const unsigned long long q = (bar - above_mass + x - 1ull) / x;
+      need = q > (unsigned long long)have ? have : (int)q;
+      if (need < 1) need = 1;
+    }
+    if (need > have) need = have;
+    keep_xb = b;
+    keep_c = need;
+    kept_mass = above_mass + (unsigned long long)need * x;
+  }
+
+  const float mp = min_p[r];
+  if (mp > 0.f && __uint_as_float(keep_xb) < mp) {
+    keep_xb = __float_as_uint(mp) - 1u;
+    keep_c = 0;
+    unsigned long long m = 0ull;
+    for (int v = threadIdx.x; v < n_local; v += kThreads) {
+      const float x = slice[v];
+      if (x >= 0.f && __float_as_uint(x) > keep_xb) m += weight_mass(x);
+    }
+    unsigned none = 0u;
+    cluster_sum2(cluster, cs, turn, m, none);
+    kept_mass = m;
+  }
+
+  int chosen = -1;          // meaningful in the CTA that writes the row's id
+  bool mine = rank == 0;    // which CTA that is
+  if (kept_mass == 0ull) {
+    chosen = imax;
+  } else {
+    const unsigned r0 = philox4x32_10(offsets[2 * r], offsets[2 * r + 1], 0u, 0u, seeds[2 * r], seeds[2 * r + 1]);
+    const double u = (double)(r0 >> 8) * (1.0 / 16777216.0);
+    unsigned long long target = (unsigned long long)(u * (double)kept_mass);
+    if (target >= kept_mass) target = kept_mass - 1ull;
+    const unsigned b = cluster_search_key(cluster, cs, slice, n_local, keep_xb, keep_c, target, true, false, above_mass, above_cnt, ties);
+    const unsigned long long x = weight_mass(__uint_as_float(b));
+    const int have = (b == keep_xb) ? keep_c : (int)ties;
+    int rnk = 0;
+    if (x > 0ull && target >= above_mass) {
+      const unsigned long long q = (target - above_mass) / x;
+      rnk = q > (unsigned long long)(have - 1) ? have - 1 : (int)q;
+    }
+    // the (rnk + 1)-th token of key b by index: the slices are in index order, so count them slice by slice
+    unsigned here = 0u;
+    for (int v = threadIdx.x; v < n_local; v += kThreads) {
+      const float xv = slice[v];
+      here += (xv >= 0.f && __float_as_uint(xv) == b) ? 1u : 0u;
+    }
+    here = (unsigned)block_sum_i((int)here, si);
+    if (threadIdx.x == 0) cs.ties_local = here;
+    cluster.sync();
+    int before = 0, owner = -1;
+    for (int c2 = 0; c2 < kClusterCtas; ++c2) {
+      const unsigned t = cluster.map_shared_rank(&cs, c2)->ties_local;
+      if (owner < 0 && have > 0 && rnk < before + (int)t) owner = c2;
+      if (owner < 0) before += (int)t;
+    }
+    if (owner < 0) {
+      chosen = imax;   // no token of that key (cannot be, with exact masses): the row's best
+    } else {
+      mine = rank == owner;
+      if (mine) {
+        const int local = nth_equal(slice, n_local, b, rnk - before, si, &s_result);
+        chosen = local < 0 ? imax : local + lo;
+      }
+    }
+  }
+  if (mine && threadIdx.x == 0) ids[r] = chosen;
+  cluster.sync();   // nobody leaves while another CTA still reads its shared memory
+}
+
 }  // namespace roost
 
 using namespace roost;
@@ -524,6 +894,22 @@ extern "C" int roost_sample(const float* logits, int64_t stride, int rows, int v
   ROOST_REQUIRE(((uintptr_t)logits & 3) == 0 && ((uintptr_t)workspace & 3) == 0 && ((uintptr_t)seeds & 3) == 0 &&
                     ((uintptr_t)offsets & 3) == 0,
                 "sample: a table is not aligned to its element size");
+  // a cluster of CTAs a row while a row's eighth fits a CTA's shared memory (and the vocabulary is worth eight CTAs);
+  // else a block a row over the workspace
+  if (vocab >= 4096 && vocab <= kClusterCtas * kSliceFloats && rows <= 65535 / kClusterCtas * kClusterCtas) {
+    const int span = (((vocab + kClusterCtas - 1) / kClusterCtas) + 3) & ~3;
+    const size_t smem = (size_t)span * sizeof(float);
+    static bool attr_set[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+      cudaFuncSetAttribute(sample_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(kSliceFloats * sizeof(float)));
+      attr_set[dev] = true;
+    }
+    sample_cluster_kernel<<<rows * kClusterCtas, kThreads, smem, (cudaStream_t)stream>>>(logits, (long long)stride, vocab, temperature, top_k, top_p,
+                                                                                       min_p, (const unsigned*)seeds, (const unsigned*)offsets, ids);
+    return check_launch("sample (cluster)");
+  }
   sample_kernel<<<rows, kThreads, 0, (cudaStream_t)stream>>>(logits, (long long)stride, vocab, temperature, top_k, top_p, min_p,
                                                             (const unsigned*)seeds, (const unsigned*)offsets, workspace, ids);
   return check_launch("sample");

@@ -337,10 +337,11 @@ def test_argmax_ties_and_nan(kernels):
         assert kernels.argmax(z.cuda()).cpu().tolist() == want
 
 
-@pytest.mark.parametrize("vocab", [387, 5000, 151936])
+@pytest.mark.parametrize("vocab", [387, 5000, 151936, 200003])
 def test_sampler_matches_the_plain_sampler(kernels, vocab):
     """Rows with different settings in one launch; a row is compared when the plain sampler's draw is not within
-    1e-4 of the kept mass from an edge of the chosen token's interval."""
+    1e-4 of the kept mass from an edge of the chosen token's interval. The sizes take both kernels: a block a row (the
+    smallest, and the largest, whose eighth no longer fits a block's shared memory) and a cluster of eight a row."""
     g = torch.Generator().manual_seed(15)
     settings = [(0.0, 0, 1.0, 0.0), (1.0, 0, 1.0, 0.0), (0.8, 0, 0.9, 0.0), (0.7, 20, 1.0, 0.0), (1.3, 50, 0.8, 0.0),
                 (1.0, 0, 1.0, 0.05), (0.9, 40, 0.95, 0.02), (0.5, 1, 1.0, 0.0), (2.0, 0, 0.5, 0.0), (1.0, 3, 0.2, 0.0)]
