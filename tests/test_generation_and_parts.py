@@ -83,6 +83,22 @@ def test_sampled_generation_is_seeded_and_stops(tiny_model_dirs, backend):
     a = engine.generate(prompts, opts)
     b = engine.generate(prompts, opts)
     assert [o.token_ids for o in a] == [o.token_ids for o in b]
+    # every token is the plain sampler's choice on the plain logits of the engine's own history, with the request's seed
+    # and the number of tokens generated so far as the offset, unless the draw falls within 1e-4 of the kept mass from an
+    # edge of the token's interval (a counter that started at 1, or a seed of another row, would show at once)
+    cfg, w = plain.load_model_dir(tiny_model_dirs["B"])
+    if dtype == torch.float32:
+        compared = 0
+        for i, (prompt, out) in enumerate(zip(prompts, a)):
+            seq = list(prompt)
+            for j, tok in enumerate(out.token_ids):
+                logits = plain.forward_logits(cfg, w, seq)[-1]
+                want, detail = plain.sample_row(logits.tolist(), 0.8, 0, 0.9, 0.0, 1000 + i, j, return_detail=True)
+                if detail["margin"] > 1e-4:
+                    assert tok == want, f"request {i}, token {j}: engine {tok}, plain {want} (margin {detail['margin']:.2e})"
+                    compared += 1
+                seq.append(tok)
+        assert compared >= 0.8 * sum(len(o.token_ids) for o in a), compared
     c = engine.generate(prompts[2:3], opts[2:3])                 # alone: the draw does not depend on the batch
     if dtype == torch.float32:
         assert c[0].token_ids == a[2].token_ids
