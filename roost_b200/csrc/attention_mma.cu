@@ -651,6 +651,24 @@ struct DecodeChunk {  // what the producer tells the consumers about a chunk
   int b, kvh, slot, q_start, n, kv_len, lo, hi, t0, ntiles;
 };
 
+__device__ __forceinline__ uint32_t decode_cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r));
+  return r;
+}
+// Every thread of the cluster that has not exited arrives and waits (the producer warps have left by then, or leave
+// soon: a thread that exits no longer counts).
+__device__ __forceinline__ void decode_cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release;\nbarrier.cluster.wait.acquire;\n" ::: "memory");
+}
+__device__ __forceinline__ float ld_cluster_f32(uint32_t addr, uint32_t rank) {
+  uint32_t remote;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(remote) : "r"(addr), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];\n" : "=f"(v) : "r"(remote));
+  return v;
+}
+
 template <int D>
 constexpr int tma_decode_stages() {
   return (96 * 1024) / (2 * kTmaTileKeys * D * 2);  // 6 at head size 128, 12 at 64
@@ -662,7 +680,11 @@ __global__ void __launch_bounds__((kTmaConsumers + 1) * 32, 2)
                                 const int32_t* __restrict__ q_indptr, const int32_t* __restrict__ kv_lens,
                                 const int32_t* __restrict__ kv_indptr, const int32_t* __restrict__ kv_indices,
                                 const int4* __restrict__ work, int items, float* __restrict__ part_o, float* __restrict__ part_ml, int q_heads,
-                                int kv_heads, int page_size, float scale_log2, int window) {
+                                int kv_heads, int page_size, float scale_log2, int window, int cluster_chunks) {
+  // cluster_chunks = S > 0: the grid is clusters of S CTAs, one cluster a (row, key/value head), the row's work items S in
+  // a row of the list (some of them empty); CTA r of a cluster takes the r-th, leaves its result in its own shared memory
+  // and the CTAs combine the S results in chunk order, with the merge kernel's arithmetic, through distributed shared
+  // memory (each a share of the row's values): no partial results in global memory and no merge kernel.
   constexpr int TK = kTmaTileKeys, STAGES = tma_decode_stages<D>(), NW = kTmaConsumers, MR = kTmaMergeRows;
   constexpr uint32_t kStageBytes = 2 * TK * D * 2;  // keys and values of TK positions
   constexpr uint32_t kQBytes = 16 * D * 2;
@@ -721,7 +743,14 @@ __global__ void __launch_bounds__((kTmaConsumers + 1) * 32, 2)
     int nq0 = 0, nq1 = 0, nkvl = 0, ntbl = 0;
     DecodeChunk nc;
     int n_fallback = 0, n_cur = -1, n_nxt = -1;
-    auto round1 = [&]() { nw = nf < total ? work[nf / kv_heads] : make_int4(-1, 0, 0, 0); };
+    auto item_of = [&](long long f) -> long long {
+      if (cluster_chunks > 0) {  // fewer than 2^31 items x heads here
+        const unsigned u = (unsigned)f, pair = u / (unsigned)cluster_chunks;
+        return (long long)((pair / (unsigned)kv_heads) * (unsigned)cluster_chunks + u % (unsigned)cluster_chunks);
+      }
+      return f / kv_heads;
+    };
+    auto round1 = [&]() { nw = nf < total ? work[item_of(nf)] : make_int4(-1, 0, 0, 0); };
     auto round2 = [&]() {
       if (nw.x >= 0) {
         nq0 = q_indptr[nw.x];
@@ -734,7 +763,7 @@ __global__ void __launch_bounds__((kTmaConsumers + 1) * 32, 2)
       nc.b = nw.x;  // padding entries (batch row -1) end the list
       nc.ntiles = 0;
       if (nc.b >= 0) {
-        nc.kvh = (int)(nf % kv_heads);
+        nc.kvh = cluster_chunks > 0 ? (int)(((unsigned)nf / (unsigned)cluster_chunks) % (unsigned)kv_heads) : (int)(nf % kv_heads);
         nc.slot = nw.w;
         nc.q_start = nq0;
         nc.n = nq1 - nq0;
@@ -844,9 +873,11 @@ __global__ void __launch_bounds__((kTmaConsumers + 1) * 32, 2)
   pdl_wait(4);
   bool ok = true;
   int g0 = 0;  // tiles of the chunks before this one
+  bool seen = false;  // this thread has read the CTA's first descriptor (with clusters its only one: desc[0] stays as it is)
   for (int k = 0; ok; ++k) {
     if (!(ok = mbar_wait_limited(desc_full(k & 1), (uint32_t)(k >> 1) & 1u, abortp, 5, &g_attention_error))) break;
     const DecodeChunk c = desc[k & 1];
+    seen = true;
     if (c.b < 0) break;
     const int rows_total = c.n * group;  // at most 16
     const int pos0 = c.kv_len - c.n;
@@ -938,7 +969,16 @@ __global__ void __launch_bounds__((kTmaConsumers + 1) * 32, 2)
           l += sm_ml[(ww * MR + pr) * 2 + 1] * fac;
           o += sm_o[((size_t)ww * MR + pr) * kScratchStride + col] * fac;
         }
-        if (c.slot < 0) {
+        if (cluster_chunks > 0) {
+          // a cluster's results: [16][D] sums and [16][2] (maximum, sum of weights) in the first stage of the ring, which
+          // no copy writes any more once the CTA's only chunk has been consumed
+          float* cl_o = reinterpret_cast<float*>(smem_gen);
+          cl_o[row * D + col] = o;
+          if (col == 0) {
+            cl_o[16 * D + row * 2] = m;
+            cl_o[16 * D + row * 2 + 1] = l;
+          }
+        } else if (c.slot < 0) {
           const float inv = l > 0.f ? 1.0f / l : 0.f;
           out[((size_t)(c.q_start + row / group) * q_heads + c.kvh * group + row % group) * D + col] = __float2bfloat16_rn(o * inv);
         } else {
@@ -952,6 +992,47 @@ __global__ void __launch_bounds__((kTmaConsumers + 1) * 32, 2)
       }
       asm volatile("bar.sync 1, %0;\n" ::"n"(NW * 32) : "memory");  // the scratch (and the Q tile) may be written again
     }
+  }
+  const bool cl_padding = seen && desc[0].b < 0;  // the cluster's items are padding: all its CTAs leave at once
+  if (cluster_chunks > 0 && !cl_padding) {
+    const int cl_rows = seen ? desc[0].n * group : 0, cl_q_start = desc[0].q_start, cl_kvh = desc[0].kvh;
+    // Every CTA of the cluster has an item of the same row (padding fills whole clusters), so all of them come here, a
+    // CTA whose wait was given up included: its numbers are wrong (or, if it never saw its item, it merges nothing), the
+    // fault is recorded, and nobody is left waiting or reads the shared memory of a CTA that has gone.
+    decode_cluster_sync();  // the results of all the cluster's CTAs are in their shared memory
+    {  // every CTA of the cluster combines its share of the row's values
+      constexpr int kMaxCluster = 8;
+      const uint32_t o_addr = smem_base, ml_addr = smem_base + 16 * D * 4;
+      for (int idx = tid + (int)decode_cluster_rank() * NW * 32; idx < cl_rows * D; idx += NW * 32 * cluster_chunks) {
+        const int row = idx / D, col = idx % D;
+        // every load first (they are independent trips to the other CTAs' shared memory), then the sums in chunk order,
+        // as the merge kernel forms them
+        float pm[kMaxCluster], pl[kMaxCluster], po[kMaxCluster];
+#pragma unroll
+        for (int cc = 0; cc < kMaxCluster; ++cc) {
+          const bool in = cc < cluster_chunks;
+          pm[cc] = in ? ld_cluster_f32(ml_addr + (row * 2) * 4, cc) : -INFINITY;
+          pl[cc] = in ? ld_cluster_f32(ml_addr + (row * 2 + 1) * 4, cc) : 0.f;
+          po[cc] = in ? ld_cluster_f32(o_addr + (row * D + col) * 4, cc) : 0.f;
+        }
+        float m = -INFINITY;
+#pragma unroll
+        for (int cc = 0; cc < kMaxCluster; ++cc) m = fmaxf(m, pm[cc]);
+        const float msafe = m == -INFINITY ? 0.f : m;
+        float l = 0.f, o = 0.f;
+#pragma unroll
+        for (int cc = 0; cc < kMaxCluster; ++cc) {
+          if (cc < cluster_chunks) {
+            const float f = exp2f(pm[cc] - msafe);
+            l += pl[cc] * f;
+            o += po[cc] * f;
+          }
+        }
+        const float inv = l > 0.f ? 1.0f / l : 0.f;
+        out[((size_t)(cl_q_start + row / group) * q_heads + cl_kvh * group + row % group) * D + col] = __float2bfloat16_rn(o * inv);
+      }
+    }
+    decode_cluster_sync();  // nobody leaves while another CTA still reads its shared memory
   }
   if (!ok) {  // a copy that was waited for in vain may still land
     const long long c0 = clock64();
@@ -1121,7 +1202,7 @@ template <int D>
 static int launch_decode_tma(const void* q, void* out, const void* k_pool, const void* v_pool, const int32_t* q_indptr, const int32_t* kv_lens,
                              const int32_t* kv_indptr, const int32_t* kv_indices, const int32_t* work, int items, float* part_o,
                              float* part_ml, int q_heads, int kv_heads, int page_size, long long pool_pages, float scale, int window,
-                             cudaStream_t s) {
+                             cudaStream_t s, int cluster_chunks) {
   CUtensorMap map;
   const int box_rows = page_size < kTmaTileKeys ? page_size : kTmaTileKeys;
   const int rc = make_pool_map(&map, k_pool, v_pool, pool_pages * kv_heads * page_size, D, box_rows);
@@ -1137,11 +1218,12 @@ static int launch_decode_tma(const void* q, void* out, const void* k_pool, const
     cudaFuncSetAttribute(attention_decode_tma_kernel<D, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   }
   const long long total = (long long)items * kv_heads;
-  const int grid = (int)(total < 2LL * sms ? total : 2LL * sms);  // two CTAs fit an SM
+  // two CTAs fit an SM; with clusters every CTA takes exactly one item
+  const int grid = (int)(cluster_chunks > 0 || total < 2LL * sms ? total : 2LL * sms);
   auto kernel = box_rows == 16 ? attention_decode_tma_kernel<D, 16> : attention_decode_tma_kernel<D, 32>;
-  launch_kernel(kernel, dim3(grid), dim3((kTmaConsumers + 1) * 32), smem, s, map, (const __nv_bfloat16*)q, (__nv_bfloat16*)out, q_indptr,
-                kv_lens, kv_indptr, kv_indices, (const int4*)work, items, part_o, part_ml, q_heads, kv_heads, page_size, scale * kLog2e,
-                window);
+  launch_kernel_cluster(kernel, dim3(grid), dim3((kTmaConsumers + 1) * 32), smem, s, cluster_chunks > 0 ? cluster_chunks : 1, map,
+                        (const __nv_bfloat16*)q, (__nv_bfloat16*)out, q_indptr, kv_lens, kv_indptr, kv_indices, (const int4*)work, items, part_o,
+                        part_ml, q_heads, kv_heads, page_size, scale * kLog2e, window, cluster_chunks);
   return check_launch("attention_decode_tma");
 }
 
@@ -1155,7 +1237,7 @@ static int launch_decode(const void* q, void* out, const void* k_pool, const voi
   if constexpr (D == 64 || D == 128) {
     if (slot_limit == kNoSlotLimit && decode_tma_serves(D, page_size, pool_pages, kv_heads, k_pool, v_pool)) {
       rc = launch_decode_tma<D>(q, out, k_pool, v_pool, q_indptr, kv_lens, kv_indptr, kv_indices, work, items, part_o, part_ml, q_heads,
-                                kv_heads, page_size, pool_pages, scale, window, s);
+                                kv_heads, page_size, pool_pages, scale, window, s, 0);
       launched = true;
     }
   }
@@ -1296,6 +1378,34 @@ extern "C" int roost_attention_decode(const void* q, void* out, const void* k_po
 // results of the split rows live in the fixed array below instead of caller-provided buffers. Every process that
 // loads the library holds the array on every GPU it touches, until it exits.
 namespace roost {
+
+extern "C" int roost_attention_decode_cluster_supported(int head_dim, int page_size, long long pool_pages, int kv_heads, const void* k_pool,
+                                                        const void* v_pool) {
+  return decode_tma_serves(head_dim, page_size, pool_pages, kv_heads, k_pool, v_pool) ? 1 : 0;
+}
+
+extern "C" int roost_attention_decode_cluster(const void* q, void* out, const void* k_pool, const void* v_pool, const int32_t* q_indptr,
+                                              const int32_t* kv_lens, const int32_t* kv_indptr, const int32_t* kv_indices,
+                                              const int32_t* work, int items, int cluster_chunks, int q_heads, int kv_heads, int head_dim,
+                                              int page_size, long long pool_pages, float scale, int window, roost_stream_t stream) {
+  ROOST_REQUIRE(items >= 0 && q_heads > 0 && kv_heads > 0 && page_size > 0, "attention_decode_cluster: sizes must be positive");
+  ROOST_REQUIRE(q_heads % kv_heads == 0, "attention_decode_cluster: q_heads must be a multiple of kv_heads");
+  ROOST_REQUIRE(cluster_chunks == 1 || cluster_chunks == 2 || cluster_chunks == 4 || cluster_chunks == 8,
+                "attention_decode_cluster: a cluster has 1, 2, 4 or 8 CTAs");
+  ROOST_REQUIRE(items % cluster_chunks == 0, "attention_decode_cluster: the work list holds cluster_chunks items a row");
+  if ((long long)items * kv_heads >= (1LL << 31)) return fail(ROOST_ERR_UNSUPPORTED, "attention_decode_cluster: too many work items");
+  if (!decode_tma_serves(head_dim, page_size, pool_pages, kv_heads, k_pool, v_pool)) {
+    return fail(ROOST_ERR_UNSUPPORTED, "attention_decode_cluster: these sizes or pools are not served (see roost_attention_decode_cluster_supported)");
+  }
+  if (items == 0) return ROOST_OK;
+  const cudaStream_t s = (cudaStream_t)stream;
+  if (head_dim == 64) {
+    return launch_decode_tma<64>(q, out, k_pool, v_pool, q_indptr, kv_lens, kv_indptr, kv_indices, work, items, nullptr, nullptr, q_heads,
+                                 kv_heads, page_size, pool_pages, scale, window, s, cluster_chunks);
+  }
+  return launch_decode_tma<128>(q, out, k_pool, v_pool, q_indptr, kv_lens, kv_indptr, kv_indices, work, items, nullptr, nullptr, q_heads,
+                                kv_heads, page_size, pool_pages, scale, window, s, cluster_chunks);
+}
 
 constexpr size_t kStaticScratchFloats = 4u * 1024u * 1024u;  // 16 MiB
 static __device__ __align__(256) float g_decode_scratch[kStaticScratchFloats];

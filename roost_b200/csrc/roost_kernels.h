@@ -17,7 +17,7 @@
 extern "C" {
 #endif
 
-#define ROOST_ABI_VERSION 6
+#define ROOST_ABI_VERSION 7
 
 #define ROOST_OK 0
 #define ROOST_ERR_INVALID 1      /* an argument is out of range or inconsistent; nothing was launched */
@@ -125,6 +125,19 @@ int roost_attention_decode(const void* q, void* out, const void* k_pool, const v
                            roost_stream_t stream);
 void roost_attention_set_decode_tma(int on);
 int roost_attention_status(void);
+/* The split decode attention without partial results in memory and without a merge kernel: the grid is thread-block
+ * clusters of cluster_chunks (1, 2, 4 or 8) CTAs, one cluster a (row, key/value head). The work list holds exactly
+ * cluster_chunks items (batch row, first key, end key, unused) a row, in key order, the row's chunks first and empty
+ * items (end key 0) after them; padding rows are cluster_chunks items of batch row -1. CTA r of a cluster takes the
+ * row's r-th item and CTA 0 combines the results in that order through distributed shared memory, with the merge
+ * kernel's arithmetic: the same bits as roost_attention_decode gives for the same chunks. Served where the copy-engine
+ * decode kernel is (roost_attention_decode_cluster_supported). */
+int roost_attention_decode_cluster_supported(int head_dim, int page_size, long long pool_pages, int kv_heads, const void* k_pool,
+                                             const void* v_pool);
+int roost_attention_decode_cluster(const void* q, void* out, const void* k_pool, const void* v_pool, const int32_t* q_indptr,
+                                   const int32_t* kv_lens, const int32_t* kv_indptr, const int32_t* kv_indices, const int32_t* work,
+                                   int items, int cluster_chunks, int q_heads, int kv_heads, int head_dim, int page_size,
+                                   long long pool_pages, float scale, int window, roost_stream_t stream);
 
 /* The split decode attention without a workspace argument. It has no counterpart in the reference: it exists for
  * callers that must not allocate device memory while they run (a host that gave the whole GPU to its own arena at

@@ -13,7 +13,7 @@ import torch
 
 from . import build
 
-ABI_VERSION = 6
+ABI_VERSION = 7
 F32, BF16 = 0, 1
 
 
@@ -75,6 +75,9 @@ _SIGNATURES = {
     "roost_attention_decode": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, ctypes.c_longlong, c_float, c_int,
                                c_void_p],
+    "roost_attention_decode_cluster": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                       c_int, c_int, c_int, c_int, ctypes.c_longlong, c_float, c_int, c_void_p],
+    "roost_attention_decode_cluster_supported": [c_int, c_int, ctypes.c_longlong, c_int, c_void_p, c_void_p],
     "roost_gemm_simt": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int, c_int, c_void_p],
     "roost_gemm_tcgen05_supported": [c_int, c_int, c_int, c_int64, c_int64],
     "roost_gemm_tcgen05": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int, c_void_p],
@@ -110,6 +113,7 @@ class KernelLibrary:
             fn.argtypes = args
             fn.restype = c_int
         self.decode_chunk = 512  # keys per work item of the split decode attention (see decode_chunk_for)
+        self.decode_cluster = True  # split rows merged by thread-block clusters where they fit (see decode_cluster_for)
         self._decode_ctas = 0
         self.launches = 0  # kernels launched through this handle (a host-side count of entry-point calls that launch)
 
@@ -130,6 +134,38 @@ class KernelLibrary:
             self._decode_ctas = 2 * torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
         items = rows * kv_heads * (-(-max(kv_cap, 1) // self.decode_chunk))
         return 2 * self.decode_chunk if self._decode_ctas < items <= 2 * self._decode_ctas else self.decode_chunk
+
+    def decode_cluster_for(self, rows: int, kv_cap: int, chunk: int, k_pool: torch.Tensor, v_pool: torch.Tensor) -> int:
+        """CTAs of a cluster that takes one (row, key/value head) of the split decode attention and merges the row's
+        chunks itself, for a step of ``rows`` rows whose requests hold at most ``kv_cap`` keys in chunks of ``chunk``: the
+        power of two that covers the chunks, when that is 2 to 8 and all the clusters run at once (two CTAs an SM);
+        else 0: partial results go through memory and the merge kernel. Same bits either way."""
+        if not self.decode_cluster:
+            return 0
+        if not self._decode_ctas:
+            self._decode_ctas = 2 * torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+        pages, nkv, page, d = k_pool.shape
+        chunks = -(-max(kv_cap, 1) // chunk)
+        size = 1
+        while size < chunks:
+            size *= 2
+        if size < 2 or size > 8 or rows * nkv * size > self._decode_ctas:
+            return 0
+        return size if self._lib.roost_attention_decode_cluster_supported(d, page, pages, nkv, _ptr(k_pool), _ptr(v_pool)) else 0
+
+    def decode_split_for(self, rows: int, kv_cap: int, k_pool: torch.Tensor, v_pool: torch.Tensor) -> tuple[int, int]:
+        """(keys per work item, CTAs a cluster or 0) of the split decode attention for a step of ``rows`` rows whose
+        requests hold at most ``kv_cap`` keys (the bounds of the captured step, so that every replay of it agrees). Where
+        clusters serve, the smallest chunk of 128, 256, 512 or 1024 keys whose clusters all run at once: more CTAs pull
+        on the memory and the merge costs no kernel (one row of 1,024 keys: 7.7 us in chunks of 128, 12.6 us in chunks of
+        512). Else the chunk of ``decode_chunk_for`` through the merge kernel. A row's bits depend on the chunk, so on
+        the step's size class, within rounding."""
+        if self.decode_cluster and kv_cap > 0:
+            for chunk in (128, 256, 512, 1024):
+                cluster = self.decode_cluster_for(rows, kv_cap, chunk, k_pool, v_pool)
+                if cluster:
+                    return chunk, cluster
+        return self.decode_chunk_for(rows, kv_cap, k_pool.shape[1]), 0
 
     # ------------------------------------------------------------------ ops
     def embedding(self, table: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
@@ -265,7 +301,11 @@ class KernelLibrary:
             self._call("roost_attention_prefill", _ptr(q), T, _ptr(out), _ptr(k_pool), _ptr(v_pool), _ptr(q_indptr), _ptr(kv_lens),
                        _ptr(kv_indptr), _ptr(kv_indices), _ptr(plan.prefill_work), plan.prefill_items, plan.prefill_tile_rows, nq, nkv, d, page,
                        k_pool.shape[0], scale, w, _stream())
-        if plan.decode_items:
+        if plan.decode_items and plan.cluster_chunks:
+            self._call("roost_attention_decode_cluster", _ptr(q), _ptr(out), _ptr(k_pool), _ptr(v_pool), _ptr(q_indptr), _ptr(kv_lens),
+                       _ptr(kv_indptr), _ptr(kv_indices), _ptr(plan.decode_work), plan.decode_items, plan.cluster_chunks, nq, nkv, d, page,
+                       k_pool.shape[0], scale, w, _stream())
+        elif plan.decode_items:
             part_o = part_ml = None
             if plan.slots:
                 part_o = torch.empty((plan.slots * nkv * 16 * d,), dtype=torch.float32, device=q.device)
@@ -446,4 +486,5 @@ def load() -> KernelLibrary:
         # programmatic dependent launch is on unless ROOST_PDL=0: the library's kernels overlap their preambles, and the
         # weight-streaming product its first loads of weights, with the tail of the kernel before them
         _LIB.set_pdl(os.environ.get("ROOST_PDL", "1") != "0")
+        _LIB.decode_cluster = os.environ.get("ROOST_DECODE_CLUSTER", "1") != "0"
     return _LIB

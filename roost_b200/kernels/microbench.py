@@ -62,19 +62,29 @@ def attention_decode(k, a) -> None:
     npages = pages_per * a.batch
     pool = torch.randn(2, npages, nkv, page, d, device="cuda", dtype=torch.bfloat16)   # keys then values, as the cache holds them
     q = torch.randn(a.batch, nq, d, device="cuda", dtype=torch.bfloat16)
-    chunk = a.chunk or k.decode_chunk
-    plan = plan_attention([a.context - 1] * a.batch, [1] * a.batch, nq // nkv, None, chunk, "cuda", 64)
+    chunk, cluster = k.decode_split_for(a.batch, a.context, pool[0], pool[1])
+    if a.chunk or a.no_cluster:
+        chunk = a.chunk or k.decode_chunk_for(a.batch, a.context, nkv)
+        cluster = 0 if a.no_cluster else k.decode_cluster_for(a.batch, a.context, chunk, pool[0], pool[1])
+    plan = plan_attention([a.context - 1] * a.batch, [1] * a.batch, nq // nkv, None, chunk, "cuda", 64, cluster)
     q_indptr = torch.arange(a.batch + 1, dtype=torch.int32, device="cuda")
     kv_lens = torch.full((a.batch,), a.context, dtype=torch.int32, device="cuda")
     kv_indptr = torch.arange(a.batch + 1, dtype=torch.int32, device="cuda") * pages_per
     gen = torch.Generator(device="cuda").manual_seed(0)
     kv_indices = (torch.arange(npages, device="cuda") if a.sequential_pages else torch.randperm(npages, device="cuda", generator=gen)).to(torch.int32)
     k.attention_set_decode_tma(not a.cp_async)
-    us = _time(lambda: k.attention_mma(q, pool[0], pool[1], q_indptr, kv_lens, kv_indptr, kv_indices, plan, d ** -0.5, None), a.warmup, a.iters)
+    call = lambda: k.attention_mma(q, pool[0], pool[1], q_indptr, kv_lens, kv_indptr, kv_indices, plan, d ** -0.5, None)
+    us = _time(call, a.warmup, a.iters)
     nbytes = a.batch * a.context * nkv * d * 2 * 2
+    form = f"clusters of {cluster}" if cluster else "decode and merge kernels"
     print(f"attention-decode batch={a.batch} context={a.context} chunk={chunk} items={plan.decode_items} "
           f"{'cp.async' if a.cp_async else 'tma'}: {us:.1f} us, {nbytes / us / 1e6:.2f} TB/s of keys and values "
-          f"(decode and merge kernels, eager launches), status {k.attention_status()}", flush=True)
+          f"({form}, eager launches), status {k.attention_status()}", flush=True)
+    # replayed from a graph, calls on pools of their own (larger than L2 together where one is over 32 MB): no host time
+    pools = [pool] + [torch.randn_like(pool) for _ in range(3)]
+    calls = [(lambda p=p: k.attention_mma(q, p[0], p[1], q_indptr, kv_lens, kv_indptr, kv_indices, plan, d ** -0.5, None)) for p in pools]
+    us = _graph_time(calls, a.warmup, a.iters)
+    print(f"  in a graph of four calls over four pools: {us:.1f} us a call, {nbytes / us / 1e6:.2f} TB/s", flush=True)
 
 
 def attention_prefill(k, a) -> None:
@@ -175,6 +185,7 @@ def main(argv=None) -> int:
     p.add_argument("--head-dim", type=int, default=128)
     p.add_argument("--page-size", type=int, default=16)
     p.add_argument("--chunk", type=int, default=0, help="keys per decode work item (default: the library's)")
+    p.add_argument("--no-cluster", action="store_true", help="split rows through partial results in memory and the merge kernel")
     p.add_argument("--tile-rows", type=int, default=0, help="packed rows per prefill work item: 64, 128 or 256 (default: the library's choice)")
     p.add_argument("--cp-async", action="store_true", help="decode attention through the cp.async kernel instead of TMA")
     p.add_argument("--mma-sync", action="store_true", help="prefill attention through the mma.sync kernel instead of tcgen05")

@@ -103,9 +103,9 @@ class PagedAttention(Mixer):
         if q.dtype == torch.bfloat16 and getattr(k, "attention_mma_supported", lambda d: False)(s.head_dim):
             group = s.num_heads // s.num_kv_heads
             tile_rows = k.attention_prefill_tile_rows(s.num_heads, cache.k_pool, cache.v_pool, batch.num_tokens * group)
-            chunk_for = getattr(k, "decode_chunk_for", None)
-            chunk = chunk_for(batch.num_rows, batch.kv_cap, s.num_kv_heads) if chunk_for and batch.kv_cap else k.decode_chunk
-            plan = batch.step_work(self, ("paged_attention", group, s.window, chunk, tile_rows))
+            split_for = getattr(k, "decode_split_for", None)
+            chunk, cluster = split_for(batch.num_rows, batch.kv_cap, cache.k_pool, cache.v_pool) if split_for and batch.kv_cap else (k.decode_chunk, 0)
+            plan = batch.step_work(self, ("paged_attention", group, s.window, chunk, tile_rows, cluster))
             return k.attention_mma(q, cache.k_pool, cache.v_pool, batch.q_indptr, batch.kv_lens, tables.kv_indptr,
                                    tables.kv_indices, plan, s.scale, s.window)
         return k.paged_attention_generic(q, cache.k_pool, cache.v_pool, batch.positions, batch.token_row,
@@ -117,29 +117,30 @@ class PagedAttention(Mixer):
         return ("short_rows", any(n <= SHORT_ROW_TOKENS for n in row_counts))
 
     def step_work_arrays(self, key, row_starts, row_counts):
-        _, group, window, chunk, tile_rows = key
-        prefill, decode, merge, _ = attention_work(row_starts, row_counts, group, window, chunk, tile_rows)
+        _, group, window, chunk, tile_rows, cluster = key
+        prefill, decode, merge, _ = attention_work(row_starts, row_counts, group, window, chunk, tile_rows, cluster)
         return [np.asarray(prefill, np.int32), np.asarray(decode, np.int32), np.asarray(merge, np.int32)]
 
     def step_work_caps(self, key, num_tokens, num_rows, kv_cap, step_class):
-        _, group, _, chunk, tile_rows = key
+        _, group, _, chunk, tile_rows, cluster = key
         short = dict([step_class[i : i + 2] for i in range(0, len(step_class), 2)]).get("short_rows", True)
-        pc, dc, mc = attention_caps(num_tokens, num_rows, kv_cap, group, chunk, tile_rows, short)
+        pc, dc, mc = attention_caps(num_tokens, num_rows, kv_cap, group, chunk, tile_rows, short, cluster)
         return [(pc * 2, -1), (dc * 4, -1), (mc * 4, -1)]     # padding items name batch row -1, which the kernels skip
 
     def step_work_bind(self, key, tensors, host_arrays=None, captured=None):
-        _, group, _, _, tile_rows = key
+        _, group, _, _, tile_rows, cluster = key
         prefill, decode, merge = tensors
         if captured is not None:       # every list at its capacity; a step of one token a row splits rows of `group` packed rows
             num_tokens, num_rows, kv_cap, step_class = captured
             (pc, _), (dc, _), (mc, _) = self.step_work_caps(key, num_tokens, num_rows, kv_cap, step_class)
-            return AttentionPlan(prefill_items=pc // 2, prefill_tile_rows=tile_rows, decode_items=dc // 4, merge_items=mc // 4, slots=dc // 4,
+            return AttentionPlan(prefill_items=pc // 2, prefill_tile_rows=tile_rows, decode_items=dc // 4, merge_items=mc // 4,
+                                 slots=0 if cluster else dc // 4, cluster_chunks=cluster,
                                  merge_rows=min(16, group) if num_tokens == num_rows else 16, prefill_work=prefill, decode_work=decode,
                                  merge_work=merge)
         hp, hd, hm = host_arrays
-        slots = int((hd[3::4] >= 0).sum())      # every chunk of a split row has a partial slot of its own
+        slots = 0 if cluster else int((hd[3::4] >= 0).sum())      # every chunk of a split row has a partial slot of its own
         return AttentionPlan(prefill_items=hp.size // 2, prefill_tile_rows=tile_rows, decode_items=hd.size // 4, merge_items=hm.size // 4,
-                             slots=slots, merge_rows=int((hm[2::4] >> 24).max()) if hm.size else 1, prefill_work=prefill,
+                             slots=slots, cluster_chunks=cluster, merge_rows=int((hm[2::4] >> 24).max()) if hm.size else 1, prefill_work=prefill,
                              decode_work=decode, merge_work=merge)
 
 

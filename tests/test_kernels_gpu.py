@@ -387,12 +387,12 @@ def test_sampler_matches_the_plain_sampler(kernels, vocab):
 
 
 # ------------------------------------------------------------------------------------------ tensor-core attention (bfloat16)
-def run_mma(kernels, q, kp, vp, lens, news, indptr, indices, scale, window, chunk=None, tile_rows=None):
+def run_mma(kernels, q, kp, vp, lens, news, indptr, indices, scale, window, chunk=None, tile_rows=None, cluster=0):
     from roost_b200.parts.attention_work import plan_attention
     nq, nkv = q.shape[1], kp.shape[1]
     starts = [n - m for n, m in zip(lens, news)]
     plan = plan_attention(starts, news, nq // nkv, window, chunk or kernels.decode_chunk, "cuda",
-                          tile_rows or kernels.attention_prefill_tile_rows(nq, kp, vp))
+                          tile_rows or kernels.attention_prefill_tile_rows(nq, kp, vp), cluster)
     q_indptr = torch.tensor([0] + list(torch.tensor(news).cumsum(0)), dtype=torch.int32).cuda()
     kv_lens = torch.tensor(lens, dtype=torch.int32).cuda()
     return kernels.attention_mma(q.cuda(), kp, vp, q_indptr, kv_lens, indptr, indices, plan, scale, window), plan
@@ -530,6 +530,42 @@ def test_attention_mma_rows_do_not_depend_on_the_batch(kernels, chunk):
     want = paged_reference(q.double(), keys, values, positions, [0, 1, 2], 0.1, None)
     close(together, want, dtype, f"chunk {chunk}", scale=2)
     close(other, together.double(), dtype, "one chunk size against the other", scale=2)
+
+
+@pytest.mark.parametrize("window", [None, 300])
+@pytest.mark.parametrize("nq,nkv,d,page,chunk,cluster", [(8, 2, 128, 16, 512, 8), (32, 8, 128, 16, 1024, 4), (14, 2, 64, 32, 512, 8),
+                                                        (4, 4, 64, 16, 1024, 2), (16, 1, 128, 64, 512, 4)])
+def test_attention_decode_clusters_give_the_merge_kernels_bits(kernels, nq, nkv, d, page, chunk, cluster, window):
+    """Split rows merged by thread-block clusters through distributed shared memory against the same rows through partial
+    results in memory and the merge kernel: the same chunks, the same order of sums, the same bits. Rows of one chunk,
+    of every chunk of the cluster, of a length that ends on a chunk's edge, rows of two tokens, and a prompt portion
+    beside them (which the prefill kernel takes either way)."""
+    dtype = torch.bfloat16
+    g = torch.Generator().manual_seed(61)
+    top = chunk * cluster
+    lens = [top, 37, chunk, chunk + 1, top - 1, 2 * chunk - 5, 700, 90]
+    news = [1, 1, 1, 2, 1, 1, 2, 60]
+    keys = [torch.randn(n, nkv, d, generator=g).to(dtype).double() for n in lens]
+    values = [torch.randn(n, nkv, d, generator=g).to(dtype).double() for n in lens]
+    positions, rows = [], []
+    for b, (n, m) in enumerate(zip(lens, news)):
+        positions += list(range(n - m, n))
+        rows += [b] * m
+    q = (torch.randn(len(positions), nq, d, generator=g) * 1.5).to(dtype)
+    kp, vp, indptr, indices = build_paged(keys, values, page, dtype, num_pages=sum(-(-n // page) for n in lens) + 3, seed=62)
+    if window:
+        assert release_passed_pages(kp, vp, indptr, indices, lens, news, window, page) > 0
+    scale = 1 / math.sqrt(d)
+    assert kernels._lib.roost_attention_decode_cluster_supported(d, page, kp.shape[0], nkv, kp.data_ptr(), vp.data_ptr())
+    plain_path, plan0 = run_mma(kernels, q, kp, vp, lens, news, indptr, indices, scale, window, chunk=chunk)
+    clustered, plan1 = run_mma(kernels, q, kp, vp, lens, news, indptr, indices, scale, window, chunk=chunk, cluster=cluster)
+    assert kernels.attention_status() == 0
+    assert (plan0.merge_items > 0 or window) and plan1.merge_items == 0 and plan1.cluster_chunks == cluster   # a window may leave every row one chunk
+    assert plan1.decode_items == cluster * sum(1 for m in news if m * (nq // nkv) <= 16)
+    assert not torch.isnan(clustered.float()).any()
+    assert torch.equal(clustered, plain_path)
+    want = paged_reference(q.double(), keys, values, positions, rows, scale, window)
+    close(clustered, want, dtype, f"clustered decode window={window}", scale=2)
 
 
 @pytest.mark.parametrize("m,n,k", [(128, 256, 64), (300, 272, 96), (1, 256, 64), (77, 18992, 1024), (2048, 6144, 4096), (513, 512, 12288)])

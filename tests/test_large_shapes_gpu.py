@@ -170,7 +170,7 @@ def test_portions_of_512_tokens_beside_three_decoding_requests(big_model, dtype)
 def test_decoding_at_contexts_of_1000_to_4090_keys_through_captured_graphs(big_model, dtype, requests):
     """The benchmark's decode: requests with 1,000 to 4,074 tokens behind them decode 16 tokens each, every step's logits
     compared. Nine requests run the captured step of twelve rows (three of them padding) with chunks of 512 keys; eight
-    run the step whose size class makes the split decode kernel take chunks of 1,024 keys. The contexts are prefilled
+    run the step whose size class makes the split decode kernel take chunks of 1,024 keys and merge them in clusters. The contexts are prefilled
     two or three requests a step (up to 7,500 tokens a step: two row groups a CTA in the prefill attention)."""
     from roost_b200.engine.executor import graph_rows
     model = H.make_model(big_model.dir, dtype, "gpu")
@@ -194,7 +194,10 @@ def test_decoding_at_contexts_of_1000_to_4090_keys_through_captured_graphs(big_m
     rows = graph_rows(requests)
     assert rows == (12 if requests == 9 else 8) and ex.graph_replays >= steps - 1 and {key[0] for key in ex._graphs if key[0] == key[1]} == {rows}
     if dtype == torch.bfloat16:
-        assert k.decode_chunk_for(rows, 4096, 8) == (512 if requests == 9 else 1024)
+        # nine requests: chunks of 512 keys through partial results and the merge kernel; eight: chunks of 1,024 keys, each
+        # row's four chunks merged by a cluster of four CTAs
+        pools = ex.storage.tensors[0][0]
+        assert k.decode_split_for(rows, 4096, pools[0], pools[1]) == ((512, 0) if requests == 9 else (1024, 4))
     compare(f"{big_model.name} decode of {requests} requests at {contexts[0]}..{contexts[-1] + steps} keys", dtype, got, want)
     k.check_device_status()
     assert all(ex.cache.get(r).tokens == len(ids) for r, ids in reqs.items())

@@ -199,6 +199,15 @@ def test_sizes_of_captured_steps_and_padding_rows():
     assert ht.max_position == 5 and ht.max_kv_len == 6 and ht.row_starts == [5, -1, -1]
     prefill, decode, merge, slots = attention_work(ht.row_starts, ht.row_counts, 4, None, 64)
     assert decode == [0, 0, 6, -1] and not prefill and not merge and slots == 0
+    # for clusters of four a row brings four items in key order, the empty ones last, and nothing to merge; under a window
+    # the first item is the chunk the window begins in
+    _, decode, merge, slots = attention_work([130, -1, 4], [1, 1, 2], 4, None, 64, cluster=4)
+    assert decode == [0, 0, 64, 0, 0, 64, 128, 1, 0, 128, 131, 2, 0, 0, 0, 3,
+                      2, 0, 6, 0, 2, 0, 0, 1, 2, 0, 0, 2, 2, 0, 0, 3] and not merge and slots == 0
+    _, decode, _, _ = attention_work([200], [1], 4, 70, 64, cluster=2)
+    assert decode == [0, 128, 192, 0, 0, 192, 201, 1]
+    with pytest.raises(ValueError):
+        attention_work([200], [1], 4, None, 64, cluster=2)
     # a step of several tokens a row: the padding tokens one to a padding row, the rest to the first; rows may stay empty
     assert [len(r[2]) for r in padded_rows([(rc, 2, [1, 2, 3], [2])], 8, 4)] == [3, 3, 1, 1]
     assert [len(r[2]) for r in padded_rows([(rc, 2, [1, 2, 3], [2])], 4, 4)] == [3, 0, 1, 0]
