@@ -745,6 +745,177 @@ __global__ void __launch_bounds__(192, 1)
   }
 }
 
+// ------------------------------------------------------------------------------------------------ few rows: k split over a cluster
+// The same product for shapes with few 128-row tiles of w and a long k (the attention's output projection, the down
+// projection): the grid is thread-block clusters of `split` CTAs, one cluster a tile, CTA r of a cluster taking the r-th
+// part of k. Two CTAs fit an SM and every CTA asks for all its first stages of w at once, before the kernel in front has
+// finished, so nearly the whole matrix is on its way when the product starts. The partial sums never go to memory:
+// every CTA leaves its accumulator in its own shared memory, and after a cluster barrier CTA r adds up, in CTA order, the
+// r-th part of the tile's rows through distributed shared memory and writes it. The order of every sum is fixed by
+// (n, k) alone, so results are the same on every run and for every batch.
+constexpr int kSplitMaxStages = 6;
+
+__device__ __forceinline__ float ld_dsmem_f32(uint32_t addr, uint32_t rank) {
+  uint32_t remote;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(remote) : "r"(addr), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];\n" : "=f"(v) : "r"(remote));
+  return v;
+}
+// Every thread of the cluster that has not exited arrives and waits; the threads of a warp need not come together.
+__device__ __forceinline__ void cluster_sync_unaligned() {
+  asm volatile("barrier.cluster.arrive.release;\nbarrier.cluster.wait.acquire;\n" ::: "memory");
+}
+
+template <typename TOut>
+__global__ void __launch_bounds__(192, 2)
+    gemm_split_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_constant__ CUtensorMap tma_x, TOut* __restrict__ out, int M,
+                      int N, int K, int64_t ldo, int ntok, int split, int stages) {
+  const uint32_t stage_w = 128 * BK * 2, stage_bytes = stage_w + (uint32_t)ntok * BK * 2;  // a multiple of 1024 bytes
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t smem_base = ((uint32_t)__cvta_generic_to_shared(smem_raw) + 1023u) & ~1023u;
+  float* red = reinterpret_cast<float*>(smem_raw + (smem_base - (uint32_t)__cvta_generic_to_shared(smem_raw)));  // [m][128], over the first stages
+  __shared__ __align__(8) uint64_t bars[2 * kSplitMaxStages + 1];
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+  const uint32_t bar0 = (uint32_t)__cvta_generic_to_shared(bars);
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (kSplitMaxStages + s); };
+  const uint32_t acc_full_bar = bar0 + 8u * (2 * kSplitMaxStages);
+  const uint32_t tmem_cols = ntok <= 32 ? 32u : 64u;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x / split, r = blockIdx.x % split;  // the cluster's tile; this CTA's rank in the cluster
+  const int kbs = (K + BK - 1) / BK;
+  const int kb0 = (int)((long long)kbs * r / split), kb1 = (int)((long long)kbs * (r + 1) / split);  // kb1 > kb0: kbs >= split
+  int prologue = 0;
+  if (threadIdx.x == 0) {
+    asm volatile("prefetch.tensormap [%0];\n" ::"l"(reinterpret_cast<uint64_t>(&tma_w)) : "memory");
+    asm volatile("prefetch.tensormap [%0];\n" ::"l"(reinterpret_cast<uint64_t>(&tma_x)) : "memory");
+    abort_flag = 0;
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    mbar_init(acc_full_bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    pdl_launch_dependents(7);
+    // no kernel writes the weights: their loads start while the kernel that produces x is still running
+    for (int kb = kb0; kb < kb1 && prologue < stages; ++kb, ++prologue) {
+      mbar_expect_tx(full_bar(prologue), stage_bytes);
+      tma_load_2d(smem_base + prologue * stage_bytes, &tma_w, full_bar(prologue), kb * BK, t * 128);
+    }
+    pdl_wait(7);
+    for (int i = 0; i < prologue; ++i) tma_load_2d(smem_base + i * stage_bytes + stage_w, &tma_x, full_bar(i), (kb0 + i) * BK, 0);
+  } else {
+    pdl_wait();
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"((uint32_t)__cvta_generic_to_shared(&tmem_base_slot)),
+                 "r"(tmem_cols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+  volatile int* abortp = &abort_flag;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = prologue % stages;
+      uint32_t phase = prologue == stages ? 1u : 0u;
+      bool ok = true;
+      for (int kb = kb0 + prologue; kb < kb1 && ok; ++kb) {
+        if (!(ok = mbar_wait(empty_bar(stage), phase ^ 1u, abortp, 1))) break;
+        const uint32_t sw = smem_base + stage * stage_bytes;
+        mbar_expect_tx(full_bar(stage), stage_bytes);
+        tma_load_2d(sw, &tma_w, full_bar(stage), kb * BK, t * 128);
+        tma_load_2d(sw + stage_w, &tma_x, full_bar(stage), kb * BK, 0);
+        if (++stage == stages) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc_bf16(128, ntok);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int kb = kb0; kb < kb1 && ok; ++kb) {
+        if (!(ok = mbar_wait(full_bar(stage), phase, abortp, 3))) break;
+        tcgen05_fence_after();
+        const uint32_t sw = smem_base + stage * stage_bytes;
+        const uint64_t a_desc = umma_desc_k_major_sw128(sw);
+        const uint64_t b_desc = umma_desc_k_major_sw128(sw + stage_w);
+#pragma unroll
+        for (int k = 0; k < BK / kUmmaK; ++k) {
+          tcgen05_mma_f16(tmem_base, a_desc + (uint64_t)(2 * k), b_desc + (uint64_t)(2 * k), idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+        }
+        tcgen05_commit(empty_bar(stage));
+        if (++stage == stages) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+      if (ok) tcgen05_commit(acc_full_bar);
+    }
+  } else {
+    // the accumulator (out transposed: a lane of tensor memory is a row of the tile, a column a row of x) into this CTA's
+    // shared memory as [row of x][128], over the first stages, which no copy writes any more
+    const int lane_group = warp & 3;
+    const int row = lane_group * 32 + lane;
+    if (mbar_wait(acc_full_bar, 0u, abortp, 4)) {
+      tcgen05_fence_after();
+      const uint32_t taddr = tmem_base + ((uint32_t)(lane_group * 32) << 16);
+      for (int cb = 0; cb < ntok && cb < M; cb += 16) {
+        uint32_t v[16];
+        tcgen05_ld_32x32b_x16(taddr + cb, v);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          if (cb + i < M) red[(cb + i) * 128 + row] = __uint_as_float(v[i]);
+        }
+      }
+    }
+    tcgen05_fence_before();
+  }
+  // Every thread of every CTA of the cluster comes here, whatever its waits returned: nobody is left waiting at the
+  // cluster's barriers and nobody reads the shared memory of a CTA that has gone.
+  __syncwarp();
+  cluster_sync_unaligned();  // the partial sums of all the cluster's CTAs are in their shared memory
+  if (warp >= 2) {
+    const int etid = (warp - 2) * 32 + lane;
+    const int lo = 128 * r / split, cnt = 128 * (r + 1) / split - lo;  // this CTA's share of the tile's rows
+    const uint32_t red_addr = smem_base;
+    for (int idx = etid; idx < cnt * M; idx += 128) {
+      const int m = idx / cnt, nl = lo + idx % cnt, n = t * 128 + nl;
+      float part[8];
+#pragma unroll
+      for (int rr = 0; rr < 8; ++rr) part[rr] = rr < split ? ld_dsmem_f32(red_addr + (uint32_t)(m * 128 + nl) * 4u, (uint32_t)rr) : 0.f;
+      float sum = part[0];
+#pragma unroll
+      for (int rr = 1; rr < 8; ++rr) {
+        if (rr < split) sum += part[rr];
+      }
+      if (n < N) out[(size_t)m * ldo + n] = from_float<TOut>(sum);
+    }
+  }
+  cluster_sync_unaligned();  // nobody leaves while another CTA still reads its shared memory
+  if (*abortp) {
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000LL) __nanosleep(256);
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(tmem_cols) : "memory");
+  }
+}
+
 // ------------------------------------------------------------------------------------------------ host side
 // A [rows, k] bfloat16 matrix with row stride ld elements as a 2-D tensor map with boxes of box_rows x 64 elements.
 static int make_map(CUtensorMap* map, const void* base, int rows, int k, int64_t ld, int box_rows) {
@@ -820,6 +991,43 @@ static int launch_stream(const CUtensorMap& mw, const CUtensorMap& mx, void* out
   if (units < grid) grid = units;
   launch_kernel(kernel, dim3((int)grid), dim3(192), smem, s, mw, mx, (TOut*)out, m, n, k, ldo, ntok, ws, flags);
   return check_launch("gemm_stream");
+}
+
+// CTAs of a cluster for the k-split product of an [n, k] weight: the most (up to 8) that still lets every cluster run at
+// once with two CTAs an SM and leaves every CTA at least two 64-wide blocks of k; 0 when the shape has too many tiles.
+static int split_for(int n, int k) {
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  const int tiles = (n + 127) / 128, kbs = (k + BK - 1) / BK;
+  int split = (2 * sms) / tiles;
+  if (split > 8) split = 8;
+  if (split > kbs / 2) split = kbs / 2;
+  while (split & (split - 1)) split &= split - 1;  // a power of two: clusters of 2, 4 and 8 fill the SMs of a GPC, 6 and 7 leave some idle
+  static const char* forced = getenv("ROOST_GEMM_SPLIT");
+  if (forced && atoi(forced) >= 2 && atoi(forced) <= 8 && atoi(forced) <= kbs / 2 && (long long)tiles * atoi(forced) <= 2 * sms) split = atoi(forced);
+  return split >= 2 ? split : 0;
+}
+
+template <typename TOut>
+static int launch_split(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int m, int n, int k, int64_t ldo, int ntok, int split,
+                        cudaStream_t s) {
+  const int stages = ntok == 16 ? 6 : (ntok == 32 ? 5 : 4);
+  const size_t smem = (size_t)stages * (128 * BK * 2 + ntok * BK * 2) + 1024;
+  auto kernel = gemm_split_kernel<TOut>;
+  static bool attr_set[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+    cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)((size_t)kSplitMaxStages * (128 * BK * 2 + 16 * BK * 2) + 1024));
+    if (dev >= 0 && dev < 64) attr_set[dev] = true;
+  }
+  const int tiles = (n + 127) / 128;
+  launch_kernel_cluster(kernel, dim3(tiles * split), dim3(192), smem, s, split, mw, mx, (TOut*)out, m, n, k, ldo, ntok, split, stages);
+  return check_launch("gemm_split");
 }
 
 static bool g_use_pairs = true;
@@ -920,6 +1128,40 @@ extern "C" int roost_gemm_stream(const void* x, const void* w, void* out, int m,
   if (rc != ROOST_OK) return rc;
   if (out_dtype == ROOST_BF16) return launch_stream<__nv_bfloat16, false>(mw, mx, out, m, n, k, ldo, ntok, ws, flags, (cudaStream_t)stream);
   return launch_stream<float, false>(mw, mx, out, m, n, k, ldo, ntok, ws, flags, (cudaStream_t)stream);
+}
+
+extern "C" int roost_gemm_split_supported(int m, int n, int k, int64_t ldx, int64_t ldw) {
+  return roost_gemm_stream_supported(m, n, k, ldx, ldw) && split_for(n, k) > 0;
+}
+
+// Where the k-split product was measured faster than the library's and than the weight-streaming kernel on a B200: clusters
+// of eight, at least four 64-wide blocks of k a CTA, at most 8 rows of x (16 with a k of 8192 or more). For 8 rows:
+// [4096, 4096] 10.3 us against 12.3 (cuBLAS) and 12.5 (stream); [4096, 12288] 21.3 against 32.1 and 23.5; [1024, 3072]
+// 5.9 against 8.6 and 10.7; but [6144, 4096] 13.4 against 11.8 and [5120, 8192] (clusters of four) 19.0 against 18.3.
+extern "C" int roost_gemm_split_preferred(int m, int n, int k, int64_t ldx, int64_t ldw) {
+  if (!roost_gemm_split_supported(m, n, k, ldx, ldw) || split_for(n, k) != 8 || k < 2048) return 0;
+  return (m <= 8 || (m <= 16 && k >= 8192)) ? 1 : 0;
+}
+
+// out = x w^T for at most 64 rows of x and a weight of few 128-row tiles and a long k: k split over thread-block clusters,
+// partial sums added up through distributed shared memory (no workspace).
+extern "C" int roost_gemm_split(const void* x, const void* w, void* out, int m, int n, int k, int64_t ldx, int64_t ldw, int64_t ldo,
+                                int out_dtype, roost_stream_t stream) {
+  ROOST_REQUIRE(out_dtype == ROOST_BF16 || out_dtype == ROOST_F32, "gemm_split: the output is bfloat16 (1) or float32 (0)");
+  ROOST_REQUIRE(ldx >= k && ldw >= k && ldo >= n, "gemm_split: a leading dimension is smaller than its row");
+  if (!roost_gemm_split_supported(m, n, k, ldx, ldw)) {
+    return fail(ROOST_ERR_UNSUPPORTED, "gemm_split: needs 1 <= m <= 64, k and the row strides multiples of 8, and few enough tiles for clusters");
+  }
+  ROOST_REQUIRE(((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0), "gemm_split: x and w must start on 16-byte boundaries");
+  const int ntok = m <= 16 ? 16 : (m <= 32 ? 32 : 64);
+  CUtensorMap mw, mx;
+  int rc = make_map(&mw, w, n, k, ldw, 128);
+  if (rc != ROOST_OK) return rc;
+  rc = make_map(&mx, x, m, k, ldx, ntok);
+  if (rc != ROOST_OK) return rc;
+  const int split = split_for(n, k);
+  if (out_dtype == ROOST_BF16) return launch_split<__nv_bfloat16>(mw, mx, out, m, n, k, ldo, ntok, split, (cudaStream_t)stream);
+  return launch_split<float>(mw, mx, out, m, n, k, ldo, ntok, split, (cudaStream_t)stream);
 }
 
 extern "C" int roost_gemm_stream_swiglu_supported(int m, int n, int k, int64_t ldx, int64_t ldw) {

@@ -13,7 +13,7 @@ import torch
 
 from . import build
 
-ABI_VERSION = 7
+ABI_VERSION = 8
 F32, BF16 = 0, 1
 
 
@@ -87,6 +87,9 @@ _SIGNATURES = {
     "roost_gemm_stream_workspace_floats": [],
     "roost_gemm_stream_workspace_flags": [],
     "roost_gemm_stream_supported": [c_int, c_int, c_int, c_int64, c_int64],
+    "roost_gemm_split_supported": [c_int, c_int, c_int, c_int64, c_int64],
+    "roost_gemm_split_preferred": [c_int, c_int, c_int, c_int64, c_int64],
+    "roost_gemm_split": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int, c_void_p],
     "roost_gemm_stream": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int, c_void_p, c_void_p,
                           c_void_p],
     "roost_gemm_stream_swiglu_supported": [c_int, c_int, c_int, c_int64, c_int64],
@@ -373,6 +376,27 @@ class KernelLibrary:
         out = torch.empty((M, N), dtype=out_dtype, device=x.device)
         self._call("roost_gemm_stream", _ptr(x), _ptr(w), _ptr(out), M, N, K, x.stride(0), w.stride(0), out.stride(0),
                    dtype_code(out_dtype), _ptr(ws[0]), _ptr(ws[1]), _stream())
+        return out
+
+    def gemm_split_supported(self, m: int, n: int, k: int, ldx: int, ldw: int) -> bool:
+        return bool(self._lib.roost_gemm_split_supported(m, n, k, ldx, ldw))
+
+    def gemm_split_preferred(self, m: int, n: int, k: int, ldx: int, ldw: int) -> bool:
+        """Whether the k-split product was measured faster than the other products for this shape."""
+        return bool(self._lib.roost_gemm_split_preferred(m, n, k, ldx, ldw))
+
+    def gemm_split(self, x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+        """x [M <= 64, K] times w [N, K] transposed for a weight of few 128-row tiles and a long K: K split over
+        thread-block clusters, the partial sums added up through distributed shared memory."""
+        _need(x, "x", torch.bfloat16); _need(w, "w", torch.bfloat16)
+        M, K = x.shape
+        N, K2 = w.shape
+        if K != K2:
+            raise KernelError(f"gemm_split: x has {K} columns, w has {K2}")
+        out_dtype = out_dtype or torch.bfloat16
+        out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+        self._call("roost_gemm_split", _ptr(x), _ptr(w), _ptr(out), M, N, K, x.stride(0), w.stride(0), out.stride(0),
+                   dtype_code(out_dtype), _stream())
         return out
 
     def gemm_stream_swiglu_supported(self, m: int, n: int, k: int, ldx: int, ldw: int) -> bool:

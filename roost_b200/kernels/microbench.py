@@ -123,7 +123,11 @@ def gemm_small(k, a) -> None:
         x = torch.randn(a.rows, kk, device="cuda", dtype=torch.bfloat16)
         t_stream = _graph_time([(lambda w=w: k.gemm_stream(x, w)) for w in ws], a.warmup, a.iters)
         t_lib = _graph_time([(lambda w=w: torch.matmul(x, w.t())) for w in ws], a.warmup, a.iters)
-        print(f"gemm-small rows={a.rows} n={n} k={kk}: stream {t_stream:.1f} us ({n * kk * 2 / t_stream / 1e6:.2f} TB/s of weights), "
+        split = ""
+        if k.gemm_split_supported(a.rows, n, kk, kk, kk):
+            t_split = _graph_time([(lambda w=w: k.gemm_split(x, w)) for w in ws], a.warmup, a.iters)
+            split = f"k split over clusters {t_split:.1f} us ({n * kk * 2 / t_split / 1e6:.2f} TB/s), "
+        print(f"gemm-small rows={a.rows} n={n} k={kk}: stream {t_stream:.1f} us ({n * kk * 2 / t_stream / 1e6:.2f} TB/s of weights), {split}"
               f"cuBLAS {t_lib:.1f} us, in one graph back to back; status {k.gemm_tcgen05_status()}", flush=True)
 
 

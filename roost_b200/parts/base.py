@@ -56,8 +56,8 @@ class Runtime:
         self.kernels = kernels
         # products of at most 64 rows: "auto" | "library" | "stream" (parts/linear.py)
         self.small_gemm = os.environ.get("ROOST_SMALL_GEMM", "auto")
-        if self.small_gemm not in ("auto", "library", "stream"):
-            raise ValueError(f"ROOST_SMALL_GEMM={self.small_gemm!r} is not one of auto, library, stream")
+        if self.small_gemm not in ("auto", "library", "stream", "split"):
+            raise ValueError(f"ROOST_SMALL_GEMM={self.small_gemm!r} is not one of auto, library, stream, split")
 
     @property
     def full_precision(self) -> bool:

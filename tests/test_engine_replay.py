@@ -167,7 +167,7 @@ def test_a_step_that_does_not_fit_changes_nothing(tiny, backend):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("policy", ["stream", "library"])
+@pytest.mark.parametrize("policy", ["stream", "split", "library"])
 def test_every_small_product_kernel_serves_the_engine(tiny_model_dirs, policy):
     """Decode steps through each of the kernels a product of few rows can run on (the default picks by size)."""
     name, t = "B", TINY["B"]

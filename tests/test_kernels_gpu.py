@@ -625,6 +625,34 @@ def test_gemm_stream_swiglu(kernels, m, inter, k):
     assert not kernels.gemm_stream_swiglu_supported(33, 2 * inter, k, k, k) and not kernels.gemm_stream_swiglu_supported(m, 2 * inter + 128, k, k, k)
 
 
+@pytest.mark.parametrize("m,n,k", [(8, 128, 256), (17, 272, 200), (1, 6144, 4096), (8, 4096, 12288), (64, 2048, 512), (33, 4096, 4096), (5, 1000, 1024),
+                                   (16, 5120, 25600)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_gemm_split(kernels, m, n, k, out_dtype):
+    """The product of decode steps with k split over a thread-block cluster a tile and the partial sums added up in CTA
+    order through distributed shared memory: clusters of 2 to 8 (and of 6), a k whose last block is part empty, a last
+    tile that is part empty, every padding of the rows of x; the same bits on every run and for every batch."""
+    assert kernels.gemm_split_supported(m, n, k, k, k)
+    a = rand((m, k), torch.bfloat16, 53)
+    w = rand((n, k), torch.bfloat16, 54)
+    want = a.double().cpu() @ w.double().cpu().T
+    got = kernels.gemm_split(a, w, out_dtype)
+    assert kernels.gemm_tcgen05_status() == 0, "a bounded wait inside the kernel was given up"
+    if out_dtype == torch.float32:
+        lib = torch.mm(a, w.t(), out_dtype=torch.float32)
+        err = float(((got.double().cpu() - want).abs() / (1 + want.abs())).max())
+        err_lib = float(((lib.double().cpu() - want).abs() / (1 + want.abs())).max())
+        assert err < max(2 * err_lib, k * 2.0 ** -23), f"{err} against the library's {err_lib}"
+    else:
+        close(got, want, torch.bfloat16, "gemm_split", scale=math.sqrt(k) / 8)
+    assert torch.equal(kernels.gemm_split(a, w, out_dtype), got), "the product is not repeatable"
+    r = m // 2
+    assert torch.equal(kernels.gemm_split(a[r : r + 1].contiguous(), w, out_dtype), got[r : r + 1]), "a row depends on its batch"
+    # too many rows of x; a row stride that is no multiple of 8; too few blocks of k to split; too many tiles for clusters
+    assert not kernels.gemm_split_supported(65, n, k, k, k) and not kernels.gemm_split_supported(m, n, k + 4, k + 4, k + 4)
+    assert not kernels.gemm_split_supported(m, n, 64, 64, 64) and not kernels.gemm_split_supported(m, 151936, 4096, 4096, 4096)
+
+
 @pytest.mark.parametrize("m,n,k", [(8, 128, 64), (17, 272, 96), (1, 6144, 4096), (8, 4096, 12288), (64, 2048, 512), (33, 4096, 4096), (5, 151936, 1024)])
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
 def test_gemm_stream(kernels, m, n, k, out_dtype):
