@@ -767,14 +767,18 @@ __device__ __forceinline__ void cluster_sync_unaligned() {
   asm volatile("barrier.cluster.arrive.release;\nbarrier.cluster.wait.acquire;\n" ::: "memory");
 }
 
-template <typename TOut>
+// SWIGLU: w's rows come in blocks of 256 (128 gate rows, then the 128 up rows of the same outputs), a tile is such a
+// block with two accumulators that share the x operand, and what is written is silu(gate) * up: out has n / 2 columns.
+template <typename TOut, bool SWIGLU>
 __global__ void __launch_bounds__(192, 2)
     gemm_split_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_constant__ CUtensorMap tma_x, TOut* __restrict__ out, int M,
                       int N, int K, int64_t ldo, int ntok, int split, int stages) {
-  const uint32_t stage_w = 128 * BK * 2, stage_bytes = stage_w + (uint32_t)ntok * BK * 2;  // a multiple of 1024 bytes
+  constexpr int WR = SWIGLU ? 256 : 128;  // rows of w in a tile
+  constexpr int P = SWIGLU ? 2 : 1;       // accumulators of a tile
+  const uint32_t stage_w = WR * BK * 2, stage_bytes = stage_w + (uint32_t)ntok * BK * 2;  // a multiple of 1024 bytes
   extern __shared__ unsigned char smem_raw[];
   const uint32_t smem_base = ((uint32_t)__cvta_generic_to_shared(smem_raw) + 1023u) & ~1023u;
-  float* red = reinterpret_cast<float*>(smem_raw + (smem_base - (uint32_t)__cvta_generic_to_shared(smem_raw)));  // [m][128], over the first stages
+  float* red = reinterpret_cast<float*>(smem_raw + (smem_base - (uint32_t)__cvta_generic_to_shared(smem_raw)));  // [P][m][128], over the first stages
   __shared__ __align__(8) uint64_t bars[2 * kSplitMaxStages + 1];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
@@ -782,7 +786,8 @@ __global__ void __launch_bounds__(192, 2)
   auto full_bar = [&](int s) { return bar0 + 8u * s; };
   auto empty_bar = [&](int s) { return bar0 + 8u * (kSplitMaxStages + s); };
   const uint32_t acc_full_bar = bar0 + 8u * (2 * kSplitMaxStages);
-  const uint32_t tmem_cols = ntok <= 32 ? 32u : 64u;
+  const uint32_t acc_cols = ntok <= 32 ? 32u : 64u;   // tensor-memory columns of one accumulator
+  const uint32_t tmem_cols = acc_cols * P;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x / split, r = blockIdx.x % split;  // the cluster's tile; this CTA's rank in the cluster
@@ -803,7 +808,7 @@ __global__ void __launch_bounds__(192, 2)
     // no kernel writes the weights: their loads start while the kernel that produces x is still running
     for (int kb = kb0; kb < kb1 && prologue < stages; ++kb, ++prologue) {
       mbar_expect_tx(full_bar(prologue), stage_bytes);
-      tma_load_2d(smem_base + prologue * stage_bytes, &tma_w, full_bar(prologue), kb * BK, t * 128);
+      tma_load_2d(smem_base + prologue * stage_bytes, &tma_w, full_bar(prologue), kb * BK, t * WR);
     }
     pdl_wait(7);
     for (int i = 0; i < prologue; ++i) tma_load_2d(smem_base + i * stage_bytes + stage_w, &tma_x, full_bar(i), (kb0 + i) * BK, 0);
@@ -831,7 +836,7 @@ __global__ void __launch_bounds__(192, 2)
         if (!(ok = mbar_wait(empty_bar(stage), phase ^ 1u, abortp, 1))) break;
         const uint32_t sw = smem_base + stage * stage_bytes;
         mbar_expect_tx(full_bar(stage), stage_bytes);
-        tma_load_2d(sw, &tma_w, full_bar(stage), kb * BK, t * 128);
+        tma_load_2d(sw, &tma_w, full_bar(stage), kb * BK, t * WR);
         tma_load_2d(sw + stage_w, &tma_x, full_bar(stage), kb * BK, 0);
         if (++stage == stages) {
           stage = 0;
@@ -854,6 +859,10 @@ __global__ void __launch_bounds__(192, 2)
 #pragma unroll
         for (int k = 0; k < BK / kUmmaK; ++k) {
           tcgen05_mma_f16(tmem_base, a_desc + (uint64_t)(2 * k), b_desc + (uint64_t)(2 * k), idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+          if constexpr (SWIGLU) {  // the up rows, 128 rows (16 KB) further down the stage
+            tcgen05_mma_f16(tmem_base + acc_cols, a_desc + (uint64_t)(2 * k) + (uint64_t)((128 * BK * 2) >> 4), b_desc + (uint64_t)(2 * k), idesc,
+                            (kb > kb0 || k > 0) ? 1u : 0u);
+          }
         }
         tcgen05_commit(empty_bar(stage));
         if (++stage == stages) {
@@ -871,12 +880,15 @@ __global__ void __launch_bounds__(192, 2)
     if (mbar_wait(acc_full_bar, 0u, abortp, 4)) {
       tcgen05_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(lane_group * 32) << 16);
-      for (int cb = 0; cb < ntok && cb < M; cb += 16) {
-        uint32_t v[16];
-        tcgen05_ld_32x32b_x16(taddr + cb, v);
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          if (cb + i < M) red[(cb + i) * 128 + row] = __uint_as_float(v[i]);
+      for (int p = 0; p < P; ++p) {
+        for (int cb = 0; cb < ntok && cb < M; cb += 16) {
+          uint32_t v[16];
+          tcgen05_ld_32x32b_x16(taddr + p * acc_cols + cb, v);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            if (cb + i < M) red[((p * M) + cb + i) * 128 + row] = __uint_as_float(v[i]);
+          }
         }
       }
     }
@@ -890,17 +902,28 @@ __global__ void __launch_bounds__(192, 2)
     const int etid = (warp - 2) * 32 + lane;
     const int lo = 128 * r / split, cnt = 128 * (r + 1) / split - lo;  // this CTA's share of the tile's rows
     const uint32_t red_addr = smem_base;
+    const int n_out = SWIGLU ? N / 2 : N;
     for (int idx = etid; idx < cnt * M; idx += 128) {
       const int m = idx / cnt, nl = lo + idx % cnt, n = t * 128 + nl;
-      float part[8];
+      float part[P][8];
 #pragma unroll
-      for (int rr = 0; rr < 8; ++rr) part[rr] = rr < split ? ld_dsmem_f32(red_addr + (uint32_t)(m * 128 + nl) * 4u, (uint32_t)rr) : 0.f;
-      float sum = part[0];
+      for (int p = 0; p < P; ++p) {
 #pragma unroll
-      for (int rr = 1; rr < 8; ++rr) {
-        if (rr < split) sum += part[rr];
+        for (int rr = 0; rr < 8; ++rr) {
+          part[p][rr] = rr < split ? ld_dsmem_f32(red_addr + (uint32_t)((p * M + m) * 128 + nl) * 4u, (uint32_t)rr) : 0.f;
+        }
       }
-      if (n < N) out[(size_t)m * ldo + n] = from_float<TOut>(sum);
+      float sum[P];
+#pragma unroll
+      for (int p = 0; p < P; ++p) {
+        sum[p] = part[p][0];
+#pragma unroll
+        for (int rr = 1; rr < 8; ++rr) {
+          if (rr < split) sum[p] += part[p][rr];
+        }
+      }
+      const float res = SWIGLU ? silu_f(sum[0]) * sum[P - 1] : sum[0];
+      if (n < n_out) out[(size_t)m * ldo + n] = from_float<TOut>(res);
     }
   }
   cluster_sync_unaligned();  // nobody leaves while another CTA still reads its shared memory
@@ -995,14 +1018,14 @@ static int launch_stream(const CUtensorMap& mw, const CUtensorMap& mx, void* out
 
 // CTAs of a cluster for the k-split product of an [n, k] weight: the most (up to 8) that still lets every cluster run at
 // once with two CTAs an SM and leaves every CTA at least two 64-wide blocks of k; 0 when the shape has too many tiles.
-static int split_for(int n, int k) {
+static int split_for(int n, int k, int tile_rows = 128) {
   static int sms = 0;
   if (sms == 0) {
     int dev = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   }
-  const int tiles = (n + 127) / 128, kbs = (k + BK - 1) / BK;
+  const int tiles = (n + tile_rows - 1) / tile_rows, kbs = (k + BK - 1) / BK;
   int split = (2 * sms) / tiles;
   if (split > 8) split = 8;
   if (split > kbs / 2) split = kbs / 2;
@@ -1012,20 +1035,21 @@ static int split_for(int n, int k) {
   return split >= 2 ? split : 0;
 }
 
-template <typename TOut>
+template <typename TOut, bool SWIGLU>
 static int launch_split(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int m, int n, int k, int64_t ldo, int ntok, int split,
                         cudaStream_t s) {
-  const int stages = ntok == 16 ? 6 : (ntok == 32 ? 5 : 4);
-  const size_t smem = (size_t)stages * (128 * BK * 2 + ntok * BK * 2) + 1024;
-  auto kernel = gemm_split_kernel<TOut>;
+  constexpr int WR = SWIGLU ? 256 : 128;
+  const int stages = SWIGLU ? 3 : (ntok == 16 ? 6 : (ntok == 32 ? 5 : 4));  // about 100 KB: two CTAs an SM
+  const size_t smem = (size_t)stages * (WR * BK * 2 + ntok * BK * 2) + 1024;
+  auto kernel = gemm_split_kernel<TOut, SWIGLU>;
   static bool attr_set[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64 || !attr_set[dev]) {
-    cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)((size_t)kSplitMaxStages * (128 * BK * 2 + 16 * BK * 2) + 1024));
+    cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024);
     if (dev >= 0 && dev < 64) attr_set[dev] = true;
   }
-  const int tiles = (n + 127) / 128;
+  const int tiles = (n + WR - 1) / WR;
   launch_kernel_cluster(kernel, dim3(tiles * split), dim3(192), smem, s, split, mw, mx, (TOut*)out, m, n, k, ldo, ntok, split, stages);
   return check_launch("gemm_split");
 }
@@ -1160,8 +1184,33 @@ extern "C" int roost_gemm_split(const void* x, const void* w, void* out, int m, 
   rc = make_map(&mx, x, m, k, ldx, ntok);
   if (rc != ROOST_OK) return rc;
   const int split = split_for(n, k);
-  if (out_dtype == ROOST_BF16) return launch_split<__nv_bfloat16>(mw, mx, out, m, n, k, ldo, ntok, split, (cudaStream_t)stream);
-  return launch_split<float>(mw, mx, out, m, n, k, ldo, ntok, split, (cudaStream_t)stream);
+  if (out_dtype == ROOST_BF16) return launch_split<__nv_bfloat16, false>(mw, mx, out, m, n, k, ldo, ntok, split, (cudaStream_t)stream);
+  return launch_split<float, false>(mw, mx, out, m, n, k, ldo, ntok, split, (cudaStream_t)stream);
+}
+
+extern "C" int roost_gemm_split_swiglu_supported(int m, int n, int k, int64_t ldx, int64_t ldw) {
+  return roost_gemm_stream_swiglu_supported(m, n, k, ldx, ldw) && split_for(n, k, 256) > 0;
+}
+
+// out[m, j] = silu(gate_j) * up_j for w's rows in blocks of 256 (128 gate rows, then the 128 up rows of the same outputs),
+// k split over thread-block clusters; out has n / 2 columns.
+extern "C" int roost_gemm_split_swiglu(const void* x, const void* w, void* out, int m, int n, int k, int64_t ldx, int64_t ldw, int64_t ldo,
+                                       int out_dtype, roost_stream_t stream) {
+  ROOST_REQUIRE(out_dtype == ROOST_BF16 || out_dtype == ROOST_F32, "gemm_split_swiglu: the output is bfloat16 (1) or float32 (0)");
+  ROOST_REQUIRE(ldx >= k && ldw >= k && ldo >= n / 2, "gemm_split_swiglu: a leading dimension is smaller than its row");
+  if (!roost_gemm_split_swiglu_supported(m, n, k, ldx, ldw)) {
+    return fail(ROOST_ERR_UNSUPPORTED, "gemm_split_swiglu: needs 1 <= m <= 32, n a multiple of 256, k and the row strides multiples of 8, and few enough tiles for clusters");
+  }
+  ROOST_REQUIRE(((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0), "gemm_split_swiglu: x and w must start on 16-byte boundaries");
+  const int ntok = m <= 16 ? 16 : 32;
+  CUtensorMap mw, mx;
+  int rc = make_map(&mw, w, n, k, ldw, 256);
+  if (rc != ROOST_OK) return rc;
+  rc = make_map(&mx, x, m, k, ldx, ntok);
+  if (rc != ROOST_OK) return rc;
+  const int split = split_for(n, k, 256);
+  if (out_dtype == ROOST_BF16) return launch_split<__nv_bfloat16, true>(mw, mx, out, m, n, k, ldo, ntok, split, (cudaStream_t)stream);
+  return launch_split<float, true>(mw, mx, out, m, n, k, ldo, ntok, split, (cudaStream_t)stream);
 }
 
 extern "C" int roost_gemm_stream_swiglu_supported(int m, int n, int k, int64_t ldx, int64_t ldw) {

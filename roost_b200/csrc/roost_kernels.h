@@ -17,7 +17,7 @@
 extern "C" {
 #endif
 
-#define ROOST_ABI_VERSION 8
+#define ROOST_ABI_VERSION 9
 
 #define ROOST_OK 0
 #define ROOST_ERR_INVALID 1      /* an argument is out of range or inconsistent; nothing was launched */
@@ -200,6 +200,11 @@ int roost_gemm_split_supported(int m, int n, int k, int64_t ldx, int64_t ldw);
 int roost_gemm_split_preferred(int m, int n, int k, int64_t ldx, int64_t ldw);  /* measured faster than the other products */
 int roost_gemm_split(const void* x, const void* w, void* out, int m, int n, int k, int64_t ldx, int64_t ldw, int64_t ldo,
                      int out_dtype, roost_stream_t stream);
+/* The k-split product with the SwiGLU of the fused product: w's rows in blocks of 256 (128 gate rows, then the 128 up
+ * rows of the same outputs), out[m, j] = silu(gate_j) * up_j with n / 2 columns; at most 32 rows of x. */
+int roost_gemm_split_swiglu_supported(int m, int n, int k, int64_t ldx, int64_t ldw);
+int roost_gemm_split_swiglu(const void* x, const void* w, void* out, int m, int n, int k, int64_t ldx, int64_t ldw, int64_t ldo,
+                            int out_dtype, roost_stream_t stream);
 /* The same with the SwiGLU of the fused product: w's rows in blocks of 256 (128 gate rows, then the 128 up rows of the
  * same outputs), out[m, j] = silu(gate_j) * up_j with n / 2 columns; at most 32 rows of x, n a multiple of 256. */
 int roost_gemm_stream_swiglu_supported(int m, int n, int k, int64_t ldx, int64_t ldw);

@@ -13,7 +13,7 @@ import torch
 
 from . import build
 
-ABI_VERSION = 8
+ABI_VERSION = 9
 F32, BF16 = 0, 1
 
 
@@ -89,6 +89,8 @@ _SIGNATURES = {
     "roost_gemm_stream_supported": [c_int, c_int, c_int, c_int64, c_int64],
     "roost_gemm_split_supported": [c_int, c_int, c_int, c_int64, c_int64],
     "roost_gemm_split_preferred": [c_int, c_int, c_int, c_int64, c_int64],
+    "roost_gemm_split_swiglu_supported": [c_int, c_int, c_int, c_int64, c_int64],
+    "roost_gemm_split_swiglu": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int, c_void_p],
     "roost_gemm_split": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int, c_void_p],
     "roost_gemm_stream": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int, c_void_p, c_void_p,
                           c_void_p],
@@ -396,6 +398,23 @@ class KernelLibrary:
         out_dtype = out_dtype or torch.bfloat16
         out = torch.empty((M, N), dtype=out_dtype, device=x.device)
         self._call("roost_gemm_split", _ptr(x), _ptr(w), _ptr(out), M, N, K, x.stride(0), w.stride(0), out.stride(0),
+                   dtype_code(out_dtype), _stream())
+        return out
+
+    def gemm_split_swiglu_supported(self, m: int, n: int, k: int, ldx: int, ldw: int) -> bool:
+        return bool(self._lib.roost_gemm_split_swiglu_supported(m, n, k, ldx, ldw))
+
+    def gemm_split_swiglu(self, x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+        """silu(x Wg^T) * (x Wu^T) for x [M <= 32, K] and w [2I, K] with gate and up rows interleaved in blocks of 128:
+        the k-split product with the activation applied to the summed accumulators; returns [M, I]."""
+        _need(x, "x", torch.bfloat16); _need(w, "w", torch.bfloat16)
+        M, K = x.shape
+        N, K2 = w.shape
+        if K != K2:
+            raise KernelError(f"gemm_split_swiglu: x has {K} columns, w has {K2}")
+        out_dtype = out_dtype or torch.bfloat16
+        out = torch.empty((M, N // 2), dtype=out_dtype, device=x.device)
+        self._call("roost_gemm_split_swiglu", _ptr(x), _ptr(w), _ptr(out), M, N, K, x.stride(0), w.stride(0), out.stride(0),
                    dtype_code(out_dtype), _stream())
         return out
 

@@ -127,6 +127,10 @@ def gemm_small(k, a) -> None:
         if k.gemm_split_supported(a.rows, n, kk, kk, kk):
             t_split = _graph_time([(lambda w=w: k.gemm_split(x, w)) for w in ws], a.warmup, a.iters)
             split = f"k split over clusters {t_split:.1f} us ({n * kk * 2 / t_split / 1e6:.2f} TB/s), "
+        if n % 256 == 0 and k.gemm_split_swiglu_supported(a.rows, n, kk, kk, kk):
+            t_sw = _graph_time([(lambda w=w: k.gemm_split_swiglu(x, w)) for w in ws], a.warmup, a.iters)
+            t_two = _graph_time([(lambda w=w: k.silu_mul(torch.matmul(x, w.t()), 128)) for w in ws], a.warmup, a.iters)
+            split += f"k split with SiLU x up {t_sw:.1f} us (cuBLAS and the SiLU kernel {t_two:.1f} us), "
         print(f"gemm-small rows={a.rows} n={n} k={kk}: stream {t_stream:.1f} us ({n * kk * 2 / t_stream / 1e6:.2f} TB/s of weights), {split}"
               f"cuBLAS {t_lib:.1f} us, in one graph back to back; status {k.gemm_tcgen05_status()}", flush=True)
 

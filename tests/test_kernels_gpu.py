@@ -604,6 +604,27 @@ def test_gemm_tcgen05_swiglu(kernels, m, inter, k):
     close(two, want, torch.bfloat16, "library product + silu_mul on the interleaved layout", scale=2)
 
 
+@pytest.mark.parametrize("m,inter,k", [(1, 128, 256), (8, 384, 200), (8, 12288, 4096), (16, 3072, 1024), (23, 1280, 2560)])
+def test_gemm_split_swiglu(kernels, m, inter, k):
+    """The k-split product with the activation on the summed accumulators: gate and up of an output in two accumulators
+    that share x, both summed over the cluster before silu(gate) * up; repeatable and independent of the batch."""
+    assert kernels.gemm_split_swiglu_supported(m, 2 * inter, k, k, k)
+    a = rand((m, k), torch.bfloat16, 56)
+    gate = rand((inter, k), torch.bfloat16, 57, 1 / math.sqrt(k))
+    up = rand((inter, k), torch.bfloat16, 58, 1 / math.sqrt(k))
+    w = torch.stack([gate.reshape(inter // 128, 128, k), up.reshape(inter // 128, 128, k)], dim=1).reshape(2 * inter, k).contiguous()
+    got = kernels.gemm_split_swiglu(a, w)
+    assert kernels.gemm_tcgen05_status() == 0, "a bounded wait inside the kernel was given up"
+    ad = a.double().cpu()
+    want = plain.silu_and_mul(ad @ gate.double().cpu().T, ad @ up.double().cpu().T)
+    close(got, want, torch.bfloat16, "gemm_split_swiglu")
+    assert torch.equal(kernels.gemm_split_swiglu(a, w), got), "the product is not repeatable"
+    r = m // 2
+    assert torch.equal(kernels.gemm_split_swiglu(a[r : r + 1].contiguous(), w), got[r : r + 1]), "a row depends on its batch"
+    assert not kernels.gemm_split_swiglu_supported(33, 2 * inter, k, k, k) and not kernels.gemm_split_swiglu_supported(m, 2 * inter + 128, k, k, k)
+    assert not kernels.gemm_split_swiglu_supported(m, 2 * 25600, 5120, 5120, 5120)      # too many tiles for clusters that all run at once
+
+
 @pytest.mark.parametrize("m,inter,k", [(1, 128, 64), (8, 384, 96), (8, 12288, 4096), (16, 3072, 1024), (23, 1280, 2560)])
 def test_gemm_stream_swiglu(kernels, m, inter, k):
     """The weight-streaming product with the activation on its accumulators: gate and up of an output in one row of tensor
