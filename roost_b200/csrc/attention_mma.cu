@@ -635,6 +635,7 @@ __global__ void __launch_bounds__(NWARPS * 32)
 constexpr int kTmaTileKeys = 32;
 constexpr int kTmaConsumers = 4;
 constexpr int kTmaMergeRows = 2;  // packed rows merged per pass
+constexpr int kEarlyTiles = 2;    // tiles of a CTA's first chunk whose copies are issued before the wait for the kernel in front
 
 // A tile of TK keys as the copies leave it: [page of RPC rows][K, V][D / 64 column blocks][RPC][64 bfloat16], 128-byte
 // swizzle, 1024-byte aligned. offset() is relative to the tile's keys; the values follow at kValues.
@@ -782,9 +783,15 @@ __global__ void __launch_bounds__((kTmaConsumers + 1) * 32, 2)
         }
       }
     };
+#ifdef ROOST_TRACE
+    unsigned long long trp[7] = {trace_now(), 0, 0, 0, 0, 0, 0};
+#endif
     round1();
     round2();
     round3();
+#ifdef ROOST_TRACE
+    trp[1] = trace_now();   // the first chunk's tables are known
+#endif
     for (int k = 0; ok; ++k) {
       const DecodeChunk c = nc;
       const int fallback = n_fallback;
@@ -842,26 +849,49 @@ __global__ void __launch_bounds__((kTmaConsumers + 1) * 32, 2)
         // the CTA's first chunk, when it lies wholly before the step's own tokens: its first tiles are on their way
         // before the kernel in front has finished
         if (c.b >= 0 && c.hi < c.kv_len - c.n) {
-          const int early = c.ntiles < STAGES ? c.ntiles : STAGES;
+          // (a tile's copies take the issuing lane about 0.3 us, and the consumers cannot begin before the descriptor and Q,
+          // which follow the wait: two tiles are as much as fits before the kernel in front is usually done)
+          const int early = c.ntiles < kEarlyTiles ? c.ntiles : kEarlyTiles;
           for (; issued < early && ok; ++issued) issue(issued);
         }
+#ifdef ROOST_TRACE
+        trp[4] = trace_now();   // the early copies are issued
+#endif
         pdl_wait(4);
+#ifdef ROOST_TRACE
+        trp[5] = trace_now();   // the kernel in front has finished
+#endif
       }
       if (lane == 0 && k >= 2) ok = mbar_wait_limited(desc_empty(k & 1), (uint32_t)((k >> 1) - 1) & 1u, abortp, 4, &g_attention_error);
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
       if (!ok) break;
       // the chunk's Q tile, then the descriptor: the barrier completes when both are in shared memory
       if (c.b >= 0) load_q_tile<D, 16, 32>(q_smem + (k & 1) * kQBytes, q, c.q_start, q_heads, group, c.kvh, 0, c.n * group, lane);
+#ifdef ROOST_TRACE
+      if (k == 0) trp[6] = trace_now();   // the copies of Q are issued
+#endif
       asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];\n" ::"r"(desc_full(k & 1)) : "memory");
       if (lane == 0) {
         desc[k & 1] = c;
         mbar_arrive(desc_full(k & 1));  // releases the descriptor to the consumers
       }
       if (c.b < 0) break;
+#ifdef ROOST_TRACE
+      if (k == 0) trp[2] = trace_now();   // the descriptor and Q are on their way
+#endif
       for (int i = issued; i < c.ntiles && ok; ++i) issue(i);
+#ifdef ROOST_TRACE
+      if (k == 0) trp[3] = trace_now();   // the chunk's last copy is issued
+#endif
       if (rounds < 2) round2();
       if (rounds < 3) round3();
     }
+#ifdef ROOST_TRACE
+    if (lane == 0 && (blockIdx.x & 7) == 0) {
+      trace_flush(4 * 4 + 3, blockIdx.x * 16, trp, 4);
+      trace_flush(4 * 4 + 3, blockIdx.x * 16 + 10, trp + 4, 3);
+    }
+#endif
     if (*abortp) {  // copies in flight land before the CTA's shared memory is given back
       const long long c0 = clock64();
       while (clock64() - c0 < 2000000LL) __nanosleep(256);
@@ -873,12 +903,18 @@ __global__ void __launch_bounds__((kTmaConsumers + 1) * 32, 2)
   pdl_wait(4);
   bool ok = true;
   int g0 = 0;  // tiles of the chunks before this one
+#ifdef ROOST_TRACE
+  unsigned long long trc[6] = {0, 0, 0, 0, 0, 0};
+#endif
   bool seen = false;  // this thread has read the CTA's first descriptor (with clusters its only one: desc[0] stays as it is)
   for (int k = 0; ok; ++k) {
     if (!(ok = mbar_wait_limited(desc_full(k & 1), (uint32_t)(k >> 1) & 1u, abortp, 5, &g_attention_error))) break;
     const DecodeChunk c = desc[k & 1];
     seen = true;
     if (c.b < 0) break;
+#ifdef ROOST_TRACE
+    if (k == 0) trc[0] = trace_now();   // descriptor and Q here
+#endif
     const int rows_total = c.n * group;  // at most 16
     const int pos0 = c.kv_len - c.n;
     uint32_t qf[D / 16][4];
@@ -934,6 +970,9 @@ __global__ void __launch_bounds__((kTmaConsumers + 1) * 32, 2)
       if (lane == 0) mbar_arrive(empty_bar(stage));
     }
     g0 += c.ntiles;
+#ifdef ROOST_TRACE
+    if (k == 0) trc[1] = trace_now();   // this warp's tiles are done
+#endif
 
     // merge the warps' states through shared memory (in warp order), MR packed rows a pass, and write the chunk's result
     for (int r0 = 0; r0 < rows_total; r0 += MR) {
@@ -993,6 +1032,9 @@ __global__ void __launch_bounds__((kTmaConsumers + 1) * 32, 2)
       asm volatile("bar.sync 1, %0;\n" ::"n"(NW * 32) : "memory");  // the scratch (and the Q tile) may be written again
     }
   }
+#ifdef ROOST_TRACE
+  trc[2] = trace_now();   // the CTA's result is in shared memory (or memory)
+#endif
   const bool cl_padding = seen && desc[0].b < 0;  // the cluster's items are padding: all its CTAs leave at once
   if (cluster_chunks > 0 && !cl_padding) {
     const int cl_rows = seen ? desc[0].n * group : 0, cl_q_start = desc[0].q_start, cl_kvh = desc[0].kvh;
@@ -1000,6 +1042,9 @@ __global__ void __launch_bounds__((kTmaConsumers + 1) * 32, 2)
     // CTA whose wait was given up included: its numbers are wrong (or, if it never saw its item, it merges nothing), the
     // fault is recorded, and nobody is left waiting or reads the shared memory of a CTA that has gone.
     decode_cluster_sync();  // the results of all the cluster's CTAs are in their shared memory
+#ifdef ROOST_TRACE
+    trc[3] = trace_now();
+#endif
     {  // every CTA of the cluster combines its share of the row's values
       constexpr int kMaxCluster = 8;
       const uint32_t o_addr = smem_base, ml_addr = smem_base + 16 * D * 4;
@@ -1032,7 +1077,14 @@ __global__ void __launch_bounds__((kTmaConsumers + 1) * 32, 2)
         out[((size_t)(cl_q_start + row / group) * q_heads + cl_kvh * group + row % group) * D + col] = __float2bfloat16_rn(o * inv);
       }
     }
+#ifdef ROOST_TRACE
+    trc[4] = trace_now();
+#endif
     decode_cluster_sync();  // nobody leaves while another CTA still reads its shared memory
+#ifdef ROOST_TRACE
+    trc[5] = trace_now();
+    if (tid == 0 && (blockIdx.x & 7) == 0) trace_flush(4 * 4 + 3, blockIdx.x * 16 + 4, trc, 6);
+#endif
   }
   if (!ok) {  // a copy that was waited for in vain may still land
     const long long c0 = clock64();

@@ -826,6 +826,10 @@ __global__ void __launch_bounds__(192, 2)
   tcgen05_fence_after();
   const uint32_t tmem_base = tmem_base_slot;
   volatile int* abortp = &abort_flag;
+#ifdef ROOST_TRACE
+  unsigned long long tr[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  tr[0] = trace_now();   // set-up done: barriers, tensor memory, the CTA-wide barrier
+#endif
 
   if (warp == 0) {
     if (lane == 0) {
@@ -853,6 +857,9 @@ __global__ void __launch_bounds__(192, 2)
       for (int kb = kb0; kb < kb1 && ok; ++kb) {
         if (!(ok = mbar_wait(full_bar(stage), phase, abortp, 3))) break;
         tcgen05_fence_after();
+#ifdef ROOST_TRACE
+        if (kb == kb0) tr[1] = trace_now();   // the first stage has landed
+#endif
         const uint32_t sw = smem_base + stage * stage_bytes;
         const uint64_t a_desc = umma_desc_k_major_sw128(sw);
         const uint64_t b_desc = umma_desc_k_major_sw128(sw + stage_w);
@@ -871,6 +878,10 @@ __global__ void __launch_bounds__(192, 2)
         }
       }
       if (ok) tcgen05_commit(acc_full_bar);
+#ifdef ROOST_TRACE
+      tr[2] = trace_now();                    // the last products are issued
+      if ((blockIdx.x & 7) == 0) trace_flush(7 * 4 + 3, blockIdx.x * 16, tr, 3);
+#endif
     }
   } else {
     // the accumulator (out transposed: a lane of tensor memory is a row of the tile, a column a row of x) into this CTA's
@@ -879,6 +890,9 @@ __global__ void __launch_bounds__(192, 2)
     const int row = lane_group * 32 + lane;
     if (mbar_wait(acc_full_bar, 0u, abortp, 4)) {
       tcgen05_fence_after();
+#ifdef ROOST_TRACE
+      tr[3] = trace_now();                    // the accumulator is complete
+#endif
       const uint32_t taddr = tmem_base + ((uint32_t)(lane_group * 32) << 16);
 #pragma unroll
       for (int p = 0; p < P; ++p) {
@@ -897,7 +911,13 @@ __global__ void __launch_bounds__(192, 2)
   // Every thread of every CTA of the cluster comes here, whatever its waits returned: nobody is left waiting at the
   // cluster's barriers and nobody reads the shared memory of a CTA that has gone.
   __syncwarp();
+#ifdef ROOST_TRACE
+  tr[4] = trace_now();                        // the partial sums are in shared memory
+#endif
   cluster_sync_unaligned();  // the partial sums of all the cluster's CTAs are in their shared memory
+#ifdef ROOST_TRACE
+  tr[5] = trace_now();
+#endif
   if (warp >= 2) {
     const int etid = (warp - 2) * 32 + lane;
     const int lo = 128 * r / split, cnt = 128 * (r + 1) / split - lo;  // this CTA's share of the tile's rows
@@ -926,7 +946,15 @@ __global__ void __launch_bounds__(192, 2)
       if (n < n_out) out[(size_t)m * ldo + n] = from_float<TOut>(res);
     }
   }
+#ifdef ROOST_TRACE
+  tr[6] = trace_now();                        // this CTA's share is written
+#endif
   cluster_sync_unaligned();  // nobody leaves while another CTA still reads its shared memory
+#ifdef ROOST_TRACE
+  tr[7] = trace_now();
+  if (threadIdx.x == 64 && (blockIdx.x & 7) == 0) trace_flush(7 * 4 + 3, blockIdx.x * 16 + 3, tr + 3, 5);
+#endif
+  trace_point(7, 2);
   if (*abortp) {
     const long long t0 = clock64();
     while (clock64() - t0 < 2000000LL) __nanosleep(256);
