@@ -33,11 +33,12 @@ class CacheGroup:
     window: int | None = None      # keys a query sees, its own included; None = all
     kv_heads: int = 0
     head_dim: int = 0
+    planes: int = 2                # tensors kept per token: keys and values, or one
     state_shape: tuple = ()
     state_dtype: torch.dtype = torch.float32
 
     def bytes_per_page(self, element_size: int) -> int:
-        return 2 * len(self.runs) * self.page_size * self.kv_heads * self.head_dim * element_size
+        return self.planes * len(self.runs) * self.page_size * self.kv_heads * self.head_dim * element_size
 
 
 def leading_releasable_pages(tokens: int, window: int, page_size: int) -> int:
@@ -198,7 +199,7 @@ class CacheManager:
 
 def build_groups(needs: list, page_size: int) -> list[CacheGroup]:
     """Sorts the schedule's runs into groups. ``needs[i]`` is the ``CacheNeed`` of run i, or None when the run
-    keeps nothing or reads another run's cache. Paged runs with the same (window, kv_heads, head_dim) share a
+    keeps nothing or reads another run's cache. Paged runs with the same (window, kv_heads, head_dim, planes) share a
     group; every state run with the same shape and dtype shares one. A group of fixed-size state always exists,
     with no runs and a zero-sized state when the model has none, so that slots are handed out and returned on
     every path."""
@@ -208,16 +209,18 @@ def build_groups(needs: list, page_size: int) -> list[CacheGroup]:
         if need is None:
             continue
         if need.kind == "paged":
-            paged.setdefault((need.window, need.kv_heads, need.head_dim), []).append(i)
+            if need.planes not in (1, 2):
+                raise ValueError(f"run {i} asks for {need.planes} tensors a token; a paged cache keeps 1 or 2")
+            paged.setdefault((need.window, need.kv_heads, need.head_dim, need.planes), []).append(i)
         elif need.kind == "state":
             state.setdefault((tuple(need.state_shape), need.state_dtype), []).append(i)
         else:
             raise ValueError(f"run {i} asks for a cache of kind '{need.kind}'")
     groups = []
-    for (window, kvh, d), runs in paged.items():
-        name = ("full" if window is None else f"window{window}") + f"_h{kvh}d{d}"
+    for (window, kvh, d, planes), runs in paged.items():
+        name = ("full" if window is None else f"window{window}") + f"_h{kvh}d{d}" + ("" if planes == 2 else f"x{planes}")
         groups.append(CacheGroup(name=name, kind="paged", runs=tuple(runs), page_size=page_size, window=window,
-                                 kv_heads=kvh, head_dim=d))
+                                 kv_heads=kvh, head_dim=d, planes=planes))
     for (shape, dt), runs in state.items():
         groups.append(CacheGroup(name="state" + "x".join(map(str, shape)), kind="state", runs=tuple(runs),
                                  state_shape=shape, state_dtype=dt))

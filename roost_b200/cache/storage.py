@@ -1,6 +1,7 @@
 """Device memory of the cache groups.
 
-A paged group is one tensor [runs, 2, pages, kv_heads, page_size, head_dim] in the compute dtype: a page id
+A paged group is one tensor [runs, planes, pages, kv_heads, page_size, head_dim] in the compute dtype (planes: keys and
+values, or the one tensor of a group whose mixers keep a single vector a token): a page id
 addresses the page of every run in the group, as the reference's "bytes per block across all layers" does
 (src/Starlings.Roost.Abstractions/State/StateGroups.cs:83-84); within a page the layout is head-major so that
 one head's keys of a page are contiguous. A state group is one tensor [runs, slots + 1, *state_shape]: the last slot
@@ -21,7 +22,7 @@ class CacheView:
     group: int                        # index of the group: selects the batch's tables
     kind: str
     page_size: int = 0
-    k_pool: torch.Tensor | None = None   # [pages, kv_heads, page_size, head_dim]
+    k_pool: torch.Tensor | None = None   # [pages, kv_heads, page_size, head_dim]; the only pool of a group with one plane
     v_pool: torch.Tensor | None = None
     state: torch.Tensor | None = None    # [slots, *state_shape]
 
@@ -33,9 +34,10 @@ class CacheStorage:
         self._view_of_run: dict[int, CacheView] = {}
         for gi, (g, cap) in enumerate(zip(groups, capacities)):
             if g.kind == "paged":
-                t = torch.zeros((max(len(g.runs), 1), 2, cap, g.kv_heads, g.page_size, g.head_dim), dtype=dtype, device=device)
+                t = torch.zeros((max(len(g.runs), 1), g.planes, cap, g.kv_heads, g.page_size, g.head_dim), dtype=dtype, device=device)
                 for li, run in enumerate(g.runs):
-                    self._view_of_run[run] = CacheView(group=gi, kind="paged", page_size=g.page_size, k_pool=t[li, 0], v_pool=t[li, 1])
+                    self._view_of_run[run] = CacheView(group=gi, kind="paged", page_size=g.page_size, k_pool=t[li, 0],
+                                                       v_pool=t[li, 1] if g.planes == 2 else None)
             else:
                 # one slot more than the pool hands out: the scratch slot that the padding rows of a captured step name
                 t = torch.zeros((max(len(g.runs), 1), cap + 1, *g.state_shape), dtype=g.state_dtype, device=device)

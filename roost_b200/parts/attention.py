@@ -80,7 +80,10 @@ class PagedAttention(Mixer):
         eps = s.qk_norm.eps if s.qk_norm is not None else 1.0
         qw = self.q_norm.weight if self.q_norm is not None else None
         kw = self.k_norm.weight if self.k_norm is not None else None
-        table = batch.rotation_table(k, inv_freq) if rotary_dim else None
+        own_table = getattr(self.position, "step_table", None) if rotary_dim else None
+        table = own_table(batch) if own_table is not None else None     # an encoding with angles of its own
+        if table is None and rotary_dim:
+            table = batch.rotation_table(k, inv_freq)
         if write_cache:
             qkv = self.qkv(x)
             q = k.qk_norm_rope_cache(qkv, s.num_heads, s.num_kv_heads, s.head_dim, q_w=qw, k_w=kw, eps=eps,

@@ -33,13 +33,15 @@ class ParamDecl:
 
 @dataclass(frozen=True)
 class CacheNeed:
-    """What one run of a mixer keeps between steps. ``paged``: keys and values, ``kv_heads`` x ``head_dim``
-    per token, every earlier token (window None) or the last ``window`` tokens. ``state``: one tensor of
-    ``state_shape`` per live request, zeroed when the request's first token arrives."""
+    """What one run of a mixer keeps between steps. ``paged``: ``planes`` tensors of ``kv_heads`` x ``head_dim`` per
+    token (2: keys and values; 1: one vector a token, a latent from which a mixer makes both), every earlier token
+    (window None) or the last ``window`` tokens. ``state``: one tensor of ``state_shape`` per live request, zeroed when
+    the request's first token arrives."""
     kind: str                       # "paged" | "state"
     kv_heads: int = 0
     head_dim: int = 0
     window: int | None = None
+    planes: int = 2
     state_shape: tuple = ()
     state_dtype: torch.dtype = torch.float32
 

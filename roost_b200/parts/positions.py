@@ -4,7 +4,9 @@ The attention mixer's fused kernel rotates the first ``rotary_dim`` elements of 
 the angle position * inv_freq[i], pairing element i with i + rotary_dim/2 (NeoX form,
 src/Starlings.Roost.Ops/CpuOps.cs:111-177). A position encoding therefore hands the mixer a table of
 frequencies in double precision and a rotary width; ``rotary_dim`` 0 means no rotation. Frequency-scaled
-variants are other tables behind the same interface.
+variants are other tables behind the same interface. An encoding whose angles are not position x frequency (several
+position axes, angles looked up in a table) gives the step's cosines and sines itself (``step_table``); the pairing of
+elements stays the kernel's.
 """
 from __future__ import annotations
 
@@ -18,6 +20,12 @@ class PositionEncoding(Part):
     def rotation(self) -> tuple[torch.Tensor | None, int]:
         """(inv_freq: float64 [rotary_dim / 2] on the device, rotary_dim)."""
         raise NotImplementedError
+
+    def step_table(self, batch) -> torch.Tensor | None:
+        """Optional: the cosines and sines of this step's tokens, float32 [T, rotary_dim / 2, 2] on the device, made from
+        the step's device tables (``batch.positions``: -1 for the padding tokens of a captured step). None (the default):
+        the kernels form position * inv_freq themselves."""
+        return None
 
     max_positions: int = 0  # 0: unbounded
 

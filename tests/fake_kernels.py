@@ -51,8 +51,11 @@ class FakeKernels:
             if not rotary_dim:
                 return x
             half = rotary_dim // 2
-            ang = positions.double()[:, None] * inv_freq[None, :]
-            c, s = torch.cos(ang)[:, None, :].float(), torch.sin(ang)[:, None, :].float()
+            if cos_sin is not None:     # the step's own table of cosines and sines [T, half, 2]
+                c, s = cos_sin[:, None, :, 0].float(), cos_sin[:, None, :, 1].float()
+            else:
+                ang = positions.double()[:, None] * inv_freq[None, :]
+                c, s = torch.cos(ang)[:, None, :].float(), torch.sin(ang)[:, None, :].float()
             x1, x2 = x[..., :half], x[..., half:rotary_dim]
             out = x.clone()
             out[..., :half] = x1 * c - x2 * s

@@ -130,3 +130,10 @@ def test_groups_are_built_from_what_the_runs_need():
     # the fixed-size state group is always there, empty for a model without such state, so slots are handed out on every path
     assert [(x.kind, x.runs, x.state_shape) for x in g] == [("paged", (0, 1), ()), ("state", (), (0,))]
     assert g[0].bytes_per_page(2) == 2 * 2 * 16 * 2 * 16 * 2
+    # a run that keeps one tensor a token (a latent) gets a group of its own, half the bytes a page
+    latent = CacheNeed("paged", kv_heads=2, head_dim=16, planes=1)
+    g = build_groups([full, latent, latent], page_size=16)
+    assert [(x.kind, x.runs, x.planes) for x in g[:2]] == [("paged", (0,), 2), ("paged", (1, 2), 1)]
+    assert g[1].bytes_per_page(2) == 1 * 2 * 16 * 2 * 16 * 2
+    with pytest.raises(ValueError):
+        build_groups([CacheNeed("paged", kv_heads=2, head_dim=16, planes=3)], page_size=16)

@@ -397,6 +397,127 @@ def test_a_toy_mixer_with_its_own_state_is_registered_built_and_stepped(backend,
     assert ex.cache.pools[1].free_count == 3
 
 
+# ------------------------------------------------------------------------------------------ a toy mixer with a latent in pages
+@dataclass(frozen=True)
+class ToyLatentSpec(MixerSpec):
+    kind: str = "toy_latent_mean"
+    hidden: int = 0
+    latent: int = 0
+    window: int | None = None
+
+
+class ToyLatentMean(Mixer):
+    """Keeps ONE vector a token in the paged cache (c_t = x_t Wc^T, `latent` wide: a cache group of one plane) and gives
+    out the mean of the cached vectors a token sees (all earlier ones and its own, or the last `window`), projected back:
+    out_t = mean_s(c_s) Wo^T. Written with host loops over the step's tables, so its model's steps run eagerly."""
+    capturable = False
+
+    def __init__(self, spec, rt):
+        self.spec, self.rt = spec, rt
+        self.down = Linear(rt, spec.latent, spec.hidden)
+        self.up = Linear(rt, spec.hidden, spec.latent)
+
+    @classmethod
+    def parameters(cls, spec):
+        return {"down": ParamDecl(shape=(spec.latent, spec.hidden)), "up": ParamDecl(shape=(spec.hidden, spec.latent))}
+
+    def load(self, params):
+        self.down.load(params["down"])
+        self.up.load(params["up"])
+
+    def cache_need(self):
+        return CacheNeed("paged", kv_heads=1, head_dim=self.spec.latent, window=self.spec.window, planes=1)
+
+    def __call__(self, x, batch, cache, write_cache=True):
+        assert cache.v_pool is None and cache.k_pool.shape[1:] == (1, cache.page_size, self.spec.latent)
+        tables = batch.groups[cache.group]
+        c = self.down(x)
+        pool = cache.k_pool.view(-1, self.spec.latent)                     # [pages * page_size, latent]: slot = page * page_size + offset
+        if write_cache:
+            pool[tables.slot_mapping.long()] = c
+        indptr, pages = tables.kv_indptr.tolist(), tables.kv_indices.tolist()
+        P, out, at = cache.page_size, [], 0
+        for b, n in enumerate(batch.row_counts):
+            kv_len = int(batch.kv_lens[b])
+            mine = pages[indptr[b]:indptr[b + 1]]
+            for i in range(n):
+                pos = kv_len - n + i
+                lo = max(0, pos - self.spec.window + 1) if self.spec.window else 0
+                slots = [mine[j // P] * P + j % P for j in range(lo, pos + 1)]
+                assert min(slots) >= 0, "a page the window has passed was read"
+                out.append(pool[torch.tensor(slots, device=pool.device)].float().mean(0))
+            at += n
+        return self.up(torch.stack(out).to(x.dtype))
+
+
+@pytest.mark.parametrize("window", [None, 6])
+def test_a_toy_mixer_that_keeps_one_latent_vector_a_token_in_pages(backend, window):
+    """A paged cache group need not hold keys and values: a mixer asks for one plane, gets pages, block tables and slots
+    from the same cache manager (window release included) and shares nothing with the attention layer's group."""
+    register_mixer("toy_latent_mean", ToyLatentMean)
+    rt = runtime(backend)
+    H_, V, I, L = 32, 40, 48, 24
+    norm = NormSpec(size=H_, eps=1e-6)
+    attn = AttentionSpec(hidden=H_, num_heads=2, num_kv_heads=1, head_dim=16, scale=0.25, qk_norm=None,
+                         position=PositionSpec(rotary_dim=16, theta=100.0))
+    ff = GatedMlpSpec(hidden=H_, intermediate=I)
+    blocks = (BlockSpec(mixer=ToyLatentSpec(hidden=H_, latent=L, window=window), feed_forward=ff, input_norm=norm, post_mixer_norm=norm),
+              BlockSpec(mixer=attn, feed_forward=ff, input_norm=norm, post_mixer_norm=norm))
+    spec = ModelSpec(architecture="ToyLatentForTests", hidden=H_, vocab=V, blocks=blocks, schedule=(RunEntry(0), RunEntry(1)),
+                     final_norm=norm, tie_embeddings=True, max_positions=0)
+    model = Model(spec, rt)
+    g = torch.Generator().manual_seed(13)
+    params = {}
+    for scope, decl in parameter_declarations(spec).items():
+        params[scope] = {k: (torch.ones(d.shape) if d.role == "vector" else torch.randn(d.shape, generator=g) * 0.2).to(rt.dtype) for k, d in decl.items()}
+    model.load(params)
+    ex = StepExecutor(model, page_size=4, num_pages=24, max_requests=3)
+    kinds = [(g_.kind, g_.planes if g_.kind == "paged" else 0, g_.window, g_.runs) for g_ in ex.groups]
+    assert kinds[:2] == [("paged", 1, window, (0,)), ("paged", 2, None, (1,))] and not ex.use_graphs
+    assert ex.storage.tensors[0].shape[:2] == (1, 1) and ex.storage.tensors[1].shape[:2] == (1, 2)
+
+    def plain_forward(ids):
+        P = {s_: {k: v.double() for k, v in p_.items()} for s_, p_ in params.items()}
+        h = P["embed"]["table"][torch.tensor(ids)]
+        pos = list(range(len(ids)))
+        for bi in (0, 1):
+            x = plain.rms_norm(h, P[f"blocks.{bi}.input_norm"]["weight"], 1e-6)
+            if bi == 0:
+                c = x @ P["blocks.0.mixer"]["down"].T
+                if rt.dtype == torch.bfloat16:
+                    c = c.to(torch.bfloat16).double()       # the cache holds the latent in the compute dtype
+                means = torch.stack([c[max(0, t - window + 1) if window else 0 : t + 1].mean(0) for t in pos])
+                mix = means @ P["blocks.0.mixer"]["up"].T
+            else:
+                qkv = P["blocks.1.mixer"]["qkv"]
+                q = plain.rope_neox((x @ qkv[:32].T).reshape(-1, 2, 16), pos, 100.0)
+                k = plain.rope_neox((x @ qkv[32:48].T).reshape(-1, 1, 16), pos, 100.0)
+                v = (x @ qkv[48:].T).reshape(-1, 1, 16)
+                mix = plain.causal_gqa_attention(q, k, v, 0.25).reshape(-1, 32) @ P["blocks.1.mixer"]["out"].T
+            h = h + mix
+            y = plain.rms_norm(h, P[f"blocks.{bi}.post_mixer_norm"]["weight"], 1e-6)
+            gu = P[f"blocks.{bi}.feed_forward"]["gate_up"]
+            h = h + plain.swiglu_mlp(y, gu[:I], gu[I:], P[f"blocks.{bi}.feed_forward"]["down"])
+        return plain.rms_norm(h, P["final_norm"]["weight"], 1e-6) @ P["embed"]["table"].T
+
+    a, b = H.random_ids(26, V, 5), H.random_ids(17, V, 6)
+    bound = 2e-5 if rt.full_precision else H.BF16_BOUND
+    free0 = [p.free_count for p in ex.cache.pools]
+    got = H.run_mixed(ex, {"a": a, "b": b}, seed=7, max_live=2, decode_tail=5)
+    assert H.scaled_error(got["a"], plain_forward(a)) < bound
+    assert H.scaled_error(got["b"], plain_forward(b)) < bound
+    got = H.run_portions(ex, "c", a, [5, 2, 11, 8])
+    assert H.scaled_error(got, plain_forward(a)) < bound
+    if window:
+        # the latent group gives back the pages its window has passed while the request lives; the attention's group keeps all
+        ex.step([StepEntry("w", a, [len(a) - 1])])
+        held = ex.cache.get("w").tables
+        assert sum(1 for p_ in held[0] if p_ >= 0) < sum(1 for p_ in held[1] if p_ >= 0) == -(-len(a) // 4)
+        ex.finish("w")
+    assert [p.free_count for p in ex.cache.pools] == free0
+    ex.cache.check_invariants()
+
+
 # ------------------------------------------------------------------------------------------ position encoding and block alone
 def test_position_encoding_part_alone(backend):
     from roost_b200.parts import POSITIONS
@@ -529,18 +650,33 @@ class ToyScaledRope:
         return self.inv_freq, self.spec.rotary_dim
 
 
-def test_a_toy_routed_feed_forward_and_a_toy_position_encoding_are_registered_built_and_stepped(backend):
+class ToyGridRope(ToyScaledRope):
+    """Two position axes: a token at position p sits at (row p // 5, column p % 5) of a grid five wide; the first half of
+    the frequencies turn with the row, the second half with the column. The angles are no longer position x frequency,
+    so the encoding hands over the step's cosines and sines itself, made on the device from the step's positions."""
+
+    def step_table(self, batch):
+        pos = batch.positions.clamp(min=0).double()
+        half = self.inv_freq.numel()
+        axis = torch.where(torch.arange(half, device=pos.device) < half // 2, torch.div(pos, 5, rounding_mode="floor")[:, None], (pos % 5)[:, None])
+        ang = axis * self.inv_freq[None, :]
+        return torch.stack([torch.cos(ang), torch.sin(ang)], dim=-1).float().contiguous()
+
+
+@pytest.mark.parametrize("encoding", ["toy_scaled_rope", "toy_grid_rope"])
+def test_a_toy_routed_feed_forward_and_a_toy_position_encoding_are_registered_built_and_stepped(backend, encoding):
     """Generality of the parts: a feed-forward with routing and another position encoding, both defined here, go into a
     model beside the package's own parts without a change to the package, and every way of stepping agrees with a
     plain whole-sequence computation."""
     from roost_b200.parts import register_feed_forward, register_position
     register_feed_forward("toy_top1_experts", ToyTop1Experts)
     register_position("toy_scaled_rope", ToyScaledRope)
+    register_position("toy_grid_rope", ToyGridRope)
     rt = runtime(backend)
     H_, V, I, E = 48, 61, 32, 3
     norm = NormSpec(size=H_, eps=1e-5)
     attn = AttentionSpec(hidden=H_, num_heads=3, num_kv_heads=1, head_dim=16, scale=0.25, qk_norm=NormSpec(size=16, eps=1e-5),
-                         position=ToyScaledRopeSpec(rotary_dim=8, theta=50.0, factor=4.0))
+                         position=ToyScaledRopeSpec(kind=encoding, rotary_dim=8, theta=50.0, factor=4.0))
     blocks = (BlockSpec(mixer=attn, feed_forward=ToyRoutedSpec(hidden=H_, intermediate=I, experts=E), input_norm=norm, post_mixer_norm=norm),
               BlockSpec(mixer=attn, feed_forward=GatedMlpSpec(hidden=H_, intermediate=I), input_norm=norm, post_mixer_norm=norm))
     spec = ModelSpec(architecture="ToyRoutedForTests", hidden=H_, vocab=V, blocks=blocks, schedule=(RunEntry(0), RunEntry(1)),
@@ -559,7 +695,11 @@ def test_a_toy_routed_feed_forward_and_a_toy_position_encoding_are_registered_bu
     def rope(x, pos):   # the toy encoding, plainly: the first 8 elements of a head, frequencies divided by 4
         half = 4
         freq = torch.pow(torch.tensor(50.0, dtype=torch.float64), -2.0 * torch.arange(half, dtype=torch.float64) / 8) / 4.0
-        ang = torch.tensor(pos, dtype=torch.float64)[:, None] * freq[None, :]
+        p64 = torch.tensor(pos, dtype=torch.float64)
+        if encoding == "toy_grid_rope":   # two axes: the first two frequencies turn with p // 5, the last two with p % 5
+            ang = torch.cat([torch.floor(p64 / 5)[:, None] * freq[None, :2], (p64 % 5)[:, None] * freq[None, 2:]], dim=1)
+        else:
+            ang = p64[:, None] * freq[None, :]
         c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
         out = x.clone()
         out[..., :half] = x[..., :half] * c - x[..., half:8] * s
