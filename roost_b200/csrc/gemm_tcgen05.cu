@@ -1058,8 +1058,6 @@ static int split_for(int n, int k, int tile_rows = 128) {
   if (split > 8) split = 8;
   if (split > kbs / 2) split = kbs / 2;
   while (split & (split - 1)) split &= split - 1;  // a power of two: clusters of 2, 4 and 8 fill the SMs of a GPC, 6 and 7 leave some idle
-  static const char* forced = getenv("ROOST_GEMM_SPLIT");
-  if (forced && atoi(forced) >= 2 && atoi(forced) <= 8 && atoi(forced) <= kbs / 2 && (long long)tiles * atoi(forced) <= 2 * sms) split = atoi(forced);
   return split >= 2 ? split : 0;
 }
 
@@ -1187,11 +1185,15 @@ extern "C" int roost_gemm_split_supported(int m, int n, int k, int64_t ldx, int6
 }
 
 // Where the k-split product was measured faster than the library's and than the weight-streaming kernel on a B200: clusters
-// of eight, at least four 64-wide blocks of k a CTA, at most 8 rows of x (16 with a k of 8192 or more). For 8 rows:
+// of eight, at least four 64-wide blocks of k a CTA, at most 8 rows of x (16 with a k of 8192 or more); clusters of four
+// with a k of 8192 or more and at most 8 rows (alone no faster than cuBLAS, in the step it is). For 8 rows:
 // [4096, 4096] 10.3 us against 12.3 (cuBLAS) and 12.5 (stream); [4096, 12288] 21.3 against 32.1 and 23.5; [1024, 3072]
 // 5.9 against 8.6 and 10.7; but [6144, 4096] 13.4 against 11.8 and [5120, 8192] (clusters of four) 19.0 against 18.3.
 extern "C" int roost_gemm_split_preferred(int m, int n, int k, int64_t ldx, int64_t ldw) {
-  if (!roost_gemm_split_supported(m, n, k, ldx, ldw) || split_for(n, k) != 8 || k < 2048) return 0;
+  if (!roost_gemm_split_supported(m, n, k, ldx, ldw)) return 0;
+  const int split = split_for(n, k);
+  if (split == 4 && k >= 8192 && m <= 8) return 1;  // the 32B sizes' output and down projections: 14.01 -> 13.82 ms a step
+  if (split != 8 || k < 2048) return 0;
   return (m <= 8 || (m <= 16 && k >= 8192)) ? 1 : 0;
 }
 
