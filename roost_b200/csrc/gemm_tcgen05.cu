@@ -1065,7 +1065,12 @@ template <typename TOut, bool SWIGLU>
 static int launch_split(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int m, int n, int k, int64_t ldo, int ntok, int split,
                         cudaStream_t s) {
   constexpr int WR = SWIGLU ? 256 : 128;
-  const int stages = SWIGLU ? 3 : (ntok == 16 ? 6 : (ntok == 32 ? 5 : 4));  // about 100 KB: two CTAs an SM
+  // At most about 100 KB, so that two CTAs fit an SM. With few rows of x four stages (72 KB) were measured best in the
+  // step (4.16 against 4.20 ms with six, 4.17 with three or five): a CTA of the next product then fits beside two of this
+  // one and has its weights on the way before these are done.
+  // A CTA with a long part of k (the 32B sizes: 32 and 100 blocks) keeps six: 13.82 against 13.93 ms a step there.
+  const int blocks_a_cta = ((k + BK - 1) / BK) / split;
+  const int stages = SWIGLU ? 3 : (ntok == 16 ? (blocks_a_cta >= 32 ? 6 : 4) : (ntok == 32 ? 5 : 4));
   const size_t smem = (size_t)stages * (WR * BK * 2 + ntok * BK * 2) + 1024;
   auto kernel = gemm_split_kernel<TOut, SWIGLU>;
   static bool attr_set[64] = {};
