@@ -162,7 +162,7 @@ def timed_decode(model, batch: int, context: int, steps: int, warmup: int):
     for i in range(warmup):
         one(i)
     torch.cuda.synchronize()
-    launches0 = k.launches
+    launches0, library0 = k.launches, k.library_launches
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler() as clocks:
         torch.cuda.synchronize()
@@ -172,13 +172,13 @@ def timed_decode(model, batch: int, context: int, steps: int, warmup: int):
         e1.record()
         torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / steps
-    launches = k.launches - launches0
+    launches, library_launches = k.launches - launches0, k.library_launches - library0
     k.check_device_status()   # a bounded wait given up inside the timed region would make the figure a fast, wrong one: fail instead
     ex.close()
     del ex
     gc.collect()
     torch.cuda.empty_cache()
-    return batch / (ms / 1e3), ms, launches, clocks.summary()
+    return batch / (ms / 1e3), ms, (launches, library_launches), clocks.summary()
 
 
 def timed_prefill(model, tokens_n: int, warmup: int = 3, iters: int = 6):
@@ -406,7 +406,9 @@ def main() -> int:
                    "l2": "inputs larger than L2: each step streams all weights (>10 GB) from HBM", "peaks": pk_kind},
         "prefill": prefill_record(cfg, args.prefill_tokens, pre_ms, pk),
         "roofline": roof,
-        "points": points, "points_detail": detail, "clocks": clocks, "gpu_launches": launches,
+        "points": points, "points_detail": detail, "clocks": clocks,
+        # kernels of this repository's library launched inside the timed region, and the cuBLAS products beside them
+        "gpu_launches": launches[0], "library_launches": launches[1],
     }
     if e2e is not None:
         line["e2e"] = e2e

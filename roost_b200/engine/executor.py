@@ -124,14 +124,19 @@ class StepGraph:
         """A replay with the tables of the last ``fits`` that returned True. ``live``: the rows of logits that are wanted."""
         self.static.upload(self._pending, self.fills)
         self.graph.replay()
-        self.ex.rt.kernels.launches += self.launches
+        self._count()
         return self.out[:live].clone()
+
+    def _count(self) -> None:
+        k = self.ex.rt.kernels
+        k.launches += self.launches
+        k.library_launches = getattr(k, "library_launches", 0) + self.library_launches
 
     def run_staged(self, staged: int, live: int) -> torch.Tensor:
         """A replay with tables staged earlier."""
         self.static.send(staged)
         self.graph.replay()
-        self.ex.rt.kernels.launches += self.launches
+        self._count()
         return self.out[:live].clone()
 
     def capture(self, ht: HostTables) -> None:
@@ -144,13 +149,15 @@ class StepGraph:
         for (key, mixer), sections in zip(self.work, self.work_sections):
             batch.work[key] = (mixer, mixer.step_work_bind(key, [self.static.views[i] for i in sections], captured=captured), None)
         graph = torch.cuda.CUDAGraph()
-        before = ex.rt.kernels.launches
+        before, before_lib = ex.rt.kernels.launches, getattr(ex.rt.kernels, "library_launches", 0)
         # one memory pool for all of an executor's graphs: they never run at the same time, so what one capture used
         # and freed serves the next
         with torch.cuda.graph(graph, pool=ex.graph_pool()):
             out = ex.forward(batch)
-        self.launches = ex.rt.kernels.launches - before   # kernels one replay launches
+        self.launches = ex.rt.kernels.launches - before   # kernels of this library one replay launches
+        self.library_launches = getattr(ex.rt.kernels, "library_launches", 0) - before_lib   # and cuBLAS products
         ex.rt.kernels.launches = before
+        ex.rt.kernels.library_launches = before_lib
         if sorted(batch.work, key=repr) != sorted((k for k, _ in self.work), key=repr):
             raise RuntimeError("the captured step asked for other work lists than the eager step before it")
         self.graph, self.out, self.batch = graph, out, batch
@@ -388,7 +395,7 @@ class StepExecutor:
         g.static.send(prep.staged)
         g.static.views[0][:n].copy_(ids_device)
         g.graph.replay()
-        self.rt.kernels.launches += g.launches
+        g._count()
         self.last_upload_bytes = g.static.total * 4
         return g.out[:n].clone()
 

@@ -121,6 +121,7 @@ class KernelLibrary:
         self.decode_cluster = True  # split rows merged by thread-block clusters where they fit (see decode_cluster_for)
         self._decode_ctas = 0
         self.launches = 0  # kernels launched through this handle (a host-side count of entry-point calls that launch)
+        self.library_launches = 0  # products handed to cuBLAS through torch beside them (counted where they are called)
 
     def _call(self, name: str, *args, launches: int = 1):
         status = getattr(self._lib, name)(*args)

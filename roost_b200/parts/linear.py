@@ -47,7 +47,7 @@ class Linear:
                 if k.gemm_stream_supported(M, self.out_features, self.in_features, x.stride(0), self.weight.stride(0)):
                     return k.gemm_stream(x, self.weight, out_dtype)   # weights streamed once by TMA, tcgen05 products
         if out_dtype == torch.bfloat16:
-            k.launches += 1
+            k.library_launches += 1
             return torch.matmul(x, self.weight.t())
         if _MM_OUT_DTYPE is None:
             try:
@@ -56,6 +56,6 @@ class Linear:
             except (TypeError, RuntimeError):
                 _MM_OUT_DTYPE = False
         if _MM_OUT_DTYPE:
-            k.launches += 1
+            k.library_launches += 1
             return torch.mm(x, self.weight.t(), out_dtype=torch.float32)
         return k.gemm_simt(x, self.weight, torch.float32)

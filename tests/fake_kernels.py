@@ -14,6 +14,7 @@ from tests.plain import qwen3_plain as plain
 
 class FakeKernels:
     launches = 0
+    library_launches = 0
 
     def embedding(self, table, ids):
         return table[ids.long()].clone()
