@@ -1200,8 +1200,9 @@ static int page_shift_of(int page_size) {
 // with the same operations in the same order, so the choice does not show in the result.
 constexpr int kPrefillWideMinRows = 65536;  // packed rows x key/value heads from which 128-row tiles are used
 // ... from which a work item of the tcgen05 kernel is two row groups (256 packed rows): one group's products then run
-// while the other's softmax does, which pays once the longest item is long enough (measured at 32/8 heads of 128: 1024
-// tokens 22 against 28 us with one group, 2048 tokens 59 against 50 us, 4096 tokens 182 against 147 us)
+// while the other's softmax does, which pays once there are enough items for every SM (measured at 32/8 heads of 128, one
+// group against two: 1024 tokens 22 against 28 us, 1536 tokens 40 against 37 us, 2048 tokens 58 against 49 us, 4096
+// tokens 181 against 146 us)
 constexpr int kPrefillTwoGroupsMinRows = 49152;
 
 template <int D, int MT>
