@@ -11,7 +11,8 @@ in the reference's manner (:408-438): an unknown option, a missing value or a re
 and exits with 2.
 
     roost generate --model DIR (--prompt-ids 1,2,3 | --prompt-file FILE) [--max-output-tokens N] [--temperature T]
-                   [--top-p P] [--top-k K] [--min-p P] [--seed S] [--stop-ids a,b] [--ignore-eos] [engine options]
+                   [--top-p P] [--top-k K] [--min-p P] [--seed S] [--stop-ids a,b] [--ignore-eos] [--repetition-penalty R]
+                   [--frequency-penalty F] [--presence-penalty P] [--logprobs] [--top-logprobs N] [engine options]
     roost chat --model DIR [--tokenizer tokenizer.json] [--template TEXT] [--stop-strings TEXT|JSON-LIST] [--max-output-tokens N]
                [sampling options as for generate] [engine options]  a console: /reset clears the conversation, /exit quits
     roost bench --model DIR [--batch N] [--prompt-tokens P] [--new-tokens K] [--seed S] [engine options]
@@ -36,9 +37,11 @@ _ENGINE_VALUED = {"--dtype", "--device", "--kernels", "--page-size", "--attentio
                   "--max-sequences", "--max-chunk-tokens"}
 _COMMANDS = {
     "generate": (_ENGINE_VALUED | {"--model", "--prompt-ids", "--prompt-file", "--max-output-tokens", "--temperature", "--top-p",
-                                   "--top-k", "--min-p", "--seed", "--stop-ids"}, {"--ignore-eos"}),
+                                   "--top-k", "--min-p", "--seed", "--stop-ids", "--repetition-penalty", "--frequency-penalty",
+                                   "--presence-penalty", "--top-logprobs"}, {"--ignore-eos", "--logprobs"}),
     "chat": (_ENGINE_VALUED | {"--model", "--tokenizer", "--template", "--stop-strings", "--max-output-tokens", "--temperature", "--top-p", "--top-k",
-                               "--min-p", "--seed", "--stop-ids"}, {"--ignore-eos"}),
+                               "--min-p", "--seed", "--stop-ids", "--repetition-penalty", "--frequency-penalty", "--presence-penalty"},
+             {"--ignore-eos"}),
     "bench": (_ENGINE_VALUED | {"--model", "--batch", "--prompt-tokens", "--new-tokens", "--seed"}, set()),
     "random-weights": ({"--config", "--out", "--seed", "--std", "--norm-std", "--mode"}, set()),
     "replay": ({"--model", "--dtype", "--out", "--max-tokens", "--page-size"}, set()),
@@ -161,14 +164,32 @@ def cmd_generate(opts) -> int:
     gen_opts = dict(max_output_tokens=_int(opts, "--max-output-tokens", 16), temperature=_float(opts, "--temperature"),
                     top_p=_float(opts, "--top-p"), top_k=_int(opts, "--top-k"), min_p=_float(opts, "--min-p"),
                     seed=_int(opts, "--seed"), stop_token_ids=tuple(_ids(opts.get("--stop-ids", ""), "--stop-ids")),
-                    ignore_eos="--ignore-eos" in opts)
+                    ignore_eos="--ignore-eos" in opts, repetition_penalty=_float(opts, "--repetition-penalty"),
+                    frequency_penalty=_float(opts, "--frequency-penalty"), presence_penalty=_float(opts, "--presence-penalty"),
+                    logprobs="--logprobs" in opts, top_logprobs=_int(opts, "--top-logprobs", 0))
+    _check_sampling(gen_opts)
     _apply_common(opts)
     from .engine.engine import GenerationOptions, RoostEngine
     engine = RoostEngine(model, dtype=dtype, **engine_opts)
     go = GenerationOptions(**gen_opts)
     for prompt, out in zip(prompts, engine.generate(prompts, go)):
-        print(json.dumps({"prompt_tokens": len(prompt), "token_ids": out.token_ids, "finish_reason": out.finish_reason}))
+        line = {"prompt_tokens": len(prompt), "token_ids": out.token_ids, "finish_reason": out.finish_reason}
+        if out.logprobs is not None:
+            line["logprobs"] = out.logprobs
+        if out.top_logprobs is not None:
+            line["top_logprobs"] = [[[t, lp] for t, lp in alts] for alts in out.top_logprobs]
+        print(json.dumps(line))
     return 0
+
+
+def _check_sampling(gen_opts: dict) -> None:
+    """The options' ranges, before anything is loaded: a bad value is a usage error."""
+    from .engine.engine import GenerationOptions
+    from .engine.request import RequestError
+    try:
+        GenerationOptions(**gen_opts).sampling().validate()
+    except RequestError as e:
+        raise UsageError(str(e)) from None
 
 
 CHAT_TEMPLATE = "<|im_start|>user\n{message}<|im_end|>\n<|im_start|>assistant\n"
@@ -191,7 +212,9 @@ def cmd_chat(opts, lines=None, out=None) -> int:
     gen_opts = dict(max_output_tokens=_int(opts, "--max-output-tokens", 256), temperature=_float(opts, "--temperature"),
                     top_p=_float(opts, "--top-p"), top_k=_int(opts, "--top-k"), min_p=_float(opts, "--min-p"),
                     seed=_int(opts, "--seed"), stop_token_ids=tuple(_ids(opts.get("--stop-ids", ""), "--stop-ids")),
-                    ignore_eos="--ignore-eos" in opts)
+                    ignore_eos="--ignore-eos" in opts, repetition_penalty=_float(opts, "--repetition-penalty"),
+                    frequency_penalty=_float(opts, "--frequency-penalty"), presence_penalty=_float(opts, "--presence-penalty"))
+    _check_sampling(gen_opts)
     template = opts.get("--template", CHAT_TEMPLATE)
     if "{message}" not in template:
         raise UsageError("--template needs the placeholder {message}")

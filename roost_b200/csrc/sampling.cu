@@ -863,6 +863,135 @@ __global__ void __cluster_dims__(kClusterCtas, 1, 1) __launch_bounds__(kThreads)
   cluster.sync();   // nobody leaves while another CTA still reads its shared memory
 }
 
+// ------------------------------------------------------------------------------------------------ penalties and logprobs
+// The reference's penalties, in its float32 form (src/Starlings.Roost.Ops/CpuOps.Sampling.cs:195-237: separate divides,
+// multiplies and subtracts, in vLLM's order): with c the token's count in the request's output so far and `seen` true when
+// c > 0 or the token is in the prompt, a seen logit x becomes x / repetition if it is above 0 and x * repetition otherwise;
+// then x - frequency * c; then, when c > 0, x - presence. A row whose slot is negative is copied as it is.
+__global__ void penalise_kernel(const float* __restrict__ logits, long long stride, int vocab, float* __restrict__ out,
+                                const int* __restrict__ counts, const unsigned* __restrict__ prompt_bits, int words,
+                                const int* __restrict__ row_slot, const float* __restrict__ repetition, const float* __restrict__ presence,
+                                const float* __restrict__ frequency) {
+  const int r = blockIdx.y;
+  const int v = blockIdx.x * blockDim.x + threadIdx.x;
+  if (v >= vocab) return;
+  float x = logits[(size_t)r * stride + v];
+  const int slot = row_slot[r];
+  if (slot >= 0) {
+    const int c = counts[(size_t)slot * vocab + v];
+    const bool seen = c > 0 || ((prompt_bits[(size_t)slot * words + (v >> 5)] >> (v & 31)) & 1u) != 0u;
+    if (seen) {
+      const float rep = repetition[r];
+      x = x > 0.f ? __fdiv_rn(x, rep) : __fmul_rn(x, rep);
+    }
+    x = __fsub_rn(x, __fmul_rn(frequency[r], (float)c));
+    if (c > 0) x = __fsub_rn(x, presence[r]);
+  }
+  out[(size_t)r * vocab + v] = x;
+}
+
+// counts[slot of row r][ids[r]] += 1 for the rows that have a slot and a token
+__global__ void count_tokens_kernel(int* __restrict__ counts, int vocab, const int* __restrict__ row_slot, const int* __restrict__ ids, int rows) {
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= rows) return;
+  const int slot = row_slot[r], id = ids[r];
+  if (slot >= 0 && id >= 0 && id < vocab) atomicAdd(&counts[(size_t)slot * vocab + id], 1);
+}
+
+// the bits of one slot's prompt tokens
+__global__ void prompt_bits_kernel(unsigned* __restrict__ bits, const int* __restrict__ ids, int n, int vocab) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int id = ids[i];
+  if (id >= 0 && id < vocab) atomicOr(&bits[id >> 5], 1u << (id & 31));
+}
+
+// Index of the largest logit that comes after (px, pv) in the order "value descending, index ascending" (NaN never; pv < 0:
+// the largest of all); -1 when there is none. The value is left in sf[0].
+__device__ __forceinline__ int block_argmax_after(const float* z, int n, float px, int pv, float* sf, int* si) {
+  float bv = 0.f;
+  int bi = -1;
+  for (int v = threadIdx.x; v < n; v += kThreads) {
+    const float x = z[v];
+    if (x != x) continue;
+    if (pv >= 0 && !(x < px || (x == px && v > pv))) continue;
+    if (bi < 0 || x > bv) {
+      bv = x;
+      bi = v;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (!better(bv, bi, ov, oi)) {
+      bv = ov;
+      bi = oi;
+    }
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  __syncthreads();
+  if (lane == 0) {
+    sf[warp] = bv;
+    si[warp] = bi;
+  }
+  __syncthreads();
+  bv = sf[lane];
+  bi = si[lane];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (!better(bv, bi, ov, oi)) {
+      bv = ov;
+      bi = oi;
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) sf[0] = bv;
+  __syncthreads();
+  return bi;
+}
+
+// The log-softmax of the raw logits at the chosen token, and the `top` highest raw logits with theirs
+// (src/Starlings.Roost.Ops/CpuOps.Sampling.cs:539-603): the maximum over the non-NaN logits, the sum of exp(x - max) over
+// them (a thread's strided partial sums, then a tree over the block in a fixed order: the same bits on every run), its
+// logarithm, and (x - max) - log(sum) for a token. A row without a chosen token gets -inf; missing top entries are id -1.
+__global__ void __launch_bounds__(kThreads) logprob_kernel(const float* __restrict__ logits, long long stride, int vocab,
+                                                          const int* __restrict__ ids, float* __restrict__ logprob, int top,
+                                                          int* __restrict__ top_ids, float* __restrict__ top_vals) {
+  __shared__ float sf[32];
+  __shared__ int si[32];
+  const int r = blockIdx.x;
+  const float* z = logits + (size_t)r * stride;
+  const int first = block_argmax_after(z, vocab, 0.f, -1, sf, si);
+  const float zmax = sf[0];
+  float part = 0.f;
+  if (first >= 0) {
+    for (int v = threadIdx.x; v < vocab; v += kThreads) {
+      const float x = z[v];
+      if (x == x) part += expf(x - zmax);
+    }
+  }
+  const float sum = block_sum_f(part, sf);
+  const float lse = logf(sum);
+  if (threadIdx.x == 0 && logprob != nullptr) {
+    const int id = ids[r];
+    logprob[r] = (id < 0 || id >= vocab || first < 0) ? -INFINITY : (z[id] - zmax) - lse;
+  }
+  float px = zmax;
+  int pv = first;
+  for (int i = 0; i < top; ++i) {   // uniform in the block: pv is the same in every thread
+    const int v = i == 0 ? first : (pv < 0 ? -1 : block_argmax_after(z, vocab, px, pv, sf, si));
+    if (i > 0 && v >= 0) px = sf[0];
+    pv = v;
+    if (threadIdx.x == 0) {
+      top_ids[(size_t)r * top + i] = v;
+      top_vals[(size_t)r * top + i] = v < 0 ? -INFINITY : (z[v] - zmax) - lse;
+    }
+  }
+}
+
 }  // namespace roost
 
 using namespace roost;
@@ -913,4 +1042,40 @@ extern "C" int roost_sample(const float* logits, int64_t stride, int rows, int v
   sample_kernel<<<rows, kThreads, 0, (cudaStream_t)stream>>>(logits, (long long)stride, vocab, temperature, top_k, top_p, min_p,
                                                             (const unsigned*)seeds, (const unsigned*)offsets, workspace, ids);
   return check_launch("sample");
+}
+
+extern "C" int roost_sample_penalise(const float* logits, int64_t stride, int rows, int vocab, float* out, const int32_t* counts,
+                                     const uint32_t* prompt_bits, const int32_t* row_slot, const float* repetition, const float* presence,
+                                     const float* frequency, roost_stream_t stream) {
+  ROOST_REQUIRE(rows >= 0 && vocab > 0 && stride >= vocab, "sample_penalise: rows, vocab and stride must be consistent");
+  ROOST_REQUIRE(logits && out && counts && prompt_bits && row_slot && repetition && presence && frequency, "sample_penalise: a table is null");
+  if (rows == 0) return ROOST_OK;
+  if (rows > 65535) return fail(ROOST_ERR_UNSUPPORTED, "sample_penalise: more than 65535 rows");
+  penalise_kernel<<<dim3((vocab + 255) / 256, rows), 256, 0, (cudaStream_t)stream>>>(logits, (long long)stride, vocab, out, counts, prompt_bits,
+                                                                                    (vocab + 31) / 32, row_slot, repetition, presence, frequency);
+  return check_launch("sample_penalise");
+}
+
+extern "C" int roost_sample_count_tokens(int32_t* counts, int vocab, const int32_t* row_slot, const int32_t* ids, int rows, roost_stream_t stream) {
+  ROOST_REQUIRE(rows >= 0 && vocab > 0 && counts && row_slot && ids, "sample_count_tokens: a table is null or a size is not positive");
+  if (rows == 0) return ROOST_OK;
+  count_tokens_kernel<<<(rows + 127) / 128, 128, 0, (cudaStream_t)stream>>>(counts, vocab, row_slot, ids, rows);
+  return check_launch("sample_count_tokens");
+}
+
+extern "C" int roost_sample_prompt_bits(uint32_t* bits, const int32_t* ids, int n, int vocab, roost_stream_t stream) {
+  ROOST_REQUIRE(n >= 0 && vocab > 0 && bits && (ids || n == 0), "sample_prompt_bits: a table is null or a size is not positive");
+  if (n == 0) return ROOST_OK;
+  prompt_bits_kernel<<<(n + 255) / 256, 256, 0, (cudaStream_t)stream>>>(bits, ids, n, vocab);
+  return check_launch("sample_prompt_bits");
+}
+
+extern "C" int roost_sample_logprobs(const float* logits, int64_t stride, int rows, int vocab, const int32_t* ids, float* logprob, int top,
+                                     int32_t* top_ids, float* top_vals, roost_stream_t stream) {
+  ROOST_REQUIRE(rows >= 0 && vocab > 0 && stride >= vocab, "sample_logprobs: rows, vocab and stride must be consistent");
+  ROOST_REQUIRE(top >= 0 && top <= vocab, "sample_logprobs: top is outside [0, vocab]");
+  ROOST_REQUIRE(logits && (logprob == nullptr || ids) && (top == 0 || (top_ids && top_vals)), "sample_logprobs: a table is null");
+  if (rows == 0) return ROOST_OK;
+  logprob_kernel<<<rows, kThreads, 0, (cudaStream_t)stream>>>(logits, (long long)stride, vocab, ids, logprob, top, top_ids, top_vals);
+  return check_launch("sample_logprobs");
 }

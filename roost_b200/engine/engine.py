@@ -53,11 +53,19 @@ class GenerationOptions:
     seed: int | None = None
     stop_token_ids: tuple = ()
     ignore_eos: bool = False
+    repetition_penalty: float | None = None   # None or 1: off
+    frequency_penalty: float | None = None    # None or 0: off
+    presence_penalty: float | None = None
+    logprobs: bool = False                     # the logprob of every generated token
+    top_logprobs: int = 0                      # and of this many most likely alternatives (needs logprobs)
 
     def sampling(self) -> SamplingParameters:
         return SamplingParameters(temperature=self.temperature or 0.0, top_p=1.0 if self.top_p is None else self.top_p,
                                   top_k=0 if self.top_k in (None, -1) else self.top_k, min_p=self.min_p or 0.0, seed=self.seed,
-                                  max_tokens=self.max_output_tokens, ignore_eos=self.ignore_eos)
+                                  max_tokens=self.max_output_tokens, ignore_eos=self.ignore_eos,
+                                  repetition_penalty=1.0 if self.repetition_penalty is None else self.repetition_penalty,
+                                  frequency_penalty=self.frequency_penalty or 0.0, presence_penalty=self.presence_penalty or 0.0,
+                                  logprobs=self.logprobs, top_logprobs=self.top_logprobs)
 
 
 @dataclass
@@ -67,6 +75,8 @@ class CompletionUpdate:
     finish_reason: str | None = None
     prompt_tokens: int = 0
     completion_tokens: int = 0
+    logprob: float | None = None
+    top_logprobs: list | None = None
 
 
 @dataclass
@@ -75,6 +85,8 @@ class Completion:
     token_ids: list = field(default_factory=list)
     finish_reason: str | None = None
     prompt_tokens: int = 0
+    logprobs: list | None = None         # one a token, when asked for
+    top_logprobs: list | None = None     # [(token id, logprob)] lists, one a token, when asked for
 
 
 class RoostEngine:
@@ -98,7 +110,8 @@ class RoostEngine:
         self.scheduler = Scheduler(self.executor.cache, SchedulerOptions(
             max_tokens_per_step=max_tokens, max_sequences_per_step=max_sequences, max_chunk_tokens=max_chunk_tokens,
             model_stop_token_ids=tuple(spec.stop_token_ids), max_context=spec.max_positions or None))
-        self.sampler = Sampler(self.model.rt.kernels, self.model.rt.device)
+        self.sampler = Sampler(self.model.rt.kernels, self.model.rt.device, max_requests=max_sequences)
+        self._extras: dict = {}     # request id -> (logprob, alternatives) of the token this step sampled
         self._seed_source = random.Random(seed)
         self._seeds: dict = {}
         self._next_id = 0
@@ -128,7 +141,13 @@ class RoostEngine:
 
     def cancel(self, request_id) -> bool:
         self._seeds.pop(request_id, None)
+        self._release(request_id)
         return self.scheduler.cancel(request_id)
+
+    def _release(self, request_id) -> None:
+        release = getattr(self.sampler, "release", None)
+        if release is not None:
+            release(request_id)
 
     def has_unfinished(self) -> bool:
         return self.scheduler.unfinished > 0
@@ -153,8 +172,12 @@ class RoostEngine:
                 raise
         events = self.scheduler.apply(plan, tokens)
         for e in events:
+            extra = self._extras.pop(e.request_id, None) if self._extras else None
+            if extra is not None and e.token is not None:
+                e.logprob, e.top_logprobs = extra
             if e.finish_reason is not None:
                 self._seeds.pop(e.request_id, None)
+                self._release(e.request_id)
         return events
 
     def _run(self, plan: StepPlan) -> dict:
@@ -164,7 +187,7 @@ class RoostEngine:
         prepared, self._prepared = self._prepared, None
         inflight, self._inflight = self._inflight, None
         sampling_rows = [r for r in plan.rows if r.samples]
-        ids_device = ids_host = event = None
+        ids_device = ids_host = event = extras_host = None
         keep = None
         if inflight is not None and len(sampling_rows) == len(plan.rows):
             keep = self.executor.adoptable(inflight.prep, entries)
@@ -185,9 +208,8 @@ class RoostEngine:
             else:
                 logits = self.executor.step(entries)
             if sampling_rows:
-                rows = [SamplingRow(r.sequence.request.sampling, self._seeds[r.sequence.request_id], r.sequence.generated)
-                        for r in sampling_rows]
-                ids_device = self.sampler(logits, rows)
+                ids_device = self.sampler(logits, [self._sampling_row(r, 0) for r in sampling_rows])
+                extras_host = self._extras_to_host()
                 ids_host, event = self._to_host(ids_device)
                 keep = list(range(len(sampling_rows)))
         if sampling_rows:
@@ -196,11 +218,12 @@ class RoostEngine:
             # now, fed with this step's tokens on the device, and the host reads this step's tokens meanwhile.
             if len(sampling_rows) == len(plan.rows) and all(r.count == 1 for r in plan.rows) and self._decode_only():
                 prep = self.executor.prepare_decode([r.sequence.request_id for r in plan.rows])
-                if prep is not None and self.chain_steps:
+                # (a request with penalties or logprobs is sampled from its accepted tokens and hands back more than an
+                # id: its steps are not started ahead)
+                plain_rows = not any(r.sequence.request.sampling.penalised or r.sequence.request.sampling.logprobs for r in plan.rows)
+                if prep is not None and self.chain_steps and plain_rows:
                     nxt = self.executor.launch_prepared(prep, ids_device)
-                    rows = [SamplingRow(r.sequence.request.sampling, self._seeds[r.sequence.request_id], r.sequence.generated + 1)
-                            for r in plan.rows]
-                    nxt_ids = self.sampler(nxt, rows)
+                    nxt_ids = self.sampler(nxt, [self._sampling_row(r, 1) for r in plan.rows])
                     self._inflight = _InFlight(prep, nxt_ids, *self._to_host(nxt_ids))
                 else:
                     self._prepared = prep
@@ -212,10 +235,52 @@ class RoostEngine:
             if self._inflight is not None:
                 self._inflight.fed = ids
             tokens = {r.sequence.request_id: t for r, t in zip(sampling_rows, ids)}
+            if extras_host is not None:
+                self._extras = self._read_extras(extras_host, sampling_rows)
         self.steps += 1
         if not self._status_with_tokens and self.steps % self.STATUS_EVERY == 0:
             self.check_device()
         return tokens
+
+    def _sampling_row(self, r, ahead: int) -> SamplingRow:
+        """The sampler's view of a planned row; ``ahead``: tokens of the request that are sampled but not yet accepted."""
+        s = r.sequence
+        p = s.request.sampling
+        if p.penalised:
+            return SamplingRow(p, self._seeds[s.request_id], s.generated + ahead, s.request_id, s.tokens[: s.prompt_len],
+                               s.tokens[s.prompt_len : s.prompt_len + s.generated])
+        return SamplingRow(p, self._seeds[s.request_id], s.generated + ahead)
+
+    def _extras_to_host(self):
+        """Starts the copies of what the last sampling call computed beside the ids; None when no row asked."""
+        ex = getattr(self.sampler, "extras", None)     # (a caller may have put a plain function in the sampler's place)
+        if ex is None or ex.logprobs is None:
+            return None
+        pin = ex.logprobs.device.type == "cuda"
+        out = []
+        for t in (ex.logprobs, ex.top_ids, ex.top_logprobs):
+            if t is None:
+                out.append(None)
+                continue
+            host = torch.empty(t.shape, dtype=t.dtype, pin_memory=pin)
+            host.copy_(t, non_blocking=True)
+            out.append(host)
+        return out
+
+    @staticmethod
+    def _read_extras(extras_host, sampling_rows) -> dict:
+        lp, top_ids, top_vals = extras_host
+        lp = lp.tolist()
+        out = {}
+        for i, r in enumerate(sampling_rows):
+            p = r.sequence.request.sampling
+            if not p.logprobs:
+                continue
+            alternatives = None
+            if p.top_logprobs and top_ids is not None:
+                alternatives = list(zip(top_ids[i, : p.top_logprobs].tolist(), top_vals[i, : p.top_logprobs].tolist()))
+            out[r.sequence.request_id] = (lp[i], alternatives)
+        return out
 
     STATUS_EVERY = 256   # steps between looks at the kernels' status words when no step reads them with its tokens
 
@@ -264,6 +329,11 @@ class RoostEngine:
                 if e.request_id in results:
                     if e.token is not None:
                         results[e.request_id].token_ids.append(e.token)
+                        if e.logprob is not None:
+                            c = results[e.request_id]
+                            c.logprobs = (c.logprobs or []) + [e.logprob]
+                            if e.top_logprobs is not None:
+                                c.top_logprobs = (c.top_logprobs or []) + [e.top_logprobs]
                     if e.finish_reason is not None:
                         results[e.request_id].finish_reason = e.finish_reason
         return [results[r] for r in order]
@@ -285,7 +355,7 @@ class RoostEngine:
                     if e.token is not None:
                         produced += 1
                     done = e.finish_reason is not None
-                    yield CompletionUpdate(rid, e.token, e.finish_reason, len(prompt_token_ids), produced)
+                    yield CompletionUpdate(rid, e.token, e.finish_reason, len(prompt_token_ids), produced, e.logprob, e.top_logprobs)
         finally:
             if not done:
                 self.cancel(rid)   # the caller stopped listening (a stop string matched, say): out of the next step

@@ -3,10 +3,13 @@
 Field names and defaults are the reference's request contract
 (src/Starlings.Roost.Abstractions/Requests/Request.cs:19-68 for the sampling parameters, :148-200 for the
 request): temperature 1 unless set (0 means greedy), top_p 1 disables, top_k 0 disables, min_p 0 disables, a
-missing seed is replaced by an engine-chosen one, stop token ids are the model's plus the request's.
+missing seed is replaced by an engine-chosen one, stop token ids are the model's plus the request's; repetition
+penalty 1 and frequency and presence penalties 0 disable (the ranges are the chat builder's,
+src/Starlings.Generation.Roost/ChatRequestBuilder.cs:199-223,240-245); logprobs off, at most 20 alternatives a token.
 """
 from __future__ import annotations
 
+import math
 from dataclasses import dataclass, field
 
 
@@ -28,6 +31,13 @@ class SamplingParameters:
     max_tokens: int | None = None
     min_tokens: int = 0
     ignore_eos: bool = False
+    repetition_penalty: float = 1.0
+    frequency_penalty: float = 0.0
+    presence_penalty: float = 0.0
+    logprobs: bool = False
+    top_logprobs: int = 0
+
+    MAX_TOP_LOGPROBS = 20
 
     def validate(self) -> None:
         if self.temperature < 0:
@@ -40,10 +50,24 @@ class SamplingParameters:
             raise RequestError("InvalidOption", f"min_p {self.min_p} is outside [0, 1]")
         if self.max_tokens is not None and self.max_tokens <= 0:
             raise RequestError("InvalidOption", f"max_tokens {self.max_tokens} must be positive")
+        if not (math.isfinite(self.repetition_penalty) and self.repetition_penalty > 0):
+            raise RequestError("InvalidOption", f"repetition_penalty must be a positive number; got {self.repetition_penalty}")
+        for name in ("frequency_penalty", "presence_penalty"):
+            v = getattr(self, name)
+            if not (math.isfinite(v) and -2 <= v <= 2):
+                raise RequestError("InvalidOption", f"{name} must be in [-2, 2]; got {v}")
+        if not 0 <= self.top_logprobs <= self.MAX_TOP_LOGPROBS:
+            raise RequestError("InvalidOption", f"top_logprobs must be in [0, {self.MAX_TOP_LOGPROBS}]; got {self.top_logprobs}")
+        if self.top_logprobs > 0 and not self.logprobs:
+            raise RequestError("InvalidOption", "top_logprobs needs logprobs set to true")
 
     @property
     def greedy(self) -> bool:
         return self.temperature <= 0
+
+    @property
+    def penalised(self) -> bool:
+        return self.repetition_penalty != 1.0 or self.frequency_penalty != 0.0 or self.presence_penalty != 0.0
 
 
 GREEDY = SamplingParameters(temperature=0.0)
@@ -67,3 +91,5 @@ class TokenEvent:
     request_id: object
     token: int | None
     finish_reason: str | None = None
+    logprob: float | None = None          # of the token, when the request asked for logprobs
+    top_logprobs: list | None = None      # [(token id, logprob)] of the highest raw logits, when it asked for alternatives

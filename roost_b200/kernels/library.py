@@ -13,7 +13,7 @@ import torch
 
 from . import build
 
-ABI_VERSION = 9
+ABI_VERSION = 10
 F32, BF16 = 0, 1
 
 
@@ -78,6 +78,10 @@ _SIGNATURES = {
     "roost_attention_decode_cluster": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                        c_int, c_int, c_int, c_int, ctypes.c_longlong, c_float, c_int, c_void_p],
     "roost_attention_decode_cluster_supported": [c_int, c_int, ctypes.c_longlong, c_int, c_void_p, c_void_p],
+    "roost_sample_penalise": [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+    "roost_sample_count_tokens": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p],
+    "roost_sample_prompt_bits": [c_void_p, c_void_p, c_int, c_int, c_void_p],
+    "roost_sample_logprobs": [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p],
     "roost_gemm_simt": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int, c_int, c_void_p],
     "roost_gemm_tcgen05_supported": [c_int, c_int, c_int, c_int64, c_int64],
     "roost_gemm_tcgen05": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int, c_void_p],
@@ -507,6 +511,50 @@ class KernelLibrary:
         self._call("roost_sample", _ptr(logits), logits.stride(0), R, V, _ptr(temperature), _ptr(top_k), _ptr(top_p),
                    _ptr(min_p), _ptr(seeds), _ptr(offsets), _ptr(workspace), _ptr(ids), _stream())
         return ids
+
+    def sample_penalise(self, logits, counts, prompt_bits, row_slot, repetition, presence, frequency) -> torch.Tensor:
+        """The rows of ``logits`` with the reference's repetition, frequency and presence penalties applied: counts
+        [slots, vocab] int32 (the requests' output tokens so far), prompt_bits [slots, (vocab + 31) // 32] int32 (the
+        prompts' tokens), row_slot [rows] int32 (-1: the row is copied as it is), the penalties float32 [rows]."""
+        _need(logits, "logits", torch.float32); _need(counts, "counts", torch.int32); _need(prompt_bits, "prompt_bits", torch.int32)
+        R, V = logits.shape
+        if counts.shape[1] != V or prompt_bits.shape != (counts.shape[0], (V + 31) // 32):
+            raise KernelError(f"sample_penalise: counts {tuple(counts.shape)} and prompt_bits {tuple(prompt_bits.shape)} do not fit a vocabulary of {V}")
+        for n, t, dt in (("row_slot", row_slot, torch.int32), ("repetition", repetition, torch.float32), ("presence", presence, torch.float32),
+                         ("frequency", frequency, torch.float32)):
+            _need(t, n, dt)
+            if t.numel() != R:
+                raise KernelError(f"sample_penalise: {n} has {t.numel()} entries for {R} rows")
+        out = torch.empty((R, V), dtype=torch.float32, device=logits.device)
+        self._call("roost_sample_penalise", _ptr(logits), logits.stride(0), R, V, _ptr(out), _ptr(counts), _ptr(prompt_bits), _ptr(row_slot),
+                   _ptr(repetition), _ptr(presence), _ptr(frequency), _stream())
+        return out
+
+    def sample_count_tokens(self, counts, row_slot, ids) -> None:
+        """counts[row_slot[r], ids[r]] += 1 for the rows with a slot and a token."""
+        _need(counts, "counts", torch.int32); _need(row_slot, "row_slot", torch.int32); _need(ids, "ids", torch.int32)
+        if row_slot.numel() != ids.numel():
+            raise KernelError("sample_count_tokens: one slot a token id is needed")
+        self._call("roost_sample_count_tokens", _ptr(counts), counts.shape[1], _ptr(row_slot), _ptr(ids), ids.numel(), _stream())
+
+    def sample_prompt_bits(self, bits_of_slot, ids) -> None:
+        """Sets the bits of the token ids ``ids`` in one slot's words (int32 [(vocab + 31) // 32], a view into the table)."""
+        _need(bits_of_slot, "bits", torch.int32); _need(ids, "ids", torch.int32)
+        self._call("roost_sample_prompt_bits", _ptr(bits_of_slot), _ptr(ids), ids.numel(), bits_of_slot.numel() * 32, _stream())
+
+    def sample_logprobs(self, logits, ids, top: int = 0):
+        """(log-softmax of the raw logits at ids [rows] float32, the ``top`` highest raw logits' ids [rows, top] int32 and
+        their log-softmax [rows, top] float32), all on the device."""
+        _need(logits, "logits", torch.float32); _need(ids, "ids", torch.int32)
+        R, V = logits.shape
+        if ids.numel() != R or not 0 <= top <= V:
+            raise KernelError(f"sample_logprobs: {ids.numel()} ids for {R} rows, or top {top} outside [0, {V}]")
+        lp = torch.empty((R,), dtype=torch.float32, device=logits.device)
+        top_ids = torch.empty((R, top), dtype=torch.int32, device=logits.device)
+        top_vals = torch.empty((R, top), dtype=torch.float32, device=logits.device)
+        self._call("roost_sample_logprobs", _ptr(logits), logits.stride(0), R, V, _ptr(ids), _ptr(lp), top, _ptr(top_ids) if top else None,
+                   _ptr(top_vals) if top else None, _stream())
+        return lp, top_ids, top_vals
 
 
 _LIB: KernelLibrary | None = None

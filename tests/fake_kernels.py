@@ -108,6 +108,38 @@ class FakeKernels:
     def argmax(self, logits):
         return torch.tensor([plain.sample_row(r.tolist(), 0.0) for r in logits], dtype=torch.int32)
 
+    def sample_penalise(self, logits, counts, prompt_bits, row_slot, repetition, presence, frequency):
+        out = logits.clone()
+        V = logits.shape[1]
+        for r in range(logits.shape[0]):
+            slot = int(row_slot[r])
+            if slot < 0:
+                continue
+            c = {v: int(n) for v, n in enumerate(counts[slot].tolist()) if n}
+            words = prompt_bits[slot].tolist()
+            prompt = [v for v in range(V) if (words[v >> 5] >> (v & 31)) & 1]
+            out[r] = torch.tensor(plain.penalise_row(logits[r].tolist(), c, prompt, float(repetition[r]), float(frequency[r]), float(presence[r])))
+        return out
+
+    def sample_count_tokens(self, counts, row_slot, ids):
+        for r in range(ids.numel()):
+            if int(row_slot[r]) >= 0 and 0 <= int(ids[r]) < counts.shape[1]:
+                counts[int(row_slot[r]), int(ids[r])] += 1
+
+    def sample_prompt_bits(self, bits_of_slot, ids):
+        for v in ids.tolist():
+            if 0 <= v < bits_of_slot.numel() * 32:
+                word = int(bits_of_slot[v >> 5]) & 0xffffffff
+                word |= 1 << (v & 31)
+                bits_of_slot[v >> 5] = word - (1 << 32) if word >= (1 << 31) else word
+
+    def sample_logprobs(self, logits, ids, top=0):
+        lp = torch.tensor([plain.logprob_at(logits[r].tolist(), int(ids[r])) for r in range(logits.shape[0])], dtype=torch.float32)
+        pairs = [plain.top_logprobs(logits[r].tolist(), top) for r in range(logits.shape[0])]
+        R = logits.shape[0]
+        return (lp, torch.tensor([p[0] for p in pairs], dtype=torch.int32).reshape(R, top),
+                torch.tensor([p[1] for p in pairs], dtype=torch.float32).reshape(R, top))
+
     def sample(self, logits, temperature, top_k, top_p, min_p, seeds, offsets, workspace=None):
         out = []
         for r in range(logits.shape[0]):

@@ -329,6 +329,55 @@ def sample_row(logits, temperature: float, top_k: int = 0, top_p: float = 1.0, m
     return chosen
 
 
+def penalise_row(logits, counts: dict, prompt_tokens, repetition: float = 1.0, frequency: float = 0.0, presence: float = 0.0):
+    """The reference's penalties on one row, in double (src/Starlings.Roost.Ops/CpuOps.Sampling.cs:195-237; vLLM's
+    order, :13-17): with c the token's count in the generated output and seen = c > 0 or the token is in the prompt, a seen
+    logit x becomes x / repetition if it is above 0 and x * repetition otherwise; then x - frequency * c; then, when
+    c > 0, x - presence."""
+    z = [float(x) for x in logits]
+    prompt = set(prompt_tokens)
+    for v in range(len(z)):
+        c = counts.get(v, 0)
+        x = z[v]
+        if c > 0 or v in prompt:
+            x = x / repetition if x > 0 else x * repetition
+        x -= frequency * c
+        if c > 0:
+            x -= presence
+        z[v] = x
+    return z
+
+
+def log_norm(logits):
+    """(max, log of the sum of exp(x - max)) over the non-NaN raw logits (src/Starlings.Roost.Ops/CpuOps.Sampling.cs:516-537)."""
+    mx = -math.inf
+    for x in logits:
+        if x > mx:
+            mx = x
+    total = 0.0
+    for x in logits:
+        if not math.isnan(x):
+            total += math.exp(x - mx)
+    return mx, math.log(total) if total > 0 else -math.inf
+
+
+def logprob_at(logits, token: int) -> float:
+    """The log-softmax of the raw logits at a token; -inf for token -1 (src/Starlings.Roost.Ops/CpuOps.Sampling.cs:166-170,566-567)."""
+    if token < 0:
+        return -math.inf
+    mx, lse = log_norm(logits)
+    return float(logits[token]) - mx - lse
+
+
+def top_logprobs(logits, k: int):
+    """The k highest raw logits, ties to the lower index, NaN skipped, with their log-softmax; missing entries are id -1
+    and -inf (src/Starlings.Roost.Ops/CpuOps.Sampling.cs:569-603)."""
+    mx, lse = log_norm(logits)
+    order = sorted((v for v in range(len(logits)) if not math.isnan(logits[v])), key=lambda v: (-logits[v], v))[:k]
+    ids = order + [-1] * (k - len(order))
+    return ids, [float(logits[v]) - mx - lse if v >= 0 else -math.inf for v in ids]
+
+
 # --------------------------------------------------------------------------------------------------
 # the reference's seeded weight generator (for the pinned greedy ids of roost-tiny)
 # --------------------------------------------------------------------------------------------------

@@ -29,6 +29,21 @@ def test_generate_doctor_and_usage_errors(tiny_model_dirs, tmp_path):
     r = roost("generate", "--model", str(model_dir), "--prompt-file", str(tmp_path / "prompts.txt"), "--max-output-tokens", "3",
               "--temperature", "0.7", "--top-p", "0.9", "--top-k", "20", "--seed", "5", "--attention-blocks", "8")
     assert r.returncode == 0 and len(r.stdout.strip().splitlines()) == 2
+    # penalties change the greedy tokens; logprobs and alternatives come with the line (the first alternative of a greedy
+    # token without penalties is the token itself)
+    r = roost("generate", "--model", str(model_dir), "--dtype", "float32", "--prompt-ids", ",".join(map(str, prompt)), "--max-output-tokens", "6",
+              "--ignore-eos", "--attention-blocks", "8", "--logprobs", "--top-logprobs", "2")
+    assert r.returncode == 0, r.stderr
+    with_lp = json.loads(r.stdout.strip().splitlines()[-1])
+    assert with_lp["token_ids"] == out["token_ids"] and len(with_lp["logprobs"]) == 6 and all(lp <= 0 for lp in with_lp["logprobs"])
+    assert [alts[0][0] for alts in with_lp["top_logprobs"]] == out["token_ids"] and all(len(alts) == 2 for alts in with_lp["top_logprobs"])
+    logits = plain.forward_logits(cfg, w, prompt)[-1].tolist()
+    assert abs(with_lp["logprobs"][0] - plain.logprob_at(logits, out["token_ids"][0])) < 1e-4
+    r = roost("generate", "--model", str(model_dir), "--dtype", "float32", "--prompt-ids", ",".join(map(str, prompt)), "--max-output-tokens", "6",
+              "--ignore-eos", "--attention-blocks", "8", "--repetition-penalty", "5", "--frequency-penalty", "2", "--presence-penalty", "2")
+    assert r.returncode == 0, r.stderr
+    penalised = json.loads(r.stdout.strip().splitlines()[-1])["token_ids"]
+    assert len(set(penalised)) == 6 and not set(penalised) & set(prompt)       # so strong that no token comes twice, nor one of the prompt
     r = roost("doctor", "--model", str(model_dir))
     assert r.returncode == 0 and "ok   weights" in r.stdout and "ok   gpu" in r.stdout
     r = roost("bench", "--model", str(model_dir), "--batch", "3", "--prompt-tokens", "20", "--new-tokens", "5", "--attention-blocks", "16")
@@ -38,7 +53,10 @@ def test_generate_doctor_and_usage_errors(tiny_model_dirs, tmp_path):
     r = roost("doctor", "--model", str(tmp_path))
     assert r.returncode == 1 and "FAIL" in r.stdout
     for bad in (["generate", "--model", "x", "--bogus", "1"], ["generate", "--model"], ["generate", "--model", "a", "--model", "b"],
-                ["serve"], [], ["generate", "--model", "x"], ["generate", "--model", "x", "--prompt-ids", "1", "--max-output-tokens", "many"]):
+                ["serve"], [], ["generate", "--model", "x"], ["generate", "--model", "x", "--prompt-ids", "1", "--max-output-tokens", "many"],
+                ["generate", "--model", "x", "--prompt-ids", "1", "--top-logprobs", "3"],          # alternatives need --logprobs
+                ["generate", "--model", "x", "--prompt-ids", "1", "--frequency-penalty", "2.5"],
+                ["generate", "--model", "x", "--prompt-ids", "1", "--repetition-penalty", "0"]):
         r = roost(*bad)
         assert r.returncode == 2 and "usage" in r.stderr, bad
     cfg_path = tmp_path / "c.json"
