@@ -497,19 +497,22 @@ __global__ void __launch_bounds__(kThreads)
 
 // ------------------------------------------------------------------------------------------------ a row on a cluster of CTAs
 // One SM reads a row of a large vocabulary at about 30 GB/s, and a search makes several passes over it: a block a row
-// takes 460 us at 151,936 tokens. Here a cluster of eight CTAs takes a row: each keeps an eighth of the row's weights in
-// shared memory, so every pass after the first reads shared memory, and the CTAs combine what they find through each
-// other's shared memory: histograms are reduced bucket range by bucket range (CTA c owns an eighth of the buckets), the
-// range that holds the crossing is found from the eight range totals, and its owner finds the bucket and tells the
+// takes 460 us at 151,936 tokens. Here a cluster of eight (or four) CTAs takes a row: each keeps its part of the row's
+// weights in shared memory, so every pass after the first reads shared memory, and the CTAs combine what they find through
+// each other's shared memory: histograms are reduced bucket range by bucket range (CTA c owns its share of the buckets),
+// the range that holds the crossing is found from the ranges' totals, and its owner finds the bucket and tells the
 // others. Every sum is an integer sum, so the result is the single block's, bit for bit.
 namespace cg = cooperative_groups;
-constexpr int kClusterCtas = 8;
-constexpr int kSliceFloats = 24576;   // of a row, in a CTA's shared memory (96 KB): rows of up to 196,608 tokens
+// Eight CTAs a row while at most eight rows are sampled (fifteen or so clusters of eight run at once); four from there on
+// (37 of them at once, one CTA an SM with its quarter of the row in shared memory), so that 64 rows take two rounds, not five.
+constexpr int kClusterMaxCtas = 8, kClusterMinCtas = 4;
+constexpr int kSliceFloats8 = 24576;   // of a row, in a CTA's shared memory (96 KB): rows of up to 196,608 tokens
+constexpr int kSliceFloats4 = 40960;   // 160 KB: rows of up to 163,840 tokens
 
 struct ClusterScratch {
   SearchScratch h;                                   // this CTA's histogram of its slice
-  unsigned long long own_mass[kBuckets / kClusterCtas];   // the cluster's totals of the buckets this CTA owns
-  unsigned own_cnt[kBuckets / kClusterCtas];
+  unsigned long long own_mass[kBuckets / kClusterMinCtas];   // the cluster's totals of the buckets this CTA owns
+  unsigned own_cnt[kBuckets / kClusterMinCtas];
   unsigned long long own_total_mass;
   unsigned own_total_cnt;
   unsigned long long pub_u64[2][2];                  // all-reduce slots, used in turn
@@ -554,7 +557,7 @@ __device__ void cluster_sum2(cg::cluster_group& cluster, ClusterScratch& cs, int
   cluster.sync();
   unsigned long long ta = 0ull;
   unsigned tb = 0u;
-  for (int r = 0; r < kClusterCtas; ++r) {
+  for (int r = 0; r < (int)cluster.num_blocks(); ++r) {
     const ClusterScratch* o = cluster.map_shared_rank(&cs, r);
     ta += o->pub_u64[turn][0];
     tb += o->pub_u32[turn][0];
@@ -568,7 +571,7 @@ __device__ void cluster_sum2(cg::cluster_group& cluster, ClusterScratch& cs, int
 __device__ unsigned cluster_search_key(cg::cluster_group& cluster, ClusterScratch& cs, const float* __restrict__ slice, int n_local, unsigned xb,
                                        int c, unsigned long long target, bool strict, bool by_count, unsigned long long& above_mass,
                                        unsigned& above_cnt, unsigned& ties) {
-  const int rank = (int)cluster.block_rank();
+  const int rank = (int)cluster.block_rank(), ctas = (int)cluster.num_blocks();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   unsigned prefix = 0u, prefix_mask = 0u;
   unsigned long long acc_mass = 0ull;
@@ -579,7 +582,7 @@ __device__ unsigned cluster_search_key(cg::cluster_group& cluster, ClusterScratc
     return strict ? m > target : m >= target;
   };
   for (int level = 0; level < 3; ++level) {
-    const int shift = digit_shift(level), buckets = 1 << digit_bits(level), own = buckets / kClusterCtas;
+    const int shift = digit_shift(level), buckets = 1 << digit_bits(level), own = buckets / ctas;
     for (int i = threadIdx.x; i < buckets; i += kThreads) {
       cs.h.mass[i] = 0ull;
       cs.h.cnt[i] = 0u;
@@ -605,7 +608,7 @@ __device__ unsigned cluster_search_key(cg::cluster_group& cluster, ClusterScratc
     unsigned mine_cnt = 0u;
     if ((int)threadIdx.x < own) {
       const int bkt = rank * own + (int)threadIdx.x;
-      for (int r = 0; r < kClusterCtas; ++r) {
+      for (int r = 0; r < ctas; ++r) {
         const ClusterScratch* o = cluster.map_shared_rank(&cs, r);
         mine_mass += o->h.mass[bkt];
         mine_cnt += o->h.cnt[bkt];
@@ -638,7 +641,7 @@ __device__ unsigned cluster_search_key(cg::cluster_group& cluster, ClusterScratc
       unsigned long long m = acc_mass;
       unsigned n = acc_cnt;
       int at = 0;
-      for (int r = kClusterCtas - 1; r >= 0; --r) {
+      for (int r = ctas - 1; r >= 0; --r) {
         const ClusterScratch* o = cluster.map_shared_rank(&cs, r);
         const unsigned long long rm = o->own_total_mass;
         const unsigned rc = o->own_total_cnt;
@@ -707,7 +710,7 @@ __device__ unsigned cluster_search_key(cg::cluster_group& cluster, ClusterScratc
   return prefix;
 }
 
-__global__ void __cluster_dims__(kClusterCtas, 1, 1) __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads)
     sample_cluster_kernel(const float* __restrict__ logits, long long stride, int vocab, const float* __restrict__ temperature,
                           const int* __restrict__ top_k, const float* __restrict__ top_p, const float* __restrict__ min_p,
                           const unsigned* __restrict__ seeds, const unsigned* __restrict__ offsets, int* __restrict__ ids) {
@@ -717,9 +720,9 @@ __global__ void __cluster_dims__(kClusterCtas, 1, 1) __launch_bounds__(kThreads)
   __shared__ int s_result;
   __shared__ ClusterScratch cs;
   cg::cluster_group cluster = cg::this_cluster();
-  const int rank = (int)cluster.block_rank();
-  const int r = blockIdx.x / kClusterCtas;
-  const int span = (((vocab + kClusterCtas - 1) / kClusterCtas) + 3) & ~3;
+  const int rank = (int)cluster.block_rank(), ctas = (int)cluster.num_blocks();
+  const int r = blockIdx.x / ctas;
+  const int span = (((vocab + ctas - 1) / ctas) + 3) & ~3;
   const int lo = min(vocab, rank * span), n_local = min(vocab, lo + span) - lo;
   const float* z = logits + (size_t)r * stride + lo;
   const float temp = temperature[r];
@@ -734,7 +737,7 @@ __global__ void __cluster_dims__(kClusterCtas, 1, 1) __launch_bounds__(kThreads)
   cluster.sync();
   float zmax = 0.f;
   int imax = -1;
-  for (int c = 0; c < kClusterCtas; ++c) {
+  for (int c = 0; c < ctas; ++c) {
     const ClusterScratch* o = cluster.map_shared_rank(&cs, c);
     const float ov = o->am_val;
     const int oi = o->am_idx;
@@ -844,7 +847,7 @@ __global__ void __cluster_dims__(kClusterCtas, 1, 1) __launch_bounds__(kThreads)
     if (threadIdx.x == 0) cs.ties_local = here;
     cluster.sync();
     int before = 0, owner = -1;
-    for (int c2 = 0; c2 < kClusterCtas; ++c2) {
+    for (int c2 = 0; c2 < ctas; ++c2) {
       const unsigned t = cluster.map_shared_rank(&cs, c2)->ties_local;
       if (owner < 0 && have > 0 && rnk < before + (int)t) owner = c2;
       if (owner < 0) before += (int)t;
@@ -1025,18 +1028,33 @@ extern "C" int roost_sample(const float* logits, int64_t stride, int rows, int v
                 "sample: a table is not aligned to its element size");
   // a cluster of CTAs a row while a row's eighth fits a CTA's shared memory (and the vocabulary is worth eight CTAs);
   // else a block a row over the workspace
-  if (vocab >= 4096 && vocab <= kClusterCtas * kSliceFloats && rows <= 65535 / kClusterCtas * kClusterCtas) {
-    const int span = (((vocab + kClusterCtas - 1) / kClusterCtas) + 3) & ~3;
-    const size_t smem = (size_t)span * sizeof(float);
+  // measured at 151,936 tokens: 8 rows 115 us and 16 rows 204 us with clusters of eight; 17 and 32 rows 137 us, 64 rows
+  // 255 us with clusters of four (450 us with eight)
+  const int ctas = rows <= 8 ? kClusterMaxCtas : kClusterMinCtas;
+  const int slice_cap = ctas == kClusterMaxCtas ? kSliceFloats8 : kSliceFloats4;
+  if (vocab >= 4096 && vocab <= ctas * slice_cap && rows <= 65535 / ctas * ctas) {
+    const int span = (((vocab + ctas - 1) / ctas) + 3) & ~3;
     static bool attr_set[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-      cudaFuncSetAttribute(sample_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(kSliceFloats * sizeof(float)));
+      cudaFuncSetAttribute(sample_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(kSliceFloats4 * sizeof(float)));
       attr_set[dev] = true;
     }
-    sample_cluster_kernel<<<rows * kClusterCtas, kThreads, smem, (cudaStream_t)stream>>>(logits, (long long)stride, vocab, temperature, top_k, top_p,
-                                                                                       min_p, (const unsigned*)seeds, (const unsigned*)offsets, ids);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(rows * ctas);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = (size_t)span * sizeof(float);
+    cfg.stream = (cudaStream_t)stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)ctas;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaLaunchKernelEx(&cfg, sample_cluster_kernel, logits, (long long)stride, vocab, temperature, top_k, top_p, min_p, (const unsigned*)seeds,
+                       (const unsigned*)offsets, ids);
     return check_launch("sample (cluster)");
   }
   sample_kernel<<<rows, kThreads, 0, (cudaStream_t)stream>>>(logits, (long long)stride, vocab, temperature, top_k, top_p, min_p,

@@ -384,6 +384,13 @@ def test_sampler_matches_the_plain_sampler(kernels, vocab):
     # a row's token does not depend on the batch it is in
     one = kernels.sample(logits[7:8].cuda(), t[7:8].cuda(), k[7:8].cuda(), p[7:8].cuda(), mp[7:8].cuda(), seeds[7:8].cuda(), offsets[7:8].cuda())
     assert one.cpu().tolist() == [got[7]]
+    # nor on how many CTAs share a row: up to eight rows a launch take clusters of eight, more take clusters of four,
+    # and every sum is a sum of integers
+    def twice(x):
+        return torch.cat([x, x]).cuda()
+    both = kernels.sample(twice(logits[:8]), twice(t[:8]), twice(k[:8]), twice(p[:8]), twice(mp[:8]), twice(seeds[:8]), twice(offsets[:8])).cpu().tolist()
+    few = kernels.sample(logits[:8].cuda(), t[:8].cuda(), k[:8].cuda(), p[:8].cuda(), mp[:8].cuda(), seeds[:8].cuda(), offsets[:8].cuda()).cpu().tolist()
+    assert both[:8] == both[8:] == few == got[:8]
 
 
 # ------------------------------------------------------------------------------------------ tensor-core attention (bfloat16)
