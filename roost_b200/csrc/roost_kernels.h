@@ -17,7 +17,7 @@
 extern "C" {
 #endif
 
-#define ROOST_ABI_VERSION 10
+#define ROOST_ABI_VERSION 11
 
 #define ROOST_OK 0
 #define ROOST_ERR_INVALID 1      /* an argument is out of range or inconsistent; nothing was launched */
@@ -228,14 +228,15 @@ int roost_sample(const float* logits, int64_t stride, int rows, int vocab, const
 /* What the reference's sampler does beside the draw (src/Starlings.Roost.Ops/CpuOps.Sampling.cs:10-46), in its float32 form.
  * roost_sample_penalise: out[r, v] (rows * vocab floats) = logits[r, v] with the repetition, frequency and presence
  * penalties of row r applied for the tokens counted in counts[row_slot[r], :] (int32 [slots, vocab]: the request's output
- * so far) or named by prompt_bits[row_slot[r], :] (bit v % 32 of word v / 32 of (vocab + 31) / 32 words a slot); a row
+ * so far) or named by prompt_bits[row_slot[r], :] (bit v % 32 of word v / 32 of (vocab + 31) / 32 words a slot), and
+ * then -inf where the token's bit in mask_bits[row_slot[r], :] is 0 (mask_bits may be null: no token is removed); a row
  * with row_slot < 0 is copied. roost_sample_count_tokens: counts[row_slot[r], ids[r]] += 1. roost_sample_prompt_bits: sets
  * the bits of n token ids in one slot's words. roost_sample_logprobs: logprob[r] = log-softmax of the raw logits of row r
  * at ids[r] (-inf for id -1; logprob may be null), and the `top` highest raw logits of the row, ties to the lower index,
  * with their log-softmax (id -1 and -inf where the row has fewer non-NaN logits). */
 int roost_sample_penalise(const float* logits, int64_t stride, int rows, int vocab, float* out, const int32_t* counts,
-                          const uint32_t* prompt_bits, const int32_t* row_slot, const float* repetition, const float* presence,
-                          const float* frequency, roost_stream_t stream);
+                          const uint32_t* prompt_bits, const uint32_t* mask_bits, const int32_t* row_slot, const float* repetition,
+                          const float* presence, const float* frequency, roost_stream_t stream);
 int roost_sample_count_tokens(int32_t* counts, int vocab, const int32_t* row_slot, const int32_t* ids, int rows, roost_stream_t stream);
 int roost_sample_prompt_bits(uint32_t* bits, const int32_t* ids, int n, int vocab, roost_stream_t stream);
 int roost_sample_logprobs(const float* logits, int64_t stride, int rows, int vocab, const int32_t* ids, float* logprob, int top,

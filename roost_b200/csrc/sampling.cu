@@ -870,11 +870,13 @@ __global__ void __launch_bounds__(kThreads)
 // The reference's penalties, in its float32 form (src/Starlings.Roost.Ops/CpuOps.Sampling.cs:195-237: separate divides,
 // multiplies and subtracts, in vLLM's order): with c the token's count in the request's output so far and `seen` true when
 // c > 0 or the token is in the prompt, a seen logit x becomes x / repetition if it is above 0 and x * repetition otherwise;
-// then x - frequency * c; then, when c > 0, x - presence. A row whose slot is negative is copied as it is.
+// then x - frequency * c; then, when c > 0, x - presence. After the penalties a token whose bit is 0 in the slot's mask
+// (bit v % 32 of word v / 32) is removed (-inf), as the reference removes it (:18-19). A row whose slot is negative is
+// copied as it is.
 __global__ void penalise_kernel(const float* __restrict__ logits, long long stride, int vocab, float* __restrict__ out,
-                                const int* __restrict__ counts, const unsigned* __restrict__ prompt_bits, int words,
-                                const int* __restrict__ row_slot, const float* __restrict__ repetition, const float* __restrict__ presence,
-                                const float* __restrict__ frequency) {
+                                const int* __restrict__ counts, const unsigned* __restrict__ prompt_bits, const unsigned* __restrict__ mask_bits,
+                                int words, const int* __restrict__ row_slot, const float* __restrict__ repetition,
+                                const float* __restrict__ presence, const float* __restrict__ frequency) {
   const int r = blockIdx.y;
   const int v = blockIdx.x * blockDim.x + threadIdx.x;
   if (v >= vocab) return;
@@ -889,6 +891,7 @@ __global__ void penalise_kernel(const float* __restrict__ logits, long long stri
     }
     x = __fsub_rn(x, __fmul_rn(frequency[r], (float)c));
     if (c > 0) x = __fsub_rn(x, presence[r]);
+    if (mask_bits != nullptr && ((mask_bits[(size_t)slot * words + (v >> 5)] >> (v & 31)) & 1u) == 0u) x = -INFINITY;
   }
   out[(size_t)r * vocab + v] = x;
 }
@@ -1063,14 +1066,15 @@ extern "C" int roost_sample(const float* logits, int64_t stride, int rows, int v
 }
 
 extern "C" int roost_sample_penalise(const float* logits, int64_t stride, int rows, int vocab, float* out, const int32_t* counts,
-                                     const uint32_t* prompt_bits, const int32_t* row_slot, const float* repetition, const float* presence,
-                                     const float* frequency, roost_stream_t stream) {
+                                     const uint32_t* prompt_bits, const uint32_t* mask_bits, const int32_t* row_slot, const float* repetition,
+                                     const float* presence, const float* frequency, roost_stream_t stream) {
   ROOST_REQUIRE(rows >= 0 && vocab > 0 && stride >= vocab, "sample_penalise: rows, vocab and stride must be consistent");
   ROOST_REQUIRE(logits && out && counts && prompt_bits && row_slot && repetition && presence && frequency, "sample_penalise: a table is null");
   if (rows == 0) return ROOST_OK;
   if (rows > 65535) return fail(ROOST_ERR_UNSUPPORTED, "sample_penalise: more than 65535 rows");
   penalise_kernel<<<dim3((vocab + 255) / 256, rows), 256, 0, (cudaStream_t)stream>>>(logits, (long long)stride, vocab, out, counts, prompt_bits,
-                                                                                    (vocab + 31) / 32, row_slot, repetition, presence, frequency);
+                                                                                    mask_bits, (vocab + 31) / 32, row_slot, repetition, presence,
+                                                                                    frequency);
   return check_launch("sample_penalise");
 }
 

@@ -58,6 +58,7 @@ class GenerationOptions:
     presence_penalty: float | None = None
     logprobs: bool = False                     # the logprob of every generated token
     top_logprobs: int = 0                      # and of this many most likely alternatives (needs logprobs)
+    allowed_token_ids: tuple | None = None     # the only tokens that may be generated; None: all
 
     def sampling(self) -> SamplingParameters:
         return SamplingParameters(temperature=self.temperature or 0.0, top_p=1.0 if self.top_p is None else self.top_p,
@@ -65,7 +66,8 @@ class GenerationOptions:
                                   max_tokens=self.max_output_tokens, ignore_eos=self.ignore_eos,
                                   repetition_penalty=1.0 if self.repetition_penalty is None else self.repetition_penalty,
                                   frequency_penalty=self.frequency_penalty or 0.0, presence_penalty=self.presence_penalty or 0.0,
-                                  logprobs=self.logprobs, top_logprobs=self.top_logprobs)
+                                  logprobs=self.logprobs, top_logprobs=self.top_logprobs,
+                                  allowed_token_ids=None if self.allowed_token_ids is None else tuple(self.allowed_token_ids))
 
 
 @dataclass
@@ -133,6 +135,8 @@ class RoostEngine:
         for t in prompt_token_ids:
             if not 0 <= int(t) < vocab:
                 raise RequestError("InvalidOption", f"prompt token id {t} is outside the vocabulary of {vocab}")
+        if sampling.allowed_token_ids is not None and any(int(t) >= vocab for t in sampling.allowed_token_ids):
+            raise RequestError("InvalidOption", f"an allowed token id is outside the vocabulary of {vocab}")
         req = Request(request_id, [int(t) for t in prompt_token_ids], sampling, tuple(stop_token_ids), priority, deadline)
         self.scheduler.add(req)
         # a request without a seed gets an engine-chosen one (src/Starlings.Generation.Roost/RoostChatClient.cs:329)

@@ -36,6 +36,7 @@ class SamplingParameters:
     presence_penalty: float = 0.0
     logprobs: bool = False
     top_logprobs: int = 0
+    allowed_token_ids: tuple | None = None    # the only tokens that may be generated (the reference's token mask); None: all
 
     MAX_TOP_LOGPROBS = 20
 
@@ -60,6 +61,8 @@ class SamplingParameters:
             raise RequestError("InvalidOption", f"top_logprobs must be in [0, {self.MAX_TOP_LOGPROBS}]; got {self.top_logprobs}")
         if self.top_logprobs > 0 and not self.logprobs:
             raise RequestError("InvalidOption", "top_logprobs needs logprobs set to true")
+        if self.allowed_token_ids is not None and (not self.allowed_token_ids or any(int(t) < 0 for t in self.allowed_token_ids)):
+            raise RequestError("InvalidOption", "allowed_token_ids must name at least one token and no negative id")
 
     @property
     def greedy(self) -> bool:
@@ -67,7 +70,9 @@ class SamplingParameters:
 
     @property
     def penalised(self) -> bool:
-        return self.repetition_penalty != 1.0 or self.frequency_penalty != 0.0 or self.presence_penalty != 0.0
+        """The request's logits are changed before the draw (penalties, or tokens removed): it has a slot of sampler state."""
+        return (self.repetition_penalty != 1.0 or self.frequency_penalty != 0.0 or self.presence_penalty != 0.0
+                or self.allowed_token_ids is not None)
 
 
 GREEDY = SamplingParameters(temperature=0.0)

@@ -13,7 +13,7 @@ import torch
 
 from . import build
 
-ABI_VERSION = 10
+ABI_VERSION = 11
 F32, BF16 = 0, 1
 
 
@@ -78,7 +78,8 @@ _SIGNATURES = {
     "roost_attention_decode_cluster": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                        c_int, c_int, c_int, c_int, ctypes.c_longlong, c_float, c_int, c_void_p],
     "roost_attention_decode_cluster_supported": [c_int, c_int, ctypes.c_longlong, c_int, c_void_p, c_void_p],
-    "roost_sample_penalise": [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+    "roost_sample_penalise": [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                              c_void_p],
     "roost_sample_count_tokens": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p],
     "roost_sample_prompt_bits": [c_void_p, c_void_p, c_int, c_int, c_void_p],
     "roost_sample_logprobs": [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p],
@@ -512,10 +513,11 @@ class KernelLibrary:
                    _ptr(min_p), _ptr(seeds), _ptr(offsets), _ptr(workspace), _ptr(ids), _stream())
         return ids
 
-    def sample_penalise(self, logits, counts, prompt_bits, row_slot, repetition, presence, frequency) -> torch.Tensor:
+    def sample_penalise(self, logits, counts, prompt_bits, row_slot, repetition, presence, frequency, mask_bits=None) -> torch.Tensor:
         """The rows of ``logits`` with the reference's repetition, frequency and presence penalties applied: counts
         [slots, vocab] int32 (the requests' output tokens so far), prompt_bits [slots, (vocab + 31) // 32] int32 (the
-        prompts' tokens), row_slot [rows] int32 (-1: the row is copied as it is), the penalties float32 [rows]."""
+        prompts' tokens), row_slot [rows] int32 (-1: the row is copied as it is), the penalties float32 [rows]; then
+        -inf where a token's bit in mask_bits (shaped as prompt_bits; None: every token stays) is 0."""
         _need(logits, "logits", torch.float32); _need(counts, "counts", torch.int32); _need(prompt_bits, "prompt_bits", torch.int32)
         R, V = logits.shape
         if counts.shape[1] != V or prompt_bits.shape != (counts.shape[0], (V + 31) // 32):
@@ -526,8 +528,12 @@ class KernelLibrary:
             if t.numel() != R:
                 raise KernelError(f"sample_penalise: {n} has {t.numel()} entries for {R} rows")
         out = torch.empty((R, V), dtype=torch.float32, device=logits.device)
-        self._call("roost_sample_penalise", _ptr(logits), logits.stride(0), R, V, _ptr(out), _ptr(counts), _ptr(prompt_bits), _ptr(row_slot),
-                   _ptr(repetition), _ptr(presence), _ptr(frequency), _stream())
+        if mask_bits is not None:
+            _need(mask_bits, "mask_bits", torch.int32)
+            if mask_bits.shape != prompt_bits.shape:
+                raise KernelError("sample_penalise: mask_bits must be shaped as prompt_bits")
+        self._call("roost_sample_penalise", _ptr(logits), logits.stride(0), R, V, _ptr(out), _ptr(counts), _ptr(prompt_bits), _ptr(mask_bits),
+                   _ptr(row_slot), _ptr(repetition), _ptr(presence), _ptr(frequency), _stream())
         return out
 
     def sample_count_tokens(self, counts, row_slot, ids) -> None:

@@ -11,7 +11,8 @@ preempted and recomputed draws the same tokens again
 
 Penalties (src/Starlings.Roost.Ops/CpuOps.Sampling.cs:13-17,195-237) need, per request, how often each token was
 generated and which tokens its prompt holds. Both live on the device, one slot a request that asked for penalties: a
-row of int32 counts over the vocabulary and a row of bits. They are brought up to date from the request's accepted
+row of int32 counts over the vocabulary and a row of bits. A third row of bits is the request's token mask (:18-19): the
+tokens it allows; the others are removed after the penalties. They are brought up to date from the request's accepted
 tokens at the start of every call (usually one token), so a step that is rolled back or a request that is preempted and
 recomputed counts nothing twice. Logprobs (:166-176,516-603) are the log-softmax of the raw logits, before penalties and
 temperature.
@@ -53,7 +54,8 @@ class Sampler:
         self.max_requests = max_requests
         self._workspace: torch.Tensor | None = None
         self._counts: torch.Tensor | None = None      # int32 [max_requests, vocab]
-        self._bits: torch.Tensor | None = None        # int32 [max_requests, (vocab + 31) // 32]
+        self._bits: torch.Tensor | None = None        # int32 [max_requests, (vocab + 31) // 32]: the prompts' tokens
+        self._mask: torch.Tensor | None = None        # the same shape: the tokens a request allows (all ones: every token)
         self._slots: dict = {}                        # request id -> [slot, output tokens counted so far]
         self._free: list[int] = []
         self.extras = SampleExtras()                  # of the last call
@@ -76,6 +78,7 @@ class Sampler:
         if self._counts is None or self._counts.shape[1] != vocab:
             self._counts = torch.zeros((self.max_requests, vocab), dtype=torch.int32, device=self.device)
             self._bits = torch.zeros((self.max_requests, (vocab + 31) // 32), dtype=torch.int32, device=self.device)
+            self._mask = torch.full((self.max_requests, (vocab + 31) // 32), -1, dtype=torch.int32, device=self.device)
             self._slots.clear()
             self._free = list(range(self.max_requests - 1, -1, -1))
         slots, new_slots, new_ids = [], [], []
@@ -94,6 +97,13 @@ class Sampler:
                 self._bits[entry[0]].zero_()
                 if r.prompt:
                     self.kernels.sample_prompt_bits(self._bits[entry[0]], self._to_device(r.prompt, torch.int32))
+                if r.params.allowed_token_ids is not None:
+                    if max(r.params.allowed_token_ids) >= vocab:
+                        raise ValueError(f"allowed token id {max(r.params.allowed_token_ids)} is outside the vocabulary of {vocab}")
+                    self._mask[entry[0]].zero_()
+                    self.kernels.sample_prompt_bits(self._mask[entry[0]], self._to_device(list(r.params.allowed_token_ids), torch.int32))
+                else:
+                    self._mask[entry[0]].fill_(-1)
             slot, counted = entry
             if counted > len(r.output):      # cannot be: accepted tokens are never taken back
                 raise RuntimeError("a request's output shrank under its penalty counts")
@@ -123,7 +133,7 @@ class Sampler:
             table[3 * S : 4 * S] = np.asarray([r.params.frequency_penalty for r in rows], np.float32).view(np.int32)
             dev = self._to_device(table, torch.int32)
             logits = self.kernels.sample_penalise(logits, self._counts, self._bits, dev[0:S], dev[S : 2 * S].view(torch.float32),
-                                                  dev[2 * S : 3 * S].view(torch.float32), dev[3 * S : 4 * S].view(torch.float32))
+                                                  dev[2 * S : 3 * S].view(torch.float32), dev[3 * S : 4 * S].view(torch.float32), self._mask)
         ids = self._draw(logits, rows)
         if any(r.params.logprobs for r in rows):
             top = max(r.params.top_logprobs for r in rows)

@@ -108,7 +108,7 @@ class FakeKernels:
     def argmax(self, logits):
         return torch.tensor([plain.sample_row(r.tolist(), 0.0) for r in logits], dtype=torch.int32)
 
-    def sample_penalise(self, logits, counts, prompt_bits, row_slot, repetition, presence, frequency):
+    def sample_penalise(self, logits, counts, prompt_bits, row_slot, repetition, presence, frequency, mask_bits=None):
         out = logits.clone()
         V = logits.shape[1]
         for r in range(logits.shape[0]):
@@ -119,6 +119,11 @@ class FakeKernels:
             words = prompt_bits[slot].tolist()
             prompt = [v for v in range(V) if (words[v >> 5] >> (v & 31)) & 1]
             out[r] = torch.tensor(plain.penalise_row(logits[r].tolist(), c, prompt, float(repetition[r]), float(frequency[r]), float(presence[r])))
+            if mask_bits is not None:
+                allowed = mask_bits[slot].tolist()
+                for v in range(V):
+                    if not (allowed[v >> 5] >> (v & 31)) & 1:
+                        out[r, v] = float("-inf")
         return out
 
     def sample_count_tokens(self, counts, row_slot, ids):

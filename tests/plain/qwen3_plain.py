@@ -348,6 +348,13 @@ def penalise_row(logits, counts: dict, prompt_tokens, repetition: float = 1.0, f
     return z
 
 
+def mask_row(logits, allowed_token_ids):
+    """Tokens outside the mask are removed before the softmax, after the penalties
+    (src/Starlings.Roost.Ops/CpuOps.Sampling.cs:18-19,240-262): here they become -inf, which the sampler never draws."""
+    allowed = set(allowed_token_ids)
+    return [x if v in allowed else -math.inf for v, x in enumerate(logits)]
+
+
 def log_norm(logits):
     """(max, log of the sum of exp(x - max)) over the non-NaN raw logits (src/Starlings.Roost.Ops/CpuOps.Sampling.cs:516-537)."""
     mx = -math.inf

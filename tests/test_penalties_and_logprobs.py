@@ -80,6 +80,16 @@ def test_penalty_kernels(kernels, vocab):
     pres = torch.tensor([0.4, 0.0, -0.5, 1.0, 0.25])
     freq = torch.tensor([0.3, 0.0, 0.1, 2.0, -0.2])
     got = kernels.sample_penalise(logits.cuda(), counts, bits, torch.tensor(row_slot, dtype=torch.int32).cuda(), rep.cuda(), pres.cuda(), freq.cuda()).cpu()
+    # with a mask: slot 2 allows four tokens, the other slots all of them
+    mask = torch.full_like(bits, -1)
+    mask[2].zero_()
+    kernels.sample_prompt_bits(mask[2], torch.tensor([0, 1, 33, vocab - 1], dtype=torch.int32).cuda())
+    masked = kernels.sample_penalise(logits.cuda(), counts, bits, torch.tensor(row_slot, dtype=torch.int32).cuda(), rep.cuda(), pres.cuda(), freq.cuda(),
+                                     mask).cpu()
+    keep = torch.zeros(vocab, dtype=torch.bool)
+    keep[[0, 1, 33, vocab - 1]] = True
+    assert torch.equal(masked[2][keep], got[2][keep]) and bool(torch.isinf(masked[2][~keep]).all()) and bool((masked[2][~keep] < 0).all())
+    assert torch.equal(masked[[0, 1, 3, 4]], got[[0, 1, 3, 4]])
     for r, slot in enumerate(row_slot):
         if slot < 0:
             assert torch.equal(got[r], logits[r])
@@ -180,6 +190,55 @@ def test_generation_with_penalties_and_logprobs_follows_the_plain_functions(tiny
     assert bare.token_ids != outs[0].token_ids
     # every slot of counts came back
     assert not engine.sampler._slots and len(engine.sampler._free) == engine.sampler.max_requests
+
+
+def test_a_token_mask_keeps_generation_inside_the_allowed_tokens(tiny_model_dirs, backend):
+    """Greedy and sampled requests that allow a handful of tokens: every generated token is one of them and is the plain
+    choice among them (penalties first, then the mask); the logprob is still that of the raw logits; a request beside
+    them is not touched. A mask that names a token outside the vocabulary is refused at admission."""
+    kind, dtype = backend
+    t = TINY["B"]
+    model = H.make_model(tiny_model_dirs["B"], dtype, kind)
+    engine = RoostEngine(model, page_size=t["page_size"], attention_blocks=64, max_sequences=8, max_tokens=48)
+    V = t["config"]["vocab_size"]
+    prompts = [H.random_ids(n, V, 350 + n) for n in (7, 15, 11)]
+    allowed = [(3, 31, 32, 33, V - 1, 100), tuple(range(40, 60)), None]
+    opts = [GenerationOptions(max_output_tokens=16, ignore_eos=True, allowed_token_ids=allowed[0], frequency_penalty=1.5, logprobs=True),
+            GenerationOptions(max_output_tokens=16, ignore_eos=True, temperature=1.0, seed=5, allowed_token_ids=allowed[1]),
+            GenerationOptions(max_output_tokens=16, ignore_eos=True)]
+    outs = engine.generate(prompts, opts)
+    bare = engine.generate(prompts[2:], opts[2:])[0]
+    assert outs[2].token_ids == bare.token_ids or dtype == torch.bfloat16
+    cfg, w = plain.load_model_dir(tiny_model_dirs["B"])
+    if dtype == torch.bfloat16:
+        w = {k: (v.to(torch.bfloat16).double() if v.dim() >= 2 else v) for k, v in w.items()}
+    compared = 0
+    for prompt, o, out, allow in zip(prompts[:2], opts[:2], outs[:2], allowed[:2]):
+        assert set(out.token_ids) <= set(allow)
+        sp = o.sampling()
+        seq, counts = list(prompt), {}
+        for n, tok in enumerate(out.token_ids):
+            raw = plain.forward_logits(cfg, w, seq)[-1].tolist()
+            z = plain.mask_row(plain.penalise_row(raw, counts, prompt, sp.repetition_penalty, sp.frequency_penalty, sp.presence_penalty), allow)
+            if sp.greedy:
+                order = sorted(allow, key=lambda v: (-z[v], v))
+                if z[order[0]] - z[order[1]] > (1e-3 if dtype == torch.float32 else 0.15):
+                    assert tok == order[0], f"token {n}: engine {tok}, plain {order[0]}"
+                    compared += 1
+                assert abs(out.logprobs[n] - plain.logprob_at(raw, tok)) < (1e-4 if dtype == torch.float32 else 0.15) * (1 + abs(out.logprobs[n]))
+            elif dtype == torch.float32:
+                want, detail = plain.sample_row(z, sp.temperature, sp.top_k, sp.top_p, sp.min_p, o.seed, n, return_detail=True)
+                if detail["margin"] > 1e-3:
+                    assert tok == want, f"token {n}: engine {tok}, plain {want}"
+                    compared += 1
+            counts[tok] = counts.get(tok, 0) + 1
+            seq.append(tok)
+    assert compared >= (20 if dtype == torch.float32 else 8), compared
+    with pytest.raises(RequestError):
+        engine.add_request(prompts[0], GenerationOptions(allowed_token_ids=(1, V)).sampling())
+    with pytest.raises(RequestError):
+        engine.add_request(prompts[0], GenerationOptions(allowed_token_ids=()).sampling())
+    assert not engine.sampler._slots
 
 
 def test_a_request_with_penalties_draws_the_same_tokens_alone_in_a_batch_and_after_preemption(tiny_model_dirs, backend):
