@@ -379,6 +379,9 @@ def main() -> int:
     model, cfg = build_model(args.layers, torch.bfloat16, sizes=sizes)
     tps, ms, launches, clocks = timed_decode(model, args.batch, args.context, args.steps, warmup)
     roof = decode_roofline(cfg, args.batch, args.context, ms, pk)
+    # (the same settling as before the end-to-end run: the contexts' prefill at full power leaves the device for some
+    # seconds in a state in which every kernel runs a few percent slower, at unchanged clock readings)
+    time.sleep(E2E_SETTLE_S)
     pre_ms = timed_prefill(model, args.prefill_tokens)
     points, detail = {}, {}
     if not args.skip_points:
@@ -404,7 +407,7 @@ def main() -> int:
                    "q_heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
                    "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"], "page_size": PAGE,
                    "l2": "inputs larger than L2: each step streams all weights (>10 GB) from HBM", "peaks": pk_kind},
-        "prefill": prefill_record(cfg, args.prefill_tokens, pre_ms, pk),
+        "prefill": dict(prefill_record(cfg, args.prefill_tokens, pre_ms, pk), settle_s=E2E_SETTLE_S),
         "roofline": roof,
         "points": points, "points_detail": detail, "clocks": clocks,
         # kernels of this repository's library launched inside the timed region, and the cuBLAS products beside them
