@@ -26,6 +26,12 @@ class GatedMlp(FeedForward):
         self.interleave = 128 if (not runtime.full_precision and spec.intermediate % 128 == 0 and spec.hidden % 8 == 0
                                   and hasattr(k, "gemm_tcgen05_swiglu")) else 0
         self.fused_min_rows = 256   # below this the 128-row tiles are mostly empty and the library product is faster
+        # ... and so it is while the product is small: measured on a B200, the library product followed by the SiLU kernel
+        # wins at rows x intermediate x hidden below about 2.5e10 (hidden 1024, intermediate 3072: 12.9 against 19.4 us at
+        # 512 rows, 32.5 against 39.5 at 2,048; hidden 4096, intermediate 12288: 55 against 62 us at 256 rows, even at 512)
+        # and the fused product above it (281 against 303 us at 2,048 rows of the latter; 116 against 130 us at 256 rows
+        # of hidden 5120, intermediate 25600).
+        self.fused_min_work = 2.5e10
         # few rows (decode steps): the weight-streaming product can apply the activation too, which saves the SiLU kernel
         # and its round trip through memory. Measured on a B200 at the 8B layer sizes the library product followed by
         # the SiLU kernel is still 2 us a layer faster, so only the "stream" policy takes this path.
@@ -52,7 +58,8 @@ class GatedMlp(FeedForward):
 
     def __call__(self, x, batch=None):
         k = self.rt.kernels
-        if self.interleave and x.shape[0] >= self.fused_min_rows and x.is_contiguous():
+        if (self.interleave and x.shape[0] >= self.fused_min_rows and x.is_contiguous()
+                and float(x.shape[0]) * self.spec.intermediate * self.spec.hidden >= self.fused_min_work):
             return self.down(k.gemm_tcgen05_swiglu(x, self.gate_up.weight))
         if (self.interleave and x.shape[0] <= self.fused_max_split_rows and x.is_contiguous()
                 and self.rt.small_gemm in self.fused_split_policies and hasattr(k, "gemm_split_swiglu")):

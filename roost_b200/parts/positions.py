@@ -30,8 +30,13 @@ class PositionEncoding(Part):
     max_positions: int = 0  # 0: unbounded
 
 
+_FREQUENCIES: dict = {}   # (theta, rotary_dim, device) -> the frequency table that equal encodings share
+
+
 class RopeNeox(PositionEncoding):
-    """f_i = theta^(-2i / rotary_dim), computed in double once at build."""
+    """f_i = theta^(-2i / rotary_dim), computed in double once at build. Encodings of equal theta and width on one device
+    hand out the same tensor: a step keeps its table of cosines and sines by that tensor, so that the layers of a model,
+    each with an encoding of its own, share one table a step."""
 
     def __init__(self, spec: PositionSpec, runtime: Runtime):
         if spec.rotary_dim <= 0 or spec.rotary_dim % 2:
@@ -40,8 +45,11 @@ class RopeNeox(PositionEncoding):
             raise ValueError(f"rope_neox: theta {spec.theta} must be positive")
         self.spec = spec
         self.max_positions = spec.max_positions
-        i = torch.arange(spec.rotary_dim // 2, dtype=torch.float64)
-        self.inv_freq = torch.pow(torch.tensor(float(spec.theta), dtype=torch.float64), -2.0 * i / spec.rotary_dim).to(runtime.device)
+        key = (float(spec.theta), spec.rotary_dim, str(torch.device(runtime.device)))
+        if key not in _FREQUENCIES:
+            i = torch.arange(spec.rotary_dim // 2, dtype=torch.float64)
+            _FREQUENCIES[key] = torch.pow(torch.tensor(float(spec.theta), dtype=torch.float64), -2.0 * i / spec.rotary_dim).to(runtime.device)
+        self.inv_freq = _FREQUENCIES[key]
 
     def rotation(self):
         return self.inv_freq, self.spec.rotary_dim

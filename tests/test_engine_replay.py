@@ -180,6 +180,27 @@ def test_every_small_product_kernel_serves_the_engine(tiny_model_dirs, policy):
 
 
 @pytest.mark.gpu
+def test_a_long_step_makes_its_rotation_table_once_for_all_layers(tiny_model_dirs, monkeypatch):
+    """The layers have an encoding each, but equal ones share their frequencies, and a step keeps its cosines and sines
+    by them: one table a step, however many layers read it. A short step makes none."""
+    from roost_b200.engine.batch import ROTATION_TABLE_MIN_TOKENS
+    name, t = "B", TINY["B"]
+    assert t["config"]["num_hidden_layers"] > 1
+    model = H.make_model(tiny_model_dirs[name], torch.bfloat16, "gpu")
+    k = model.rt.kernels
+    made = []
+    real = k.rope_table
+    monkeypatch.setattr(k, "rope_table", lambda positions, inv_freq: (made.append(positions.numel()), real(positions, inv_freq))[1])
+    ex = StepExecutor(model, page_size=t["page_size"], num_pages=40, max_requests=4, use_graphs=False)
+    n = ROTATION_TABLE_MIN_TOKENS + 5
+    ids = H.random_ids(n + 1, t["config"]["vocab_size"], seed=45)
+    ex.step([StepEntry("r", ids[:n], [n - 1])])
+    assert made == [n]
+    ex.step([StepEntry("r", ids[n:], [0])])
+    assert made == [n]
+
+
+@pytest.mark.gpu
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
 def test_a_captured_step_filled_up_with_padding_rows(tiny_model_dirs, dtype):
     """Eleven, then nine decoding requests are served by the captured step of twelve rows. The logits are those of an

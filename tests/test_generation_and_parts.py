@@ -168,6 +168,32 @@ def test_feed_forward_part_alone(backend):
         FEED_FORWARDS.build(GatedMlpSpec(hidden=8, intermediate=8, activation="gelu"), rt)
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("rows", [3, 40, 300])
+def test_feed_forward_part_on_the_interleaved_layout(rows):
+    """An intermediate size of a multiple of 128 stores gate and up in blocks of 128; few rows take the product split over
+    clusters, more the library product and the SiLU kernel, many the fused tensor-core product (made to here: by its own
+    rule it starts at larger products). All are the same function."""
+    rt = runtime(("gpu", torch.bfloat16))
+    spec = GatedMlpSpec(hidden=136, intermediate=256)
+    g = torch.Generator().manual_seed(2)
+    gate_up = (torch.randn(512, 136, generator=g) * 0.1).to(rt.dtype)
+    down = (torch.randn(136, 256, generator=g) * 0.1).to(rt.dtype)
+    x = torch.randn(rows, 136, generator=g).to(rt.dtype)
+    want = plain.swiglu_mlp(x.double(), gate_up[:256].double(), gate_up[256:].double(), down.double())
+    outs = []
+    for work in (None, 0.0):
+        ff = FEED_FORWARDS.build(spec, rt)
+        assert ff.interleave == 128
+        if work is not None:
+            ff.fused_min_work = work
+        ff.load({"gate_up": gate_up.to(rt.device), "down": down.to(rt.device)})
+        outs.append(ff(x.to(rt.device), None))
+        assert H.scaled_error(outs[-1], want) < 2 ** -5
+    if rows < 256:
+        assert torch.equal(outs[0], outs[1])      # the threshold moves nothing below the fused product's rows
+
+
 def attention_spec(window=None, position=True):
     return AttentionSpec(hidden=48, num_heads=6, num_kv_heads=2, head_dim=16, scale=0.25, window=window,
                          qk_norm=NormSpec(size=16, eps=1e-6), position=PositionSpec(rotary_dim=16, theta=1e4) if position else None)
