@@ -149,27 +149,26 @@ __global__ void qk_norm_rope_cache_kernel(const T* __restrict__ qkv, int64_t qkv
 
 // bfloat16, every element rotated, a head of 64, 128 or 256 elements, 16-byte aligned rows, more than a few tokens.
 // A lane owns four elements of the head's first half and the four that pair with them in the second half (two 8-byte
-// accesses), so a rotation needs no exchange between lanes; D / 8 lanes serve a head slot and a warp 32 / (D / 8)
-// slots at a time; the sum of squares is reduced over the slot's lanes. A block of eight warps takes several tokens
-// in turn: the norm weights stay in registers for all of them, and the cosines and sines of the next token are
-// computed (by D / 2 of the threads, in the reference's 64-bit form) while the heads of the current one are processed.
+// accesses), so a rotation needs no exchange between lanes. D / 8 lanes serve a part of a token: some of its head slots
+// in turn, four loaded ahead; the sum of squares is reduced over the part's lanes. The part's cosines and sines (read from
+// the step's table, else computed in the reference's 64-bit form), the norm weights and the token's place in the cache
+// stay in registers, nothing goes through shared memory and no thread waits for another. A token has as many parts as
+// fill the device's thread slots once: measured on a B200 against a block that takes whole tokens in turn with their
+// table in shared memory, 15.3 against 15.2 us at 2,048 tokens of 32 + 8 + 8 heads, 5.6 against 6.6 at 512, 43 against
+// 53 at 8,192; two to six times as many parts were slower.
 template <int D>
-__global__ void __launch_bounds__(256, 4) qk_norm_rope_cache_vec_kernel(
+__global__ void __launch_bounds__(256, 4) qk_norm_rope_cache_parts_kernel(
     const __nv_bfloat16* __restrict__ qkv, int64_t qkv_stride, __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_pool,
     __nv_bfloat16* __restrict__ v_pool, const void* __restrict__ q_w, const void* __restrict__ k_w, const double* __restrict__ inv_freq,
     const int32_t* __restrict__ positions, const int32_t* __restrict__ slot_mapping, const float2* __restrict__ step_table, int tokens,
-    int tokens_per_block, int q_heads, int kv_heads, float eps, int page_size, int page_shift, int64_t pool_pages, int slots_per_token,
-    int wdtype) {
-  constexpr int kLanes = D / 8;          // lanes of a head slot
-  constexpr int kSlots = 32 / kLanes;    // head slots of a warp's pass
+    int parts, int slots_per_part, int q_heads, int kv_heads, float eps, int page_size, int page_shift, int64_t pool_pages,
+    int slots_per_token, int wdtype) {
+  constexpr int kLanes = D / 8;          // lanes of a part
   constexpr int kHalf = D / 2;
-  constexpr int kWarps = 8;
-  __shared__ float2 cos_sin[2][kHalf];
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int sub = lane / kLanes, c = lane % kLanes;   // which slot of the pass; which four pairs of its head
-  // The lanes of this thread's head slot. A pass may hold a key head beside a value head (or beside no head at all): the
-  // slots of a warp then take different branches, and an exchange may name only the lanes that take it together.
-  const unsigned slot_lanes = kLanes == 32 ? 0xffffffffu : ((1u << kLanes) - 1u) << (sub * kLanes);
+  constexpr int kAhead = 4;
+  const int lane = threadIdx.x & 31;
+  const int sub = lane / kLanes, c = lane % kLanes;   // which part of the warp's; which four pairs of a head
+  const unsigned part_lanes = kLanes == 32 ? 0xffffffffu : ((1u << kLanes) - 1u) << (sub * kLanes);
   float wq_lo[4], wq_hi[4], wk_lo[4], wk_hi[4];
 #pragma unroll
   for (int e = 0; e < 4; ++e) {
@@ -179,22 +178,26 @@ __global__ void __launch_bounds__(256, 4) qk_norm_rope_cache_vec_kernel(
     wk_hi[e] = k_w ? load_w(k_w, kHalf + 4 * c + e, wdtype) : 1.0f;
   }
   const bool normed = q_w != nullptr;
-  const double freq = (int)threadIdx.x < kHalf && step_table == nullptr ? inv_freq[threadIdx.x] : 0.0;
+  const int64_t group = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) / kLanes;
+  const int t = (int)(group / parts), part = (int)(group - (int64_t)t * parts);
   pdl_launch_dependents(3);
   pdl_wait(3);
-  const int t0 = blockIdx.x * tokens_per_block;
-  const int t1 = min(tokens, t0 + tokens_per_block);
-  auto table = [&](int t, int buf) {
-    if ((int)threadIdx.x < kHalf && step_table != nullptr) {
-      cos_sin[buf][threadIdx.x] = step_table[(size_t)t * kHalf + threadIdx.x];
-    } else if ((int)threadIdx.x < kHalf) {
-      double ang = (double)positions[t] * freq;
+  if (t >= tokens) return;   // a whole part: its lanes leave together
+  float cs[4], sn[4];
+  if (step_table != nullptr) {
+    const float4 r0 = *reinterpret_cast<const float4*>(step_table + (size_t)t * kHalf + 4 * c);
+    const float4 r1 = *reinterpret_cast<const float4*>(step_table + (size_t)t * kHalf + 4 * c + 2);
+    cs[0] = r0.x; sn[0] = r0.y; cs[1] = r0.z; sn[1] = r0.w;
+    cs[2] = r1.x; sn[2] = r1.y; cs[3] = r1.z; sn[3] = r1.w;
+  } else {
+    const double pos = (double)positions[t];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      double ang = pos * inv_freq[4 * c + e];
       ang -= 6.283185307179586476925286766559 * rint(ang * 0.15915494309189533576888376337251);
-      float sn, cs;
-      sincosf((float)ang, &sn, &cs);
-      cos_sin[buf][threadIdx.x] = make_float2(cs, sn);
+      sincosf((float)ang, &sn[e], &cs[e]);
     }
-  };
+  }
   auto unpack = [](const uint2 u, float (&v)[4]) {
     v[0] = __uint_as_float(u.x << 16); v[1] = __uint_as_float(u.x & 0xffff0000u);
     v[2] = __uint_as_float(u.y << 16); v[3] = __uint_as_float(u.y & 0xffff0000u);
@@ -203,85 +206,60 @@ __global__ void __launch_bounds__(256, 4) qk_norm_rope_cache_vec_kernel(
     const __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
     *reinterpret_cast<uint2*>(p) = make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b));
   };
-  if (t0 < t1) table(t0, 0);
-  __syncthreads();
-  for (int t = t0; t < t1; ++t) {
-    const int buf = (t - t0) & 1;
-    if (t + 1 < t1) table(t + 1, buf ^ 1);
-    float cs[4], sn[4];
-    {
-      const float4 r0 = *reinterpret_cast<const float4*>(&cos_sin[buf][4 * c]);
-      const float4 r1 = *reinterpret_cast<const float4*>(&cos_sin[buf][4 * c + 2]);
-      cs[0] = r0.x; sn[0] = r0.y; cs[1] = r0.z; sn[1] = r0.w;
-      cs[2] = r1.x; sn[2] = r1.y; cs[3] = r1.z; sn[3] = r1.w;
-    }
-    const int slot = slot_mapping ? slot_mapping[t] : -1;
-    const unsigned page = slot < 0 ? 0u : (page_shift >= 0 ? (unsigned)slot >> page_shift : (unsigned)slot / (unsigned)page_size);
-    const unsigned off = slot < 0 ? 0u : (unsigned)slot - page * (unsigned)page_size;
-    const bool cache_ok = slot >= 0 && (int64_t)page < pool_pages;
-    const __nv_bfloat16* row = qkv + (size_t)t * qkv_stride;
-    // the loads of up to three passes are issued before the first is used: enough bytes in flight to keep the memory busy
-    constexpr int kAhead = 3;
-    for (int base0 = warp * kSlots; base0 < slots_per_token; base0 += kAhead * kWarps * kSlots) {
-      uint2 raw_lo[kAhead], raw_hi[kAhead];
+  const int slot = slot_mapping ? slot_mapping[t] : -1;
+  const unsigned page = slot < 0 ? 0u : (page_shift >= 0 ? (unsigned)slot >> page_shift : (unsigned)slot / (unsigned)page_size);
+  const unsigned off = slot < 0 ? 0u : (unsigned)slot - page * (unsigned)page_size;
+  const bool cache_ok = slot >= 0 && (int64_t)page < pool_pages;
+  const __nv_bfloat16* row = qkv + (size_t)t * qkv_stride + 4 * c;
+  const int s_end = min(slots_per_token, (part + 1) * slots_per_part);
+  for (int s0 = part * slots_per_part; s0 < s_end; s0 += kAhead) {
+    uint2 raw_lo[kAhead], raw_hi[kAhead];
 #pragma unroll
-      for (int p = 0; p < kAhead; ++p) {
-        const int slot_idx = base0 + p * kWarps * kSlots + sub;
-        if (slot_idx < slots_per_token) {
-          const __nv_bfloat16* src = row + (size_t)slot_idx * D + 4 * c;
-          raw_lo[p] = *reinterpret_cast<const uint2*>(src);
-          raw_hi[p] = *reinterpret_cast<const uint2*>(src + kHalf);
-        }
-      }
-#pragma unroll
-      for (int p = 0; p < kAhead; ++p) {
-        const int slot_idx = base0 + p * kWarps * kSlots + sub;
-        if (slot_idx >= slots_per_token) continue;   // whole slots only: the lanes of a slot stay together
-        __nv_bfloat16* dst;
-        if (slot_idx >= q_heads + kv_heads) {   // a value head: copied as it is
-          if (!cache_ok) continue;
-          dst = v_pool + (((size_t)page * kv_heads + (slot_idx - q_heads - kv_heads)) * page_size + off) * D + 4 * c;
-          *reinterpret_cast<uint2*>(dst) = raw_lo[p];
-          *reinterpret_cast<uint2*>(dst + kHalf) = raw_hi[p];
-          continue;
-        }
-        float lo[4], hi[4];
-        unpack(raw_lo[p], lo);
-        unpack(raw_hi[p], hi);
-        const bool is_q = slot_idx < q_heads;
-        float inv = 1.0f;
-        if (normed) {
-          float ss = 0.f;
-#pragma unroll
-          for (int e = 0; e < 4; ++e) ss += lo[e] * lo[e] + hi[e] * hi[e];
-#pragma unroll
-          for (int o = kLanes / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(slot_lanes, ss, o, kLanes);
-          inv = 1.0f / sqrtf(ss / (float)D + eps);
-        }
-        float o_lo[4], o_hi[4];
-        if (is_q) {
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float x1 = lo[e] * inv * wq_lo[e], x2 = hi[e] * inv * wq_hi[e];
-            o_lo[e] = x1 * cs[e] - x2 * sn[e];
-            o_hi[e] = x2 * cs[e] + x1 * sn[e];
-          }
-          dst = q_out + ((size_t)t * q_heads + slot_idx) * D + 4 * c;
-        } else {
-          if (!cache_ok) continue;
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float x1 = lo[e] * inv * wk_lo[e], x2 = hi[e] * inv * wk_hi[e];
-            o_lo[e] = x1 * cs[e] - x2 * sn[e];
-            o_hi[e] = x2 * cs[e] + x1 * sn[e];
-          }
-          dst = k_pool + (((size_t)page * kv_heads + (slot_idx - q_heads)) * page_size + off) * D + 4 * c;
-        }
-        store_half(dst, o_lo);
-        store_half(dst + kHalf, o_hi);
+    for (int p = 0; p < kAhead; ++p) {
+      if (s0 + p < s_end) {
+        const __nv_bfloat16* src = row + (size_t)(s0 + p) * D;
+        raw_lo[p] = *reinterpret_cast<const uint2*>(src);
+        raw_hi[p] = *reinterpret_cast<const uint2*>(src + kHalf);
       }
     }
-    __syncthreads();   // the next token's table is complete; this token's is free to be written again
+#pragma unroll
+    for (int p = 0; p < kAhead; ++p) {
+      const int slot_idx = s0 + p;
+      if (slot_idx >= s_end) break;
+      __nv_bfloat16* dst;
+      if (slot_idx >= q_heads + kv_heads) {   // a value head: copied as it is
+        if (!cache_ok) continue;
+        dst = v_pool + (((size_t)page * kv_heads + (slot_idx - q_heads - kv_heads)) * page_size + off) * D + 4 * c;
+        *reinterpret_cast<uint2*>(dst) = raw_lo[p];
+        *reinterpret_cast<uint2*>(dst + kHalf) = raw_hi[p];
+        continue;
+      }
+      float lo[4], hi[4];
+      unpack(raw_lo[p], lo);
+      unpack(raw_hi[p], hi);
+      const bool is_q = slot_idx < q_heads;
+      if (!is_q && !cache_ok) continue;
+      float inv = 1.0f;
+      if (normed) {
+        float ss = 0.f;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) ss += lo[e] * lo[e] + hi[e] * hi[e];
+#pragma unroll
+        for (int o = kLanes / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(part_lanes, ss, o, kLanes);
+        inv = 1.0f / sqrtf(ss / (float)D + eps);
+      }
+      float o_lo[4], o_hi[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float x1 = lo[e] * inv * (is_q ? wq_lo[e] : wk_lo[e]), x2 = hi[e] * inv * (is_q ? wq_hi[e] : wk_hi[e]);
+        o_lo[e] = x1 * cs[e] - x2 * sn[e];
+        o_hi[e] = x2 * cs[e] + x1 * sn[e];
+      }
+      dst = is_q ? q_out + ((size_t)t * q_heads + slot_idx) * D + 4 * c
+                 : k_pool + (((size_t)page * kv_heads + (slot_idx - q_heads)) * page_size + off) * D + 4 * c;
+      store_half(dst, o_lo);
+      store_half(dst + kHalf, o_hi);
+    }
   }
 }
 
@@ -321,19 +299,28 @@ extern "C" int roost_qk_norm_rope_cache(const void* qkv, int64_t qkv_stride, voi
   // bfloat16 heads of 64, 128 or 256 elements, all rotated, from 64 tokens on: the vector kernel
   if (dtype == ROOST_BF16 && vector_ok && rotary_dim == head_dim && tokens >= 64 && (head_dim == 64 || head_dim == 128 || head_dim == 256) &&
       (q_w == nullptr) == (k_w == nullptr)) {
-    const int per_block = tokens >= 1024 ? 4 : (tokens >= 256 ? 2 : 1);   // measured: 1, 2 and 4 within 10 %, 8 a third slower
-    const dim3 vgrid((tokens + per_block - 1) / per_block);
+    // as many parts a token as fill the device's thread slots once, at most one a head slot
+    const int lanes = head_dim / 8;
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    int64_t parts = (int64_t)sms * 1024 / ((int64_t)tokens * lanes);
+    parts = parts < 1 ? 1 : (parts > slots ? slots : parts);
+    const int per_part = (int)((slots + parts - 1) / parts);
+    parts = (slots + per_part - 1) / per_part;
+    const int64_t blocks = ((int64_t)tokens * parts * lanes + 255) / 256;
+    if (blocks > 0x7fffffff) return fail(ROOST_ERR_UNSUPPORTED, "qk_norm_rope_cache: more blocks than a grid holds");
     int page_shift = -1;   // pages of a power of two of tokens: a shift instead of a division
     for (int b = 0; b < 31 && page_size > 0; ++b)
       if (page_size == (1 << b)) page_shift = b;
     auto launch = [&](auto kernel) {
-      launch_kernel(kernel, vgrid, dim3(256), 0, (cudaStream_t)stream, (const __nv_bfloat16*)qkv, qkv_stride, (__nv_bfloat16*)q_out,
-                    (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, q_w, k_w, inv_freq, positions, slot_mapping, (const float2*)cos_sin, tokens,
-                    per_block, q_heads, kv_heads, eps, page_size, page_shift, pool_pages, slots, wdtype);
+      launch_kernel(kernel, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, (const __nv_bfloat16*)qkv, qkv_stride,
+                    (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, q_w, k_w, inv_freq, positions, slot_mapping,
+                    (const float2*)cos_sin, tokens, (int)parts, per_part, q_heads, kv_heads, eps, page_size, page_shift, pool_pages, slots,
+                    wdtype);
     };
-    if (head_dim == 64) launch(qk_norm_rope_cache_vec_kernel<64>);
-    else if (head_dim == 128) launch(qk_norm_rope_cache_vec_kernel<128>);
-    else launch(qk_norm_rope_cache_vec_kernel<256>);
+    if (head_dim == 64) launch(qk_norm_rope_cache_parts_kernel<64>);
+    else if (head_dim == 128) launch(qk_norm_rope_cache_parts_kernel<128>);
+    else launch(qk_norm_rope_cache_parts_kernel<256>);
     return check_launch("qk_norm_rope_cache");
   }
   ROOST_DISPATCH_DTYPE(dtype, T, {

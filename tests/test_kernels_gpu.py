@@ -135,10 +135,13 @@ def test_qk_norm_rope_cache(kernels, dtype, nq, nkv, d, rot, page):
                                                      # head slots that share a warp's pass and take different branches: key
                                                      # heads beside value heads, a query head beside a key head, a value head
                                                      # and an empty slot
-                                                     (150, 4, 2, 64, 16, "same"), (70, 5, 1, 64, 16, "float32"), (90, 3, 1, 128, 16, "same")])
+                                                     (150, 4, 2, 64, 16, "same"), (70, 5, 1, 64, 16, "float32"), (90, 3, 1, 128, 16, "same"),
+                                                     # so many tokens that one part serves all the head slots of a token, and
+                                                     # parts of several slots whose last is shorter
+                                                     (9600, 2, 1, 128, 16, "same"), (2048, 7, 2, 128, 16, "same")])
 def test_qk_norm_rope_cache_of_many_tokens(kernels, dtype, T, nq, nkv, d, page, weights):
-    """Steps of many tokens (bfloat16 heads of 64, 128 or 256 take a kernel of their own): several tokens a block, some
-    tokens skipped (slot -1), slots scattered over the pool, norm weights in either dtype or none."""
+    """Steps of many tokens (bfloat16 heads of 64, 128 or 256 take a kernel of their own): a token's head slots in one or
+    several parts, some tokens skipped (slot -1), slots scattered over the pool, norm weights in either dtype or none."""
     eps, theta = 1e-6, 1e6
     g = torch.Generator().manual_seed(T + d)
     pages = -(-T // page) + 3
