@@ -10,9 +10,11 @@ import random
 import pytest
 import torch
 
+from roost_b200 import GenerationOptions, RoostEngine
 from roost_b200.engine.executor import StepExecutor
 from roost_b200.weights.random_init import write_random_model
 from tests import helpers as H
+from tests.plain import qwen3_plain as plain
 
 pytestmark = pytest.mark.gpu
 
@@ -56,3 +58,61 @@ def test_a_random_configuration_in_random_portions_and_batches(tmp_path, seed):
         if dtype == torch.bfloat16:
             assert H.rms_error(got[rid], want) <= H.BF16_RMS_BOUND, (rid, cfg, page, lens)
     ex.close()
+
+
+@pytest.mark.parametrize("seed", [9006, 9007, 9012, 9043, 9139, 9142, 9144, 9230, 9232])
+def test_a_random_configuration_through_the_entry_point(tmp_path, seed):
+    """The same draws through ``RoostEngine.generate``: three to eleven requests, greedy and sampled (temperature, top-k,
+    top-p, min-p, a seed each), under random limits of rows and tokens a step and with as few pages as the largest request
+    needs or more, so that prompts are cut, requests wait, some are preempted and computed again, and decode steps are
+    started ahead. Every token is the plain implementation's choice on the engine's own history, unless the plain top two
+    (or the draw and the edge of its token's interval) are too close to call. The seeds are a sample of a run of some
+    thousands; what differed there were draws between two tokens of equal probability to seven digits, or a kept set whose
+    edge lay within 1e-4 of top-p or of the min-p floor."""
+    rng, cfg, page, dtype, _, _ = draw(seed)
+    V = cfg["vocab_size"]
+    prompts = [H.random_ids(rng.choice([rng.randrange(1, 20), rng.randrange(20, 120), rng.randrange(120, 300)]), V, seed * 17 + i)
+               for i in range(rng.randrange(3, 12))]
+    opts = []
+    for i in range(len(prompts)):
+        new = rng.choice([1, 2, rng.randrange(3, 30), rng.randrange(30, 70)])
+        if rng.random() < 0.4:
+            opts.append(GenerationOptions(max_output_tokens=new, ignore_eos=True, temperature=rng.choice([0.5, 0.9, 1.3]), top_k=rng.choice([0, 0, 5, 40]),
+                                          top_p=rng.choice([1.0, 0.9, 0.5]), min_p=rng.choice([0.0, 0.0, 0.05]), seed=seed * 100 + i))
+        else:
+            opts.append(GenerationOptions(max_output_tokens=new, ignore_eos=True))
+    pages_of = [-(-(len(p) + o.max_output_tokens + 1) // page) for p, o in zip(prompts, opts)]
+    biggest, total = max(pages_of), sum(pages_of)
+    blocks = rng.choice([biggest + 1, biggest + 3, (biggest + total) // 2, total + 4])
+    max_seq = rng.randrange(1, 7)
+    max_tok = rng.choice([8, 16, 33, 64, 128, 256])
+    chain = rng.random() < 0.7
+    write_random_model(tmp_path, cfg, seed=seed, std=rng.choice([0.05, 0.08]), norm_std=rng.choice([0.0, 0.1]))
+    model = H.make_model(tmp_path, dtype, "gpu")
+    engine = RoostEngine(model, page_size=page, attention_blocks=blocks, max_sequences=max_seq, max_tokens=max_tok, chain_steps=chain)
+    outs = engine.generate(prompts, opts)
+    engine.check_device()
+    pc, w = plain.load_model_dir(tmp_path)
+    if dtype == torch.bfloat16:
+        w = {k: (v.to(torch.bfloat16).double() if v.dim() >= 2 else v) for k, v in w.items()}
+    compared = 0
+    for i, (p, o, out) in enumerate(zip(prompts, opts, outs)):
+        assert out.finish_reason == "length" and len(out.token_ids) == o.max_output_tokens
+        logits = plain.forward_logits(pc, w, list(p) + out.token_ids[:-1])
+        for j, tok in enumerate(out.token_ids):
+            row = logits[len(p) - 1 + j]
+            if o.temperature:
+                if dtype == torch.float32:
+                    want, detail = plain.sample_row(row.tolist(), o.temperature, o.top_k, o.top_p, o.min_p, o.seed, j, return_detail=True)
+                    if detail["margin"] > 1e-4:
+                        assert tok == want, f"request {i}, token {j}: engine {tok}, plain sampler {want} (margin {detail['margin']:.2e})"
+                        compared += 1
+            else:
+                top = row.topk(2)
+                gap = float(top.values[0] - top.values[1])
+                if gap > (1e-3 if dtype == torch.float32 else 0.15):
+                    assert tok == int(top.indices[0]), f"request {i}, token {j}: engine {tok}, plain {int(top.indices[0])} (gap {gap:.3g})"
+                    compared += 1
+    assert compared > 20
+    engine.executor.cache.check_invariants()
+    assert all(pool.used_count == 0 for pool in engine.executor.cache.pools)       # every page and slot came back
