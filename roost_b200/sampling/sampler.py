@@ -67,6 +67,16 @@ class Sampler:
         if entry is not None:
             self._free.append(entry[0])
 
+    def _grow(self) -> None:
+        """Twice as many slots. A request keeps its slot from its first sampled token to its end, also while it waits
+        (preempted, or behind requests that came later but are ordered before it), so more requests than a step has rows
+        can hold one."""
+        old = self.max_requests
+        pad = lambda t, fill: torch.cat([t, torch.full_like(t, fill)])
+        self._counts, self._bits, self._mask = pad(self._counts, 0), pad(self._bits, 0), pad(self._mask, -1)
+        self.max_requests = 2 * old
+        self._free = list(range(2 * old - 1, old - 1, -1))
+
     def _to_device(self, values, dtype) -> torch.Tensor:
         host = torch.tensor(values, dtype=dtype)
         if self.device.type == "cuda":
@@ -91,7 +101,7 @@ class Sampler:
             entry = self._slots.get(r.request_id)
             if entry is None:
                 if not self._free:
-                    raise RuntimeError(f"more than {self.max_requests} live requests ask for penalties")
+                    self._grow()
                 entry = self._slots[r.request_id] = [self._free.pop(), 0]
                 self._counts[entry[0]].zero_()
                 self._bits[entry[0]].zero_()

@@ -266,3 +266,24 @@ def test_a_request_with_penalties_draws_the_same_tokens_alone_in_a_batch_and_aft
     assert rid in roomy.sampler._slots
     roomy.cancel(rid)
     assert rid not in roomy.sampler._slots and len(roomy.sampler._free) == roomy.sampler.max_requests
+
+
+def test_more_requests_with_penalties_than_a_step_has_rows(tiny_model_dirs, backend):
+    """A request keeps its counts from its first sampled token to its end, also while it waits: preempted, its pages
+    gone, with requests that are ordered before it taking the step's rows. With two rows a step and pages for little more
+    than one request, more than two requests hold counts at a time; the tokens are those of an engine with room for all."""
+    kind, dtype = backend
+    if dtype != torch.float32:
+        pytest.skip("compared token for token: float32 only")
+    model = H.make_model(tiny_model_dirs["A"], dtype, kind)
+    V = TINY["A"]["config"]["vocab_size"]
+    prompts = [H.random_ids(n, V, 370 + n) for n in (12, 19, 5, 9)]
+    opts = [GenerationOptions(max_output_tokens=n, ignore_eos=True, repetition_penalty=1.3, frequency_penalty=0.5, temperature=t, seed=40 + i)
+            for i, (n, t) in enumerate(zip((50, 40, 36, 30), (None, 0.8, None, 0.9)))]
+    roomy = RoostEngine(model, page_size=16, attention_blocks=64, max_sequences=8, max_tokens=128)
+    want = [o.token_ids for o in roomy.generate(prompts, opts)]
+    tight = RoostEngine(model, page_size=16, attention_blocks=5, max_sequences=2, max_tokens=128)
+    got = [o.token_ids for o in tight.generate(prompts, opts)]
+    assert tight.stats()["preemptions"] > 0 and tight.sampler.max_requests > 2, "no request waited with counts of its own"
+    assert got == want
+    assert not tight.sampler._slots and len(tight.sampler._free) == tight.sampler.max_requests
