@@ -52,7 +52,7 @@ class GenerationOptions:
     min_p: float | None = None
     seed: int | None = None
     stop_token_ids: tuple = ()
-    ignore_eos: bool = False
+    ignore_eos: bool = False               # generate past the model's stop ids (stop_token_ids above still end the request)
     repetition_penalty: float | None = None   # None or 1: off
     frequency_penalty: float | None = None    # None or 0: off
     presence_penalty: float | None = None

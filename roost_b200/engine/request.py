@@ -30,7 +30,7 @@ class SamplingParameters:
     seed: int | None = None
     max_tokens: int | None = None
     min_tokens: int = 0
-    ignore_eos: bool = False
+    ignore_eos: bool = False                  # the model's stop ids do not end the request (its own stop_token_ids still do)
     repetition_penalty: float = 1.0
     frequency_penalty: float = 0.0
     presence_penalty: float = 0.0

@@ -240,8 +240,9 @@ class Scheduler:
 
     def _finish_reason(self, s: Sequence, tok: int) -> str | None:
         sp = s.request.sampling
-        if not sp.ignore_eos and s.generated >= sp.min_tokens:
-            if tok in s.request.stop_token_ids or tok in self.options.model_stop_token_ids:
+        if s.generated >= sp.min_tokens:
+            # ``ignore_eos`` switches off the model's stop ids (config.json's eos_token_id), not the request's own
+            if tok in s.request.stop_token_ids or (not sp.ignore_eos and tok in self.options.model_stop_token_ids):
                 return "stop"
         if sp.max_tokens is not None and s.generated >= sp.max_tokens:
             return "length"

@@ -78,10 +78,12 @@ def test_order_is_priority_then_deadline_then_arrival():
 
 
 def test_finishes_on_stop_token_max_tokens_and_frees_pages():
-    s, cm = make(model_stop_token_ids=(fake_token("m", 6),))
+    s, cm = make(model_stop_token_ids=(fake_token("m", 6), fake_token("i", 4)))
     s.add(req("m", 5, max_tokens=50))
     s.add(Request("r", [1, 2, 3], SamplingParameters(temperature=0.0, max_tokens=50), stop_token_ids=(fake_token("r", 5),)))
-    s.add(Request("i", [1, 2, 3], SamplingParameters(temperature=0.0, max_tokens=3, ignore_eos=True), stop_token_ids=(fake_token("i", 4),)))
+    # ignore_eos: the model's stop ids do not end the request, its own still do
+    s.add(Request("i", [1, 2, 3], SamplingParameters(temperature=0.0, max_tokens=3, ignore_eos=True)))
+    s.add(Request("j", [1, 2, 3], SamplingParameters(temperature=0.0, max_tokens=50, ignore_eos=True), stop_token_ids=(fake_token("j", 4),)))
     reasons = {}
     while s.unfinished:
         _, events = run_step(s)
@@ -89,7 +91,8 @@ def test_finishes_on_stop_token_max_tokens_and_frees_pages():
             if e.finish_reason:
                 reasons[e.request_id] = (e.finish_reason, e.token)
         cm.check_invariants()
-    assert reasons == {"m": ("stop", fake_token("m", 6)), "r": ("stop", fake_token("r", 5)), "i": ("length", fake_token("i", 5))}
+    assert reasons == {"m": ("stop", fake_token("m", 6)), "r": ("stop", fake_token("r", 5)), "i": ("length", fake_token("i", 5)),
+                       "j": ("stop", fake_token("j", 4))}
     assert cm.pools[0].free_count == cm.pools[0].capacity and not list(cm.live_requests)
 
 
