@@ -403,11 +403,11 @@ class RoostEngine:
                     if e.finish_reason is not None:
                         live = False
                         if not stop_token:
-                            tail, matched = matcher.push(detok.flush())
-                            tail += matcher.flush()
+                            tail, _ = matcher.push(detok.flush())
+                            tail += matcher.flush()     # (a stop string that waited for a longer one is decided here)
                             if tail:
                                 yield TextUpdate(tail)
-                            reason = "stop" if matched is not None else e.finish_reason
+                            reason = "stop" if matcher.matched is not None else e.finish_reason
                         else:
                             tail = matcher.flush()
                             if tail:

@@ -17,7 +17,9 @@ REPLACEMENT = "\ufffd"   # what a decoder puts where a token sequence ends insid
 class StopMatcher:
     """Finds the first stop string in text that arrives in pieces. ``push(piece)`` returns (text safe to emit, the stop
     string that matched or None); once a string has matched nothing more is emitted. ``flush()`` returns what was held
-    back when no more text will come."""
+    back when no more text will come. The decision is the one the whole text would give, however it is cut into pieces:
+    a stop string that is complete waits while another one that begins before it, or at the same place and longer, can
+    still become complete."""
 
     def __init__(self, stop_strings=()):
         stops = [s for s in stop_strings]
@@ -28,34 +30,52 @@ class StopMatcher:
         self.held = ""
         self.matched: str | None = None
 
+    def _complete(self, text: str):
+        """The earliest complete match in ``text``, the longest among those that start there: (start, stop) or None."""
+        best = None
+        for s in self.stops:
+            at = text.find(s)
+            if at >= 0 and (best is None or (at, -len(s)) < (best[0], -len(best[1]))):
+                best = (at, s)
+        return best
+
     def push(self, piece: str) -> tuple[str, str | None]:
         if self.matched is not None:
             return "", self.matched
         if not self.stops:
             return piece, None
         text = self.held + piece
-        best = None   # (start, -length, stop)
-        for s in self.stops:
-            at = text.find(s)
-            if at >= 0 and (best is None or (at, -len(s)) < best[:2]):
-                best = (at, -len(s), s)
-        if best is not None:
-            self.matched = best[2]
+        best = self._complete(text)
+        # Where the earliest stop string begins that the text's end is still inside of (a proper prefix of it reaches the
+        # end). Text from there on is held back; and a complete match is only final if no such string begins before it, or
+        # at its start and longer: that one would win once it is complete.
+        limit = len(text) if best is None else best[0] + 1
+        open_at = None
+        for i in range(max(0, len(text) - max(len(s) for s in self.stops) + 1), min(limit, len(text))):
+            rest = len(text) - i
+            if any(len(s) > rest and s.startswith(text[i:]) and (best is None or i < best[0] or len(s) > len(best[1])) for s in self.stops):
+                open_at = i
+                break
+        if best is not None and open_at is None:
+            self.matched = best[1]
             self.held = ""
             return text[: best[0]], self.matched
-        # hold back the longest tail of the text that is a proper prefix of some stop string
-        keep = 0
-        for s in self.stops:
-            for n in range(min(len(s) - 1, len(text)), keep, -1):
-                if text.endswith(s[:n]):
-                    keep = n
-                    break
-        self.held = text[len(text) - keep :] if keep else ""
-        return text[: len(text) - keep], None
+        if open_at is None:
+            self.held = ""
+            return text, None
+        self.held = text[open_at:]
+        return text[:open_at], None
 
     def flush(self) -> str:
+        """No more text will come: what was held back, up to a stop string that is complete in it (``matched`` then names it)."""
         out, self.held = self.held, ""
-        return out if self.matched is None else ""
+        if self.matched is not None:
+            return ""
+        best = self._complete(out) if self.stops else None
+        if best is not None:
+            self.matched = best[1]
+            return out[: best[0]]
+        return out
 
 
 class IncrementalDetokenizer:

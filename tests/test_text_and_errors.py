@@ -51,17 +51,52 @@ def test_stop_matcher_holds_back_partial_matches_and_prefers_the_earliest_then_l
         if matched:
             break
     # "abE" may begin END: the E waits; "ENx" is no stop: it is given out, the x waits (xy); "xEN" gives x out; ...
-    assert out == ["ab", "", "EN", "x", ""] and matched == "END"     # END is whole with "DI": the first whole match stands
-    assert m.flush() == "" and m.push("more") == ("", "END")
+    # END is whole with "DI", but ENDING, which begins at the same place and would win, is still open: it is decided with "NG!"
+    assert out == ["ab", "", "EN", "x", "", ""] and matched == "ENDING"
+    assert m.flush() == "" and m.push("more") == ("", "ENDING")
     m = StopMatcher(["ab", "abc"])
-    assert m.push("zab") == ("z", "ab")        # a whole match is taken at once, though "abc" might still have come
+    assert m.push("zab") == ("z", None)        # "abc" might still come, and at the same start the longest wins
+    assert m.push("d") == ("", "ab")           # it did not
+    m = StopMatcher(["ab", "abc"])
+    assert m.push("zab") == ("z", None) and m.flush() == "" and m.matched == "ab"      # nor when the text ends there
     m = StopMatcher(["abc", "ab"])
     assert m.push("zabc") == ("z", "abc")      # same start: the longest
+    m = StopMatcher(["abcd", "bc"])
+    assert m.push("abc") == ("", None)         # "bc" is whole, but "abcd" begins before it and is still open
+    assert m.push("d!") == ("", "abcd")
+    m = StopMatcher(["abcd", "bc"])
+    assert m.push("abc") == ("", None) and m.push("x") == ("a", "bc")
     m = StopMatcher(["stop"])
     assert m.push("no st") == ("no ", None) and m.flush() == "st"
     assert StopMatcher([]).push("anything") == ("anything", None)
     with pytest.raises(ValueError):
         StopMatcher([""])
+
+
+def test_stop_matcher_decides_as_on_the_whole_text_however_it_is_cut():
+    """Random texts over three letters, random stop strings that overlap and contain one another, random cuts: what is
+    given out is the text before the earliest match of the whole text, and the match named is the longest that begins
+    there, as if the text had come in one piece."""
+    import random
+    rng = random.Random(11)
+    for _ in range(3000):
+        stops = ["".join(rng.choice("abc") for _ in range(rng.randrange(1, 6))) for _ in range(rng.randrange(1, 5))]
+        text = "".join(rng.choice("abc" if rng.random() < 0.8 else "xyz") for _ in range(rng.randrange(1, 40)))
+        want = None
+        for s in stops:
+            at = text.find(s)
+            if at >= 0 and (want is None or (at, -len(s)) < (want[0], -len(want[1]))):
+                want = (at, s)
+        cuts = sorted(rng.sample(range(1, len(text)), min(len(text) - 1, rng.randrange(0, 8)))) if len(text) > 1 else []
+        m = StopMatcher(stops)
+        got = ""
+        for piece in (text[a:b] for a, b in zip([0] + cuts, cuts + [len(text)])):
+            emit, matched = m.push(piece)
+            got += emit
+            if matched is not None:
+                break
+        got += m.flush()
+        assert (got, m.matched) == ((text[: want[0]], want[1]) if want else (text, None)), (stops, text, cuts)
 
 
 def test_stop_matcher_never_emits_a_prefix_of_the_match_whatever_the_cut():
