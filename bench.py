@@ -9,8 +9,8 @@ that each hold ``--context`` tokens, timed on the device with CUDA events; ``e2e
 Python entry point (``RoostEngine.step``: host token ids in from pinned memory, sampled ids back to the host,
 every step). ``prefill`` is one 2,048-token prompt; ``roofline`` the decode step's bytes (every weight once and
 the live requests' cache) over its time against the measured copy bandwidth; ``points`` decode at batch 1 and
-64 at the same context and at batch 1, 8 and 64 with 1,024-token contexts (tokens a second; ``points_detail`` has each
-point's step time and roofline fraction); ``other_sizes`` the same figures at the Qwen3-0.6B and -32B layer sizes and
+64 at the same context, at batch 1, 8 and 64 with 1,024-token contexts and at batch 1 and 8 with 16,384-token contexts
+(tokens a second; ``points_detail`` has each point's step time and roofline fraction); ``other_sizes`` the same figures at the Qwen3-0.6B and -32B layer sizes and
 the 0.6B serving workload. After every timed region the kernels' status words are read: a bounded wait given up inside
 it fails the run instead of printing a fast, wrong number. Weights are seeded random values, token ids seeded uniform-random, and the contexts of the device-timed
 decode runs are filled with random keys and values instead of being prefilled (their values do not change the
@@ -360,6 +360,8 @@ def main() -> int:
     ap.add_argument("--point-batches", default="1,64", help="batch sizes of the extra decode points (the 32B configuration names 1, 8 and 32)")
     ap.add_argument("--point-contexts", default="1024", help="further context lengths of the decode points (the 8B configuration starts at 1,024)")
     ap.add_argument("--point-context-batches", default="1,8,64", help="batch sizes measured at each of --point-contexts")
+    ap.add_argument("--point-long-contexts", default="16384", help="long context lengths of the decode points, measured at --point-long-batches")
+    ap.add_argument("--point-long-batches", default="1,8", help="batch sizes at --point-long-contexts (batch 8 at 16,384 keys holds 19 GB of keys and values)")
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-other-sizes", action="store_true", help="leave out the 0.6B and 32B figures that the 8B line carries")
     args = ap.parse_args()
@@ -385,8 +387,10 @@ def main() -> int:
     pre_ms = timed_prefill(model, args.prefill_tokens)
     points, detail = {}, {}
     if not args.skip_points:
-        # the rest of the metric at these sizes: the other batches at this context, and every batch at 1,024 tokens
+        # the rest of the metric at these sizes: the other batches at this context, every batch at 1,024 tokens, and a
+        # long context, where the attention kernel's share of the step is largest
         todo = [(b, args.context) for b in _ints(args.point_batches)] + [(b, c) for c in _ints(args.point_contexts) for b in _ints(args.point_context_batches)]
+        todo += [(b, c) for c in _ints(args.point_long_contexts) for b in _ints(args.point_long_batches)]
         for b, c in todo:
             name = f"decode_b{b}" + ("" if c == args.context else f"_ctx{c}")
             p_tps, p_ms, _, _ = timed_decode(model, b, c, max(8, args.steps // 2), warmup)
